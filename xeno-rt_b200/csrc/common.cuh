@@ -1,0 +1,83 @@
+// Shared helpers of the sm_100a kernels: dtype codes, conversions, status codes, reductions.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// dtype codes, the same integers as DType.code on the Python side
+#define XRT_F32 0
+#define XRT_BF16 1
+
+// Tokens in one block of the cache; the attention kernels tile keys by it.
+#define XRT_BLOCK_TOKENS 64
+
+// Status codes returned by every launcher.  0 = launched; negative = the arguments were refused
+// before any launch; positive = a cudaError_t reported by the launch.
+#define XRT_OK 0
+#define XRT_ERR_ARGUMENT -1
+#define XRT_ERR_UNSUPPORTED -2
+
+#define XRT_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace xrt {
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a thread block with a fixed order: lanes by butterfly, then warps in index order.
+// `scratch` holds at least 33 floats of shared memory.  Every thread gets the total.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    for (int w = 0; w < n_warps; ++w) total += scratch[w];
+    scratch[32] = total;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+inline int launch_status() {
+  cudaError_t err = cudaPeekAtLastError();
+  return err == cudaSuccess ? XRT_OK : (int)err;
+}
+
+}  // namespace xrt
+
+// Dispatch on a dtype code: runs BODY with `T` bound to float or __nv_bfloat16.
+#define XRT_DISPATCH_DTYPE(code, T, ...)            \
+  do {                                              \
+    if ((code) == XRT_F32) {                        \
+      using T = float;                              \
+      __VA_ARGS__                                   \
+    } else if ((code) == XRT_BF16) {                \
+      using T = __nv_bfloat16;                      \
+      __VA_ARGS__                                   \
+    } else {                                        \
+      return XRT_ERR_UNSUPPORTED;                   \
+    }                                               \
+  } while (0)

@@ -1,0 +1,33 @@
+// Embedding gather: rows of the table to the 32-bit residual stream.
+// Restates crates/xrt-cuda/src/lib.rs:815-882 (embedding_kernel) of the reference, which writes
+// zeros for an id outside the table while its host wrapper refuses such ids (1217-1225); here the
+// kernel writes zeros and raises an error flag that the host reads.
+#include "common.cuh"
+
+namespace xrt {
+
+template <typename TW>
+__global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__ table,
+                                 const int* __restrict__ ids, int hidden, int vocab,
+                                 int* __restrict__ error_flag) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool ok = id >= 0 && id < vocab;
+  if (!ok && threadIdx.x == 0 && error_flag != nullptr) atomicExch(error_flag, 1);
+  const TW* row = table + (size_t)(ok ? id : 0) * hidden;
+  float* dst = out + (size_t)t * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = ok ? to_float(row[c]) : 0.f;
+}
+
+}  // namespace xrt
+
+XRT_EXPORT int xrt_embedding(float* out, const void* table, const int* ids, int n_tokens, int hidden,
+                             int vocab, int table_dtype, int* error_flag, cudaStream_t stream) {
+  if (n_tokens < 0 || hidden <= 0 || vocab <= 0) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  XRT_DISPATCH_DTYPE(table_dtype, TW, {
+    xrt::embedding_kernel<TW><<<n_tokens, 256, 0, stream>>>(out, (const TW*)table, ids, hidden, vocab,
+                                                          error_flag);
+  });
+  return xrt::launch_status();
+}

@@ -1,0 +1,224 @@
+"""Python bindings of the CUDA kernels: one function per exported launcher.
+
+The kernels are plain ``extern "C"`` launchers that take device pointers, sizes and a stream; the
+functions here check shapes, dtypes, contiguity and device of the torch tensors they are given,
+pass the current torch stream and turn a refusal or launch error into ``KernelError``.  There is
+no fallback: without a CUDA device or without the built library every function raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+
+import torch
+
+from ..core import KernelError
+from . import build as _build
+
+_lib = None
+_lock = threading.Lock()
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_F = ctypes.c_float
+
+_CODES = {torch.float32: 0, torch.bfloat16: 1}
+
+_SIGNATURES = {
+    "xrt_embedding": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "xrt_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
+    "xrt_swiglu": [_P, _P, _I, _I, _I, _I, _P],
+    "xrt_rope_table": [_P, _P, _P, _F, _I, _I, _P],
+    "xrt_qk_rope_kv_write": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I,
+                             _I, _I, _I, _I, _P],
+    "xrt_attention_reference": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
+    "xrt_gemm_reference": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
+    "xrt_sample": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P],
+    "xrt_mark_seen": [_P, _I, _P, _P, _I, _I, _P],
+}
+
+
+def library():
+    """The loaded kernel library; builds it first if it is missing or stale."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            path = _build.build()
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as exc:
+                raise KernelError(f"cannot load {path}: {exc}") from None
+            for name, argtypes in _SIGNATURES.items():
+                try:
+                    fn = getattr(lib, name)
+                except AttributeError:
+                    raise KernelError(f"{path} does not export {name}") from None
+                fn.argtypes = argtypes
+                fn.restype = _I
+            _lib = lib
+    return _lib
+
+
+def require_device() -> None:
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: this library runs on the GPU only and has no CPU fallback")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _code(dtype) -> int:
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} is not handled by the kernels (float32, bfloat16)") from None
+
+
+def _ptr(t, name: str, dtype=None) -> int:
+    if t is None:
+        return 0
+    if not t.is_cuda:
+        raise KernelError(f"{name} is not on a CUDA device")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} is not contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    return t.data_ptr()
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status == -1:
+        raise KernelError(f"{what}: the kernel refused its arguments")
+    if status == -2:
+        raise KernelError(f"{what}: sizes or dtypes outside what the kernel handles")
+    raise KernelError(f"{what}: CUDA launch error {status}")
+
+
+def embedding(out, table, ids, error_flag) -> None:
+    """out[t, :] = table[ids[t], :] as float32; raises error_flag[0] on an id outside the table."""
+    n, hidden = out.shape
+    vocab = table.shape[0]
+    if table.shape[1] != hidden or ids.numel() != n:
+        raise KernelError("embedding: shapes do not fit")
+    _check(library().xrt_embedding(_ptr(out, "out", torch.float32), _ptr(table, "table"),
+                                   _ptr(ids, "ids", torch.int32), n, hidden, vocab, _code(table.dtype),
+                                   _ptr(error_flag, "error_flag", torch.int32), _stream()), "embedding")
+
+
+def rmsnorm(out, x, weight, eps: float, rows=None) -> None:
+    """out[r] = rmsnorm(x[rows[r]] if rows is given else x[r]) * weight; x is float32."""
+    n_rows, width = out.shape
+    if x.shape[1] != width or weight.numel() != width or (rows is None and x.shape[0] != n_rows):
+        raise KernelError("rmsnorm: shapes do not fit")
+    if rows is not None and rows.numel() != n_rows:
+        raise KernelError("rmsnorm: one row index per output row is needed")
+    _check(library().xrt_rmsnorm(_ptr(out, "out"), _ptr(x, "x", torch.float32), _ptr(weight, "weight"),
+                                 _ptr(rows, "rows", torch.int32), n_rows, width, float(eps),
+                                 _code(weight.dtype), _code(out.dtype), _stream()), "rmsnorm")
+
+
+def swiglu(out, gate_up) -> None:
+    """out[t, f] = silu(gate_up[t, f]) * gate_up[t, F + f]."""
+    n, width = out.shape
+    if gate_up.shape[0] != n or gate_up.shape[1] != 2 * width:
+        raise KernelError("swiglu: shapes do not fit")
+    _check(library().xrt_swiglu(_ptr(out, "out"), _ptr(gate_up, "gate_up"), n, width, _code(gate_up.dtype),
+                                _code(out.dtype), _stream()), "swiglu")
+
+
+def rope_table(cos_sin, positions, freq, scale: float) -> None:
+    """cos_sin[t, i] = (cos, sin)(positions[t] * scale / freq[i]); cos_sin is float32 [T, half, 2]."""
+    n, half = cos_sin.shape[0], cos_sin.shape[1]
+    if positions.numel() != n or freq.numel() != half or cos_sin.shape[2] != 2:
+        raise KernelError("rope_table: shapes do not fit")
+    _check(library().xrt_rope_table(_ptr(cos_sin, "cos_sin", torch.float32),
+                                    _ptr(positions, "positions", torch.int32), _ptr(freq, "freq", torch.float32),
+                                    float(scale), n, half, _stream()), "rope_table")
+
+
+def qk_rope_kv_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, q_norm_w, k_norm_w, eps: float,
+                     cos_sin, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int, head_dim: int,
+                     write_kv: bool = True) -> None:
+    """Head norms, rotation, q output and cache write in one kernel; see rotary_kv.cu."""
+    n = qkv.shape[0]
+    rope_half = 0 if cos_sin is None else cos_sin.shape[1]
+    if q_out.shape != (n, n_heads * head_dim) or tok_slot.numel() != n or tok_pos.numel() != n:
+        raise KernelError("qk_rope_kv_write: shapes do not fit")
+    if write_kv:
+        for pool in (k_pool, v_pool):
+            if pool.dim() != 4 or pool.shape[1] != n_kv_heads or pool.shape[2] != 64 or pool.shape[3] != head_dim:
+                raise KernelError("qk_rope_kv_write: the cache pool must be [blocks, kv heads, 64, head_dim]")
+        if qkv.shape[1] < v_offset + n_kv_heads * head_dim:
+            raise KernelError("qk_rope_kv_write: the q/k/v row is too short")
+    norm_dtype = q_norm_w.dtype if q_norm_w is not None else torch.float32
+    cache_dtype = k_pool.dtype if write_kv else q_out.dtype
+    _check(library().xrt_qk_rope_kv_write(
+        _ptr(q_out, "q_out"), _ptr(k_pool if write_kv else None, "k_pool"),
+        _ptr(v_pool if write_kv else None, "v_pool"), _ptr(qkv, "qkv", torch.float32), qkv.shape[1], k_offset,
+        v_offset, _ptr(q_norm_w, "q_norm_w"), _ptr(k_norm_w, "k_norm_w"), float(eps),
+        _ptr(cos_sin, "cos_sin", torch.float32), rope_half, _ptr(tok_slot, "tok_slot", torch.int32),
+        _ptr(tok_pos, "tok_pos", torch.int32), _ptr(block_table, "block_table", torch.int32),
+        block_table.shape[1], n, n_heads, n_kv_heads, head_dim, 1 if write_kv else 0, _code(norm_dtype),
+        _code(q_out.dtype), _code(cache_dtype), _stream()), "qk_rope_kv_write")
+
+
+def attention_reference(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int,
+                        head_dim: int, scale: float, window: int = 0) -> None:
+    """Causal GQA attention over the cache, one warp per (token, head); any dtype."""
+    n = q.shape[0]
+    if q.shape != (n, n_heads * head_dim) or out.shape != q.shape:
+        raise KernelError("attention_reference: shapes do not fit")
+    if k_pool.shape != v_pool.shape or k_pool.shape[1:] != (n_kv_heads, 64, head_dim):
+        raise KernelError("attention_reference: the cache pool must be [blocks, kv heads, 64, head_dim]")
+    _check(library().xrt_attention_reference(
+        _ptr(out, "out"), _ptr(q, "q"), _ptr(k_pool, "k_pool"), _ptr(v_pool, "v_pool", k_pool.dtype),
+        _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
+        _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
+        float(scale), int(window), _code(q.dtype), _code(k_pool.dtype), _code(out.dtype), _stream()),
+        "attention_reference")
+
+
+def gemm_reference(out, x, w, accumulate: bool = False) -> None:
+    """out = x . w^T (or out += x . w^T into a float32 out) with 32-bit fused multiply-adds."""
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape != (m, n):
+        raise KernelError(f"gemm: shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm: rows must be contiguous")
+    if not x.is_cuda or not out.is_cuda:
+        raise KernelError("gemm: operands must be on a CUDA device")
+    _check(library().xrt_gemm_reference(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0),
+                                        out.stride(0), _code(x.dtype), _code(w.dtype), _code(out.dtype),
+                                        1 if accumulate else 0, _stream()), "gemm_reference")
+
+
+def fill_normal(out, key: int, mean: float, std: float) -> None:
+    """Fills ``out`` with the seeded normal stream ``key`` (see weights/random_init.py)."""
+    _check(library().xrt_fill_normal(_ptr(out, "out"), out.numel(), key & ((1 << 64) - 1), float(mean),
+                                     float(std), _code(out.dtype), _stream()), "fill_normal")
+
+
+def sample(out_ids, logits, row_slot, temperature, top_k, top_p, penalty, seen, rng_key, rng_counter) -> None:
+    """One token id per row of float32 logits; see sampling.cu for the conventions."""
+    n, vocab = logits.shape
+    seen_words = 0 if seen is None else seen.shape[1]
+    _check(library().xrt_sample(
+        _ptr(out_ids, "out_ids", torch.int32), _ptr(logits, "logits", torch.float32), n, vocab,
+        _ptr(row_slot, "row_slot", torch.int32), _ptr(temperature, "temperature", torch.float32),
+        _ptr(top_k, "top_k", torch.int32), _ptr(top_p, "top_p", torch.float32),
+        _ptr(penalty, "penalty", torch.float32), _ptr(seen, "seen", torch.int32), seen_words,
+        _ptr(rng_key, "rng_key", torch.int64), _ptr(rng_counter, "rng_counter", torch.int32), _stream()), "sample")
+
+
+def mark_seen(seen, slots, ids, vocab: int) -> None:
+    """Sets the bit of ids[i] in the bitmap of slots[i]."""
+    n = ids.numel()
+    _check(library().xrt_mark_seen(_ptr(seen, "seen", torch.int32), seen.shape[1],
+                                   _ptr(slots, "slots", torch.int32), _ptr(ids, "ids", torch.int32), n, vocab,
+                                   _stream()), "mark_seen")

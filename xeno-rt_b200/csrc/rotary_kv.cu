@@ -1,0 +1,162 @@
+// Rotation tables, and the fused step between the q/k/v product and attention:
+// optional per-head RMSNorm of q and k, rotation of q and k, q written for the attention kernel
+// and k, v written into the cache blocks of each token's sequence.
+//
+// Formulas of the reference:
+//   angle = pos * scale / base^(2i/rope_dim), in 32-bit   crates/xrt-kernels/src/cpu/rope.rs:59-68
+//   h[i]      = x0 * cos - x1 * sin                        crates/xrt-kernels/src/cpu/rope.rs:19-35
+//   h[i+half] = x0 * sin + x1 * cos      (x0 = h[i], x1 = h[i + half]; split-half pairing)
+//   head norm = RMSNorm over each head slice, one weight   crates/xrt-models/src/llama.rs:1025-1040
+//   order     = projection, head norm, rotation, cache     crates/xrt-models/src/llama.rs:488-503
+#include "common.cuh"
+
+namespace xrt {
+
+// cos_sin[t, i] = (cos, sin) of pos[t] * scale / freq[i]; freq is the divisor table base^(2i/rd).
+__global__ void rope_table_kernel(float2* __restrict__ cos_sin, const int* __restrict__ pos,
+                                  const float* __restrict__ freq, float scale, int n_tokens, int half) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_tokens * half) return;
+  const int t = i / half, p = i - t * half;
+  const float angle = __fdiv_rn(__fmul_rn((float)pos[t], scale), freq[p]);
+  float s, c;
+  sincosf(angle, &s, &c);
+  cos_sin[i] = make_float2(c, s);
+}
+
+// One warp per (token, head) among [q heads | k heads | v heads].  MAX_PER_LANE * 32 >= head_dim.
+template <typename TN, typename TQ, typename TC, int MAX_PER_LANE>
+__global__ void qk_rope_kv_write_kernel(
+    TQ* __restrict__ q_out, TC* __restrict__ k_pool, TC* __restrict__ v_pool,
+    const float* __restrict__ qkv, int row_stride, int k_offset, int v_offset,
+    const TN* __restrict__ q_norm_w, const TN* __restrict__ k_norm_w, float eps,
+    const float2* __restrict__ cos_sin, int rope_half,
+    const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
+    const int* __restrict__ block_table, int max_blocks,
+    int n_heads, int n_kv_heads, int head_dim, int write_kv) {
+  extern __shared__ float staged[];  // [warps][head_dim]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int head_slot = blockIdx.y * (blockDim.x >> 5) + warp;
+  const int n_slots = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+  if (head_slot >= n_slots) return;
+  const int slot = tok_slot[t];
+  const int pos = tok_pos[t];
+
+  // which of q / k / v, and which head of it
+  int kind, head;
+  if (head_slot < n_heads) { kind = 0; head = head_slot; }
+  else if (head_slot < n_heads + n_kv_heads) { kind = 1; head = head_slot - n_heads; }
+  else { kind = 2; head = head_slot - n_heads - n_kv_heads; }
+
+  if (slot < 0) {  // a padding row: q is zeroed, the cache is not touched
+    if (kind == 0)
+      for (int d = lane; d < head_dim; d += 32)
+        q_out[(size_t)t * n_heads * head_dim + head * head_dim + d] = from_float<TQ>(0.f);
+    return;
+  }
+
+  const float* src = qkv + (size_t)t * row_stride +
+                     (kind == 0 ? 0 : (kind == 1 ? k_offset : v_offset)) + head * head_dim;
+  float v[MAX_PER_LANE];
+  float sq = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAX_PER_LANE; ++j) {
+    const int d = lane + 32 * j;
+    v[j] = d < head_dim ? src[d] : 0.f;
+    sq = fmaf(v[j], v[j], sq);
+  }
+  const TN* norm_w = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+  if (norm_w != nullptr) {
+    const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)head_dim + eps);
+#pragma unroll
+    for (int j = 0; j < MAX_PER_LANE; ++j) {
+      const int d = lane + 32 * j;
+      if (d < head_dim) v[j] = (v[j] * inv) * to_float(norm_w[d]);
+    }
+  }
+
+  float* mine = staged + warp * head_dim;
+  if (kind != 2 && rope_half > 0) {
+#pragma unroll
+    for (int j = 0; j < MAX_PER_LANE; ++j) {
+      const int d = lane + 32 * j;
+      if (d < head_dim) mine[d] = v[j];
+    }
+    __syncwarp();
+    const float2* cs = cos_sin + (size_t)t * rope_half;
+#pragma unroll
+    for (int j = 0; j < MAX_PER_LANE; ++j) {
+      const int d = lane + 32 * j;
+      if (d < rope_half) {
+        const float2 a = cs[d];
+        v[j] = mine[d] * a.x - mine[d + rope_half] * a.y;
+      } else if (d < 2 * rope_half) {
+        const float2 a = cs[d - rope_half];
+        v[j] = mine[d - rope_half] * a.y + mine[d] * a.x;
+      }
+    }
+  }
+
+  if (kind == 0) {
+    TQ* dst = q_out + (size_t)t * n_heads * head_dim + head * head_dim;
+#pragma unroll
+    for (int j = 0; j < MAX_PER_LANE; ++j) {
+      const int d = lane + 32 * j;
+      if (d < head_dim) dst[d] = from_float<TQ>(v[j]);
+    }
+  } else {
+    const int block = block_table[(size_t)slot * max_blocks + pos / XRT_BLOCK_TOKENS];
+    if (block < 0) return;  // the host reserves blocks before the step; nothing to write into
+    TC* pool = kind == 1 ? k_pool : v_pool;
+    TC* dst = pool + (((size_t)block * n_kv_heads + head) * XRT_BLOCK_TOKENS + pos % XRT_BLOCK_TOKENS) * head_dim;
+#pragma unroll
+    for (int j = 0; j < MAX_PER_LANE; ++j) {
+      const int d = lane + 32 * j;
+      if (d < head_dim) dst[d] = from_float<TC>(v[j]);
+    }
+  }
+}
+
+}  // namespace xrt
+
+XRT_EXPORT int xrt_rope_table(float* cos_sin, const int* pos, const float* freq, float scale, int n_tokens,
+                              int half, cudaStream_t stream) {
+  if (n_tokens < 0 || half < 0) return XRT_ERR_ARGUMENT;
+  const int total = n_tokens * half;
+  if (total == 0) return XRT_OK;
+  xrt::rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>((float2*)cos_sin, pos, freq, scale,
+                                                                  n_tokens, half);
+  return xrt::launch_status();
+}
+
+// qkv: 32-bit rows of `row_stride` floats holding q at 0, k at k_offset, v at v_offset.
+// q_out: [n_tokens, n_heads * head_dim] in q_dtype.  k_pool / v_pool: the cache blocks of this
+// layer, [n_blocks, n_kv_heads, 64, head_dim] in cache_dtype.  Norm weights may be null (no head
+// norm) and share norm_dtype.  write_kv = 0 leaves the cache alone (a layer reading another's).
+XRT_EXPORT int xrt_qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, const float* qkv, int row_stride,
+                                    int k_offset, int v_offset, const void* q_norm_w, const void* k_norm_w,
+                                    float eps, const float* cos_sin, int rope_half, const int* tok_slot,
+                                    const int* tok_pos, const int* block_table, int max_blocks, int n_tokens,
+                                    int n_heads, int n_kv_heads, int head_dim, int write_kv, int norm_dtype,
+                                    int q_dtype, int cache_dtype, cudaStream_t stream) {
+  if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0) return XRT_ERR_ARGUMENT;
+  if (head_dim > 256 || 2 * rope_half > head_dim) return XRT_ERR_UNSUPPORTED;
+  if ((q_norm_w == nullptr) != (k_norm_w == nullptr)) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  const int warps = 4;
+  const int n_slots = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+  dim3 grid(n_tokens, (n_slots + warps - 1) / warps);
+  const size_t smem = (size_t)warps * head_dim * sizeof(float);
+  XRT_DISPATCH_DTYPE(norm_dtype, TN, {
+    XRT_DISPATCH_DTYPE(q_dtype, TQ, {
+      XRT_DISPATCH_DTYPE(cache_dtype, TC, {
+        xrt::qk_rope_kv_write_kernel<TN, TQ, TC, 8><<<grid, warps * 32, smem, stream>>>(
+            (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, qkv, row_stride, k_offset, v_offset, (const TN*)q_norm_w,
+            (const TN*)k_norm_w, eps, (const float2*)cos_sin, rope_half, tok_slot, tok_pos, block_table,
+            max_blocks, n_heads, n_kv_heads, head_dim, write_kv);
+      });
+    });
+  });
+  return xrt::launch_status();
+}

@@ -1,0 +1,38 @@
+"""What a step hands to every part: the tokens of the step as flat device arrays."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..core import DType
+
+
+@dataclass
+class StepContext:
+    """The tokens of one step, all sequences laid end to end (T tokens of n sequences).
+
+    Device tensors (int32): ``token_ids`` [T]; ``tok_pos`` [T] absolute position of each token in
+    its sequence; ``tok_slot`` [T] cache slot of each token (-1 marks a padding row, which every
+    kernel skips); ``cu_seqlens`` [n + 1] where each sequence's tokens begin; ``seq_slot`` [n];
+    ``seq_start`` [n] length of each sequence before this step.
+    Host values: ``new_lens`` tokens each sequence brings; ``starts``; ``all_single`` every
+    sequence brings exactly one token (a decode step); ``max_new`` and ``max_context`` the
+    largest new-token count and the largest length after the step.
+    ``shared`` holds what parts compute once per step and share across layers (rotation tables).
+    """
+    n_tokens: int
+    n_seqs: int
+    token_ids: torch.Tensor
+    tok_pos: torch.Tensor
+    tok_slot: torch.Tensor
+    cu_seqlens: torch.Tensor
+    seq_slot: torch.Tensor
+    seq_start: torch.Tensor
+    new_lens: list
+    starts: list
+    all_single: bool
+    max_new: int
+    max_context: int
+    dtype: DType
+    shared: dict = field(default_factory=dict)

@@ -1,0 +1,37 @@
+"""SwiGLU feed-forward: down( silu(gate(h)) * up(h) ), added to the residual
+(crates/xrt-models/src/llama.rs:584-601; crates/xrt-kernels/src/cpu/silu.rs:1-3, 22-24)."""
+from __future__ import annotations
+
+import torch
+
+from ..core import DType, torch_dtype
+from ..csrc import ops
+from .linear import linear
+from .registry import register_part
+
+
+class SwiGLUFeedForward:
+    """params: ``width``, ``inner`` (the feed-forward width).
+    weights: ``gate``, ``up`` [inner, width], ``down`` [width, inner]."""
+
+    @classmethod
+    def weight_shapes(cls, params):
+        d, f = params["width"], params["inner"]
+        return {"gate": ((f, d), "matrix"), "up": ((f, d), "matrix"), "down": ((d, f), "matrix")}
+
+    def __init__(self, params, weights, dtype: DType, device):
+        self.width = int(params["width"])
+        self.inner = int(params["inner"])
+        # one fused weight [2 * inner, width]: gate rows, then up rows
+        self.w_gate_up = torch.cat([weights["gate"], weights["up"]], dim=0).contiguous()
+        self.w_down = weights["down"]
+        self.act_dtype = torch_dtype(dtype)
+
+    def forward(self, h, residual, ctx):
+        gate_up = linear(h, self.w_gate_up, out_dtype=torch.float32)
+        act = torch.empty((h.shape[0], self.inner), dtype=self.act_dtype, device=h.device)
+        ops.swiglu(act, gate_up)
+        linear(act, self.w_down, accumulate_into=residual)
+
+
+register_part("feed_forward", "swiglu", SwiGLUFeedForward)
