@@ -1,0 +1,145 @@
+"""The cache's host side: no slot or block lost, held twice or freed twice (no GPU)."""
+import random
+
+import pytest
+
+import xeno_rt_b200  # noqa: F401
+from xeno_rt_b200.cache import BlockAllocator, Cache, KVNeed, SlotAllocator, StateNeed
+from xeno_rt_b200.core import CacheError, DType
+
+
+def test_block_allocator_books_balance():
+    a = BlockAllocator(8)
+    first = a.take(3)
+    assert first == [0, 1, 2] and a.free == 5 and a.held == 3
+    second = a.take(5)
+    assert sorted(first + second) == list(range(8))
+    with pytest.raises(CacheError, match="full"):
+        a.take(1)
+    a.give_back([1])
+    with pytest.raises(CacheError, match="twice"):
+        a.give_back([1])
+    with pytest.raises(CacheError, match="does not exist"):
+        a.give_back([8])
+    assert a.take(1) == [1]  # what was given back is used again first
+    a.check()
+
+
+def test_slot_allocator():
+    s = SlotAllocator(2)
+    a, b = s.open(), s.open()
+    assert {a, b} == {0, 1}
+    with pytest.raises(CacheError, match="no free slot"):
+        s.open()
+    s.close(a)
+    with pytest.raises(CacheError, match="not open"):
+        s.close(a)
+    assert s.open() == a
+    s.check()
+
+
+def _cache(max_tokens=64 * 6, max_positions=256, needs=None, max_slots=None):
+    needs = needs if needs is not None else [KVNeed(2, 16), KVNeed(2, 16)]
+    return Cache(needs, max_tokens, max_positions, DType.F32, "cpu", max_slots)
+
+
+def test_reserve_advance_close():
+    c = _cache()
+    assert c.n_blocks == 6 and c.blocks_per_seq == 4 and len(c.kv_groups) == 1
+    s = c.open_slot()
+    assert c.reserve(s, 70) == 0  # two blocks
+    assert c.blocks_free() == 4 and c.length(s) == 0
+    c.advance(s, 70)
+    assert c.reserve(s, 1) == 70 and c.blocks_free() == 4  # position 70 is inside the second block
+    c.advance(s, 1)
+    c.advance(s, 57)  # up to 128, still the two blocks
+    with pytest.raises(CacheError, match="passes what was reserved"):
+        c.advance(s, 1)
+    assert c.reserve(s, 1) == 128 and c.blocks_free() == 3
+    c.check()
+    c.close_slot(s)
+    assert c.blocks_free() == 6
+    with pytest.raises(CacheError, match="not open"):
+        c.close_slot(s)
+    with pytest.raises(CacheError, match="not open"):
+        c.length(s)
+    c.check()
+
+
+def test_limits():
+    c = _cache(max_tokens=64 * 3, max_positions=100)
+    a, b = c.open_slot(), c.open_slot()
+    with pytest.raises(CacheError, match="positions"):
+        c.reserve(a, 101)
+    c.reserve(a, 100)
+    c.reserve(b, 64)
+    with pytest.raises(CacheError, match="full"):
+        c.reserve(b, 65)
+    with pytest.raises(CacheError, match="at least one token"):
+        c.reserve(b, 0)
+    c.check()
+
+
+def test_blocks_are_used_again_and_tables_follow():
+    c = _cache()
+    a = c.open_slot()
+    c.reserve(a, 128)
+    c.advance(a, 128)
+    blocks_a = list(c.kv_groups[0].table_host[a, :2])
+    c.flush_tables()
+    assert c.kv_groups[0].table[a, :2].tolist() == blocks_a
+    c.close_slot(a)
+    b = c.open_slot()
+    assert b == a
+    c.reserve(b, 10)
+    assert c.kv_groups[0].table_host[b, 0] == min(blocks_a)
+    c.flush_tables()
+    assert c.kv_groups[0].table[b].tolist()[1:] == [-1] * (c.blocks_per_seq - 1)
+    c.check()
+
+
+def test_groups_have_storage_of_their_own_and_state_is_zeroed():
+    needs = [KVNeed(2, 16), KVNeed(2, 16, window=32), None, StateNeed((3, 5)), KVNeed(2, 16)]
+    c = _cache(needs=needs)
+    assert len(c.kv_groups) == 2 and len(c.state_groups) == 1
+    full, windowed = c.store(0), c.store(1)
+    assert full.k.data_ptr() != windowed.k.data_ptr() and full.block_table is not windowed.block_table
+    assert c.store(4).k.shape == full.k.shape and c.store(4).k.data_ptr() != full.k.data_ptr()
+    assert c.store(2) is None
+    state = c.store(3).state
+    assert tuple(state.shape) == (c.max_slots, 3, 5)
+    extra = c.register_sequence_state("t.x", (2,), state.dtype)
+    s = c.open_slot()
+    state[s] += 1
+    extra[s] += 1
+    c.close_slot(s)
+    assert c.open_slot() == s and float(state[s].abs().sum()) == 0.0 and float(extra[s].abs().sum()) == 0.0
+
+
+def test_random_traffic_never_loses_or_doubles_a_block():
+    rng = random.Random(3)
+    c = _cache(max_tokens=64 * 20, max_positions=640, max_slots=6)
+    live = {}
+    for _ in range(400):
+        op = rng.random()
+        if op < 0.3 and c.slots.free:
+            live[c.open_slot()] = 0
+        elif op < 0.8 and live:
+            s = rng.choice(list(live))
+            n = rng.randint(1, 90)
+            try:
+                c.reserve(s, n)
+                c.advance(s, n)
+                live[s] += n
+            except CacheError:
+                pass
+        elif live:
+            s = rng.choice(list(live))
+            c.close_slot(s)
+            del live[s]
+        c.check()
+        for s, n in live.items():
+            assert c.length(s) == n
+    for s in list(live):
+        c.close_slot(s)
+    assert c.blocks_free() == 20 and c.slots.free == 6

@@ -1,0 +1,236 @@
+"""Each CUDA kernel alone against a plain float64 reference of the same operation, at sizes other
+than the tiny models': widths that are no power of two, head sizes 16..256, odd head counts."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import model as pm
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def ops():
+    from xeno_rt_b200.csrc import ops as o
+    return o
+
+
+def rel(got, want):
+    got = got.detach().double().cpu().numpy() if isinstance(got, torch.Tensor) else got
+    return float(np.abs(got - want).max() / max(np.abs(want).max(), 1e-30))
+
+
+def f64(t):
+    return t.detach().double().cpu().numpy()
+
+
+@pytest.mark.parametrize("table_dtype", ["float32", "bfloat16"])
+def test_embedding(table_dtype):
+    table = torch.randn(203, 100, device=DEV).to(DT[table_dtype])
+    ids = torch.tensor([0, 202, 5, 5, 100], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 100, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().embedding(out, table, ids, flag)
+    assert torch.equal(out, table[ids.long()].float()) and int(flag) == 0
+    bad = torch.tensor([1, 203], dtype=torch.int32, device=DEV)
+    out2 = torch.ones(2, 100, device=DEV)
+    ops().embedding(out2, table, bad, flag)
+    assert int(flag) == 1 and float(out2[1].abs().sum()) == 0.0 and torch.equal(out2[0], table[1].float())
+
+
+@pytest.mark.parametrize("width", [1, 7, 100, 4100])
+@pytest.mark.parametrize("out_dtype,w_dtype", [("float32", "float32"), ("bfloat16", "bfloat16"), ("bfloat16", "float32")])
+def test_rmsnorm(width, out_dtype, w_dtype):
+    x = torch.randn(9, width, device=DEV) * 3
+    w = (1 + 0.1 * torch.randn(width, device=DEV)).to(DT[w_dtype])
+    out = torch.empty(9, width, device=DEV, dtype=DT[out_dtype])
+    ops().rmsnorm(out, x, w, 3e-6)
+    want = pm.rmsnorm(f64(x), f64(w), 3e-6)
+    assert rel(out, want) < (1e-6 if out_dtype == "float32" else 5e-3)
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    gathered = torch.empty(3, width, device=DEV, dtype=DT[out_dtype])
+    ops().rmsnorm(gathered, x, w, 3e-6, rows)
+    assert torch.equal(gathered, out[rows.long()])
+
+
+def test_swiglu():
+    gu = torch.randn(5, 2 * 136, device=DEV) * 4
+    out = torch.empty(5, 136, device=DEV)
+    ops().swiglu(out, gu)
+    assert rel(out, pm.swiglu(f64(gu[:, :136]), f64(gu[:, 136:]))) < 1e-6
+    out_b = torch.empty(5, 136, device=DEV, dtype=torch.bfloat16)
+    ops().swiglu(out_b, gu)
+    assert rel(out_b, pm.swiglu(f64(gu[:, :136]), f64(gu[:, 136:]))) < 5e-3
+
+
+@pytest.mark.parametrize("half,base,scale", [(8, 10000.0, 1.0), (24, 1e6, 1.0), (64, 500000.0, 0.5)])
+def test_rope_table(half, base, scale):
+    pos = torch.tensor([0, 1, 17, 4095, 100000], dtype=torch.int32, device=DEV)
+    freq = torch.from_numpy(pm.rope_frequencies(2 * half, base)).to(DEV)
+    table = torch.empty(5, half, 2, device=DEV)
+    ops().rope_table(table, pos, freq, scale)
+    angle = (pos.cpu().numpy().astype(np.float32)[:, None] * np.float32(scale) / freq.cpu().numpy()[None]).astype(np.float32)
+    assert np.abs(f64(table[..., 0]) - np.cos(angle.astype(np.float64))).max() < 2e-7
+    assert np.abs(f64(table[..., 1]) - np.sin(angle.astype(np.float64))).max() < 2e-7
+
+
+def _cache_for(seq_lens, n_kv, hd, dtype, shuffle_seed=0):
+    """Pools and a block table whose blocks are deliberately out of order."""
+    blocks_per = [(n + 63) // 64 for n in seq_lens]
+    total = sum(blocks_per) + 3
+    perm = np.random.default_rng(shuffle_seed).permutation(total)
+    table = np.full((len(seq_lens) + 1, max(blocks_per)), -1, dtype=np.int32)
+    at = 0
+    for s, n in enumerate(blocks_per):
+        table[s + 1, :n] = perm[at:at + n]  # slot s + 1 holds sequence s; slot 0 stays empty
+        at += n
+    k = torch.zeros(total, n_kv, 64, hd, device=DEV, dtype=dtype)
+    v = torch.zeros_like(k)
+    return k, v, torch.from_numpy(table).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,rope_dim,qk_norm", [(5, 1, 48, 48, True), (4, 2, 16, 16, False),
+                                                        (3, 3, 256, 64, True), (8, 2, 80, 80, False)])
+def test_qk_rope_kv_write(dtype, nh, nkv, hd, rope_dim, qk_norm):
+    seq_lens = [70, 3]
+    starts = [60, 0]  # the first sequence continues at position 60 and crosses a block edge
+    new = [10, 3]
+    T = sum(new)
+    qw, kw = nh * hd, nkv * hd
+    qkv = torch.randn(T, qw + 2 * kw, device=DEV)
+    tok_pos = torch.tensor([starts[0] + i for i in range(new[0])] + list(range(new[1])), dtype=torch.int32, device=DEV)
+    tok_slot = torch.tensor([1] * new[0] + [2] * new[1], dtype=torch.int32, device=DEV)
+    k_pool, v_pool, table = _cache_for(seq_lens, nkv, hd, DT[dtype])
+    qn = (1 + 0.1 * torch.randn(hd, device=DEV)) if qk_norm else None
+    kn = (1 + 0.1 * torch.randn(hd, device=DEV)) if qk_norm else None
+    freq = torch.from_numpy(pm.rope_frequencies(rope_dim, 10000.0)).to(DEV)
+    cs = torch.empty(T, rope_dim // 2, 2, device=DEV)
+    ops().rope_table(cs, tok_pos, freq, 1.0)
+    q_out = torch.empty(T, qw, device=DEV, dtype=DT[dtype])
+    ops().qk_rope_kv_write(q_out, k_pool, v_pool, qkv, qw, qw + kw, qn, kn, 1e-6, cs, tok_slot, tok_pos, table,
+                           nh, nkv, hd)
+    q, k, v = f64(qkv[:, :qw]), f64(qkv[:, qw:qw + kw]), f64(qkv[:, qw + kw:])
+    if qk_norm:
+        q = pm.head_rmsnorm(q, f64(qn), nh, hd, 1e-6)
+        k = pm.head_rmsnorm(k, f64(kn), nkv, hd, 1e-6)
+    pos = tok_pos.cpu().numpy()
+    q = pm.rope(q, pos, nh, hd, rope_dim, 10000.0, 1.0)
+    k = pm.rope(k, pos, nkv, hd, rope_dim, 10000.0, 1.0)
+    tol = 2e-6 if dtype == "float32" else 5e-3
+    assert rel(q_out, q) < tol
+    tab = table.cpu().numpy()
+    for t in range(T):
+        slot, p = int(tok_slot[t]), int(pos[t])
+        blk = tab[slot, p // 64]
+        assert rel(k_pool[blk, :, p % 64, :].reshape(-1), k[t]) < tol
+        assert rel(v_pool[blk, :, p % 64, :].reshape(-1), v[t]) < tol
+    # nothing else in the pools was touched
+    assert int((k_pool != 0).any(dim=-1).sum()) == T * nkv
+
+
+def _fill_cache(k_pool, v_pool, table, slot, k, v):
+    """k, v: [S, n_kv, hd] for the sequence of ``slot``."""
+    tab = table.cpu().numpy()
+    for p in range(k.shape[0]):
+        blk = tab[slot, p // 64]
+        k_pool[blk, :, p % 64, :] = k[p].to(k_pool.dtype)
+        v_pool[blk, :, p % 64, :] = v[p].to(v_pool.dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (5, 1, 48), (6, 3, 128), (2, 2, 256)])
+def test_attention_reference_kernel(dtype, nh, nkv, hd):
+    """Two sequences: one whole (130 tokens, every position a query) and one continuing at position
+    199 with a single token."""
+    torch.manual_seed(nh * hd)
+    lens = [130, 200]
+    k_pool, v_pool, table = _cache_for(lens, nkv, hd, DT[dtype], shuffle_seed=hd)
+    ks = [torch.randn(n, nkv, hd, device=DEV) for n in lens]
+    vs = [torch.randn(n, nkv, hd, device=DEV) for n in lens]
+    for s in range(2):
+        _fill_cache(k_pool, v_pool, table, s + 1, ks[s], vs[s])
+    q = torch.randn(131, nh * hd, device=DEV).to(DT[dtype])
+    tok_pos = torch.tensor(list(range(130)) + [199], dtype=torch.int32, device=DEV)
+    tok_slot = torch.tensor([1] * 130 + [2], dtype=torch.int32, device=DEV)
+    out = torch.empty_like(q)
+    ops().attention_reference(out, q, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd))
+    def cached(x):
+        return f64(x.to(DT[dtype])).reshape(x.shape[0], -1)
+    want0 = pm.causal_gqa_attention(f64(q[:130]), cached(ks[0]), cached(vs[0]), nh, nkv, hd)
+    q_last = np.zeros((200, nh * hd))
+    q_last[199] = f64(q[130])
+    want1 = pm.causal_gqa_attention(q_last, cached(ks[1]), cached(vs[1]), nh, nkv, hd)[199]
+    tol = 2e-6 if dtype == "float32" else 1e-2
+    assert rel(out[:130], want0) < tol
+    assert rel(out[130], want1) < tol
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_a_far_key_and_respects_the_window(dtype):
+    """One key among 700 is made to stand out; the result must be that key's value.  With a window
+    that excludes it, it must not be."""
+    nh, nkv, hd, S = 4, 2, 64, 700
+    k_pool, v_pool, table = _cache_for([S], nkv, hd, DT[dtype], shuffle_seed=1)
+    k = torch.randn(S, nkv, hd, device=DEV) * 0.1
+    v = torch.randn(S, nkv, hd, device=DEV)
+    q = torch.randn(1, nh, hd, device=DEV) * 0.1
+    far = 13  # in the first block, 686 positions back
+    k[far, 1] = q[0, 3] * 400  # head 3 reads kv head 1
+    _fill_cache(k_pool, v_pool, table, 1, k, v)
+    qf = q.reshape(1, nh * hd).to(DT[dtype])
+    tok_pos = torch.tensor([S - 1], dtype=torch.int32, device=DEV)
+    tok_slot = torch.tensor([1], dtype=torch.int32, device=DEV)
+    out = torch.empty_like(qf)
+    ops().attention_reference(out, qf, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd))
+    got = out.float().reshape(nh, hd)
+    assert torch.allclose(got[3], v[far, 1].to(DT[dtype]).float(), atol=2e-2)
+    assert not torch.allclose(got[2], v[far, 1].to(DT[dtype]).float(), atol=0.2)
+    ops().attention_reference(out, qf, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd),
+                              window=S - far - 1)  # keys far+1 .. S-1: the far key is just outside
+    assert not torch.allclose(out.float().reshape(nh, hd)[3], v[far, 1].float(), atol=0.2)
+    ops().attention_reference(out, qf, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd),
+                              window=S - far)  # the far key is the window's first
+    assert torch.allclose(out.float().reshape(nh, hd)[3], v[far, 1].to(DT[dtype]).float(), atol=2e-2)
+
+
+@pytest.mark.parametrize("xd,wd,od", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "float32"),
+                                      ("bfloat16", "bfloat16", "bfloat16")])
+@pytest.mark.parametrize("m,n,k", [(1, 203, 100), (7, 64, 17), (130, 136, 96), (65, 320, 260)])
+def test_gemm_reference(xd, wd, od, m, n, k):
+    x = torch.randn(m, k, device=DEV).to(DT[xd])
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(DT[wd])
+    out = torch.empty(m, n, device=DEV, dtype=DT[od])
+    ops().gemm_reference(out, x, w)
+    want = f64(x) @ f64(w).T
+    assert rel(out, want) < (2e-6 if od == "float32" else 5e-3)
+    if od == "float32":
+        base = torch.randn(m, n, device=DEV)
+        acc = base.clone()
+        ops().gemm_reference(acc, x, w, accumulate=True)
+        assert rel(acc, f64(base) + want) < 2e-6
+
+
+def test_gemm_rows_do_not_depend_on_the_batch():
+    x = torch.randn(70, 100, device=DEV)
+    w = torch.randn(203, 100, device=DEV)
+    whole = torch.empty(70, 203, device=DEV)
+    ops().gemm_reference(whole, x, w)
+    one = torch.empty(1, 203, device=DEV)
+    ops().gemm_reference(one, x[69:70].contiguous(), w)
+    assert torch.equal(one[0], whole[69])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_fill_normal_matches_the_host_generator(dtype):
+    from xeno_rt_b200.weights import normal_values, tensor_key
+    key = tensor_key(3, "model.layers.0.mlp.up_proj.weight")
+    out = torch.empty(1000, 37, device=DEV, dtype=DT[dtype])
+    ops().fill_normal(out, key, 0.0, 0.02)
+    host = torch.from_numpy(normal_values(key, 37000, 0.0, 0.02)).to(DT[dtype]).reshape(1000, 37)
+    same = (out.cpu() == host).float().mean()
+    assert same > 0.999  # identical but for rare last-bit differences of log and cos
+    assert torch.allclose(out.cpu().float(), host.float(), atol=1e-4)

@@ -1,0 +1,214 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16: each request alone and
+whole; with the last 32 tokens one by one; in batches of unequal lengths whose shorter requests
+end earlier, one batch after another so that slots and blocks are used again; long decoding; the
+first tokens of a sequence; padding."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import CONFIGS, TOL, make_folder, random_prompts, scaled_error
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+LENGTHS = {"tiny-llama": [5, 9, 13, 70, 128], "tiny-qwen3": [1, 7, 16, 31, 97, 200], "tiny-odd": [3, 65, 130]}
+
+
+@pytest.fixture(scope="module")
+def setups(tmp_path_factory):
+    """For each tiny configuration: folder (sharpened weights), prompts, plain logits."""
+    from plain.files import read_model_folder
+    from plain.model import forward_logits
+    out = {}
+    root = tmp_path_factory.mktemp("models")
+    for name in CONFIGS:
+        folder = make_folder(root, name, sharpen=6.0)
+        cfg, weights = read_model_folder(folder)
+        prompts = random_prompts(cfg["vocab_size"], LENGTHS[name], seed=len(name))
+        out[name] = (folder, prompts, [forward_logits(cfg, weights, p) for p in prompts])
+    return out
+
+
+@pytest.fixture(scope="module")
+def engines(setups):
+    from xeno_rt_b200.engine import Engine, Model
+    made = {}
+
+    def get(name, dtype, max_tokens=64 * 12):
+        key = (name, dtype, max_tokens)
+        if key not in made:
+            made[key] = Engine(Model.load(setups[name][0], dtype=dtype), max_tokens=max_tokens)
+        return made[key]
+    return get
+
+
+def _whole(engine, prompt):
+    from xeno_rt_b200.engine import StepEntry
+    slot = engine.open_slot()
+    logits = engine.step([StepEntry(slot, prompt, list(range(len(prompt))))]).cpu().numpy()
+    engine.close_slot(slot)
+    return logits
+
+
+def _tail_one_by_one(engine, prompt, tail=32):
+    from xeno_rt_b200.engine import StepEntry
+    slot = engine.open_slot()
+    head = max(1, len(prompt) - tail)
+    parts = [engine.step([StepEntry(slot, prompt[:head], list(range(head)))]).cpu().numpy()]
+    for t in range(head, len(prompt)):
+        parts.append(engine.step([StepEntry(slot, [prompt[t]], [0])]).cpu().numpy())
+    engine.close_slot(slot)
+    return np.concatenate(parts)
+
+
+def _batch(engine, prompts, decode=8, pad_to=None):
+    """The prompts minus their last ``decode`` tokens in one step, then one token each; a request
+    leaves (and its slot is closed) when its tokens run out.  Returns logits for each request."""
+    from xeno_rt_b200.engine import StepEntry
+    slots = [engine.open_slot() for _ in prompts]
+    heads = [max(1, len(p) - decode) for p in prompts]
+    logits = engine.step([StepEntry(s, p[:h], list(range(h))) for s, p, h in zip(slots, prompts, heads)]).cpu().numpy()
+    outs, offset = [[] for _ in prompts], 0
+    for i, h in enumerate(heads):
+        outs[i].append(logits[offset:offset + h])
+        offset += h
+    live = list(range(len(prompts)))
+    step = 0
+    while True:
+        for i in [i for i in live if heads[i] + step >= len(prompts[i])]:
+            engine.close_slot(slots[i])
+            live.remove(i)
+        if not live:
+            break
+        entries = [StepEntry(slots[i], [prompts[i][heads[i] + step]], [0]) for i in live]
+        logits = engine.step(entries, pad_to=pad_to).cpu().numpy()
+        for row, i in enumerate(live):
+            outs[i].append(logits[row:row + 1])
+        step += 1
+    return [np.concatenate(o) for o in outs]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_each_request_alone_and_whole(setups, engines, name, dtype):
+    _, prompts, refs = setups[name]
+    engine = engines(name, dtype)
+    for p, r in zip(prompts, refs):
+        assert scaled_error(_whole(engine, p), r) < TOL[dtype], (name, dtype, len(p))
+    engine.cache.check()
+    assert engine.cache.blocks_free() == engine.cache.n_blocks
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_last_32_tokens_one_by_one(setups, engines, name, dtype):
+    _, prompts, refs = setups[name]
+    engine = engines(name, dtype)
+    for p, r in zip(prompts, refs):
+        got = _tail_one_by_one(engine, p)
+        assert scaled_error(got, r) < TOL[dtype], (name, dtype, len(p))
+        # cutting the tokens into steps changes the result by rounding only
+        assert scaled_error(got, _whole(engine, p).astype(np.float64)) < (1e-5 if dtype == "float32" else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_unequal_batches_one_after_another(setups, engines, name, dtype):
+    folder, prompts, refs = setups[name]
+    # a cache that holds one batch but not two: the second batch must reuse blocks and slots
+    need = sum((len(p) + 63) // 64 * 64 for p in prompts)
+    engine = engines(name, dtype, max_tokens=need)
+    for round_ in range(3):
+        order = list(range(len(prompts)))
+        if round_ == 1:
+            order.reverse()
+        if round_ == 2:
+            order = order[1:] + order[:1]
+        got = _batch(engine, [prompts[i] for i in order], decode=8)
+        for i, g in zip(order, got):
+            assert scaled_error(g, refs[i]) < TOL[dtype], (name, dtype, round_, len(prompts[i]))
+        engine.cache.check()
+        assert engine.cache.blocks_free() == engine.cache.n_blocks
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_padding_changes_no_result(setups, engines, dtype):
+    _, prompts, refs = setups["tiny-qwen3"]
+    engine = engines("tiny-qwen3", dtype)
+    plain_run = _batch(engine, prompts[:4], decode=6)
+    padded_run = _batch(engine, prompts[:4], decode=6, pad_to=16)
+    for a, b in zip(plain_run, padded_run):
+        assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(setups, engines, dtype):
+    """300 tokens one by one from the first token on: positions cross four block edges."""
+    from plain.files import read_model_folder
+    from plain.model import forward_logits
+    from xeno_rt_b200.engine import StepEntry
+    folder, _, _ = setups["tiny-odd"]
+    cfg, weights = read_model_folder(folder)
+    (prompt,) = random_prompts(cfg["vocab_size"], [300], seed=9)
+    ref = forward_logits(cfg, weights, prompt)
+    engine = engines("tiny-odd", dtype)
+    slot = engine.open_slot()
+    rows = [engine.step([StepEntry(slot, [t], [0])]).cpu().numpy() for t in prompt]
+    engine.close_slot(slot)
+    got = np.concatenate(rows)
+    assert scaled_error(got[:4], ref[:4]) < TOL[dtype]  # the first tokens of a sequence
+    assert scaled_error(got, ref) < TOL[dtype]
+    worst = int(np.abs(got - ref).max(axis=1).argmax())
+    assert scaled_error(got[worst:worst + 1], ref[worst:worst + 1]) < TOL[dtype], worst
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_steps_of_several_tokens_continue_a_sequence(setups, engines, dtype):
+    """Chunks of unequal size (not only prompts and single tokens) continue where the slot stands."""
+    from xeno_rt_b200.engine import StepEntry
+    _, prompts, refs = setups["tiny-qwen3"]
+    p, r = prompts[-1], refs[-1]  # 200 tokens
+    engine = engines("tiny-qwen3", dtype)
+    slot = engine.open_slot()
+    parts, at = [], 0
+    for size in (63, 1, 2, 64, 70):
+        parts.append(engine.step([StepEntry(slot, p[at:at + size], list(range(size)))]).cpu().numpy())
+        at += size
+    engine.close_slot(slot)
+    assert at == 200 and scaled_error(np.concatenate(parts), r) < TOL[dtype]
+
+
+def test_step_errors(setups, engines):
+    from xeno_rt_b200.core import CacheError, RuntimeFault
+    from xeno_rt_b200.engine import StepEntry
+    engine = engines("tiny-llama", "float32")
+    slot = engine.open_slot()
+    with pytest.raises(RuntimeFault, match="outside the vocabulary"):
+        engine.step([StepEntry(slot, [256], [0])])
+    with pytest.raises(RuntimeFault, match="at least one token"):
+        engine.step([StepEntry(slot, [], [])])
+    with pytest.raises(RuntimeFault, match="wanted place"):
+        engine.step([StepEntry(slot, [1, 2], [2])])
+    with pytest.raises(RuntimeFault, match="twice"):
+        engine.step([StepEntry(slot, [1], [0]), StepEntry(slot, [2], [0])])
+    with pytest.raises(CacheError, match="positions"):
+        engine.step([StepEntry(slot, [1] * 129, [0])])
+    assert engine.step([StepEntry(slot, [1, 2], [])]) is None
+    engine.close_slot(slot)
+    with pytest.raises(CacheError, match="not open"):
+        engine.step([StepEntry(slot, [1], [0])])
+    engine.cache.check()
+
+
+def test_random_model_on_the_device_matches_the_written_folder(tmp_path):
+    """Model.random draws on the GPU what write_random_model draws on the host."""
+    from xeno_rt_b200.engine import Engine, Model, StepEntry
+    from helpers import TINY_QWEN3
+    from xeno_rt_b200.weights import write_random_model
+    folder = write_random_model(str(tmp_path / "m"), TINY_QWEN3, seed=5, dtype="bfloat16")
+    a = Engine(Model.load(folder, dtype="bfloat16"), 128)
+    b = Engine(Model.random(TINY_QWEN3, seed=5, dtype="bfloat16"), 128)
+    prompt = list(range(40))
+    la = a.step([StepEntry(a.open_slot(), prompt, [39])])
+    lb = b.step([StepEntry(b.open_slot(), prompt, [39])])
+    assert torch.allclose(la, lb, atol=2e-3)

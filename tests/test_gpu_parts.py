@@ -1,0 +1,275 @@
+"""Each part alone against its plain function, and the generality of the assembly: a toy mixer
+with state of its own, a layer run twice, a layer reading another layer's cache."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import model as pm
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 1e-5, "bfloat16": 2e-2}
+
+
+def f64(t):
+    return t.detach().double().cpu().numpy()
+
+
+def rel(got, want):
+    return float(np.abs(f64(got) - want).max() / np.abs(want).max())
+
+
+def context_for(cache, token_lists, dtype):
+    from xeno_rt_b200.engine import StepEntry, build_context
+    slots = [cache.open_slot() for _ in token_lists]
+    ctx, _ = build_context([StepEntry(s, t) for s, t in zip(slots, token_lists)], cache, 10 ** 6, dtype, DEV)
+    cache.flush_tables()
+    return ctx, slots
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_part(dtype):
+    from xeno_rt_b200.core import parse_dtype
+    from xeno_rt_b200.parts import part_class
+    w = 1 + 0.1 * torch.randn(100, device=DEV)
+    part = part_class("norm", "rmsnorm")({"width": 100, "eps": 2e-6}, {"weight": w}, parse_dtype(dtype), DEV)
+    x = torch.randn(6, 100, device=DEV)
+    out = part.forward(x)
+    assert out.dtype == DT[dtype] and rel(out, pm.rmsnorm(f64(x), f64(w), 2e-6)) < TOL[dtype]
+    rows = torch.tensor([5, 2], dtype=torch.int32, device=DEV)
+    assert torch.equal(part.forward(x, rows), out[[5, 2]])
+
+
+def test_rotary_part_and_no_position():
+    from xeno_rt_b200.cache import Cache, KVNeed
+    from xeno_rt_b200.core import DType
+    from xeno_rt_b200.parts import part_class
+    cache = Cache([KVNeed(1, 16)], 256, 4096, DType.F32, DEV)
+    ctx, _ = context_for(cache, [[1] * 70, [2] * 3], DType.F32)
+    part = part_class("position", "rotary")({"rope_dim": 48, "base": 50000.0, "scale": 1.0}, {}, DType.F32, DEV)
+    table = part.tables(ctx)
+    assert part.tables(ctx) is table  # once a step
+    pos = ctx.tok_pos.cpu().numpy().astype(np.float32)
+    angle = (pos[:, None] / pm.rope_frequencies(48, 50000.0)[None]).astype(np.float32).astype(np.float64)
+    assert np.abs(f64(table[..., 0]) - np.cos(angle)).max() < 2e-7
+    assert part_class("position", "none")({}, {}, DType.F32, DEV).tables(ctx) is None
+
+
+def _attention_setup(dtype, nh, nkv, hd, d, qk_norm, token_lists):
+    from xeno_rt_b200.cache import Cache
+    from xeno_rt_b200.core import parse_dtype
+    from xeno_rt_b200.parts import part_class
+    dt = parse_dtype(dtype)
+    g = torch.Generator(device="cpu").manual_seed(hd + nh)
+    mk = lambda *s: (torch.randn(*s, generator=g) * 0.15).to(DEV).to(DT[dtype])
+    weights = {"q": mk(nh * hd, d), "k": mk(nkv * hd, d), "v": mk(nkv * hd, d), "o": mk(d, nh * hd)}
+    if qk_norm:
+        weights["q_norm"] = (1 + 0.1 * torch.randn(hd, generator=g)).to(DEV)
+        weights["k_norm"] = (1 + 0.1 * torch.randn(hd, generator=g)).to(DEV)
+    params = {"width": d, "n_heads": nh, "n_kv_heads": nkv, "head_dim": hd, "qk_norm": qk_norm, "eps": 1e-6,
+              "window": None, "position": {"kind": "rotary", "params": {"rope_dim": hd, "base": 10000.0, "scale": 1.0}}}
+    part = part_class("mixer", "attention")(params, weights, dt, DEV)
+    cache = Cache([part.cache_need()], 64 * 8, 1024, dt, DEV)
+    return part, cache, weights, dt
+
+
+def _plain_attention(h, weights, nh, nkv, hd, qk_norm):
+    q, k, v = pm.linear(h, f64(weights["q"])), pm.linear(h, f64(weights["k"])), pm.linear(h, f64(weights["v"]))
+    if qk_norm:
+        q = pm.head_rmsnorm(q, f64(weights["q_norm"]), nh, hd, 1e-6)
+        k = pm.head_rmsnorm(k, f64(weights["k_norm"]), nkv, hd, 1e-6)
+    pos = np.arange(h.shape[0])
+    q, k = pm.rope(q, pos, nh, hd, hd, 10000.0, 1.0), pm.rope(k, pos, nkv, hd, hd, 10000.0, 1.0)
+    return pm.linear(pm.causal_gqa_attention(q, k, v, nh, nkv, hd), f64(weights["o"]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,d,qk_norm", [(5, 1, 48, 100, True), (4, 4, 32, 72, False)])
+def test_attention_part_prompt_then_single_tokens(dtype, nh, nkv, hd, d, qk_norm):
+    from xeno_rt_b200.engine import StepEntry, build_context
+    lens = [75, 9]
+    part, cache, weights, dt = _attention_setup(dtype, nh, nkv, hd, d, qk_norm, lens)
+    hs = [torch.randn(n, d, device=DEV).to(DT[dtype]) for n in lens]
+    wants = [_plain_attention(f64(h), weights, nh, nkv, hd, qk_norm) for h in hs]
+    slots = [cache.open_slot() for _ in lens]
+    heads = [n - 4 for n in lens]
+    # the prompts' heads in one step
+    ctx, _ = build_context([StepEntry(s, [0] * k) for s, k in zip(slots, heads)], cache, 10, dt, DEV)
+    cache.flush_tables()
+    residual = torch.zeros(sum(heads), d, device=DEV)
+    part.forward(torch.cat([h[:k] for h, k in zip(hs, heads)]), residual, ctx, cache.store(0))
+    for s, k in zip(slots, heads):
+        cache.advance(s, k)
+    got = [[residual[:heads[0]]], [residual[heads[0]:]]]
+    for t in range(4):
+        ctx, _ = build_context([StepEntry(s, [0]) for s in slots], cache, 10, dt, DEV)
+        cache.flush_tables()
+        residual = torch.zeros(2, d, device=DEV)
+        part.forward(torch.cat([h[k + t:k + t + 1] for h, k in zip(hs, heads)]), residual, ctx, cache.store(0))
+        for i, s in enumerate(slots):
+            cache.advance(s, 1)
+            got[i].append(residual[i:i + 1])
+    for i in range(2):
+        assert rel(torch.cat(got[i]), wants[i]) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_feed_forward_embedding_and_head_parts(dtype):
+    from xeno_rt_b200.core import parse_dtype
+    from xeno_rt_b200.parts import part_class
+    dt = parse_dtype(dtype)
+    mk = lambda *s: (torch.randn(*s, device=DEV) * 0.2).to(DT[dtype])
+    w = {"gate": mk(136, 100), "up": mk(136, 100), "down": mk(100, 136)}
+    ffn = part_class("feed_forward", "swiglu")({"width": 100, "inner": 136}, w, dt, DEV)
+    h = torch.randn(7, 100, device=DEV).to(DT[dtype])
+    residual = torch.randn(7, 100, device=DEV)
+    want = f64(residual) + pm.linear(pm.swiglu(pm.linear(f64(h), f64(w["gate"])), pm.linear(f64(h), f64(w["up"]))),
+                                     f64(w["down"]))
+    ffn.forward(h, residual, None)
+    assert rel(residual, want) < TOL[dtype]
+    table = mk(203, 100)
+    emb = part_class("embedding", "token")({"vocab_size": 203, "width": 100}, {"weight": table}, dt, DEV)
+    ids = torch.tensor([5, 202, 0], dtype=torch.int32, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(ids, flag), table[ids.long()].float())
+    head = part_class("lm_head", "linear")({"vocab_size": 203, "width": 100}, {"weight": table}, dt, DEV)
+    logits = head.forward(h)
+    assert logits.dtype == torch.float32 and rel(logits, pm.linear(f64(h), f64(table))) < TOL[dtype]
+
+
+class RunningMeanMixer:
+    """A toy mixer with a state of its own: y_t = W . mean(h_0 .. h_t) of its sequence.  The state
+    kept for each sequence is the sum of its inputs so far (its length comes with the step)."""
+
+    @classmethod
+    def weight_shapes(cls, params):
+        return {"w": ((params["width"], params["width"]), "matrix")}
+
+    def __init__(self, params, weights, dtype, device):
+        self.width = params["width"]
+        self.w = weights["w"]
+
+    def cache_need(self):
+        from xeno_rt_b200.cache import StateNeed
+        return StateNeed((self.width,), "float32")
+
+    def forward(self, h, residual, ctx, store, owns_cache=True):
+        cu = ctx.cu_seqlens.tolist()
+        for i, slot in enumerate(ctx.seq_slot.tolist()):
+            seg = h[cu[i]:cu[i + 1]].float()
+            sums = store.state[slot] + torch.cumsum(seg, dim=0)
+            counts = torch.arange(1, seg.shape[0] + 1, device=h.device).float() + ctx.starts[i]
+            residual[cu[i]:cu[i + 1]] += (sums / counts[:, None]) @ self.w.float().T
+            store.state[slot] = sums[-1]
+
+
+def _toy_spec(schedule=None, share=False):
+    from xeno_rt_b200.parts import LayerSpec, ModelSpec, PartSpec, SchedulePlace
+    d, vocab = 40, 50
+    norm = lambda name: PartSpec("rmsnorm", {"width": d, "eps": 1e-5}, {"weight": name})
+    attn = PartSpec("attention", {"width": d, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16, "qk_norm": False,
+                                  "eps": 1e-5, "window": None,
+                                  "position": {"kind": "rotary", "params": {"rope_dim": 16, "base": 100.0, "scale": 1.0}}},
+                    {"q": "l0.q", "k": "l0.k", "v": "l0.v", "o": "l0.o"})
+    ffn = lambda i: PartSpec("swiglu", {"width": d, "inner": 24}, {"gate": f"l{i}.g", "up": f"l{i}.u", "down": f"l{i}.d"})
+    layers = [LayerSpec(norm("l0.n1"), attn, norm("l0.n2"), ffn(0)),
+              LayerSpec(norm("l1.n1"), PartSpec("test_running_mean", {"width": d}, {"w": "l1.w"}), norm("l1.n2"), ffn(1))]
+    schedule = schedule or [SchedulePlace(0), SchedulePlace(1)]
+    return ModelSpec(vocab_size=vocab, hidden_size=d, max_positions=256,
+                     embedding=PartSpec("token", {"vocab_size": vocab, "width": d}, {"weight": "emb"}),
+                     layers=layers, schedule=schedule, final_norm=norm("fn"),
+                     lm_head=PartSpec("linear", {"vocab_size": vocab, "width": d}, {"weight": "emb"}))
+
+
+def _toy_model(spec, dtype="float32"):
+    from xeno_rt_b200.core import parse_dtype
+    from xeno_rt_b200.engine import Model
+    from xeno_rt_b200.weights import random_tensors
+    dt = parse_dtype(dtype)
+    tensors = {k: v.to(DEV) for k, v in random_tensors(spec.expected_tensors(), 4, dt).items()}
+    for k in tensors:
+        if k.endswith((".q", ".k", ".w")):
+            tensors[k] = tensors[k] * 8
+    return Model(spec, tensors, dt, DEV), tensors
+
+
+def _plain_toy(tensors, schedule, tokens):
+    """The toy model restated on whole sequences with the plain functions."""
+    w = {k: f64(v) for k, v in tensors.items()}
+    x = pm.embedding(w["emb"], tokens)
+    pos = np.arange(len(tokens))
+    kv_of_place = {}
+    for i, (layer, cache_from) in enumerate(schedule):
+        h = pm.rmsnorm(x, w[f"l{layer}.n1"], 1e-5)
+        if layer == 0:
+            q = pm.rope(pm.linear(h, w["l0.q"]), pos, 2, 16, 16, 100.0, 1.0)
+            if cache_from is None:
+                k = pm.rope(pm.linear(h, w["l0.k"]), pos, 1, 16, 16, 100.0, 1.0)
+                kv_of_place[i] = (k, pm.linear(h, w["l0.v"]))
+            k, v = kv_of_place[i if cache_from is None else cache_from]
+            x = x + pm.linear(pm.causal_gqa_attention(q, k, v, 2, 1, 16), w["l0.o"])
+        else:
+            means = np.cumsum(h, axis=0) / np.arange(1, len(tokens) + 1)[:, None]
+            x = x + pm.linear(means, w["l1.w"])
+        h = pm.rmsnorm(x, w[f"l{layer}.n2"], 1e-5)
+        x = x + pm.linear(pm.swiglu(pm.linear(h, w[f"l{layer}.g"]), pm.linear(h, w[f"l{layer}.u"])), w[f"l{layer}.d"])
+    return pm.linear(pm.rmsnorm(x, w["fn"], 1e-5), w["emb"])
+
+
+def _run_cut(engine, tokens, cuts):
+    from xeno_rt_b200.engine import StepEntry
+    slot = engine.open_slot()
+    parts, at = [], 0
+    for size in cuts:
+        parts.append(engine.step([StepEntry(slot, tokens[at:at + size], list(range(size)))]).cpu().numpy())
+        at += size
+    engine.close_slot(slot)
+    return np.concatenate(parts)
+
+
+def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
+    from xeno_rt_b200.engine import Engine
+    from xeno_rt_b200.parts import register_part
+    register_part("mixer", "test_running_mean", RunningMeanMixer, replace=True)
+    spec = _toy_spec()
+    model, tensors = _toy_model(spec)
+    engine = Engine(model, 64 * 4)
+    assert len(engine.cache.kv_groups) == 1 and len(engine.cache.state_groups) == 1
+    tokens = np.random.default_rng(0).integers(0, 50, size=70).tolist()
+    want = _plain_toy(tensors, [(0, None), (1, None)], tokens)
+    assert np.abs(_run_cut(engine, tokens, [70]) - want).max() / np.abs(want).max() < 2e-5
+    assert np.abs(_run_cut(engine, tokens, [40] + [1] * 30) - want).max() / np.abs(want).max() < 2e-5
+    # the slot is used again: its state must start from zero
+    assert np.abs(_run_cut(engine, tokens, [3, 67]) - want).max() / np.abs(want).max() < 2e-5
+
+
+def test_a_layer_named_twice_and_a_layer_reading_anothers_cache():
+    from xeno_rt_b200.engine import Engine
+    from xeno_rt_b200.parts import SchedulePlace, register_part
+    register_part("mixer", "test_running_mean", RunningMeanMixer, replace=True)
+    tokens = np.random.default_rng(1).integers(0, 50, size=80).tolist()
+    # layer 0 runs twice with a cache of its own each time, then once more reading the first place's cache
+    schedule = [SchedulePlace(0), SchedulePlace(1), SchedulePlace(0), SchedulePlace(0, cache_from=0)]
+    spec = _toy_spec(schedule)
+    model, tensors = _toy_model(spec)
+    engine = Engine(model, 64 * 4)
+    assert engine.cache.kv_groups[0].k.shape[0] == 2  # two places own keys and values, the fourth owns none
+    want = _plain_toy(tensors, [(0, None), (1, None), (0, None), (0, 0)], tokens)
+    assert np.abs(_run_cut(engine, tokens, [80]) - want).max() / np.abs(want).max() < 2e-5
+    assert np.abs(_run_cut(engine, tokens, [50] + [1] * 30) - want).max() / np.abs(want).max() < 2e-5
+
+
+def test_spec_errors():
+    from xeno_rt_b200.core import ConfigError
+    from xeno_rt_b200.parts import SchedulePlace, part_class
+    with pytest.raises(ConfigError, match="no mixer part named"):
+        part_class("mixer", "nonexistent")
+    spec = _toy_spec([SchedulePlace(0), SchedulePlace(0, cache_from=1)])
+    with pytest.raises(ConfigError, match="does not come before"):
+        spec.validate()
+    spec = _toy_spec([SchedulePlace(5)])
+    with pytest.raises(ConfigError, match="names layer 5"):
+        spec.validate()

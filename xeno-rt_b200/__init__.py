@@ -11,3 +11,8 @@ from .core import (XrtError, ConfigError, WeightError, CacheError, KernelError, 
                    DType, parse_dtype)
 
 __version__ = "0.1.0"
+from . import models  # registers the architectures
+from .config import load_config, config_from_dict, register_architecture
+from .engine import (Model, Engine, StepEntry, Runtime, Session, GenerateRequest, GenerateResult)
+from .sampling import SamplerConfig
+from .weights import write_random_model

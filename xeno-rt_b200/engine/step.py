@@ -89,6 +89,7 @@ class Engine:
     def __init__(self, model, max_tokens: int, max_slots: int | None = None):
         self.model = model
         self.cache = model.new_cache(max_tokens, max_slots)
+        self.last_context = None
 
     def open_slot(self) -> int:
         return self.cache.open_slot()
@@ -104,6 +105,7 @@ class Engine:
         model = self.model
         ctx, want_rows = build_context(entries, self.cache, model.vocab_size, model.dtype, model.device, pad_to)
         self.cache.flush_tables()
+        self.last_context = ctx
         logits = model.forward(ctx, self.cache, want_rows)
         for e in entries:
             self.cache.advance(e.slot, len(e.tokens))
