@@ -1,0 +1,305 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the Llama-3-8B shape in bfloat16 with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens a second at batch 8 with every sequence near
+the benchmark context (the timed steps end at that many positions): K decode steps, each the
+model's step function plus sampling, timed on the device with CUDA events after W warm-up steps.
+``e2e`` is the same through the Python entry point (``Session.generate_batch``): host token ids in,
+host token ids out, with the copies that go with them every step.  ``prefill`` times one prompt of
+2,048 tokens; ``roofline`` is the decode step's bytes (every weight it uses once, and the cache of
+the live sequences) over its time, against the measured copy bandwidth; ``points`` are decode at
+batch 1 and 64.  Weights are random N(0, 0.02) drawn on the device, prompts are uniform random
+token ids.  The weights (about 15 GB read a step) are far larger than the L2 cache, so nothing is
+flushed between steps.  More than one GPU is outside this library: it says so and exits with 2.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA3_8B = {
+    "architectures": ["LlamaForCausalLM"], "vocab_size": 128256, "max_position_embeddings": 8192,
+    "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False,
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+PREFILL_TOKENS = 2048
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            raw = json.load(fh)
+        return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
+    except Exception:
+        return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=10)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            cells = [c.strip() for c in line.split(",")]
+            if len(cells) < 6:
+                continue
+            try:
+                clocks.append(float(cells[0]))
+                max_clock = float(cells[1])
+            except ValueError:
+                continue
+            for name, cell in zip(names, cells[2:6]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def weight_bytes_per_step(cfg, n_layers: int) -> int:
+    """Bytes of every weight a decode step reads once: the layers' matrices and norms, the final
+    norm and the output matrix (of the embedding only the batch's rows are read)."""
+    d, f, hd = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    qw, kw = cfg["num_attention_heads"] * hd, cfg["num_key_value_heads"] * hd
+    per_layer = (qw + 2 * kw) * d + d * qw + 3 * f * d + 2 * d
+    return 2 * (n_layers * per_layer + d + cfg["vocab_size"] * d)
+
+
+def kv_bytes_per_token(cfg, n_layers: int) -> int:
+    return 2 * 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * n_layers
+
+
+def prefill_flops(cfg, n_layers: int, tokens: int) -> float:
+    d, f, hd = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    qw, kw = cfg["num_attention_heads"] * hd, cfg["num_key_value_heads"] * hd
+    per_token = 2 * n_layers * ((qw + 2 * kw) * d + d * qw + 3 * f * d)
+    attention = n_layers * 2 * 2 * qw * tokens * tokens / 2  # QK^T and PV over the causal half
+    return tokens * per_token + attention + 2 * cfg["vocab_size"] * d  # the output matrix on one row
+
+
+def fill_batch(engine, batch: int, length: int, vocab: int, chunk_tokens: int = 16384):
+    """Opens ``batch`` slots and runs uniform random prompts of ``length`` tokens through the model
+    in pieces, so that every sequence's cache holds real keys and values.  Returns the slots."""
+    import torch
+    from xeno_rt_b200.engine import StepEntry
+    gen = torch.Generator().manual_seed(1234)
+    slots = [engine.open_slot() for _ in range(batch)]
+    per_step = max(1, chunk_tokens // max(1, min(length, 2048)))
+    for lo in range(0, batch, per_step):
+        group = slots[lo:lo + per_step]
+        done = 0
+        while done < length:
+            size = min(2048, length - done)
+            tokens = torch.randint(0, vocab, (len(group), size), generator=gen).tolist()
+            engine.step([StepEntry(s, t, []) for s, t in zip(group, tokens)])
+            done += size
+    torch.cuda.synchronize()
+    return slots
+
+
+def time_decode(model, batch: int, context: int, steps: int, warmup: int, sample_clocks: bool = False):
+    """Device-timed decode: sequences of ``context - steps - warmup`` tokens, then warm-up and K
+    timed steps of step function + sampling, fed with the sampled ids."""
+    import torch
+    from xeno_rt_b200.csrc import ops
+    from xeno_rt_b200.engine import Engine, StepEntry
+    from xeno_rt_b200.sampling import Sampler, SamplerConfig
+
+    vocab = model.vocab_size
+    start_len = context - steps - warmup
+    engine = Engine(model, batch * ((context + 63) // 64 * 64), max_slots=batch)
+    sampler = Sampler(engine.cache, vocab)
+    slots = fill_batch(engine, batch, start_len, vocab)
+    sampler.begin(slots, list(range(batch)))
+    row_slot = torch.tensor(slots, dtype=torch.int32, device=model.device)
+    configs = [SamplerConfig(temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.0)] * batch
+    tokens = [[1]] * batch
+
+    def one_step(tokens):
+        logits = engine.step([StepEntry(s, t, [0]) for s, t in zip(slots, tokens)])
+        return sampler.sample(logits, row_slot, configs)
+
+    for _ in range(warmup):
+        ids = one_step(tokens)
+        tokens = [[t] for t in ids.tolist()]
+    torch.cuda.synchronize()
+    sampler_clocks = ClockSampler()
+    if sample_clocks:
+        sampler_clocks.start()
+        time.sleep(0.3)
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_before = ops.launch_count()
+    torch.cuda.synchronize()
+    begin.record()
+    for _ in range(steps):
+        ids = one_step(tokens)
+        # the next step's ids are known on the host only after a read; the device-timed loop
+        # feeds a fixed id instead so that nothing waits on the host (the model's work is the same)
+    end.record()
+    torch.cuda.synchronize()
+    ms = begin.elapsed_time(end)
+    launches = ops.launch_count() - launches_before
+    clocks = sampler_clocks.stop() if sample_clocks else None
+    for s in slots:
+        engine.close_slot(s)
+    del engine
+    torch.cuda.empty_cache()
+    return {"ms_per_step": ms / steps, "tokens_per_s": batch * steps / (ms / 1e3), "launches": launches,
+            "clocks": clocks, "mean_context": context - steps / 2}
+
+
+def time_prefill(model, tokens: int, iters: int, warmup: int):
+    import torch
+    from xeno_rt_b200.engine import Engine, StepEntry
+    engine = Engine(model, (tokens + 63) // 64 * 64, max_slots=1)
+    prompt = torch.randint(0, model.vocab_size, (tokens,), generator=torch.Generator().manual_seed(7)).tolist()
+    times = []
+    for i in range(warmup + iters):
+        slot = engine.open_slot()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        engine.step([StepEntry(slot, prompt, [tokens - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(begin.elapsed_time(end))
+        engine.close_slot(slot)
+    del engine
+    torch.cuda.empty_cache()
+    return statistics.median(times)
+
+
+def time_e2e(model, batch: int, context: int, steps: int):
+    """Decode tokens a second through Session.generate_batch: host ids in, host ids out."""
+    import torch
+    from xeno_rt_b200 import GenerateRequest, Runtime
+    runtime = Runtime(model, max_batch=batch)
+    session = runtime.new_session()
+    gen = torch.Generator().manual_seed(99)
+    prompt_len = context - steps - 1
+    prompts = torch.randint(0, model.vocab_size, (batch, prompt_len), generator=gen).tolist()
+    requests = [GenerateRequest(p, max_tokens=steps + 1, temperature=0.0, repetition_penalty=1.0, stop_ids=())
+                for p in prompts]
+    results, stats = session.generate_batch(requests)
+    lay_ints = 3 * batch + 3 * batch + 1
+    out = {"value": stats.decode_tokens_per_second, "unit": "tokens/s", "h2d_bytes_per_step": 4 * lay_ints + 16 * batch,
+           "d2h_bytes_per_step": 4 * batch, "decode_steps": stats.decode_steps,
+           "prefill_s": round(stats.prefill_seconds, 4)}
+    session.backend = None
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_ours(args) -> int:
+    import torch
+    import xeno_rt_b200  # noqa: F401
+    from xeno_rt_b200.engine import Model
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: bench.py needs a B200"}))
+        return 1
+    cfg = dict(LLAMA3_8B)
+    full_layers = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = args.layers or full_layers
+    n_layers = cfg["num_hidden_layers"]
+    pk = peaks()
+    t0 = time.time()
+    model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    torch.cuda.synchronize()
+    setup_s = time.time() - t0
+
+    main = time_decode(model, args.batch, args.context, args.steps, args.warmup, sample_clocks=True)
+    bytes_step = weight_bytes_per_step(cfg, n_layers) + args.batch * main["mean_context"] * kv_bytes_per_token(cfg, n_layers)
+    achieved = bytes_step / (main["ms_per_step"] / 1e3) / 1e9
+    points = {}
+    for b in (1, 64):
+        r = time_decode(model, b, args.context, max(8, args.steps // 2), args.warmup)
+        points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
+    prefill_ms = time_prefill(model, PREFILL_TOKENS, iters=5, warmup=max(3, args.warmup // 2))
+    flops = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
+    e2e = time_e2e(model, args.batch, args.context, args.steps)
+
+    line = {
+        "metric": "decode tok/s @ batch 8 (Llama-3-8B bf16, context 4096)", "value": round(main["tokens_per_s"], 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
+        "impl": "ours",
+        "config": {"model": "Llama-3-8B shape", "layers": n_layers, "layers_of_model": full_layers,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": args.batch, "seq_len": args.context, "parallelism": "none (1 GPU)",
+                   "cache_block_tokens": 64, "l2": "inputs larger than L2 (15 GB of weights a step), no flush",
+                   "peaks": pk["source"], "setup_s": round(setup_s, 1)},
+        "e2e": e2e,
+        "gpu_launches": main["launches"],
+        "clocks": main["clocks"],
+        "prefill": {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3), "frac": round(flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=4096)
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust workspace (no setup.py or pyproject.toml, pip refuses it), there is "
+                          "no cargo or rustc here, and its model path is CPU-only and takes GGUF-quantised weights only"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

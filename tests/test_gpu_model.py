@@ -212,3 +212,21 @@ def test_random_model_on_the_device_matches_the_written_folder(tmp_path):
     la = a.step([StepEntry(a.open_slot(), prompt, [39])])
     lb = b.step([StepEntry(b.open_slot(), prompt, [39])])
     assert torch.allclose(la, lb, atol=2e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_graph_replay_equals_eager_steps(setups, dtype):
+    """Decode steps replayed from a CUDA graph give what the same steps give launched one by one,
+    also when the batch shrinks and when a slot is used again."""
+    from xeno_rt_b200.engine import Engine, Model
+    folder, prompts, refs = setups["tiny-qwen3"]
+    model = Model.load(folder, dtype=dtype)
+    eager = Engine(model, 64 * 12, use_graphs=False)
+    graphed = Engine(model, 64 * 12, use_graphs=True)
+    for _ in range(2):
+        a = _batch(eager, prompts[:5], decode=8)
+        b = _batch(graphed, prompts[:5], decode=8)
+        for x, y, r in zip(a, b, refs):
+            assert np.array_equal(x, y)
+            assert scaled_error(y, r) < TOL[dtype]
+    assert graphed._graphs and not eager._graphs

@@ -89,8 +89,24 @@ def _ptr(t, name: str, dtype=None) -> int:
     return t.data_ptr()
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels of this library were launched so far (a graph replay counts the kernels
+    that were captured into it)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
 def _check(status: int, what: str) -> None:
+    global _launches
     if status == 0:
+        _launches += 1
         return
     if status == -1:
         raise KernelError(f"{what}: the kernel refused its arguments")

@@ -6,9 +6,14 @@ The reference has three entry points for one sequence (``forward_token``, ``forw
 ``forward_batch_all_logits``, crates/xrt-models/src/llama.rs:388, 617, 830); here there is one for
 many.  Its checks are the reference's (llama.rs:395-408, 434-439, 624-626, 1044-1049): a step continues
 exactly where the slot stands, is not empty, and brings ids inside the vocabulary.
+
+Steps in which every sequence brings one token are replayed from a CUDA graph: the step's arrays
+are copied into fixed device buffers (padded with rows that every kernel skips, up to the next
+power of two) and one graph launch runs what would otherwise be hundreds of kernel launches.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -16,7 +21,10 @@ import torch
 
 from ..cache import Cache
 from ..core import RuntimeFault
+from ..csrc import ops
 from ..parts import StepContext
+
+GRAPH_MAX_BATCH = 256
 
 
 @dataclass
@@ -28,10 +36,37 @@ class StepEntry:
     want: list = field(default_factory=list)
 
 
-def build_context(entries, cache: Cache, vocab_size: int, dtype, device, pad_to: int | None = None):
-    """Checks the entries, reserves cache room and lays the tokens end to end.  Returns
-    (context, wanted rows as a device tensor or None).  ``pad_to`` appends padding rows (slot -1)
-    up to that many tokens; padding changes no result."""
+class _Staging:
+    """Pinned host buffers for the step's arrays, used in turn; a buffer is reused only after the
+    copy that read it has completed."""
+
+    def __init__(self, device, count: int = 4):
+        self.device = torch.device(device)
+        self.pinned = self.device.type == "cuda"
+        self.buffers = [None] * count
+        self.events = [None] * count
+        self.turn = 0
+
+    def take(self, n_ints: int):
+        i = self.turn
+        self.turn = (self.turn + 1) % len(self.buffers)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.buffers[i]
+        if buf is None or buf.numel() < n_ints:
+            size = max(1024, 1 << (n_ints - 1).bit_length())
+            buf = torch.empty(size, dtype=torch.int32, pin_memory=self.pinned)
+            self.buffers[i] = buf
+        return i, buf[:n_ints]
+
+    def copied(self, i: int) -> None:
+        if self.pinned:
+            event = torch.cuda.Event()
+            event.record()
+            self.events[i] = event
+
+
+def _check_entries(entries, vocab_size: int) -> None:
     if not entries:
         raise RuntimeFault("a step needs at least one sequence")
     slots = [e.slot for e in entries]
@@ -46,22 +81,28 @@ def build_context(entries, cache: Cache, vocab_size: int, dtype, device, pad_to:
         for w in e.want:
             if not (0 <= w < len(e.tokens)):
                 raise RuntimeFault(f"slot {e.slot}: wanted place {w} is outside the {len(e.tokens)} tokens of the step")
-    starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
-    new_lens = [len(e.tokens) for e in entries]
-    total = sum(new_lens)
-    padded = max(total, pad_to or 0)
-    n = len(entries)
-    # one int32 buffer, one copy: ids | positions | slots | cu_seqlens | seq_slot | seq_start | wanted rows
-    wanted = []
-    offset = 0
-    buf = np.zeros(3 * padded + (n + 1) + 2 * n, dtype=np.int32)
-    ids, pos, slot_of = buf[:padded], buf[padded:2 * padded], buf[2 * padded:3 * padded]
+
+
+def layout(padded: int, n: int):
+    """Offsets of the step's arrays inside one int32 buffer:
+    ids | positions | slots (each ``padded``) | cu_seqlens (n + 1) | seq_slot (n) | seq_start (n)."""
+    a = 3 * padded
+    return {"ids": (0, padded), "pos": (padded, 2 * padded), "slot": (2 * padded, a), "cu": (a, a + n + 1),
+            "seq_slot": (a + n + 1, a + 2 * n + 1), "seq_start": (a + 2 * n + 1, a + 3 * n + 1), "size": a + 3 * n + 1}
+
+
+def fill_arrays(buf: np.ndarray, entries, starts, padded: int, n_rows: int):
+    """Writes the step's arrays into ``buf`` (see ``layout``; ``n_rows`` >= len(entries) sequence
+    rows, the rest being padding) and returns the wanted rows."""
+    lay = layout(padded, n_rows)
+    buf[:lay["size"]] = 0
+    ids, pos, slot_of = (buf[lay[k][0]:lay[k][1]] for k in ("ids", "pos", "slot"))
+    cu, seq_slot, seq_start = (buf[lay[k][0]:lay[k][1]] for k in ("cu", "seq_slot", "seq_start"))
     slot_of[:] = -1
-    cu = buf[3 * padded:3 * padded + n + 1]
-    seq_slot = buf[3 * padded + n + 1:3 * padded + 2 * n + 1]
-    seq_start = buf[3 * padded + 2 * n + 1:]
+    seq_slot[:] = -1
+    wanted, offset = [], 0
     for i, e in enumerate(entries):
-        k = new_lens[i]
+        k = len(e.tokens)
         ids[offset:offset + k] = e.tokens
         pos[offset:offset + k] = np.arange(starts[i], starts[i] + k)
         slot_of[offset:offset + k] = e.slot
@@ -70,26 +111,85 @@ def build_context(entries, cache: Cache, vocab_size: int, dtype, device, pad_to:
         seq_start[i] = starts[i]
         wanted.extend(offset + w for w in e.want)
         offset += k
-    cu[n] = offset
-    dev = torch.from_numpy(buf).to(device)
+    cu[len(entries):] = offset
+    return wanted
+
+
+def context_from(dev: torch.Tensor, padded: int, n_rows: int, new_lens, starts, dtype, max_context=None):
+    lay = layout(padded, n_rows)
+    view = lambda k: dev[lay[k][0]:lay[k][1]]
+    return StepContext(
+        n_tokens=padded, n_seqs=n_rows, token_ids=view("ids"), tok_pos=view("pos"), tok_slot=view("slot"),
+        cu_seqlens=view("cu"), seq_slot=view("seq_slot"), seq_start=view("seq_start"), new_lens=list(new_lens),
+        starts=list(starts), all_single=all(k == 1 for k in new_lens), max_new=max(new_lens),
+        max_context=max_context if max_context is not None else max(s + k for s, k in zip(starts, new_lens)),
+        dtype=dtype)
+
+
+def build_context(entries, cache: Cache, vocab_size: int, dtype, device, pad_to: int | None = None, staging=None):
+    """Checks the entries, reserves cache room and lays the tokens end to end on the device.
+    Returns (context, wanted rows as a device tensor or None).  ``pad_to`` appends padding rows
+    (slot -1) up to that many tokens; padding changes no result."""
+    _check_entries(entries, vocab_size)
+    starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
+    new_lens = [len(e.tokens) for e in entries]
+    padded = max(sum(new_lens), pad_to or 0)
+    n = len(entries)
+    size = layout(padded, n)["size"]
+    staging = staging or _Staging(device, count=1)
+    turn, host = staging.take(size)
+    wanted = fill_arrays(host.numpy(), entries, starts, padded, n)
+    dev = host.to(device, non_blocking=True)
+    staging.copied(turn)
     want_rows = torch.tensor(wanted, dtype=torch.int32, device=device) if wanted else None
-    ctx = StepContext(
-        n_tokens=padded, n_seqs=n, token_ids=dev[:padded], tok_pos=dev[padded:2 * padded],
-        tok_slot=dev[2 * padded:3 * padded], cu_seqlens=dev[3 * padded:3 * padded + n + 1],
-        seq_slot=dev[3 * padded + n + 1:3 * padded + 2 * n + 1], seq_start=dev[3 * padded + 2 * n + 1:],
-        new_lens=new_lens, starts=starts, all_single=all(k == 1 for k in new_lens), max_new=max(new_lens),
-        max_context=max(s + k for s, k in zip(starts, new_lens)), dtype=dtype)
-    return ctx, want_rows
+    return context_from(dev, padded, n, new_lens, starts, dtype), want_rows
+
+
+class _DecodeGraph:
+    """One captured decode step for up to ``bucket`` sequences."""
+
+    def __init__(self, engine: "Engine", bucket: int):
+        model, cache = engine.model, engine.cache
+        self.bucket = bucket
+        self.size = layout(bucket, bucket)["size"]
+        self.static = torch.zeros(self.size, dtype=torch.int32, device=model.device)
+        lay = layout(bucket, bucket)
+        self.static[lay["slot"][0]:lay["slot"][1]] = -1
+        self.static[lay["seq_slot"][0]:lay["seq_slot"][1]] = -1
+        self.rows = torch.arange(bucket, dtype=torch.int32, device=model.device)
+        capacity = cache.blocks_per_seq * 64
+        make = lambda: context_from(self.static, bucket, bucket, [1] * bucket, [0] * bucket, model.dtype,
+                                    max_context=capacity)
+        side = torch.cuda.Stream(device=model.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ctx = make()
+            ctx.captured = True
+            model.forward(ctx, cache, self.rows)  # warm-up: every kernel and allocation once, eagerly
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(self.graph):
+            ctx = make()
+            ctx.captured = True
+            self.logits = model.forward(ctx, cache, self.rows)
+        self.launches = ops.launch_count() - before
 
 
 class Engine:
     """A model with its cache.  ``step`` is the one way tokens go through the model; generation
     and trace replay both call it."""
 
-    def __init__(self, model, max_tokens: int, max_slots: int | None = None):
+    def __init__(self, model, max_tokens: int, max_slots: int | None = None, use_graphs: bool | None = None):
         self.model = model
         self.cache = model.new_cache(max_tokens, max_slots)
         self.last_context = None
+        self.staging = _Staging(model.device)
+        if use_graphs is None:
+            use_graphs = os.environ.get("XRT_NO_GRAPHS", "0") in ("", "0")
+        self.use_graphs = use_graphs and model.device.type == "cuda"
+        self._graphs: dict[int, _DecodeGraph] = {}
 
     def open_slot(self) -> int:
         return self.cache.open_slot()
@@ -97,16 +197,47 @@ class Engine:
     def close_slot(self, slot: int) -> None:
         self.cache.close_slot(slot)
 
-    def step(self, entries, pad_to: int | None = None):
+    def step(self, entries, pad_to: int | None = None, graph: bool | None = None):
         """Runs one step.  ``entries``: StepEntry list.  Returns float32 logits
         [number of wanted places, vocabulary] on the device, in the order of the entries and of
         their ``want`` lists, or None if nothing is wanted."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         model = self.model
-        ctx, want_rows = build_context(entries, self.cache, model.vocab_size, model.dtype, model.device, pad_to)
+        use_graph = self.use_graphs if graph is None else graph
+        if (use_graph and pad_to is None and len(entries) <= GRAPH_MAX_BATCH
+                and all(len(e.tokens) == 1 for e in entries)):
+            return self._graph_step(entries)
+        ctx, want_rows = build_context(entries, self.cache, model.vocab_size, model.dtype, model.device, pad_to,
+                                       self.staging)
         self.cache.flush_tables()
         self.last_context = ctx
         logits = model.forward(ctx, self.cache, want_rows)
         for e in entries:
             self.cache.advance(e.slot, len(e.tokens))
         return logits
+
+    def _graph_step(self, entries):
+        model = self.model
+        _check_entries(entries, model.vocab_size)
+        n = len(entries)
+        bucket = 1 << (n - 1).bit_length()
+        starts = [self.cache.reserve(e.slot, 1) for e in entries]
+        g = self._graphs.get(bucket)
+        if g is None:
+            self.cache.flush_tables()
+            g = self._graphs[bucket] = _DecodeGraph(self, bucket)
+        turn, host = self.staging.take(g.size)
+        wanted = fill_arrays(host.numpy(), entries, starts, bucket, bucket)
+        g.static.copy_(host, non_blocking=True)
+        self.staging.copied(turn)
+        self.cache.flush_tables()
+        self.last_context = context_from(g.static, bucket, bucket, [1] * n, starts, model.dtype)
+        g.graph.replay()
+        ops.add_launches(g.launches)
+        for e in entries:
+            self.cache.advance(e.slot, 1)
+        if not wanted:
+            return None
+        if wanted == list(range(n)):
+            return g.logits[:n].clone()
+        return g.logits[torch.tensor(wanted, dtype=torch.int64, device=model.device)]

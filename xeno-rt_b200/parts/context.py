@@ -35,4 +35,6 @@ class StepContext:
     max_new: int
     max_context: int
     dtype: DType
+    captured: bool = False  # the step is being captured into (or replayed from) a CUDA graph:
+    #                         launch shapes must not depend on the sequences' lengths
     shared: dict = field(default_factory=dict)
