@@ -234,3 +234,104 @@ def test_fill_normal_matches_the_host_generator(dtype):
     same = (out.cpu() == host).float().mean()
     assert same > 0.999  # identical but for rare last-bit differences of log and cos
     assert torch.allclose(out.cpu().float(), host.float(), atol=1e-4)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 16, 17, 40, 64])
+@pytest.mark.parametrize("n,k", [(203, 104), (64, 4096), (136, 96), (8, 40)])
+def test_gemm_skinny(m, n, k):
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    want = f64(x) @ f64(w).T
+    out = torch.empty(m, n, device=DEV)
+    ops().gemm_skinny(out, x, w)
+    assert rel(out, want) < 1e-5  # bfloat16 operands are exact in float64; only the sum's order differs
+    out_b = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    ops().gemm_skinny(out_b, x, w)
+    assert rel(out_b, want) < 5e-3
+    base = torch.randn(m, n, device=DEV)
+    acc = base.clone()
+    ops().gemm_skinny(acc, x, w, "accumulate")
+    assert rel(acc, f64(base) + want) < 1e-5
+    # a row's result does not depend on how many rows the call carries
+    one = torch.empty(1, n, device=DEV)
+    ops().gemm_skinny(one, x[m - 1:m].contiguous(), w)
+    assert torch.equal(one[0], out[m - 1])
+
+
+@pytest.mark.parametrize("m,inner,k", [(1, 136, 96), (9, 203, 104), (33, 64, 4096)])
+def test_gemm_skinny_swiglu(m, inner, k):
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inner, k, device=DEV) * 0.1).to(torch.bfloat16)
+    out = torch.empty(m, inner, device=DEV, dtype=torch.bfloat16)
+    ops().gemm_skinny(out, x, w, "swiglu", up_rows=inner)
+    want = pm.swiglu(f64(x) @ f64(w[:inner]).T, f64(x) @ f64(w[inner:]).T)
+    assert rel(out, want) < 5e-3
+
+
+def test_gemm_skinny_refuses_what_it_cannot_take():
+    from xeno_rt_b200.core import KernelError
+    x = torch.randn(2, 100, device=DEV).to(torch.bfloat16)  # K = 100 is no multiple of 8
+    w = torch.randn(16, 100, device=DEV).to(torch.bfloat16)
+    with pytest.raises(KernelError, match="outside what the kernel handles"):
+        ops().gemm_skinny(torch.empty(2, 16, device=DEV), x, w)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (5, 1, 48), (32, 8, 128), (6, 3, 80), (16, 1, 256), (8, 8, 64)])
+@pytest.mark.parametrize("chunk,n_splits", [(64, 11), (256, 3), (704, 1)])
+def test_attention_decode_kernel(nh, nkv, hd, chunk, n_splits):
+    """Five sequences of unequal lengths (one of a single token, one ending at a block edge, one a
+    padding row), one token each, against the plain attention of the full sequences."""
+    torch.manual_seed(nh + hd + chunk)
+    lens = [1, 64, 65, 300, 700]
+    k_pool, v_pool, table = _cache_for(lens, nkv, hd, torch.bfloat16, shuffle_seed=hd)
+    ks = [torch.randn(n, nkv, hd, device=DEV) for n in lens]
+    vs = [torch.randn(n, nkv, hd, device=DEV) for n in lens]
+    for s in range(len(lens)):
+        _fill_cache(k_pool, v_pool, table, s + 1, ks[s], vs[s])
+    order = [3, 0, -1, 4, 1, 2]  # token rows: sequences in another order, and a padding row
+    q = torch.randn(len(order), nh * hd, device=DEV).to(torch.bfloat16)
+    tok_slot = torch.tensor([s + 1 if s >= 0 else -1 for s in order], dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([lens[s] - 1 if s >= 0 else 0 for s in order], dtype=torch.int32, device=DEV)
+    out = torch.full_like(q, 7.0)
+    ops().attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd), 0,
+                           chunk, n_splits)
+    bf = lambda x: f64(x.to(torch.bfloat16)).reshape(x.shape[0], -1)
+    for row, s in enumerate(order):
+        if s < 0:
+            assert float(out[row].float().abs().sum()) == 0.0
+            continue
+        n = lens[s]
+        q_full = np.zeros((n, nh * hd))
+        q_full[n - 1] = f64(q[row])
+        want = pm.causal_gqa_attention(q_full, bf(ks[s]), bf(vs[s]), nh, nkv, hd)[n - 1]
+        assert rel(out[row], want) < 1.5e-2, (row, s)
+
+
+def test_attention_decode_finds_a_far_key_and_respects_the_window():
+    nh, nkv, hd, S = 8, 2, 128, 1500
+    k_pool, v_pool, table = _cache_for([S], nkv, hd, torch.bfloat16, shuffle_seed=2)
+    k = torch.randn(S, nkv, hd, device=DEV) * 0.1
+    v = torch.randn(S, nkv, hd, device=DEV)
+    q = torch.randn(1, nh, hd, device=DEV) * 0.1
+    far = 70  # second block, 1429 positions back
+    k[far, 1] = q[0, 6] * 400  # head 6 reads kv head 1
+    _fill_cache(k_pool, v_pool, table, 1, k, v)
+    qf = q.reshape(1, nh * hd).to(torch.bfloat16)
+    tok_pos = torch.tensor([S - 1], dtype=torch.int32, device=DEV)
+    tok_slot = torch.tensor([1], dtype=torch.int32, device=DEV)
+    target = v[far, 1].to(torch.bfloat16).float()
+    for chunk, n_splits in ((128, 12), (1536, 1)):
+        out = torch.empty_like(qf)
+        run = lambda window: ops().attention_decode(out, qf, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd,
+                                                    1 / math.sqrt(hd), window, chunk, n_splits)
+        run(0)
+        assert torch.allclose(out.float().reshape(nh, hd)[6], target, atol=3e-2)
+        assert not torch.allclose(out.float().reshape(nh, hd)[5], target, atol=0.2)
+        run(S - far - 1)  # the far key is just outside the window
+        assert not torch.allclose(out.float().reshape(nh, hd)[6], target, atol=0.2)
+        run(S - far)  # the far key is the window's first
+        assert torch.allclose(out.float().reshape(nh, hd)[6], target, atol=3e-2)
+        ref = torch.empty_like(qf)
+        ops().attention_reference(ref, qf, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd),
+                                  window=S - far)
+        assert torch.allclose(out.float(), ref.float(), atol=3e-2)

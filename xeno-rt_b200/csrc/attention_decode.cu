@@ -1,0 +1,249 @@
+// Decode attention in bfloat16: one new token a sequence against the keys and values of its cache
+// blocks, split along the sequence so that a handful of sequences still fill the GPU, then a
+// combine step.  (The reference's decode form: crates/xrt-models/src/llama.rs:504-574, an online
+// softmax over the cached positions, parallel over kv heads with the group's query heads inside.)
+//
+// Grid (splits, kv heads, tokens).  A block of four warps serves one kv head of one token for the
+// keys [split * chunk, (split + 1) * chunk): the group's query heads (up to 16) are the rows of the
+// MMA, so the group shares every key and value that is read.  Tiles of 64 keys (one cache block,
+// contiguous in memory) are copied to shared memory with cp.async, double-buffered; warp w takes
+// keys 16w .. 16w+16 of each tile with its own online-softmax state; the four states are merged
+// through shared memory in warp order.  With one split the block writes the output, otherwise
+// (m, l, o) partials that the combine kernel merges in split order.  Nothing depends on how many
+// other tokens the launch carries, and launch shapes depend on `chunk` and the grid only, so the
+// launch can be captured in a CUDA graph and replayed for other lengths.
+#include "attention_mma.cuh"
+
+namespace xrt {
+
+constexpr int DEC_WARPS = 4;
+
+template <int HD_MAX>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+                        const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ tok_slot,
+                        const int* __restrict__ tok_pos, const int* __restrict__ block_table, int max_blocks,
+                        int n_heads, int n_kv_heads, int head_dim, float scale_log2, int window, int chunk,
+                        int n_splits) {
+  constexpr int D_TILES = HD_MAX / 8;
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int split = blockIdx.x, kv_head = blockIdx.y, tok = blockIdx.z;
+  const int slot = tok_slot[tok];
+  if (slot < 0) {  // a padding row: zeros (with several splits the combine kernel writes them)
+    if (n_splits == 1) {
+      const int group = n_heads / n_kv_heads;
+      __nv_bfloat16* dst = out + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
+      for (int i = threadIdx.x; i < group * head_dim; i += blockDim.x) dst[i] = __float2bfloat16_rn(0.f);
+    }
+    return;
+  }
+  const int pos = tok_pos[tok];
+  const int len = pos + 1;
+  const int first_key = window > 0 ? max(0, len - window) : 0;
+  const int begin = max(split * chunk, (first_key / XRT_BLOCK_TOKENS) * XRT_BLOCK_TOKENS);
+  const int end = min((split + 1) * chunk, len);
+  if (begin >= end) return;  // this split holds no visible key: the combine step skips it too
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int group = n_heads / n_kv_heads;
+  const int row_bytes = tile_row_bytes(head_dim);
+  const int tile_bytes = XRT_BLOCK_TOKENS * row_bytes;
+  unsigned char* k_tiles = smem;                   // [2][64 rows]
+  unsigned char* v_tiles = smem + 2 * tile_bytes;  // [2][64 rows]
+
+  // query fragments: rows = the group's heads (rows at or beyond the group are zero)
+  uint32_t qf[D_TILES / 2][4];
+  {
+    const __nv_bfloat16* qt = q + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
+#pragma unroll
+    for (int ks = 0; ks < D_TILES / 2; ++ks) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = g + (e & 1) * 8, dim = ks * 16 + (e >> 1) * 8 + 2 * t;
+        qf[ks][e] = (row < group && dim < head_dim)
+                        ? *reinterpret_cast<const uint32_t*>(qt + (size_t)row * head_dim + dim) : 0u;
+      }
+    }
+  }
+
+  const int* blocks = block_table + (size_t)slot * max_blocks;
+  const size_t head_stride = (size_t)XRT_BLOCK_TOKENS * head_dim;
+  auto issue_tile = [&](int tile_index, int buffer) {
+    const int key0 = begin + tile_index * XRT_BLOCK_TOKENS;
+    const int block = blocks[key0 / XRT_BLOCK_TOKENS];
+    const size_t base = ((size_t)block * n_kv_heads + kv_head) * head_stride;
+    const int live = min(XRT_BLOCK_TOKENS, len - key0);
+    copy_tile_async(k_tiles + buffer * tile_bytes, k_pool + base, XRT_BLOCK_TOKENS, live, head_dim);
+    copy_tile_async(v_tiles + buffer * tile_bytes, v_pool + base, XRT_BLOCK_TOKENS, live, head_dim);
+    cp_async_commit();
+  };
+
+  SoftmaxState<D_TILES> st;
+  st.init();
+  const int key_lo[2] = {first_key, first_key};
+  const int key_hi[2] = {len, len};
+  const int n_tiles = (end - begin + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS;  // begin is a multiple of 64
+  issue_tile(0, 0);
+  for (int i = 0; i < n_tiles; ++i) {
+    if (i + 1 < n_tiles) { issue_tile(i + 1, (i + 1) & 1); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
+    __syncthreads();
+    const int key_abs = begin + i * XRT_BLOCK_TOKENS + warp * 16;
+    if (key_abs < end)
+      attend_16_keys<D_TILES>(st, qf, k_tiles + (i & 1) * tile_bytes, v_tiles + (i & 1) * tile_bytes, warp * 16,
+                              key_abs, key_lo, key_hi, head_dim, scale_log2);
+    __syncthreads();  // the buffer is free for the tile after next
+  }
+
+  // merge the four warps: maxima first, then the rescaled sums and outputs in warp order
+  float* merge_m = reinterpret_cast<float*>(smem);                 // [warps][16]
+  float* merge_l = merge_m + DEC_WARPS * 16;                       // [warps][16]
+  float* merge_o = merge_l + DEC_WARPS * 16;                       // [warps][16][head_dim]
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+    st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    if (t == 0) { merge_m[warp * 16 + g + r * 8] = st.m[r]; merge_l[warp * 16 + g + r * 8] = st.l[r]; }
+  }
+#pragma unroll
+  for (int dt = 0; dt < D_TILES; ++dt) {
+    if (dt * 8 < head_dim) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        merge_o[((size_t)warp * 16 + g + (e >> 1) * 8) * head_dim + dt * 8 + 2 * t + (e & 1)] = st.o[dt][e];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < group * head_dim; idx += blockDim.x) {
+    const int row = idx / head_dim, d = idx - row * head_dim;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, merge_m[w * 16 + row]);
+    float l = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float mw = merge_m[w * 16 + row];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
+      l += f * merge_l[w * 16 + row];
+      o += f * merge_o[((size_t)w * 16 + row) * head_dim + d];
+    }
+    const int head = kv_head * group + row;
+    if (n_splits == 1) {
+      out[((size_t)tok * n_heads + head) * head_dim + d] = __float2bfloat16_rn(o / l);
+    } else {
+      const size_t p = ((size_t)tok * n_heads + head) * n_splits + split;
+      part_o[p * head_dim + d] = o;
+      if (d == 0) { part_ml[p * 2] = m; part_ml[p * 2 + 1] = l; }
+    }
+  }
+}
+
+// One warp per (token, head): merges the splits' partials in split order.
+__global__ void attention_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
+                                         const float* __restrict__ part_ml, const int* __restrict__ tok_slot,
+                                         const int* __restrict__ tok_pos, int n_tokens, int n_heads, int head_dim,
+                                         int window, int chunk, int n_splits) {
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp_global >= n_tokens * n_heads) return;
+  const int tok = warp_global / n_heads;
+  __nv_bfloat16* dst = out + (size_t)warp_global * head_dim;
+  if (tok_slot[tok] < 0) {
+    for (int d = lane; d < head_dim; d += 32) dst[d] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int len = tok_pos[tok] + 1;
+  const int first_key = window > 0 ? max(0, len - window) : 0;
+  const int first_block_key = (first_key / XRT_BLOCK_TOKENS) * XRT_BLOCK_TOKENS;
+  const size_t base = (size_t)warp_global * n_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) {
+    const bool live = max(s * chunk, first_block_key) < min((s + 1) * chunk, len);
+    if (live) m = fmaxf(m, part_ml[(base + s) * 2]);
+  }
+  float l = 0.f;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const bool live = max(s * chunk, first_block_key) < min((s + 1) * chunk, len);
+    if (!live) continue;
+    const float ms = part_ml[(base + s) * 2];
+    const float f = ms == -INFINITY ? 0.f : exp2f(ms - m);
+    l += f * part_ml[(base + s) * 2 + 1];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int d = lane + 32 * j;
+      if (d < head_dim) acc[j] += f * part_o[(base + s) * head_dim + d];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int d = lane + 32 * j;
+    if (d < head_dim) dst[d] = __float2bfloat16_rn(acc[j] / l);
+  }
+}
+
+template <int HD_MAX>
+int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_bfloat16* q,
+                  const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, const int* tok_slot, const int* tok_pos,
+                  const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                  float scale, int window, int chunk, int n_splits, cudaStream_t stream) {
+  const int tile_bytes = XRT_BLOCK_TOKENS * (head_dim * 2 + 16);
+  const int merge_bytes = DEC_WARPS * 16 * (2 + head_dim) * (int)sizeof(float);
+  const int smem = max(4 * tile_bytes, merge_bytes);
+  auto kernel = attention_decode_kernel<HD_MAX>;
+  static int smem_allowed = 0;  // raised once a size class; not a stream operation
+  if (smem > 48 * 1024 && smem > smem_allowed) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return (int)err;
+    smem_allowed = smem;
+  }
+  dim3 grid(n_splits, n_kv_heads, n_tokens);
+  kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(out, part_o, part_ml, q, k_pool, v_pool, tok_slot, tok_pos,
+                                                block_table, max_blocks, n_heads, n_kv_heads, head_dim,
+                                                scale * 1.4426950408889634f, window, chunk, n_splits);
+  return launch_status();
+}
+
+}  // namespace xrt
+
+// q, out: bfloat16 [n_tokens, n_heads * head_dim], one token a sequence; pools bfloat16
+// [blocks, kv heads, 64, head_dim].  `chunk` (a multiple of 64) keys a split, `n_splits` splits
+// cover the longest sequence the launch may meet.  part_o: float32 [n_tokens * n_heads * n_splits *
+// head_dim] and part_ml: float32 [n_tokens * n_heads * n_splits * 2] are scratch, needed when
+// n_splits > 1.  The group n_heads / n_kv_heads is at most 16; n_tokens at most 65535.
+XRT_EXPORT int xrt_attention_decode(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
+                                    const void* v_pool, const int* tok_slot, const int* tok_pos,
+                                    const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
+                                    int head_dim, float scale, int window, int chunk, int n_splits,
+                                    cudaStream_t stream) {
+  if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || chunk <= 0 || n_splits <= 0)
+    return XRT_ERR_ARGUMENT;
+  if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256 || n_heads / n_kv_heads > 16 ||
+      chunk % XRT_BLOCK_TOKENS != 0 || n_tokens > 65535 || n_kv_heads > 65535)
+    return XRT_ERR_UNSUPPORTED;
+  if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  auto* o = (__nv_bfloat16*)out;
+  auto* qp = (const __nv_bfloat16*)q;
+  auto* kp = (const __nv_bfloat16*)k_pool;
+  auto* vp = (const __nv_bfloat16*)v_pool;
+  int status;
+#define XRT_DECODE(HD) status = xrt::launch_decode<HD>(o, part_o, part_ml, qp, kp, vp, tok_slot, tok_pos, block_table, \
+                                                       max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale,   \
+                                                       window, chunk, n_splits, stream)
+  if (head_dim <= 32) XRT_DECODE(32);
+  else if (head_dim <= 64) XRT_DECODE(64);
+  else if (head_dim <= 128) XRT_DECODE(128);
+  else XRT_DECODE(256);
+#undef XRT_DECODE
+  if (status != XRT_OK) return status;
+  if (n_splits > 1) {
+    const int warps = n_tokens * n_heads;
+    xrt::attention_combine_kernel<<<(warps * 32 + 255) / 256, 256, 0, stream>>>(
+        o, part_o, part_ml, tok_slot, tok_pos, n_tokens, n_heads, head_dim, window, chunk, n_splits);
+    return xrt::launch_status();
+  }
+  return XRT_OK;
+}

@@ -1,0 +1,156 @@
+// Building blocks of the bfloat16 attention kernels: asynchronous copies of key/value tiles from
+// the cache blocks into padded shared-memory rows, ldmatrix loads of the MMA operands, the
+// m16n8k16 tensor-core instruction and the online-softmax update of one 16-row query tile against
+// 16 keys.  Scores, running maxima and sums, and the output accumulators are 32-bit.
+#pragma once
+
+#include "common.cuh"
+
+namespace xrt {
+
+// A row of a key/value tile holds head_dim bfloat16 and 16 bytes of padding, so that the eight rows
+// an ldmatrix reads fall into different banks for every head_dim that is a multiple of 16.
+__device__ __forceinline__ int tile_row_bytes(int head_dim) { return head_dim * 2 + 16; }
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// 16 bytes global -> shared; src_bytes = 0 writes zeros (used for keys beyond the sequence)
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copies `rows` rows of head_dim bfloat16 from a contiguous global tile into padded shared rows.
+// Rows at or beyond `live_rows` are zero-filled.  All threads of the block take part.
+__device__ __forceinline__ void copy_tile_async(unsigned char* dst, const __nv_bfloat16* src, int rows, int live_rows,
+                                                int head_dim) {
+  const int chunks_per_row = head_dim / 8;  // 16-byte pieces
+  const int row_bytes = tile_row_bytes(head_dim);
+  for (int c = threadIdx.x; c < rows * chunks_per_row; c += blockDim.x) {
+    const int r = c / chunks_per_row, j = c - r * chunks_per_row;
+    cp_async_16(smem_addr(dst + r * row_bytes + j * 16), src + (size_t)r * head_dim + j * 8, r < live_rows ? 16 : 0);
+  }
+}
+
+// The running state of one warp's 16 query rows: lane (g = lane / 4, t = lane % 4) holds rows g
+// and g + 8; `o` holds, for each 8-wide slice of head_dim, the four accumulators of the MMA layout.
+template <int D_TILES>
+struct SoftmaxState {
+  float m[2];        // running maximum of the scaled scores (base-2 exponent domain)
+  float l[2];        // this lane's share of the running sum
+  float o[D_TILES][4];
+  __device__ __forceinline__ void init() {
+    m[0] = m[1] = -INFINITY;
+    l[0] = l[1] = 0.f;
+#pragma unroll
+    for (int i = 0; i < D_TILES; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+  }
+};
+
+// One warp: scores of its 16 query rows (fragments qf[ks]) against the 16 keys that start at row
+// `key_row` of the key tile `ks_tile`, the online-softmax update, and the product with the same 16
+// rows of the value tile `vs_tile`.  `scale_log2` = scale * log2(e).  Keys whose absolute index is
+// not in [key_lo[r], key_hi[r]) are masked for row r (r = 0: row g, r = 1: row g + 8).
+template <int D_TILES>
+__device__ __forceinline__ void attend_16_keys(SoftmaxState<D_TILES>& st, const uint32_t (*qf)[4],
+                                               const unsigned char* ks_tile, const unsigned char* vs_tile,
+                                               int key_row, int key_abs, const int (&key_lo)[2], const int (&key_hi)[2],
+                                               int head_dim, float scale_log2) {
+  const int lane = threadIdx.x & 31, t = lane & 3;
+  const int row_bytes = tile_row_bytes(head_dim);
+  const int j = lane >> 3, r = lane & 7;
+  float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  // K operand: matrix j of an x4 load = keys (j / 2) * 8 .., dims ks * 16 + (j % 2) * 8 ..
+  const uint32_t k_base = smem_addr(ks_tile + (key_row + (j >> 1) * 8 + r) * row_bytes + (j & 1) * 16);
+#pragma unroll
+  for (int ks = 0; ks < D_TILES / 2; ++ks) {
+    if (ks * 16 < head_dim) {
+      uint32_t kf[4];
+      ldmatrix_x4(kf, k_base + ks * 32);
+      mma_16816(s[0], qf[ks], kf[0], kf[1]);
+      mma_16816(s[1], qf[ks], kf[2], kf[3]);
+    }
+  }
+  // mask, scale, row maxima
+  float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int key = key_abs + nt * 8 + 2 * t + (e & 1);
+      const int row = e >> 1;
+      const bool live = key >= key_lo[row] && key < key_hi[row];
+      s[nt][e] = live ? s[nt][e] * scale_log2 : -INFINITY;
+      tile_max[row] = fmaxf(tile_max[row], s[nt][e]);
+    }
+  float corr[2];
+#pragma unroll
+  for (int row = 0; row < 2; ++row) {
+    tile_max[row] = fmaxf(tile_max[row], __shfl_xor_sync(0xffffffffu, tile_max[row], 1));
+    tile_max[row] = fmaxf(tile_max[row], __shfl_xor_sync(0xffffffffu, tile_max[row], 2));
+    const float m_new = fmaxf(st.m[row], tile_max[row]);
+    // a row with no live key so far keeps m = -inf; exp2(-inf - -inf) must not be NaN
+    corr[row] = m_new == -INFINITY ? 1.f : exp2f(st.m[row] - m_new);
+    st.m[row] = m_new;
+    st.l[row] *= corr[row];
+  }
+  uint32_t pf[4];
+  {
+    float p[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = e >> 1;
+        p[nt][e] = st.m[row] == -INFINITY ? 0.f : exp2f(s[nt][e] - st.m[row]);
+        st.l[row] += p[nt][e];
+      }
+    pf[0] = pack_bf16(p[0][0], p[0][1]);
+    pf[1] = pack_bf16(p[0][2], p[0][3]);
+    pf[2] = pack_bf16(p[1][0], p[1][1]);
+    pf[3] = pack_bf16(p[1][2], p[1][3]);
+  }
+  // V operand (transposed load): matrix j = keys (j % 2) * 8 .., dims d0 + (j / 2) * 8 ..
+  const uint32_t v_base = smem_addr(vs_tile + (key_row + (j & 1) * 8 + r) * row_bytes + (j >> 1) * 16);
+#pragma unroll
+  for (int dt = 0; dt < D_TILES; dt += 2) {
+    if (dt * 8 < head_dim) {
+      uint32_t vf[4];
+      ldmatrix_x4_trans(vf, v_base + dt * 16);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        st.o[dt][e] *= corr[e >> 1];
+        st.o[dt + 1][e] *= corr[e >> 1];
+      }
+      mma_16816(st.o[dt], pf, vf[0], vf[1]);
+      mma_16816(st.o[dt + 1], pf, vf[2], vf[3]);
+    }
+  }
+}
+
+}  // namespace xrt

@@ -32,6 +32,8 @@ _SIGNATURES = {
                              _I, _I, _I, _I, _P],
     "xrt_attention_reference": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
     "xrt_gemm_reference": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "xrt_gemm_skinny": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
     "xrt_sample": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P],
     "xrt_mark_seen": [_P, _I, _P, _P, _I, _I, _P],
@@ -212,6 +214,48 @@ def gemm_reference(out, x, w, accumulate: bool = False) -> None:
     _check(library().xrt_gemm_reference(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0),
                                         out.stride(0), _code(x.dtype), _code(w.dtype), _code(out.dtype),
                                         1 if accumulate else 0, _stream()), "gemm_reference")
+
+
+SKINNY_MAX_ROWS = 64
+
+
+def gemm_skinny(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
+    """bfloat16 product for at most 64 rows that streams the weight once; ``mode`` is "store",
+    "accumulate" (into a float32 out) or "swiglu" (out[m, n] = silu(x . w[n]) * (x . w[n + up_rows]))."""
+    m, k = x.shape
+    n = out.shape[1]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_skinny: operands must be bfloat16")
+    rows_needed = n + up_rows if mode == "swiglu" else n
+    if w.shape[1] != k or w.shape[0] < rows_needed or out.shape[0] != m or (mode != "swiglu" and w.shape[0] != n):
+        raise KernelError(f"gemm_skinny: shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if x.stride(1) != 1 or out.stride(1) != 1 or not x.is_cuda or not out.is_cuda:
+        raise KernelError("gemm_skinny: rows must be contiguous and on a CUDA device")
+    code = {"store": 0, "accumulate": 1, "swiglu": 2}[mode]
+    _check(library().xrt_gemm_skinny(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
+                                     _code(out.dtype), code, up_rows, _stream()), "gemm_skinny")
+
+
+def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int,
+                     head_dim: int, scale: float, window: int, chunk: int, n_splits: int) -> None:
+    """bfloat16 attention of one token a sequence over its cache blocks, split along the keys."""
+    n = q.shape[0]
+    if q.shape != (n, n_heads * head_dim) or out.shape != q.shape or tok_slot.numel() != n or tok_pos.numel() != n:
+        raise KernelError("attention_decode: shapes do not fit")
+    if k_pool.shape != v_pool.shape or k_pool.shape[1:] != (n_kv_heads, 64, head_dim):
+        raise KernelError("attention_decode: the cache pool must be [blocks, kv heads, 64, head_dim]")
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty(n * n_heads * n_splits * head_dim, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(n * n_heads * n_splits * 2, dtype=torch.float32, device=q.device)
+    _check(library().xrt_attention_decode(
+        _ptr(out, "out", torch.bfloat16), _ptr(part_o, "part_o"), _ptr(part_ml, "part_ml"),
+        _ptr(q, "q", torch.bfloat16), _ptr(k_pool, "k_pool", torch.bfloat16), _ptr(v_pool, "v_pool", torch.bfloat16),
+        _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
+        _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
+        float(scale), int(window), int(chunk), int(n_splits), _stream()), "attention_decode")
+    if n_splits > 1:
+        add_launches(1)  # the combine kernel
 
 
 def fill_normal(out, key: int, mean: float, std: float) -> None:

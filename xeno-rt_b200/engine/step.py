@@ -23,6 +23,7 @@ from ..cache import Cache
 from ..core import RuntimeFault
 from ..csrc import ops
 from ..parts import StepContext
+from ..parts.context import context_bucket
 
 GRAPH_MAX_BATCH = 256
 
@@ -148,7 +149,7 @@ def build_context(entries, cache: Cache, vocab_size: int, dtype, device, pad_to:
 class _DecodeGraph:
     """One captured decode step for up to ``bucket`` sequences."""
 
-    def __init__(self, engine: "Engine", bucket: int):
+    def __init__(self, engine: "Engine", bucket: int, context: int):
         model, cache = engine.model, engine.cache
         self.bucket = bucket
         self.size = layout(bucket, bucket)["size"]
@@ -157,9 +158,8 @@ class _DecodeGraph:
         self.static[lay["slot"][0]:lay["slot"][1]] = -1
         self.static[lay["seq_slot"][0]:lay["seq_slot"][1]] = -1
         self.rows = torch.arange(bucket, dtype=torch.int32, device=model.device)
-        capacity = cache.blocks_per_seq * 64
         make = lambda: context_from(self.static, bucket, bucket, [1] * bucket, [0] * bucket, model.dtype,
-                                    max_context=capacity)
+                                    max_context=context)
         side = torch.cuda.Stream(device=model.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -189,7 +189,7 @@ class Engine:
         if use_graphs is None:
             use_graphs = os.environ.get("XRT_NO_GRAPHS", "0") in ("", "0")
         self.use_graphs = use_graphs and model.device.type == "cuda"
-        self._graphs: dict[int, _DecodeGraph] = {}
+        self._graphs: dict[tuple, _DecodeGraph] = {}  # (batch bucket, context bucket) -> graph
 
     def open_slot(self) -> int:
         return self.cache.open_slot()
@@ -222,10 +222,11 @@ class Engine:
         n = len(entries)
         bucket = 1 << (n - 1).bit_length()
         starts = [self.cache.reserve(e.slot, 1) for e in entries]
-        g = self._graphs.get(bucket)
+        key = (bucket, context_bucket(max(starts) + 1))
+        g = self._graphs.get(key)
         if g is None:
             self.cache.flush_tables()
-            g = self._graphs[bucket] = _DecodeGraph(self, bucket)
+            g = self._graphs[key] = _DecodeGraph(self, *key)
         turn, host = self.staging.take(g.size)
         wanted = fill_arrays(host.numpy(), entries, starts, bucket, bucket)
         g.static.copy_(host, non_blocking=True)

@@ -2,6 +2,29 @@
 and the caller uses the kernel that takes any."""
 from __future__ import annotations
 
+from ..csrc import ops
+from .context import context_bucket
+
+SM_COUNT = 148
+DECODE_BLOCKS_PER_SM = 3
+
+
+def decode_split(n_seqs: int, n_kv_heads: int, max_context: int):
+    """(keys a split, number of splits) for decode attention: enough thread blocks to fill the GPU
+    when sequences are few, at least two tiles of 64 keys a split where the context allows."""
+    blocks = max(1, (max_context + 63) // 64)
+    want = -(-SM_COUNT * DECODE_BLOCKS_PER_SM // (n_seqs * n_kv_heads))
+    splits = max(1, min(want, (blocks + 1) // 2))
+    chunk = 64 * (-(-blocks // splits))
+    return chunk, -(-blocks * 64 // chunk)
+
 
 def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window) -> bool:
+    if n_heads // n_kv_heads > 16:
+        return False
+    if ctx.all_single and ctx.n_tokens <= 65535:
+        chunk, n_splits = decode_split(ctx.n_tokens, n_kv_heads, context_bucket(ctx.max_context))
+        ops.attention_decode(out, q, store.k, store.v, ctx.tok_slot, ctx.tok_pos, store.block_table, n_heads,
+                             n_kv_heads, head_dim, scale, window, chunk, n_splits)
+        return True
     return False

@@ -38,3 +38,11 @@ class StepContext:
     captured: bool = False  # the step is being captured into (or replayed from) a CUDA graph:
     #                         launch shapes must not depend on the sequences' lengths
     shared: dict = field(default_factory=dict)
+
+
+def context_bucket(max_context: int) -> int:
+    """The power of two (at least 256) at or above a context length.  Launch shapes that depend on
+    the context (how attention splits the keys) are chosen from this, so that they change only
+    when a power of two is crossed: a captured CUDA graph stays valid in between, and a step gives
+    the same result replayed from a graph or launched kernel by kernel."""
+    return max(256, 1 << (max(1, int(max_context)) - 1).bit_length())

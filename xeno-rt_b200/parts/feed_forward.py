@@ -28,9 +28,14 @@ class SwiGLUFeedForward:
         self.act_dtype = torch_dtype(dtype)
 
     def forward(self, h, residual, ctx):
-        gate_up = linear(h, self.w_gate_up, out_dtype=torch.float32)
         act = torch.empty((h.shape[0], self.inner), dtype=self.act_dtype, device=h.device)
-        ops.swiglu(act, gate_up)
+        fused = False
+        if self.act_dtype == torch.bfloat16 and h.dtype == torch.bfloat16:
+            from . import linear_bf16
+            fused = linear_bf16.run_swiglu(act, h, self.w_gate_up, self.inner)
+        if not fused:
+            gate_up = linear(h, self.w_gate_up, out_dtype=torch.float32)
+            ops.swiglu(act, gate_up)
         linear(act, self.w_down, accumulate_into=residual)
 
 
