@@ -79,17 +79,18 @@ gemm_skinny_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
     }
   }
   // the last, partial block of 32 (K is a multiple of 8: a 16-byte piece is wholly inside or outside)
-  if ((K & 31) != 0 && (n_full % k_ways) == k_lane) {
+  if ((K & 31) != 0 && (n_full % k_ways) == k_lane) {  // uniform over the warp
     const int k0 = n_full * 32 + t * 8;
-    if (k0 < K) {
-      const uint4 wv = ldg_stream(wp + k0);
+    const bool inside = k0 < K;  // differs between lanes: only the loads are conditional, every
+    //                              lane runs the MMAs (a lane outside contributes zeros)
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const uint4 wv = inside ? ldg_stream(wp + k0) : zero;
 #pragma unroll
-      for (int mt = 0; mt < M_TILES; ++mt) {
-        const uint4 xa = *reinterpret_cast<const uint4*>(xlo[mt] + k0);
-        const uint4 xb = *reinterpret_cast<const uint4*>(xhi[mt] + k0);
-        mma_bf16_16816(acc[mt], xa.x, xb.x, xa.y, xb.y, wv.x, wv.y);
-        mma_bf16_16816(acc[mt], xa.z, xb.z, xa.w, xb.w, wv.z, wv.w);
-      }
+    for (int mt = 0; mt < M_TILES; ++mt) {
+      const uint4 xa = inside ? *reinterpret_cast<const uint4*>(xlo[mt] + k0) : zero;
+      const uint4 xb = inside ? *reinterpret_cast<const uint4*>(xhi[mt] + k0) : zero;
+      mma_bf16_16816(acc[mt], xa.x, xb.x, xa.y, xb.y, wv.x, wv.y);
+      mma_bf16_16816(acc[mt], xa.z, xb.z, xa.w, xb.w, wv.z, wv.w);
     }
   }
 

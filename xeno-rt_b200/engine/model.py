@@ -41,6 +41,10 @@ class Model:
         self.final_norm = build("norm", spec.final_norm)
         self.lm_head = build("lm_head", spec.lm_head)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        parts = [self.embedding, self.final_norm, self.lm_head]
+        for layer in self.layers:
+            parts += [layer.mixer_norm, layer.mixer, layer.ffn_norm, layer.ffn]
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
 
     # ------------------------------------------------------------------ construction
     @classmethod

@@ -188,7 +188,7 @@ class Engine:
         self.staging = _Staging(model.device)
         if use_graphs is None:
             use_graphs = os.environ.get("XRT_NO_GRAPHS", "0") in ("", "0")
-        self.use_graphs = use_graphs and model.device.type == "cuda"
+        self.use_graphs = use_graphs and model.device.type == "cuda" and model.graph_safe
         self._graphs: dict[tuple, _DecodeGraph] = {}  # (batch bucket, context bucket) -> graph
 
     def open_slot(self) -> int:
@@ -203,7 +203,7 @@ class Engine:
         their ``want`` lists, or None if nothing is wanted."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         model = self.model
-        use_graph = self.use_graphs if graph is None else graph
+        use_graph = self.use_graphs if graph is None else (graph and self.model.graph_safe)
         if (use_graph and pad_to is None and len(entries) <= GRAPH_MAX_BATCH
                 and all(len(e.tokens) == 1 for e in entries)):
             return self._graph_step(entries)

@@ -25,6 +25,8 @@ class GroupedQueryAttention:
     weights: ``q`` [n_heads*head_dim, width], ``k``, ``v`` [n_kv_heads*head_dim, width],
     ``o`` [width, n_heads*head_dim], and with qk_norm ``q_norm``, ``k_norm`` [head_dim]."""
 
+    graph_safe = True
+
     @classmethod
     def weight_shapes(cls, params):
         d, nh, nkv, hd = params["width"], params["n_heads"], params["n_kv_heads"], params["head_dim"]

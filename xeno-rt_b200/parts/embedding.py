@@ -12,6 +12,8 @@ class TokenEmbedding:
     """x = E[token], no scaling (crates/xrt-models/src/llama.rs:1042-1055).
     params: ``vocab_size``, ``width``.  weights: ``weight`` [vocab, width]."""
 
+    graph_safe = True
+
     @classmethod
     def weight_shapes(cls, params):
         return {"weight": ((params["vocab_size"], params["width"]), "matrix")}
@@ -31,6 +33,8 @@ class OutputHead:
     """logits = W . normed, no scaling or cap (crates/xrt-models/src/llama.rs:604-613); W is the
     embedding when the model ties them (llama.rs:301-305), which the spec expresses by giving both
     parts the same tensor name.  params: ``vocab_size``, ``width``.  weights: ``weight``."""
+
+    graph_safe = True
 
     @classmethod
     def weight_shapes(cls, params):

@@ -14,6 +14,8 @@ class SwiGLUFeedForward:
     """params: ``width``, ``inner`` (the feed-forward width).
     weights: ``gate``, ``up`` [inner, width], ``down`` [width, inner]."""
 
+    graph_safe = True
+
     @classmethod
     def weight_shapes(cls, params):
         d, f = params["width"], params["inner"]

@@ -12,6 +12,8 @@ from .registry import register_part
 class RMSNorm:
     """params: ``width``, ``eps``.  weights: ``weight`` [width]."""
 
+    graph_safe = True
+
     @classmethod
     def weight_shapes(cls, params):
         return {"weight": ((params["width"],), "vector")}

@@ -16,6 +16,11 @@ position        ``tables(ctx) -> tensor | None``: per-step rotation table [T, ha
                 (cos, sin), cached in ``ctx.shared``; None means no rotation.
 embedding       ``forward(token_ids, error_flag) -> x`` float32 [T, D].
 lm_head         ``forward(normed) -> logits`` float32 [R, V].
+A part class may set ``graph_safe = True`` to say that its ``forward`` only launches device work
+in stream order whose shapes depend on nothing but the number of tokens and the context bucket (no
+reads back to the host, no data-dependent Python branches); decode steps of a model whose parts
+all say so are captured in CUDA graphs, any other model runs every step kernel by kernel.
+
 arrangement     a function ``(layer_parts, x, ctx, store, owns_cache) -> None`` that runs one layer.
 """
 from __future__ import annotations
