@@ -335,3 +335,61 @@ def test_attention_decode_finds_a_far_key_and_respects_the_window():
         ops().attention_reference(ref, qf, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd),
                                   window=S - far)
         assert torch.allclose(out.float(), ref.float(), atol=3e-2)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (5, 1, 48), (8, 2, 128), (6, 3, 80), (2, 1, 256)])
+def test_attention_prefill_kernel(nh, nkv, hd):
+    """Four sequences end to end: a whole prompt of 150 tokens, one of a single token, one that
+    continues at position 100 with 70 more tokens (across a block edge), and a skipped one."""
+    torch.manual_seed(nh * hd + 1)
+    totals = [150, 1, 170, 64]
+    starts = [0, 0, 100, 0]
+    new = [150, 1, 70, 5]
+    k_pool, v_pool, table = _cache_for(totals, nkv, hd, torch.bfloat16, shuffle_seed=hd + 1)
+    ks = [torch.randn(n, nkv, hd, device=DEV) for n in totals]
+    vs = [torch.randn(n, nkv, hd, device=DEV) for n in totals]
+    for s in range(4):
+        _fill_cache(k_pool, v_pool, table, s + 1, ks[s], vs[s])
+    T = sum(new)
+    q = torch.randn(T, nh * hd, device=DEV).to(torch.bfloat16)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(new)]), dtype=torch.int32, device=DEV)
+    seq_slot = torch.tensor([1, 2, 3, -1], dtype=torch.int32, device=DEV)
+    seq_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    out = torch.full_like(q, 5.0)
+    ops().attention_prefill(out, q, k_pool, v_pool, cu, seq_slot, seq_start, table, max(new), nh, nkv, hd,
+                            1 / math.sqrt(hd))
+    bf = lambda x: f64(x.to(torch.bfloat16)).reshape(x.shape[0], -1)
+    at = 0
+    for s in range(3):
+        q_full = np.zeros((totals[s], nh * hd))
+        q_full[starts[s]:] = f64(q[at:at + new[s]])
+        want = pm.causal_gqa_attention(q_full, bf(ks[s]), bf(vs[s]), nh, nkv, hd)[starts[s]:]
+        assert rel(out[at:at + new[s]], want) < 1.5e-2, s
+        at += new[s]
+    assert bool((out[at:] == 5.0).all())  # the skipped sequence's rows are untouched
+    # the same rows through the kernel that takes any case
+    ref = torch.empty_like(q)
+    tok_slot = torch.tensor([1] * 150 + [2] + [3] * 70 + [-1] * 5, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(list(range(150)) + [0] + list(range(100, 170)) + [0] * 5, dtype=torch.int32, device=DEV)
+    ops().attention_reference(ref, q, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd))
+    assert torch.allclose(out[:221].float(), ref[:221].float(), atol=3e-2)
+
+
+def test_attention_prefill_window_edge():
+    """With a window of 70 keys, row i sees keys i-69 .. i: the kernel must agree with the plain
+    windowed attention at every row, in particular where the window's edge crosses a block edge."""
+    nh, nkv, hd, S, window = 4, 2, 64, 200, 70
+    k_pool, v_pool, table = _cache_for([S], nkv, hd, torch.bfloat16, shuffle_seed=5)
+    k = torch.randn(S, nkv, hd, device=DEV)
+    v = torch.randn(S, nkv, hd, device=DEV)
+    _fill_cache(k_pool, v_pool, table, 1, k, v)
+    q = (torch.randn(S, nh * hd, device=DEV) * 2).to(torch.bfloat16)
+    cu = torch.tensor([0, S], dtype=torch.int32, device=DEV)
+    one = lambda x: torch.tensor([x], dtype=torch.int32, device=DEV)
+    out = torch.empty_like(q)
+    ops().attention_prefill(out, q, k_pool, v_pool, cu, one(1), one(0), table, S, nh, nkv, hd, 1 / math.sqrt(hd), window)
+    bf = lambda x: f64(x.to(torch.bfloat16)).reshape(x.shape[0], -1)
+    want = pm.causal_gqa_attention(f64(q), bf(k), bf(v), nh, nkv, hd, window=window)
+    assert rel(out, want) < 1.5e-2
+    full = pm.causal_gqa_attention(f64(q), bf(k), bf(v), nh, nkv, hd)
+    assert np.abs(want[150] - full[150]).max() > 0.05  # the window matters in this case

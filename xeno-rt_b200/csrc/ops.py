@@ -34,6 +34,7 @@ _SIGNATURES = {
     "xrt_gemm_reference": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_skinny": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
     "xrt_sample": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P],
     "xrt_mark_seen": [_P, _I, _P, _P, _I, _I, _P],
@@ -256,6 +257,23 @@ def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_h
         float(scale), int(window), int(chunk), int(n_splits), _stream()), "attention_decode")
     if n_splits > 1:
         add_launches(1)  # the combine kernel
+
+
+def attention_prefill(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, block_table, max_new: int,
+                      n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """bfloat16 causal attention of sequences laid end to end, each continuing at seq_start."""
+    n = q.shape[0]
+    n_seqs = seq_slot.numel()
+    if q.shape != (n, n_heads * head_dim) or out.shape != q.shape or cu_seqlens.numel() != n_seqs + 1:
+        raise KernelError("attention_prefill: shapes do not fit")
+    if k_pool.shape != v_pool.shape or k_pool.shape[1:] != (n_kv_heads, 64, head_dim):
+        raise KernelError("attention_prefill: the cache pool must be [blocks, kv heads, 64, head_dim]")
+    _check(library().xrt_attention_prefill(
+        _ptr(out, "out", torch.bfloat16), _ptr(q, "q", torch.bfloat16), _ptr(k_pool, "k_pool", torch.bfloat16),
+        _ptr(v_pool, "v_pool", torch.bfloat16), _ptr(cu_seqlens, "cu_seqlens", torch.int32),
+        _ptr(seq_slot, "seq_slot", torch.int32), _ptr(seq_start, "seq_start", torch.int32),
+        _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n_seqs, int(max_new), n_heads,
+        n_kv_heads, head_dim, float(scale), int(window), _stream()), "attention_prefill")
 
 
 def fill_normal(out, key: int, mean: float, std: float) -> None:

@@ -72,7 +72,8 @@ class GroupedQueryAttention:
         ops.qk_rope_kv_write(q, store.k, store.v, qkv, self.q_width, self.q_width + self.kv_width, self.q_norm,
                              self.k_norm, self.eps, self.position.tables(ctx), ctx.tok_slot, ctx.tok_pos,
                              store.block_table, self.n_heads, self.n_kv_heads, self.head_dim, write_kv=owns_cache)
-        attended = torch.empty_like(q)
+        # padding rows belong to no sequence: kernels that walk sequences leave them unwritten
+        attended = torch.zeros_like(q) if sum(ctx.new_lens) < ctx.n_tokens else torch.empty_like(q)
         self.attend(attended, q, ctx, store)
         linear(attended, self.w_o, accumulate_into=residual)
 

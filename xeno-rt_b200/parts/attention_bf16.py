@@ -27,4 +27,8 @@ def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window) -> boo
         ops.attention_decode(out, q, store.k, store.v, ctx.tok_slot, ctx.tok_pos, store.block_table, n_heads,
                              n_kv_heads, head_dim, scale, window, chunk, n_splits)
         return True
+    if ctx.n_seqs <= 65535 and n_heads <= 65535:
+        ops.attention_prefill(out, q, store.k, store.v, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
+                              store.block_table, ctx.max_new, n_heads, n_kv_heads, head_dim, scale, window)
+        return True
     return False

@@ -14,10 +14,15 @@ def aligned(x, weight) -> bool:
 def run(out, x, weight, accumulate: bool) -> bool:
     if not aligned(x, weight):
         return False
-    if x.shape[0] <= ops.SKINNY_MAX_ROWS:
-        ops.gemm_skinny(out, x, weight, "accumulate" if accumulate else "store")
+    mode = "accumulate" if accumulate else "store"
+    rows = x.shape[0]
+    if rows <= ops.SKINNY_MAX_ROWS:
+        ops.gemm_skinny(out, x, weight, mode)
         return True
-    return False
+    for lo in range(0, rows, ops.SKINNY_MAX_ROWS):
+        hi = min(rows, lo + ops.SKINNY_MAX_ROWS)
+        ops.gemm_skinny(out[lo:hi], x[lo:hi], weight, mode)
+    return True
 
 
 def run_swiglu(out, x, weight_gate_up, inner: int) -> bool:
@@ -25,7 +30,8 @@ def run_swiglu(out, x, weight_gate_up, inner: int) -> bool:
     fused kernel takes the shape."""
     if not aligned(x, weight_gate_up):
         return False
-    if x.shape[0] <= ops.SKINNY_MAX_ROWS:
-        ops.gemm_skinny(out, x, weight_gate_up, "swiglu", up_rows=inner)
-        return True
-    return False
+    rows = x.shape[0]
+    for lo in range(0, rows, ops.SKINNY_MAX_ROWS):
+        hi = min(rows, lo + ops.SKINNY_MAX_ROWS)
+        ops.gemm_skinny(out[lo:hi], x[lo:hi], weight_gate_up, "swiglu", up_rows=inner)
+    return True
