@@ -241,10 +241,21 @@ def run_ours(args) -> int:
     torch.cuda.synchronize()
     setup_s = time.time() - t0
 
+    if args.only == "prefill":  # a short run for profiling: one prompt of 2,048 tokens
+        prefill_ms = time_prefill(model, PREFILL_TOKENS, iters=max(1, args.steps), warmup=args.warmup)
+        flops = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
+        print(json.dumps({"only": "prefill", "ms": round(prefill_ms, 3), "tokens": PREFILL_TOKENS, "layers": n_layers,
+                          "tflops": round(flops / (prefill_ms / 1e3) / 1e12, 1)}))
+        return 0
     main = time_decode(model, args.batch, args.context, args.steps, args.warmup, sample_clocks=True)
     bytes_step = weight_bytes_per_step(cfg, n_layers) + args.batch * main["mean_context"] * kv_bytes_per_token(cfg, n_layers)
     achieved = bytes_step / (main["ms_per_step"] / 1e3) / 1e9
     points = {}
+    if args.only == "decode":  # a short run for profiling: the headline step alone
+        print(json.dumps({"only": "decode", "ms_per_step": round(main["ms_per_step"], 4),
+                          "tokens_per_s": round(main["tokens_per_s"], 1), "roofline_gbs": round(achieved, 1),
+                          "layers": n_layers, "batch": args.batch, "context": args.context}))
+        return 0
     for b in (1, 64):
         r = time_decode(model, b, args.context, max(8, args.steps // 2), args.warmup)
         points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
@@ -287,6 +298,8 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=4096)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")
+    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                        help="a short run of one part, for profiling; prints its own small JSON line")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -296,7 +309,7 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
-    if args.warmup < 3:
+    if args.warmup < 3 and args.only == "all":
         args.warmup = 3
     return run_ours(args)
 
