@@ -247,3 +247,79 @@ XRT_EXPORT int xrt_attention_decode(void* out, float* part_o, float* part_ml, co
   }
   return XRT_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same attention for callers that cannot allocate: the scratch lives in this library's device
+// image.  See attention_decode_static.h for who needs this and what the limits are.
+#include <stdio.h>
+
+#include "attention_decode_static.h"
+
+namespace xrt {
+
+constexpr size_t STATIC_SCRATCH_FLOATS = XRT_DECODE_STATIC_SCRATCH_BYTES / sizeof(float);
+constexpr int STATIC_MAX_DEVICES = 64;
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float decode_static_scratch[STATIC_SCRATCH_FLOATS];
+static float* decode_static_scratch_address[STATIC_MAX_DEVICES] = {};
+
+static void refuse(char* message, int message_len, const char* text) {
+  if (message != nullptr && message_len > 0) snprintf(message, (size_t)message_len, "%s", text);
+}
+
+}  // namespace xrt
+
+int xrt_attention_decode_static(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                const int* tok_slot, const int* tok_pos, const int* block_table, int max_blocks,
+                                int n_tokens, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                                int chunk, int n_splits, cudaStream_t stream, char* message, int message_len) {
+  char text[256];
+  if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || n_splits <= 0) {
+    xrt::refuse(message, message_len, "xrt_attention_decode_static: a size is not positive");
+    return XRT_ERR_ARGUMENT;
+  }
+  // floats of scratch: the (maximum, sum) pairs first, rounded up to 64 floats, then the outputs
+  const size_t rows = (size_t)n_tokens * n_heads * n_splits;
+  const size_t ml_floats = (rows * 2 + 63) / 64 * 64;
+  const size_t need = n_splits > 1 ? ml_floats + rows * head_dim : 0;
+  if (need > xrt::STATIC_SCRATCH_FLOATS) {
+    snprintf(text, sizeof(text),
+             "xrt_attention_decode_static: %d tokens x %d heads x %d splits need %zu bytes of scratch, the "
+             "built-in scratch holds %u; use fewer splits or tokens, or xrt_attention_decode with scratch of your own",
+             n_tokens, n_heads, n_splits, need * sizeof(float), (unsigned)XRT_DECODE_STATIC_SCRATCH_BYTES);
+    xrt::refuse(message, message_len, text);
+    return XRT_ERR_SCRATCH;
+  }
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) {
+    xrt::refuse(message, message_len, "xrt_attention_decode_static: cudaGetDevice failed");
+    return (int)err;
+  }
+  if (device < 0 || device >= xrt::STATIC_MAX_DEVICES) {
+    xrt::refuse(message, message_len, "xrt_attention_decode_static: device ordinal out of range");
+    return XRT_ERR_UNSUPPORTED;
+  }
+  // Set-up, once a device, with that device current: the device address of the scratch array.
+  if (xrt::decode_static_scratch_address[device] == nullptr) {
+    float* address = nullptr;
+    err = cudaGetSymbolAddress((void**)&address, xrt::decode_static_scratch);
+    if (err != cudaSuccess || address == nullptr) {
+      snprintf(text, sizeof(text), "xrt_attention_decode_static: cudaGetSymbolAddress failed: %s",
+               cudaGetErrorString(err));
+      xrt::refuse(message, message_len, text);
+      return err != cudaSuccess ? (int)err : XRT_ERR_UNSUPPORTED;
+    }
+    xrt::decode_static_scratch_address[device] = address;
+  }
+  float* scratch = xrt::decode_static_scratch_address[device];
+  const int status = xrt_attention_decode(out, scratch + ml_floats, scratch, q, k_pool, v_pool, tok_slot, tok_pos,
+                                          block_table, max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale,
+                                          window, chunk, n_splits, stream);
+  if (status == XRT_ERR_ARGUMENT) xrt::refuse(message, message_len, "xrt_attention_decode_static: the kernel refused its arguments");
+  if (status == XRT_ERR_UNSUPPORTED)
+    xrt::refuse(message, message_len, "xrt_attention_decode_static: head_dim must be a multiple of 16 up to 256, at most "
+                                      "16 query heads a kv head, chunk a multiple of 64, at most 65535 tokens");
+  return status;
+}
