@@ -237,43 +237,43 @@ def test_fill_normal_matches_the_host_generator(dtype):
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 16, 17, 40, 64])
-@pytest.mark.parametrize("n,k", [(203, 104), (64, 4096), (136, 96), (8, 40)])
-def test_gemm_skinny(m, n, k):
+@pytest.mark.parametrize("n,k", [(203, 104), (64, 4096), (136, 96), (8, 40), (24, 1544)])
+def test_gemm_stream(m, n, k):
     x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
     want = f64(x) @ f64(w).T
     out = torch.empty(m, n, device=DEV)
-    ops().gemm_skinny(out, x, w)
+    ops().gemm_stream(out, x, w)
     assert rel(out, want) < 1e-5  # bfloat16 operands are exact in float64; only the sum's order differs
     out_b = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
-    ops().gemm_skinny(out_b, x, w)
+    ops().gemm_stream(out_b, x, w)
     assert rel(out_b, want) < 5e-3
     base = torch.randn(m, n, device=DEV)
     acc = base.clone()
-    ops().gemm_skinny(acc, x, w, "accumulate")
+    ops().gemm_stream(acc, x, w, "accumulate")
     assert rel(acc, f64(base) + want) < 1e-5
     # a row's result does not depend on how many rows the call carries
     one = torch.empty(1, n, device=DEV)
-    ops().gemm_skinny(one, x[m - 1:m].contiguous(), w)
+    ops().gemm_stream(one, x[m - 1:m].contiguous(), w)
     assert torch.equal(one[0], out[m - 1])
 
 
 @pytest.mark.parametrize("m,inner,k", [(1, 136, 96), (9, 203, 104), (33, 64, 4096)])
-def test_gemm_skinny_swiglu(m, inner, k):
+def test_gemm_stream_swiglu(m, inner, k):
     x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(2 * inner, k, device=DEV) * 0.1).to(torch.bfloat16)
     out = torch.empty(m, inner, device=DEV, dtype=torch.bfloat16)
-    ops().gemm_skinny(out, x, w, "swiglu", up_rows=inner)
+    ops().gemm_stream(out, x, w, "swiglu", up_rows=inner)
     want = pm.swiglu(f64(x) @ f64(w[:inner]).T, f64(x) @ f64(w[inner:]).T)
     assert rel(out, want) < 5e-3
 
 
-def test_gemm_skinny_refuses_what_it_cannot_take():
+def test_gemm_stream_refuses_what_it_cannot_take():
     from xeno_rt_b200.core import KernelError
     x = torch.randn(2, 100, device=DEV).to(torch.bfloat16)  # K = 100 is no multiple of 8
     w = torch.randn(16, 100, device=DEV).to(torch.bfloat16)
     with pytest.raises(KernelError, match="outside what the kernel handles"):
-        ops().gemm_skinny(torch.empty(2, 16, device=DEV), x, w)
+        ops().gemm_stream(torch.empty(2, 16, device=DEV), x, w)
 
 
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (5, 1, 48), (32, 8, 128), (6, 3, 80), (16, 1, 256), (8, 8, 64)])

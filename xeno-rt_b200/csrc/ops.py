@@ -32,7 +32,7 @@ _SIGNATURES = {
                              _I, _I, _I, _I, _P],
     "xrt_attention_reference": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
     "xrt_gemm_reference": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
-    "xrt_gemm_skinny": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "xrt_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
@@ -217,24 +217,22 @@ def gemm_reference(out, x, w, accumulate: bool = False) -> None:
                                         1 if accumulate else 0, _stream()), "gemm_reference")
 
 
-SKINNY_MAX_ROWS = 64
-
-
-def gemm_skinny(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
+STREAM_MAX_ROWS = 64
+def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
     """bfloat16 product for at most 64 rows that streams the weight once; ``mode`` is "store",
     "accumulate" (into a float32 out) or "swiglu" (out[m, n] = silu(x . w[n]) * (x . w[n + up_rows]))."""
     m, k = x.shape
     n = out.shape[1]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
-        raise KernelError("gemm_skinny: operands must be bfloat16")
+        raise KernelError("gemm_stream: operands must be bfloat16")
     rows_needed = n + up_rows if mode == "swiglu" else n
     if w.shape[1] != k or w.shape[0] < rows_needed or out.shape[0] != m or (mode != "swiglu" and w.shape[0] != n):
-        raise KernelError(f"gemm_skinny: shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        raise KernelError(f"gemm_stream: shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     if x.stride(1) != 1 or out.stride(1) != 1 or not x.is_cuda or not out.is_cuda:
-        raise KernelError("gemm_skinny: rows must be contiguous and on a CUDA device")
+        raise KernelError("gemm_stream: rows must be contiguous and on a CUDA device")
     code = {"store": 0, "accumulate": 1, "swiglu": 2}[mode]
-    _check(library().xrt_gemm_skinny(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
-                                     _code(out.dtype), code, up_rows, _stream()), "gemm_skinny")
+    _check(library().xrt_gemm_stream(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
+                                     _code(out.dtype), code, up_rows, _stream()), "gemm_stream")
 
 
 def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int,

@@ -16,12 +16,12 @@ def run(out, x, weight, accumulate: bool) -> bool:
         return False
     mode = "accumulate" if accumulate else "store"
     rows = x.shape[0]
-    if rows <= ops.SKINNY_MAX_ROWS:
-        ops.gemm_skinny(out, x, weight, mode)
+    if rows <= ops.STREAM_MAX_ROWS:
+        ops.gemm_stream(out, x, weight, mode)
         return True
-    for lo in range(0, rows, ops.SKINNY_MAX_ROWS):
-        hi = min(rows, lo + ops.SKINNY_MAX_ROWS)
-        ops.gemm_skinny(out[lo:hi], x[lo:hi], weight, mode)
+    for lo in range(0, rows, ops.STREAM_MAX_ROWS):
+        hi = min(rows, lo + ops.STREAM_MAX_ROWS)
+        ops.gemm_stream(out[lo:hi], x[lo:hi], weight, mode)
     return True
 
 
@@ -31,7 +31,7 @@ def run_swiglu(out, x, weight_gate_up, inner: int) -> bool:
     if not aligned(x, weight_gate_up):
         return False
     rows = x.shape[0]
-    for lo in range(0, rows, ops.SKINNY_MAX_ROWS):
-        hi = min(rows, lo + ops.SKINNY_MAX_ROWS)
-        ops.gemm_skinny(out[lo:hi], x[lo:hi], weight_gate_up, "swiglu", up_rows=inner)
+    for lo in range(0, rows, ops.STREAM_MAX_ROWS):
+        hi = min(rows, lo + ops.STREAM_MAX_ROWS)
+        ops.gemm_stream(out[lo:hi], x[lo:hi], weight_gate_up, "swiglu", up_rows=inner)
     return True
