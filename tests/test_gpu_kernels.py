@@ -393,3 +393,47 @@ def test_attention_prefill_window_edge():
     assert rel(out, want) < 1.5e-2
     full = pm.causal_gqa_attention(f64(q), bf(k), bf(v), nh, nkv, hd)
     assert np.abs(want[150] - full[150]).max() > 0.05  # the window matters in this case
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (65, 8, 8), (200, 300, 136), (129, 513, 1032), (1000, 136, 96)])
+def test_gemm_tcgen05(m, n, k):
+    """Sizes that are no multiple of the 128 x 256 x 64 tile: TMA zero-fills what reaches beyond."""
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    want = f64(x) @ f64(w).T
+    out = torch.full((m, n), 7.0, device=DEV)
+    ops().gemm_tcgen05(out, x, w)
+    assert rel(out, want) < 1e-5
+    out_b = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    ops().gemm_tcgen05(out_b, x, w)
+    assert rel(out_b, want) < 5e-3
+    base = torch.randn(m, n, device=DEV)
+    acc = base.clone()
+    ops().gemm_tcgen05(acc, x, w, "accumulate")
+    assert rel(acc, f64(base) + want) < 1e-5
+    from xeno_rt_b200.csrc import ops as o
+    o.check_error_flag(DEV)
+
+
+def test_gemm_tcgen05_many_tiles_and_row_invariance():
+    """More tiles than multiprocessors (the persistent loop and both accumulators are used), and a
+    row's result is the same bits whatever the number of rows."""
+    m, n, k = 700, 2100, 520
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    out = torch.empty(m, n, device=DEV)
+    ops().gemm_tcgen05(out, x, w)
+    assert rel(out, f64(x) @ f64(w).T) < 1e-5
+    part = torch.empty(70, n, device=DEV)
+    ops().gemm_tcgen05(part, x[300:370].contiguous(), w)
+    assert torch.equal(part, out[300:370])
+
+
+@pytest.mark.parametrize("m,inner,k", [(128, 128, 64), (130, 203, 104), (300, 136, 96)])
+def test_gemm_tcgen05_swiglu(m, inner, k):
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inner, k, device=DEV) * 0.1).to(torch.bfloat16)
+    out = torch.empty(m, inner, device=DEV, dtype=torch.bfloat16)
+    ops().gemm_tcgen05(out, x, w, "swiglu", up_rows=inner)
+    want = pm.swiglu(f64(x) @ f64(w[:inner]).T, f64(x) @ f64(w[inner:]).T)
+    assert rel(out, want) < 5e-3

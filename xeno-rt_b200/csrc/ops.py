@@ -33,6 +33,7 @@ _SIGNATURES = {
     "xrt_attention_reference": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
     "xrt_gemm_reference": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "xrt_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
@@ -218,6 +219,48 @@ def gemm_reference(out, x, w, accumulate: bool = False) -> None:
 
 
 STREAM_MAX_ROWS = 64
+_error_flags: dict = {}
+
+
+def error_flag(device) -> torch.Tensor:
+    """The int32 flag of ``device`` that kernels raise when a bounded wait inside them ran out.
+    Made when a model is built (never inside a stream capture)."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _error_flags:
+        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_flags[key]
+
+
+def check_error_flag(device) -> None:
+    """Reads the flag back (a synchronisation) and raises if a kernel raised it."""
+    flag = error_flag(device)
+    value = int(flag.item())
+    if value != 0:
+        flag.zero_()
+        raise KernelError(f"a kernel reported error {value}: a bounded wait on a copy or a tensor-core operation ran "
+                          f"out; results of the last steps are not valid")
+
+
+def gemm_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
+    """bfloat16 product for many rows on the tcgen05 tensor cores with TMA-fed operands; modes as
+    for ``gemm_stream``."""
+    m, k = x.shape
+    n = out.shape[1]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tcgen05: operands must be bfloat16")
+    rows_needed = n + up_rows if mode == "swiglu" else n
+    if w.shape[1] != k or w.shape[0] < rows_needed or out.shape[0] != m or (mode != "swiglu" and w.shape[0] != n):
+        raise KernelError(f"gemm_tcgen05: shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if x.stride(1) != 1 or out.stride(1) != 1 or not x.is_cuda or not out.is_cuda:
+        raise KernelError("gemm_tcgen05: rows must be contiguous and on a CUDA device")
+    code = {"store": 0, "accumulate": 1, "swiglu": 2}[mode]
+    flag = error_flag(x.device)
+    _check(library().xrt_gemm_tcgen05(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
+                                      w.shape[0], _code(out.dtype), code, up_rows, flag.data_ptr(), _stream()),
+           "gemm_tcgen05")
+
+
 def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
     """bfloat16 product for at most 64 rows that streams the weight once; ``mode`` is "store",
     "accumulate" (into a float32 out) or "swiglu" (out[m, n] = silu(x . w[n]) * (x . w[n + up_rows]))."""

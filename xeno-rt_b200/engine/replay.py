@@ -33,6 +33,7 @@ class Replayer:
             if rid not in self.slots:
                 raise RuntimeFault(f"step {record.get('step')}: request {rid!r} ends but was never seen")
             self.engine.close_slot(self.slots.pop(rid))
+        self.engine.check_errors()
         if logits is None:
             return None
         return logits.float().cpu().numpy().astype(np.float32)

@@ -43,7 +43,9 @@ class DeviceBackend:
         n = len(slots)
         row_slot = torch.tensor(slots, dtype=torch.int32, device=self.engine.model.device)
         ids = self.sampler.sample(logits[:n], row_slot, [r.sampler_config() for r in requests])
-        return ids.tolist()
+        out = ids.tolist()
+        self.engine.check_errors()
+        return out
 
 
 class Runtime:

@@ -197,6 +197,11 @@ class Engine:
     def close_slot(self, slot: int) -> None:
         self.cache.close_slot(slot)
 
+    def check_errors(self) -> None:
+        """Reads the device's error flag (a synchronisation): raises if a token id outside the
+        vocabulary reached the embedding kernel or a bounded wait inside a kernel ran out."""
+        ops.check_error_flag(self.model.device)
+
     def step(self, entries, pad_to: int | None = None, graph: bool | None = None):
         """Runs one step.  ``entries``: StepEntry list.  Returns float32 logits
         [number of wanted places, vocabulary] on the device, in the order of the entries and of

@@ -19,9 +19,7 @@ def run(out, x, weight, accumulate: bool) -> bool:
     if rows <= ops.STREAM_MAX_ROWS:
         ops.gemm_stream(out, x, weight, mode)
         return True
-    for lo in range(0, rows, ops.STREAM_MAX_ROWS):
-        hi = min(rows, lo + ops.STREAM_MAX_ROWS)
-        ops.gemm_stream(out[lo:hi], x[lo:hi], weight, mode)
+    ops.gemm_tcgen05(out, x, weight, mode)
     return True
 
 
@@ -30,8 +28,8 @@ def run_swiglu(out, x, weight_gate_up, inner: int) -> bool:
     fused kernel takes the shape."""
     if not aligned(x, weight_gate_up):
         return False
-    rows = x.shape[0]
-    for lo in range(0, rows, ops.STREAM_MAX_ROWS):
-        hi = min(rows, lo + ops.STREAM_MAX_ROWS)
-        ops.gemm_stream(out[lo:hi], x[lo:hi], weight_gate_up, "swiglu", up_rows=inner)
+    if x.shape[0] <= ops.STREAM_MAX_ROWS:
+        ops.gemm_stream(out, x, weight_gate_up, "swiglu", up_rows=inner)
+    else:
+        ops.gemm_tcgen05(out, x, weight_gate_up, "swiglu", up_rows=inner)
     return True
