@@ -165,16 +165,20 @@ __global__ void attention_combine_kernel(__nv_bfloat16* __restrict__ out, const 
   float acc[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  // splits in order; loads are predicated rather than skipped so that several splits' loads are
+  // in flight at once (a dead split's partials are never read: they may hold anything)
+#pragma unroll 4
   for (int s = 0; s < n_splits; ++s) {
     const bool live = max(s * chunk, first_block_key) < min((s + 1) * chunk, len);
-    if (!live) continue;
-    const float ms = part_ml[(base + s) * 2];
+    const float ms = live ? part_ml[(base + s) * 2] : -INFINITY;
+    const float ls = live ? part_ml[(base + s) * 2 + 1] : 0.f;
     const float f = ms == -INFINITY ? 0.f : exp2f(ms - m);
-    l += f * part_ml[(base + s) * 2 + 1];
+    l += f * ls;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int d = lane + 32 * j;
-      if (d < head_dim) acc[j] += f * part_o[(base + s) * head_dim + d];
+      const float o = (live && d < head_dim) ? part_o[(base + s) * head_dim + d] : 0.f;
+      acc[j] += f * o;
     }
   }
 #pragma unroll

@@ -25,7 +25,6 @@ constexpr int GS_WARPS = 8;
 constexpr int GS_THREADS = GS_WARPS * 32;
 constexpr int GS_ROWS = 8;                      // weight rows of one group
 constexpr int GS_SLAB = 512;                    // k elements a stage
-constexpr int GS_STAGES = 3;
 constexpr int GS_ROW_BYTES = GS_SLAB * 2 + 64;  // padded: a quarter warp (two rows x four 16-byte pieces) hits 32 banks
 
 __device__ __forceinline__ void gs_cp_async(uint32_t dst, const void* src, int src_bytes) {
@@ -40,7 +39,7 @@ __device__ __forceinline__ void gs_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
 }
 
 // MODE 0: store, 1: add into float out, 2: SwiGLU (two groups of rows: gate and up)
-template <int M_TILES, int MODE, typename TO>
+template <int M_TILES, int MODE, int GS_STAGES, typename TO>
 __global__ void __launch_bounds__(GS_THREADS)
 gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    int M, int N, int K, int ldx, int ldo, long long up_offset) {
@@ -166,14 +165,14 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
   }
 }
 
-template <int M_TILES, int MODE, typename TO>
-int launch_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, long long up_offset,
-                  cudaStream_t stream) {
+template <int M_TILES, int MODE, int GS_STAGES, typename TO>
+int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
+                         long long up_offset, cudaStream_t stream) {
   constexpr int GROUPS = MODE == 2 ? 2 : 1;
   constexpr int RING_BYTES = GS_STAGES * GROUPS * GS_ROWS * GS_ROW_BYTES;
   constexpr int PARTIAL_BYTES = GS_WARPS * GROUPS * M_TILES * 16 * (GS_ROWS + 1) * (int)sizeof(float);
   constexpr int SMEM = RING_BYTES > PARTIAL_BYTES ? RING_BYTES : PARTIAL_BYTES;
-  auto kernel = gemm_stream_kernel<M_TILES, MODE, TO>;
+  auto kernel = gemm_stream_kernel<M_TILES, MODE, GS_STAGES, TO>;
   static bool allowed = false;
   if (SMEM > 48 * 1024 && !allowed) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -184,6 +183,18 @@ int launch_stream(void* out, const void* x, const void* w, int M, int N, int K, 
   kernel<<<blocks, GS_THREADS, SMEM, stream>>>((TO*)out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, M, N, K, ldx,
                                              ldo, up_offset);
   return launch_status();
+}
+
+// Three stages (eight blocks a multiprocessor) when the blocks outnumber what the GPU holds at
+// once; six stages when they do not, so that a block keeps five slabs in flight instead of two.
+template <int M_TILES, int MODE, typename TO>
+int launch_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, long long up_offset,
+                  cudaStream_t stream) {
+  const int blocks = (N + GS_ROWS - 1) / GS_ROWS;
+  constexpr int GROUPS = MODE == 2 ? 2 : 1;
+  if (blocks <= 148 * (GROUPS == 2 ? 2 : 4))  // 6 stages: 52 KB (104 KB for SwiGLU), four (two) blocks a multiprocessor
+    return launch_stream_staged<M_TILES, MODE, 6, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, stream);
+  return launch_stream_staged<M_TILES, MODE, 3, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, stream);
 }
 
 template <int M_TILES>
