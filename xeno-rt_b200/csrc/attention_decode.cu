@@ -28,6 +28,8 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         int n_splits) {
   constexpr int D_TILES = HD_MAX / 8;
   extern __shared__ __align__(16) unsigned char smem[];
+  pdl_trigger();
+  pdl_wait();
   const int split = blockIdx.x, kv_head = blockIdx.y, tok = blockIdx.z;
   const int slot = tok_slot[tok];
   if (slot < 0) {  // a padding row: zeros (with several splits the combine kernel writes them)
@@ -144,6 +146,8 @@ __global__ void attention_combine_kernel(__nv_bfloat16* __restrict__ out, const 
                                          const float* __restrict__ part_ml, const int* __restrict__ tok_slot,
                                          const int* __restrict__ tok_pos, int n_tokens, int n_heads, int head_dim,
                                          int window, int chunk, int n_splits) {
+  pdl_trigger();
+  pdl_wait();
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp_global >= n_tokens * n_heads) return;
   const int tok = warp_global / n_heads;
@@ -204,9 +208,9 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_
     smem_allowed = smem;
   }
   dim3 grid(n_splits, n_kv_heads, n_tokens);
-  kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(out, part_o, part_ml, q, k_pool, v_pool, tok_slot, tok_pos,
-                                                block_table, max_blocks, n_heads, n_kv_heads, head_dim,
-                                                scale * 1.4426950408889634f, window, chunk, n_splits);
+  launch_kernel(kernel, grid, dim3(DEC_WARPS * 32), (size_t)smem, stream, out, part_o, part_ml, q, k_pool, v_pool,
+                tok_slot, tok_pos, block_table, max_blocks, n_heads, n_kv_heads, head_dim,
+                scale * 1.4426950408889634f, window, chunk, n_splits);
   return launch_status();
 }
 
@@ -245,8 +249,9 @@ XRT_EXPORT int xrt_attention_decode(void* out, float* part_o, float* part_ml, co
   if (status != XRT_OK) return status;
   if (n_splits > 1) {
     const int warps = n_tokens * n_heads;
-    xrt::attention_combine_kernel<<<(warps * 32 + 255) / 256, 256, 0, stream>>>(
-        o, part_o, part_ml, tok_slot, tok_pos, n_tokens, n_heads, head_dim, window, chunk, n_splits);
+    xrt::launch_kernel(xrt::attention_combine_kernel, dim3((warps * 32 + 255) / 256), dim3(256), 0, stream, o,
+                       (const float*)part_o, (const float*)part_ml, tok_slot, tok_pos, n_tokens, n_heads, head_dim,
+                       window, chunk, n_splits);
     return xrt::launch_status();
   }
   return XRT_OK;

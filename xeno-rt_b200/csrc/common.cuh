@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 // dtype codes, the same integers as DType.code on the Python side
 #define XRT_F32 0
@@ -59,6 +60,42 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   }
   __syncthreads();
   return scratch[32];
+}
+
+// Programmatic dependent launch.  A kernel launched with `pdl` may begin while the kernel before it
+// in the stream is still running: what it does before pdl_wait() (prefetching weights, set-up)
+// overlaps the predecessor's tail and hides its own launch latency; pdl_wait() returns once the
+// predecessor has completed and its writes are visible.  Every kernel of the decode step calls
+// pdl_trigger() first (its successor may be launched) and pdl_wait() before it touches anything a
+// predecessor wrote or reads anything it will overwrite.  XRT_PDL=0 in the environment turns the
+// launch attribute off (the instructions are then no-ops).
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* env = getenv("XRT_PDL");
+    enabled = (env != nullptr && env[0] == '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  const bool pdl = pdl_enabled();
+  config.attrs = pdl ? attribute : nullptr;
+  config.numAttrs = pdl ? 1 : 0;
+  cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
 }
 
 inline int launch_status() {

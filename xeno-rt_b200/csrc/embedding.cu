@@ -10,6 +10,8 @@ template <typename TW>
 __global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__ table,
                                  const int* __restrict__ ids, int hidden, int vocab,
                                  int* __restrict__ error_flag) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
@@ -25,6 +27,8 @@ __global__ void embedding_vec_kernel(float* __restrict__ out, const TW* __restri
                                      const int* __restrict__ ids, int hidden, int vocab,
                                      int* __restrict__ error_flag) {
   constexpr int PER = 16 / (int)sizeof(TW);
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
@@ -52,9 +56,9 @@ XRT_EXPORT int xrt_embedding(float* out, const void* table, const int* ids, int 
   const bool vec = hidden % 8 == 0 && (((uintptr_t)out | (uintptr_t)table) & 15) == 0;
   XRT_DISPATCH_DTYPE(table_dtype, TW, {
     if (vec)
-      xrt::embedding_vec_kernel<TW><<<n_tokens, 128, 0, stream>>>(out, (const TW*)table, ids, hidden, vocab, error_flag);
+      xrt::launch_kernel(xrt::embedding_vec_kernel<TW>, dim3(n_tokens), dim3(128), 0, stream, out, (const TW*)table, ids, hidden, vocab, error_flag);
     else
-      xrt::embedding_kernel<TW><<<n_tokens, 256, 0, stream>>>(out, (const TW*)table, ids, hidden, vocab, error_flag);
+      xrt::launch_kernel(xrt::embedding_kernel<TW>, dim3(n_tokens), dim3(256), 0, stream, out, (const TW*)table, ids, hidden, vocab, error_flag);
   });
   return xrt::launch_status();
 }

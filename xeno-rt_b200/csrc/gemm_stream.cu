@@ -50,6 +50,7 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
   constexpr int COPIES = STAGE_ROWS * CHUNKS_PER_ROW / GS_THREADS;  // per thread and stage
   extern __shared__ __align__(128) unsigned char smem[];
 
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * GS_ROWS;
   const int n_slabs = (K + GS_SLAB - 1) / GS_SLAB;
@@ -79,6 +80,9 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
     asm volatile("cp.async.commit_group;");
   }
 
+  // The weights do not depend on the step: the first slabs are on their way while the kernel before
+  // this one finishes.  X and the output do: wait for it here.
+  pdl_wait();
   const __nv_bfloat16* xlo[M_TILES];
   const __nv_bfloat16* xhi[M_TILES];
 #pragma unroll
@@ -180,20 +184,16 @@ int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, 
     allowed = true;
   }
   const int blocks = (N + GS_ROWS - 1) / GS_ROWS;
-  kernel<<<blocks, GS_THREADS, SMEM, stream>>>((TO*)out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, M, N, K, ldx,
-                                             ldo, up_offset);
+  launch_kernel(kernel, dim3(blocks), dim3(GS_THREADS), SMEM, stream, (TO*)out, (const __nv_bfloat16*)x,
+                (const __nv_bfloat16*)w, M, N, K, ldx, ldo, up_offset);
   return launch_status();
 }
 
-// Three stages (eight blocks a multiprocessor) when the blocks outnumber what the GPU holds at
-// once; six stages when they do not, so that a block keeps five slabs in flight instead of two.
+// Three stages: 26 KB a block, eight blocks a multiprocessor (a deeper ring with fewer resident
+// blocks measured slower, also for the small products).
 template <int M_TILES, int MODE, typename TO>
 int launch_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, long long up_offset,
                   cudaStream_t stream) {
-  const int blocks = (N + GS_ROWS - 1) / GS_ROWS;
-  constexpr int GROUPS = MODE == 2 ? 2 : 1;
-  if (blocks <= 148 * (GROUPS == 2 ? 2 : 4))  // 6 stages: 52 KB (104 KB for SwiGLU), four (two) blocks a multiprocessor
-    return launch_stream_staged<M_TILES, MODE, 6, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, stream);
   return launch_stream_staged<M_TILES, MODE, 3, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, stream);
 }
 

@@ -45,6 +45,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_vec_kernel(TO* __restrict__ out, const float* __restrict__ x, const TW* __restrict__ w,
                    const int* __restrict__ rows, int width, float eps) {
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = rows != nullptr ? rows[r] : r;
   const float* xr = x + (size_t)src * width;
@@ -81,6 +83,8 @@ template <typename TW, typename TO>
 __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x, const TW* __restrict__ w,
                                const int* __restrict__ rows, int width, float eps) {
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = rows != nullptr ? rows[r] : r;
   const float* xr = x + (size_t)src * width;
@@ -108,15 +112,15 @@ XRT_EXPORT int xrt_rmsnorm(void* out, const float* x, const void* weight, const 
   XRT_DISPATCH_DTYPE(weight_dtype, TW, {
     XRT_DISPATCH_DTYPE(out_dtype, TO, {
       if (vec && chunks <= 1)
-        xrt::rmsnorm_vec_kernel<TW, TO, 1><<<n_rows, xrt::NORM_THREADS, 0, stream>>>((TO*)out, x, (const TW*)weight, rows, width, eps);
+        xrt::launch_kernel(xrt::rmsnorm_vec_kernel<TW, TO, 1>, dim3(n_rows), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
       else if (vec && chunks <= 2)
-        xrt::rmsnorm_vec_kernel<TW, TO, 2><<<n_rows, xrt::NORM_THREADS, 0, stream>>>((TO*)out, x, (const TW*)weight, rows, width, eps);
+        xrt::launch_kernel(xrt::rmsnorm_vec_kernel<TW, TO, 2>, dim3(n_rows), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
       else if (vec && chunks <= 4)
-        xrt::rmsnorm_vec_kernel<TW, TO, 4><<<n_rows, xrt::NORM_THREADS, 0, stream>>>((TO*)out, x, (const TW*)weight, rows, width, eps);
+        xrt::launch_kernel(xrt::rmsnorm_vec_kernel<TW, TO, 4>, dim3(n_rows), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
       else if (vec)
-        xrt::rmsnorm_vec_kernel<TW, TO, 8><<<n_rows, xrt::NORM_THREADS, 0, stream>>>((TO*)out, x, (const TW*)weight, rows, width, eps);
+        xrt::launch_kernel(xrt::rmsnorm_vec_kernel<TW, TO, 8>, dim3(n_rows), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
       else
-        xrt::rmsnorm_kernel<TW, TO><<<n_rows, threads, 0, stream>>>((TO*)out, x, (const TW*)weight, rows, width, eps);
+        xrt::launch_kernel(xrt::rmsnorm_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
     });
   });
   return xrt::launch_status();

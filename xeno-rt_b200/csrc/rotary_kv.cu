@@ -15,6 +15,8 @@ namespace xrt {
 // cos_sin[t, i] = (cos, sin) of pos[t] * scale / freq[i]; freq is the divisor table base^(2i/rd).
 __global__ void rope_table_kernel(float2* __restrict__ cos_sin, const int* __restrict__ pos,
                                   const float* __restrict__ freq, float scale, int n_tokens, int half) {
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_tokens * half) return;
   const int t = i / half, p = i - t * half;
@@ -35,6 +37,8 @@ __global__ void qk_rope_kv_write_kernel(
     const int* __restrict__ block_table, int max_blocks,
     int n_heads, int n_kv_heads, int head_dim, int write_kv) {
   extern __shared__ float staged[];  // [warps][head_dim]
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int head_slot = blockIdx.y * (blockDim.x >> 5) + warp;
@@ -125,8 +129,8 @@ XRT_EXPORT int xrt_rope_table(float* cos_sin, const int* pos, const float* freq,
   if (n_tokens < 0 || half < 0) return XRT_ERR_ARGUMENT;
   const int total = n_tokens * half;
   if (total == 0) return XRT_OK;
-  xrt::rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>((float2*)cos_sin, pos, freq, scale,
-                                                                  n_tokens, half);
+  xrt::launch_kernel(xrt::rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, (float2*)cos_sin, pos, freq,
+                     scale, n_tokens, half);
   return xrt::launch_status();
 }
 
@@ -151,7 +155,7 @@ XRT_EXPORT int xrt_qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, con
   XRT_DISPATCH_DTYPE(norm_dtype, TN, {
     XRT_DISPATCH_DTYPE(q_dtype, TQ, {
       XRT_DISPATCH_DTYPE(cache_dtype, TC, {
-        xrt::qk_rope_kv_write_kernel<TN, TQ, TC, 8><<<grid, warps * 32, smem, stream>>>(
+        xrt::launch_kernel(xrt::qk_rope_kv_write_kernel<TN, TQ, TC, 8>, grid, dim3(warps * 32), smem, stream,
             (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, qkv, row_stride, k_offset, v_offset, (const TN*)q_norm_w,
             (const TN*)k_norm_w, eps, (const float2*)cos_sin, rope_half, tok_slot, tok_pos, block_table,
             max_blocks, n_heads, n_kv_heads, head_dim, write_kv);

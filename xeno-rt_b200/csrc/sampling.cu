@@ -168,6 +168,8 @@ sample_kernel(int* __restrict__ out_ids, const float* __restrict__ logits, int v
   __shared__ float bcast_max;
   __shared__ int bcast_arg;
 
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const int slot = row_slot[row];
   if (slot < 0) { if (threadIdx.x == 0) out_ids[row] = -1; return; }
@@ -286,9 +288,8 @@ XRT_EXPORT int xrt_sample(int* out_ids, const float* logits, int n_rows, int voc
   if (n_rows < 0 || vocab <= 0) return XRT_ERR_ARGUMENT;
   if (seen != nullptr && seen_words * 32 < vocab) return XRT_ERR_ARGUMENT;
   if (n_rows == 0) return XRT_OK;
-  xrt::sample_kernel<<<n_rows, xrt::SAMPLE_THREADS, 0, stream>>>(out_ids, logits, vocab, row_slot, temperature,
-                                                               top_k, top_p, penalty, seen, seen_words, rng_key,
-                                                               rng_counter);
+  xrt::launch_kernel(xrt::sample_kernel, dim3(n_rows), dim3(xrt::SAMPLE_THREADS), 0, stream, out_ids, logits, vocab,
+                     row_slot, temperature, top_k, top_p, penalty, (const uint32_t*)seen, seen_words, rng_key, rng_counter);
   return xrt::launch_status();
 }
 
