@@ -437,3 +437,40 @@ def test_gemm_tcgen05_swiglu(m, inner, k):
     ops().gemm_tcgen05(out, x, w, "swiglu", up_rows=inner)
     want = pm.swiglu(f64(x) @ f64(w[:inner]).T, f64(x) @ f64(w[inner:]).T)
     assert rel(out, want) < 5e-3
+
+
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 40, 64, 100, 128])
+@pytest.mark.parametrize("n,k", [(203, 104), (4096, 512), (136, 96), (8, 40), (300, 2056)])
+def test_gemm_decode_tcgen05(m, n, k):
+    """Swapped-operand product: any N (tiles of 128 weight rows), K split across blocks or not."""
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    want = f64(x) @ f64(w).T
+    out = torch.full((m, n), 7.0, device=DEV)
+    ops().gemm_decode_tcgen05(out, x, w)
+    assert rel(out, want) < 1e-5
+    out_b = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    ops().gemm_decode_tcgen05(out_b, x, w)
+    assert rel(out_b, want) < 5e-3
+    base = torch.randn(m, n, device=DEV)
+    acc = base.clone()
+    ops().gemm_decode_tcgen05(acc, x, w, "accumulate")
+    assert rel(acc, f64(base) + want) < 1e-5
+    one = torch.empty(1, n, device=DEV)
+    ops().gemm_decode_tcgen05(one, x[m - 1:m].contiguous(), w)
+    assert torch.equal(one[0], out[m - 1])  # a row's result does not depend on the other rows
+    again = torch.empty_like(out)
+    ops().gemm_decode_tcgen05(again, x, w)
+    assert torch.equal(again, out)  # nor on which block finished a tile last
+    from xeno_rt_b200.csrc import ops as o
+    o.check_error_flag(DEV)
+
+
+@pytest.mark.parametrize("m,inner,k", [(1, 136, 96), (9, 203, 104), (64, 256, 4096), (33, 1000, 520)])
+def test_gemm_decode_tcgen05_swiglu(m, inner, k):
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inner, k, device=DEV) * 0.1).to(torch.bfloat16)
+    out = torch.empty(m, inner, device=DEV, dtype=torch.bfloat16)
+    ops().gemm_decode_tcgen05(out, x, w, "swiglu", up_rows=inner)
+    want = pm.swiglu(f64(x) @ f64(w[:inner]).T, f64(x) @ f64(w[inner:]).T)
+    assert rel(out, want) < 5e-3

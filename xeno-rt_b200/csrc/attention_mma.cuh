@@ -153,4 +153,92 @@ __device__ __forceinline__ void attend_16_keys(SoftmaxState<D_TILES>& st, const 
   }
 }
 
+// One warp: scores of its 16 query rows against KEY_TILES * 8 keys that start at row `key_row` of
+// the key tile, one online-softmax update for all of them (one rescale of the output accumulators
+// a call, which is what makes long steps cheap), and the product with the same rows of the value
+// tile.  `masked` (uniform over the warp) says whether any key of the range may be hidden from a
+// row; without it the comparisons are skipped.
+template <int D_TILES, int KEY_TILES>
+__device__ __forceinline__ void attend_keys(SoftmaxState<D_TILES>& st, const uint32_t (*qf)[4],
+                                            const unsigned char* ks_tile, const unsigned char* vs_tile, int key_row,
+                                            int key_abs, const int (&key_lo)[2], const int (&key_hi)[2], bool masked,
+                                            int head_dim, float scale_log2) {
+  static_assert(KEY_TILES % 2 == 0, "keys come in groups of 16");
+  const int lane = threadIdx.x & 31, t = lane & 3;
+  const int row_bytes = tile_row_bytes(head_dim);
+  const int j = lane >> 3, r = lane & 7;
+  float s[KEY_TILES][4];
+#pragma unroll
+  for (int nt = 0; nt < KEY_TILES; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+  const uint32_t k_base = smem_addr(ks_tile + (key_row + (j >> 1) * 8 + r) * row_bytes + (j & 1) * 16);
+#pragma unroll
+  for (int ks = 0; ks < D_TILES / 2; ++ks) {
+    if (ks * 16 < head_dim) {
+#pragma unroll
+      for (int kp = 0; kp < KEY_TILES / 2; ++kp) {
+        uint32_t kf[4];
+        ldmatrix_x4(kf, k_base + kp * 16 * row_bytes + ks * 32);
+        mma_16816(s[2 * kp], qf[ks], kf[0], kf[1]);
+        mma_16816(s[2 * kp + 1], qf[ks], kf[2], kf[3]);
+      }
+    }
+  }
+  float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < KEY_TILES; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int row = e >> 1;
+      bool live = true;
+      if (masked) {
+        const int key = key_abs + nt * 8 + 2 * t + (e & 1);
+        live = key >= key_lo[row] && key < key_hi[row];
+      }
+      s[nt][e] = live ? s[nt][e] * scale_log2 : -INFINITY;
+      tile_max[row] = fmaxf(tile_max[row], s[nt][e]);
+    }
+  float corr[2];
+#pragma unroll
+  for (int row = 0; row < 2; ++row) {
+    tile_max[row] = fmaxf(tile_max[row], __shfl_xor_sync(0xffffffffu, tile_max[row], 1));
+    tile_max[row] = fmaxf(tile_max[row], __shfl_xor_sync(0xffffffffu, tile_max[row], 2));
+    const float m_new = fmaxf(st.m[row], tile_max[row]);
+    corr[row] = m_new == -INFINITY ? 1.f : exp2f(st.m[row] - m_new);
+    st.m[row] = m_new;
+    st.l[row] *= corr[row];
+  }
+#pragma unroll
+  for (int nt = 0; nt < KEY_TILES; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int row = e >> 1;
+      s[nt][e] = st.m[row] == -INFINITY ? 0.f : exp2f(s[nt][e] - st.m[row]);
+      st.l[row] += s[nt][e];
+    }
+#pragma unroll
+  for (int dt = 0; dt < D_TILES; ++dt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) st.o[dt][e] *= corr[e >> 1];
+  const uint32_t v_base = smem_addr(vs_tile + (key_row + (j & 1) * 8 + r) * row_bytes + (j >> 1) * 16);
+#pragma unroll
+  for (int kp = 0; kp < KEY_TILES / 2; ++kp) {
+    uint32_t pf[4];
+    pf[0] = pack_bf16(s[2 * kp][0], s[2 * kp][1]);
+    pf[1] = pack_bf16(s[2 * kp][2], s[2 * kp][3]);
+    pf[2] = pack_bf16(s[2 * kp + 1][0], s[2 * kp + 1][1]);
+    pf[3] = pack_bf16(s[2 * kp + 1][2], s[2 * kp + 1][3]);
+#pragma unroll
+    for (int dt = 0; dt < D_TILES; dt += 2) {
+      if (dt * 8 < head_dim) {
+        uint32_t vf[4];
+        ldmatrix_x4_trans(vf, v_base + kp * 16 * row_bytes + dt * 16);
+        mma_16816(st.o[dt], pf, vf[0], vf[1]);
+        mma_16816(st.o[dt + 1], pf, vf[2], vf[3]);
+      }
+    }
+  }
+}
+
 }  // namespace xrt

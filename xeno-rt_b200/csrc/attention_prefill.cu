@@ -27,7 +27,8 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
                          int n_heads, int n_kv_heads, int head_dim, float scale_log2, int window) {
   constexpr int D_TILES = HD_MAX / 8;
   extern __shared__ __align__(16) unsigned char smem[];
-  const int q_tile = blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
+  // later query tiles walk more keys: they are scheduled first
+  const int q_tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
   const int slot = seq_slot[seq];
   if (slot < 0) return;
   const int tok0 = cu_seqlens[seq];
@@ -73,6 +74,10 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   const int warp_last_row = min(warp_first_row + 15, n_new - 1);
   const int warp_hi = warp_first_row < n_new ? start + warp_last_row + 1 : 0;
   const int warp_lo = window > 0 ? max(0, start + warp_first_row + 1 - window) : 0;
+  // every row of the warp sees the keys in [warp_max_lo, warp_min_hi): a tile inside needs no mask
+  const int warp_min_hi = warp_first_row < n_new ? start + warp_first_row + 1 : 0;
+  const int warp_max_lo = window > 0 ? max(0, start + warp_last_row + 1 - window) : 0;
+  const bool partial_warp = warp_first_row + 15 >= n_new;  // some rows lie beyond the sequence and see nothing
 
   const int* blocks = block_table + (size_t)slot * max_blocks;
   const size_t head_stride = (size_t)XRT_BLOCK_TOKENS * head_dim;
@@ -94,12 +99,11 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
     else cp_async_wait<0>();
     __syncthreads();
     const int key0 = (first_tile + i) * XRT_BLOCK_TOKENS;
-#pragma unroll
-    for (int sub = 0; sub < XRT_BLOCK_TOKENS / 16; ++sub) {
-      const int key_abs = key0 + sub * 16;
-      if (key_abs < warp_hi && key_abs + 16 > warp_lo)  // uniform over the warp
-        attend_16_keys<D_TILES>(st, qf, k_tiles + (i & 1) * tile_bytes, v_tiles + (i & 1) * tile_bytes, sub * 16,
-                                key_abs, key_lo, key_hi, head_dim, scale_log2);
+    // uniform over the warp: does the tile hold any key this warp's rows see, and may it hide one?
+    if (key0 < warp_hi && key0 + XRT_BLOCK_TOKENS > warp_lo) {
+      const bool masked = partial_warp || key0 + XRT_BLOCK_TOKENS > warp_min_hi || key0 < warp_max_lo;
+      attend_keys<D_TILES, XRT_BLOCK_TOKENS / 8>(st, qf, k_tiles + (i & 1) * tile_bytes, v_tiles + (i & 1) * tile_bytes,
+                                                 0, key0, key_lo, key_hi, masked, head_dim, scale_log2);
     }
     __syncthreads();
   }

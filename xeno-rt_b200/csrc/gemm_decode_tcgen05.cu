@@ -1,0 +1,420 @@
+// Y[M, N] = X[M, K] . W[N, K]^T for few rows (decode steps) on the fifth-generation tensor cores,
+// with the operands swapped: the WEIGHT rows are the MMA's 128 lanes (M of tcgen05.mma), the batch
+// rows its N (16 .. 128), so that a step of a handful of sequences still fills the tensor core's
+// rows, and the product's time is the time to stream W from HBM.
+//
+// The reference streams each weight row once per token (crates/xrt-kernels/src/cpu/matmul.rs:100-192,
+// 194-320).  Here the weight is streamed by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a deep
+// ring of shared-memory stages: no registers are held by bytes in flight, and a persistent block
+// per multiprocessor never drains its pipeline between work items.
+//
+// Work items are (tile of 128 weight rows, split of K).  K is split so that the items fill the
+// multiprocessors evenly even when N is small; every split writes its 128 x NB partial sums to
+// scratch memory, and the block that finishes a tile's last split (found with one atomic counter a
+// tile, no block ever waits for another) adds the partials IN SPLIT ORDER and applies the epilogue:
+// the result does not depend on which block came last, nor on the number of rows M.
+// Epilogues: store (32-bit or bfloat16), add into the 32-bit residual stream, SwiGLU (an item then
+// streams 128 gate rows and the 128 matching up rows into two accumulators).
+//
+// Six warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues the MMAs, warps 2-5 read the
+// accumulators (tcgen05.ld, one TMEM lane quarter each) while the MMA warp fills the other
+// accumulator.  Every mbarrier wait is bounded; a wait that runs out raises the error flag and an
+// abort flag, all roles leave their loops, TMEM is freed and the block returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace xrt {
+
+constexpr int DG_ROWS = 128, DG_BK = 64, DG_UMMA_K = 16;
+constexpr int DG_W_BYTES = DG_ROWS * DG_BK * 2;  // 16 KB: one slab of one group of weight rows
+constexpr int DG_THREADS = 192;
+constexpr long long DG_SPIN_LIMIT = 1ll << 24;
+
+__device__ __forceinline__ uint32_t dg_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void dg_mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void dg_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void dg_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool dg_mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (long long spin = 0; spin < DG_SPIN_LIMIT; ++spin) {
+    uint32_t done;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if ((spin & 1023) == 1023 && *abort_flag) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ void dg_tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+// K-major operand in 128-byte-swizzled rows of 128 bytes, groups of eight rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t dg_smem_desc(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// kind::f16, bfloat16 A and B, float32 D, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t dg_instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(DG_ROWS >> 4) << 24);
+}
+__device__ __forceinline__ void dg_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+               " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+               ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void dg_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void dg_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void dg_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void dg_ld16(uint32_t (&r)[16], uint32_t addr) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(addr));
+}
+__device__ __forceinline__ void dg_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+struct DecodeGemmShape {
+  int M, N, K, ldo;
+  int nb;            // batch rows padded to a multiple of 16: the MMA's N
+  int tiles;         // tiles of 128 weight rows
+  int splits;        // splits of K
+  int k_per_split;   // 64-wide slabs a split
+  int up_rows;       // SwiGLU: the up rows start this many rows after the gate rows
+  int stages;        // ring depth
+  int tmem_cols;     // power of two >= 2 accumulators
+};
+
+// MODE 0: store, 1: add into float out, 2: SwiGLU.
+template <int MODE, typename TO>
+__global__ void __launch_bounds__(DG_THREADS, 1)
+gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                           TO* __restrict__ out, float* __restrict__ partial, int* __restrict__ counters,
+                           const DecodeGemmShape shape, int* __restrict__ error_flag) {
+  constexpr int GROUPS = MODE == 2 ? 2 : 1;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int x_bytes = shape.nb * DG_BK * 2;
+  const int stage_bytes = GROUPS * DG_W_BYTES + ((x_bytes + 1023) & ~1023);
+  const int stages = shape.stages;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_bytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + stages;
+  uint64_t* acc_full = bars + 2 * stages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_items = shape.tiles * shape.splits;
+  const int k_iters_total = (shape.K + DG_BK - 1) / DG_BK;
+  const int acc_cols = GROUPS * shape.nb;  // TMEM columns of one accumulator set
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { dg_mbar_init(dg_smem(&full[s]), 1); dg_mbar_init(dg_smem(&empty[s]), 1); }
+    for (int a = 0; a < 2; ++a) { dg_mbar_init(dg_smem(&acc_full[a]), 1); dg_mbar_init(dg_smem(&acc_empty[a]), 128); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dg_smem(tmem_slot)), "r"(shape.tmem_cols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  dg_fence_before();
+  __syncthreads();
+  dg_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // item -> (tile, split); consecutive items are the splits of one tile
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+      int it = 0;
+      bool ok = true, waited = false;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const int tile = item / shape.splits, split = item % shape.splits;
+        const int kb0 = split * shape.k_per_split;
+        const int kb1 = min(k_iters_total, kb0 + shape.k_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % stages;
+          ok = dg_mbar_wait(dg_smem(&empty[s]), ((it / stages) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          const uint32_t bar = dg_smem(&full[s]);
+          unsigned char* stage = smem + (size_t)s * stage_bytes;
+          dg_mbar_expect_tx(bar, GROUPS * DG_W_BYTES + x_bytes);
+          // the weights do not depend on the step: they may be on their way while the kernel before
+          // this one finishes; X does, so the first X load waits for it
+          dg_tma_load_2d(dg_smem(stage), &map_w, kb * DG_BK, tile * DG_ROWS, bar);
+          if (MODE == 2) dg_tma_load_2d(dg_smem(stage + DG_W_BYTES), &map_w, kb * DG_BK, shape.up_rows + tile * DG_ROWS, bar);
+          if (!waited) { pdl_wait(); waited = true; }
+          dg_tma_load_2d(dg_smem(stage + GROUPS * DG_W_BYTES), &map_x, kb * DG_BK, 0, bar);
+        }
+      }
+      if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 4); }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issue
+    if (lane == 0) {
+      const uint32_t idesc = dg_instr_desc(shape.nb);
+      int it = 0, item_i = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++item_i) {
+        const int split = item % shape.splits;
+        const int kb0 = split * shape.k_per_split;
+        const int kb1 = min(k_iters_total, kb0 + shape.k_per_split);
+        const int a = item_i & 1;
+        ok = dg_mbar_wait(dg_smem(&acc_empty[a]), ((item_i >> 1) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        dg_fence_after();
+        const uint32_t tmem_d = tmem_base + a * acc_cols;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % stages;
+          ok = dg_mbar_wait(dg_smem(&full[s]), (it / stages) & 1, abort_flag);
+          if (!ok) break;
+          dg_fence_after();
+          unsigned char* stage = smem + (size_t)s * stage_bytes;
+          const uint64_t desc_x = dg_smem_desc(dg_smem(stage + GROUPS * DG_W_BYTES));
+#pragma unroll
+          for (int gr = 0; gr < GROUPS; ++gr) {
+            const uint64_t desc_w = dg_smem_desc(dg_smem(stage + gr * DG_W_BYTES));
+#pragma unroll
+            for (int k = 0; k < DG_BK / DG_UMMA_K; ++k)
+              dg_mma(tmem_d + gr * shape.nb, desc_w + 2 * k, desc_x + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          dg_commit(dg_smem(&empty[s]));
+        }
+        if (ok) dg_commit(dg_smem(&acc_full[a]));
+      }
+      if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 4); }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    pdl_wait();  // the output (and the residual it adds into) belongs to the step
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // weight row inside the tile = TMEM lane
+    int item_i = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++item_i) {
+      const int tile = item / shape.splits, split = item % shape.splits;
+      const int kb0 = split * shape.k_per_split;
+      const bool has_k = kb0 < k_iters_total;  // a split beyond K (uneven division) contributes zeros
+      const int a = item_i & 1;
+      const int n = tile * DG_ROWS + r;  // output column = weight row
+      const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * acc_cols;
+      if (has_k) {
+        ok = dg_mbar_wait(dg_smem(&acc_full[a]), (item_i >> 1) & 1, abort_flag);
+        if (!ok) break;
+        dg_fence_after();
+      }
+      if (shape.splits == 1) {
+        // one split: straight to the output
+        for (int c = 0; c < shape.nb; c += 16) {
+          uint32_t v[16], u[16];
+          dg_ld16(v, tmem_row + c);
+          if (MODE == 2) dg_ld16(u, tmem_row + shape.nb + c);
+          dg_wait_ld();
+          if (n < shape.N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = c + j;
+              if (m < shape.M) {
+                float val = __uint_as_float(v[j]);
+                if (MODE == 2) val = (val / (1.0f + expf(-val))) * __uint_as_float(u[j]);
+                TO* dst = out + (size_t)m * shape.ldo + n;
+                if (MODE == 1) *dst = from_float<TO>(to_float(*dst) + val);
+                else *dst = from_float<TO>(val);
+              }
+            }
+          }
+        }
+      } else {
+        // partial[(tile * splits + split)][group][batch row][128]: lanes write consecutive floats
+        float* mine = partial + ((size_t)item * GROUPS) * shape.nb * DG_ROWS;
+        for (int c = 0; c < acc_cols; c += 16) {
+          uint32_t v[16];
+          if (has_k) { dg_ld16(v, tmem_row + c); dg_wait_ld(); }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) mine[(size_t)(c + j) * DG_ROWS + r] = has_k ? __uint_as_float(v[j]) : 0.f;
+        }
+      }
+      if (has_k) {
+        dg_fence_before();
+        dg_mbar_arrive(dg_smem(&acc_empty[a]));
+      }
+      if (shape.splits > 1) {
+        // the block that brings a tile's last split adds the partials in split order
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+        if (threadIdx.x == 64) {
+          const int before = atomicAdd(&counters[tile], 1);
+          *last_flag = before == shape.splits - 1;
+          if (before == shape.splits - 1) counters[tile] = 0;  // ready for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag) {
+          __threadfence();
+          const float* first = partial + ((size_t)tile * shape.splits * GROUPS) * shape.nb * DG_ROWS;
+          const size_t split_stride = (size_t)GROUPS * shape.nb * DG_ROWS;
+          if (n < shape.N) {
+            for (int m = 0; m < shape.M; ++m) {
+              float sum = 0.f, sum_up = 0.f;
+              for (int s = 0; s < shape.splits; ++s) {
+                sum += __ldcg(first + s * split_stride + (size_t)m * DG_ROWS + r);
+                if (MODE == 2) sum_up += __ldcg(first + s * split_stride + (size_t)(shape.nb + m) * DG_ROWS + r);
+              }
+              if (MODE == 2) sum = (sum / (1.0f + expf(-sum))) * sum_up;
+              TO* dst = out + (size_t)m * shape.ldo + n;
+              if (MODE == 1) *dst = from_float<TO>(to_float(*dst) + sum);
+              else *dst = from_float<TO>(sum);
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag is rewritten for the next item
+      }
+    }
+    if (!ok && lane == 0) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 4); }
+  }
+
+  dg_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    dg_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(shape.tmem_cols));
+  }
+}
+
+typedef CUresult (*DgEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static DgEncodeFn dg_encode() {
+  static DgEncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<DgEncodeFn>(ptr);
+  }
+  return fn;
+}
+
+static bool dg_make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+  DgEncodeFn encode = dg_encode();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)DG_BK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1u, 1u};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Splits of K so that tiles * splits fills whole rounds of `sms` blocks; at least 4 slabs a split.
+static int choose_splits(int tiles, int k_iters, int sms) {
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= 16; ++s) {
+    const int per = (k_iters + s - 1) / s;
+    if (s > 1 && per < 4) break;
+    if ((s - 1) * per >= k_iters) continue;  // the last split would be empty
+    const long long items = (long long)tiles * s;
+    const long long rounds = (items + sms - 1) / sms;
+    const double eff = (double)items / (double)(rounds * sms);
+    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+  }
+  return best;
+}
+
+template <int MODE, typename TO>
+int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorMap& map_w, const CUtensorMap& map_x,
+                       const DecodeGemmShape& shape, int smem, int blocks, int* error_flag, cudaStream_t stream) {
+  auto kernel = gemm_decode_tcgen05_kernel<MODE, TO>;
+  static int allowed = 0;
+  if (smem > allowed) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return (int)err;
+    allowed = smem;
+  }
+  launch_kernel(kernel, dim3(blocks), dim3(DG_THREADS), (size_t)smem, stream, map_w, map_x, (TO*)out, partial, counters,
+                shape, error_flag);
+  return launch_status();
+}
+
+}  // namespace xrt
+
+// How much scratch a call needs: floats of `partial` (0 when K is not split).  The same
+// arithmetic as the launcher's, for the caller that allocates.
+XRT_EXPORT long long xrt_gemm_decode_tcgen05_scratch(int M, int N, int K, int mode, int sm_count) {
+  const int tiles = (N + xrt::DG_ROWS - 1) / xrt::DG_ROWS;
+  const int k_iters = (K + xrt::DG_BK - 1) / xrt::DG_BK;
+  const int splits = xrt::choose_splits(tiles, k_iters, sm_count);
+  if (splits == 1) return 0;
+  const int nb = (M + 15) / 16 * 16;
+  return (long long)tiles * splits * (mode == 2 ? 2 : 1) * nb * xrt::DG_ROWS;
+}
+
+// x: bfloat16 [M, K] with row stride ldx, M <= 128; w: bfloat16 [w_rows, K] contiguous; K and ldx
+// multiples of 8, bases 16-byte aligned.  out: [M, N] with row stride ldo.  Modes as for
+// xrt_gemm_stream.  partial: float32 scratch of xrt_gemm_decode_tcgen05_scratch floats (may be null
+// when that is 0); counters: int32 [at least ceil(N / 128)], zero before the first call (the
+// kernel leaves them zero).  error_flag (may be null) is set to 4 if a bounded wait ran out.
+XRT_EXPORT int xrt_gemm_decode_tcgen05(void* out, const void* x, const void* w, float* partial, int* counters, int M,
+                                       int N, int K, int ldx, int ldo, int w_rows, int out_dtype, int mode,
+                                       int up_rows, int sm_count, int* error_flag, cudaStream_t stream) {
+  if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldo < N || mode < 0 || mode > 2 || sm_count <= 0) return XRT_ERR_ARGUMENT;
+  if (mode == 1 && out_dtype != XRT_F32) return XRT_ERR_ARGUMENT;
+  if (mode == 2 ? w_rows < up_rows + N : w_rows < N) return XRT_ERR_ARGUMENT;
+  if (out_dtype != XRT_F32 && out_dtype != XRT_BF16) return XRT_ERR_UNSUPPORTED;
+  if (K % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || M > 128) return XRT_ERR_UNSUPPORTED;
+  if (M == 0) return XRT_OK;
+  xrt::DecodeGemmShape shape;
+  shape.M = M; shape.N = N; shape.K = K; shape.ldo = ldo;
+  shape.nb = (M + 15) / 16 * 16;
+  shape.tiles = (N + xrt::DG_ROWS - 1) / xrt::DG_ROWS;
+  const int k_iters = (K + xrt::DG_BK - 1) / xrt::DG_BK;
+  shape.splits = xrt::choose_splits(shape.tiles, k_iters, sm_count);
+  shape.k_per_split = (k_iters + shape.splits - 1) / shape.splits;
+  shape.up_rows = up_rows;
+  const int groups = mode == 2 ? 2 : 1;
+  const int x_bytes = shape.nb * xrt::DG_BK * 2;
+  const int stage_bytes = groups * xrt::DG_W_BYTES + ((x_bytes + 1023) & ~1023);
+  const int budget = 200 * 1024;
+  shape.stages = budget / stage_bytes;
+  if (shape.stages > 12) shape.stages = 12;
+  if (shape.stages < 2) return XRT_ERR_UNSUPPORTED;
+  int cols = 32;
+  while (cols < 2 * groups * shape.nb) cols *= 2;
+  if (cols > 512) return XRT_ERR_UNSUPPORTED;
+  shape.tmem_cols = cols;
+  if (shape.splits > 1 && (partial == nullptr || counters == nullptr)) return XRT_ERR_ARGUMENT;
+  const int smem = shape.stages * stage_bytes + 512 + 1024;
+  const int items = shape.tiles * shape.splits;
+  const int blocks = items < sm_count ? items : sm_count;
+  CUtensorMap map_w, map_x;
+  if (!xrt::dg_make_map(&map_w, w, w_rows, K, K, xrt::DG_ROWS) || !xrt::dg_make_map(&map_x, x, M, K, ldx, shape.nb))
+    return XRT_ERR_UNSUPPORTED;
+  if (mode == 1)
+    return xrt::launch_decode_gemm<1, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, error_flag, stream);
+  if (mode == 2) {
+    if (out_dtype == XRT_BF16)
+      return xrt::launch_decode_gemm<2, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, error_flag, stream);
+    return xrt::launch_decode_gemm<2, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, error_flag, stream);
+  }
+  if (out_dtype == XRT_BF16)
+    return xrt::launch_decode_gemm<0, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, error_flag, stream);
+  return xrt::launch_decode_gemm<0, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, error_flag, stream);
+}

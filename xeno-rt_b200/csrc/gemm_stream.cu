@@ -39,11 +39,15 @@ __device__ __forceinline__ void gs_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
 }
 
 // MODE 0: store, 1: add into float out, 2: SwiGLU (two groups of rows: gate and up)
-template <int M_TILES, int MODE, int GS_STAGES, typename TO>
-__global__ void __launch_bounds__(GS_THREADS)
+template <int M_TILES, int MODE, int GS_STAGES, int ROW_GROUPS, typename TO>
+__global__ void __launch_bounds__(GS_THREADS, (M_TILES >= 4 ? 2 : 1))
 gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    int M, int N, int K, int ldx, int ldo, long long up_offset) {
-  constexpr int GROUPS = MODE == 2 ? 2 : 1;
+  // ROW_GROUPS groups of 8 weight rows a block (SwiGLU: as many gate groups and as many up groups);
+  // every X fragment a warp loads is used for all of them, which is what keeps the L1 traffic of
+  // many batch rows below the shared-memory traffic of the weights
+  constexpr int GROUPS = ROW_GROUPS * (MODE == 2 ? 2 : 1);
+  constexpr int BLOCK_ROWS = ROW_GROUPS * GS_ROWS;
   constexpr int STAGE_ROWS = GROUPS * GS_ROWS;
   constexpr int STAGE_BYTES = STAGE_ROWS * GS_ROW_BYTES;
   constexpr int CHUNKS_PER_ROW = GS_SLAB / 8;                       // 16-byte pieces of a row's slab
@@ -52,7 +56,7 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
 
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int row0 = blockIdx.x * GS_ROWS;
+  const int row0 = blockIdx.x * BLOCK_ROWS;
   const int n_slabs = (K + GS_SLAB - 1) / GS_SLAB;
 
   // where this thread's copies come from and go to (the same for every slab, shifted by the slab)
@@ -62,8 +66,8 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
 #pragma unroll
   for (int i = 0; i < COPIES; ++i) {
     const int c = threadIdx.x + i * GS_THREADS, r = c / CHUNKS_PER_ROW, j = c % CHUNKS_PER_ROW;
-    const int row = min(row0 + (r % GS_ROWS), N - 1);  // clamped rows are read twice and never stored
-    copy_src[i] = w + (size_t)row * K + (r >= GS_ROWS ? up_offset : 0) + j * 8;
+    const int row = min(row0 + (r % BLOCK_ROWS), N - 1);  // clamped rows are read twice and never stored
+    copy_src[i] = w + (size_t)row * K + (r >= BLOCK_ROWS ? up_offset : 0) + j * 8;
     copy_dst[i] = (uint32_t)__cvta_generic_to_shared(smem + r * GS_ROW_BYTES + j * 16);
     copy_k[i] = j * 8;
   }
@@ -99,11 +103,11 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
       for (int i = 0; i < 4; ++i) acc[gr][mt][i] = 0.f;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
+  constexpr bool EARLY_X = M_TILES < 4;  // few batch rows: X of a slab is loaded before the wait and hides under it;
+  //                                        many: one half slab at a time, to keep the registers for accumulators
   for (int s = 0; s < n_slabs; ++s) {
-    // X of this slab first: it does not depend on the stage and hides under the wait
     uint4 xa[2][M_TILES], xb[2][M_TILES];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
+    auto load_x = [&](int h) {
       const int k = s * GS_SLAB + warp * 64 + h * 32 + t * 8;
       const bool inside = k < K;  // differs between lanes; only loads are conditional, every lane runs the MMAs
 #pragma unroll
@@ -111,7 +115,8 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
         xa[h][mt] = inside ? *reinterpret_cast<const uint4*>(xlo[mt] + k) : zero;
         xb[h][mt] = inside ? *reinterpret_cast<const uint4*>(xhi[mt] + k) : zero;
       }
-    }
+    };
+    if (EARLY_X) { load_x(0); load_x(1); }
     asm volatile("cp.async.wait_group %0;" ::"n"(GS_STAGES - 2));
     __syncthreads();  // slab s has landed for every thread, and every warp is done with slab s - 1
     if (s + GS_STAGES - 1 < n_slabs) issue(s + GS_STAGES - 1);  // into the stage that slab s - 1 used
@@ -119,6 +124,7 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
     const unsigned char* base = smem + (s % GS_STAGES) * STAGE_BYTES;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
+      if (!EARLY_X) load_x(h);
       const int kk = warp * 64 + h * 32 + t * 8;
 #pragma unroll
       for (int gr = 0; gr < GROUPS; ++gr) {
@@ -148,42 +154,42 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
       p[(g + 8) * P_ROW + 2 * t + 1] = acc[gr][mt][3];
     }
   __syncthreads();
-  for (int e = threadIdx.x; e < M_TILES * 16 * GS_ROWS; e += blockDim.x) {
-    const int n = e % GS_ROWS, m = e / GS_ROWS;
+  for (int e = threadIdx.x; e < M_TILES * 16 * BLOCK_ROWS; e += blockDim.x) {
+    const int nb = e % BLOCK_ROWS, m = e / BLOCK_ROWS;
+    const int rg = nb / GS_ROWS, n = nb % GS_ROWS;
     const int mt = m / 16, mr = m % 16;
-    const int row = row0 + n;
+    const int row = row0 + nb;
     if (m >= M || row >= N) continue;
-    float sums[GROUPS];
-#pragma unroll
-    for (int gr = 0; gr < GROUPS; ++gr) {
+    auto total = [&](int gr) {
       float sum = 0.f;
 #pragma unroll
       for (int ww = 0; ww < GS_WARPS; ++ww)
         sum += partial[((((size_t)ww * GROUPS + gr) * M_TILES + mt) * 16 + mr) * P_ROW + n];
-      sums[gr] = sum;
-    }
+      return sum;
+    };
+    const float first = total(rg);
     TO* dst = out + (size_t)m * ldo + row;
-    if (MODE == 2) *dst = from_float<TO>((sums[0] / (1.0f + expf(-sums[0]))) * sums[GROUPS - 1]);
-    else if (MODE == 1) *dst = from_float<TO>(to_float(*dst) + sums[0]);
-    else *dst = from_float<TO>(sums[0]);
+    if (MODE == 2) *dst = from_float<TO>((first / (1.0f + expf(-first))) * total(ROW_GROUPS + rg));
+    else if (MODE == 1) *dst = from_float<TO>(to_float(*dst) + first);
+    else *dst = from_float<TO>(first);
   }
 }
 
-template <int M_TILES, int MODE, int GS_STAGES, typename TO>
+template <int M_TILES, int MODE, int GS_STAGES, int ROW_GROUPS, typename TO>
 int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
                          long long up_offset, cudaStream_t stream) {
-  constexpr int GROUPS = MODE == 2 ? 2 : 1;
+  constexpr int GROUPS = ROW_GROUPS * (MODE == 2 ? 2 : 1);
   constexpr int RING_BYTES = GS_STAGES * GROUPS * GS_ROWS * GS_ROW_BYTES;
   constexpr int PARTIAL_BYTES = GS_WARPS * GROUPS * M_TILES * 16 * (GS_ROWS + 1) * (int)sizeof(float);
   constexpr int SMEM = RING_BYTES > PARTIAL_BYTES ? RING_BYTES : PARTIAL_BYTES;
-  auto kernel = gemm_stream_kernel<M_TILES, MODE, GS_STAGES, TO>;
+  auto kernel = gemm_stream_kernel<M_TILES, MODE, GS_STAGES, ROW_GROUPS, TO>;
   static bool allowed = false;
   if (SMEM > 48 * 1024 && !allowed) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (err != cudaSuccess) return (int)err;
     allowed = true;
   }
-  const int blocks = (N + GS_ROWS - 1) / GS_ROWS;
+  const int blocks = (N + ROW_GROUPS * GS_ROWS - 1) / (ROW_GROUPS * GS_ROWS);
   launch_kernel(kernel, dim3(blocks), dim3(GS_THREADS), SMEM, stream, (TO*)out, (const __nv_bfloat16*)x,
                 (const __nv_bfloat16*)w, M, N, K, ldx, ldo, up_offset);
   return launch_status();
@@ -194,7 +200,8 @@ int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, 
 template <int M_TILES, int MODE, typename TO>
 int launch_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, long long up_offset,
                   cudaStream_t stream) {
-  return launch_stream_staged<M_TILES, MODE, 3, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, stream);
+  // more than 32 batch rows: two row groups a block halve the X traffic per weight byte
+  return launch_stream_staged<M_TILES, MODE, 3, (M_TILES >= 4 ? 2 : 1), TO>(out, x, w, M, N, K, ldx, ldo, up_offset, stream);
 }
 
 template <int M_TILES>

@@ -34,6 +34,7 @@ _SIGNATURES = {
     "xrt_gemm_reference": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "xrt_gemm_decode_tcgen05": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
@@ -61,6 +62,8 @@ def library():
                     raise KernelError(f"{path} does not export {name}") from None
                 fn.argtypes = argtypes
                 fn.restype = _I
+            lib.xrt_gemm_decode_tcgen05_scratch.argtypes = [_I, _I, _I, _I, _I]
+            lib.xrt_gemm_decode_tcgen05_scratch.restype = ctypes.c_longlong
             _lib = lib
     return _lib
 
@@ -240,6 +243,49 @@ def check_error_flag(device) -> None:
         flag.zero_()
         raise KernelError(f"a kernel reported error {value}: a bounded wait on a copy or a tensor-core operation ran "
                           f"out; results of the last steps are not valid")
+
+
+DECODE_TCGEN05_MAX_ROWS = 128
+_counters: dict = {}
+_sm_counts: dict = {}
+_COUNTER_SLOTS = 1 << 16
+
+
+def device_state(device):
+    """Per-device state of the kernels, made when a model is built (never inside a stream capture):
+    the error flag, the tile counters of the split-K decode product (zero between launches) and
+    the number of multiprocessors."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _counters:
+        _counters[key] = torch.zeros(_COUNTER_SLOTS, dtype=torch.int32, device=device)
+        _sm_counts[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return error_flag(device), _counters[key], _sm_counts[key]
+
+
+def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
+    """bfloat16 product for at most 128 rows on the tcgen05 tensor cores with swapped operands:
+    the weight is streamed once by TMA, K is split across blocks and summed in split order."""
+    m, k = x.shape
+    n = out.shape[1]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_decode_tcgen05: operands must be bfloat16")
+    rows_needed = n + up_rows if mode == "swiglu" else n
+    if w.shape[1] != k or w.shape[0] < rows_needed or out.shape[0] != m or (mode != "swiglu" and w.shape[0] != n):
+        raise KernelError(f"gemm_decode_tcgen05: shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if x.stride(1) != 1 or out.stride(1) != 1 or not x.is_cuda or not out.is_cuda:
+        raise KernelError("gemm_decode_tcgen05: rows must be contiguous and on a CUDA device")
+    if (n + 127) // 128 > _COUNTER_SLOTS:
+        raise KernelError("gemm_decode_tcgen05: more tiles than counters")
+    code = {"store": 0, "accumulate": 1, "swiglu": 2}[mode]
+    flag, counters, sms = device_state(x.device)
+    lib = library()
+    floats = lib.xrt_gemm_decode_tcgen05_scratch(m, n, k, code, sms)
+    partial = torch.empty(floats, dtype=torch.float32, device=x.device) if floats else None
+    _check(lib.xrt_gemm_decode_tcgen05(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), _ptr(partial, "partial"),
+                                       counters.data_ptr(), m, n, k, x.stride(0), out.stride(0), w.shape[0],
+                                       _code(out.dtype), code, up_rows, sms, flag.data_ptr(), _stream()),
+           "gemm_decode_tcgen05")
 
 
 def gemm_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0) -> None:

@@ -40,7 +40,7 @@ class Model:
         self.arrangements = [part_class("arrangement", l.arrangement) for l in spec.layers]
         self.final_norm = build("norm", spec.final_norm)
         self.lm_head = build("lm_head", spec.lm_head)
-        self.error_flag = ops.error_flag(self.device)
+        self.error_flag = ops.device_state(self.device)[0]
         parts = [self.embedding, self.final_norm, self.lm_head]
         for layer in self.layers:
             parts += [layer.mixer_norm, layer.mixer, layer.ffn_norm, layer.ffn]

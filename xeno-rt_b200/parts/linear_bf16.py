@@ -1,8 +1,16 @@
 """Choice among the bfloat16 matrix-product kernels.  ``run`` returns False when none of the
-tensor-core kernels takes the shape, and the caller uses the CUDA-core kernel that takes any."""
+tensor-core kernels takes the shape, and the caller uses the CUDA-core kernel that takes any.
+
+Few rows (decode steps): the weight-streaming tcgen05 kernel with swapped operands and split K
+(``XRT_DECODE_GEMM=stream`` selects the mma.sync streaming kernel instead, for comparison).
+Many rows (prompts): the tiled tcgen05 kernel."""
 from __future__ import annotations
 
+import os
+
 from ..csrc import ops
+
+USE_STREAM = os.environ.get("XRT_DECODE_GEMM", "tcgen05") == "stream"
 
 
 def aligned(x, weight) -> bool:
@@ -11,15 +19,20 @@ def aligned(x, weight) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and weight.is_contiguous())
 
 
+def _product(out, x, weight, mode: str, up_rows: int = 0) -> None:
+    rows = x.shape[0]
+    if USE_STREAM and rows <= ops.STREAM_MAX_ROWS:
+        ops.gemm_stream(out, x, weight, mode, up_rows)
+    elif rows <= ops.DECODE_TCGEN05_MAX_ROWS:
+        ops.gemm_decode_tcgen05(out, x, weight, mode, up_rows)
+    else:
+        ops.gemm_tcgen05(out, x, weight, mode, up_rows)
+
+
 def run(out, x, weight, accumulate: bool) -> bool:
     if not aligned(x, weight):
         return False
-    mode = "accumulate" if accumulate else "store"
-    rows = x.shape[0]
-    if rows <= ops.STREAM_MAX_ROWS:
-        ops.gemm_stream(out, x, weight, mode)
-        return True
-    ops.gemm_tcgen05(out, x, weight, mode)
+    _product(out, x, weight, "accumulate" if accumulate else "store")
     return True
 
 
@@ -28,8 +41,5 @@ def run_swiglu(out, x, weight_gate_up, inner: int) -> bool:
     fused kernel takes the shape."""
     if not aligned(x, weight_gate_up):
         return False
-    if x.shape[0] <= ops.STREAM_MAX_ROWS:
-        ops.gemm_stream(out, x, weight_gate_up, "swiglu", up_rows=inner)
-    else:
-        ops.gemm_tcgen05(out, x, weight_gate_up, "swiglu", up_rows=inner)
+    _product(out, x, weight_gate_up, "swiglu", inner)
     return True
