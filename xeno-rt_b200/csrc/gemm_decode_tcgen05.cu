@@ -30,6 +30,7 @@ constexpr int DG_ROWS = 128, DG_BK = 64, DG_UMMA_K = 16;
 constexpr int DG_W_BYTES = DG_ROWS * DG_BK * 2;  // 16 KB: one slab of one group of weight rows
 constexpr int DG_THREADS = 192;
 constexpr long long DG_SPIN_LIMIT = 1ll << 24;
+constexpr int DG_MAX_SPLITS = 8;
 
 __device__ __forceinline__ uint32_t dg_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void dg_mbar_init(uint32_t bar, int count) {
@@ -147,7 +148,12 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         const int tile = item / shape.splits, split = item % shape.splits;
         const int kb0 = split * shape.k_per_split;
         const int kb1 = min(k_iters_total, kb0 + shape.k_per_split);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        // Blocks that work at the same time start their walk over K at different slabs (a rotation
+        // that depends on the tile only, so the order of the sum is fixed per output element):
+        // otherwise every block asks the L2 for the same few lines of X at the same moment.
+        const int span = kb1 - kb0, rotate = span > 0 ? (tile * 5) % span : 0;
+        for (int i = 0; i < span; ++i, ++it) {
+          const int kb = kb0 + (i + rotate) % span;
           const int s = it % stages;
           ok = dg_mbar_wait(dg_smem(&empty[s]), ((it / stages) & 1) ^ 1, abort_flag);
           if (!ok) break;
@@ -179,7 +185,7 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         if (!ok) break;
         dg_fence_after();
         const uint32_t tmem_d = tmem_base + a * acc_cols;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {  // the slabs arrive in the producer's rotated order
           const int s = it % stages;
           ok = dg_mbar_wait(dg_smem(&full[s]), (it / stages) & 1, abort_flag);
           if (!ok) break;
@@ -240,13 +246,18 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
           }
         }
       } else {
-        // partial[(tile * splits + split)][group][batch row][128]: lanes write consecutive floats
-        float* mine = partial + ((size_t)item * GROUPS) * shape.nb * DG_ROWS;
+        // partial[(tile * splits + split)][group][weight row][NB]: a thread owns its row's NB floats
+        float* mine = partial + ((size_t)item * GROUPS) * DG_ROWS * shape.nb;
         for (int c = 0; c < acc_cols; c += 16) {
           uint32_t v[16];
           if (has_k) { dg_ld16(v, tmem_row + c); dg_wait_ld(); }
+          const int gr = c / shape.nb, col = c - gr * shape.nb;
+          float4* dst4 = reinterpret_cast<float4*>(mine + ((size_t)gr * DG_ROWS + r) * shape.nb + col);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) mine[(size_t)(c + j) * DG_ROWS + r] = has_k ? __uint_as_float(v[j]) : 0.f;
+          for (int j = 0; j < 4; ++j)
+            dst4[j] = has_k ? make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                          __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
         }
       }
       if (has_k) {
@@ -265,19 +276,43 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*last_flag) {
           __threadfence();
-          const float* first = partial + ((size_t)tile * shape.splits * GROUPS) * shape.nb * DG_ROWS;
-          const size_t split_stride = (size_t)GROUPS * shape.nb * DG_ROWS;
+          const float* first = partial + ((size_t)tile * shape.splits * GROUPS) * DG_ROWS * shape.nb;
+          const size_t split_stride = (size_t)GROUPS * DG_ROWS * shape.nb;
           if (n < shape.N) {
-            for (int m = 0; m < shape.M; ++m) {
-              float sum = 0.f, sum_up = 0.f;
-              for (int s = 0; s < shape.splits; ++s) {
-                sum += __ldcg(first + s * split_stride + (size_t)m * DG_ROWS + r);
-                if (MODE == 2) sum_up += __ldcg(first + s * split_stride + (size_t)(shape.nb + m) * DG_ROWS + r);
+            // sixteen batch rows at a time, every split's partial loaded (16 bytes a load) before the
+            // first is added: the loads are in flight together, the additions stay in split order
+            for (int m0 = 0; m0 < shape.M; m0 += 16) {
+              float sums[GROUPS][16];
+#pragma unroll
+              for (int gr = 0; gr < GROUPS; ++gr) {
+                float4 part[DG_MAX_SPLITS][4];
+                const float* row = first + ((size_t)gr * DG_ROWS + r) * shape.nb + m0;
+#pragma unroll
+                for (int s = 0; s < DG_MAX_SPLITS; ++s)
+#pragma unroll
+                  for (int q = 0; q < 4; ++q)
+                    part[s][q] = s < shape.splits ? __ldcg(reinterpret_cast<const float4*>(row + s * split_stride) + q)
+                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                  for (int s = 0; s < DG_MAX_SPLITS; ++s) {
+                    t.x += part[s][q].x; t.y += part[s][q].y; t.z += part[s][q].z; t.w += part[s][q].w;
+                  }
+                  sums[gr][4 * q] = t.x; sums[gr][4 * q + 1] = t.y; sums[gr][4 * q + 2] = t.z; sums[gr][4 * q + 3] = t.w;
+                }
               }
-              if (MODE == 2) sum = (sum / (1.0f + expf(-sum))) * sum_up;
-              TO* dst = out + (size_t)m * shape.ldo + n;
-              if (MODE == 1) *dst = from_float<TO>(to_float(*dst) + sum);
-              else *dst = from_float<TO>(sum);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (m0 + j < shape.M) {
+                  float val = sums[0][j];
+                  if (MODE == 2) val = (val / (1.0f + expf(-val))) * sums[GROUPS - 1][j];
+                  TO* dst = out + (size_t)(m0 + j) * shape.ldo + n;
+                  if (MODE == 1) *dst = from_float<TO>(to_float(*dst) + val);
+                  else *dst = from_float<TO>(val);
+                }
+              }
             }
           }
         }
@@ -323,18 +358,25 @@ static bool dg_make_map(CUtensorMap* map, const void* base, int rows, int cols, 
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Splits of K so that tiles * splits fills whole rounds of `sms` blocks; at least 4 slabs a split.
-static int choose_splits(int tiles, int k_iters, int sms) {
+// Splits of K: more splits fill the multiprocessors more evenly when the tiles are few, but every
+// split writes and the last reads a 128 x NB partial tile.  The choice minimises
+// (weight bytes + partial traffic) / (share of the block rounds that do work).  It depends on N, K
+// and the padded batch NB (16, 32, ... 128), so a row's sum has the same order for every batch of
+// the same NB; between NB classes it may differ by rounding.  At least 4 slabs a split.
+static int choose_splits(int tiles, int k_iters, int sms, int groups, int nb) {
   int best = 1;
-  double best_eff = 0.0;
-  for (int s = 1; s <= 16; ++s) {
+  double best_cost = 0.0;
+  const double weight_bytes = (double)groups * DG_ROWS * k_iters * DG_BK * 2;
+  for (int s = 1; s <= DG_MAX_SPLITS; ++s) {
     const int per = (k_iters + s - 1) / s;
     if (s > 1 && per < 4) break;
     if ((s - 1) * per >= k_iters) continue;  // the last split would be empty
     const long long items = (long long)tiles * s;
     const long long rounds = (items + sms - 1) / sms;
-    const double eff = (double)items / (double)(rounds * sms);
-    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    const double busy = (double)items / (double)(rounds * sms);
+    const double partial_bytes = s > 1 ? 2.0 * s * groups * nb * DG_ROWS * 4 : 0.0;
+    const double cost = (weight_bytes + partial_bytes) / busy;
+    if (s == 1 || cost < best_cost * 0.98) { best_cost = cost; best = s; }
   }
   return best;
 }
@@ -361,7 +403,7 @@ int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorM
 XRT_EXPORT long long xrt_gemm_decode_tcgen05_scratch(int M, int N, int K, int mode, int sm_count) {
   const int tiles = (N + xrt::DG_ROWS - 1) / xrt::DG_ROWS;
   const int k_iters = (K + xrt::DG_BK - 1) / xrt::DG_BK;
-  const int splits = xrt::choose_splits(tiles, k_iters, sm_count);
+  const int splits = xrt::choose_splits(tiles, k_iters, sm_count, mode == 2 ? 2 : 1, (M + 15) / 16 * 16);
   if (splits == 1) return 0;
   const int nb = (M + 15) / 16 * 16;
   return (long long)tiles * splits * (mode == 2 ? 2 : 1) * nb * xrt::DG_ROWS;
@@ -386,7 +428,7 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05(void* out, const void* x, const void* w, 
   shape.nb = (M + 15) / 16 * 16;
   shape.tiles = (N + xrt::DG_ROWS - 1) / xrt::DG_ROWS;
   const int k_iters = (K + xrt::DG_BK - 1) / xrt::DG_BK;
-  shape.splits = xrt::choose_splits(shape.tiles, k_iters, sm_count);
+  shape.splits = xrt::choose_splits(shape.tiles, k_iters, sm_count, mode == 2 ? 2 : 1, shape.nb);
   shape.k_per_split = (k_iters + shape.splits - 1) / shape.splits;
   shape.up_rows = up_rows;
   const int groups = mode == 2 ? 2 : 1;

@@ -1,16 +1,19 @@
 """Choice among the bfloat16 matrix-product kernels.  ``run`` returns False when none of the
 tensor-core kernels takes the shape, and the caller uses the CUDA-core kernel that takes any.
 
-Few rows (decode steps): the weight-streaming tcgen05 kernel with swapped operands and split K
-(``XRT_DECODE_GEMM=stream`` selects the mma.sync streaming kernel instead, for comparison).
-Many rows (prompts): the tiled tcgen05 kernel."""
+Up to 16 rows: the cp.async weight-streaming kernel (its fixed cost is the lowest, which is what
+counts when a product reads 30 to 100 MB).  17 to 128 rows: the weight-streaming tcgen05 kernel with
+swapped operands and split K (the batch is the MMA's N, so its time stays the time to read the
+weight).  More rows (prompts): the tiled tcgen05 kernel.  ``XRT_DECODE_GEMM=stream`` or ``tcgen05``
+forces one of the two decode kernels wherever it applies, for comparison."""
 from __future__ import annotations
 
 import os
 
 from ..csrc import ops
 
-USE_STREAM = os.environ.get("XRT_DECODE_GEMM", "tcgen05") == "stream"
+FORCE = os.environ.get("XRT_DECODE_GEMM", "")
+STREAM_ROWS = 16
 
 
 def aligned(x, weight) -> bool:
@@ -21,7 +24,8 @@ def aligned(x, weight) -> bool:
 
 def _product(out, x, weight, mode: str, up_rows: int = 0) -> None:
     rows = x.shape[0]
-    if USE_STREAM and rows <= ops.STREAM_MAX_ROWS:
+    stream_rows = ops.STREAM_MAX_ROWS if FORCE == "stream" else (0 if FORCE == "tcgen05" else STREAM_ROWS)
+    if rows <= stream_rows:
         ops.gemm_stream(out, x, weight, mode, up_rows)
     elif rows <= ops.DECODE_TCGEN05_MAX_ROWS:
         ops.gemm_decode_tcgen05(out, x, weight, mode, up_rows)
