@@ -6,14 +6,16 @@ from ..csrc import ops
 from .context import context_bucket
 
 SM_COUNT = 148
-DECODE_BLOCKS_PER_SM = 3
+DECODE_BLOCKS_PER_SM = 3   # 70 KB of shared memory a block at head size 128
+DECODE_WAVES = 2           # blocks wanted = what the GPU holds at once, times this (measured: 1 leaves a long tail
+#                            at 64 sequences, 4 costs more in partials at 8)
 
 
 def decode_split(n_seqs: int, n_kv_heads: int, max_context: int):
     """(keys a split, number of splits) for decode attention: enough thread blocks to fill the GPU
     when sequences are few, at least two tiles of 64 keys a split where the context allows."""
     blocks = max(1, (max_context + 63) // 64)
-    want = -(-SM_COUNT * DECODE_BLOCKS_PER_SM // (n_seqs * n_kv_heads))
+    want = -(-SM_COUNT * DECODE_BLOCKS_PER_SM * DECODE_WAVES // (n_seqs * n_kv_heads))
     splits = max(1, min(want, (blocks + 1) // 2))
     chunk = 64 * (-(-blocks // splits))
     return chunk, -(-blocks * 64 // chunk)
