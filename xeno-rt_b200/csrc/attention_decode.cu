@@ -71,13 +71,15 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
 
   const int* blocks = block_table + (size_t)slot * max_blocks;
   const size_t head_stride = (size_t)XRT_BLOCK_TOKENS * head_dim;
+  TileCopier copier;
+  copier.init(head_dim);
   auto issue_tile = [&](int tile_index, int buffer) {
     const int key0 = begin + tile_index * XRT_BLOCK_TOKENS;
     const int block = blocks[key0 / XRT_BLOCK_TOKENS];
     const size_t base = ((size_t)block * n_kv_heads + kv_head) * head_stride;
     const int live = min(XRT_BLOCK_TOKENS, len - key0);
-    copy_tile_async(k_tiles + buffer * tile_bytes, k_pool + base, XRT_BLOCK_TOKENS, live, head_dim);
-    copy_tile_async(v_tiles + buffer * tile_bytes, v_pool + base, XRT_BLOCK_TOKENS, live, head_dim);
+    copier.copy(k_tiles + buffer * tile_bytes, k_pool + base, XRT_BLOCK_TOKENS, live);
+    copier.copy(v_tiles + buffer * tile_bytes, v_pool + base, XRT_BLOCK_TOKENS, live);
     cp_async_commit();
   };
 
@@ -101,7 +103,8 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   // merge the four warps: maxima first, then the rescaled sums and outputs in warp order
   float* merge_m = reinterpret_cast<float*>(smem);                 // [warps][16]
   float* merge_l = merge_m + DEC_WARPS * 16;                       // [warps][16]
-  float* merge_o = merge_l + DEC_WARPS * 16;                       // [warps][16][head_dim]
+  float* merge_o = merge_l + DEC_WARPS * 16;                       // [warps][16][head_dim + 8]: rows in different banks
+  const int merge_stride = head_dim + 8;
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
@@ -113,7 +116,7 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     if (dt * 8 < head_dim) {
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        merge_o[((size_t)warp * 16 + g + (e >> 1) * 8) * head_dim + dt * 8 + 2 * t + (e & 1)] = st.o[dt][e];
+        merge_o[((size_t)warp * 16 + g + (e >> 1) * 8) * merge_stride + dt * 8 + 2 * t + (e & 1)] = st.o[dt][e];
     }
   }
   __syncthreads();
@@ -128,7 +131,7 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
       const float mw = merge_m[w * 16 + row];
       const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
       l += f * merge_l[w * 16 + row];
-      o += f * merge_o[((size_t)w * 16 + row) * head_dim + d];
+      o += f * merge_o[((size_t)w * 16 + row) * merge_stride + d];
     }
     const int head = kv_head * group + row;
     if (n_splits == 1) {
@@ -198,7 +201,7 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_
                   const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                   float scale, int window, int chunk, int n_splits, cudaStream_t stream) {
   const int tile_bytes = XRT_BLOCK_TOKENS * (head_dim * 2 + 16);
-  const int merge_bytes = DEC_WARPS * 16 * (2 + head_dim) * (int)sizeof(float);
+  const int merge_bytes = DEC_WARPS * 16 * (2 + head_dim + 8) * (int)sizeof(float);
   const int smem = max(4 * tile_bytes, merge_bytes);
   auto kernel = attention_decode_kernel<HD_MAX>;
   static int smem_allowed = 0;  // raised once a size class; not a stream operation

@@ -43,17 +43,40 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Copies `rows` rows of head_dim bfloat16 from a contiguous global tile into padded shared rows.
-// Rows at or beyond `live_rows` are zero-filled.  All threads of the block take part.
-__device__ __forceinline__ void copy_tile_async(unsigned char* dst, const __nv_bfloat16* src, int rows, int live_rows,
-                                                int head_dim) {
-  const int chunks_per_row = head_dim / 8;  // 16-byte pieces
-  const int row_bytes = tile_row_bytes(head_dim);
-  for (int c = threadIdx.x; c < rows * chunks_per_row; c += blockDim.x) {
-    const int r = c / chunks_per_row, j = c - r * chunks_per_row;
-    cp_async_16(smem_addr(dst + r * row_bytes + j * 16), src + (size_t)r * head_dim + j * 8, r < live_rows ? 16 : 0);
+// How one thread takes part in copying tiles of `rows` x head_dim bfloat16 (contiguous in global
+// memory) into padded shared rows: computed once a kernel, so that a tile costs a thread a few
+// additions and its 16-byte asynchronous copies.  When the block's threads are a multiple of the
+// 16-byte pieces of a row (head sizes 16, 32, 64, 128, 256 with 128 threads) a thread keeps one
+// column of pieces and steps down the rows; other head sizes divide per piece.
+struct TileCopier {
+  int pieces_per_row, row_bytes, head_dim;
+  int first_row, piece, row_step;  // the regular case
+  bool regular;
+  __device__ __forceinline__ void init(int head_dim_) {
+    head_dim = head_dim_;
+    pieces_per_row = head_dim / 8;
+    row_bytes = tile_row_bytes(head_dim);
+    regular = blockDim.x % pieces_per_row == 0;
+    first_row = threadIdx.x / pieces_per_row;
+    piece = threadIdx.x - first_row * pieces_per_row;
+    row_step = blockDim.x / pieces_per_row;
   }
-}
+  // Rows at or beyond `live_rows` are zero-filled.  All threads of the block take part.
+  __device__ __forceinline__ void copy(unsigned char* dst, const __nv_bfloat16* src, int rows, int live_rows) const {
+    if (regular) {
+      uint32_t d = smem_addr(dst + first_row * row_bytes + piece * 16);
+      const __nv_bfloat16* s = src + (size_t)first_row * head_dim + piece * 8;
+      const uint32_t d_step = (uint32_t)(row_step * row_bytes);
+      const size_t s_step = (size_t)row_step * head_dim;
+      for (int r = first_row; r < rows; r += row_step, d += d_step, s += s_step) cp_async_16(d, s, r < live_rows ? 16 : 0);
+    } else {
+      for (int c = threadIdx.x; c < rows * pieces_per_row; c += blockDim.x) {
+        const int r = c / pieces_per_row, j = c - r * pieces_per_row;
+        cp_async_16(smem_addr(dst + r * row_bytes + j * 16), src + (size_t)r * head_dim + j * 8, r < live_rows ? 16 : 0);
+      }
+    }
+  }
+};
 
 // The running state of one warp's 16 query rows: lane (g = lane / 4, t = lane % 4) holds rows g
 // and g + 8; `o` holds, for each 8-wide slice of head_dim, the four accumulators of the MMA layout.

@@ -81,13 +81,15 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
 
   const int* blocks = block_table + (size_t)slot * max_blocks;
   const size_t head_stride = (size_t)XRT_BLOCK_TOKENS * head_dim;
+  TileCopier copier;
+  copier.init(head_dim);
   auto issue_tile = [&](int tile_index, int buffer) {
     const int key0 = (first_tile + tile_index) * XRT_BLOCK_TOKENS;
     const int block = blocks[key0 / XRT_BLOCK_TOKENS];
     const size_t base = ((size_t)block * n_kv_heads + kv_head) * head_stride;
     const int live = min(XRT_BLOCK_TOKENS, block_hi - key0);
-    copy_tile_async(k_tiles + buffer * tile_bytes, k_pool + base, XRT_BLOCK_TOKENS, live, head_dim);
-    copy_tile_async(v_tiles + buffer * tile_bytes, v_pool + base, XRT_BLOCK_TOKENS, live, head_dim);
+    copier.copy(k_tiles + buffer * tile_bytes, k_pool + base, XRT_BLOCK_TOKENS, live);
+    copier.copy(v_tiles + buffer * tile_bytes, v_pool + base, XRT_BLOCK_TOKENS, live);
     cp_async_commit();
   };
 
