@@ -195,13 +195,15 @@ int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, 
   return launch_status();
 }
 
-// Three stages: 26 KB a block, eight blocks a multiprocessor (a deeper ring with fewer resident
-// blocks measured slower, also for the small products).
+// Three stages: 26 KB a block; registers allow four blocks a multiprocessor.  Rings of 4, 5 and 6
+// stages were measured: they help single shapes (the output matrix at one row reaches 6.7 TB/s with
+// 5) and lose on others; over a whole decode step of 8 sequences 3 stages is the fastest.
 template <int M_TILES, int MODE, typename TO>
 int launch_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, long long up_offset,
                   cudaStream_t stream) {
   // more than 32 batch rows: two row groups a block halve the X traffic per weight byte
-  return launch_stream_staged<M_TILES, MODE, 3, (M_TILES >= 4 ? 2 : 1), TO>(out, x, w, M, N, K, ldx, ldo, up_offset, stream);
+  constexpr int RG = M_TILES >= 4 ? 2 : 1;
+  return launch_stream_staged<M_TILES, MODE, 3, RG, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, stream);
 }
 
 template <int M_TILES>
