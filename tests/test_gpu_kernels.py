@@ -277,8 +277,8 @@ def test_gemm_stream_refuses_what_it_cannot_take():
 
 
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (5, 1, 48), (32, 8, 128), (6, 3, 80), (16, 1, 256), (8, 8, 64)])
-@pytest.mark.parametrize("chunk,n_splits", [(64, 11), (256, 3), (704, 1)])
-def test_attention_decode_kernel(nh, nkv, hd, chunk, n_splits):
+@pytest.mark.parametrize("chunk,n_splits,fused", [(64, 11, True), (64, 11, False), (256, 3, True), (704, 1, True)])
+def test_attention_decode_kernel(nh, nkv, hd, chunk, n_splits, fused):
     """Five sequences of unequal lengths (one of a single token, one ending at a block edge, one a
     padding row), one token each, against the plain attention of the full sequences."""
     torch.manual_seed(nh + hd + chunk)
@@ -294,7 +294,14 @@ def test_attention_decode_kernel(nh, nkv, hd, chunk, n_splits):
     tok_pos = torch.tensor([lens[s] - 1 if s >= 0 else 0 for s in order], dtype=torch.int32, device=DEV)
     out = torch.full_like(q, 7.0)
     ops().attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd), 0,
-                           chunk, n_splits)
+                           chunk, n_splits, fused=fused)
+    if fused:  # the merge by the last block gives the bits of the merge by the second kernel, and leaves the counters zero
+        two = torch.full_like(q, 7.0)
+        ops().attention_decode(two, q, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd), 0,
+                               chunk, n_splits, fused=False)
+        assert torch.equal(out, two)
+        from xeno_rt_b200.csrc import ops as o
+        assert int(o.device_state(DEV)[1].abs().sum()) == 0
     bf = lambda x: f64(x.to(torch.bfloat16)).reshape(x.shape[0], -1)
     for row, s in enumerate(order):
         if s < 0:

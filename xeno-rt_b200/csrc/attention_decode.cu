@@ -25,15 +25,15 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ tok_slot,
                         const int* __restrict__ tok_pos, const int* __restrict__ block_table, int max_blocks,
                         int n_heads, int n_kv_heads, int head_dim, float scale_log2, int window, int chunk,
-                        int n_splits) {
+                        int n_splits, int* __restrict__ counters) {
   constexpr int D_TILES = HD_MAX / 8;
   extern __shared__ __align__(16) unsigned char smem[];
   pdl_trigger();
   pdl_wait();
   const int split = blockIdx.x, kv_head = blockIdx.y, tok = blockIdx.z;
   const int slot = tok_slot[tok];
-  if (slot < 0) {  // a padding row: zeros (with several splits the combine kernel writes them)
-    if (n_splits == 1) {
+  if (slot < 0) {  // a padding row: zeros (with several splits and no counters the combine kernel writes them)
+    if (n_splits == 1 || (counters != nullptr && split == 0)) {
       const int group = n_heads / n_kv_heads;
       __nv_bfloat16* dst = out + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
       for (int i = threadIdx.x; i < group * head_dim; i += blockDim.x) dst[i] = __float2bfloat16_rn(0.f);
@@ -94,9 +94,9 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     else cp_async_wait<0>();
     __syncthreads();
     const int key_abs = begin + i * XRT_BLOCK_TOKENS + warp * 16;
-    if (key_abs < end)
+    if (key_abs < end)  // only the first and the last 16 keys a warp sees can hold a hidden key
       attend_16_keys<D_TILES>(st, qf, k_tiles + (i & 1) * tile_bytes, v_tiles + (i & 1) * tile_bytes, warp * 16,
-                              key_abs, key_lo, key_hi, head_dim, scale_log2);
+                              key_abs, key_lo, key_hi, key_abs < first_key || key_abs + 16 > len, head_dim, scale_log2);
     __syncthreads();  // the buffer is free for the tile after next
   }
 
@@ -141,6 +141,63 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
       part_o[p * head_dim + d] = o;
       if (d == 0) { part_ml[p * 2] = m; part_ml[p * 2 + 1] = l; }
     }
+  }
+  if (n_splits == 1 || counters == nullptr) return;
+
+  // The block that brings the last live split of this (token, kv head) merges all of them, in
+  // split order (no block waits for another; which block is last does not change the result).
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  const int first_block_key = (first_key / XRT_BLOCK_TOKENS) * XRT_BLOCK_TOKENS;
+  if (threadIdx.x == 0) {
+    int n_live = 0;
+    for (int s = 0; s < n_splits; ++s) n_live += max(s * chunk, first_block_key) < min((s + 1) * chunk, len);
+    int* counter = counters + tok * n_kv_heads + kv_head;
+    const int before = atomicAdd(counter, 1);
+    is_last = before == n_live - 1;
+    if (is_last) *counter = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  float* all_m = reinterpret_cast<float*>(smem);      // [group][n_splits]: the split's maximum, then its weight
+  float* all_l = all_m + group * n_splits;            // [group][n_splits]
+  float* row_l = all_l + group * n_splits;            // [group]
+  for (int i = threadIdx.x; i < group * n_splits; i += blockDim.x) {
+    const int row = i / n_splits, s = i - row * n_splits;
+    const bool live = max(s * chunk, first_block_key) < min((s + 1) * chunk, len);
+    const size_t p = ((size_t)tok * n_heads + kv_head * group + row) * n_splits + s;
+    all_m[i] = live ? __ldcg(part_ml + p * 2) : -INFINITY;
+    all_l[i] = live ? __ldcg(part_ml + p * 2 + 1) : 0.f;
+  }
+  __syncthreads();
+  if (threadIdx.x < group) {
+    const int row = threadIdx.x;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, all_m[row * n_splits + s]);
+    float l = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = all_m[row * n_splits + s];
+      const float f = ms == -INFINITY ? 0.f : exp2f(ms - m);
+      all_m[row * n_splits + s] = f;
+      l += f * all_l[row * n_splits + s];
+    }
+    row_l[row] = l;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < group * head_dim; idx += blockDim.x) {
+    const int row = idx / head_dim, d = idx - row * head_dim;
+    const int head = kv_head * group + row;
+    const float* po = part_o + ((size_t)tok * n_heads + head) * n_splits * head_dim + d;
+    float o = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < n_splits; ++s) {
+      const float f = all_m[row * n_splits + s];  // 0 for a split without visible keys: its partials are never read
+      const float v = f != 0.f ? __ldcg(po + (size_t)s * head_dim) : 0.f;
+      o += f * v;
+    }
+    out[((size_t)tok * n_heads + head) * head_dim + d] = __float2bfloat16_rn(o / row_l[row]);
   }
 }
 
@@ -199,7 +256,7 @@ template <int HD_MAX>
 int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_bfloat16* q,
                   const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, const int* tok_slot, const int* tok_pos,
                   const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                  float scale, int window, int chunk, int n_splits, cudaStream_t stream) {
+                  float scale, int window, int chunk, int n_splits, int* counters, cudaStream_t stream) {
   const int tile_bytes = XRT_BLOCK_TOKENS * (head_dim * 2 + 16);
   const int merge_bytes = DEC_WARPS * 16 * (2 + head_dim + 8) * (int)sizeof(float);
   const int smem = max(4 * tile_bytes, merge_bytes);
@@ -213,8 +270,50 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_
   dim3 grid(n_splits, n_kv_heads, n_tokens);
   launch_kernel(kernel, grid, dim3(DEC_WARPS * 32), (size_t)smem, stream, out, part_o, part_ml, q, k_pool, v_pool,
                 tok_slot, tok_pos, block_table, max_blocks, n_heads, n_kv_heads, head_dim,
-                scale * 1.4426950408889634f, window, chunk, n_splits);
+                scale * 1.4426950408889634f, window, chunk, n_splits, counters);
   return launch_status();
+}
+
+}  // namespace xrt
+
+namespace xrt {
+
+// counters == nullptr: partials, then the combine kernel.  Otherwise the last block of a
+// (token, kv head) combines, and `counters` (int32 [n_tokens * n_kv_heads], zero before the call)
+// is left zero.
+static int attention_decode_impl(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
+                                 const void* v_pool, const int* tok_slot, const int* tok_pos, const int* block_table,
+                                 int max_blocks, int n_tokens, int n_heads, int n_kv_heads, int head_dim, float scale,
+                                 int window, int chunk, int n_splits, int* counters, cudaStream_t stream) {
+  if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || chunk <= 0 || n_splits <= 0)
+    return XRT_ERR_ARGUMENT;
+  if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256 || n_heads / n_kv_heads > 16 ||
+      chunk % XRT_BLOCK_TOKENS != 0 || n_tokens > 65535 || n_kv_heads > 65535 || n_splits > 512)
+    return XRT_ERR_UNSUPPORTED;
+  if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  auto* o = (__nv_bfloat16*)out;
+  auto* qp = (const __nv_bfloat16*)q;
+  auto* kp = (const __nv_bfloat16*)k_pool;
+  auto* vp = (const __nv_bfloat16*)v_pool;
+  int status;
+#define XRT_DECODE(HD) status = launch_decode<HD>(o, part_o, part_ml, qp, kp, vp, tok_slot, tok_pos, block_table,      \
+                                                  max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, \
+                                                  chunk, n_splits, counters, stream)
+  if (head_dim <= 32) XRT_DECODE(32);
+  else if (head_dim <= 64) XRT_DECODE(64);
+  else if (head_dim <= 128) XRT_DECODE(128);
+  else XRT_DECODE(256);
+#undef XRT_DECODE
+  if (status != XRT_OK) return status;
+  if (n_splits > 1 && counters == nullptr) {
+    const int warps = n_tokens * n_heads;
+    launch_kernel(attention_combine_kernel, dim3((warps * 32 + 255) / 256), dim3(256), 0, stream, o,
+                  (const float*)part_o, (const float*)part_ml, tok_slot, tok_pos, n_tokens, n_heads, head_dim, window,
+                  chunk, n_splits);
+    return launch_status();
+  }
+  return XRT_OK;
 }
 
 }  // namespace xrt
@@ -224,40 +323,29 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_
 // cover the longest sequence the launch may meet.  part_o: float32 [n_tokens * n_heads * n_splits *
 // head_dim] and part_ml: float32 [n_tokens * n_heads * n_splits * 2] are scratch, needed when
 // n_splits > 1.  The group n_heads / n_kv_heads is at most 16; n_tokens at most 65535.
+// This entry point merges the splits with a second kernel.
 XRT_EXPORT int xrt_attention_decode(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
                                     const void* v_pool, const int* tok_slot, const int* tok_pos,
                                     const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
                                     int head_dim, float scale, int window, int chunk, int n_splits,
                                     cudaStream_t stream) {
-  if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || chunk <= 0 || n_splits <= 0)
-    return XRT_ERR_ARGUMENT;
-  if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256 || n_heads / n_kv_heads > 16 ||
-      chunk % XRT_BLOCK_TOKENS != 0 || n_tokens > 65535 || n_kv_heads > 65535)
-    return XRT_ERR_UNSUPPORTED;
-  if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return XRT_ERR_ARGUMENT;
-  if (n_tokens == 0) return XRT_OK;
-  auto* o = (__nv_bfloat16*)out;
-  auto* qp = (const __nv_bfloat16*)q;
-  auto* kp = (const __nv_bfloat16*)k_pool;
-  auto* vp = (const __nv_bfloat16*)v_pool;
-  int status;
-#define XRT_DECODE(HD) status = xrt::launch_decode<HD>(o, part_o, part_ml, qp, kp, vp, tok_slot, tok_pos, block_table, \
-                                                       max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale,   \
-                                                       window, chunk, n_splits, stream)
-  if (head_dim <= 32) XRT_DECODE(32);
-  else if (head_dim <= 64) XRT_DECODE(64);
-  else if (head_dim <= 128) XRT_DECODE(128);
-  else XRT_DECODE(256);
-#undef XRT_DECODE
-  if (status != XRT_OK) return status;
-  if (n_splits > 1) {
-    const int warps = n_tokens * n_heads;
-    xrt::launch_kernel(xrt::attention_combine_kernel, dim3((warps * 32 + 255) / 256), dim3(256), 0, stream, o,
-                       (const float*)part_o, (const float*)part_ml, tok_slot, tok_pos, n_tokens, n_heads, head_dim,
-                       window, chunk, n_splits);
-    return xrt::launch_status();
-  }
-  return XRT_OK;
+  return xrt::attention_decode_impl(out, part_o, part_ml, q, k_pool, v_pool, tok_slot, tok_pos, block_table, max_blocks,
+                                    n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits, nullptr,
+                                    stream);
+}
+
+// The same, with the merge done by the block that brings a (token, kv head)'s last split: one
+// launch instead of two.  counters: int32 [at least n_tokens * n_kv_heads], zero before the first
+// call (the kernel leaves them zero).
+XRT_EXPORT int xrt_attention_decode_fused(void* out, float* part_o, float* part_ml, int* counters, const void* q,
+                                          const void* k_pool, const void* v_pool, const int* tok_slot,
+                                          const int* tok_pos, const int* block_table, int max_blocks, int n_tokens,
+                                          int n_heads, int n_kv_heads, int head_dim, float scale, int window, int chunk,
+                                          int n_splits, cudaStream_t stream) {
+  if (counters == nullptr) return XRT_ERR_ARGUMENT;
+  return xrt::attention_decode_impl(out, part_o, part_ml, q, k_pool, v_pool, tok_slot, tok_pos, block_table, max_blocks,
+                                    n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits, counters,
+                                    stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -103,7 +103,7 @@ template <int D_TILES>
 __device__ __forceinline__ void attend_16_keys(SoftmaxState<D_TILES>& st, const uint32_t (*qf)[4],
                                                const unsigned char* ks_tile, const unsigned char* vs_tile,
                                                int key_row, int key_abs, const int (&key_lo)[2], const int (&key_hi)[2],
-                                               int head_dim, float scale_log2) {
+                                               bool masked, int head_dim, float scale_log2) {
   const int lane = threadIdx.x & 31, t = lane & 3;
   const int row_bytes = tile_row_bytes(head_dim);
   const int j = lane >> 3, r = lane & 7;
@@ -125,9 +125,12 @@ __device__ __forceinline__ void attend_16_keys(SoftmaxState<D_TILES>& st, const 
   for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int key = key_abs + nt * 8 + 2 * t + (e & 1);
       const int row = e >> 1;
-      const bool live = key >= key_lo[row] && key < key_hi[row];
+      bool live = true;
+      if (masked) {  // uniform over the warp: only tiles at an edge of a row's key range pay for the comparisons
+        const int key = key_abs + nt * 8 + 2 * t + (e & 1);
+        live = key >= key_lo[row] && key < key_hi[row];
+      }
       s[nt][e] = live ? s[nt][e] * scale_log2 : -INFINITY;
       tile_max[row] = fmaxf(tile_max[row], s[nt][e]);
     }
@@ -142,6 +145,8 @@ __device__ __forceinline__ void attend_16_keys(SoftmaxState<D_TILES>& st, const 
     st.m[row] = m_new;
     st.l[row] *= corr[row];
   }
+  // once a row's maximum has settled the accumulators need no rescaling: skip it for the whole warp
+  const bool rescale = __any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f);
   uint32_t pf[4];
   {
     float p[2][4];
@@ -165,10 +170,12 @@ __device__ __forceinline__ void attend_16_keys(SoftmaxState<D_TILES>& st, const 
     if (dt * 8 < head_dim) {
       uint32_t vf[4];
       ldmatrix_x4_trans(vf, v_base + dt * 16);
+      if (rescale) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        st.o[dt][e] *= corr[e >> 1];
-        st.o[dt + 1][e] *= corr[e >> 1];
+        for (int e = 0; e < 4; ++e) {
+          st.o[dt][e] *= corr[e >> 1];
+          st.o[dt + 1][e] *= corr[e >> 1];
+        }
       }
       mma_16816(st.o[dt], pf, vf[0], vf[1]);
       mma_16816(st.o[dt + 1], pf, vf[2], vf[3]);
@@ -240,10 +247,12 @@ __device__ __forceinline__ void attend_keys(SoftmaxState<D_TILES>& st, const uin
       s[nt][e] = st.m[row] == -INFINITY ? 0.f : exp2f(s[nt][e] - st.m[row]);
       st.l[row] += s[nt][e];
     }
+  if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {  // not once the maxima have settled
 #pragma unroll
-  for (int dt = 0; dt < D_TILES; ++dt)
+    for (int dt = 0; dt < D_TILES; ++dt)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) st.o[dt][e] *= corr[e >> 1];
+      for (int e = 0; e < 4; ++e) st.o[dt][e] *= corr[e >> 1];
+  }
   const uint32_t v_base = smem_addr(vs_tile + (key_row + (j & 1) * 8 + r) * row_bytes + (j >> 1) * 16);
 #pragma unroll
   for (int kp = 0; kp < KEY_TILES / 2; ++kp) {

@@ -35,6 +35,7 @@ _SIGNATURES = {
     "xrt_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_gemm_decode_tcgen05": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "xrt_attention_decode_fused": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
@@ -325,8 +326,10 @@ def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
 
 
 def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int,
-                     head_dim: int, scale: float, window: int, chunk: int, n_splits: int) -> None:
-    """bfloat16 attention of one token a sequence over its cache blocks, split along the keys."""
+                     head_dim: int, scale: float, window: int, chunk: int, n_splits: int, fused: bool = True) -> None:
+    """bfloat16 attention of one token a sequence over its cache blocks, split along the keys.
+    ``fused``: the splits are merged by the last block of each (token, kv head) instead of by a
+    second kernel (needs the device's tile counters; falls back when there are too many)."""
     n = q.shape[0]
     if q.shape != (n, n_heads * head_dim) or out.shape != q.shape or tok_slot.numel() != n or tok_pos.numel() != n:
         raise KernelError("attention_decode: shapes do not fit")
@@ -336,6 +339,15 @@ def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_h
     if n_splits > 1:
         part_o = torch.empty(n * n_heads * n_splits * head_dim, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(n * n_heads * n_splits * 2, dtype=torch.float32, device=q.device)
+    if fused and n_splits > 1 and n * n_kv_heads <= _COUNTER_SLOTS:
+        _, counters, _ = device_state(q.device)
+        _check(library().xrt_attention_decode_fused(
+            _ptr(out, "out", torch.bfloat16), _ptr(part_o, "part_o"), _ptr(part_ml, "part_ml"), counters.data_ptr(),
+            _ptr(q, "q", torch.bfloat16), _ptr(k_pool, "k_pool", torch.bfloat16), _ptr(v_pool, "v_pool", torch.bfloat16),
+            _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
+            _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
+            float(scale), int(window), int(chunk), int(n_splits), _stream()), "attention_decode")
+        return
     _check(library().xrt_attention_decode(
         _ptr(out, "out", torch.bfloat16), _ptr(part_o, "part_o"), _ptr(part_ml, "part_ml"),
         _ptr(q, "q", torch.bfloat16), _ptr(k_pool, "k_pool", torch.bfloat16), _ptr(v_pool, "v_pool", torch.bfloat16),

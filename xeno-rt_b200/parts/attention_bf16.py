@@ -7,6 +7,7 @@ from .context import context_bucket
 
 SM_COUNT = 148
 DECODE_BLOCKS_PER_SM = 3   # 70 KB of shared memory a block at head size 128
+FUSED_COMBINE_MAX = 32     # (tokens x kv heads) up to which the splits are merged inside the attention kernel
 DECODE_WAVES = 2           # blocks wanted = what the GPU holds at once, times this (measured: 1 leaves a long tail
 #                            at 64 sequences, 4 costs more in partials at 8)
 
@@ -26,8 +27,11 @@ def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window) -> boo
         return False
     if ctx.all_single and ctx.n_tokens <= 65535:
         chunk, n_splits = decode_split(ctx.n_tokens, n_kv_heads, context_bucket(ctx.max_context))
+        # few sequences: the last block of a (token, kv head) merges its splits (one launch less);
+        # many: a second kernel merges them with more threads (measured faster from 8 sequences on)
+        fused = ctx.n_tokens * n_kv_heads <= FUSED_COMBINE_MAX
         ops.attention_decode(out, q, store.k, store.v, ctx.tok_slot, ctx.tok_pos, store.block_table, n_heads,
-                             n_kv_heads, head_dim, scale, window, chunk, n_splits)
+                             n_kv_heads, head_dim, scale, window, chunk, n_splits, fused=fused)
         return True
     if ctx.n_seqs <= 65535 and n_heads <= 65535:
         ops.attention_prefill(out, q, store.k, store.v, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
