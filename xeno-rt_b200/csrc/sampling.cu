@@ -21,6 +21,7 @@
 namespace xrt {
 
 constexpr int SAMPLE_THREADS = 1024;
+constexpr int HIST_COPIES = SAMPLE_THREADS / 64;  // private histograms of the radix select
 
 __device__ __forceinline__ uint64_t sm64(uint64_t x) {
   x += 0x9E3779B97F4A7C15ull;
@@ -88,6 +89,7 @@ __device__ int ordered_pick(F weight, int n, uint64_t target, uint64_t* scan_scr
   const int seg = (n + blockDim.x - 1) / blockDim.x;
   const int lo = min(n, (int)threadIdx.x * seg), hi = min(n, lo + seg);
   uint64_t local = 0;
+#pragma unroll 4
   for (int i = lo; i < hi; ++i) local += weight(i);
   if (threadIdx.x == 0) *result = -1;
   uint64_t total;
@@ -109,21 +111,43 @@ __device__ int ordered_pick(F weight, int n, uint64_t target, uint64_t* scan_scr
 // Returns the key; *inside gets want minus the weight of {key > K} (what the keys equal to K still
 // have to supply, >= 1 if want >= 1) and *at_key the weight of {key == K}.  If the whole weight is
 // below `want`, returns 0 with *inside = 0.
-template <typename F, typename K>
-__device__ uint32_t radix_select(F weight, K key_of, int n, uint64_t want, unsigned long long* hist,
+template <typename A, typename F>
+__device__ uint32_t radix_select(A adjusted, F weight, int n, uint64_t want, unsigned long long* hist,
                                  uint64_t* inside, uint64_t* at_key, uint32_t* shared_prefix) {
   uint32_t prefix = 0, mask = 0;
   uint64_t remaining = want;
   for (int pass = 3; pass >= 0; --pass) {
     const int shift = pass * 8;
-    for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0ull;
+    // HIST_COPIES private histograms (a pair of warps shares one): logits crowd into a few bins
+    // of the leading byte, and a thousand threads adding to the same shared-memory word serialise
+    unsigned long long* mine = hist + 258 + (threadIdx.x >> 6) * 256;
+    for (int b = threadIdx.x; b < HIST_COPIES * 256; b += blockDim.x) hist[258 + b] = 0ull;
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      const uint32_t k = key_of(i);
+    auto count = [&](int i, float a) {
+      const uint32_t k = order_key(a);
       if ((k & mask) == prefix) {
-        const uint64_t w = weight(i);
-        if (w) atomicAdd(&hist[(k >> shift) & 255u], (unsigned long long)w);
+        const uint64_t w = weight(i, a);
+        if (w) atomicAdd(&mine[(k >> shift) & 255u], (unsigned long long)w);
       }
+    };
+    {
+      // four loads in flight a thread; the histogram updates follow them
+      int i = threadIdx.x;
+      for (; i + 3 * (int)blockDim.x < n; i += 4 * blockDim.x) {
+        float a[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) a[u] = adjusted(i + u * blockDim.x);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) count(i + u * blockDim.x, a[u]);
+      }
+      for (; i < n; i += blockDim.x) count(i, adjusted(i));
+    }
+    __syncthreads();
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) {
+      unsigned long long sum = 0ull;
+#pragma unroll
+      for (int c = 0; c < HIST_COPIES; ++c) sum += hist[258 + c * 256 + b];
+      hist[b] = sum;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -159,7 +183,7 @@ sample_kernel(int* __restrict__ out_ids, const float* __restrict__ logits, int v
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const float* __restrict__ penalty, const uint32_t* __restrict__ seen, int seen_words,
               const unsigned long long* __restrict__ rng_key, unsigned int* __restrict__ rng_counter) {
-  __shared__ unsigned long long hist[258];
+  __shared__ unsigned long long hist[258 + HIST_COPIES * 256];  // merged bins, two result words, private copies
   __shared__ uint64_t scan_scratch[33];
   __shared__ float red_val[32];
   __shared__ int red_idx[32];
@@ -180,9 +204,22 @@ sample_kernel(int* __restrict__ out_ids, const float* __restrict__ logits, int v
 
   // maximum and its first index
   float best = -INFINITY; int best_i = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float a = view.adjusted(i);
-    if (a > best) { best = a; best_i = i; }
+  {
+    // eight loads in flight a thread: a row is read once and the pass is bound by load latency
+    constexpr int UNROLL = 8;
+    int i = threadIdx.x;
+    for (; i + (UNROLL - 1) * (int)blockDim.x < vocab; i += UNROLL * blockDim.x) {
+      float a[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) a[u] = view.adjusted(i + u * blockDim.x);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+        if (a[u] > best) { best = a[u]; best_i = i + u * blockDim.x; }  // indices rise: the first maximum is kept
+    }
+    for (; i < vocab; i += blockDim.x) {
+      const float a = view.adjusted(i);
+      if (a > best) { best = a; best_i = i; }
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -207,54 +244,68 @@ sample_kernel(int* __restrict__ out_ids, const float* __restrict__ logits, int v
   if (threadIdx.x == 0) { counter = rng_counter[slot]; rng_counter[slot] = counter + 1; }
   if (temp <= 1e-5f) { if (threadIdx.x == 0) out_ids[row] = row_arg; return; }
 
+  auto adjusted = [&](int i) { return view.adjusted(i); };
   auto key_of = [&](int i) { return order_key(view.adjusted(i)); };
+  // this thread's share of the sum of weight(i, adjusted(i)) over the row, four loads in flight
+  auto strided_sum = [&](auto weight) {
+    uint64_t local = 0;
+    int i = threadIdx.x;
+    for (; i + 3 * (int)blockDim.x < vocab; i += 4 * blockDim.x) {
+      float a[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) a[u] = view.adjusted(i + u * blockDim.x);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) local += weight(i + u * blockDim.x, a[u]);
+    }
+    for (; i < vocab; i += blockDim.x) local += weight(i, view.adjusted(i));
+    return local;
+  };
 
   // top-k: threshold key and the last index kept among equal keys
   uint32_t k_key = 0u; int k_last = vocab;  // kept: key > k_key, or key == k_key and i <= k_last
   const int k = top_k[row];
   if (k > 0 && k < vocab) {
     uint64_t inside, at_key;
-    auto one = [&](int) { return (uint64_t)1; };
-    k_key = radix_select(one, key_of, vocab, (uint64_t)k, hist, &inside, &at_key, shared_prefix);
+    auto one = [&](int, float) { return (uint64_t)1; };
+    k_key = radix_select(adjusted, one, vocab, (uint64_t)k, hist, &inside, &at_key, shared_prefix);
     if (at_key > inside) {
       auto tie = [&](int i) { return (uint64_t)(key_of(i) == k_key); };
       k_last = ordered_pick(tie, vocab, inside - 1, scan_scratch, &pick_result);
     }
   }
   const float inv_temp = 1.0f / temp;
-  auto mass = [&](int i) -> uint64_t {
-    const float a = view.adjusted(i);
+  auto mass_of = [&](int i, float a) -> uint64_t {
     const uint32_t key = order_key(a);
     if (key < k_key || (key == k_key && i > k_last)) return 0ull;
     return (uint64_t)(expf((a - row_max) * inv_temp) * 4294967296.0f);
   };
+  auto mass = [&](int i) -> uint64_t { return mass_of(i, view.adjusted(i)); };
 
   // top-p: threshold by probability mass
   uint32_t p_key = 0u; int p_last = vocab;
   const float p = top_p[row];
   if (p < 1.0f) {
-    uint64_t local = 0;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) local += mass(i);
+    const uint64_t local = strided_sum(mass_of);
     uint64_t total;
     block_exclusive_scan(local, scan_scratch, &total);
     uint64_t want = (uint64_t)ceil((double)p * (double)total);
     if (want < 1) want = 1;
     uint64_t inside, at_key;
-    p_key = radix_select(mass, key_of, vocab, want, hist, &inside, &at_key, shared_prefix);
+    p_key = radix_select(adjusted, mass_of, vocab, want, hist, &inside, &at_key, shared_prefix);
     if (at_key > inside) {
       // equal keys have equal mass: how many of them the remaining mass needs
       auto tie_mass = [&](int i) { return key_of(i) == p_key ? mass(i) : 0ull; };
       p_last = ordered_pick(tie_mass, vocab, inside - 1, scan_scratch, &pick_result);
     }
   }
-  auto kept_mass = [&](int i) -> uint64_t {
-    const uint32_t key = order_key(view.adjusted(i));
+  auto kept_mass_of = [&](int i, float a) -> uint64_t {
+    const uint32_t key = order_key(a);
     if (key < p_key || (key == p_key && i > p_last)) return 0ull;
-    return mass(i);
+    return mass_of(i, a);
   };
+  auto kept_mass = [&](int i) -> uint64_t { return kept_mass_of(i, view.adjusted(i)); };
 
-  uint64_t local = 0;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) local += kept_mass(i);
+  const uint64_t local = strided_sum(kept_mass_of);
   uint64_t total;
   block_exclusive_scan(local, scan_scratch, &total);
   __shared__ unsigned int shared_u;
