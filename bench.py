@@ -31,6 +31,11 @@ LLAMA3_8B = {
     "num_key_value_heads": 8, "head_dim": 128, "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
     "tie_word_embeddings": False,
 }
+QWEN3_8B = dict(LLAMA3_8B, architectures=["Qwen3ForCausalLM"], vocab_size=151936, max_position_embeddings=40960,
+                intermediate_size=12288, num_hidden_layers=36, rope_theta=1000000.0, rms_norm_eps=1e-6)
+QWEN3_32B = dict(QWEN3_8B, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64)
+SHAPES = {"llama3-8b": ("Llama-3-8B shape", LLAMA3_8B), "qwen3-8b": ("Qwen3-8B shape", QWEN3_8B),
+          "qwen3-32b": ("Qwen3-32B shape", QWEN3_32B)}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 PREFILL_TOKENS = 2048
 
@@ -232,7 +237,8 @@ def run_ours(args) -> int:
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device: bench.py needs a B200"}))
         return 1
-    cfg = dict(LLAMA3_8B)
+    shape_name, shape_cfg = SHAPES[args.shape]
+    cfg = dict(shape_cfg)
     full_layers = cfg["num_hidden_layers"]
     cfg["num_hidden_layers"] = args.layers or full_layers
     n_layers = cfg["num_hidden_layers"]
@@ -265,12 +271,12 @@ def run_ours(args) -> int:
     e2e = time_e2e(model, args.batch, args.context, args.steps)
 
     line = {
-        "metric": "decode tok/s @ batch 8 (Llama-3-8B bf16, context 4096)", "value": round(main["tokens_per_s"], 1),
+        "metric": f"decode tok/s @ batch {args.batch} ({shape_name.replace(' shape', '')} bf16, context {args.context})", "value": round(main["tokens_per_s"], 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
         "impl": "ours",
-        "config": {"model": "Llama-3-8B shape", "layers": n_layers, "layers_of_model": full_layers,
+        "config": {"model": shape_name, "layers": n_layers, "layers_of_model": full_layers,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
@@ -299,6 +305,8 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=4096)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")
+    parser.add_argument("--shape", default="llama3-8b", choices=sorted(SHAPES),
+                        help="the model shape to time (the default is the headline configuration)")
     parser.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                         help="a short run of one part, for profiling; prints its own small JSON line")
     args = parser.parse_args()

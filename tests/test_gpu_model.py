@@ -230,3 +230,36 @@ def test_graph_replay_equals_eager_steps(setups, dtype):
             assert np.array_equal(x, y)
             assert scaled_error(y, r) < TOL[dtype]
     assert graphed._graphs and not eager._graphs
+
+
+def test_full_width_layers_agree_between_the_32_bit_and_the_bfloat16_path():
+    """Two layers at the widths of the 8B models (hidden 4096, 32 heads over 8 kv heads of 128, feed-forward
+    14336): the products, attention and fused kernels run at the sizes they are tuned for (the tiled tcgen05 product
+    for the prompts, both decode products for 3 and 20 rows).  The 32-bit path, which the other tests tie to the
+    plain implementation, is the oracle here; whole prompts and one-by-one decoding must agree too."""
+    from xeno_rt_b200.engine import Engine, Model, StepEntry
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "vocab_size": 5000, "max_position_embeddings": 1024,
+           "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 2, "num_attention_heads": 32,
+           "num_key_value_heads": 8, "head_dim": 128, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+           "tie_word_embeddings": False}
+    lengths = [300, 70, 129] + [40] * 17
+    prompts = random_prompts(5000, lengths, seed=11)
+    results = {}
+    for dtype in ("float32", "bfloat16"):
+        model = Model.random(cfg, seed=3, dtype=dtype)
+        engine = Engine(model, 64 * 40)
+        results[dtype] = {}
+        for n_seq in (3, 20):
+            got = _batch(engine, prompts[:n_seq], decode=4)
+            results[dtype][n_seq] = got
+            engine.cache.check()
+        whole = _whole(engine, prompts[0])
+        assert scaled_error(results[dtype][3][0], whole.astype(np.float64)) < (1e-5 if dtype == "float32" else 2e-2)
+        del engine, model
+        torch.cuda.empty_cache()
+    for n_seq in (3, 20):
+        for a, b in zip(results["bfloat16"][n_seq], results["float32"][n_seq]):
+            assert scaled_error(a, b.astype(np.float64)) < TOL["bfloat16"]
+    # the 32-bit result does not depend on the batch at all
+    for a, b in zip(results["float32"][3], results["float32"][20][:3]):
+        assert np.array_equal(a, b)
