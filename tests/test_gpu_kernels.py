@@ -482,3 +482,42 @@ def test_gemm_decode_tcgen05_swiglu(m, inner, k):
     ops().gemm_decode_tcgen05(out, x, w, "swiglu", up_rows=inner)
     want = pm.swiglu(f64(x) @ f64(w[:inner]).T, f64(x) @ f64(w[inner:]).T)
     assert rel(out, want) < 5e-3
+
+
+@pytest.mark.parametrize("nh,nkv", [(8, 2), (5, 1), (4, 4)])
+def test_attention_prefill_tcgen05_kernel(nh, nkv):
+    """The tcgen05 attention (head size 128) on the case of the mma.sync kernel's test: a whole prompt of 150 tokens,
+    one of a single token, one that continues at position 100 with 70 more (across a block edge), a skipped one;
+    plus a prompt of 300 tokens (three query tiles, five key blocks)."""
+    hd = 128
+    torch.manual_seed(nh * 7 + nkv)
+    totals = [150, 1, 170, 64, 300]
+    starts = [0, 0, 100, 0, 0]
+    new = [150, 1, 70, 5, 300]
+    slots = [1, 2, 3, -1, 5]
+    k_pool, v_pool, table = _cache_for(totals, nkv, hd, torch.bfloat16, shuffle_seed=nh)
+    ks = [torch.randn(n, nkv, hd, device=DEV) for n in totals]
+    vs = [torch.randn(n, nkv, hd, device=DEV) for n in totals]
+    for s in range(5):
+        _fill_cache(k_pool, v_pool, table, s + 1, ks[s], vs[s])
+    T = sum(new)
+    q = torch.randn(T, nh * hd, device=DEV).to(torch.bfloat16)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(new)]), dtype=torch.int32, device=DEV)
+    seq_slot = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    seq_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    out = torch.full_like(q, 5.0)
+    ops().attention_prefill_tcgen05(out, q, k_pool, v_pool, cu, seq_slot, seq_start, table, max(new), nh, nkv, hd,
+                                    1 / math.sqrt(hd))
+    from xeno_rt_b200.csrc import ops as o
+    o.check_error_flag(DEV)
+    bf = lambda x: f64(x.to(torch.bfloat16)).reshape(x.shape[0], -1)
+    at = 0
+    for s in range(5):
+        if slots[s] >= 0:
+            q_full = np.zeros((totals[s], nh * hd))
+            q_full[starts[s]:] = f64(q[at:at + new[s]])
+            want = pm.causal_gqa_attention(q_full, bf(ks[s]), bf(vs[s]), nh, nkv, hd)[starts[s]:]
+            assert rel(out[at:at + new[s]], want) < 1.5e-2, s
+        else:
+            assert bool((out[at:at + new[s]] == 5.0).all())  # the skipped sequence's rows are untouched
+        at += new[s]

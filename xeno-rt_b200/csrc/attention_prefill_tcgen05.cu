@@ -1,0 +1,401 @@
+// Causal grouped-query attention for prompts on the fifth-generation tensor cores (head size 128).
+// (The reference's prefill form: crates/xrt-models/src/llama.rs:728-770: for token t the keys
+// 0 .. start + t, read from the cache so that earlier context is included.)
+//
+// A block owns 128 consecutive new tokens of one sequence for one query head and walks the
+// sequence's cache blocks (64 keys each).  Six warps:
+//   warp 0    TMA: the Q tile once, then for each block its K and V tiles ([64 keys x 128], two
+//             64-column halves each, 128-byte swizzle) into a three-stage ring.
+//   warp 1    owns TMEM and issues the MMAs: S = Q K^T (128 x 64, eight tcgen05.mma over the head
+//             size) into one of two S buffers, and O_tile = P V (128 x 128, four tcgen05.mma over the
+//             64 keys) into one of two O buffers.  K is a K-major operand as stored; V ([key][dim])
+//             is an MN-major operand as stored: no transposition anywhere.  QK^T of the next block
+//             is issued before PV of this one, so the tensor core works while the softmax runs.
+//   warps 2-5 softmax and output, ONE THREAD PER QUERY ROW (TMEM lane): it reads its row of S
+//             (tcgen05.ld), masks, keeps the running maximum and sum in 32-bit without any
+//             shuffle, writes P as bfloat16 into shared memory in the MMA's operand layout, and
+//             folds each finished O_tile into its 128 output accumulators (registers) with the
+//             rescaling factor of that block.
+// Every mbarrier wait is bounded; a wait that runs out raises the error flag and an abort flag, all
+// roles leave their loops, TMEM is freed and the block returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace xrt {
+
+constexpr int FA_ROWS = 128, FA_KEYS = 64, FA_HD = 128, FA_STAGES = 3;
+constexpr int FA_Q_BYTES = FA_ROWS * FA_HD * 2;        // 32 KB (two halves of 16 KB)
+constexpr int FA_KV_HALF = FA_KEYS * 64 * 2;           // 8 KB: 64 keys x 64 dims
+constexpr int FA_STAGE_BYTES = 4 * FA_KV_HALF;         // K halves, then V halves
+constexpr int FA_P_BYTES = FA_ROWS * FA_KEYS * 2;      // 16 KB
+constexpr int FA_THREADS = 192;
+constexpr int FA_TMEM_COLS = 512;
+constexpr int FA_SMEM = FA_Q_BYTES + FA_STAGES * FA_STAGE_BYTES + 2 * FA_P_BYTES + 512 + 1024;
+constexpr long long FA_SPIN_LIMIT = 1ll << 24;
+
+__device__ __forceinline__ uint32_t fa_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void fa_mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void fa_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void fa_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool fa_mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (long long spin = 0; spin < FA_SPIN_LIMIT; ++spin) {
+    uint32_t done;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if ((spin & 1023) == 1023 && *abort_flag) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ void fa_tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+// K-major operand: rows of 128 bytes (64 bfloat16 of the contraction), 128-byte swizzle, groups of
+// eight rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t fa_desc_k_major(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// MN-major operand (V as stored, [key][dim]): 128-byte rows hold 64 consecutive dims of one key
+// (the contraction index advances from row to row); groups of eight keys are 1024 bytes apart
+// (stride byte offset), the next 64 dims are `chunk_bytes` further (leading byte offset).
+__device__ __forceinline__ uint64_t fa_desc_mn_major(uint32_t addr, uint32_t chunk_bytes) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(chunk_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f16, bfloat16 A and B, float32 D; A K-major; B K-major or MN-major (bit 16).
+__device__ __forceinline__ constexpr uint32_t fa_instr_desc(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void fa_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+               " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+               ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void fa_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void fa_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fa_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fa_ld32(uint32_t (&r)[32], uint32_t addr) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(addr));
+}
+__device__ __forceinline__ void fa_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                 const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                                 const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
+                                 const int* __restrict__ seq_start, const int* __restrict__ block_table, int max_blocks,
+                                 int n_heads, int n_kv_heads, float scale_log2, int* __restrict__ error_flag) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* q_tile = smem;
+  unsigned char* kv_ring = smem + FA_Q_BYTES;
+  unsigned char* p_tiles = kv_ring + FA_STAGES * FA_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_tiles + 2 * FA_P_BYTES);
+  uint64_t* q_full = bars;                 // [1]
+  uint64_t* kv_full = bars + 1;            // [FA_STAGES]
+  uint64_t* kv_empty = kv_full + FA_STAGES;
+  uint64_t* s_full = kv_empty + FA_STAGES; // [2] ...
+  uint64_t* s_empty = s_full + 2;
+  uint64_t* p_full = s_empty + 2;
+  uint64_t* p_empty = p_full + 2;
+  uint64_t* o_full = p_empty + 2;
+  uint64_t* o_empty = o_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  // later query tiles walk more keys: they are scheduled first
+  const int q_index = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
+  const int slot = seq_slot[seq];
+  const int tok0 = cu_seqlens[seq];
+  const int n_new = cu_seqlens[seq + 1] - tok0;
+  const int row0 = q_index * FA_ROWS;
+  if (slot < 0 || row0 >= n_new) return;  // the whole block leaves before any barrier or allocation
+  const int start = seq_start[seq];
+  const int kv_head = head / (n_heads / n_kv_heads);
+  const int last_row = min(row0 + FA_ROWS, n_new) - 1;
+  const int n_tiles = (start + last_row + 1 + FA_KEYS - 1) / FA_KEYS;  // keys 0 .. position of the last row
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    fa_mbar_init(fa_smem(q_full), 1);
+    for (int s = 0; s < FA_STAGES; ++s) { fa_mbar_init(fa_smem(&kv_full[s]), 1); fa_mbar_init(fa_smem(&kv_empty[s]), 1); }
+    for (int b = 0; b < 2; ++b) {
+      fa_mbar_init(fa_smem(&s_full[b]), 1);   fa_mbar_init(fa_smem(&s_empty[b]), 128);
+      fa_mbar_init(fa_smem(&p_full[b]), 128); fa_mbar_init(fa_smem(&p_empty[b]), 1);
+      fa_mbar_init(fa_smem(&o_full[b]), 1);   fa_mbar_init(fa_smem(&o_empty[b]), 128);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(fa_smem(tmem_slot)), "r"(FA_TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  fa_fence_before();
+  __syncthreads();
+  fa_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base;             // two S buffers of 64 columns
+  const uint32_t tmem_o = tmem_base + 2 * FA_KEYS;  // two O buffers of 128 columns
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+      fa_mbar_expect_tx(fa_smem(q_full), FA_Q_BYTES);
+      fa_tma_load_2d(fa_smem(q_tile), &map_q, head * FA_HD, tok0 + row0, fa_smem(q_full));
+      fa_tma_load_2d(fa_smem(q_tile + FA_Q_BYTES / 2), &map_q, head * FA_HD + 64, tok0 + row0, fa_smem(q_full));
+      const int* blocks = block_table + (size_t)slot * max_blocks;
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % FA_STAGES;
+        ok = fa_mbar_wait(fa_smem(&kv_empty[s]), ((j / FA_STAGES) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        const int pool_row = (blocks[j] * n_kv_heads + kv_head) * FA_KEYS;
+        const uint32_t bar = fa_smem(&kv_full[s]);
+        unsigned char* stage = kv_ring + s * FA_STAGE_BYTES;
+        fa_mbar_expect_tx(bar, FA_STAGE_BYTES);
+        fa_tma_load_2d(fa_smem(stage), &map_k, 0, pool_row, bar);
+        fa_tma_load_2d(fa_smem(stage + FA_KV_HALF), &map_k, 64, pool_row, bar);
+        fa_tma_load_2d(fa_smem(stage + 2 * FA_KV_HALF), &map_v, 0, pool_row, bar);
+        fa_tma_load_2d(fa_smem(stage + 3 * FA_KV_HALF), &map_v, 64, pool_row, bar);
+      }
+      if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 5); }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issue
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = fa_instr_desc(FA_ROWS, FA_KEYS, false);
+      constexpr uint32_t idesc_pv = fa_instr_desc(FA_ROWS, FA_HD, true);
+      bool ok = fa_mbar_wait(fa_smem(q_full), 0, abort_flag);
+      auto issue_qk = [&](int j) {
+        const int s = j % FA_STAGES, b = j & 1;
+        if (!fa_mbar_wait(fa_smem(&kv_full[s]), (j / FA_STAGES) & 1, abort_flag)) return false;
+        if (!fa_mbar_wait(fa_smem(&s_empty[b]), ((j >> 1) & 1) ^ 1, abort_flag)) return false;
+        fa_fence_after();
+        unsigned char* stage = kv_ring + s * FA_STAGE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < FA_HD / 16; ++ks) {  // 16 dims a step; 4 steps a 64-dim half
+          const uint64_t a = fa_desc_k_major(fa_smem(q_tile + (ks / 4) * (FA_Q_BYTES / 2))) + 2 * (ks % 4);
+          const uint64_t bd = fa_desc_k_major(fa_smem(stage + (ks / 4) * FA_KV_HALF)) + 2 * (ks % 4);
+          fa_mma(tmem_s + b * FA_KEYS, a, bd, idesc_qk, ks > 0);
+        }
+        fa_commit(fa_smem(&s_full[b]));
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+        if (!ok) break;
+        const int s = j % FA_STAGES, b = j & 1;
+        ok = fa_mbar_wait(fa_smem(&p_full[b]), (j >> 1) & 1, abort_flag) &&
+             fa_mbar_wait(fa_smem(&o_empty[b]), ((j >> 1) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        fa_fence_after();
+        unsigned char* stage = kv_ring + s * FA_STAGE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < FA_KEYS / 16; ++ks) {  // 16 keys a step
+          const uint64_t a = fa_desc_k_major(fa_smem(p_tiles + b * FA_P_BYTES)) + 2 * ks;
+          const uint64_t bd = fa_desc_mn_major(fa_smem(stage + 2 * FA_KV_HALF + ks * 2048), FA_KV_HALF);
+          fa_mma(tmem_o + b * FA_HD, a, bd, idesc_pv, ks > 0);
+        }
+        fa_commit(fa_smem(&o_full[b]));
+        fa_commit(fa_smem(&kv_empty[s]));
+        fa_commit(fa_smem(&p_empty[b]));
+      }
+      if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 5); }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax and output: one thread a row
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;           // row of the tile = TMEM lane
+    const int row = row0 + r;                    // new-token index in the sequence
+    const bool row_live = row < n_new;
+    const int key_hi = row_live ? start + row + 1 : 0;  // keys [0, key_hi) are visible
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    float o_acc[FA_HD];
+#pragma unroll
+    for (int d = 0; d < FA_HD; ++d) o_acc[d] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, corr_pending = 1.f;
+    bool ok = true;
+
+    auto fold = [&](int j, float corr) {  // O_acc = O_acc * corr + O_tile(j)
+      const int b = j & 1;
+      if (!fa_mbar_wait(fa_smem(&o_full[b]), (j >> 1) & 1, abort_flag)) return false;
+      fa_fence_after();
+#pragma unroll
+      for (int c = 0; c < FA_HD; c += 32) {
+        uint32_t v[32];
+        fa_ld32(v, tmem_o + lane_base + b * FA_HD + c);
+        fa_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o_acc[c + i] = fmaf(o_acc[c + i], corr, __uint_as_float(v[i]));
+      }
+      fa_fence_before();
+      fa_mbar_arrive(fa_smem(&o_empty[b]));
+      return true;
+    };
+
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int b = j & 1;
+      ok = fa_mbar_wait(fa_smem(&s_full[b]), (j >> 1) & 1, abort_flag);
+      if (!ok) break;
+      fa_fence_after();
+      float s[FA_KEYS];
+#pragma unroll
+      for (int c = 0; c < FA_KEYS; c += 32) {
+        uint32_t v[32];
+        fa_ld32(v, tmem_s + lane_base + b * FA_KEYS + c);
+        fa_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(v[i]);
+      }
+      fa_fence_before();
+      fa_mbar_arrive(fa_smem(&s_empty[b]));  // the tensor core may write the block after next into this buffer
+      const int key0 = j * FA_KEYS;
+      float tile_max = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < FA_KEYS; ++i) {
+        s[i] = (key0 + i < key_hi) ? s[i] * scale_log2 : -INFINITY;
+        tile_max = fmaxf(tile_max, s[i]);
+      }
+      const float m_new = fmaxf(m_run, tile_max);
+      const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
+      float sum = 0.f;
+      // P in the operand layout: row r holds 64 keys = 128 bytes; 16-byte piece c sits at c ^ (r % 8)
+      ok = fa_mbar_wait(fa_smem(&p_empty[b]), ((j >> 1) & 1) ^ 1, abort_flag);
+      if (!ok) break;
+      unsigned char* p_row = p_tiles + b * FA_P_BYTES + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float p0 = m_new == -INFINITY ? 0.f : exp2f(s[c * 8 + 2 * i] - m_new);
+          const float p1 = m_new == -INFINITY ? 0.f : exp2f(s[c * 8 + 2 * i + 1] - m_new);
+          sum += p0 + p1;
+          __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+          packed[i] = *reinterpret_cast<uint32_t*>(&pair);
+        }
+        *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads P through the async proxy
+      fa_mbar_arrive(fa_smem(&p_full[b]));
+      l_run = l_run * corr + sum;
+      m_run = m_new;
+      // fold the block before this one while the tensor core multiplies this one's P with V
+      if (j > 0) ok = fold(j - 1, corr_pending);
+      corr_pending = corr;
+    }
+    if (ok && n_tiles > 0) ok = fold(n_tiles - 1, corr_pending);
+    if (ok && row_live) {
+      const float inv = 1.0f / l_run;
+      __nv_bfloat16* dst = out + ((size_t)(tok0 + row) * n_heads + head) * FA_HD;
+#pragma unroll
+      for (int d = 0; d < FA_HD; d += 8) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          __nv_bfloat162 pair = __floats2bfloat162_rn(o_acc[d + 2 * i] * inv, o_acc[d + 2 * i + 1] * inv);
+          packed[i] = *reinterpret_cast<uint32_t*>(&pair);
+        }
+        *reinterpret_cast<uint4*>(dst + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+    }
+    if (!ok && lane == 0) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 5); }
+  }
+
+  fa_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    fa_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(FA_TMEM_COLS));
+  }
+}
+
+typedef CUresult (*FaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static FaEncodeFn fa_encode() {
+  static FaEncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<FaEncodeFn>(ptr);
+  }
+  return fn;
+}
+
+// A map over a row-major bfloat16 matrix [rows, cols], boxes of box_rows x 64 columns, 128-byte swizzle.
+static bool fa_make_map(CUtensorMap* map, const void* base, long long rows, int cols, int box_rows) {
+  FaEncodeFn encode = fa_encode();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1u, 1u};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace xrt
+
+// q, out: bfloat16 [n_tokens, n_heads * 128], the sequences' new tokens end to end (cu_seqlens[n_seqs + 1]);
+// pools: bfloat16 [n_blocks, n_kv_heads, 64, 128]; seq_slot[n_seqs] (< 0: skipped), seq_start[n_seqs] = tokens each
+// sequence held before this step; max_new = the most new tokens any sequence brings.  Head size 128 only, no window.
+// error_flag (may be null) is set to 5 if a bounded wait ran out.
+XRT_EXPORT int xrt_attention_prefill_tcgen05(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                             const int* cu_seqlens, const int* seq_slot, const int* seq_start,
+                                             const int* block_table, int max_blocks, int n_blocks, int n_tokens,
+                                             int n_seqs, int max_new, int n_heads, int n_kv_heads, int head_dim,
+                                             float scale, int* error_flag, cudaStream_t stream) {
+  if (n_seqs < 0 || max_new < 0 || n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 ||
+      n_blocks <= 0)
+    return XRT_ERR_ARGUMENT;
+  if (head_dim != xrt::FA_HD || n_seqs > 65535 || n_heads > 65535) return XRT_ERR_UNSUPPORTED;
+  if (((uintptr_t)q & 15) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || ((uintptr_t)out & 15))
+    return XRT_ERR_UNSUPPORTED;
+  if (n_seqs == 0 || max_new == 0 || n_tokens == 0) return XRT_OK;
+  CUtensorMap map_q, map_k, map_v;
+  const long long pool_rows = (long long)n_blocks * n_kv_heads * xrt::FA_KEYS;
+  if (!xrt::fa_make_map(&map_q, q, n_tokens, n_heads * xrt::FA_HD, xrt::FA_ROWS) ||
+      !xrt::fa_make_map(&map_k, k_pool, pool_rows, xrt::FA_HD, xrt::FA_KEYS) ||
+      !xrt::fa_make_map(&map_v, v_pool, pool_rows, xrt::FA_HD, xrt::FA_KEYS))
+    return XRT_ERR_UNSUPPORTED;
+  static bool allowed = false;
+  if (!allowed) {
+    cudaError_t err = cudaFuncSetAttribute(xrt::attention_prefill_tcgen05_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, xrt::FA_SMEM);
+    if (err != cudaSuccess) return (int)err;
+    allowed = true;
+  }
+  dim3 grid((max_new + xrt::FA_ROWS - 1) / xrt::FA_ROWS, n_heads, n_seqs);
+  xrt::attention_prefill_tcgen05_kernel<<<grid, xrt::FA_THREADS, xrt::FA_SMEM, stream>>>(
+      map_q, map_k, map_v, (__nv_bfloat16*)out, cu_seqlens, seq_slot, seq_start, block_table, max_blocks, n_heads,
+      n_kv_heads, scale * 1.4426950408889634f, error_flag);
+  return xrt::launch_status();
+}

@@ -38,6 +38,7 @@ _SIGNATURES = {
     "xrt_attention_decode_fused": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "xrt_attention_prefill_tcgen05": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
     "xrt_sample": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P],
     "xrt_mark_seen": [_P, _I, _P, _P, _I, _I, _P],
@@ -373,6 +374,24 @@ def attention_prefill(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, b
         _ptr(seq_slot, "seq_slot", torch.int32), _ptr(seq_start, "seq_start", torch.int32),
         _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n_seqs, int(max_new), n_heads,
         n_kv_heads, head_dim, float(scale), int(window), _stream()), "attention_prefill")
+
+
+def attention_prefill_tcgen05(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, block_table, max_new: int,
+                              n_heads: int, n_kv_heads: int, head_dim: int, scale: float) -> None:
+    """bfloat16 causal attention of sequences laid end to end on the tcgen05 tensor cores (head size 128)."""
+    n = q.shape[0]
+    n_seqs = seq_slot.numel()
+    if q.shape != (n, n_heads * head_dim) or out.shape != q.shape or cu_seqlens.numel() != n_seqs + 1:
+        raise KernelError("attention_prefill_tcgen05: shapes do not fit")
+    if k_pool.shape != v_pool.shape or k_pool.shape[1:] != (n_kv_heads, 64, head_dim):
+        raise KernelError("attention_prefill_tcgen05: the cache pool must be [blocks, kv heads, 64, head_dim]")
+    flag = error_flag(q.device)
+    _check(library().xrt_attention_prefill_tcgen05(
+        _ptr(out, "out", torch.bfloat16), _ptr(q, "q", torch.bfloat16), _ptr(k_pool, "k_pool", torch.bfloat16),
+        _ptr(v_pool, "v_pool", torch.bfloat16), _ptr(cu_seqlens, "cu_seqlens", torch.int32),
+        _ptr(seq_slot, "seq_slot", torch.int32), _ptr(seq_start, "seq_start", torch.int32),
+        _ptr(block_table, "block_table", torch.int32), block_table.shape[1], k_pool.shape[0], n, n_seqs, int(max_new),
+        n_heads, n_kv_heads, head_dim, float(scale), flag.data_ptr(), _stream()), "attention_prefill_tcgen05")
 
 
 def fill_normal(out, key: int, mean: float, std: float) -> None:

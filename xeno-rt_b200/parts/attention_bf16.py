@@ -2,11 +2,15 @@
 and the caller uses the kernel that takes any."""
 from __future__ import annotations
 
+import os
+
 from ..csrc import ops
 from .context import context_bucket
 
 SM_COUNT = 148
 DECODE_BLOCKS_PER_SM = 3   # 70 KB of shared memory a block at head size 128
+TCGEN05_MIN_NEW = 32       # prompts at least this long use the tcgen05 attention (tiles of 128 query rows)
+PREFILL_KERNEL = os.environ.get("XRT_PREFILL_ATTN", "")  # "mma" forces the mma.sync kernel, for comparison
 FUSED_COMBINE_MAX = 32     # (tokens x kv heads) up to which the splits are merged inside the attention kernel
 DECODE_WAVES = 2           # blocks wanted = what the GPU holds at once, times this (measured: 1 leaves a long tail
 #                            at 64 sequences, 4 costs more in partials at 8)
@@ -34,6 +38,10 @@ def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window) -> boo
                              n_kv_heads, head_dim, scale, window, chunk, n_splits, fused=fused)
         return True
     if ctx.n_seqs <= 65535 and n_heads <= 65535:
+        if head_dim == 128 and window == 0 and ctx.max_new >= TCGEN05_MIN_NEW and PREFILL_KERNEL != "mma":
+            ops.attention_prefill_tcgen05(out, q, store.k, store.v, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
+                                          store.block_table, ctx.max_new, n_heads, n_kv_heads, head_dim, scale)
+            return True
         ops.attention_prefill(out, q, store.k, store.v, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
                               store.block_table, ctx.max_new, n_heads, n_kv_heads, head_dim, scale, window)
         return True
