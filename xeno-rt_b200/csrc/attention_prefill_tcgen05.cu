@@ -95,6 +95,14 @@ __device__ __forceinline__ void fa_ld32(uint32_t (&r)[32], uint32_t addr) {
                  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                : "r"(addr));
 }
+// 2^x by the special-function unit; exp2(-inf) = 0.  Inputs are differences to a running maximum
+// (at most 0) and the result feeds a bfloat16 product or a 32-bit sum: the unit's 2 ulp are far
+// inside bfloat16's 8 bits.
+__device__ __forceinline__ float fa_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void fa_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __global__ void __launch_bounds__(FA_THREADS, 1)
@@ -138,9 +146,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     fa_mbar_init(fa_smem(q_full), 1);
     for (int s = 0; s < FA_STAGES; ++s) { fa_mbar_init(fa_smem(&kv_full[s]), 1); fa_mbar_init(fa_smem(&kv_empty[s]), 1); }
     for (int b = 0; b < 2; ++b) {
-      fa_mbar_init(fa_smem(&s_full[b]), 1);   fa_mbar_init(fa_smem(&s_empty[b]), 128);
-      fa_mbar_init(fa_smem(&p_full[b]), 128); fa_mbar_init(fa_smem(&p_empty[b]), 1);
-      fa_mbar_init(fa_smem(&o_full[b]), 1);   fa_mbar_init(fa_smem(&o_empty[b]), 128);
+      // the four softmax warps arrive once each (lane 0, after the warp has synchronised): a hundred
+      // and twenty-eight arrivals on one shared-memory word would serialise
+      fa_mbar_init(fa_smem(&s_full[b]), 1);  fa_mbar_init(fa_smem(&s_empty[b]), 4);
+      fa_mbar_init(fa_smem(&p_full[b]), 4);  fa_mbar_init(fa_smem(&p_empty[b]), 1);
+      fa_mbar_init(fa_smem(&o_full[b]), 1);  fa_mbar_init(fa_smem(&o_empty[b]), 4);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -252,7 +262,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         for (int i = 0; i < 32; ++i) o_acc[c + i] = fmaf(o_acc[c + i], corr, __uint_as_float(v[i]));
       }
       fa_fence_before();
-      fa_mbar_arrive(fa_smem(&o_empty[b]));
+      __syncwarp();
+      if (lane == 0) fa_mbar_arrive(fa_smem(&o_empty[b]));
       return true;
     };
 
@@ -271,16 +282,21 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(v[i]);
       }
       fa_fence_before();
-      fa_mbar_arrive(fa_smem(&s_empty[b]));  // the tensor core may write the block after next into this buffer
+      __syncwarp();
+      if (lane == 0) fa_mbar_arrive(fa_smem(&s_empty[b]));  // the tensor core may write the block after next into this buffer
       const int key0 = j * FA_KEYS;
-      float tile_max = -INFINITY;
+      // Only blocks that reach past the first row's last visible key can hide a key from a row
+      // (uniform over the thread block); every other block skips the comparisons.
+      if (key0 + FA_KEYS > start + row0 + 1) {
 #pragma unroll
-      for (int i = 0; i < FA_KEYS; ++i) {
-        s[i] = (key0 + i < key_hi) ? s[i] * scale_log2 : -INFINITY;
-        tile_max = fmaxf(tile_max, s[i]);
+        for (int i = 0; i < FA_KEYS; ++i) s[i] = (key0 + i < key_hi) ? s[i] : -INFINITY;
       }
-      const float m_new = fmaxf(m_run, tile_max);
-      const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
+      float tile_max = -INFINITY;  // of the raw scores: the scale is positive and is applied inside the exponent
+#pragma unroll
+      for (int i = 0; i < FA_KEYS; ++i) tile_max = fmaxf(tile_max, s[i]);
+      const float m_new = fmaxf(m_run, tile_max * scale_log2);
+      const float corr = m_new == -INFINITY ? 1.f : fa_exp2(m_run - m_new);
+      const float neg_m = m_new == -INFINITY ? 0.f : -m_new;  // a row without visible keys: exp2(-inf) = 0 all the same
       float sum = 0.f;
       // P in the operand layout: row r holds 64 keys = 128 bytes; 16-byte piece c sits at c ^ (r % 8)
       ok = fa_mbar_wait(fa_smem(&p_empty[b]), ((j >> 1) & 1) ^ 1, abort_flag);
@@ -291,8 +307,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         uint32_t packed[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float p0 = m_new == -INFINITY ? 0.f : exp2f(s[c * 8 + 2 * i] - m_new);
-          const float p1 = m_new == -INFINITY ? 0.f : exp2f(s[c * 8 + 2 * i + 1] - m_new);
+          const float p0 = fa_exp2(fmaf(s[c * 8 + 2 * i], scale_log2, neg_m));
+          const float p1 = fa_exp2(fmaf(s[c * 8 + 2 * i + 1], scale_log2, neg_m));
           sum += p0 + p1;
           __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
           packed[i] = *reinterpret_cast<uint32_t*>(&pair);
@@ -300,7 +316,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads P through the async proxy
-      fa_mbar_arrive(fa_smem(&p_full[b]));
+      __syncwarp();
+      if (lane == 0) fa_mbar_arrive(fa_smem(&p_full[b]));
       l_run = l_run * corr + sum;
       m_run = m_new;
       // fold the block before this one while the tensor core multiplies this one's P with V
