@@ -28,13 +28,24 @@
 
 namespace xrt {
 
-constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_STAGES = 4, TC_UMMA_K = 16;
-constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;        // 16 KB
+constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_UMMA_K = 16;
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;        // 16 KB: 128 rows of X, one slab of K
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;        // 32 KB
-constexpr int TC_THREADS = 192;
+// MT = 1: tiles of 128 x 256, four stages, two accumulators (the epilogue of a tile overlaps the MMAs
+// of the next).  MT = 2: tiles of 256 x 256 (two MMAs a slab share the W tile: a third fewer operand
+// bytes per flop, which is what bounds this kernel), three stages, one accumulator of all 512 TMEM
+// columns and eight epilogue warps to drain it.
+template <int MT> struct TcShape {
+  static constexpr int STAGES = MT == 1 ? 4 : 3;
+  static constexpr int STAGE_BYTES = MT * TC_A_BYTES + TC_BN * TC_BK * 2;
+  static constexpr int ACC_SETS = MT == 1 ? 2 : 1;
+  static constexpr int EPI_WARPS = 4 * MT;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+  static constexpr int STAGING_BYTES = EPI_WARPS * 32 * 33 * 4;    // a 32 x 32 patch (padded) an epilogue warp
+  static constexpr int SMEM = STAGES * STAGE_BYTES + STAGING_BYTES + 256 + 1024;  // + barriers + alignment slack
+};
 constexpr int TC_TMEM_COLS = 512;
 constexpr long long TC_SPIN_LIMIT = 1ll << 24;
-constexpr int TC_SMEM = TC_STAGES * (TC_A_BYTES + TC_B_BYTES) + 256 + 1024;  // + barriers + alignment slack
 
 __device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -98,34 +109,58 @@ __device__ __forceinline__ void tc_ld32(uint32_t (&r)[32], uint32_t addr) {
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// Four consecutive outputs of one row: 16 bytes of float32 (stored, or added into the residual
+// stream) or 8 bytes of bfloat16.
+template <int MODE>
+__device__ __forceinline__ void store_quad(float* dst, float a, float b, float c, float d) {
+  float4* p = reinterpret_cast<float4*>(dst);
+  if (MODE == 1) {
+    const float4 old = *p;
+    *p = make_float4(old.x + a, old.y + b, old.z + c, old.w + d);
+  } else {
+    *p = make_float4(a, b, c, d);
+  }
+}
+template <int MODE>
+__device__ __forceinline__ void store_quad(__nv_bfloat16* dst, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 packed;
+  packed.x = *reinterpret_cast<uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
 // MODE 0: store, 1: add into float out, 2: SwiGLU.  n_tiles_n counts tiles of 256 output columns
 // (SwiGLU: of 128, each computed from 128 gate rows and 128 up rows of W).
-template <int MODE, typename TO>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+template <int MODE, int MT, typename TO>
+__global__ void __launch_bounds__(TcShape<MT>::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     TO* __restrict__ out, int M, int N, int K, int ldo, int up_rows, int* __restrict__ error_flag) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int TC_STAGES = TcShape<MT>::STAGES, ACC_SETS = TcShape<MT>::ACC_SETS;
+  constexpr int STAGE_A = MT * TC_A_BYTES;
   unsigned char* a_stages = smem;
-  unsigned char* b_stages = smem + TC_STAGES * TC_A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TC_STAGES * (TC_A_BYTES + TC_B_BYTES));
+  unsigned char* b_stages = smem + TC_STAGES * STAGE_A;
+  float* staging = reinterpret_cast<float*>(smem + TC_STAGES * TcShape<MT>::STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TC_STAGES * TcShape<MT>::STAGE_BYTES + TcShape<MT>::STAGING_BYTES);
   uint64_t* full = bars;                       // [TC_STAGES]
   uint64_t* empty = bars + TC_STAGES;          // [TC_STAGES]
-  uint64_t* acc_full = bars + 2 * TC_STAGES;   // [2]
-  uint64_t* acc_empty = acc_full + 2;          // [2]
+  uint64_t* acc_full = bars + 2 * TC_STAGES;   // [ACC_SETS] (room for two)
+  uint64_t* acc_empty = acc_full + 2;          // [ACC_SETS]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int N_PER_TILE = MODE == 2 ? TC_BN / 2 : TC_BN;  // output columns a tile
-  const int tiles_m = (M + TC_BM - 1) / TC_BM;
+  const int tiles_m = (M + MT * TC_BM - 1) / (MT * TC_BM);
   const int tiles_n = (N + N_PER_TILE - 1) / N_PER_TILE;
   const int n_tiles = tiles_m * tiles_n;
   const int k_iters = (K + TC_BK - 1) / TC_BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TC_STAGES; ++s) { tc_mbar_init(tc_smem(&full[s]), 1); tc_mbar_init(tc_smem(&empty[s]), 1); }
-    for (int a = 0; a < 2; ++a) { tc_mbar_init(tc_smem(&acc_full[a]), 1); tc_mbar_init(tc_smem(&acc_empty[a]), 128); }
+    for (int a = 0; a < 2; ++a) { tc_mbar_init(tc_smem(&acc_full[a]), 1); tc_mbar_init(tc_smem(&acc_empty[a]), 32 * TcShape<MT>::EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -152,8 +187,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           ok = tc_mbar_wait(tc_smem(&empty[s]), ((it / TC_STAGES) & 1) ^ 1, abort_flag);
           if (!ok) break;
           const uint32_t bar = tc_smem(&full[s]);
-          tc_mbar_expect_tx(bar, TC_A_BYTES + TC_B_BYTES);
-          tc_tma_load_2d(tc_smem(a_stages + s * TC_A_BYTES), &map_x, kb * TC_BK, m_blk * TC_BM, bar);
+          tc_mbar_expect_tx(bar, STAGE_A + TC_B_BYTES);
+#pragma unroll
+          for (int h = 0; h < MT; ++h)
+            tc_tma_load_2d(tc_smem(a_stages + s * STAGE_A + h * TC_A_BYTES), &map_x, kb * TC_BK,
+                           (m_blk * MT + h) * TC_BM, bar);
           const int w_row0 = n_blk * N_PER_TILE;
           const int w_row1 = MODE == 2 ? up_rows + w_row0 : w_row0 + 128;
           tc_tma_load_2d(tc_smem(b_stages + s * TC_B_BYTES), &map_w, kb * TC_BK, w_row0, bar);
@@ -169,21 +207,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       int it = 0, tile_i = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tile_i) {
-        const int a = tile_i & 1;
-        ok = tc_mbar_wait(tc_smem(&acc_empty[a]), ((tile_i >> 1) & 1) ^ 1, abort_flag);
+        const int a = tile_i % ACC_SETS;
+        ok = tc_mbar_wait(tc_smem(&acc_empty[a]), ((tile_i / ACC_SETS) & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + a * TC_BN;
+        const uint32_t tmem_d = tmem_base + a * MT * TC_BN;
         for (int kb = 0; kb < k_iters; ++kb, ++it) {
           const int s = it % TC_STAGES;
           ok = tc_mbar_wait(tc_smem(&full[s]), (it / TC_STAGES) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint64_t desc_a = tc_smem_desc(tc_smem(a_stages + s * TC_A_BYTES));
           const uint64_t desc_b = tc_smem_desc(tc_smem(b_stages + s * TC_B_BYTES));
 #pragma unroll
-          for (int k = 0; k < TC_BK / TC_UMMA_K; ++k)  // 32 bytes further along K inside the swizzle atom
-            tc_mma(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0);
+          for (int h = 0; h < MT; ++h) {
+            const uint64_t desc_a = tc_smem_desc(tc_smem(a_stages + s * STAGE_A + h * TC_A_BYTES));
+#pragma unroll
+            for (int k = 0; k < TC_BK / TC_UMMA_K; ++k)  // 32 bytes further along K inside the swizzle atom
+              tc_mma(tmem_d + h * TC_BN, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0);
+          }
           tc_commit(tc_smem(&empty[s]));
         }
         if (ok) tc_commit(tc_smem(&acc_full[a]));
@@ -193,18 +234,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // the TMEM lanes this warp may read: 32 * quarter ..
+    const int half = (warp - 2) / 4;  // which 128 rows of the tile (always 0 for tiles of 128 rows)
     int tile_i = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tile_i) {
       const int m_blk = tile % tiles_m, n_blk = tile / tiles_m;
-      const int a = tile_i & 1;
-      ok = tc_mbar_wait(tc_smem(&acc_full[a]), (tile_i >> 1) & 1, abort_flag);
+      const int a = tile_i % ACC_SETS;
+      ok = tc_mbar_wait(tc_smem(&acc_full[a]), (tile_i / ACC_SETS) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const int row = m_blk * TC_BM + quarter * 32 + lane;
-      const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * TC_BN;
+      const int row0 = (m_blk * MT + half) * TC_BM + quarter * 32;  // the warp's first row
+      const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (a * MT + half) * TC_BN;
       const int col0 = n_blk * N_PER_TILE;
-      TO* dst_row = out + (size_t)row * ldo + col0;
+      // A thread holds one ROW of the accumulator; written as it is, every store instruction of the
+      // warp would touch 32 lines.  The warp turns each 32 x 32 patch around in shared memory and
+      // writes it with 16 bytes a lane, four whole 128-byte row pieces an instruction.
+      float* patch = staging + (warp - 2) * 32 * 33;
+      const int sub_row = lane >> 3, sub_col = (lane & 7) * 4;
 #pragma unroll 1
       for (int c = 0; c < N_PER_TILE; c += 32) {
         uint32_t v[32];
@@ -221,16 +267,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         } else {
           tc_wait_ld();
         }
-        if (row < M) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (col0 + c + j < N) {
-              const float val = __uint_as_float(v[j]);
-              if (MODE == 1) dst_row[c + j] = from_float<TO>(to_float(dst_row[c + j]) + val);
-              else dst_row[c + j] = from_float<TO>(val);
+        for (int j = 0; j < 32; ++j) patch[lane * 33 + j] = __uint_as_float(v[j]);
+        __syncwarp();
+        // the residual values first, all eight loads in flight (a load may not pass a store that
+        // could alias it, so a read-modify-write a row piece at a time would wait for each in turn)
+        float4 old[8];
+        if (MODE == 1) {
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int row = row0 + it * 4 + sub_row, col = col0 + c + sub_col;
+            const float* src = reinterpret_cast<const float*>(out) + (size_t)row * ldo + col;
+            const bool whole = row < M && col + 3 < N && (((uintptr_t)src) & 15) == 0;
+            old[it] = whole ? *reinterpret_cast<const float4*>(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int pr = it * 4 + sub_row;  // row of the patch
+          const int row = row0 + pr, col = col0 + c + sub_col;
+          const float* src = patch + pr * 33 + sub_col;
+          if (row < M) {
+            TO* dst = out + (size_t)row * ldo + col;
+            if (col + 3 < N && (((uintptr_t)dst) & (4 * sizeof(TO) - 1)) == 0) {
+              if (MODE == 1)
+                store_quad<0>(dst, old[it].x + src[0], old[it].y + src[1], old[it].z + src[2], old[it].w + src[3]);
+              else
+                store_quad<0>(dst, src[0], src[1], src[2], src[3]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (col + e < N) {
+                  if (MODE == 1) dst[e] = from_float<TO>(to_float(dst[e]) + src[e]);
+                  else dst[e] = from_float<TO>(src[e]);
+                }
             }
           }
         }
+        __syncwarp();
       }
       tc_fence_before();
       tc_mbar_arrive(tc_smem(&acc_empty[a]));
@@ -275,21 +349,43 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int MODE, typename TO>
-int launch_tcgen05(void* out, const CUtensorMap& map_x, const CUtensorMap& map_w, int M, int N, int K, int ldo,
-                   int up_rows, int* error_flag, int sm_count, cudaStream_t stream) {
-  auto kernel = gemm_tcgen05_kernel<MODE, TO>;
+template <int MODE, int MT, typename TO>
+int launch_tcgen05_tiled(void* out, const CUtensorMap& map_x, const CUtensorMap& map_w, int M, int N, int K, int ldo,
+                         int up_rows, int* error_flag, int sm_count, cudaStream_t stream) {
+  auto kernel = gemm_tcgen05_kernel<MODE, MT, TO>;
   static bool allowed = false;
   if (!allowed) {
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<MT>::SMEM);
     if (err != cudaSuccess) return (int)err;
     allowed = true;
   }
   constexpr int n_per_tile = MODE == 2 ? TC_BN / 2 : TC_BN;
-  const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + n_per_tile - 1) / n_per_tile);
+  const int tiles = ((M + MT * TC_BM - 1) / (MT * TC_BM)) * ((N + n_per_tile - 1) / n_per_tile);
   const int blocks = tiles < sm_count ? tiles : sm_count;
-  kernel<<<blocks, TC_THREADS, TC_SMEM, stream>>>(map_x, map_w, (TO*)out, M, N, K, ldo, up_rows, error_flag);
+  kernel<<<blocks, TcShape<MT>::THREADS, TcShape<MT>::SMEM, stream>>>(map_x, map_w, (TO*)out, M, N, K, ldo, up_rows,
+                                                                      error_flag);
   return launch_status();
+}
+
+// Tiles of 256 rows for products of few tiles, when they keep the multiprocessors about as busy as
+// tiles of 128 rows would (the larger tile moves a third fewer operand bytes per flop and drains its
+// accumulator with twice the warps; with many tiles the overlap of the small tile's two accumulators wins).
+// XRT_GEMM_TILE_ROWS=128 or 256 forces one, for comparison.
+template <int MODE, typename TO>
+int launch_tcgen05(void* out, const CUtensorMap& map_x, const CUtensorMap& map_w, int M, int N, int K, int ldo,
+                   int up_rows, int* error_flag, int sm_count, cudaStream_t stream) {
+  constexpr int n_per_tile = MODE == 2 ? TC_BN / 2 : TC_BN;
+  const long long tiles_n = (N + n_per_tile - 1) / n_per_tile;
+  auto busy = [&](long long tiles) { return (double)tiles / (double)(((tiles + sm_count - 1) / sm_count) * sm_count); };
+  const long long small_tiles = ((M + 127) / 128) * tiles_n;
+  const double small = busy(small_tiles), large = 1.25 * busy(((M + 255) / 256) * tiles_n);
+  static int forced = -1;
+  if (forced < 0) { const char* e = getenv("XRT_GEMM_TILE_ROWS"); forced = e ? atoi(e) : 0; }
+  // measured at 2,048 and 8,192 rows: the large tile wins where the small one leaves under two rounds of work
+  const bool use_large = forced == 256 || (forced != 128 && M > 128 && small_tiles <= 2 * sm_count && large > small);
+  if (use_large)
+    return launch_tcgen05_tiled<MODE, 2, TO>(out, map_x, map_w, M, N, K, ldo, up_rows, error_flag, sm_count, stream);
+  return launch_tcgen05_tiled<MODE, 1, TO>(out, map_x, map_w, M, N, K, ldo, up_rows, error_flag, sm_count, stream);
 }
 
 }  // namespace xrt
