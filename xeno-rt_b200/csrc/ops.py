@@ -42,6 +42,7 @@ _SIGNATURES = {
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
     "xrt_sample": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P],
     "xrt_mark_seen": [_P, _I, _P, _P, _I, _I, _P],
+    "xrt_decode_chain": [_P, _I, _P, _I, _P, _P],
 }
 
 
@@ -68,6 +69,14 @@ def library():
             lib.xrt_gemm_decode_tcgen05_scratch.restype = ctypes.c_longlong
             _lib = lib
     return _lib
+
+
+def _kernels():
+    """The library, for a launch that is issued now: phases waiting in a chain are launched first,
+    so that device work keeps the order in which the parts asked for it."""
+    if _chain is not None and _chain.entries:
+        chain_flush()
+    return library()
 
 
 def require_device() -> None:
@@ -130,7 +139,7 @@ def embedding(out, table, ids, error_flag) -> None:
     vocab = table.shape[0]
     if table.shape[1] != hidden or ids.numel() != n:
         raise KernelError("embedding: shapes do not fit")
-    _check(library().xrt_embedding(_ptr(out, "out", torch.float32), _ptr(table, "table"),
+    _check(_kernels().xrt_embedding(_ptr(out, "out", torch.float32), _ptr(table, "table"),
                                    _ptr(ids, "ids", torch.int32), n, hidden, vocab, _code(table.dtype),
                                    _ptr(error_flag, "error_flag", torch.int32), _stream()), "embedding")
 
@@ -142,7 +151,10 @@ def rmsnorm(out, x, weight, eps: float, rows=None) -> None:
         raise KernelError("rmsnorm: shapes do not fit")
     if rows is not None and rows.numel() != n_rows:
         raise KernelError("rmsnorm: one row index per output row is needed")
-    _check(library().xrt_rmsnorm(_ptr(out, "out"), _ptr(x, "x", torch.float32), _ptr(weight, "weight"),
+    if _chain is not None and _chain.takes_norm(out, x, weight, rows):
+        _chain.add_norm(out, x, weight, eps, rows)
+        return
+    _check(_kernels().xrt_rmsnorm(_ptr(out, "out"), _ptr(x, "x", torch.float32), _ptr(weight, "weight"),
                                  _ptr(rows, "rows", torch.int32), n_rows, width, float(eps),
                                  _code(weight.dtype), _code(out.dtype), _stream()), "rmsnorm")
 
@@ -152,7 +164,7 @@ def swiglu(out, gate_up) -> None:
     n, width = out.shape
     if gate_up.shape[0] != n or gate_up.shape[1] != 2 * width:
         raise KernelError("swiglu: shapes do not fit")
-    _check(library().xrt_swiglu(_ptr(out, "out"), _ptr(gate_up, "gate_up"), n, width, _code(gate_up.dtype),
+    _check(_kernels().xrt_swiglu(_ptr(out, "out"), _ptr(gate_up, "gate_up"), n, width, _code(gate_up.dtype),
                                 _code(out.dtype), _stream()), "swiglu")
 
 
@@ -161,7 +173,7 @@ def rope_table(cos_sin, positions, freq, scale: float) -> None:
     n, half = cos_sin.shape[0], cos_sin.shape[1]
     if positions.numel() != n or freq.numel() != half or cos_sin.shape[2] != 2:
         raise KernelError("rope_table: shapes do not fit")
-    _check(library().xrt_rope_table(_ptr(cos_sin, "cos_sin", torch.float32),
+    _check(_kernels().xrt_rope_table(_ptr(cos_sin, "cos_sin", torch.float32),
                                     _ptr(positions, "positions", torch.int32), _ptr(freq, "freq", torch.float32),
                                     float(scale), n, half, _stream()), "rope_table")
 
@@ -182,7 +194,7 @@ def qk_rope_kv_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, q
             raise KernelError("qk_rope_kv_write: the q/k/v row is too short")
     norm_dtype = q_norm_w.dtype if q_norm_w is not None else torch.float32
     cache_dtype = k_pool.dtype if write_kv else q_out.dtype
-    _check(library().xrt_qk_rope_kv_write(
+    _check(_kernels().xrt_qk_rope_kv_write(
         _ptr(q_out, "q_out"), _ptr(k_pool if write_kv else None, "k_pool"),
         _ptr(v_pool if write_kv else None, "v_pool"), _ptr(qkv, "qkv", torch.float32), qkv.shape[1], k_offset,
         v_offset, _ptr(q_norm_w, "q_norm_w"), _ptr(k_norm_w, "k_norm_w"), float(eps),
@@ -200,7 +212,7 @@ def attention_reference(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, 
         raise KernelError("attention_reference: shapes do not fit")
     if k_pool.shape != v_pool.shape or k_pool.shape[1:] != (n_kv_heads, 64, head_dim):
         raise KernelError("attention_reference: the cache pool must be [blocks, kv heads, 64, head_dim]")
-    _check(library().xrt_attention_reference(
+    _check(_kernels().xrt_attention_reference(
         _ptr(out, "out"), _ptr(q, "q"), _ptr(k_pool, "k_pool"), _ptr(v_pool, "v_pool", k_pool.dtype),
         _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
         _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
@@ -218,7 +230,7 @@ def gemm_reference(out, x, w, accumulate: bool = False) -> None:
         raise KernelError("gemm: rows must be contiguous")
     if not x.is_cuda or not out.is_cuda:
         raise KernelError("gemm: operands must be on a CUDA device")
-    _check(library().xrt_gemm_reference(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0),
+    _check(_kernels().xrt_gemm_reference(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0),
                                         out.stride(0), _code(x.dtype), _code(w.dtype), _code(out.dtype),
                                         1 if accumulate else 0, _stream()), "gemm_reference")
 
@@ -243,6 +255,8 @@ def check_error_flag(device) -> None:
     value = int(flag.item())
     if value != 0:
         flag.zero_()
+        for state in _chain_state.values():  # a chain that gave up leaves its barrier half counted
+            state.zero_()
         raise KernelError(f"a kernel reported error {value}: a bounded wait on a copy or a tensor-core operation ran "
                           f"out; results of the last steps are not valid")
 
@@ -262,7 +276,120 @@ def device_state(device):
     if key not in _counters:
         _counters[key] = torch.zeros(_COUNTER_SLOTS, dtype=torch.int32, device=device)
         _sm_counts[key] = torch.cuda.get_device_properties(device).multi_processor_count
+        _chain_state[key] = torch.zeros(2, dtype=torch.int32, device=device)  # the chain kernel's barrier
     return error_flag(device), _counters[key], _sm_counts[key]
+
+
+# ---------------------------------------------------------------------------------------------------
+# The decode chain: norms and few-row products that parts ask for are queued and run by one launch of
+# the persistent kernel of decode_chain.cu instead of one kernel each.
+
+CHAIN_MAX_ROWS = 16
+CHAIN_MAX_PHASES = 12
+_chain_state: dict = {}
+_chain = None
+
+
+class _ChainPhase(ctypes.Structure):
+    _fields_ = [("x", _P), ("w", _P), ("out", _P), ("rows", _P), ("up_offset", ctypes.c_longlong),
+                ("kind", _I), ("mode", _I), ("m", _I), ("n", _I), ("k", _I), ("ldx", _I), ("ldo", _I),
+                ("out_dtype", _I), ("w_dtype", _I), ("unit_rows", _I), ("first_unit", _I), ("splits", _I),
+                ("chunk", _I), ("eps", _F), ("reserved", _I)]
+
+
+def chain_enabled() -> bool:
+    """XRT_DECODE_CHAIN=1 turns the chain on for model steps.  It is off by default: measured on a
+    B200 at the 8B shape a decode step of 8 sequences takes 5.69 ms with it and 5.28 ms with one
+    kernel per phase (1 sequence: 4.74 against 3.92 ms): a meeting of all blocks between two phases costs
+    about what a kernel boundary costs, and the ring of 135 KB a block holds only 3 microseconds of
+    the weight stream."""
+    import os
+    return os.environ.get("XRT_DECODE_CHAIN", "0") == "1"
+
+
+class _Chain:
+    """Phases waiting for one launch.  ``entries`` holds (phase, tensors kept alive, the call that
+    runs the phase as a kernel of its own)."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.entries = []
+
+    @staticmethod
+    def _aligned(*tensors) -> bool:
+        return all(t is None or (t.is_cuda and t.data_ptr() % 16 == 0) for t in tensors)
+
+    def takes_norm(self, out, x, weight, rows) -> bool:
+        width = out.shape[1]
+        return (0 < out.shape[0] <= CHAIN_MAX_ROWS and width % 4 == 0 and x.dtype == torch.float32
+                and out.is_contiguous() and x.is_contiguous() and weight.is_contiguous()
+                and self._aligned(out, x, weight) and (rows is None or rows.dtype == torch.int32))
+
+    def takes_product(self, out, x, w) -> bool:
+        return (0 < x.shape[0] <= CHAIN_MAX_ROWS and w.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+                and w.is_contiguous() and self._aligned(x, w))
+
+    def _add(self, phase, keep, alone) -> None:
+        self.entries.append((phase, keep, alone))
+        if len(self.entries) == CHAIN_MAX_PHASES:
+            chain_flush()
+
+    def add_norm(self, out, x, weight, eps, rows) -> None:
+        ph = _ChainPhase(x=x.data_ptr(), w=weight.data_ptr(), out=out.data_ptr(),
+                         rows=0 if rows is None else rows.data_ptr(), up_offset=0, kind=0, mode=0, m=out.shape[0],
+                         n=0, k=out.shape[1], ldx=x.stride(0), ldo=out.stride(0), out_dtype=_code(out.dtype),
+                         w_dtype=_code(weight.dtype), eps=float(eps))
+        self._add(ph, (out, x, weight, rows), lambda: rmsnorm(out, x, weight, eps, rows))
+
+    def add_product(self, out, x, w, code: int, up_rows: int) -> None:
+        ph = _ChainPhase(x=x.data_ptr(), w=w.data_ptr(), out=out.data_ptr(), rows=0, up_offset=up_rows * w.shape[1],
+                         kind=1, mode=code, m=x.shape[0], n=out.shape[1], k=x.shape[1], ldx=x.stride(0),
+                         ldo=out.stride(0), out_dtype=_code(out.dtype), w_dtype=_code(w.dtype), eps=0.0)
+        mode = ("store", "accumulate", "swiglu")[code]
+        self._add(ph, (out, x, w), lambda: gemm_stream(out, x, w, mode, up_rows))
+
+
+def chain_begin(device) -> None:
+    """From here to ``chain_end`` norms and products of at most CHAIN_MAX_ROWS rows are queued; any
+    other kernel of this library launches what is queued first.  Only for code all of whose device
+    work goes through this module (a part says so with ``chain_safe = True``)."""
+    global _chain
+    if _chain is not None:
+        raise KernelError("a decode chain is open already")
+    device_state(device)
+    _chain = _Chain(device)
+
+
+def chain_flush() -> None:
+    global _chain
+    chain = _chain
+    if chain is None or not chain.entries:
+        return
+    entries, chain.entries = chain.entries, []
+    key = chain.device.index if chain.device.index is not None else torch.cuda.current_device()
+    flag, _, sms = device_state(chain.device)
+    sync = _chain_state[key]
+    phases = (_ChainPhase * len(entries))(*[e[0] for e in entries])
+    status = library().xrt_decode_chain(ctypes.addressof(phases), len(entries), sync.data_ptr(), sms, flag.data_ptr(),
+                                        _stream())
+    if status == -2:  # sizes the persistent kernel does not take: each phase as a kernel of its own
+        _chain = None
+        try:
+            for _, _, alone in entries:
+                alone()
+        finally:
+            _chain = chain
+        return
+    _check(status, "decode_chain")
+
+
+def chain_end(discard: bool = False) -> None:
+    global _chain
+    try:
+        if not discard:
+            chain_flush()
+    finally:
+        _chain = None
 
 
 def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
@@ -304,7 +431,7 @@ def gemm_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
         raise KernelError("gemm_tcgen05: rows must be contiguous and on a CUDA device")
     code = {"store": 0, "accumulate": 1, "swiglu": 2}[mode]
     flag = error_flag(x.device)
-    _check(library().xrt_gemm_tcgen05(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
+    _check(_kernels().xrt_gemm_tcgen05(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
                                       w.shape[0], _code(out.dtype), code, up_rows, flag.data_ptr(), _stream()),
            "gemm_tcgen05")
 
@@ -322,7 +449,10 @@ def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
     if x.stride(1) != 1 or out.stride(1) != 1 or not x.is_cuda or not out.is_cuda:
         raise KernelError("gemm_stream: rows must be contiguous and on a CUDA device")
     code = {"store": 0, "accumulate": 1, "swiglu": 2}[mode]
-    _check(library().xrt_gemm_stream(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
+    if _chain is not None and _chain.takes_product(out, x, w):
+        _chain.add_product(out, x, w, code, up_rows)
+        return
+    _check(_kernels().xrt_gemm_stream(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
                                      _code(out.dtype), code, up_rows, _stream()), "gemm_stream")
 
 
@@ -342,14 +472,14 @@ def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_h
         part_ml = torch.empty(n * n_heads * n_splits * 2, dtype=torch.float32, device=q.device)
     if fused and n_splits > 1 and n * n_kv_heads <= _COUNTER_SLOTS:
         _, counters, _ = device_state(q.device)
-        _check(library().xrt_attention_decode_fused(
+        _check(_kernels().xrt_attention_decode_fused(
             _ptr(out, "out", torch.bfloat16), _ptr(part_o, "part_o"), _ptr(part_ml, "part_ml"), counters.data_ptr(),
             _ptr(q, "q", torch.bfloat16), _ptr(k_pool, "k_pool", torch.bfloat16), _ptr(v_pool, "v_pool", torch.bfloat16),
             _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
             _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
             float(scale), int(window), int(chunk), int(n_splits), _stream()), "attention_decode")
         return
-    _check(library().xrt_attention_decode(
+    _check(_kernels().xrt_attention_decode(
         _ptr(out, "out", torch.bfloat16), _ptr(part_o, "part_o"), _ptr(part_ml, "part_ml"),
         _ptr(q, "q", torch.bfloat16), _ptr(k_pool, "k_pool", torch.bfloat16), _ptr(v_pool, "v_pool", torch.bfloat16),
         _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
@@ -368,7 +498,7 @@ def attention_prefill(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, b
         raise KernelError("attention_prefill: shapes do not fit")
     if k_pool.shape != v_pool.shape or k_pool.shape[1:] != (n_kv_heads, 64, head_dim):
         raise KernelError("attention_prefill: the cache pool must be [blocks, kv heads, 64, head_dim]")
-    _check(library().xrt_attention_prefill(
+    _check(_kernels().xrt_attention_prefill(
         _ptr(out, "out", torch.bfloat16), _ptr(q, "q", torch.bfloat16), _ptr(k_pool, "k_pool", torch.bfloat16),
         _ptr(v_pool, "v_pool", torch.bfloat16), _ptr(cu_seqlens, "cu_seqlens", torch.int32),
         _ptr(seq_slot, "seq_slot", torch.int32), _ptr(seq_start, "seq_start", torch.int32),
@@ -386,7 +516,7 @@ def attention_prefill_tcgen05(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_
     if k_pool.shape != v_pool.shape or k_pool.shape[1:] != (n_kv_heads, 64, head_dim):
         raise KernelError("attention_prefill_tcgen05: the cache pool must be [blocks, kv heads, 64, head_dim]")
     flag = error_flag(q.device)
-    _check(library().xrt_attention_prefill_tcgen05(
+    _check(_kernels().xrt_attention_prefill_tcgen05(
         _ptr(out, "out", torch.bfloat16), _ptr(q, "q", torch.bfloat16), _ptr(k_pool, "k_pool", torch.bfloat16),
         _ptr(v_pool, "v_pool", torch.bfloat16), _ptr(cu_seqlens, "cu_seqlens", torch.int32),
         _ptr(seq_slot, "seq_slot", torch.int32), _ptr(seq_start, "seq_start", torch.int32),
@@ -396,7 +526,7 @@ def attention_prefill_tcgen05(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_
 
 def fill_normal(out, key: int, mean: float, std: float) -> None:
     """Fills ``out`` with the seeded normal stream ``key`` (see weights/random_init.py)."""
-    _check(library().xrt_fill_normal(_ptr(out, "out"), out.numel(), key & ((1 << 64) - 1), float(mean),
+    _check(_kernels().xrt_fill_normal(_ptr(out, "out"), out.numel(), key & ((1 << 64) - 1), float(mean),
                                      float(std), _code(out.dtype), _stream()), "fill_normal")
 
 
@@ -404,7 +534,7 @@ def sample(out_ids, logits, row_slot, temperature, top_k, top_p, penalty, seen, 
     """One token id per row of float32 logits; see sampling.cu for the conventions."""
     n, vocab = logits.shape
     seen_words = 0 if seen is None else seen.shape[1]
-    _check(library().xrt_sample(
+    _check(_kernels().xrt_sample(
         _ptr(out_ids, "out_ids", torch.int32), _ptr(logits, "logits", torch.float32), n, vocab,
         _ptr(row_slot, "row_slot", torch.int32), _ptr(temperature, "temperature", torch.float32),
         _ptr(top_k, "top_k", torch.int32), _ptr(top_p, "top_p", torch.float32),
@@ -415,6 +545,6 @@ def sample(out_ids, logits, row_slot, temperature, top_k, top_p, penalty, seen, 
 def mark_seen(seen, slots, ids, vocab: int) -> None:
     """Sets the bit of ids[i] in the bitmap of slots[i]."""
     n = ids.numel()
-    _check(library().xrt_mark_seen(_ptr(seen, "seen", torch.int32), seen.shape[1],
+    _check(_kernels().xrt_mark_seen(_ptr(seen, "seen", torch.int32), seen.shape[1],
                                    _ptr(slots, "slots", torch.int32), _ptr(ids, "ids", torch.int32), n, vocab,
                                    _stream()), "mark_seen")

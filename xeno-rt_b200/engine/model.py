@@ -45,6 +45,9 @@ class Model:
         for layer in self.layers:
             parts += [layer.mixer_norm, layer.mixer, layer.ffn_norm, layer.ffn]
         self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
+        # steps of few tokens run their norms and products through the persistent chain kernel
+        self.chain_safe = (dtype is DType.BF16 and ops.chain_enabled()
+                           and all(getattr(p, "chain_safe", False) for p in parts))
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -97,11 +100,21 @@ class Model:
         logits [len(want_rows), vocab] (None if no row is wanted).  The order inside is that of
         crates/xrt-models/src/llama.rs:432-613; the final norm and the output matrix see only the
         wanted rows (llama.rs:814-819 does so for the last token)."""
-        x = self.embedding.forward(ctx.token_ids, self.error_flag)
-        for i, place in enumerate(self.spec.schedule):
-            owns = place.cache_from is None
-            store = cache.store(i if owns else place.cache_from)
-            self.arrangements[place.layer](self.layers[place.layer], x, ctx, store, owns)
-        if want_rows is None or want_rows.numel() == 0:
-            return None
-        return self.lm_head.forward(self.final_norm.forward(x, want_rows))
+        chained = self.chain_safe and 0 < ctx.n_tokens <= ops.CHAIN_MAX_ROWS
+        if chained:
+            ops.chain_begin(self.device)
+        done = False
+        try:
+            x = self.embedding.forward(ctx.token_ids, self.error_flag)
+            for i, place in enumerate(self.spec.schedule):
+                owns = place.cache_from is None
+                store = cache.store(i if owns else place.cache_from)
+                self.arrangements[place.layer](self.layers[place.layer], x, ctx, store, owns)
+            logits = None
+            if want_rows is not None and want_rows.numel() > 0:
+                logits = self.lm_head.forward(self.final_norm.forward(x, want_rows))
+            done = True
+        finally:
+            if chained:
+                ops.chain_end(discard=not done)
+        return logits

@@ -26,6 +26,7 @@ class GroupedQueryAttention:
     ``o`` [width, n_heads*head_dim], and with qk_norm ``q_norm``, ``k_norm`` [head_dim]."""
 
     graph_safe = True
+    chain_safe = True
 
     @classmethod
     def weight_shapes(cls, params):

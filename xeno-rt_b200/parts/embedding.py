@@ -13,6 +13,7 @@ class TokenEmbedding:
     params: ``vocab_size``, ``width``.  weights: ``weight`` [vocab, width]."""
 
     graph_safe = True
+    chain_safe = True
 
     @classmethod
     def weight_shapes(cls, params):
@@ -35,6 +36,7 @@ class OutputHead:
     parts the same tensor name.  params: ``vocab_size``, ``width``.  weights: ``weight``."""
 
     graph_safe = True
+    chain_safe = True
 
     @classmethod
     def weight_shapes(cls, params):

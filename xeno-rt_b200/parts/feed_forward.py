@@ -15,6 +15,7 @@ class SwiGLUFeedForward:
     weights: ``gate``, ``up`` [inner, width], ``down`` [width, inner]."""
 
     graph_safe = True
+    chain_safe = True
 
     @classmethod
     def weight_shapes(cls, params):

@@ -20,6 +20,9 @@ A part class may set ``graph_safe = True`` to say that its ``forward`` only laun
 in stream order whose shapes depend on nothing but the number of tokens and the context bucket (no
 reads back to the host, no data-dependent Python branches); decode steps of a model whose parts
 all say so are captured in CUDA graphs, any other model runs every step kernel by kernel.
+``chain_safe = True`` says that all device work of ``forward`` goes through the kernel functions of
+``csrc.ops`` (torch is used to allocate only): steps of few tokens of a model whose parts all say so
+queue their norms and products and run them in one persistent kernel between two attention calls.
 
 arrangement     a function ``(layer_parts, x, ctx, store, owns_cache) -> None`` that runs one layer.
 """
