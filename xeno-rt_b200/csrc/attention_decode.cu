@@ -12,113 +12,26 @@
 // (m, l, o) partials that the combine kernel merges in split order.  Nothing depends on how many
 // other tokens the launch carries, and launch shapes depend on `chunk` and the grid only, so the
 // launch can be captured in a CUDA graph and replayed for other lengths.
+#include <cuda.h>
+
 #include "attention_mma.cuh"
 
 namespace xrt {
 
 constexpr int DEC_WARPS = 4;
 
-template <int HD_MAX>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
-attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
-                        const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
-                        const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ tok_slot,
-                        const int* __restrict__ tok_pos, const int* __restrict__ block_table, int max_blocks,
-                        int n_heads, int n_kv_heads, int head_dim, float scale_log2, int window, int chunk,
-                        int n_splits, int* __restrict__ counters) {
-  constexpr int D_TILES = HD_MAX / 8;
-  extern __shared__ __align__(16) unsigned char smem[];
-  pdl_trigger();
-  pdl_wait();
-  const int split = blockIdx.x, kv_head = blockIdx.y, tok = blockIdx.z;
-  const int slot = tok_slot[tok];
-  if (slot < 0) {  // a padding row: zeros (with several splits and no counters the combine kernel writes them)
-    if (n_splits == 1 || (counters != nullptr && split == 0)) {
-      const int group = n_heads / n_kv_heads;
-      __nv_bfloat16* dst = out + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
-      for (int i = threadIdx.x; i < group * head_dim; i += blockDim.x) dst[i] = __float2bfloat16_rn(0.f);
-    }
-    return;
-  }
-  const int pos = tok_pos[tok];
-  const int len = pos + 1;
-  const int first_key = window > 0 ? max(0, len - window) : 0;
-  const int begin = max(split * chunk, (first_key / XRT_BLOCK_TOKENS) * XRT_BLOCK_TOKENS);
-  const int end = min((split + 1) * chunk, len);
-  if (begin >= end) return;  // this split holds no visible key: the combine step skips it too
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int group = n_heads / n_kv_heads;
-  const int row_bytes = tile_row_bytes(head_dim);
-  const int tile_bytes = XRT_BLOCK_TOKENS * row_bytes;
-  unsigned char* k_tiles = smem;                   // [2][64 rows]
-  unsigned char* v_tiles = smem + 2 * tile_bytes;  // [2][64 rows]
-
-  // query fragments: rows = the group's heads (rows at or beyond the group are zero)
-  uint32_t qf[D_TILES / 2][4];
-  {
-    const __nv_bfloat16* qt = q + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
-#pragma unroll
-    for (int ks = 0; ks < D_TILES / 2; ++ks) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int row = g + (e & 1) * 8, dim = ks * 16 + (e >> 1) * 8 + 2 * t;
-        qf[ks][e] = (row < group && dim < head_dim)
-                        ? *reinterpret_cast<const uint32_t*>(qt + (size_t)row * head_dim + dim) : 0u;
-      }
-    }
-  }
-
-  const int* blocks = block_table + (size_t)slot * max_blocks;
-  const size_t head_stride = (size_t)XRT_BLOCK_TOKENS * head_dim;
-  TileCopier copier;
-  copier.init(head_dim);
-  auto issue_tile = [&](int tile_index, int buffer) {
-    const int key0 = begin + tile_index * XRT_BLOCK_TOKENS;
-    const int block = blocks[key0 / XRT_BLOCK_TOKENS];
-    const size_t base = ((size_t)block * n_kv_heads + kv_head) * head_stride;
-    const int live = min(XRT_BLOCK_TOKENS, len - key0);
-    copier.copy(k_tiles + buffer * tile_bytes, k_pool + base, XRT_BLOCK_TOKENS, live);
-    copier.copy(v_tiles + buffer * tile_bytes, v_pool + base, XRT_BLOCK_TOKENS, live);
-    cp_async_commit();
-  };
-
-  SoftmaxState<D_TILES> st;
-  st.init();
-  const int key_lo[2] = {first_key, first_key};
-  const int key_hi[2] = {len, len};
-  const int n_tiles = (end - begin + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS;  // begin is a multiple of 64
-  issue_tile(0, 0);
-  for (int i = 0; i < n_tiles; ++i) {
-    if (i + 1 < n_tiles) { issue_tile(i + 1, (i + 1) & 1); cp_async_wait<1>(); }
-    else cp_async_wait<0>();
-    __syncthreads();
-    const int key_abs = begin + i * XRT_BLOCK_TOKENS + warp * 16;
-    if (key_abs < end)  // only the first and the last 16 keys a warp sees can hold a hidden key
-      attend_16_keys<D_TILES>(st, qf, k_tiles + (i & 1) * tile_bytes, v_tiles + (i & 1) * tile_bytes, warp * 16,
-                              key_abs, key_lo, key_hi, key_abs < first_key || key_abs + 16 > len, head_dim, scale_log2);
-    __syncthreads();  // the buffer is free for the tile after next
-  }
-
-  // merge the four warps: maxima first, then the rescaled sums and outputs in warp order
+// What every form of the kernel does once its four warps have left their running state in the merge
+// area [warps][16 rows] of shared memory: merge them in warp order, write the output (one split) or
+// this split's partials, and, with counters, let the block that brings the last split merge all.
+__device__ __forceinline__ void decode_finish(unsigned char* smem, __nv_bfloat16* __restrict__ out,
+                                              float* __restrict__ part_o, float* __restrict__ part_ml,
+                                              int* __restrict__ counters, int tok, int kv_head, int split,
+                                              int n_splits, int chunk, int first_key, int len, int group, int n_heads,
+                                              int n_kv_heads, int head_dim) {
   float* merge_m = reinterpret_cast<float*>(smem);                 // [warps][16]
   float* merge_l = merge_m + DEC_WARPS * 16;                       // [warps][16]
   float* merge_o = merge_l + DEC_WARPS * 16;                       // [warps][16][head_dim + 8]: rows in different banks
   const int merge_stride = head_dim + 8;
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
-    st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
-    if (t == 0) { merge_m[warp * 16 + g + r * 8] = st.m[r]; merge_l[warp * 16 + g + r * 8] = st.l[r]; }
-  }
-#pragma unroll
-  for (int dt = 0; dt < D_TILES; ++dt) {
-    if (dt * 8 < head_dim) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        merge_o[((size_t)warp * 16 + g + (e >> 1) * 8) * merge_stride + dt * 8 + 2 * t + (e & 1)] = st.o[dt][e];
-    }
-  }
   __syncthreads();
   for (int idx = threadIdx.x; idx < group * head_dim; idx += blockDim.x) {
     const int row = idx / head_dim, d = idx - row * head_dim;
@@ -201,6 +114,157 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   }
 }
 
+// BY_HEADS: the group has at most 8 query heads; they are the MMA's columns and the keys its rows
+// (half the MMAs and half the softmax work per key; see attend_16_keys_heads).  Otherwise the heads
+// (up to 16) are the rows.  Both leave the same per-warp state in shared memory for the merge.
+template <int HD_MAX, bool BY_HEADS>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+                        const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ tok_slot,
+                        const int* __restrict__ tok_pos, const int* __restrict__ block_table, int max_blocks,
+                        int n_heads, int n_kv_heads, int head_dim, float scale_log2, int window, int chunk,
+                        int n_splits, int* __restrict__ counters) {
+  constexpr int D_TILES = HD_MAX / 8;
+  extern __shared__ __align__(16) unsigned char smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int split = blockIdx.x, kv_head = blockIdx.y, tok = blockIdx.z;
+  const int slot = tok_slot[tok];
+  if (slot < 0) {  // a padding row: zeros (with several splits and no counters the combine kernel writes them)
+    if (n_splits == 1 || (counters != nullptr && split == 0)) {
+      const int group = n_heads / n_kv_heads;
+      __nv_bfloat16* dst = out + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
+      for (int i = threadIdx.x; i < group * head_dim; i += blockDim.x) dst[i] = __float2bfloat16_rn(0.f);
+    }
+    return;
+  }
+  const int pos = tok_pos[tok];
+  const int len = pos + 1;
+  const int first_key = window > 0 ? max(0, len - window) : 0;
+  const int begin = max(split * chunk, (first_key / XRT_BLOCK_TOKENS) * XRT_BLOCK_TOKENS);
+  const int end = min((split + 1) * chunk, len);
+  if (begin >= end) return;  // this split holds no visible key: the combine step skips it too
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int group = n_heads / n_kv_heads;
+  const int row_bytes = tile_row_bytes(head_dim);
+  const int tile_bytes = XRT_BLOCK_TOKENS * row_bytes;
+  unsigned char* k_tiles = smem;                   // [2][64 rows]
+  unsigned char* v_tiles = smem + 2 * tile_bytes;  // [2][64 rows]
+
+  const int* blocks = block_table + (size_t)slot * max_blocks;
+  const size_t head_stride = (size_t)XRT_BLOCK_TOKENS * head_dim;
+  TileCopier copier;
+  copier.init(head_dim);
+  auto issue_tile = [&](int tile_index, int buffer) {
+    const int key0 = begin + tile_index * XRT_BLOCK_TOKENS;
+    const int block = blocks[key0 / XRT_BLOCK_TOKENS];
+    const size_t base = ((size_t)block * n_kv_heads + kv_head) * head_stride;
+    const int live = min(XRT_BLOCK_TOKENS, len - key0);
+    copier.copy(k_tiles + buffer * tile_bytes, k_pool + base, XRT_BLOCK_TOKENS, live);
+    copier.copy(v_tiles + buffer * tile_bytes, v_pool + base, XRT_BLOCK_TOKENS, live);
+    cp_async_commit();
+  };
+
+  const int n_tiles = (end - begin + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS;  // begin is a multiple of 64
+  float* merge_m = reinterpret_cast<float*>(smem);                 // [warps][16]
+  float* merge_l = merge_m + DEC_WARPS * 16;                       // [warps][16]
+  float* merge_o = merge_l + DEC_WARPS * 16;                       // [warps][16][head_dim + 8]: rows in different banks
+  const int merge_stride = head_dim + 8;
+  const __nv_bfloat16* qt = q + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
+
+  if constexpr (BY_HEADS) {
+    // query operand: column g = head g of the group (zero at or beyond the group)
+    uint32_t qb[D_TILES / 2][2];
+#pragma unroll
+    for (int ks = 0; ks < D_TILES / 2; ++ks)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int dim = ks * 16 + e * 8 + 2 * t;
+        qb[ks][e] = (g < group && dim < head_dim) ? *reinterpret_cast<const uint32_t*>(qt + (size_t)g * head_dim + dim) : 0u;
+      }
+    HeadColumnState<D_TILES> st;
+    st.init();
+    issue_tile(0, 0);
+    for (int i = 0; i < n_tiles; ++i) {
+      if (i + 1 < n_tiles) { issue_tile(i + 1, (i + 1) & 1); cp_async_wait<1>(); }
+      else cp_async_wait<0>();
+      __syncthreads();
+      const int key_abs = begin + i * XRT_BLOCK_TOKENS + warp * 16;
+      if (key_abs < end)  // only the first and the last 16 keys a warp sees can hold a hidden key
+        attend_16_keys_heads<D_TILES>(st, qb, k_tiles + (i & 1) * tile_bytes, v_tiles + (i & 1) * tile_bytes, warp * 16,
+                                      key_abs, first_key, len, key_abs < first_key || key_abs + 16 > len, head_dim,
+                                      scale_log2);
+      __syncthreads();  // the buffer is free for the tile after next
+    }
+    // this warp's state into the merge area: row = head; the sums are spread over the lanes of a t
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 4);
+      st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 8);
+      st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 16);
+      if (g == 0) { merge_m[warp * 16 + 2 * t + h] = st.m[h]; merge_l[warp * 16 + 2 * t + h] = st.l[h]; }
+    }
+#pragma unroll
+    for (int dt = 0; dt < D_TILES / 2; ++dt) {
+      if (dt * 16 < head_dim) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          merge_o[((size_t)warp * 16 + 2 * t + (e & 1)) * merge_stride + dt * 16 + g + (e >> 1) * 8] = st.o[dt][e];
+      }
+    }
+  } else {
+    // query fragments: rows = the group's heads (rows at or beyond the group are zero)
+    uint32_t qf[D_TILES / 2][4];
+    {
+  #pragma unroll
+      for (int ks = 0; ks < D_TILES / 2; ++ks) {
+  #pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int row = g + (e & 1) * 8, dim = ks * 16 + (e >> 1) * 8 + 2 * t;
+          qf[ks][e] = (row < group && dim < head_dim)
+                          ? *reinterpret_cast<const uint32_t*>(qt + (size_t)row * head_dim + dim) : 0u;
+        }
+      }
+    }
+
+    SoftmaxState<D_TILES> st;
+    st.init();
+    const int key_lo[2] = {first_key, first_key};
+    const int key_hi[2] = {len, len};
+    issue_tile(0, 0);
+    for (int i = 0; i < n_tiles; ++i) {
+      if (i + 1 < n_tiles) { issue_tile(i + 1, (i + 1) & 1); cp_async_wait<1>(); }
+      else cp_async_wait<0>();
+      __syncthreads();
+      const int key_abs = begin + i * XRT_BLOCK_TOKENS + warp * 16;
+      if (key_abs < end)  // only the first and the last 16 keys a warp sees can hold a hidden key
+        attend_16_keys<D_TILES>(st, qf, k_tiles + (i & 1) * tile_bytes, v_tiles + (i & 1) * tile_bytes, warp * 16,
+                                key_abs, key_lo, key_hi, key_abs < first_key || key_abs + 16 > len, head_dim, scale_log2);
+      __syncthreads();  // the buffer is free for the tile after next
+    }
+
+    // merge the four warps: maxima first, then the rescaled sums and outputs in warp order
+  #pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+      st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+      if (t == 0) { merge_m[warp * 16 + g + r * 8] = st.m[r]; merge_l[warp * 16 + g + r * 8] = st.l[r]; }
+    }
+  #pragma unroll
+    for (int dt = 0; dt < D_TILES; ++dt) {
+      if (dt * 8 < head_dim) {
+  #pragma unroll
+        for (int e = 0; e < 4; ++e)
+          merge_o[((size_t)warp * 16 + g + (e >> 1) * 8) * merge_stride + dt * 8 + 2 * t + (e & 1)] = st.o[dt][e];
+      }
+    }
+  }
+  decode_finish(smem, out, part_o, part_ml, counters, tok, kv_head, split, n_splits, chunk, first_key, len, group, n_heads,
+                n_kv_heads, head_dim);
+}
+
 // One warp per (token, head): merges the splits' partials in split order.
 __global__ void attention_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
                                          const float* __restrict__ part_ml, const int* __restrict__ tok_slot,
@@ -252,15 +316,210 @@ __global__ void attention_combine_kernel(__nv_bfloat16* __restrict__ out, const 
   }
 }
 
+// The form with the heads as columns, fed by TMA: a cache block's keys and values for one kv head
+// are 64 x head_dim contiguous bfloat16, which one thread fetches with one tensor copy per 64 dims
+// (cp.async.bulk.tensor, 128-byte swizzle so that ldmatrix meets no bank conflict) instead of every
+// thread issuing 16-byte copies: the copies were more than half of the instructions of the kernel
+// above, which is bound by instruction issue.  Two buffers; the copy of tile i + 1 is issued before
+// the wait for tile i.  The wait is bounded: if it runs out the block raises the error flag, waits
+// (bounded) for its copies in flight and leaves without writing.
+constexpr int DEC_BOX_BYTES = 64 * 128;
+constexpr unsigned DEC_SPIN_LIMIT = 1u << 22;
+
+__device__ __forceinline__ bool dec_mbar_wait(uint32_t bar, uint32_t parity) {
+  for (unsigned spin = 0; spin < DEC_SPIN_LIMIT; ++spin) {
+    uint32_t done;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
 template <int HD_MAX>
-int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_bfloat16* q,
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                            const __nv_bfloat16* __restrict__ q, const int* __restrict__ tok_slot,
+                            const int* __restrict__ tok_pos, const int* __restrict__ block_table, int max_blocks,
+                            int n_heads, int n_kv_heads, int head_dim, float scale_log2, int window, int chunk,
+                            int n_splits, int* __restrict__ counters, int* __restrict__ error_flag) {
+  constexpr int D_TILES = HD_MAX / 8;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full[2];
+  pdl_trigger();
+  pdl_wait();
+  const int split = blockIdx.x, kv_head = blockIdx.y, tok = blockIdx.z;
+  const int slot = tok_slot[tok];
+  const int group = n_heads / n_kv_heads;
+  if (slot < 0) {  // a padding row: zeros (with several splits and no counters the combine kernel writes them)
+    if (n_splits == 1 || (counters != nullptr && split == 0)) {
+      __nv_bfloat16* dst = out + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
+      for (int i = threadIdx.x; i < group * head_dim; i += blockDim.x) dst[i] = __float2bfloat16_rn(0.f);
+    }
+    return;
+  }
+  const int len = tok_pos[tok] + 1;
+  const int first_key = window > 0 ? max(0, len - window) : 0;
+  const int begin = max(split * chunk, (first_key / XRT_BLOCK_TOKENS) * XRT_BLOCK_TOKENS);
+  const int end = min((split + 1) * chunk, len);
+  if (begin >= end) return;  // this split holds no visible key: the combine step skips it too
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int boxes = head_dim / 64;
+  const int tile_bytes = boxes * DEC_BOX_BYTES;
+  unsigned char* k_tiles = smem;                   // [2][boxes][64 rows x 128 bytes]
+  unsigned char* v_tiles = smem + 2 * tile_bytes;
+  const uint32_t full_addr[2] = {smem_addr(&full[0]), smem_addr(&full[1])};
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full_addr[0]));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full_addr[1]));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int* blocks = block_table + (size_t)slot * max_blocks;
+  auto issue_tile = [&](int tile_index, int buffer) {  // one thread
+    const int key0 = begin + tile_index * XRT_BLOCK_TOKENS;
+    const int row0 = (blocks[key0 / XRT_BLOCK_TOKENS] * n_kv_heads + kv_head) * XRT_BLOCK_TOKENS;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_addr[buffer]), "r"(2 * tile_bytes)
+                 : "memory");
+    for (int b = 0; b < boxes; ++b) {
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                   ::"r"(smem_addr(k_tiles + buffer * tile_bytes + b * DEC_BOX_BYTES)), "l"(&map_k), "r"(b * 64), "r"(row0),
+                     "r"(full_addr[buffer]) : "memory");
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                   ::"r"(smem_addr(v_tiles + buffer * tile_bytes + b * DEC_BOX_BYTES)), "l"(&map_v), "r"(b * 64), "r"(row0),
+                     "r"(full_addr[buffer]) : "memory");
+    }
+  };
+
+  // query operand: column g = head g of the group (zero at or beyond the group)
+  const __nv_bfloat16* qt = q + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
+  uint32_t qb[D_TILES / 2][2];
+#pragma unroll
+  for (int ks = 0; ks < D_TILES / 2; ++ks)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int dim = ks * 16 + e * 8 + 2 * t;
+      qb[ks][e] = (g < group && dim < head_dim) ? *reinterpret_cast<const uint32_t*>(qt + (size_t)g * head_dim + dim) : 0u;
+    }
+  HeadColumnState<D_TILES> st;
+  st.init();
+  const int n_tiles = (end - begin + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS;  // begin is a multiple of 64
+  if (threadIdx.x == 0) issue_tile(0, 0);
+  int failed = 0, i = 0;
+  for (; i < n_tiles; ++i) {
+    // the buffer of tile i + 1 held tile i - 1, which every warp left before the barrier that ended the last round
+    if (threadIdx.x == 0 && i + 1 < n_tiles) issue_tile(i + 1, (i + 1) & 1);
+    if (!dec_mbar_wait(full_addr[i & 1], (uint32_t)(i >> 1) & 1u)) failed = 1;
+    const int key_abs = begin + i * XRT_BLOCK_TOKENS + warp * 16;
+    if (!failed && key_abs < end)  // only the first and the last 16 keys a warp sees can hold a hidden key
+      attend_16_keys_heads<D_TILES, true>(st, qb, k_tiles + (i & 1) * tile_bytes, v_tiles + (i & 1) * tile_bytes,
+                                          warp * 16, key_abs, first_key, len,
+                                          key_abs < first_key || key_abs + 16 > len, head_dim, scale_log2);
+    if (__syncthreads_or(failed)) { failed = 1; break; }
+  }
+  if (failed) {
+    if (threadIdx.x == 0) {
+      if (error_flag != nullptr) atomicCAS(error_flag, 0, 6);
+      // copies in flight write this block's shared memory: they must have landed before it is given back
+      dec_mbar_wait(full_addr[i & 1], (uint32_t)(i >> 1) & 1u);
+      if (i + 1 < n_tiles) dec_mbar_wait(full_addr[(i + 1) & 1], (uint32_t)((i + 1) >> 1) & 1u);
+    }
+    __syncthreads();
+    return;
+  }
+
+  // this warp's state into the merge area: row = head; the sums are spread over the lanes of a t
+  float* merge_m = reinterpret_cast<float*>(smem);
+  float* merge_l = merge_m + DEC_WARPS * 16;
+  float* merge_o = merge_l + DEC_WARPS * 16;
+  const int merge_stride = head_dim + 8;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 4);
+    st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 8);
+    st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 16);
+    if (g == 0) { merge_m[warp * 16 + 2 * t + h] = st.m[h]; merge_l[warp * 16 + 2 * t + h] = st.l[h]; }
+  }
+#pragma unroll
+  for (int dt = 0; dt < D_TILES / 2; ++dt) {
+    if (dt * 16 < head_dim) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        merge_o[((size_t)warp * 16 + 2 * t + (e & 1)) * merge_stride + dt * 16 + g + (e >> 1) * 8] = st.o[dt][e];
+    }
+  }
+  decode_finish(smem, out, part_o, part_ml, counters, tok, kv_head, split, n_splits, chunk, first_key, len, group, n_heads,
+                n_kv_heads, head_dim);
+}
+
+typedef CUresult (*DecEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static DecEncodeFn dec_encode() {
+  static DecEncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<DecEncodeFn>(ptr);
+  }
+  return fn;
+}
+
+// A map over a cache pool seen as a row-major bfloat16 matrix [blocks * kv heads * 64, head_dim]:
+// boxes of 64 rows x 64 dims, 128-byte swizzle.
+static bool dec_make_map(CUtensorMap* map, const void* base, long long rows, int head_dim) {
+  DecEncodeFn encode = dec_encode();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
+  const cuuint32_t box[2] = {64u, 64u};
+  const cuuint32_t elem[2] = {1u, 1u};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int HD_MAX>
+int launch_decode_tma(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_bfloat16* q,
+                      const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, long long pool_rows, const int* tok_slot,
+                      const int* tok_pos, const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
+                      int head_dim, float scale, int window, int chunk, int n_splits, int* counters, int* error_flag,
+                      cudaStream_t stream) {
+  CUtensorMap map_k, map_v;
+  if (!dec_make_map(&map_k, k_pool, pool_rows, head_dim) || !dec_make_map(&map_v, v_pool, pool_rows, head_dim))
+    return XRT_ERR_UNSUPPORTED;
+  const int merge_bytes = DEC_WARPS * 16 * (2 + head_dim + 8) * (int)sizeof(float);
+  const int smem = 1024 + max(4 * (head_dim / 64) * DEC_BOX_BYTES, merge_bytes);
+  auto kernel = attention_decode_tma_kernel<HD_MAX>;
+  static int smem_allowed = 0;  // raised once a size class; not a stream operation
+  if (smem > 48 * 1024 && smem > smem_allowed) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return (int)err;
+    smem_allowed = smem;
+  }
+  dim3 grid(n_splits, n_kv_heads, n_tokens);
+  launch_kernel(kernel, grid, dim3(DEC_WARPS * 32), (size_t)smem, stream, map_k, map_v, out, part_o, part_ml, q, tok_slot,
+                tok_pos, block_table, max_blocks, n_heads, n_kv_heads, head_dim, scale * 1.4426950408889634f, window,
+                chunk, n_splits, counters, error_flag);
+  return launch_status();
+}
+
+template <int HD_MAX, bool BY_HEADS>
+int launch_decode_as(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_bfloat16* q,
                   const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, const int* tok_slot, const int* tok_pos,
                   const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                   float scale, int window, int chunk, int n_splits, int* counters, cudaStream_t stream) {
   const int tile_bytes = XRT_BLOCK_TOKENS * (head_dim * 2 + 16);
   const int merge_bytes = DEC_WARPS * 16 * (2 + head_dim + 8) * (int)sizeof(float);
   const int smem = max(4 * tile_bytes, merge_bytes);
-  auto kernel = attention_decode_kernel<HD_MAX>;
+  auto kernel = attention_decode_kernel<HD_MAX, BY_HEADS>;
   static int smem_allowed = 0;  // raised once a size class; not a stream operation
   if (smem > 48 * 1024 && smem > smem_allowed) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -274,6 +533,36 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_
   return launch_status();
 }
 
+// Groups of at most 8 query heads take the form with the heads as the MMA's columns, fed by TMA when
+// the head size is a multiple of 64 and the caller says how many blocks the pools hold.
+// XRT_DECODE_ATTN in the environment, for comparison: "rows" keeps the heads-as-rows form everywhere,
+// "cp" keeps the 16-byte asynchronous copies.
+template <int HD_MAX>
+int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_bfloat16* q,
+                  const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, long long pool_rows, const int* tok_slot,
+                  const int* tok_pos, const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
+                  int head_dim, float scale, int window, int chunk, int n_splits, int* counters, int* error_flag,
+                  cudaStream_t stream) {
+  static int rows_only = -1, copies_only = 0;
+  if (rows_only < 0) {
+    const char* env = getenv("XRT_DECODE_ATTN");
+    rows_only = (env != nullptr && env[0] == 'r') ? 1 : 0;
+    copies_only = (env != nullptr && env[0] == 'c') ? 1 : 0;
+  }
+  if (n_heads / n_kv_heads <= 8 && !rows_only && !copies_only && pool_rows > 0 && head_dim % 64 == 0 &&
+      (((uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0)
+    return launch_decode_tma<HD_MAX>(out, part_o, part_ml, q, k_pool, v_pool, pool_rows, tok_slot, tok_pos, block_table,
+                                     max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
+                                     counters, error_flag, stream);
+  if (n_heads / n_kv_heads <= 8 && !rows_only)
+    return launch_decode_as<HD_MAX, true>(out, part_o, part_ml, q, k_pool, v_pool, tok_slot, tok_pos, block_table,
+                                          max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk,
+                                          n_splits, counters, stream);
+  return launch_decode_as<HD_MAX, false>(out, part_o, part_ml, q, k_pool, v_pool, tok_slot, tok_pos, block_table,
+                                         max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk,
+                                         n_splits, counters, stream);
+}
+
 }  // namespace xrt
 
 namespace xrt {
@@ -282,9 +571,10 @@ namespace xrt {
 // (token, kv head) combines, and `counters` (int32 [n_tokens * n_kv_heads], zero before the call)
 // is left zero.
 static int attention_decode_impl(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
-                                 const void* v_pool, const int* tok_slot, const int* tok_pos, const int* block_table,
-                                 int max_blocks, int n_tokens, int n_heads, int n_kv_heads, int head_dim, float scale,
-                                 int window, int chunk, int n_splits, int* counters, cudaStream_t stream) {
+                                 const void* v_pool, int n_blocks, const int* tok_slot, const int* tok_pos,
+                                 const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
+                                 int head_dim, float scale, int window, int chunk, int n_splits, int* counters,
+                                 int* error_flag, cudaStream_t stream) {
   if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || chunk <= 0 || n_splits <= 0)
     return XRT_ERR_ARGUMENT;
   if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256 || n_heads / n_kv_heads > 16 ||
@@ -297,9 +587,10 @@ static int attention_decode_impl(void* out, float* part_o, float* part_ml, const
   auto* kp = (const __nv_bfloat16*)k_pool;
   auto* vp = (const __nv_bfloat16*)v_pool;
   int status;
-#define XRT_DECODE(HD) status = launch_decode<HD>(o, part_o, part_ml, qp, kp, vp, tok_slot, tok_pos, block_table,      \
-                                                  max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, \
-                                                  chunk, n_splits, counters, stream)
+  const long long pool_rows = (long long)n_blocks * n_kv_heads * XRT_BLOCK_TOKENS;  // 0: the pools' size is not known
+#define XRT_DECODE(HD) status = launch_decode<HD>(o, part_o, part_ml, qp, kp, vp, pool_rows, tok_slot, tok_pos, block_table, \
+                                                  max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window,      \
+                                                  chunk, n_splits, counters, error_flag, stream)
   if (head_dim <= 32) XRT_DECODE(32);
   else if (head_dim <= 64) XRT_DECODE(64);
   else if (head_dim <= 128) XRT_DECODE(128);
@@ -323,29 +614,31 @@ static int attention_decode_impl(void* out, float* part_o, float* part_ml, const
 // cover the longest sequence the launch may meet.  part_o: float32 [n_tokens * n_heads * n_splits *
 // head_dim] and part_ml: float32 [n_tokens * n_heads * n_splits * 2] are scratch, needed when
 // n_splits > 1.  The group n_heads / n_kv_heads is at most 16; n_tokens at most 65535.
+// n_blocks: blocks in each pool (0 if unknown: the kernels fed by TMA are then not used); error_flag
+// (may be null): raised if a bounded wait on a copy ran out.
 // This entry point merges the splits with a second kernel.
 XRT_EXPORT int xrt_attention_decode(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
-                                    const void* v_pool, const int* tok_slot, const int* tok_pos,
+                                    const void* v_pool, int n_blocks, const int* tok_slot, const int* tok_pos,
                                     const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
-                                    int head_dim, float scale, int window, int chunk, int n_splits,
+                                    int head_dim, float scale, int window, int chunk, int n_splits, int* error_flag,
                                     cudaStream_t stream) {
-  return xrt::attention_decode_impl(out, part_o, part_ml, q, k_pool, v_pool, tok_slot, tok_pos, block_table, max_blocks,
-                                    n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits, nullptr,
-                                    stream);
+  return xrt::attention_decode_impl(out, part_o, part_ml, q, k_pool, v_pool, n_blocks, tok_slot, tok_pos, block_table,
+                                    max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
+                                    nullptr, error_flag, stream);
 }
 
 // The same, with the merge done by the block that brings a (token, kv head)'s last split: one
 // launch instead of two.  counters: int32 [at least n_tokens * n_kv_heads], zero before the first
 // call (the kernel leaves them zero).
 XRT_EXPORT int xrt_attention_decode_fused(void* out, float* part_o, float* part_ml, int* counters, const void* q,
-                                          const void* k_pool, const void* v_pool, const int* tok_slot,
+                                          const void* k_pool, const void* v_pool, int n_blocks, const int* tok_slot,
                                           const int* tok_pos, const int* block_table, int max_blocks, int n_tokens,
                                           int n_heads, int n_kv_heads, int head_dim, float scale, int window, int chunk,
-                                          int n_splits, cudaStream_t stream) {
+                                          int n_splits, int* error_flag, cudaStream_t stream) {
   if (counters == nullptr) return XRT_ERR_ARGUMENT;
-  return xrt::attention_decode_impl(out, part_o, part_ml, q, k_pool, v_pool, tok_slot, tok_pos, block_table, max_blocks,
-                                    n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits, counters,
-                                    stream);
+  return xrt::attention_decode_impl(out, part_o, part_ml, q, k_pool, v_pool, n_blocks, tok_slot, tok_pos, block_table,
+                                    max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
+                                    counters, error_flag, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -414,9 +707,10 @@ int xrt_attention_decode_static(void* out, const void* q, const void* k_pool, co
     xrt::decode_static_scratch_address[device] = address;
   }
   float* scratch = xrt::decode_static_scratch_address[device];
-  const int status = xrt_attention_decode(out, scratch + ml_floats, scratch, q, k_pool, v_pool, tok_slot, tok_pos,
+  // the pools' size is not among this entry's arguments: 0 keeps it on the kernels that need no tensor map
+  const int status = xrt_attention_decode(out, scratch + ml_floats, scratch, q, k_pool, v_pool, 0, tok_slot, tok_pos,
                                           block_table, max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale,
-                                          window, chunk, n_splits, stream);
+                                          window, chunk, n_splits, nullptr, stream);
   if (status == XRT_ERR_ARGUMENT) xrt::refuse(message, message_len, "xrt_attention_decode_static: the kernel refused its arguments");
   if (status == XRT_ERR_UNSUPPORTED)
     xrt::refuse(message, message_len, "xrt_attention_decode_static: head_dim must be a multiple of 16 up to 256, at most "

@@ -273,4 +273,131 @@ __device__ __forceinline__ void attend_keys(SoftmaxState<D_TILES>& st, const uin
   }
 }
 
+// ---- the same update with the roles swapped (decode) ------------------------------------------------
+// One new token a sequence has only its group's query heads as rows: 4 or 8 of the MMA's 16.  With
+// the KEYS as the MMA's 16 rows and the heads as its 8 columns nothing but columns beyond the group
+// is padding, the scores of 16 keys cost half the MMAs, and a thread holds 4 scores instead of 8:
+//   S^T[key][head] = sum_d K[key][d] Q[head][d]      A = K rows (ldmatrix), B = Q from registers
+//   O^T[dim][head] += sum_key V[key][dim] P[key][head]   A = V^T (ldmatrix.trans), B = P, brought from
+//                                                     the accumulator layout by two 8x8 transposes
+// Lane (g, t) holds heads 2t and 2t + 1: their running maxima (equal in all lanes of a t), its share
+// of their sums, and for every 16 dims the outputs (dim g, dim g + 8) x (head 2t, head 2t + 1).
+
+__device__ __forceinline__ float fast_exp2(float x) {  // 2^x for x <= 0; -inf gives 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint32_t transpose_8x8(uint32_t fragment) {
+  uint32_t out;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(out) : "r"(fragment));
+  return out;
+}
+
+template <int D_TILES>
+struct HeadColumnState {
+  float m[2];
+  float l[2];
+  float o[D_TILES / 2][4];
+  __device__ __forceinline__ void init() {
+    m[0] = m[1] = -INFINITY;
+    l[0] = l[1] = 0.f;
+#pragma unroll
+    for (int i = 0; i < D_TILES / 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+  }
+};
+
+// qb[ks] = the two 32-bit words Q[head g][ks * 16 + 2t ..] and Q[head g][ks * 16 + 8 + 2t ..]
+// (zero for g at or beyond the group).  Keys outside [key_lo, key_hi) are masked.
+// SWIZZLED: the tiles were written by TMA with the 128-byte swizzle: boxes of 64 rows x 64 dims
+// (8 KB each, the boxes of a tile one after another), the 16-byte piece c of row r stored at piece
+// c ^ (r % 8).  Such a tile holds the whole cache block, also rows beyond the sequence, which may be
+// anything: masked keys' values are cleared in the registers (0 x NaN would poison the sum).
+template <int D_TILES, bool SWIZZLED = false>
+__device__ __forceinline__ void attend_16_keys_heads(HeadColumnState<D_TILES>& st, const uint32_t (*qb)[2],
+                                                     const unsigned char* ks_tile, const unsigned char* vs_tile,
+                                                     int key_row, int key_abs, int key_lo, int key_hi, bool masked,
+                                                     int head_dim, float scale_log2) {
+  const int lane = threadIdx.x & 31, g = lane >> 2;
+  const int row_bytes = tile_row_bytes(head_dim);
+  float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // two chains of dependent MMAs
+  // K as the A operand: matrix j of an x4 load = keys (j % 2) * 8 .., dims ks * 16 + (j / 2) * 8 ..
+  const uint32_t k_base = SWIZZLED ? smem_addr(ks_tile + (key_row + (lane & 15)) * 128)
+                                   : smem_addr(ks_tile + (key_row + (lane & 15)) * row_bytes + (lane >> 4) * 16);
+  const uint32_t k_piece = (uint32_t)((lane >> 4) ^ (lane & 7));  // this lane's piece of a step, before the step's own bits
+#pragma unroll
+  for (int ks = 0; ks < D_TILES / 2; ++ks) {
+    if (ks * 16 < head_dim) {
+      uint32_t kf[4];
+      if (SWIZZLED) ldmatrix_x4(kf, k_base + (ks >> 2) * 8192 + ((k_piece ^ ((2 * ks) & 7)) << 4));
+      else ldmatrix_x4(kf, k_base + ks * 32);
+      mma_16816(s[ks & 1], kf, qb[ks][0], qb[ks][1]);
+    }
+  }
+  // c0, c1: key g x heads 2t, 2t+1; c2, c3: key g + 8
+  float v[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    bool live = true;
+    if (masked) {  // uniform over the warp: only the 16 keys at an edge of the range pay for the comparisons
+      const int key = key_abs + g + (e >> 1) * 8;
+      live = key >= key_lo && key < key_hi;
+    }
+    v[e] = live ? (s[0][e] + s[1][e]) * scale_log2 : -INFINITY;
+  }
+  float corr[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float tile_max = fmaxf(v[h], v[h + 2]);
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
+    const float m_new = fmaxf(st.m[h], tile_max);
+    // a head with no live key so far keeps m = -inf; 2^(-inf - -inf) must not be NaN
+    corr[h] = m_new == -INFINITY ? 1.f : fast_exp2(st.m[h] - m_new);
+    st.m[h] = m_new;
+    const float base = m_new == -INFINITY ? 0.f : m_new;  // then every score is -inf and every weight 0
+    v[h] = fast_exp2(v[h] - base);
+    v[h + 2] = fast_exp2(v[h + 2] - base);
+    st.l[h] = st.l[h] * corr[h] + (v[h] + v[h + 2]);
+  }
+  const bool rescale = __any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f);
+  const uint32_t p_lo = transpose_8x8(pack_bf16(v[0], v[1]));  // keys 2t, 2t+1 of head g
+  const uint32_t p_hi = transpose_8x8(pack_bf16(v[2], v[3]));  // keys 2t+8, 2t+9
+  // V^T as the A operand (transposed load): matrix j = keys (j / 2) * 8 .., dims dt * 16 + (j % 2) * 8 ..
+  const int j = lane >> 3, r = lane & 7;
+  const uint32_t v_base = SWIZZLED ? smem_addr(vs_tile + (key_row + (j >> 1) * 8 + r) * 128)
+                                   : smem_addr(vs_tile + (key_row + (j >> 1) * 8 + r) * row_bytes + (j & 1) * 16);
+  const uint32_t v_piece = (uint32_t)((j & 1) ^ r);
+  uint32_t keep_lo = 0xffffffffu, keep_hi = 0xffffffffu;  // values of keys 2t, 2t+1 and of keys 2t+8, 2t+9
+  if (SWIZZLED && masked) {
+    const int t = lane & 3;
+    auto live = [&](int key) { return key >= key_lo && key < key_hi; };
+    keep_lo = (live(key_abs + 2 * t) ? 0x0000ffffu : 0u) | (live(key_abs + 2 * t + 1) ? 0xffff0000u : 0u);
+    keep_hi = (live(key_abs + 2 * t + 8) ? 0x0000ffffu : 0u) | (live(key_abs + 2 * t + 9) ? 0xffff0000u : 0u);
+  }
+#pragma unroll
+  for (int dt = 0; dt < D_TILES / 2; ++dt) {
+    if (dt * 16 < head_dim) {
+      uint32_t vf[4];
+      if (SWIZZLED) {
+        ldmatrix_x4_trans(vf, v_base + (dt >> 2) * 8192 + ((v_piece ^ ((2 * dt) & 7)) << 4));
+        if (masked) { vf[0] &= keep_lo; vf[1] &= keep_lo; vf[2] &= keep_hi; vf[3] &= keep_hi; }
+      } else {
+        ldmatrix_x4_trans(vf, v_base + dt * 32);
+      }
+      if (rescale) {
+        st.o[dt][0] *= corr[0];
+        st.o[dt][1] *= corr[1];
+        st.o[dt][2] *= corr[0];
+        st.o[dt][3] *= corr[1];
+      }
+      mma_16816(st.o[dt], vf, p_lo, p_hi);
+    }
+  }
+}
+
 }  // namespace xrt

@@ -12,17 +12,26 @@ DECODE_BLOCKS_PER_SM = 3   # 70 KB of shared memory a block at head size 128
 TCGEN05_MIN_NEW = 32       # prompts at least this long use the tcgen05 attention (tiles of 128 query rows)
 PREFILL_KERNEL = os.environ.get("XRT_PREFILL_ATTN", "")  # "mma" forces the mma.sync kernel, for comparison
 FUSED_COMBINE_MAX = 32     # (tokens x kv heads) up to which the splits are merged inside the attention kernel
-DECODE_WAVES = 2           # blocks wanted = what the GPU holds at once, times this (measured: 1 leaves a long tail
-#                            at 64 sequences, 4 costs more in partials at 8)
+SPLIT_OVERHEAD_TILES = 2   # what a block costs beside its tiles (query load, merge, partials), in tiles of 64 keys
 
 
 def decode_split(n_seqs: int, n_kv_heads: int, max_context: int):
-    """(keys a split, number of splits) for decode attention: enough thread blocks to fill the GPU
-    when sequences are few, at least two tiles of 64 keys a split where the context allows."""
+    """(keys a split, number of splits) for decode attention.  Blocks run in rounds of what the GPU
+    holds at once; the time is about rounds x (tiles a split + a fixed cost), so the split count is
+    chosen to fill the last round (512 pairs of sequence and kv head in 2 splits are 2.3 rounds and
+    run like 3; in 6 splits they are 6.9 rounds of a third the length).  At least two tiles a split
+    where the context allows."""
     blocks = max(1, (max_context + 63) // 64)
-    want = -(-SM_COUNT * DECODE_BLOCKS_PER_SM * DECODE_WAVES // (n_seqs * n_kv_heads))
-    splits = max(1, min(want, (blocks + 1) // 2))
-    chunk = 64 * (-(-blocks // splits))
+    pairs = max(1, n_seqs * n_kv_heads)
+    slots = SM_COUNT * DECODE_BLOCKS_PER_SM
+    best, best_cost = 1, None
+    for splits in range(1, max(1, min((blocks + 1) // 2, 64)) + 1):
+        tiles = -(-blocks // splits)
+        rounds = -(-pairs * (-(-blocks // tiles)) // slots)
+        cost = rounds * (tiles + SPLIT_OVERHEAD_TILES)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = splits, cost
+    chunk = 64 * (-(-blocks // best))
     return chunk, -(-blocks * 64 // chunk)
 
 
