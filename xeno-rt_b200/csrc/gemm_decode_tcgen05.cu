@@ -232,6 +232,14 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
           if (MODE == 2) dg_ld16(u, tmem_row + shape.nb + c);
           dg_wait_ld();
           if (n < shape.N) {
+            // the residual values first, all sixteen loads in flight (a load may not pass a store that
+            // could alias it: read-modify-write one value at a time would wait for each in turn)
+            float old[16];
+            if (MODE == 1) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                old[j] = c + j < shape.M ? __ldcg(reinterpret_cast<const float*>(out) + (size_t)(c + j) * shape.ldo + n) : 0.f;
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int m = c + j;
@@ -239,7 +247,7 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 float val = __uint_as_float(v[j]);
                 if (MODE == 2) val = (val / (1.0f + expf(-val))) * __uint_as_float(u[j]);
                 TO* dst = out + (size_t)m * shape.ldo + n;
-                if (MODE == 1) *dst = from_float<TO>(to_float(*dst) + val);
+                if (MODE == 1) *dst = from_float<TO>(old[j] + val);
                 else *dst = from_float<TO>(val);
               }
             }
@@ -303,13 +311,19 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                   sums[gr][4 * q] = t.x; sums[gr][4 * q + 1] = t.y; sums[gr][4 * q + 2] = t.z; sums[gr][4 * q + 3] = t.w;
                 }
               }
+              float old[16];
+              if (MODE == 1) {  // all sixteen residual loads in flight before the first store
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  old[j] = m0 + j < shape.M ? __ldcg(reinterpret_cast<const float*>(out) + (size_t)(m0 + j) * shape.ldo + n) : 0.f;
+              }
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 if (m0 + j < shape.M) {
                   float val = sums[0][j];
                   if (MODE == 2) val = (val / (1.0f + expf(-val))) * sums[GROUPS - 1][j];
                   TO* dst = out + (size_t)(m0 + j) * shape.ldo + n;
-                  if (MODE == 1) *dst = from_float<TO>(to_float(*dst) + val);
+                  if (MODE == 1) *dst = from_float<TO>(old[j] + val);
                   else *dst = from_float<TO>(val);
                 }
               }
@@ -374,7 +388,9 @@ static int choose_splits(int tiles, int k_iters, int sms, int groups, int nb) {
     const long long items = (long long)tiles * s;
     const long long rounds = (items + sms - 1) / sms;
     const double busy = (double)items / (double)(rounds * sms);
-    const double partial_bytes = s > 1 ? 2.0 * s * groups * nb * DG_ROWS * 4 : 0.0;
+    // a split item also pays for its fence, counter and barriers, and its epilogue cannot hide behind
+    // the next item's few slabs: measured about 10 microseconds an item, the time of 450 KB of weights
+    const double partial_bytes = s > 1 ? 2.0 * s * groups * nb * DG_ROWS * 4 + s * 450.0 * 1024 : 0.0;
     const double cost = (weight_bytes + partial_bytes) / busy;
     if (s == 1 || cost < best_cost * 0.98) { best_cost = cost; best = s; }
   }

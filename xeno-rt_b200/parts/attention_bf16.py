@@ -11,7 +11,7 @@ SM_COUNT = 148
 DECODE_BLOCKS_PER_SM = 3   # 70 KB of shared memory a block at head size 128
 TCGEN05_MIN_NEW = 32       # prompts at least this long use the tcgen05 attention (tiles of 128 query rows)
 PREFILL_KERNEL = os.environ.get("XRT_PREFILL_ATTN", "")  # "mma" forces the mma.sync kernel, for comparison
-FUSED_COMBINE_MAX = 32     # (tokens x kv heads) up to which the splits are merged inside the attention kernel
+FUSED_COMBINE_MAX = 32     # (tokens x kv heads) up to which the splits are merged inside the attention kernel (measured again with 6 splits at 8 sequences: the second kernel is still faster there)
 SPLIT_OVERHEAD_TILES = 2   # what a block costs beside its tiles (query load, merge, partials), in tiles of 64 keys
 
 

@@ -14,7 +14,6 @@ from ..csrc import ops
 
 FORCE = os.environ.get("XRT_DECODE_GEMM", "")
 STREAM_ROWS = 16
-SMALL_WEIGHT = 20 * 1024 * 1024  # elements: 40 MB of bfloat16
 
 
 def aligned(x, weight) -> bool:
@@ -26,8 +25,6 @@ def aligned(x, weight) -> bool:
 def _product(out, x, weight, mode: str, up_rows: int = 0) -> None:
     rows = x.shape[0]
     stream_rows = ops.STREAM_MAX_ROWS if FORCE == "stream" else (0 if FORCE == "tcgen05" else STREAM_ROWS)
-    if not FORCE and rows <= ops.STREAM_MAX_ROWS and weight.numel() <= SMALL_WEIGHT:
-        stream_rows = ops.STREAM_MAX_ROWS  # a small weight would be split over K: the streaming kernel's fixed cost is lower
     if rows <= stream_rows:
         ops.gemm_stream(out, x, weight, mode, up_rows)
     elif rows <= ops.DECODE_TCGEN05_MAX_ROWS:
