@@ -134,3 +134,51 @@ def test_on_token_and_request_defaults():
     backend = ScriptedBackend({1: [5, 6, 7]})
     generate(backend, [req(1, 2, max_tokens=3)], 100, 64, on_token=lambda i, t: seen.append((i, t)))
     assert seen == [(0, 5), (0, 6), (0, 7)]
+
+
+class PipelinedBackend(ScriptedBackend):
+    """The same scripts through the calls of a backend that starts the next step before the ids
+    reach the host.  'Device ids' are a list the host side of the test never looks at before
+    ``sample_end``; a step fed by them records which rows it ran."""
+
+    def sample_begin(self, logits, slots, requests):
+        return {"ids": ScriptedBackend.sample(self, logits, slots, requests), "slots": list(slots)}
+
+    def sample_end(self, pending):
+        return list(pending["ids"])
+
+    def forward_sampled(self, slots, pending):
+        assert list(slots) == pending["slots"]  # the rows line up with the sampler's rows
+        self.calls.append(("forward_sampled", list(slots), [[t] for t in pending["ids"]]))
+        for s in slots:
+            self.open[s]["fed"] += 1
+        return list(slots)
+
+    def rows(self, logits, rows):
+        self.calls.append(("rows", list(rows)))
+        return [logits[r] for r in rows]
+
+
+@pytest.mark.parametrize("scripts,limits", [
+    ({1: [10, 11, 99], 2: [20, 99], 3: [30, 31, 32, 33, 34]}, (8, 8, 4)),
+    ({1: [10, 11, 12, 13], 2: [20, 21, 22, 23], 3: [30, 31, 32, 33]}, (3, 3, 3)),
+    ({1: [99], 2: [20, 21, 99], 3: [30, 99]}, (5, 5, 5)),
+])
+def test_pipelined_backend_same_results(scripts, limits):
+    """Starting the next step early changes no result and no finish reason; a sequence that ends on
+    a stop token has run one step too many, and its row is dropped from that step's logits."""
+    def run(backend):
+        requests = [req(f, 4 + f, max_tokens=m) for f, m in zip((1, 2, 3), limits)]
+        results, stats = generate(backend, requests, vocab_size=100, context_length=64, default_stop_ids=(99,))
+        assert not backend.open  # every slot given back
+        assert sorted(backend.closed) == sorted(set(backend.closed))
+        return [(r.tokens, r.finish_reason) for r in results], stats
+    plain, plain_stats = run(ScriptedBackend(scripts))
+    piped_backend = PipelinedBackend(scripts)
+    piped, piped_stats = run(piped_backend)
+    assert piped == plain
+    assert piped_stats.tokens == plain_stats.tokens and piped_stats.decode_steps == plain_stats.decode_steps
+    kinds = [c[0] for c in piped_backend.calls]
+    assert kinds[0] == "forward"
+    if limits == (3, 3, 3):  # nobody stops: every decode step was started early except none at the token limit
+        assert kinds.count("forward") == 1 and kinds.count("forward_sampled") == 2 and "rows" not in kinds

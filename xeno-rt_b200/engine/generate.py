@@ -84,6 +84,12 @@ class SequenceProgress:
     def finished(self) -> bool:
         return self.finish_reason is not None
 
+    def goes_on_unless_stopped(self) -> bool:
+        """Whether the token that is being sampled now will be fed to another step unless it is a stop
+        token: what can be said before the token is known."""
+        return (not self.finished and self.length < self.context_length
+                and len(self.generated) + 1 < self.request.max_tokens)
+
     def accept(self, token: int) -> bool:
         """Takes the token sampled from the current logits.  Returns True if the token is kept
         and must be fed to the next step, False if the sequence has ended."""
@@ -142,7 +148,14 @@ def plan_batches(requests, context_length: int, capacity_tokens: int, max_batch:
 def generate(backend, requests, vocab_size: int, context_length: int, default_stop_ids=(),
              capacity_tokens: int | None = None, max_batch: int = 64, on_token=None):
     """Runs every request to its end, batch after batch.  Returns (results in request order,
-    GenerateStats).  ``on_token(request index, token)`` is called for each kept token."""
+    GenerateStats).  ``on_token(request index, token)`` is called for each kept token.
+
+    A backend may offer ``sample_begin`` / ``sample_end`` / ``forward_sampled`` / ``rows``: then the
+    next step is started before this step's ids have reached the host (the ids go from the sampler
+    to the step on the device), whenever no sequence is about to end for a reason known in advance
+    (token limit, context).  A sequence that then ends on a stop token has run one step for nothing;
+    the rows of the others are what they would have been.  Decisions and results are the same
+    either way."""
     for r in requests:
         validate_request(r, vocab_size, context_length)
     capacity = capacity_tokens if capacity_tokens is not None else sum(
@@ -162,13 +175,21 @@ def generate(backend, requests, vocab_size: int, context_length: int, default_st
                 t0 = time.perf_counter()
                 logits = backend.forward([slots[i] for i in live], [list(requests[i].prompt_ids) for i in live])
                 first = True
+                pipelined = hasattr(backend, "sample_begin")
                 while live:
-                    sampled = backend.sample(logits, [slots[i] for i in live], [requests[i] for i in live])
+                    ahead = None
+                    if pipelined:
+                        pending = backend.sample_begin(logits, [slots[i] for i in live], [requests[i] for i in live])
+                        if all(progress[i].goes_on_unless_stopped() for i in live):
+                            ahead = backend.forward_sampled([slots[i] for i in live], pending)
+                        sampled = backend.sample_end(pending)
+                    else:
+                        sampled = backend.sample(logits, [slots[i] for i in live], [requests[i] for i in live])
                     if first:
                         stats.prefill_seconds += time.perf_counter() - t0
                         first = False
-                    feed = []
-                    for i, token in zip(live, sampled):
+                    feed, kept_rows = [], []
+                    for row, (i, token) in enumerate(zip(live, sampled)):
                         n_before = len(progress[i].generated)
                         keep = progress[i].accept(int(token))
                         if len(progress[i].generated) > n_before:
@@ -179,11 +200,16 @@ def generate(backend, requests, vocab_size: int, context_length: int, default_st
                                 on_token(i, int(token))
                         if keep:
                             feed.append((i, int(token)))
+                            kept_rows.append(row)
                         else:
                             backend.close_slot(slots.pop(i))
+                    n_before = len(live)
                     live = [i for i, _ in feed]
                     if live:
-                        logits = backend.forward([slots[i] for i in live], [[t] for _, t in feed])
+                        if ahead is None:
+                            logits = backend.forward([slots[i] for i in live], [[t] for _, t in feed])
+                        else:  # the step is running already; rows of sequences that stopped are dropped
+                            logits = ahead if len(live) == n_before else backend.rows(ahead, kept_rows)
                         stats.decode_steps += 1
         finally:
             for slot in slots.values():

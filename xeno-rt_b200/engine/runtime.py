@@ -23,6 +23,9 @@ class DeviceBackend:
     def __init__(self, engine: Engine):
         self.engine = engine
         self.sampler = Sampler(engine.cache, engine.model.vocab_size)
+        self.track_seen = True
+        self._host = None  # pinned: the step's ids and the error flag
+        self._explicit_slots = False
 
     def open_slot(self) -> int:
         return self.engine.open_slot()
@@ -32,20 +35,66 @@ class DeviceBackend:
 
     def begin(self, slots, requests) -> None:
         self.sampler.begin(slots, [r.seed if r.seed is not None else fresh_seed() for r in requests])
+        # the history of seen ids is only read by the repetition penalty
+        self.track_seen = any(r.repetition_penalty != 1.0 for r in requests)
 
     def forward(self, slots, token_lists):
         logits = self.engine.step([StepEntry(s, t, [len(t) - 1]) for s, t in zip(slots, token_lists)])
-        ctx = self.engine.last_context
-        self.sampler.observe(ctx.tok_slot, ctx.token_ids)
+        if self.track_seen:
+            ctx = self.engine.last_context
+            self.sampler.observe(ctx.tok_slot, ctx.token_ids)
         return logits
 
-    def sample(self, logits, slots, requests) -> list:
+    def sample_begin(self, logits, slots, requests):
+        """Launches the sampling of one id a sequence and the copy of the ids (with the device's error
+        flag) to pinned host memory.  Nothing here waits for the device: the slots of the rows are the
+        step's own device array, the options are cached on the device while they stay the same."""
         n = len(slots)
-        row_slot = torch.tensor(slots, dtype=torch.int32, device=self.engine.model.device)
+        device = self.engine.model.device
+        if self._explicit_slots:
+            row_slot = torch.tensor(slots, dtype=torch.int32, device=device)
+            self._explicit_slots = False
+        else:
+            row_slot = self.engine.last_context.seq_slot[:n]
         ids = self.sampler.sample(logits[:n], row_slot, [r.sampler_config() for r in requests])
-        out = ids.tolist()
-        self.engine.check_errors()
+        if self._host is None or self._host.numel() < n + 1:
+            self._host = torch.empty(max(64, n + 1), dtype=torch.int32, pin_memory=ids.is_cuda)
+        self._host[:n].copy_(ids, non_blocking=True)
+        self._host[n:n + 1].copy_(self.engine.model.error_flag, non_blocking=True)
+        event = None
+        if ids.is_cuda:
+            event = torch.cuda.Event()
+            event.record()
+        return ids, n, event
+
+    def sample_end(self, pending) -> list:
+        """The ids of ``sample_begin`` on the host (one synchronisation, on the copy only)."""
+        _, n, event = pending
+        if event is not None:
+            event.synchronize()
+        out = self._host[:n].tolist()
+        if int(self._host[n]) != 0:
+            self.engine.check_errors()  # raises, and clears the flag
         return out
+
+    def sample(self, logits, slots, requests) -> list:
+        return self.sample_end(self.sample_begin(logits, slots, requests))
+
+    def forward_sampled(self, slots, pending):
+        """The next decode step of the same sequences, fed with the ids that ``sample_begin`` left
+        on the device."""
+        ids, n, _ = pending
+        logits = self.engine.step_sampled(slots, ids[:n])
+        if self.track_seen:
+            ctx = self.engine.last_context
+            self.sampler.observe(ctx.tok_slot, ctx.token_ids)
+        return logits
+
+    def rows(self, logits, rows):
+        """Some rows of a step's logits (sequences that ended are dropped); the next sampling is told
+        its slots explicitly."""
+        self._explicit_slots = True
+        return logits[torch.tensor(rows, dtype=torch.int64, device=logits.device)]
 
 
 class Runtime:

@@ -221,7 +221,18 @@ class Engine:
             self.cache.advance(e.slot, len(e.tokens))
         return logits
 
-    def _graph_step(self, entries):
+    def step_sampled(self, slots, ids: torch.Tensor):
+        """One decode step of the sequences in ``slots`` whose next tokens are ``ids`` (int32, on the
+        device, one a sequence, as a sampler left them): the ids never visit the host, so the step
+        can be launched before the host has seen them.  Logits of every row.  Falls back to reading
+        the ids when the step cannot be replayed from a graph."""
+        n = len(slots)
+        if self.use_graphs and n <= GRAPH_MAX_BATCH:
+            return self._graph_step([StepEntry(s, [0], [0]) for s in slots], ids_device=ids)
+        tokens = ids[:n].tolist()
+        return self.step([StepEntry(s, [int(t)], [0]) for s, t in zip(slots, tokens)])
+
+    def _graph_step(self, entries, ids_device=None):
         model = self.model
         _check_entries(entries, model.vocab_size)
         n = len(entries)
@@ -236,6 +247,8 @@ class Engine:
         wanted = fill_arrays(host.numpy(), entries, starts, bucket, bucket)
         g.static.copy_(host, non_blocking=True)
         self.staging.copied(turn)
+        if ids_device is not None:  # the ids are the first array of the layout
+            g.static[:n].copy_(ids_device[:n], non_blocking=True)
         self.cache.flush_tables()
         self.last_context = context_from(g.static, bucket, bucket, [1] * n, starts, model.dtype)
         g.graph.replay()

@@ -39,6 +39,8 @@ class Sampler:
         self.rng_key = cache.register_sequence_state("sampler.rng_key", (), torch.int64)
         self.rng_counter = cache.register_sequence_state("sampler.rng_counter", (), torch.int32)
         self.seen = cache.register_sequence_state("sampler.seen", (words,), torch.int32)
+        self._options_key = None
+        self._options = None
 
     def begin(self, slots: list, seeds: list) -> None:
         """Sets the random stream of freshly opened slots (their counters and bitmaps are zero)."""
@@ -54,13 +56,17 @@ class Sampler:
         """One id for each row of float32 logits [n, vocab]; ``configs[i]`` are the options of row i.
         Returns an int32 device tensor [n]."""
         n = logits.shape[0]
-        params = np.empty((4, n), dtype=np.float32)
-        for i, c in enumerate(configs):
-            params[0, i] = c.temperature
-            params[1, i] = np.int32(c.top_k).view(np.float32)
-            params[2, i] = c.top_p
-            params[3, i] = c.repetition_penalty
-        dev = torch.from_numpy(params).to(self.device)
+        key = tuple((c.temperature, c.top_k, c.top_p, c.repetition_penalty) for c in configs)
+        if key != self._options_key:  # the options of a batch stay the same from step to step: one copy a batch
+            params = np.empty((4, n), dtype=np.float32)
+            for i, c in enumerate(configs):
+                params[0, i] = c.temperature
+                params[1, i] = np.int32(c.top_k).view(np.float32)
+                params[2, i] = c.top_p
+                params[3, i] = c.repetition_penalty
+            self._options = torch.from_numpy(params).to(self.device)
+            self._options_key = key
+        dev = self._options
         out = torch.empty(n, dtype=torch.int32, device=self.device)
         ops.sample(out, logits, row_slot, dev[0], dev[1].view(torch.int32), dev[2], dev[3], self.seen,
                    self.rng_key, self.rng_counter)
