@@ -262,6 +262,145 @@ def test_a_layer_named_twice_and_a_layer_reading_anothers_cache():
     assert np.abs(_run_cut(engine, tokens, [50] + [1] * 30) - want).max() / np.abs(want).max() < 2e-5
 
 
+class RoutedFeedForward:
+    """A toy feed-forward with routing: a 32-bit softmax router over E experts picks one expert a
+    token; y = p_e * W2_e . relu(W1_e . h).  Defined here, never in the framework."""
+
+    @classmethod
+    def weight_shapes(cls, params):
+        d, f, e = params["width"], params["inner"], params["experts"]
+        return {"router": ((e, d), "matrix"), "w1": ((e * f, d), "matrix"), "w2": ((e * d, f), "matrix")}
+
+    def __init__(self, params, weights, dtype, device):
+        self.d, self.f, self.e = params["width"], params["inner"], params["experts"]
+        self.router = weights["router"].float()
+        self.w1 = weights["w1"].float().view(self.e, self.f, self.d)
+        self.w2 = weights["w2"].float().view(self.e, self.d, self.f)
+
+    def forward(self, h, residual, ctx):
+        h = h.float()
+        probs = torch.softmax(h @ self.router.T, dim=-1)
+        top = probs.argmax(dim=-1)
+        for e in range(self.e):
+            rows = (top == e).nonzero().flatten()
+            if rows.numel():
+                y = torch.relu(h[rows] @ self.w1[e].T) @ self.w2[e].T
+                residual[rows] += probs[rows, e, None] * y
+
+
+class LinearAngles:
+    """A toy position encoding: pair i of a head is turned by pos * (i + 1) * step radians (not a
+    power law).  It fits the rotation interface by handing the attention kernel another table."""
+
+    @classmethod
+    def weight_shapes(cls, params):
+        return {}
+
+    def __init__(self, params, weights, dtype, device):
+        self.half = params["rope_dim"] // 2
+        self.step = float(params["step"])
+
+    def tables(self, ctx):
+        key = ("test_linear_angles", self.half, self.step)
+        if key not in ctx.shared:
+            i = torch.arange(1, self.half + 1, device=ctx.tok_pos.device, dtype=torch.float32)
+            angle = ctx.tok_pos.float()[:, None] * (i * self.step)[None]
+            ctx.shared[key] = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1).contiguous()
+        return ctx.shared[key]
+
+
+def test_toy_feed_forward_with_routing_and_another_position_encoding():
+    """Both toy parts are registered from here, chosen by the spec for one layer of two, built and
+    stepped (whole, cut into steps, and in a batch of two) without a change to the framework."""
+    from xeno_rt_b200.engine import Engine, StepEntry
+    from xeno_rt_b200.parts import LayerSpec, ModelSpec, PartSpec, SchedulePlace, register_part
+    register_part("feed_forward", "test_routed", RoutedFeedForward, replace=True)
+    register_part("position", "test_linear_angles", LinearAngles, replace=True)
+    d, vocab, hd, nh, nkv, experts, inner = 40, 50, 16, 3, 1, 3, 24
+    norm = lambda name: PartSpec("rmsnorm", {"width": d, "eps": 1e-5}, {"weight": name})
+
+    def attn(i, position):
+        return PartSpec("attention", {"width": d, "n_heads": nh, "n_kv_heads": nkv, "head_dim": hd, "qk_norm": False,
+                                      "eps": 1e-5, "window": None, "position": position},
+                        {"q": f"l{i}.q", "k": f"l{i}.k", "v": f"l{i}.v", "o": f"l{i}.o"})
+    layers = [
+        LayerSpec(norm("l0.n1"), attn(0, {"kind": "test_linear_angles", "params": {"rope_dim": 12, "step": 0.05}}),
+                  norm("l0.n2"), PartSpec("test_routed", {"width": d, "inner": inner, "experts": experts},
+                                          {"router": "l0.r", "w1": "l0.w1", "w2": "l0.w2"})),
+        LayerSpec(norm("l1.n1"), attn(1, {"kind": "rotary", "params": {"rope_dim": 16, "base": 100.0, "scale": 1.0}}),
+                  norm("l1.n2"), PartSpec("swiglu", {"width": d, "inner": inner}, {"gate": "l1.g", "up": "l1.u", "down": "l1.d"})),
+    ]
+    spec = ModelSpec(vocab_size=vocab, hidden_size=d, max_positions=256,
+                     embedding=PartSpec("token", {"vocab_size": vocab, "width": d}, {"weight": "emb"}),
+                     layers=layers, schedule=[SchedulePlace(0), SchedulePlace(1)], final_norm=norm("fn"),
+                     lm_head=PartSpec("linear", {"vocab_size": vocab, "width": d}, {"weight": "emb"}))
+    model, tensors = _toy_model(spec)
+    for k in tensors:
+        if k.endswith(".r"):
+            tensors[k] = tensors[k] * 40  # a clear winner among the experts, so that rounding cannot flip the choice
+    from xeno_rt_b200.engine import Model
+    model = Model(spec, tensors, model.dtype, DEV)
+    assert not model.graph_safe  # the toy parts do not promise what graph replay needs: steps run kernel by kernel
+
+    def plain(tokens):
+        w = {k: f64(v) for k, v in tensors.items()}
+        x = pm.embedding(w["emb"], tokens)
+        pos = np.arange(len(tokens))
+        for i in (0, 1):
+            h = pm.rmsnorm(x, w[f"l{i}.n1"], 1e-5)
+            q, k, v = pm.linear(h, w[f"l{i}.q"]), pm.linear(h, w[f"l{i}.k"]), pm.linear(h, w[f"l{i}.v"])
+            if i == 0:
+                def turn(t, heads):
+                    t = t.reshape(len(tokens), heads, hd).copy()
+                    angle = pos[:, None] * (np.arange(1, 7) * 0.05)[None]
+                    c, s_ = np.cos(angle)[:, None, :], np.sin(angle)[:, None, :]
+                    a, b = t[..., :6].copy(), t[..., 6:12].copy()  # pairs (j, j + half) of the first 12 dims
+                    t[..., :6], t[..., 6:12] = a * c - b * s_, a * s_ + b * c
+                    return t.reshape(len(tokens), heads * hd)
+                q, k = turn(q, nh), turn(k, nkv)
+            else:
+                q = pm.rope(q, pos, nh, hd, 16, 100.0, 1.0)
+                k = pm.rope(k, pos, nkv, hd, 16, 100.0, 1.0)
+            x = x + pm.linear(pm.causal_gqa_attention(q, k, v, nh, nkv, hd), w[f"l{i}.o"])
+            h = pm.rmsnorm(x, w[f"l{i}.n2"], 1e-5)
+            if i == 0:
+                logits = pm.linear(h, w["l0.r"])
+                probs = np.exp(logits - logits.max(-1, keepdims=True))
+                probs /= probs.sum(-1, keepdims=True)
+                y = np.zeros_like(x)
+                for t in range(len(tokens)):
+                    e = int(probs[t].argmax())
+                    w1 = w["l0.w1"].reshape(experts, inner, d)[e]
+                    w2 = w["l0.w2"].reshape(experts, d, inner)[e]
+                    y[t] = probs[t, e] * (w2 @ np.maximum(w1 @ h[t], 0))
+                x = x + y
+            else:
+                x = x + pm.linear(pm.swiglu(pm.linear(h, w["l1.g"]), pm.linear(h, w["l1.u"])), w["l1.d"])
+        return pm.linear(pm.rmsnorm(x, w["fn"], 1e-5), w["emb"])
+
+    rng = np.random.default_rng(3)
+    a, b = rng.integers(0, vocab, size=70).tolist(), rng.integers(0, vocab, size=33).tolist()
+    want_a, want_b = plain(a), plain(b)
+    engine = Engine(model, 64 * 4)
+    close = lambda got, want: np.abs(got - want).max() / np.abs(want).max() < 2e-5
+    assert close(_run_cut(engine, a, [70]), want_a)
+    assert close(_run_cut(engine, a, [38] + [1] * 32), want_a)
+    # a batch of two of unequal lengths, prompts in one step and then one token each; the shorter ends earlier
+    sa, sb = engine.open_slot(), engine.open_slot()
+    first = engine.step([StepEntry(sa, a[:60], list(range(60))), StepEntry(sb, b[:30], list(range(30)))]).cpu().numpy()
+    got_a, got_b = [first[:60]], [first[60:]]
+    for t in range(10):
+        entries = [StepEntry(sa, [a[60 + t]], [0])] + ([StepEntry(sb, [b[30 + t]], [0])] if t < 3 else [])
+        out = engine.step(entries).cpu().numpy()
+        got_a.append(out[:1])
+        if t < 3:
+            got_b.append(out[1:2])
+        if t == 2:
+            engine.close_slot(sb)
+    engine.close_slot(sa)
+    assert close(np.concatenate(got_a), want_a) and close(np.concatenate(got_b), want_b)
+
+
 def test_spec_errors():
     from xeno_rt_b200.core import ConfigError
     from xeno_rt_b200.parts import SchedulePlace, part_class
