@@ -105,3 +105,33 @@ def test_big_vocabulary_and_padding_rows():
     assert got[0] == 150000 and got[1] == -1 and 0 <= got[2] < vocab
     top40 = set(torch.topk(logits[2], 40).indices.tolist())
     assert got[2] in top40
+
+
+def test_small_top_k_over_a_big_vocabulary_gathered_or_not():
+    """A small top_k gathers its candidates into shared memory first (everything in the bin of the
+    k-th largest logit or above, at most 4,096); when more than that share the bin the kernel walks
+    the vocabulary instead.  Both ways keep the same set: equal values at the cut in index order."""
+    vocab = 70001
+    rng = np.random.default_rng(5)
+    # (1) gathered: ties at the cut.  300 equal logits share the 40th place; ids in rising order win
+    logits = (rng.normal(size=vocab) * 0.5).astype(np.float32)
+    high = rng.choice(vocab, size=30, replace=False)
+    logits[high] = 6.0 + rng.random(30).astype(np.float32)
+    tied = np.setdiff1d(rng.choice(vocab, size=320, replace=False), high)[:300]
+    logits[tied] = 4.25
+    got = run_sampler(logits, 3000, 1.0, 40, 1.0, 1.0)
+    kept = set(high.tolist()) | set(np.sort(tied)[:10].tolist())
+    assert set(got.tolist()) <= kept
+    ids, probs = ps.candidate_distribution(logits, (), 1.0, 40, 1.0, 1.0)
+    assert set(ids.tolist()) == kept
+    # (2) not gathered: every logit equal, 70,001 elements in one bin; top_k 40 keeps ids 0 .. 39
+    flat = np.full(vocab, 1.5, dtype=np.float32)
+    got = run_sampler(flat, 2000, 1.0, 40, 1.0, 1.0)
+    assert set(got.tolist()) <= set(range(40)) and len(set(got.tolist())) > 30
+    # (3) the reference's defaults on the gathered path against the plain sampler's kept set
+    logits = (rng.normal(size=vocab) * 3.0).astype(np.float32)
+    ids, probs = ps.candidate_distribution(logits, (7, 8), 0.8, 40, 0.95, 1.1)
+    got = run_sampler(logits, 4000, 0.8, 40, 0.95, 1.1, history=(7, 8))
+    assert set(got.tolist()) <= set(ids.tolist())
+    top = int(ids[np.argmax(probs)])
+    assert abs((got == top).mean() - probs.max()) < 4 * np.sqrt(probs.max() * (1 - probs.max()) / 4000) + 1e-3

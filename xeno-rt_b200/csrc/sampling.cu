@@ -177,6 +177,9 @@ __device__ uint32_t radix_select(A adjusted, F weight, int n, uint64_t want, uns
   return prefix;
 }
 
+constexpr int SAMPLE_CANDIDATES = 4096;                      // room for the candidates of a small top_k
+constexpr int SAMPLE_DYNAMIC_BYTES = SAMPLE_CANDIDATES * 8;  // their ids and values; first the 4,096-bin histogram
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(int* __restrict__ out_ids, const float* __restrict__ logits, int vocab,
               const int* __restrict__ row_slot, const float* __restrict__ temperature,
@@ -191,6 +194,11 @@ sample_kernel(int* __restrict__ out_ids, const float* __restrict__ logits, int v
   __shared__ int pick_result;
   __shared__ float bcast_max;
   __shared__ int bcast_arg;
+  __shared__ int cut_bin, cut_count;
+  extern __shared__ __align__(16) unsigned char dynamic[];
+  int* cand_id = reinterpret_cast<int*>(dynamic);
+  float* cand_val = reinterpret_cast<float*>(dynamic + SAMPLE_CANDIDATES * 4);
+  unsigned int* fine_hist = reinterpret_cast<unsigned int*>(dynamic);  // 4,096 bins, before the candidates are written
 
   pdl_trigger();
   pdl_wait();
@@ -201,6 +209,72 @@ sample_kernel(int* __restrict__ out_ids, const float* __restrict__ logits, int v
   view.logits = logits + (size_t)row * vocab;
   view.penalty = penalty[row];
   view.seen = (seen != nullptr && view.penalty > 1.0f) ? seen + (size_t)slot * seen_words : nullptr;
+  const float temp = temperature[row];
+  const int k = top_k[row];
+
+  // A small top_k first gathers its candidates: one pass counts the adjusted logits into 4,096 bins
+  // of the order key's top 12 bits, the bin that holds the k-th largest is found, and every element
+  // of that bin or above (k plus what shares the bin) is copied to shared memory IN INDEX ORDER
+  // (a thread owns a contiguous run of ids; its offset comes from a scan of the counts).  All later
+  // steps run over these few candidates instead of the vocabulary: the kept set, its masses and the
+  // draw are the same, since they only ever look at elements at or above the top_k threshold.
+  int n = vocab;  // elements the later steps walk: the vocabulary, or the candidates
+  bool compact = false;
+  if (temp > 1e-5f && k > 0 && k < vocab) {
+    for (int b = threadIdx.x; b < 4096; b += blockDim.x) fine_hist[b] = 0u;
+    __syncthreads();
+    {
+      int i = threadIdx.x;
+      for (; i + 7 * (int)blockDim.x < vocab; i += 8 * blockDim.x) {
+        float a[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) a[u] = view.adjusted(i + u * blockDim.x);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) atomicAdd(&fine_hist[order_key(a[u]) >> 20], 1u);
+      }
+      for (; i < vocab; i += blockDim.x) atomicAdd(&fine_hist[order_key(view.adjusted(i)) >> 20], 1u);
+    }
+    __syncthreads();
+    {
+      // thread t looks at bins 4095 - 4t .. 4092 - 4t (from the top); a scan tells how many lie above them
+      uint64_t local = 0;
+      if (threadIdx.x == 0) { cut_bin = 0; cut_count = vocab; }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) local += fine_hist[4095 - 4 * (int)threadIdx.x - j];
+      uint64_t total;
+      const uint64_t before = block_exclusive_scan(local, scan_scratch, &total);
+      if (before < (uint64_t)k && (uint64_t)k <= before + local) {
+        uint64_t above = before;
+        for (int j = 0; j < 4; ++j) {
+          const int bin = 4095 - 4 * (int)threadIdx.x - j;
+          above += fine_hist[bin];
+          if (above >= (uint64_t)k) { cut_bin = bin; cut_count = (int)above; break; }
+        }
+      }
+      __syncthreads();
+    }
+    if (cut_count <= SAMPLE_CANDIDATES) {
+      const uint32_t cut = (uint32_t)cut_bin;
+      const int total_kept = cut_count;
+      const int seg = (vocab + blockDim.x - 1) / blockDim.x;
+      const int lo = min(vocab, (int)threadIdx.x * seg), hi = min(vocab, lo + seg);
+      uint64_t mine = 0;
+      for (int i = lo; i < hi; ++i) mine += (order_key(view.adjusted(i)) >> 20) >= cut;
+      uint64_t total;
+      uint64_t at = block_exclusive_scan(mine, scan_scratch, &total);  // also: every thread is done with the histogram
+      for (int i = lo; i < hi && mine > 0; ++i) {
+        const float a = view.adjusted(i);
+        if ((order_key(a) >> 20) >= cut) { cand_id[at] = i; cand_val[at] = a; ++at; }
+      }
+      __syncthreads();
+      compact = true;
+      n = total_kept;
+    } else {
+      __syncthreads();
+    }
+  }
+  auto adjusted = [&](int j) { return compact ? cand_val[j] : view.adjusted(j); };
+  auto id_of = [&](int j) { return compact ? cand_id[j] : j; };
 
   // maximum and its first index
   float best = -INFINITY; int best_i = 0x7fffffff;
@@ -208,16 +282,16 @@ sample_kernel(int* __restrict__ out_ids, const float* __restrict__ logits, int v
     // eight loads in flight a thread: a row is read once and the pass is bound by load latency
     constexpr int UNROLL = 8;
     int i = threadIdx.x;
-    for (; i + (UNROLL - 1) * (int)blockDim.x < vocab; i += UNROLL * blockDim.x) {
+    for (; i + (UNROLL - 1) * (int)blockDim.x < n; i += UNROLL * blockDim.x) {
       float a[UNROLL];
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) a[u] = view.adjusted(i + u * blockDim.x);
+      for (int u = 0; u < UNROLL; ++u) a[u] = adjusted(i + u * blockDim.x);
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u)
         if (a[u] > best) { best = a[u]; best_i = i + u * blockDim.x; }  // indices rise: the first maximum is kept
     }
-    for (; i < vocab; i += blockDim.x) {
-      const float a = view.adjusted(i);
+    for (; i < n; i += blockDim.x) {
+      const float a = adjusted(i);
       if (a > best) { best = a; best_i = i; }
     }
   }
@@ -237,40 +311,37 @@ sample_kernel(int* __restrict__ out_ids, const float* __restrict__ logits, int v
   }
   __syncthreads();
   const float row_max = bcast_max;
-  const int row_arg = bcast_arg;
+  const int row_arg = id_of(bcast_arg);
 
-  const float temp = temperature[row];
   unsigned int counter = 0;
   if (threadIdx.x == 0) { counter = rng_counter[slot]; rng_counter[slot] = counter + 1; }
   if (temp <= 1e-5f) { if (threadIdx.x == 0) out_ids[row] = row_arg; return; }
 
-  auto adjusted = [&](int i) { return view.adjusted(i); };
-  auto key_of = [&](int i) { return order_key(view.adjusted(i)); };
-  // this thread's share of the sum of weight(i, adjusted(i)) over the row, four loads in flight
+  auto key_of = [&](int i) { return order_key(adjusted(i)); };
+  // this thread's share of the sum of weight(i, adjusted(i)) over the elements, four loads in flight
   auto strided_sum = [&](auto weight) {
     uint64_t local = 0;
     int i = threadIdx.x;
-    for (; i + 3 * (int)blockDim.x < vocab; i += 4 * blockDim.x) {
+    for (; i + 3 * (int)blockDim.x < n; i += 4 * blockDim.x) {
       float a[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) a[u] = view.adjusted(i + u * blockDim.x);
+      for (int u = 0; u < 4; ++u) a[u] = adjusted(i + u * blockDim.x);
 #pragma unroll
       for (int u = 0; u < 4; ++u) local += weight(i + u * blockDim.x, a[u]);
     }
-    for (; i < vocab; i += blockDim.x) local += weight(i, view.adjusted(i));
+    for (; i < n; i += blockDim.x) local += weight(i, adjusted(i));
     return local;
   };
 
   // top-k: threshold key and the last index kept among equal keys
-  uint32_t k_key = 0u; int k_last = vocab;  // kept: key > k_key, or key == k_key and i <= k_last
-  const int k = top_k[row];
-  if (k > 0 && k < vocab) {
+  uint32_t k_key = 0u; int k_last = n;  // kept: key > k_key, or key == k_key and i <= k_last
+  if (k > 0 && k < n) {
     uint64_t inside, at_key;
     auto one = [&](int, float) { return (uint64_t)1; };
-    k_key = radix_select(adjusted, one, vocab, (uint64_t)k, hist, &inside, &at_key, shared_prefix);
+    k_key = radix_select(adjusted, one, n, (uint64_t)k, hist, &inside, &at_key, shared_prefix);
     if (at_key > inside) {
       auto tie = [&](int i) { return (uint64_t)(key_of(i) == k_key); };
-      k_last = ordered_pick(tie, vocab, inside - 1, scan_scratch, &pick_result);
+      k_last = ordered_pick(tie, n, inside - 1, scan_scratch, &pick_result);
     }
   }
   const float inv_temp = 1.0f / temp;
@@ -279,10 +350,10 @@ sample_kernel(int* __restrict__ out_ids, const float* __restrict__ logits, int v
     if (key < k_key || (key == k_key && i > k_last)) return 0ull;
     return (uint64_t)(expf((a - row_max) * inv_temp) * 4294967296.0f);
   };
-  auto mass = [&](int i) -> uint64_t { return mass_of(i, view.adjusted(i)); };
+  auto mass = [&](int i) -> uint64_t { return mass_of(i, adjusted(i)); };
 
   // top-p: threshold by probability mass
-  uint32_t p_key = 0u; int p_last = vocab;
+  uint32_t p_key = 0u; int p_last = n;
   const float p = top_p[row];
   if (p < 1.0f) {
     const uint64_t local = strided_sum(mass_of);
@@ -291,11 +362,11 @@ sample_kernel(int* __restrict__ out_ids, const float* __restrict__ logits, int v
     uint64_t want = (uint64_t)ceil((double)p * (double)total);
     if (want < 1) want = 1;
     uint64_t inside, at_key;
-    p_key = radix_select(adjusted, mass_of, vocab, want, hist, &inside, &at_key, shared_prefix);
+    p_key = radix_select(adjusted, mass_of, n, want, hist, &inside, &at_key, shared_prefix);
     if (at_key > inside) {
       // equal keys have equal mass: how many of them the remaining mass needs
       auto tie_mass = [&](int i) { return key_of(i) == p_key ? mass(i) : 0ull; };
-      p_last = ordered_pick(tie_mass, vocab, inside - 1, scan_scratch, &pick_result);
+      p_last = ordered_pick(tie_mass, n, inside - 1, scan_scratch, &pick_result);
     }
   }
   auto kept_mass_of = [&](int i, float a) -> uint64_t {
@@ -303,7 +374,7 @@ sample_kernel(int* __restrict__ out_ids, const float* __restrict__ logits, int v
     if (key < p_key || (key == p_key && i > p_last)) return 0ull;
     return mass_of(i, a);
   };
-  auto kept_mass = [&](int i) -> uint64_t { return kept_mass_of(i, view.adjusted(i)); };
+  auto kept_mass = [&](int i) -> uint64_t { return kept_mass_of(i, adjusted(i)); };
 
   const uint64_t local = strided_sum(kept_mass_of);
   uint64_t total;
@@ -313,8 +384,8 @@ sample_kernel(int* __restrict__ out_ids, const float* __restrict__ logits, int v
     shared_u = (unsigned int)(sm64(rng_key[slot] + ((uint64_t)counter + 1ull) * 0x9E3779B97F4A7C15ull) >> 32);
   __syncthreads();
   const uint64_t target = __umul64hi((uint64_t)shared_u << 32, total);  // floor(u / 2^32 * total)
-  const int pick = total > 0 ? ordered_pick(kept_mass, vocab, target, scan_scratch, &pick_result) : -1;
-  if (threadIdx.x == 0) out_ids[row] = pick >= 0 ? pick : row_arg;
+  const int pick = total > 0 ? ordered_pick(kept_mass, n, target, scan_scratch, &pick_result) : -1;
+  if (threadIdx.x == 0) out_ids[row] = pick >= 0 ? id_of(pick) : row_arg;
 }
 
 // Marks token ids as seen in their slot's bitmap (the history the repetition penalty looks at).
@@ -339,7 +410,14 @@ XRT_EXPORT int xrt_sample(int* out_ids, const float* logits, int n_rows, int voc
   if (n_rows < 0 || vocab <= 0) return XRT_ERR_ARGUMENT;
   if (seen != nullptr && seen_words * 32 < vocab) return XRT_ERR_ARGUMENT;
   if (n_rows == 0) return XRT_OK;
-  xrt::launch_kernel(xrt::sample_kernel, dim3(n_rows), dim3(xrt::SAMPLE_THREADS), 0, stream, out_ids, logits, vocab,
+  static bool allowed = false;
+  if (!allowed) {  // static and dynamic shared memory together pass 48 KB
+    cudaError_t err = cudaFuncSetAttribute(xrt::sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           xrt::SAMPLE_DYNAMIC_BYTES);
+    if (err != cudaSuccess) return (int)err;
+    allowed = true;
+  }
+  xrt::launch_kernel(xrt::sample_kernel, dim3(n_rows), dim3(xrt::SAMPLE_THREADS), xrt::SAMPLE_DYNAMIC_BYTES, stream, out_ids, logits, vocab,
                      row_slot, temperature, top_k, top_p, penalty, (const uint32_t*)seen, seen_words, rng_key, rng_counter);
   return xrt::launch_status();
 }
