@@ -94,7 +94,9 @@ def _cache_for(seq_lens, n_kv, hd, dtype, shuffle_seed=0):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nh,nkv,hd,rope_dim,qk_norm", [(5, 1, 48, 48, True), (4, 2, 16, 16, False),
-                                                        (3, 3, 256, 64, True), (8, 2, 80, 80, False)])
+                                                        (3, 3, 256, 64, True), (8, 2, 80, 80, False),
+                                                        (12, 4, 128, 128, True), (7, 1, 128, 128, False),
+                                                        (4, 2, 128, 64, False)])
 def test_qk_rope_kv_write(dtype, nh, nkv, hd, rope_dim, qk_norm):
     seq_lens = [70, 3]
     starts = [60, 0]  # the first sequence continues at position 60 and crosses a block edge

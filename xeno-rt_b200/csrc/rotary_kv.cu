@@ -122,6 +122,90 @@ __global__ void qk_rope_kv_write_kernel(
   }
 }
 
+// The same for head size 128 with the rotation over all of the head (or none): a lane holds four
+// consecutive dims (one 16-byte load), the partner of dim d, d +- 64, sits sixteen lanes away (a
+// shuffle instead of shared memory), and a block of eight warps walks all heads of one token, so a
+// prompt launches one block a token instead of twelve.
+__device__ __forceinline__ void store4_as(float* dst, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4_as(__nv_bfloat16* dst, const float (&v)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<uint32_t*>(&a);
+  t.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(dst) = t;
+}
+
+template <typename TN, typename TQ, typename TC>
+__global__ void __launch_bounds__(256)
+qk_rope_kv_write_128_kernel(
+    TQ* __restrict__ q_out, TC* __restrict__ k_pool, TC* __restrict__ v_pool,
+    const float* __restrict__ qkv, int row_stride, int k_offset, int v_offset,
+    const TN* __restrict__ q_norm_w, const TN* __restrict__ k_norm_w, float eps,
+    const float2* __restrict__ cos_sin, int rope_half,
+    const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
+    const int* __restrict__ block_table, int max_blocks,
+    int n_heads, int n_kv_heads, int write_kv) {
+  constexpr int HD = 128;
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int n_slots = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+  const int slot = tok_slot[t];
+  const int pos = tok_pos[t];
+  // (cos, sin) of this lane's four pairs: dims 4 * (lane % 16) .. of the first half
+  float c[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+  if (rope_half > 0 && slot >= 0) {
+    const float4* cs = reinterpret_cast<const float4*>(cos_sin + (size_t)t * rope_half + 4 * (lane & 15));
+    const float4 a = cs[0], b = cs[1];
+    c[0] = a.x; sn[0] = a.y; c[1] = a.z; sn[1] = a.w; c[2] = b.x; sn[2] = b.y; c[3] = b.z; sn[3] = b.w;
+  }
+  int block = -1;
+  if (slot >= 0 && write_kv) block = block_table[(size_t)slot * max_blocks + pos / XRT_BLOCK_TOKENS];
+  for (int head_slot = warp; head_slot < n_slots; head_slot += 8) {
+    int kind, head;
+    if (head_slot < n_heads) { kind = 0; head = head_slot; }
+    else if (head_slot < n_heads + n_kv_heads) { kind = 1; head = head_slot - n_heads; }
+    else { kind = 2; head = head_slot - n_heads - n_kv_heads; }
+    float v[4];
+    if (slot < 0) {  // a padding row: q is zeroed, the cache is not touched
+      if (kind == 0) {
+        v[0] = v[1] = v[2] = v[3] = 0.f;
+        store4_as(q_out + (size_t)t * n_heads * HD + head * HD + 4 * lane, v);
+      }
+      continue;
+    }
+    const float* src = qkv + (size_t)t * row_stride + (kind == 0 ? 0 : (kind == 1 ? k_offset : v_offset)) + head * HD;
+    const float4 raw = *reinterpret_cast<const float4*>(src + 4 * lane);
+    v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+    const TN* norm_w = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+    if (norm_w != nullptr) {
+      float sq = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sq = fmaf(v[j], v[j], sq);
+      const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)HD + eps);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = (v[j] * inv) * to_float(norm_w[4 * lane + j]);
+    }
+    if (kind != 2 && rope_half > 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+        // first half: x0 cos - x1 sin; second half: x0 sin + x1 cos, with x0 the first-half element
+        v[j] = lane < 16 ? v[j] * c[j] - other * sn[j] : other * sn[j] + v[j] * c[j];
+      }
+    }
+    if (kind == 0) {
+      store4_as(q_out + (size_t)t * n_heads * HD + head * HD + 4 * lane, v);
+    } else if (block >= 0) {  // the host reserves blocks before the step; otherwise nothing to write into
+      TC* pool = kind == 1 ? k_pool : v_pool;
+      store4_as(pool + (((size_t)block * n_kv_heads + head) * XRT_BLOCK_TOKENS + pos % XRT_BLOCK_TOKENS) * HD + 4 * lane, v);
+    }
+  }
+}
+
 }  // namespace xrt
 
 XRT_EXPORT int xrt_rope_table(float* cos_sin, const int* pos, const float* freq, float scale, int n_tokens,
@@ -148,6 +232,22 @@ XRT_EXPORT int xrt_qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, con
   if (head_dim > 256 || 2 * rope_half > head_dim) return XRT_ERR_UNSUPPORTED;
   if ((q_norm_w == nullptr) != (k_norm_w == nullptr)) return XRT_ERR_ARGUMENT;
   if (n_tokens == 0) return XRT_OK;
+  const bool fast = head_dim == 128 && (rope_half == 0 || rope_half == 64) && row_stride % 4 == 0 && k_offset % 4 == 0 &&
+                    v_offset % 4 == 0 &&
+                    (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)cos_sin) & 15) == 0;
+  if (fast) {
+    XRT_DISPATCH_DTYPE(norm_dtype, TN, {
+      XRT_DISPATCH_DTYPE(q_dtype, TQ, {
+        XRT_DISPATCH_DTYPE(cache_dtype, TC, {
+          xrt::launch_kernel(xrt::qk_rope_kv_write_128_kernel<TN, TQ, TC>, dim3(n_tokens), dim3(256), 0, stream,
+              (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, qkv, row_stride, k_offset, v_offset, (const TN*)q_norm_w,
+              (const TN*)k_norm_w, eps, (const float2*)cos_sin, rope_half, tok_slot, tok_pos, block_table,
+              max_blocks, n_heads, n_kv_heads, write_kv);
+        });
+      });
+    });
+    return xrt::launch_status();
+  }
   const int warps = 4;
   const int n_slots = n_heads + (write_kv ? 2 * n_kv_heads : 0);
   dim3 grid(n_tokens, (n_slots + warps - 1) / warps);
