@@ -580,3 +580,38 @@ def test_decode_chain(m, width, inner, vocab):
     again = run(True)
     for a, b in zip(one, again):
         assert torch.equal(a, b)
+
+
+def test_attention_prefill_tcgen05_scores_that_jump():
+    """The kernel takes its exponents against a reference value that moves only when a row's maximum
+    has outgrown it by more than 8 (in base 2), and then rescales what it has accumulated.  Here the
+    scores stay small for the first key blocks, then one key far along (position 200) and a still larger
+    one (position 330) stand out for the later rows, by scaling those keys: rows before them must not
+    feel them, rows after them must be dominated by them, and every row must match the plain attention."""
+    nh, nkv, hd, S = 4, 2, 128, 400
+    torch.manual_seed(11)
+    k = torch.randn(S, nkv, hd, device=DEV) * 0.3
+    v = torch.randn(S, nkv, hd, device=DEV)
+    q = torch.randn(S, nh * hd, device=DEV) * 0.3
+    direction = torch.randn(hd, device=DEV)
+    direction /= direction.norm()
+    q = (q.view(S, nh, hd) + 6.0 * direction).reshape(S, nh * hd)  # every query leans towards `direction`
+    k[200] += 20.0 * direction  # its score is 6 * 20 / sqrt(128) = 10.6 above the others': a factor e^10.6
+    k[330] += 45.0 * direction  # and a much larger one later: 23.9
+    k_pool, v_pool, table = _cache_for([S], nkv, hd, torch.bfloat16, shuffle_seed=3)
+    _fill_cache(k_pool, v_pool, table, 1, k, v)
+    qb = q.to(torch.bfloat16)
+    cu = torch.tensor([0, S], dtype=torch.int32, device=DEV)
+    one = lambda x: torch.tensor([x], dtype=torch.int32, device=DEV)
+    out = torch.empty_like(qb)
+    ops().attention_prefill_tcgen05(out, qb, k_pool, v_pool, cu, one(1), one(0), table, S, nh, nkv, hd, 1 / math.sqrt(hd))
+    from xeno_rt_b200.csrc import ops as o
+    o.check_error_flag(DEV)
+    bf = lambda x: f64(x.to(torch.bfloat16)).reshape(x.shape[0], -1)
+    want = pm.causal_gqa_attention(f64(qb), bf(k), bf(v), nh, nkv, hd)
+    assert rel(out, want) < 1.5e-2
+    vb = bf(v)
+    # after position 330 a row's output is almost exactly the value at 330
+    assert np.abs(f64(out[399]).reshape(nh, hd)[0] - vb[330].reshape(nkv, hd)[0]).max() < 0.05
+    # and between 200 and 329 mostly the value at 200
+    assert np.abs(f64(out[300]).reshape(nh, hd)[0] - vb[200].reshape(nkv, hd)[0]).max() < 0.3

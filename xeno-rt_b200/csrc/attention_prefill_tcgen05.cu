@@ -7,15 +7,24 @@
 //   warp 0    TMA: the Q tile once, then for each block its K and V tiles ([64 keys x 128], two
 //             64-column halves each, 128-byte swizzle) into a three-stage ring.
 //   warp 1    owns TMEM and issues the MMAs: S = Q K^T (128 x 64, eight tcgen05.mma over the head
-//             size) into one of two S buffers, and O_tile = P V (128 x 128, four tcgen05.mma over the
-//             64 keys) into one of two O buffers.  K is a K-major operand as stored; V ([key][dim])
-//             is an MN-major operand as stored: no transposition anywhere.  QK^T of the next block
-//             is issued before PV of this one, so the tensor core works while the softmax runs.
-//   warps 2-5 softmax and output, ONE THREAD PER QUERY ROW (TMEM lane): it reads its row of S
-//             (tcgen05.ld), masks, keeps the running maximum and sum in 32-bit without any
-//             shuffle, writes P as bfloat16 into shared memory in the MMA's operand layout, and
-//             folds each finished O_tile into its 128 output accumulators (registers) with the
-//             rescaling factor of that block.
+//             size) into one of two S buffers, and O += P V (128 x 128, four tcgen05.mma over the
+//             64 keys) accumulated in TMEM over all blocks.  K is a K-major operand as stored; V
+//             ([key][dim]) is an MN-major operand as stored: no transposition anywhere.  QK^T of the
+//             next block is issued before PV of this one, so the tensor core works while the softmax
+//             runs.
+//   warps 2-9 softmax and output, TWO THREADS PER QUERY ROW (TMEM lane): warps 2-5 take keys 0-31
+//             of a block and dims 0-63 of the output, warps 6-9 keys 32-63 and dims 64-127 (a warp
+//             reaches the TMEM lanes of its number modulo 4, so warps w and w + 4 share 32 rows).
+//             A thread reads its half row of S (tcgen05.ld), masks, keeps its share of the sum in
+//             32-bit, and writes P as bfloat16 into shared memory in the MMA's operand layout; the
+//             two halves of a row meet once a block, through shared memory and a barrier of their
+//             two warps, to agree on the row's maximum.  The exponents are taken
+//             against a reference value m of the row that only moves when the row's maximum has
+//             grown by more than 8 (a factor 256) beyond it: softmax does not depend on m as long as
+//             P and the sum use the same one, P stays within 2^8 (bfloat16 keeps its 8 bits of
+//             precision at any magnitude), and the accumulated O in TMEM has to be rescaled (read,
+//             multiplied, written back by the row's thread, after the products issued so far have
+//             completed) only on those rare moves instead of once a block.
 // Every mbarrier wait is bounded; a wait that runs out raises the error flag and an abort flag, all
 // roles leave their loops, TMEM is freed and the block returns.
 #include <cuda.h>
@@ -24,14 +33,13 @@
 
 namespace xrt {
 
-constexpr int FA_ROWS = 128, FA_KEYS = 64, FA_HD = 128, FA_STAGES = 3;
+constexpr int FA_ROWS = 128, FA_KEYS = 128, FA_HD = 128, FA_STAGES = 2;
 constexpr int FA_Q_BYTES = FA_ROWS * FA_HD * 2;        // 32 KB (two halves of 16 KB)
-constexpr int FA_KV_HALF = FA_KEYS * 64 * 2;           // 8 KB: 64 keys x 64 dims
-constexpr int FA_STAGE_BYTES = 4 * FA_KV_HALF;         // K halves, then V halves
-constexpr int FA_P_BYTES = FA_ROWS * FA_KEYS * 2;      // 16 KB
-constexpr int FA_THREADS = 192;
-constexpr int FA_TMEM_COLS = 512;
-constexpr int FA_SMEM = FA_Q_BYTES + FA_STAGES * FA_STAGE_BYTES + 2 * FA_P_BYTES + 512 + 1024;
+constexpr int FA_BOX = 64 * 64 * 2;                    // 8 KB: what one tensor copy brings, 64 keys x 64 dims
+constexpr int FA_KV_HALF = FA_KEYS * 64 * 2;           // 16 KB: 128 keys (two cache blocks) x 64 dims
+constexpr int FA_STAGE_BYTES = 4 * FA_KV_HALF;         // K halves, then V halves: 64 KB
+constexpr int FA_P_BYTES = FA_ROWS * FA_KEYS * 2;      // 32 KB (two halves of 64 keys)
+constexpr int fa_smem_bytes(int nh) { return nh * FA_Q_BYTES + FA_STAGES * FA_STAGE_BYTES + nh * FA_P_BYTES + 512 + 1024; }
 constexpr long long FA_SPIN_LIMIT = 1ll << 24;
 
 __device__ __forceinline__ uint32_t fa_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -86,6 +94,15 @@ __device__ __forceinline__ void fa_commit(uint32_t bar) {
 }
 __device__ __forceinline__ void fa_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fa_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fa_st32(uint32_t addr, const uint32_t (&r)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+               "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                 "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                 "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                 "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+               : "memory");
+}
 __device__ __forceinline__ void fa_ld32(uint32_t (&r)[32], uint32_t addr) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -105,7 +122,12 @@ __device__ __forceinline__ float fa_exp2(float x) {
 }
 __device__ __forceinline__ void fa_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-__global__ void __launch_bounds__(FA_THREADS, 1)
+// NH = query heads of one kv head that a block serves; its K and V tiles are fetched once for all of
+// them.  With steps of 128 keys (two cache blocks: a tcgen05.mma costs about a hundred cycles
+// whatever its N, so QK^T is issued with N = 128, and a step's chain of barrier hand-overs is paid
+// half as often) the two S buffers and O of one head take 384 of the 512 TMEM columns: NH = 1.
+template <int NH>
+__global__ void __launch_bounds__(64 + 128 * NH, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                                  const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
@@ -113,58 +135,66 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  int n_heads, int n_kv_heads, float scale_log2, int* __restrict__ error_flag) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  unsigned char* q_tile = smem;
-  unsigned char* kv_ring = smem + FA_Q_BYTES;
-  unsigned char* p_tiles = kv_ring + FA_STAGES * FA_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_tiles + 2 * FA_P_BYTES);
+  unsigned char* q_tiles = smem;                                   // [NH] x 32 KB
+  unsigned char* kv_ring = smem + NH * FA_Q_BYTES;
+  unsigned char* p_tiles = kv_ring + FA_STAGES * FA_STAGE_BYTES;   // [NH] x 16 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_tiles + NH * FA_P_BYTES);
   uint64_t* q_full = bars;                 // [1]
-  uint64_t* kv_full = bars + 1;            // [FA_STAGES]
-  uint64_t* kv_empty = kv_full + FA_STAGES;
-  uint64_t* s_full = kv_empty + FA_STAGES; // [2] ...
-  uint64_t* s_empty = s_full + 2;
-  uint64_t* p_full = s_empty + 2;
-  uint64_t* p_empty = p_full + 2;
-  uint64_t* o_full = p_empty + 2;
-  uint64_t* o_empty = o_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_empty + 2);
+  uint64_t* k_full = bars + 1;             // [FA_STAGES] each: K and V of a step have barriers of their own,
+  uint64_t* k_empty = k_full + FA_STAGES;  //   since a step's K is free again (after its QK^T) a whole step
+  uint64_t* v_full = k_empty + FA_STAGES;  //   before its V (after its PV): the next K is fetched that much earlier
+  uint64_t* v_empty = v_full + FA_STAGES;
+  uint64_t* s_full = v_empty + FA_STAGES;  // [2]
+  uint64_t* s_empty = s_full + 2;          // [2]
+  uint64_t* p_full = s_empty + 2;          // [1]
+  uint64_t* p_empty = p_full + 1;          // [1]
+  uint64_t* pv_done = p_empty + 1;         // [1]: completes once for every block's P V
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   // later query tiles walk more keys: they are scheduled first
-  const int q_index = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
+  const int q_index = gridDim.x - 1 - blockIdx.x, head0 = blockIdx.y * NH, seq = blockIdx.z;
   const int slot = seq_slot[seq];
   const int tok0 = cu_seqlens[seq];
   const int n_new = cu_seqlens[seq + 1] - tok0;
   const int row0 = q_index * FA_ROWS;
   if (slot < 0 || row0 >= n_new) return;  // the whole block leaves before any barrier or allocation
   const int start = seq_start[seq];
-  const int kv_head = head / (n_heads / n_kv_heads);
+  const int kv_head = head0 / (n_heads / n_kv_heads);  // the same for all NH heads: NH divides the group
   const int last_row = min(row0 + FA_ROWS, n_new) - 1;
   const int n_tiles = (start + last_row + 1 + FA_KEYS - 1) / FA_KEYS;  // keys 0 .. position of the last row
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  static_assert(NH * (2 * FA_KEYS + FA_HD) <= 512, "S buffers and O must fit in TMEM");
+  constexpr int TMEM_COLS = 512;  // S: NH x 2 buffers x 128 columns; O: NH x 128
 
   if (threadIdx.x == 0) {
     fa_mbar_init(fa_smem(q_full), 1);
-    for (int s = 0; s < FA_STAGES; ++s) { fa_mbar_init(fa_smem(&kv_full[s]), 1); fa_mbar_init(fa_smem(&kv_empty[s]), 1); }
-    for (int b = 0; b < 2; ++b) {
-      // the four softmax warps arrive once each (lane 0, after the warp has synchronised): a hundred
-      // and twenty-eight arrivals on one shared-memory word would serialise
-      fa_mbar_init(fa_smem(&s_full[b]), 1);  fa_mbar_init(fa_smem(&s_empty[b]), 4);
-      fa_mbar_init(fa_smem(&p_full[b]), 4);  fa_mbar_init(fa_smem(&p_empty[b]), 1);
-      fa_mbar_init(fa_smem(&o_full[b]), 1);  fa_mbar_init(fa_smem(&o_empty[b]), 4);
+    for (int s = 0; s < FA_STAGES; ++s) {
+      fa_mbar_init(fa_smem(&k_full[s]), 1); fa_mbar_init(fa_smem(&k_empty[s]), 1);
+      fa_mbar_init(fa_smem(&v_full[s]), 1); fa_mbar_init(fa_smem(&v_empty[s]), 1);
     }
+    for (int b = 0; b < 2; ++b) {
+      // the softmax warps arrive once each (lane 0, after the warp has synchronised): hundreds of
+      // arrivals on one shared-memory word would serialise
+      fa_mbar_init(fa_smem(&s_full[b]), 1);
+      fa_mbar_init(fa_smem(&s_empty[b]), 4 * NH);
+    }
+    fa_mbar_init(fa_smem(p_full), 4 * NH);
+    fa_mbar_init(fa_smem(p_empty), 1);
+    fa_mbar_init(fa_smem(pv_done), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(fa_smem(tmem_slot)), "r"(FA_TMEM_COLS));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(fa_smem(tmem_slot)), "n"(TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
   fa_fence_before();
   __syncthreads();
   fa_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base;             // two S buffers of 64 columns
-  const uint32_t tmem_o = tmem_base + 2 * FA_KEYS;  // two O buffers of 128 columns
+  const uint32_t tmem_s = tmem_base;                        // [head][buffer] x 64 columns
+  const uint32_t tmem_o = tmem_base + NH * 2 * FA_KEYS;     // [head] x 128 columns
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
@@ -172,23 +202,39 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
-      fa_mbar_expect_tx(fa_smem(q_full), FA_Q_BYTES);
-      fa_tma_load_2d(fa_smem(q_tile), &map_q, head * FA_HD, tok0 + row0, fa_smem(q_full));
-      fa_tma_load_2d(fa_smem(q_tile + FA_Q_BYTES / 2), &map_q, head * FA_HD + 64, tok0 + row0, fa_smem(q_full));
+      fa_mbar_expect_tx(fa_smem(q_full), NH * FA_Q_BYTES);
+#pragma unroll
+      for (int h = 0; h < NH; ++h) {
+        fa_tma_load_2d(fa_smem(q_tiles + h * FA_Q_BYTES), &map_q, (head0 + h) * FA_HD, tok0 + row0, fa_smem(q_full));
+        fa_tma_load_2d(fa_smem(q_tiles + h * FA_Q_BYTES + FA_Q_BYTES / 2), &map_q, (head0 + h) * FA_HD + 64, tok0 + row0,
+                       fa_smem(q_full));
+      }
       const int* blocks = block_table + (size_t)slot * max_blocks;
+      const int n_blocks = (start + last_row + 1 + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS;  // cache blocks the rows see
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % FA_STAGES;
-        ok = fa_mbar_wait(fa_smem(&kv_empty[s]), ((j / FA_STAGES) & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        const int pool_row = (blocks[j] * n_kv_heads + kv_head) * FA_KEYS;
-        const uint32_t bar = fa_smem(&kv_full[s]);
         unsigned char* stage = kv_ring + s * FA_STAGE_BYTES;
-        fa_mbar_expect_tx(bar, FA_STAGE_BYTES);
-        fa_tma_load_2d(fa_smem(stage), &map_k, 0, pool_row, bar);
-        fa_tma_load_2d(fa_smem(stage + FA_KV_HALF), &map_k, 64, pool_row, bar);
-        fa_tma_load_2d(fa_smem(stage + 2 * FA_KV_HALF), &map_v, 0, pool_row, bar);
-        fa_tma_load_2d(fa_smem(stage + 3 * FA_KV_HALF), &map_v, 64, pool_row, bar);
+        int pool_row[2];  // the step's two cache blocks; beyond the last one the last again (masked)
+#pragma unroll
+        for (int part = 0; part < 2; ++part)
+          pool_row[part] = (blocks[min(2 * j + part, n_blocks - 1)] * n_kv_heads + kv_head) * XRT_BLOCK_TOKENS;
+        ok = fa_mbar_wait(fa_smem(&k_empty[s]), ((j / FA_STAGES) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        fa_mbar_expect_tx(fa_smem(&k_full[s]), 2 * FA_KV_HALF);
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          fa_tma_load_2d(fa_smem(stage + part * FA_BOX), &map_k, 0, pool_row[part], fa_smem(&k_full[s]));
+          fa_tma_load_2d(fa_smem(stage + FA_KV_HALF + part * FA_BOX), &map_k, 64, pool_row[part], fa_smem(&k_full[s]));
+        }
+        ok = fa_mbar_wait(fa_smem(&v_empty[s]), ((j / FA_STAGES) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        fa_mbar_expect_tx(fa_smem(&v_full[s]), 2 * FA_KV_HALF);
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          fa_tma_load_2d(fa_smem(stage + 2 * FA_KV_HALF + part * FA_BOX), &map_v, 0, pool_row[part], fa_smem(&v_full[s]));
+          fa_tma_load_2d(fa_smem(stage + 3 * FA_KV_HALF + part * FA_BOX), &map_v, 64, pool_row[part], fa_smem(&v_full[s]));
+        }
       }
       if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 5); }
     }
@@ -200,72 +246,61 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       bool ok = fa_mbar_wait(fa_smem(q_full), 0, abort_flag);
       auto issue_qk = [&](int j) {
         const int s = j % FA_STAGES, b = j & 1;
-        if (!fa_mbar_wait(fa_smem(&kv_full[s]), (j / FA_STAGES) & 1, abort_flag)) return false;
+        if (!fa_mbar_wait(fa_smem(&k_full[s]), (j / FA_STAGES) & 1, abort_flag)) return false;
         if (!fa_mbar_wait(fa_smem(&s_empty[b]), ((j >> 1) & 1) ^ 1, abort_flag)) return false;
         fa_fence_after();
         unsigned char* stage = kv_ring + s * FA_STAGE_BYTES;
 #pragma unroll
-        for (int ks = 0; ks < FA_HD / 16; ++ks) {  // 16 dims a step; 4 steps a 64-dim half
-          const uint64_t a = fa_desc_k_major(fa_smem(q_tile + (ks / 4) * (FA_Q_BYTES / 2))) + 2 * (ks % 4);
-          const uint64_t bd = fa_desc_k_major(fa_smem(stage + (ks / 4) * FA_KV_HALF)) + 2 * (ks % 4);
-          fa_mma(tmem_s + b * FA_KEYS, a, bd, idesc_qk, ks > 0);
+        for (int h = 0; h < NH; ++h) {
+#pragma unroll
+          for (int ks = 0; ks < FA_HD / 16; ++ks) {  // 16 dims a step; 4 steps a 64-dim half
+            const uint64_t a = fa_desc_k_major(fa_smem(q_tiles + h * FA_Q_BYTES + (ks / 4) * (FA_Q_BYTES / 2))) + 2 * (ks % 4);
+            const uint64_t bd = fa_desc_k_major(fa_smem(stage + (ks / 4) * FA_KV_HALF)) + 2 * (ks % 4);
+            fa_mma(tmem_s + (h * 2 + b) * FA_KEYS, a, bd, idesc_qk, ks > 0);
+          }
         }
         fa_commit(fa_smem(&s_full[b]));
+        fa_commit(fa_smem(&k_empty[s]));
         return true;
       };
       if (ok) ok = issue_qk(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);
         if (!ok) break;
-        const int s = j % FA_STAGES, b = j & 1;
-        ok = fa_mbar_wait(fa_smem(&p_full[b]), (j >> 1) & 1, abort_flag) &&
-             fa_mbar_wait(fa_smem(&o_empty[b]), ((j >> 1) & 1) ^ 1, abort_flag);
+        const int s = j % FA_STAGES;
+        ok = fa_mbar_wait(fa_smem(p_full), (uint32_t)j & 1u, abort_flag) &&  // P is written, and O rescaled if it had to be
+             fa_mbar_wait(fa_smem(&v_full[s]), (j / FA_STAGES) & 1, abort_flag);
         if (!ok) break;
         fa_fence_after();
         unsigned char* stage = kv_ring + s * FA_STAGE_BYTES;
 #pragma unroll
-        for (int ks = 0; ks < FA_KEYS / 16; ++ks) {  // 16 keys a step
-          const uint64_t a = fa_desc_k_major(fa_smem(p_tiles + b * FA_P_BYTES)) + 2 * ks;
-          const uint64_t bd = fa_desc_mn_major(fa_smem(stage + 2 * FA_KV_HALF + ks * 2048), FA_KV_HALF);
-          fa_mma(tmem_o + b * FA_HD, a, bd, idesc_pv, ks > 0);
+        for (int h = 0; h < NH; ++h) {
+#pragma unroll
+          for (int ks = 0; ks < FA_KEYS / 16; ++ks) {  // 16 keys a step
+            const uint64_t a = fa_desc_k_major(fa_smem(p_tiles + h * FA_P_BYTES + (ks / 4) * (FA_P_BYTES / 2))) + 2 * (ks % 4);
+            const uint64_t bd = fa_desc_mn_major(fa_smem(stage + 2 * FA_KV_HALF + ks * 2048), FA_KV_HALF);
+            fa_mma(tmem_o + h * FA_HD, a, bd, idesc_pv, j > 0 || ks > 0);
+          }
         }
-        fa_commit(fa_smem(&o_full[b]));
-        fa_commit(fa_smem(&kv_empty[s]));
-        fa_commit(fa_smem(&p_empty[b]));
+        fa_commit(fa_smem(pv_done));
+        fa_commit(fa_smem(&v_empty[s]));
+        fa_commit(fa_smem(p_empty));
       }
       if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 5); }
     }
   } else {
-    // ---------------------------------------------------------------- softmax and output: one thread a row
+    // ---------------------------------------------------------------- softmax and output: one thread a row and head
     const int quarter = warp & 3;
+    const int h = (warp - 2) >> 2;               // which of the block's heads
+    const int head = head0 + h;
     const int r = quarter * 32 + lane;           // row of the tile = TMEM lane
     const int row = row0 + r;                    // new-token index in the sequence
     const bool row_live = row < n_new;
     const int key_hi = row_live ? start + row + 1 : 0;  // keys [0, key_hi) are visible
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    float o_acc[FA_HD];
-#pragma unroll
-    for (int d = 0; d < FA_HD; ++d) o_acc[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, corr_pending = 1.f;
+    const uint32_t my_s = tmem_s + lane_base + h * 2 * FA_KEYS, my_o = tmem_o + lane_base + h * FA_HD;
+    float m_ref = -INFINITY, l_run = 0.f;  // the reference value of the exponents (scaled, base 2) and the sum
     bool ok = true;
-
-    auto fold = [&](int j, float corr) {  // O_acc = O_acc * corr + O_tile(j)
-      const int b = j & 1;
-      if (!fa_mbar_wait(fa_smem(&o_full[b]), (j >> 1) & 1, abort_flag)) return false;
-      fa_fence_after();
-#pragma unroll
-      for (int c = 0; c < FA_HD; c += 32) {
-        uint32_t v[32];
-        fa_ld32(v, tmem_o + lane_base + b * FA_HD + c);
-        fa_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c + i] = fmaf(o_acc[c + i], corr, __uint_as_float(v[i]));
-      }
-      fa_fence_before();
-      __syncwarp();
-      if (lane == 0) fa_mbar_arrive(fa_smem(&o_empty[b]));
-      return true;
-    };
 
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int b = j & 1;
@@ -274,12 +309,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       fa_fence_after();
       float s[FA_KEYS];
 #pragma unroll
-      for (int c = 0; c < FA_KEYS; c += 32) {
-        uint32_t v[32];
-        fa_ld32(v, tmem_s + lane_base + b * FA_KEYS + c);
+      for (int c = 0; c < FA_KEYS; c += 64) {
+        uint32_t v0[32], v1[32];  // two loads on their way before the wait
+        fa_ld32(v0, my_s + b * FA_KEYS + c);
+        fa_ld32(v1, my_s + b * FA_KEYS + c + 32);
         fa_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(v[i]);
+        for (int i = 0; i < 32; ++i) { s[c + i] = __uint_as_float(v0[i]); s[c + 32 + i] = __uint_as_float(v1[i]); }
       }
       fa_fence_before();
       __syncwarp();
@@ -291,53 +327,91 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
         for (int i = 0; i < FA_KEYS; ++i) s[i] = (key0 + i < key_hi) ? s[i] : -INFINITY;
       }
-      float tile_max = -INFINITY;  // of the raw scores: the scale is positive and is applied inside the exponent
+      // the maximum of the raw scores (the scale is positive and is applied inside the exponent)
+      float part_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < FA_KEYS; ++i) tile_max = fmaxf(tile_max, s[i]);
-      const float m_new = fmaxf(m_run, tile_max * scale_log2);
-      const float corr = m_new == -INFINITY ? 1.f : fa_exp2(m_run - m_new);
-      const float neg_m = m_new == -INFINITY ? 0.f : -m_new;  // a row without visible keys: exp2(-inf) = 0 all the same
-      float sum = 0.f;
-      // P in the operand layout: row r holds 64 keys = 128 bytes; 16-byte piece c sits at c ^ (r % 8)
-      ok = fa_mbar_wait(fa_smem(&p_empty[b]), ((j >> 1) & 1) ^ 1, abort_flag);
+      for (int i = 0; i < FA_KEYS; i += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) part_max[u] = fmaxf(part_max[u], s[i + u]);
+      }
+      const float m_tile = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])) * scale_log2;
+      // move the reference only when the maximum has outgrown it by more than 8; the first visible key sets it
+      const bool moves = m_tile > m_ref + 8.0f || (m_ref == -INFINITY && m_tile != -INFINITY);
+      if (__any_sync(0xffffffffu, moves)) {
+        const float factor = (moves && m_ref != -INFINITY) ? fa_exp2(m_ref - m_tile) : 1.0f;
+        if (j > 0) {  // O holds the products of the blocks so far: they must have completed before it is rewritten
+          ok = fa_mbar_wait(fa_smem(pv_done), (uint32_t)(j - 1) & 1u, abort_flag);
+          if (!ok) break;
+          fa_fence_after();
+          if (__any_sync(0xffffffffu, factor != 1.0f)) {
+#pragma unroll
+            for (int c = 0; c < FA_HD; c += 32) {
+              uint32_t v[32];
+              fa_ld32(v, my_o + c);
+              fa_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
+              fa_st32(my_o + c, v);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            fa_fence_before();
+          }
+        }
+        l_run *= factor;
+        if (moves) m_ref = m_tile;
+      }
+      const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;  // a row without visible keys: exp2(-inf) = 0 all the same
+      float part_sum[4] = {0.f, 0.f, 0.f, 0.f};
+      // P in the operand layout: two halves of 64 keys; in a half row r holds 128 bytes and its 16-byte
+      // piece c sits at c ^ (r % 8).  One P buffer a head: the product that read it (the step before)
+      // was issued as soon as it was written and is long done by now.
+      ok = fa_mbar_wait(fa_smem(p_empty), ((uint32_t)j & 1u) ^ 1u, abort_flag);
       if (!ok) break;
-      unsigned char* p_row = p_tiles + b * FA_P_BYTES + r * 128;
+      unsigned char* p_row = p_tiles + h * FA_P_BYTES + r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < FA_KEYS / 8; ++c) {
         uint32_t packed[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float p0 = fa_exp2(fmaf(s[c * 8 + 2 * i], scale_log2, neg_m));
           const float p1 = fa_exp2(fmaf(s[c * 8 + 2 * i + 1], scale_log2, neg_m));
-          sum += p0 + p1;
+          part_sum[i] += p0 + p1;
           __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
           packed[i] = *reinterpret_cast<uint32_t*>(&pair);
         }
-        *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        *reinterpret_cast<uint4*>(p_row + (c / 8) * (FA_P_BYTES / 2) + (((c % 8) ^ (r & 7)) << 4)) =
+            make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads P through the async proxy
       __syncwarp();
-      if (lane == 0) fa_mbar_arrive(fa_smem(&p_full[b]));
-      l_run = l_run * corr + sum;
-      m_run = m_new;
-      // fold the block before this one while the tensor core multiplies this one's P with V
-      if (j > 0) ok = fold(j - 1, corr_pending);
-      corr_pending = corr;
+      if (lane == 0) fa_mbar_arrive(fa_smem(p_full));
+      l_run += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
     }
-    if (ok && n_tiles > 0) ok = fold(n_tiles - 1, corr_pending);
-    if (ok && row_live) {
-      const float inv = 1.0f / l_run;
+    if (ok && n_tiles > 0) ok = fa_mbar_wait(fa_smem(pv_done), (uint32_t)(n_tiles - 1) & 1u, abort_flag);
+    if (ok && n_tiles > 0) {
+      fa_fence_after();
+      const float inv = row_live ? 1.0f / l_run : 0.f;
       __nv_bfloat16* dst = out + ((size_t)(tok0 + row) * n_heads + head) * FA_HD;
 #pragma unroll
-      for (int d = 0; d < FA_HD; d += 8) {
-        uint32_t packed[4];
+      for (int c = 0; c < FA_HD; c += 32) {
+        uint32_t v[32];
+        fa_ld32(v, my_o + c);  // all lanes take part; rows beyond the sequence store nothing
+        fa_wait_ld();
+        if (row_live) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          __nv_bfloat162 pair = __floats2bfloat162_rn(o_acc[d + 2 * i] * inv, o_acc[d + 2 * i + 1] * inv);
-          packed[i] = *reinterpret_cast<uint32_t*>(&pair);
+          for (int d = 0; d < 32; d += 8) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[d + 2 * i]) * inv,
+                                                          __uint_as_float(v[d + 2 * i + 1]) * inv);
+              packed[i] = *reinterpret_cast<uint32_t*>(&pair);
+            }
+            *reinterpret_cast<uint4*>(dst + c + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
         }
-        *reinterpret_cast<uint4*>(dst + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
+      fa_fence_before();
     }
     if (!ok && lane == 0) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 5); }
   }
@@ -346,7 +420,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   __syncthreads();
   if (warp == 1) {
     fa_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(FA_TMEM_COLS));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TMEM_COLS));
   }
 }
 
@@ -398,20 +472,20 @@ XRT_EXPORT int xrt_attention_prefill_tcgen05(void* out, const void* q, const voi
     return XRT_ERR_UNSUPPORTED;
   if (n_seqs == 0 || max_new == 0 || n_tokens == 0) return XRT_OK;
   CUtensorMap map_q, map_k, map_v;
-  const long long pool_rows = (long long)n_blocks * n_kv_heads * xrt::FA_KEYS;
+  const long long pool_rows = (long long)n_blocks * n_kv_heads * XRT_BLOCK_TOKENS;
   if (!xrt::fa_make_map(&map_q, q, n_tokens, n_heads * xrt::FA_HD, xrt::FA_ROWS) ||
-      !xrt::fa_make_map(&map_k, k_pool, pool_rows, xrt::FA_HD, xrt::FA_KEYS) ||
-      !xrt::fa_make_map(&map_v, v_pool, pool_rows, xrt::FA_HD, xrt::FA_KEYS))
+      !xrt::fa_make_map(&map_k, k_pool, pool_rows, xrt::FA_HD, XRT_BLOCK_TOKENS) ||
+      !xrt::fa_make_map(&map_v, v_pool, pool_rows, xrt::FA_HD, XRT_BLOCK_TOKENS))
     return XRT_ERR_UNSUPPORTED;
   static bool allowed = false;
   if (!allowed) {
-    cudaError_t err = cudaFuncSetAttribute(xrt::attention_prefill_tcgen05_kernel,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, xrt::FA_SMEM);
+    cudaError_t err = cudaFuncSetAttribute(xrt::attention_prefill_tcgen05_kernel<1>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, xrt::fa_smem_bytes(1));
     if (err != cudaSuccess) return (int)err;
     allowed = true;
   }
   dim3 grid((max_new + xrt::FA_ROWS - 1) / xrt::FA_ROWS, n_heads, n_seqs);
-  xrt::attention_prefill_tcgen05_kernel<<<grid, xrt::FA_THREADS, xrt::FA_SMEM, stream>>>(
+  xrt::attention_prefill_tcgen05_kernel<1><<<grid, 64 + 128, xrt::fa_smem_bytes(1), stream>>>(
       map_q, map_k, map_v, (__nv_bfloat16*)out, cu_seqlens, seq_slot, seq_start, block_table, max_blocks, n_heads,
       n_kv_heads, scale * 1.4426950408889634f, error_flag);
   return xrt::launch_status();
