@@ -67,6 +67,12 @@ class _Staging:
             self.events[i] = event
 
 
+def batch_bucket(n: int) -> int:
+    """Rows of the captured decode step that serves ``n`` sequences: a power of two up to 8, a
+    multiple of 8 beyond (the rows above ``n`` are padding: slot -1)."""
+    return 1 << (n - 1).bit_length() if n <= 8 else (n + 7) // 8 * 8
+
+
 def _check_entries(entries, vocab_size: int) -> None:
     if not entries:
         raise RuntimeFault("a step needs at least one sequence")
@@ -236,7 +242,7 @@ class Engine:
         model = self.model
         _check_entries(entries, model.vocab_size)
         n = len(entries)
-        bucket = 1 << (n - 1).bit_length()
+        bucket = batch_bucket(n)
         starts = [self.cache.reserve(e.slot, 1) for e in entries]
         key = (bucket, context_bucket(max(starts) + 1))
         g = self._graphs.get(key)
