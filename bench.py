@@ -208,7 +208,11 @@ def time_prefill(model, tokens: int, iters: int, warmup: int):
 
 
 def time_e2e(model, batch: int, context: int, steps: int):
-    """Decode tokens a second through Session.generate_batch: host ids in, host ids out."""
+    """Decode tokens a second through Session.generate_batch: host ids in, host ids out.  At least 256
+    decode steps: the first tenths of a second after the prompts' step (32 k tokens at full power) run
+    about 8 % slower than the steady state (measured: 5.09 ms a step right after it, 4.71 ms after a
+    pause of two seconds), and 64 steps would lie wholly inside that."""
+    steps = max(steps, 256)
     import torch
     from xeno_rt_b200 import GenerateRequest, Runtime
     runtime = Runtime(model, max_batch=batch)
