@@ -13,24 +13,29 @@ TCGEN05_MIN_NEW = 32       # prompts at least this long use the tcgen05 attentio
 PREFILL_KERNEL = os.environ.get("XRT_PREFILL_ATTN", "")  # "mma" forces the mma.sync kernel, for comparison
 FUSED_COMBINE_MAX = 32     # (tokens x kv heads) up to which the splits are merged inside the attention kernel (measured again with 6 splits at 8 sequences: the second kernel is still faster there)
 SPLIT_OVERHEAD_TILES = 2   # what a block costs beside its tiles (query load, merge, partials), in tiles of 64 keys
+SPLIT_MERGE_TILES = 0.6    # what every further split costs the merge of a (token, kv head), in the same unit (measured
+#                            at 1, 2 and 4 sequences: 16, 8..16 and 8 splits are the fastest there, not 32, 22 and 13)
 
 
 def decode_split(n_seqs: int, n_kv_heads: int, max_context: int):
     """(keys a split, number of splits) for decode attention.  Blocks run in rounds of what the GPU
-    holds at once; the time is about rounds x (tiles a split + a fixed cost), so the split count is
-    chosen to fill the last round (512 pairs of sequence and kv head in 2 splits are 2.3 rounds and
-    run like 3; in 6 splits they are 6.9 rounds of a third the length).  At least two tiles a split
-    where the context allows."""
+    holds at once; the time is about rounds x (tiles a split + a fixed cost) + a cost of merging that
+    grows with the splits, so the split count is chosen to fill the last round (512 pairs of sequence
+    and kv head in 2 splits are 2.3 rounds and run like 3; in 4 splits they are 4.6 rounds of half the
+    length).  At least two tiles a split where the context allows."""
     blocks = max(1, (max_context + 63) // 64)
     pairs = max(1, n_seqs * n_kv_heads)
     slots = SM_COUNT * DECODE_BLOCKS_PER_SM
-    best, best_cost = 1, None
+    costs = {}
     for splits in range(1, max(1, min((blocks + 1) // 2, 64)) + 1):
         tiles = -(-blocks // splits)
-        rounds = -(-pairs * (-(-blocks // tiles)) // slots)
-        cost = rounds * (tiles + SPLIT_OVERHEAD_TILES)
-        if best_cost is None or cost < best_cost:
-            best, best_cost = splits, cost
+        real = -(-blocks // tiles)  # splits that hold keys
+        rounds = -(-pairs * real // slots)
+        costs.setdefault(real, rounds * (tiles + SPLIT_OVERHEAD_TILES) + SPLIT_MERGE_TILES * real)
+    least = min(costs.values())
+    # among the counts within 4 % of the least cost: one that divides the blocks evenly if there is one, then the smallest
+    close = [n for n, c in costs.items() if c <= 1.04 * least]
+    best = min(close, key=lambda n: (blocks % n != 0, n))
     chunk = 64 * (-(-blocks // best))
     return chunk, -(-blocks * 64 // chunk)
 
