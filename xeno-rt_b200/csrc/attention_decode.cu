@@ -326,6 +326,17 @@ __global__ void attention_combine_kernel(__nv_bfloat16* __restrict__ out, const 
 constexpr int DEC_BOX_BYTES = 64 * 128;
 constexpr unsigned DEC_SPIN_LIMIT = 1u << 22;
 
+__device__ __forceinline__ uint32_t dec_map_rank(uint32_t local_smem, int rank) {  // the same place in another block of the cluster
+  uint32_t remote;
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ float dec_ld_cluster(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ bool dec_mbar_wait(uint32_t bar, uint32_t parity) {
   for (unsigned spin = 0; spin < DEC_SPIN_LIMIT; ++spin) {
     uint32_t done;
@@ -343,7 +354,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const __nv_bfloat16* __restrict__ q, const int* __restrict__ tok_slot,
                             const int* __restrict__ tok_pos, const int* __restrict__ block_table, int max_blocks,
                             int n_heads, int n_kv_heads, int head_dim, float scale_log2, int window, int chunk,
-                            int n_splits, int* __restrict__ counters, int* __restrict__ error_flag) {
+                            int n_splits, int* __restrict__ counters, int* __restrict__ error_flag, int clustered) {
   constexpr int D_TILES = HD_MAX / 8;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -354,7 +365,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int slot = tok_slot[tok];
   const int group = n_heads / n_kv_heads;
   if (slot < 0) {  // a padding row: zeros (with several splits and no counters the combine kernel writes them)
-    if (n_splits == 1 || (counters != nullptr && split == 0)) {
+    // (the same for every block of a cluster: all of them leave here, none waits for another)
+    if (n_splits == 1 || ((counters != nullptr || clustered) && split == 0)) {
       __nv_bfloat16* dst = out + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
       for (int i = threadIdx.x; i < group * head_dim; i += blockDim.x) dst[i] = __float2bfloat16_rn(0.f);
     }
@@ -364,7 +376,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int first_key = window > 0 ? max(0, len - window) : 0;
   const int begin = max(split * chunk, (first_key / XRT_BLOCK_TOKENS) * XRT_BLOCK_TOKENS);
   const int end = min((split + 1) * chunk, len);
-  if (begin >= end) return;  // this split holds no visible key: the combine step skips it too
+  const bool has_keys = begin < end;
+  if (!has_keys && !clustered) return;  // this split holds no visible key: the combine step skips it too
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int boxes = head_dim / 64;
@@ -407,8 +420,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
   HeadColumnState<D_TILES> st;
   st.init();
-  const int n_tiles = (end - begin + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS;  // begin is a multiple of 64
-  if (threadIdx.x == 0) issue_tile(0, 0);
+  const int n_tiles = has_keys ? (end - begin + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS : 0;  // begin is a multiple of 64
+  if (threadIdx.x == 0 && n_tiles > 0) issue_tile(0, 0);
   int failed = 0, i = 0;
   for (; i < n_tiles; ++i) {
     // the buffer of tile i + 1 held tile i - 1, which every warp left before the barrier that ended the last round
@@ -429,7 +442,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       if (i + 1 < n_tiles) dec_mbar_wait(full_addr[(i + 1) & 1], (uint32_t)((i + 1) >> 1) & 1u);
     }
     __syncthreads();
-    return;
+    if (!clustered) return;  // in a cluster the block still meets the others (its state below is meaningless)
   }
 
   // this warp's state into the merge area: row = head; the sums are spread over the lanes of a t
@@ -452,8 +465,57 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         merge_o[((size_t)warp * 16 + 2 * t + (e & 1)) * merge_stride + dt * 16 + g + (e >> 1) * 8] = st.o[dt][e];
     }
   }
-  decode_finish(smem, out, part_o, part_ml, counters, tok, kv_head, split, n_splits, chunk, first_key, len, group, n_heads,
-                n_kv_heads, head_dim);
+  if (!clustered) {
+    decode_finish(smem, out, part_o, part_ml, counters, tok, kv_head, split, n_splits, chunk, first_key, len, group, n_heads,
+                  n_kv_heads, head_dim);
+    return;
+  }
+
+  // The splits of a (token, kv head) are the blocks of one thread-block cluster: each leaves its
+  // merged (m, l, o) in its own shared memory, the cluster meets, and block `split` merges one slice
+  // of the outputs from all blocks' shared memory (distributed shared memory), in split order.
+  // No partials in global memory, no second kernel, no counter.
+  __syncthreads();
+  float* cta_ml = merge_o + DEC_WARPS * 16 * merge_stride;  // [group][2], behind the warps' states
+  float* cta_o = cta_ml + 2 * 16;                           // [group][head_dim]
+  for (int idx = threadIdx.x; idx < group * head_dim; idx += blockDim.x) {
+    const int row = idx / head_dim, d = idx - row * head_dim;
+    float m = -INFINITY, l = 0.f, o = 0.f;
+    if (has_keys) {
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, merge_m[w * 16 + row]);
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; ++w) {
+        const float mw = merge_m[w * 16 + row];
+        const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
+        l += f * merge_l[w * 16 + row];
+        o += f * merge_o[((size_t)w * 16 + row) * merge_stride + d];
+      }
+    }
+    cta_o[idx] = o;
+    if (d == 0) { cta_ml[row * 2] = m; cta_ml[row * 2 + 1] = l; }
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  {
+    const int total = group * head_dim;
+    const int per = (total + n_splits - 1) / n_splits;
+    const uint32_t ml_local = smem_addr(cta_ml), o_local = smem_addr(cta_o);
+    for (int idx = split * per + threadIdx.x; idx < min(total, (split + 1) * per); idx += blockDim.x) {
+      const int row = idx / head_dim;
+      float m = -INFINITY;
+      for (int s2 = 0; s2 < n_splits; ++s2) m = fmaxf(m, dec_ld_cluster(dec_map_rank(ml_local + row * 8, s2)));
+      float l = 0.f, o = 0.f;
+      for (int s2 = 0; s2 < n_splits; ++s2) {
+        const float ms = dec_ld_cluster(dec_map_rank(ml_local + row * 8, s2));
+        const float f = ms == -INFINITY ? 0.f : exp2f(ms - m);
+        l += f * dec_ld_cluster(dec_map_rank(ml_local + row * 8 + 4, s2));
+        o += f * dec_ld_cluster(dec_map_rank(o_local + idx * 4, s2));
+      }
+      out[((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim + idx] = __float2bfloat16_rn(o / l);
+    }
+  }
+  // nobody leaves while another block may still read its shared memory
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 typedef CUresult (*DecEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -486,17 +548,40 @@ static bool dec_make_map(CUtensorMap* map, const void* base, long long rows, int
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+constexpr int DEC_MAX_CLUSTER = 16;
+
+// shared memory of the TMA kernel: the tiles (or the warps' states that reuse their room), then a
+// block's merged state for the cluster merge
+inline int decode_tma_smem(int head_dim) {
+  const int merge_bytes = DEC_WARPS * 16 * (2 + head_dim + 8) * (int)sizeof(float) + (2 * 16 + 8 * head_dim) * (int)sizeof(float);
+  return 1024 + max(4 * (head_dim / 64) * DEC_BOX_BYTES, merge_bytes);
+}
+
+// XRT_DECODE_ATTN=nocluster keeps the merge by a second kernel or by the last block, for comparison.
+// Only for few (token, kv head) pairs: measured at the 8B shape, clusters win at 1 to 4 sequences (3.77
+// against 3.87 ms and 4.12 against 4.25 ms a step) and lose at 8 (4.90 against 4.68 ms: clusters of 6
+// blocks of 66 KB each are harder to place than single blocks).
+constexpr int DEC_CLUSTER_MAX_PAIRS = 32;
+
+inline bool decode_cluster_wanted(int n_splits, int pairs) {
+  static int off = -1;
+  if (off < 0) {
+    const char* env = getenv("XRT_DECODE_ATTN");
+    off = (env != nullptr && env[0] == 'n') ? 1 : 0;
+  }
+  return !off && n_splits >= 2 && n_splits <= DEC_MAX_CLUSTER && pairs <= DEC_CLUSTER_MAX_PAIRS;
+}
+
 template <int HD_MAX>
 int launch_decode_tma(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_bfloat16* q,
                       const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, long long pool_rows, const int* tok_slot,
                       const int* tok_pos, const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
                       int head_dim, float scale, int window, int chunk, int n_splits, int* counters, int* error_flag,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, bool* merged) {
   CUtensorMap map_k, map_v;
   if (!dec_make_map(&map_k, k_pool, pool_rows, head_dim) || !dec_make_map(&map_v, v_pool, pool_rows, head_dim))
     return XRT_ERR_UNSUPPORTED;
-  const int merge_bytes = DEC_WARPS * 16 * (2 + head_dim + 8) * (int)sizeof(float);
-  const int smem = 1024 + max(4 * (head_dim / 64) * DEC_BOX_BYTES, merge_bytes);
+  const int smem = decode_tma_smem(head_dim);
   auto kernel = attention_decode_tma_kernel<HD_MAX>;
   static int smem_allowed = 0;  // raised once a size class; not a stream operation
   if (smem > 48 * 1024 && smem > smem_allowed) {
@@ -504,10 +589,53 @@ int launch_decode_tma(__nv_bfloat16* out, float* part_o, float* part_ml, const _
     if (err != cudaSuccess) return (int)err;
     smem_allowed = smem;
   }
-  dim3 grid(n_splits, n_kv_heads, n_tokens);
-  launch_kernel(kernel, grid, dim3(DEC_WARPS * 32), (size_t)smem, stream, map_k, map_v, out, part_o, part_ml, q, tok_slot,
-                tok_pos, block_table, max_blocks, n_heads, n_kv_heads, head_dim, scale * 1.4426950408889634f, window,
-                chunk, n_splits, counters, error_flag);
+  // 2 to 16 splits: the splits of a (token, kv head) as one thread-block cluster that merges itself
+  // through distributed shared memory, if the device can hold such a cluster (asked once a size)
+  static int cluster_ok[DEC_MAX_CLUSTER + 1][5] = {};  // by splits and head-size class: 0 unknown, 1 yes, 2 no
+  const bool clustered = decode_cluster_wanted(n_splits, n_tokens * n_kv_heads) && [&]() {
+    int& known = cluster_ok[n_splits][HD_MAX / 64];
+    if (known == 0) {
+      known = 2;
+      if (n_splits <= 8 || cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+        cudaLaunchConfig_t probe = {};
+        probe.gridDim = dim3(n_splits, 1, 1);
+        probe.blockDim = dim3(DEC_WARPS * 32);
+        probe.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = n_splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        probe.attrs = attr;
+        probe.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &probe) == cudaSuccess && clusters >= 1) known = 1;
+        cudaGetLastError();  // a refusal here is an answer, not an error of the stream
+      }
+    }
+    return known == 1;
+  }();
+  *merged = clustered;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(n_splits, n_kv_heads, n_tokens);
+  config.blockDim = dim3(DEC_WARPS * 32);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int n_attrs = 0;
+  if (pdl_enabled()) {
+    attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attrs;
+  }
+  if (clustered) {
+    attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+    attrs[n_attrs].val.clusterDim.x = n_splits; attrs[n_attrs].val.clusterDim.y = 1; attrs[n_attrs].val.clusterDim.z = 1;
+    ++n_attrs;
+  }
+  config.attrs = n_attrs ? attrs : nullptr;
+  config.numAttrs = n_attrs;
+  cudaLaunchKernelEx(&config, kernel, map_k, map_v, out, part_o, part_ml, q, tok_slot, tok_pos, block_table, max_blocks,
+                     n_heads, n_kv_heads, head_dim, scale * 1.4426950408889634f, window, chunk, n_splits, counters, error_flag,
+                     clustered ? 1 : 0);
   return launch_status();
 }
 
@@ -542,7 +670,8 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_
                   const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, long long pool_rows, const int* tok_slot,
                   const int* tok_pos, const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
                   int head_dim, float scale, int window, int chunk, int n_splits, int* counters, int* error_flag,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, bool* merged) {
+  *merged = false;
   static int rows_only = -1, copies_only = 0;
   if (rows_only < 0) {
     const char* env = getenv("XRT_DECODE_ATTN");
@@ -553,7 +682,7 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_
       (((uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0)
     return launch_decode_tma<HD_MAX>(out, part_o, part_ml, q, k_pool, v_pool, pool_rows, tok_slot, tok_pos, block_table,
                                      max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
-                                     counters, error_flag, stream);
+                                     counters, error_flag, stream, merged);
   if (n_heads / n_kv_heads <= 8 && !rows_only)
     return launch_decode_as<HD_MAX, true>(out, part_o, part_ml, q, k_pool, v_pool, tok_slot, tok_pos, block_table,
                                           max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk,
@@ -574,7 +703,7 @@ static int attention_decode_impl(void* out, float* part_o, float* part_ml, const
                                  const void* v_pool, int n_blocks, const int* tok_slot, const int* tok_pos,
                                  const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
                                  int head_dim, float scale, int window, int chunk, int n_splits, int* counters,
-                                 int* error_flag, cudaStream_t stream) {
+                                 int* error_flag, cudaStream_t stream, int* merged_out = nullptr) {
   if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || chunk <= 0 || n_splits <= 0)
     return XRT_ERR_ARGUMENT;
   if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256 || n_heads / n_kv_heads > 16 ||
@@ -587,17 +716,19 @@ static int attention_decode_impl(void* out, float* part_o, float* part_ml, const
   auto* kp = (const __nv_bfloat16*)k_pool;
   auto* vp = (const __nv_bfloat16*)v_pool;
   int status;
+  bool merged = false;  // the attention kernel merged its splits itself (as clusters)
   const long long pool_rows = (long long)n_blocks * n_kv_heads * XRT_BLOCK_TOKENS;  // 0: the pools' size is not known
 #define XRT_DECODE(HD) status = launch_decode<HD>(o, part_o, part_ml, qp, kp, vp, pool_rows, tok_slot, tok_pos, block_table, \
                                                   max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window,      \
-                                                  chunk, n_splits, counters, error_flag, stream)
+                                                  chunk, n_splits, counters, error_flag, stream, &merged)
   if (head_dim <= 32) XRT_DECODE(32);
   else if (head_dim <= 64) XRT_DECODE(64);
   else if (head_dim <= 128) XRT_DECODE(128);
   else XRT_DECODE(256);
 #undef XRT_DECODE
   if (status != XRT_OK) return status;
-  if (n_splits > 1 && counters == nullptr) {
+  if (merged_out != nullptr) *merged_out = merged ? 1 : 0;
+  if (n_splits > 1 && counters == nullptr && !merged) {
     const int warps = n_tokens * n_heads;
     launch_kernel(attention_combine_kernel, dim3((warps * 32 + 255) / 256), dim3(256), 0, stream, o,
                   (const float*)part_o, (const float*)part_ml, tok_slot, tok_pos, n_tokens, n_heads, head_dim, window,
@@ -615,16 +746,18 @@ static int attention_decode_impl(void* out, float* part_o, float* part_ml, const
 // head_dim] and part_ml: float32 [n_tokens * n_heads * n_splits * 2] are scratch, needed when
 // n_splits > 1.  The group n_heads / n_kv_heads is at most 16; n_tokens at most 65535.
 // n_blocks: blocks in each pool (0 if unknown: the kernels fed by TMA are then not used); error_flag
-// (may be null): raised if a bounded wait on a copy ran out.
+// (may be null): raised if a bounded wait on a copy ran out; *merged (may be null) is set to 1 when
+// the attention kernel merged its splits itself, as thread-block clusters (then the partials are not
+// touched and no second kernel runs), else 0.
 // This entry point merges the splits with a second kernel.
 XRT_EXPORT int xrt_attention_decode(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
                                     const void* v_pool, int n_blocks, const int* tok_slot, const int* tok_pos,
                                     const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
                                     int head_dim, float scale, int window, int chunk, int n_splits, int* error_flag,
-                                    cudaStream_t stream) {
+                                    cudaStream_t stream, int* merged) {
   return xrt::attention_decode_impl(out, part_o, part_ml, q, k_pool, v_pool, n_blocks, tok_slot, tok_pos, block_table,
                                     max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
-                                    nullptr, error_flag, stream);
+                                    nullptr, error_flag, stream, merged);
 }
 
 // The same, with the merge done by the block that brings a (token, kv head)'s last split: one
@@ -634,11 +767,11 @@ XRT_EXPORT int xrt_attention_decode_fused(void* out, float* part_o, float* part_
                                           const void* k_pool, const void* v_pool, int n_blocks, const int* tok_slot,
                                           const int* tok_pos, const int* block_table, int max_blocks, int n_tokens,
                                           int n_heads, int n_kv_heads, int head_dim, float scale, int window, int chunk,
-                                          int n_splits, int* error_flag, cudaStream_t stream) {
+                                          int n_splits, int* error_flag, cudaStream_t stream, int* merged) {
   if (counters == nullptr) return XRT_ERR_ARGUMENT;
   return xrt::attention_decode_impl(out, part_o, part_ml, q, k_pool, v_pool, n_blocks, tok_slot, tok_pos, block_table,
                                     max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
-                                    counters, error_flag, stream);
+                                    counters, error_flag, stream, merged);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -710,7 +843,7 @@ int xrt_attention_decode_static(void* out, const void* q, const void* k_pool, co
   // the pools' size is not among this entry's arguments: 0 keeps it on the kernels that need no tensor map
   const int status = xrt_attention_decode(out, scratch + ml_floats, scratch, q, k_pool, v_pool, 0, tok_slot, tok_pos,
                                           block_table, max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale,
-                                          window, chunk, n_splits, nullptr, stream);
+                                          window, chunk, n_splits, nullptr, stream, nullptr);
   if (status == XRT_ERR_ARGUMENT) xrt::refuse(message, message_len, "xrt_attention_decode_static: the kernel refused its arguments");
   if (status == XRT_ERR_UNSUPPORTED)
     xrt::refuse(message, message_len, "xrt_attention_decode_static: head_dim must be a multiple of 16 up to 256, at most "

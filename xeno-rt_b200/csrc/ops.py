@@ -35,8 +35,8 @@ _SIGNATURES = {
     "xrt_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_gemm_decode_tcgen05": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "xrt_attention_decode_fused": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P],
-    "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P],
+    "xrt_attention_decode_fused": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P],
+    "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P],
     "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "xrt_attention_prefill_tcgen05": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
@@ -467,6 +467,7 @@ def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_h
     if k_pool.shape != v_pool.shape or k_pool.shape[1:] != (n_kv_heads, 64, head_dim):
         raise KernelError("attention_decode: the cache pool must be [blocks, kv heads, 64, head_dim]")
     part_o = part_ml = None
+    merged = ctypes.c_int(0)  # set by the launcher when the splits merged themselves as clusters
     flag = error_flag(q.device)
     if n_splits > 1:
         part_o = torch.empty(n * n_heads * n_splits * head_dim, dtype=torch.float32, device=q.device)
@@ -478,15 +479,17 @@ def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_h
             _ptr(q, "q", torch.bfloat16), _ptr(k_pool, "k_pool", torch.bfloat16), _ptr(v_pool, "v_pool", torch.bfloat16),
             k_pool.shape[0], _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
             _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
-            float(scale), int(window), int(chunk), int(n_splits), flag.data_ptr(), _stream()), "attention_decode")
+            float(scale), int(window), int(chunk), int(n_splits), flag.data_ptr(), _stream(), ctypes.byref(merged)),
+            "attention_decode")
         return
     _check(_kernels().xrt_attention_decode(
         _ptr(out, "out", torch.bfloat16), _ptr(part_o, "part_o"), _ptr(part_ml, "part_ml"),
         _ptr(q, "q", torch.bfloat16), _ptr(k_pool, "k_pool", torch.bfloat16), _ptr(v_pool, "v_pool", torch.bfloat16),
         k_pool.shape[0], _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
         _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
-        float(scale), int(window), int(chunk), int(n_splits), flag.data_ptr(), _stream()), "attention_decode")
-    if n_splits > 1:
+        float(scale), int(window), int(chunk), int(n_splits), flag.data_ptr(), _stream(), ctypes.byref(merged)),
+        "attention_decode")
+    if n_splits > 1 and not merged.value:
         add_launches(1)  # the combine kernel
 
 

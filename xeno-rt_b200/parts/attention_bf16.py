@@ -13,6 +13,10 @@ TCGEN05_MIN_NEW = 32       # prompts at least this long use the tcgen05 attentio
 PREFILL_KERNEL = os.environ.get("XRT_PREFILL_ATTN", "")  # "mma" forces the mma.sync kernel, for comparison
 FUSED_COMBINE_MAX = 32     # (tokens x kv heads) up to which the splits are merged inside the attention kernel (measured again with 6 splits at 8 sequences: the second kernel is still faster there)
 SPLIT_OVERHEAD_TILES = 2   # what a block costs beside its tiles (query load, merge, partials), in tiles of 64 keys
+CLUSTER_MAX_PAIRS, CLUSTER_MAX_SPLITS = 32, 16  # up to so many (token, kv head) pairs the kernel runs a pair's splits
+#                            as one thread-block cluster that merges itself through distributed shared memory (csrc/
+#                            attention_decode.cu has the same two numbers); a split then costs the merge far less
+CLUSTER_MERGE_TILES = 0.2
 SPLIT_MERGE_TILES = 0.6    # what every further split costs the merge of a (token, kv head), in the same unit (measured
 #                            at 1, 2 and 4 sequences: 16, 8..16 and 8 splits are the fastest there, not 32, 22 and 13)
 
@@ -30,8 +34,12 @@ def decode_split(n_seqs: int, n_kv_heads: int, max_context: int):
     for splits in range(1, max(1, min((blocks + 1) // 2, 64)) + 1):
         tiles = -(-blocks // splits)
         real = -(-blocks // tiles)  # splits that hold keys
-        rounds = -(-pairs * real // slots)
-        costs.setdefault(real, rounds * (tiles + SPLIT_OVERHEAD_TILES) + SPLIT_MERGE_TILES * real)
+        clustered = pairs <= CLUSTER_MAX_PAIRS and real <= CLUSTER_MAX_SPLITS
+        # whole clusters have to find room: about two blocks a multiprocessor instead of three (measured at 4
+        # sequences: 8 splits, 256 blocks, beat 13 and 16)
+        rounds = -(-pairs * real // (SM_COUNT * 2 if clustered else slots))
+        merge = CLUSTER_MERGE_TILES if clustered else SPLIT_MERGE_TILES
+        costs.setdefault(real, rounds * (tiles + SPLIT_OVERHEAD_TILES) + merge * real)
     least = min(costs.values())
     # among the counts within 4 % of the least cost: one that divides the blocks evenly if there is one, then the smallest
     close = [n for n, c in costs.items() if c <= 1.04 * least]
