@@ -360,12 +360,15 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full[2];
   pdl_trigger();
-  pdl_wait();
+  // The step's arrays (slots, positions, block table) were written before the step began: they may be
+  // read, and tiles of old keys fetched, while the kernel before this one (which writes q and the
+  // newest key and value) is still running.
   const int split = blockIdx.x, kv_head = blockIdx.y, tok = blockIdx.z;
   const int slot = tok_slot[tok];
   const int group = n_heads / n_kv_heads;
   if (slot < 0) {  // a padding row: zeros (with several splits and no counters the combine kernel writes them)
     // (the same for every block of a cluster: all of them leave here, none waits for another)
+    pdl_wait();
     if (n_splits == 1 || ((counters != nullptr || clustered) && split == 0)) {
       __nv_bfloat16* dst = out + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
       for (int i = threadIdx.x; i < group * head_dim; i += blockDim.x) dst[i] = __float2bfloat16_rn(0.f);
@@ -377,7 +380,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int begin = max(split * chunk, (first_key / XRT_BLOCK_TOKENS) * XRT_BLOCK_TOKENS);
   const int end = min((split + 1) * chunk, len);
   const bool has_keys = begin < end;
-  if (!has_keys && !clustered) return;  // this split holds no visible key: the combine step skips it too
+  if (!has_keys && !clustered) { pdl_wait(); return; }  // this split holds no visible key: the combine step skips it too
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int boxes = head_dim / 64;
@@ -409,6 +412,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   };
 
   // query operand: column g = head g of the group (zero at or beyond the group)
+  // the first tile before the wait, unless it holds the newest key (position len - 1)
+  const bool early = has_keys && begin + XRT_BLOCK_TOKENS <= len - 1;
+  if (threadIdx.x == 0 && early) issue_tile(0, 0);
+  pdl_wait();
   const __nv_bfloat16* qt = q + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
   uint32_t qb[D_TILES / 2][2];
 #pragma unroll
@@ -421,7 +428,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   HeadColumnState<D_TILES> st;
   st.init();
   const int n_tiles = has_keys ? (end - begin + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS : 0;  // begin is a multiple of 64
-  if (threadIdx.x == 0 && n_tiles > 0) issue_tile(0, 0);
+  if (threadIdx.x == 0 && n_tiles > 0 && !early) issue_tile(0, 0);
   int failed = 0, i = 0;
   for (; i < n_tiles; ++i) {
     // the buffer of tile i + 1 held tile i - 1, which every warp left before the barrier that ended the last round
