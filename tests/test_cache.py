@@ -116,9 +116,49 @@ def test_groups_have_storage_of_their_own_and_state_is_zeroed():
     assert c.open_slot() == s and float(state[s].abs().sum()) == 0.0 and float(extra[s].abs().sum()) == 0.0
 
 
-def test_random_traffic_never_loses_or_doubles_a_block():
+def test_a_windowed_group_gives_blocks_back_as_the_sequence_moves_on():
+    """Window of 70 keys: a token at position p sees p-69 .. p.  Block b (positions 64 b .. 64 b + 63) may
+    go once the sequence's length L has 64 b + 63 <= L - 70; the group that keeps every key holds on."""
+    c = _cache(max_tokens=64 * 8, max_positions=512, needs=[KVNeed(2, 16), KVNeed(2, 16, window=70)], max_slots=3)
+    full, windowed = c.kv_groups
+    assert full.need.window is None and windowed.need.window == 70
+    s = c.open_slot()
+    c.reserve(s, 133)
+    assert windowed.allocator.held == 3  # the prompt's own step needs every block: its first tokens see the first keys
+    c.advance(s, 133)  # the next token, at 133, sees 64 .. 133: block 0 (0 .. 63) is done
+    assert windowed.allocator.held == 2 and full.allocator.held == 3
+    assert windowed.table_host[s, 0] == -1 and windowed.table_host[s, 1] >= 0
+    c.check()
+    c.reserve(s, 1)
+    c.advance(s, 1)  # length 134: the next token sees 65 .. 134; block 1 still holds visible keys
+    assert windowed.allocator.held == 2
+    for _ in range(62):
+        c.reserve(s, 1)
+        c.advance(s, 1)
+    assert c.length(s) == 196 and windowed.allocator.held == 3  # block 3 was taken for 192 ..; block 1 still needed
+    released = int(windowed.table_host[s, 1])
+    c.reserve(s, 1)
+    c.advance(s, 1)  # length 197: the next token sees 128 .. 197, so block 1 (64 .. 127) is done
+    assert windowed.allocator.held == 2 and windowed.table_host[s, 1] == -1
+    c.check()
+    # what was given back is used by another sequence while the first one lives on
+    t = c.open_slot()
+    c.reserve(t, 10)
+    assert int(windowed.table_host[t, 0]) == released and int(full.table_host[t, 0]) == 4  # used again; the other group has no old block
+    c.advance(t, 10)
+    c.check()
+    c.close_slot(s)
+    c.close_slot(t)
+    assert windowed.allocator.free == 8 and full.allocator.free == 8
+    c.check()
+    with pytest.raises(CacheError, match="not open"):
+        c.close_slot(s)
+
+
+@pytest.mark.parametrize("window", [None, 100])
+def test_random_traffic_never_loses_or_doubles_a_block(window):
     rng = random.Random(3)
-    c = _cache(max_tokens=64 * 20, max_positions=640, max_slots=6)
+    c = _cache(max_tokens=64 * 20, max_positions=640, max_slots=6, needs=[KVNeed(2, 16), KVNeed(2, 16, window=window)])
     live = {}
     for _ in range(400):
         op = rng.random()
@@ -142,4 +182,4 @@ def test_random_traffic_never_loses_or_doubles_a_block():
             assert c.length(s) == n
     for s in list(live):
         c.close_slot(s)
-    assert c.blocks_free() == 20 and c.slots.free == 6
+    assert all(g.allocator.free == 20 for g in c.kv_groups) and c.slots.free == 6

@@ -262,6 +262,100 @@ def test_a_layer_named_twice_and_a_layer_reading_anothers_cache():
     assert np.abs(_run_cut(engine, tokens, [50] + [1] * 30) - want).max() / np.abs(want).max() < 2e-5
 
 
+def _windowed_spec():
+    """Three attention layers of one shape: keys of the last 70 positions, every key, and the last 150
+    positions read from the first layer's storage (which must then keep 150)."""
+    from xeno_rt_b200.parts import LayerSpec, ModelSpec, PartSpec, SchedulePlace
+    d, vocab = 40, 50
+    norm = lambda name: PartSpec("rmsnorm", {"width": d, "eps": 1e-5}, {"weight": name})
+    attn = lambda i, window: PartSpec(
+        "attention", {"width": d, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16, "qk_norm": False, "eps": 1e-5,
+                      "window": window,
+                      "position": {"kind": "rotary", "params": {"rope_dim": 16, "base": 100.0, "scale": 1.0}}},
+        {"q": f"l{i}.q", "k": f"l{i}.k", "v": f"l{i}.v", "o": f"l{i}.o"})
+    ffn = lambda i: PartSpec("swiglu", {"width": d, "inner": 24}, {"gate": f"l{i}.g", "up": f"l{i}.u", "down": f"l{i}.d"})
+    layer = lambda i, window: LayerSpec(norm(f"l{i}.n1"), attn(i, window), norm(f"l{i}.n2"), ffn(i))
+    return ModelSpec(vocab_size=vocab, hidden_size=d, max_positions=512,
+                     embedding=PartSpec("token", {"vocab_size": vocab, "width": d}, {"weight": "emb"}),
+                     layers=[layer(0, 70), layer(1, None), layer(2, 150)],
+                     schedule=[SchedulePlace(0), SchedulePlace(1), SchedulePlace(0)],
+                     final_norm=norm("fn"),
+                     lm_head=PartSpec("linear", {"vocab_size": vocab, "width": d}, {"weight": "emb"}))
+
+
+def _plain_windowed(tensors, schedule, tokens):
+    """schedule: (layer, window, place whose keys it reads or None) for each place."""
+    w = {k: f64(v) for k, v in tensors.items()}
+    x = pm.embedding(w["emb"], tokens)
+    pos = np.arange(len(tokens))
+    kv_of_place = {}
+    for i, (layer, window, cache_from) in enumerate(schedule):
+        h = pm.rmsnorm(x, w[f"l{layer}.n1"], 1e-5)
+        q = pm.rope(pm.linear(h, w[f"l{layer}.q"]), pos, 2, 16, 16, 100.0, 1.0)
+        if cache_from is None:
+            kv_of_place[i] = (pm.rope(pm.linear(h, w[f"l{layer}.k"]), pos, 1, 16, 16, 100.0, 1.0),
+                              pm.linear(h, w[f"l{layer}.v"]))
+        k, v = kv_of_place[i if cache_from is None else cache_from]
+        x = x + pm.linear(pm.causal_gqa_attention(q, k, v, 2, 1, 16, window=window), w[f"l{layer}.o"])
+        h = pm.rmsnorm(x, w[f"l{layer}.n2"], 1e-5)
+        x = x + pm.linear(pm.swiglu(pm.linear(h, w[f"l{layer}.g"]), pm.linear(h, w[f"l{layer}.u"])), w[f"l{layer}.d"])
+    return pm.linear(pm.rmsnorm(x, w["fn"], 1e-5), w["emb"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_windowed_and_full_layers_in_one_model_release_their_blocks(dtype):
+    """Layers that see a window of keys have a storage group of their own that gives blocks back while
+    the sequence runs; the results must be those of plain windowed attention at every position,
+    however the tokens are cut, and with a second sequence taking the blocks that the first gave back."""
+    from xeno_rt_b200.engine import Engine, StepEntry
+    from xeno_rt_b200.parts import SchedulePlace
+    tol = {"float32": 2e-5, "bfloat16": 3e-2}[dtype]
+    spec = _windowed_spec()
+    model, tensors = _toy_model(spec, dtype)
+    engine = Engine(model, 64 * 12)
+    groups = {g.need.window: g for g in engine.cache.kv_groups}
+    assert set(groups) == {70, None}
+    tokens = np.random.default_rng(5).integers(0, 50, size=330).tolist()
+    want = _plain_windowed(tensors, [(0, 70, None), (1, None, None), (0, 70, None)], tokens)
+    scale = np.abs(want).max()
+    assert np.abs(want - _plain_windowed(tensors, [(0, None, None), (1, None, None), (0, None, None)], tokens)).max() \
+        > 0.05 * scale  # the window matters for these weights
+    assert np.abs(_run_cut(engine, tokens, [330]) - want).max() / scale < tol
+    assert np.abs(_run_cut(engine, tokens, [100, 130] + [1] * 100) - want).max() / scale < tol
+
+    # two sequences of unequal lengths; the longer one gives blocks back that the next batch's sequences take
+    other = np.random.default_rng(6).integers(0, 50, size=200).tolist()
+    want_other = _plain_windowed(tensors, [(0, 70, None), (1, None, None), (0, 70, None)], other)
+    for _ in range(2):
+        a, b = engine.open_slot(), engine.open_slot()
+        got_a = [engine.step([StepEntry(a, tokens[:150], list(range(150))), StepEntry(b, other[:90], list(range(90)))])]
+        got_b = [got_a[0][150:]]
+        got_a[0] = got_a[0][:150]
+        for i in range(110):
+            out = engine.step([StepEntry(a, [tokens[150 + i]], [0]), StepEntry(b, [other[90 + i]], [0])])
+            got_a.append(out[:1]); got_b.append(out[1:])
+            engine.cache.check()
+        engine.close_slot(b)
+        for i in range(70):
+            got_a.append(engine.step([StepEntry(a, [tokens[260 + i]], [0])]))
+        # length 330: positions up to 330 - 70 are behind the window: blocks 0 .. 3 of six are given back
+        # (a block number stands for that block of every place of the group)
+        assert groups[70].allocator.held == 2 and groups[None].allocator.held == 6
+        engine.close_slot(a)
+        assert np.abs(torch.cat(got_a).cpu().numpy() - want).max() / scale < tol
+        assert np.abs(torch.cat(got_b).cpu().numpy() - want_other).max() / np.abs(want_other).max() < tol
+    assert engine.cache.blocks_free() == engine.cache.n_blocks
+
+    # a layer that sees 150 keys reads the storage of the layer that sees 70: the storage keeps 150
+    spec = _windowed_spec()
+    spec.schedule = [SchedulePlace(0), SchedulePlace(1), SchedulePlace(2, cache_from=0)]
+    model = type(model)(spec, tensors, model.dtype, DEV)
+    engine = Engine(model, 64 * 12)
+    assert {g.need.window for g in engine.cache.kv_groups} == {150, None}
+    want = _plain_windowed(tensors, [(0, 70, None), (1, None, None), (2, 150, 0)], tokens)
+    assert np.abs(_run_cut(engine, tokens, [200] + [1] * 130) - want).max() / np.abs(want).max() < tol
+
+
 class RoutedFeedForward:
     """A toy feed-forward with routing: a 32-bit softmax router over E experts picks one expert a
     token; y = p_e * W2_e . relu(W1_e . h).  Defined here, never in the framework."""

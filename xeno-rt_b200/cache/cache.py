@@ -4,6 +4,9 @@
 * **Block storage** for keys and values: a pool of blocks of 64 token positions for each group of
   layers with the same need; a sequence holds ceil(length / 64) blocks of every group, listed in
   the group's block table; blocks go back to the pool when the slot is closed and are used again.
+  A group whose layers see only a window of the most recent keys gives a block back as soon as the
+  sequence has moved past it: no later token can see its keys (its table entry becomes -1, and the
+  attention kernels start at the block that holds the window's first key).
 * **Fixed-size state** per sequence: per layer for mixers that ask for it (``StateNeed``), and per
   sequence for whoever registers some (the sampler keeps its generator state and the set of seen
   token ids here).  State is zeroed when a slot is opened.
@@ -59,6 +62,15 @@ class _KVGroup:
         self.table_host = np.full((max_slots, blocks_per_seq), -1, dtype=np.int32)
         self.table = torch.full((max_slots, blocks_per_seq), -1, dtype=torch.int32, device=device)
         self.dirty: set[int] = set()
+        self.first_block = [0] * max_slots  # blocks before it were given back (windowed groups)
+
+    def blocks_behind_the_window(self, length: int) -> int:
+        """How many leading blocks hold no key that a token at position ``length`` or later sees:
+        such a token sees positions > its own - window, so a block is done when its last
+        position, 64 b + 63, is <= length - window."""
+        if self.need.window is None:
+            return 0
+        return max(0, (length - int(self.need.window) + 1) // BLOCK_TOKENS)
 
     def nbytes(self) -> int:
         return 2 * self.k.numel() * self.k.element_size()
@@ -153,8 +165,9 @@ class Cache:
             raise CacheError(f"slot {slot} is not open (closed twice, or never opened)")
         n = self._n_seq_blocks[slot]
         for group in self.kv_groups:
-            group.allocator.give_back(int(b) for b in group.table_host[slot, :n])
+            group.allocator.give_back(int(b) for b in group.table_host[slot, group.first_block[slot]:n])
             group.table_host[slot, :n] = -1
+            group.first_block[slot] = 0
             group.dirty.add(slot)
         self._n_seq_blocks[slot] = 0
         self.lengths[slot] = 0
@@ -194,6 +207,16 @@ class Cache:
         if self.length(slot) + n_new > self._n_seq_blocks[slot] * BLOCK_TOKENS:
             raise CacheError(f"slot {slot}: advancing by {n_new} passes what was reserved")
         self.lengths[slot] += n_new
+        for group in self.kv_groups:
+            done = min(group.blocks_behind_the_window(self.lengths[slot]), self._n_seq_blocks[slot])
+            first = group.first_block[slot]
+            if done > first:
+                # Kernels already launched still read the old table and the old blocks: the table
+                # changes with the next flush and the blocks are written again only by later steps.
+                group.allocator.give_back(int(b) for b in group.table_host[slot, first:done])
+                group.table_host[slot, first:done] = -1
+                group.first_block[slot] = done
+                group.dirty.add(slot)
 
     def flush_tables(self) -> None:
         """Brings the device block tables up to date with the host's (before kernels read them)."""
@@ -222,9 +245,14 @@ class Cache:
             for slot in range(self.max_slots):
                 row = group.table_host[slot]
                 n = self._n_seq_blocks[slot] if self.slots.is_open(slot) else 0
-                if (row[n:] != -1).any():
+                first = group.first_block[slot] if self.slots.is_open(slot) else 0
+                if (row[n:] != -1).any() or (row[:first] != -1).any():
                     raise CacheError(f"slot {slot} lists blocks beyond what it holds")
-                held.extend(int(b) for b in row[:n])
+                if (row[first:n] < 0).any():
+                    raise CacheError(f"slot {slot} misses a block that it should hold")
+                if first > group.blocks_behind_the_window(self.lengths[slot]):
+                    raise CacheError(f"slot {slot} gave back a block that its window still covers")
+                held.extend(int(b) for b in row[first:n])
             if len(held) != len(set(held)):
                 raise CacheError("a block is listed by two sequences")
             if len(held) != group.allocator.held:

@@ -6,9 +6,11 @@ reference, shapes are checked at load and the model is assembled from registered
 """
 from __future__ import annotations
 
+import dataclasses
+
 import torch
 
-from ..cache import Cache
+from ..cache import Cache, KVNeed
 from ..config import config_from_dict, load_config
 from ..core import DType, KernelError, log, parse_dtype, torch_dtype
 from ..csrc import ops
@@ -89,6 +91,15 @@ class Model:
         needs = []
         for place in self.spec.schedule:
             needs.append(None if place.cache_from is not None else self.layers[place.layer].mixer.cache_need())
+        # A place that reads another place's keys may see further back than the owner does: the
+        # storage keeps the widest window of all its users (None = every key).
+        for place in self.spec.schedule:
+            if place.cache_from is None:
+                continue
+            owner, reader = needs[place.cache_from], self.layers[place.layer].mixer.cache_need()
+            if isinstance(owner, KVNeed) and isinstance(reader, KVNeed) and owner.window is not None:
+                wider = None if reader.window is None else max(owner.window, reader.window)
+                needs[place.cache_from] = dataclasses.replace(owner, window=wider)
         return needs
 
     def new_cache(self, max_tokens: int, max_slots: int | None = None) -> Cache:
