@@ -252,10 +252,11 @@ def run_ours(args) -> int:
     torch.cuda.synchronize()
     setup_s = time.time() - t0
 
-    if args.only == "prefill":  # a short run for profiling: one prompt of 2,048 tokens
-        prefill_ms = time_prefill(model, PREFILL_TOKENS, iters=max(1, args.steps), warmup=args.warmup)
-        flops = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
-        print(json.dumps({"only": "prefill", "ms": round(prefill_ms, 3), "tokens": PREFILL_TOKENS, "layers": n_layers,
+    if args.only == "prefill":  # a short run for profiling: one prompt (of 2,048 tokens unless --prefill-tokens says otherwise)
+        prefill_ms = time_prefill(model, args.prefill_tokens, iters=max(1, args.steps), warmup=args.warmup)
+        flops = prefill_flops(cfg, n_layers, args.prefill_tokens)
+        print(json.dumps({"only": "prefill", "ms": round(prefill_ms, 3), "tokens": args.prefill_tokens, "layers": n_layers,
+                          "tokens_per_s": round(args.prefill_tokens / (prefill_ms / 1e3), 1),
                           "tflops": round(flops / (prefill_ms / 1e3) / 1e12, 1)}))
         return 0
     main = time_decode(model, args.batch, args.context, args.steps, args.warmup, sample_clocks=True)
@@ -311,6 +312,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")
     parser.add_argument("--shape", default="llama3-8b", choices=sorted(SHAPES),
                         help="the model shape to time (the default is the headline configuration)")
+    parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                        help="prompt length of --only prefill (the full line always uses 2,048)")
     parser.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                         help="a short run of one part, for profiling; prints its own small JSON line")
     args = parser.parse_args()

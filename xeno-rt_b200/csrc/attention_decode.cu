@@ -401,14 +401,15 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int row0 = (blocks[key0 / XRT_BLOCK_TOKENS] * n_kv_heads + kv_head) * XRT_BLOCK_TOKENS;
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_addr[buffer]), "r"(2 * tile_bytes)
                  : "memory");
-    for (int b = 0; b < boxes; ++b) {
-      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                   ::"r"(smem_addr(k_tiles + buffer * tile_bytes + b * DEC_BOX_BYTES)), "l"(&map_k), "r"(b * 64), "r"(row0),
-                     "r"(full_addr[buffer]) : "memory");
-      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                   ::"r"(smem_addr(v_tiles + buffer * tile_bytes + b * DEC_BOX_BYTES)), "l"(&map_v), "r"(b * 64), "r"(row0),
-                     "r"(full_addr[buffer]) : "memory");
-    }
+    // one copy a tile: the map's third dimension walks the row's pieces of 64 dims, so that the boxes of 64 rows x
+    // 128 bytes land one behind the other (a copy instruction costs the thread that issues it about 200 cycles,
+    // and this thread's warp has its 16 keys to work on like the others)
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_addr(k_tiles + buffer * tile_bytes)), "l"(&map_k), "r"(0), "r"(row0), "r"(0), "r"(full_addr[buffer])
+                 : "memory");
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_addr(v_tiles + buffer * tile_bytes)), "l"(&map_v), "r"(0), "r"(row0), "r"(0), "r"(full_addr[buffer])
+                 : "memory");
   };
 
   // query operand: column g = head g of the group (zero at or beyond the group)
@@ -541,16 +542,17 @@ static DecEncodeFn dec_encode() {
   return fn;
 }
 
-// A map over a cache pool seen as a row-major bfloat16 matrix [blocks * kv heads * 64, head_dim]:
-// boxes of 64 rows x 64 dims, 128-byte swizzle.
+// A map over a cache pool, a row-major bfloat16 matrix [blocks * kv heads * 64, head_dim], seen as
+// [head_dim / 64 pieces][rows][64 dims]: a box is 64 dims x 64 rows x all pieces, 128-byte swizzle, so one copy
+// brings a whole tile of 64 keys as head_dim / 64 boxes of 64 rows x 128 bytes, one behind the other.
 static bool dec_make_map(CUtensorMap* map, const void* base, long long rows, int head_dim) {
   DecEncodeFn encode = dec_encode();
   if (encode == nullptr) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
-  const cuuint32_t box[2] = {64u, 64u};
-  const cuuint32_t elem[2] = {1u, 1u};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+  const cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(head_dim / 64)};
+  const cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2, 128u};
+  const cuuint32_t box[3] = {64u, 64u, (cuuint32_t)(head_dim / 64)};
+  const cuuint32_t elem[3] = {1u, 1u, 1u};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }

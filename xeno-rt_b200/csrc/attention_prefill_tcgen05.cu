@@ -3,28 +3,26 @@
 // 0 .. start + t, read from the cache so that earlier context is included.)
 //
 // A block owns 128 consecutive new tokens of one sequence for one query head and walks the
-// sequence's cache blocks (64 keys each).  Six warps:
-//   warp 0    TMA: the Q tile once, then for each block its K and V tiles ([64 keys x 128], two
-//             64-column halves each, 128-byte swizzle) into a three-stage ring.
-//   warp 1    owns TMEM and issues the MMAs: S = Q K^T (128 x 64, eight tcgen05.mma over the head
-//             size) into one of two S buffers, and O += P V (128 x 128, four tcgen05.mma over the
-//             64 keys) accumulated in TMEM over all blocks.  K is a K-major operand as stored; V
+// sequence's keys in steps of 128 (two cache blocks of 64).  Six warps:
+//   warp 0    TMA: the Q tile once, then for each step its K and V tiles ([128 keys x 128], as boxes
+//             of 64 keys x 64 dims, 128-byte swizzle) into a ring of two stages.  K and V of a stage
+//             have barriers of their own: K is free again after the step's QK^T, a whole step before V.
+//   warp 1    owns TMEM and issues the MMAs: S = Q K^T (128 x 128, eight tcgen05.mma over the head
+//             size) into one of two S buffers, and O += P V (128 x 128, eight tcgen05.mma over the
+//             step's keys) accumulated in TMEM over all steps.  K is a K-major operand as stored; V
 //             ([key][dim]) is an MN-major operand as stored: no transposition anywhere.  QK^T of the
-//             next block is issued before PV of this one, so the tensor core works while the softmax
+//             next step is issued before PV of this one, so the tensor core works while the softmax
 //             runs.
-//   warps 2-9 softmax and output, TWO THREADS PER QUERY ROW (TMEM lane): warps 2-5 take keys 0-31
-//             of a block and dims 0-63 of the output, warps 6-9 keys 32-63 and dims 64-127 (a warp
-//             reaches the TMEM lanes of its number modulo 4, so warps w and w + 4 share 32 rows).
-//             A thread reads its half row of S (tcgen05.ld), masks, keeps its share of the sum in
-//             32-bit, and writes P as bfloat16 into shared memory in the MMA's operand layout; the
-//             two halves of a row meet once a block, through shared memory and a barrier of their
-//             two warps, to agree on the row's maximum.  The exponents are taken
+//   warps 2-5 softmax and output, one thread a query row (TMEM lane).  A thread reads its row of S
+//             (tcgen05.ld), masks (only steps that reach the diagonal), keeps the row's sum in 32-bit,
+//             and writes P as bfloat16 into one of two buffers in shared memory in the MMA's operand
+//             layout.  The exponents are taken
 //             against a reference value m of the row that only moves when the row's maximum has
 //             grown by more than 8 (a factor 256) beyond it: softmax does not depend on m as long as
 //             P and the sum use the same one, P stays within 2^8 (bfloat16 keeps its 8 bits of
 //             precision at any magnitude), and the accumulated O in TMEM has to be rescaled (read,
 //             multiplied, written back by the row's thread, after the products issued so far have
-//             completed) only on those rare moves instead of once a block.
+//             completed) only on those rare moves instead of once a step.
 // Every mbarrier wait is bounded; a wait that runs out raises the error flag and an abort flag, all
 // roles leave their loops, TMEM is freed and the block returns.
 #include <cuda.h>
@@ -39,7 +37,10 @@ constexpr int FA_BOX = 64 * 64 * 2;                    // 8 KB: what one tensor 
 constexpr int FA_KV_HALF = FA_KEYS * 64 * 2;           // 16 KB: 128 keys (two cache blocks) x 64 dims
 constexpr int FA_STAGE_BYTES = 4 * FA_KV_HALF;         // K halves, then V halves: 64 KB
 constexpr int FA_P_BYTES = FA_ROWS * FA_KEYS * 2;      // 32 KB (two halves of 64 keys)
-constexpr int fa_smem_bytes(int nh) { return nh * FA_Q_BYTES + FA_STAGES * FA_STAGE_BYTES + nh * FA_P_BYTES + 512 + 1024; }
+constexpr int FA_P_BUFFERS = 2;                        // P of a step is written while the product before it still reads its own
+constexpr int fa_smem_bytes(int nh) {
+  return nh * FA_Q_BYTES + FA_STAGES * FA_STAGE_BYTES + nh * FA_P_BUFFERS * FA_P_BYTES + 512 + 1024;
+}
 constexpr long long FA_SPIN_LIMIT = 1ll << 24;
 
 __device__ __forceinline__ uint32_t fa_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -137,8 +138,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* q_tiles = smem;                                   // [NH] x 32 KB
   unsigned char* kv_ring = smem + NH * FA_Q_BYTES;
-  unsigned char* p_tiles = kv_ring + FA_STAGES * FA_STAGE_BYTES;   // [NH] x 16 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_tiles + NH * FA_P_BYTES);
+  unsigned char* p_tiles = kv_ring + FA_STAGES * FA_STAGE_BYTES;   // [NH][FA_P_BUFFERS] x 32 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_tiles + NH * FA_P_BUFFERS * FA_P_BYTES);
   uint64_t* q_full = bars;                 // [1]
   uint64_t* k_full = bars + 1;             // [FA_STAGES] each: K and V of a step have barriers of their own,
   uint64_t* k_empty = k_full + FA_STAGES;  //   since a step's K is free again (after its QK^T) a whole step
@@ -146,9 +147,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   uint64_t* v_empty = v_full + FA_STAGES;
   uint64_t* s_full = v_empty + FA_STAGES;  // [2]
   uint64_t* s_empty = s_full + 2;          // [2]
-  uint64_t* p_full = s_empty + 2;          // [1]
-  uint64_t* p_empty = p_full + 1;          // [1]
-  uint64_t* pv_done = p_empty + 1;         // [1]: completes once for every block's P V
+  uint64_t* p_full = s_empty + 2;          // [2]
+  uint64_t* p_empty = p_full + 2;          // [2]
+  uint64_t* pv_done = p_empty + 2;         // [1]: completes once for every step's P V
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -179,8 +180,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       fa_mbar_init(fa_smem(&s_full[b]), 1);
       fa_mbar_init(fa_smem(&s_empty[b]), 4 * NH);
     }
-    fa_mbar_init(fa_smem(p_full), 4 * NH);
-    fa_mbar_init(fa_smem(p_empty), 1);
+    for (int b = 0; b < FA_P_BUFFERS; ++b) {
+      fa_mbar_init(fa_smem(&p_full[b]), 4 * NH);
+      fa_mbar_init(fa_smem(&p_empty[b]), 1);
+    }
     fa_mbar_init(fa_smem(pv_done), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -268,7 +271,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);
         if (!ok) break;
         const int s = j % FA_STAGES;
-        ok = fa_mbar_wait(fa_smem(p_full), (uint32_t)j & 1u, abort_flag) &&  // P is written, and O rescaled if it had to be
+        const int pb = j & 1;
+        ok = fa_mbar_wait(fa_smem(&p_full[pb]), (uint32_t)(j >> 1) & 1u, abort_flag) &&  // P is written, and O rescaled if it had to be
              fa_mbar_wait(fa_smem(&v_full[s]), (j / FA_STAGES) & 1, abort_flag);
         if (!ok) break;
         fa_fence_after();
@@ -277,14 +281,14 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         for (int h = 0; h < NH; ++h) {
 #pragma unroll
           for (int ks = 0; ks < FA_KEYS / 16; ++ks) {  // 16 keys a step
-            const uint64_t a = fa_desc_k_major(fa_smem(p_tiles + h * FA_P_BYTES + (ks / 4) * (FA_P_BYTES / 2))) + 2 * (ks % 4);
+            const uint64_t a = fa_desc_k_major(fa_smem(p_tiles + (h * FA_P_BUFFERS + pb) * FA_P_BYTES + (ks / 4) * (FA_P_BYTES / 2))) + 2 * (ks % 4);
             const uint64_t bd = fa_desc_mn_major(fa_smem(stage + 2 * FA_KV_HALF + ks * 2048), FA_KV_HALF);
             fa_mma(tmem_o + h * FA_HD, a, bd, idesc_pv, j > 0 || ks > 0);
           }
         }
         fa_commit(fa_smem(pv_done));
         fa_commit(fa_smem(&v_empty[s]));
-        fa_commit(fa_smem(p_empty));
+        fa_commit(fa_smem(&p_empty[pb]));
       }
       if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 5); }
     }
@@ -363,11 +367,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;  // a row without visible keys: exp2(-inf) = 0 all the same
       float part_sum[4] = {0.f, 0.f, 0.f, 0.f};
       // P in the operand layout: two halves of 64 keys; in a half row r holds 128 bytes and its 16-byte
-      // piece c sits at c ^ (r % 8).  One P buffer a head: the product that read it (the step before)
-      // was issued as soon as it was written and is long done by now.
-      ok = fa_mbar_wait(fa_smem(p_empty), ((uint32_t)j & 1u) ^ 1u, abort_flag);
+      // piece c sits at c ^ (r % 8).  Two P buffers a head: with one, the exponents of a step could
+      // only start when the product of the step before had completed, and that product only when
+      // they were all written: the tensor core and the softmax threads took turns.
+      ok = fa_mbar_wait(fa_smem(&p_empty[b]), ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_flag);
       if (!ok) break;
-      unsigned char* p_row = p_tiles + h * FA_P_BYTES + r * 128;
+      unsigned char* p_row = p_tiles + (h * FA_P_BUFFERS + b) * FA_P_BYTES + r * 128;
 #pragma unroll
       for (int c = 0; c < FA_KEYS / 8; ++c) {
         uint32_t packed[4];
@@ -384,7 +389,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads P through the async proxy
       __syncwarp();
-      if (lane == 0) fa_mbar_arrive(fa_smem(p_full));
+      if (lane == 0) fa_mbar_arrive(fa_smem(&p_full[b]));
       l_run += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
     }
     if (ok && n_tiles > 0) ok = fa_mbar_wait(fa_smem(pv_done), (uint32_t)(n_tiles - 1) & 1u, abort_flag);
