@@ -5,7 +5,7 @@
 // A block owns 128 consecutive new tokens of one sequence for one query head and walks the
 // sequence's keys in steps of 128 (two cache blocks of 64).  Six warps:
 //   warp 0    TMA: the Q tile once, then for each step its K and V tiles ([128 keys x 128], as boxes
-//             of 64 keys x 64 dims, 128-byte swizzle) into a ring of two stages.  K and V of a stage
+//             of 64 keys x 64 dims, 128-byte swizzle) into a ring of three stages.  K and V of a stage
 //             have barriers of their own: K is free again after the step's QK^T, a whole step before V.
 //   warp 1    owns TMEM and issues the MMAs: S = Q K^T (128 x 128, eight tcgen05.mma over the head
 //             size) into one of two S buffers, and O += P V (128 x 128, eight tcgen05.mma over the
@@ -15,8 +15,8 @@
 //             runs.
 //   warps 2-5 softmax and output, one thread a query row (TMEM lane).  A thread reads its row of S
 //             (tcgen05.ld), masks (only steps that reach the diagonal), keeps the row's sum in 32-bit,
-//             and writes P as bfloat16 into one of two buffers in shared memory in the MMA's operand
-//             layout.  The exponents are taken
+//             and writes P as bfloat16 pairs into one of two buffers in tensor memory (tcgen05.st),
+//             from where P V reads it as its A operand.  The exponents are taken
 //             against a reference value m of the row that only moves when the row's maximum has
 //             grown by more than 8 (a factor 256) beyond it: softmax does not depend on m as long as
 //             P and the sum use the same one, P stays within 2^8 (bfloat16 keeps its 8 bits of
@@ -31,16 +31,14 @@
 
 namespace xrt {
 
-constexpr int FA_ROWS = 128, FA_KEYS = 128, FA_HD = 128, FA_STAGES = 2;
+constexpr int FA_ROWS = 128, FA_KEYS = 128, FA_HD = 128, FA_STAGES = 3;
 constexpr int FA_Q_BYTES = FA_ROWS * FA_HD * 2;        // 32 KB (two halves of 16 KB)
 constexpr int FA_BOX = 64 * 64 * 2;                    // 8 KB: what one tensor copy brings, 64 keys x 64 dims
 constexpr int FA_KV_HALF = FA_KEYS * 64 * 2;           // 16 KB: 128 keys (two cache blocks) x 64 dims
 constexpr int FA_STAGE_BYTES = 4 * FA_KV_HALF;         // K halves, then V halves: 64 KB
-constexpr int FA_P_BYTES = FA_ROWS * FA_KEYS * 2;      // 32 KB (two halves of 64 keys)
+constexpr int FA_P_COLS = FA_KEYS / 2;                 // P in TMEM: bfloat16 pairs, 64 columns of 32 bits a step
 constexpr int FA_P_BUFFERS = 2;                        // P of a step is written while the product before it still reads its own
-constexpr int fa_smem_bytes(int nh) {
-  return nh * FA_Q_BYTES + FA_STAGES * FA_STAGE_BYTES + nh * FA_P_BUFFERS * FA_P_BYTES + 512 + 1024;
-}
+constexpr int fa_smem_bytes(int nh) { return nh * FA_Q_BYTES + FA_STAGES * FA_STAGE_BYTES + 512 + 1024; }
 constexpr long long FA_SPIN_LIMIT = 1ll << 24;
 
 __device__ __forceinline__ uint32_t fa_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -90,6 +88,14 @@ __device__ __forceinline__ void fa_mma(uint32_t tmem_d, uint64_t desc_a, uint64_
                " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with A read from tensor memory: row r of A in lane r, two bfloat16 of the contraction a
+// 32-bit column (the lower index in the lower half), 8 columns an instruction.
+__device__ __forceinline__ void fa_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+               " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void fa_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -138,8 +144,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* q_tiles = smem;                                   // [NH] x 32 KB
   unsigned char* kv_ring = smem + NH * FA_Q_BYTES;
-  unsigned char* p_tiles = kv_ring + FA_STAGES * FA_STAGE_BYTES;   // [NH][FA_P_BUFFERS] x 32 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_tiles + NH * FA_P_BUFFERS * FA_P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_ring + FA_STAGES * FA_STAGE_BYTES);
   uint64_t* q_full = bars;                 // [1]
   uint64_t* k_full = bars + 1;             // [FA_STAGES] each: K and V of a step have barriers of their own,
   uint64_t* k_empty = k_full + FA_STAGES;  //   since a step's K is free again (after its QK^T) a whole step
@@ -165,8 +170,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int last_row = min(row0 + FA_ROWS, n_new) - 1;
   const int n_tiles = (start + last_row + 1 + FA_KEYS - 1) / FA_KEYS;  // keys 0 .. position of the last row
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  static_assert(NH * (2 * FA_KEYS + FA_HD) <= 512, "S buffers and O must fit in TMEM");
-  constexpr int TMEM_COLS = 512;  // S: NH x 2 buffers x 128 columns; O: NH x 128
+  static_assert(NH * (2 * FA_KEYS + FA_HD + FA_P_BUFFERS * FA_P_COLS) <= 512, "S buffers, O and P buffers must fit in TMEM");
+  constexpr int TMEM_COLS = 512;  // S: NH x 2 buffers x 128 columns; O: NH x 128; P: NH x 2 buffers x 64
 
   if (threadIdx.x == 0) {
     fa_mbar_init(fa_smem(q_full), 1);
@@ -198,6 +203,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s = tmem_base;                        // [head][buffer] x 64 columns
   const uint32_t tmem_o = tmem_base + NH * 2 * FA_KEYS;     // [head] x 128 columns
+  const uint32_t tmem_p = tmem_o + NH * FA_HD;              // [head][buffer] x 64 columns
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
@@ -281,9 +287,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         for (int h = 0; h < NH; ++h) {
 #pragma unroll
           for (int ks = 0; ks < FA_KEYS / 16; ++ks) {  // 16 keys a step
-            const uint64_t a = fa_desc_k_major(fa_smem(p_tiles + (h * FA_P_BUFFERS + pb) * FA_P_BYTES + (ks / 4) * (FA_P_BYTES / 2))) + 2 * (ks % 4);
             const uint64_t bd = fa_desc_mn_major(fa_smem(stage + 2 * FA_KV_HALF + ks * 2048), FA_KV_HALF);
-            fa_mma(tmem_o + h * FA_HD, a, bd, idesc_pv, j > 0 || ks > 0);
+            fa_mma_a_tmem(tmem_o + h * FA_HD, tmem_p + (h * FA_P_BUFFERS + pb) * FA_P_COLS + ks * 8, bd, idesc_pv, j > 0 || ks > 0);
           }
         }
         fa_commit(fa_smem(pv_done));
@@ -366,28 +371,29 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       }
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;  // a row without visible keys: exp2(-inf) = 0 all the same
       float part_sum[4] = {0.f, 0.f, 0.f, 0.f};
-      // P in the operand layout: two halves of 64 keys; in a half row r holds 128 bytes and its 16-byte
-      // piece c sits at c ^ (r % 8).  Two P buffers a head: with one, the exponents of a step could
-      // only start when the product of the step before had completed, and that product only when
-      // they were all written: the tensor core and the softmax threads took turns.
+      // P goes into tensor memory as the A operand of P V: the row's lane, bfloat16 pairs of
+      // consecutive keys a column.  Two P buffers a head: with one, the exponents of a step could
+      // only be stored when the product of the step before had completed, and that product only
+      // when they all were: the tensor core and the softmax threads took turns.
       ok = fa_mbar_wait(fa_smem(&p_empty[b]), ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_flag);
       if (!ok) break;
-      unsigned char* p_row = p_tiles + (h * FA_P_BUFFERS + b) * FA_P_BYTES + r * 128;
+      fa_fence_after();
+      const uint32_t my_p = tmem_p + lane_base + (h * FA_P_BUFFERS + b) * FA_P_COLS;
 #pragma unroll
-      for (int c = 0; c < FA_KEYS / 8; ++c) {
-        uint32_t packed[4];
+      for (int half = 0; half < 2; ++half) {
+        uint32_t packed[32];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float p0 = fa_exp2(fmaf(s[c * 8 + 2 * i], scale_log2, neg_m));
-          const float p1 = fa_exp2(fmaf(s[c * 8 + 2 * i + 1], scale_log2, neg_m));
-          part_sum[i] += p0 + p1;
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = fa_exp2(fmaf(s[half * 64 + 2 * i], scale_log2, neg_m));
+          const float p1 = fa_exp2(fmaf(s[half * 64 + 2 * i + 1], scale_log2, neg_m));
+          part_sum[i & 3] += p0 + p1;
           __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
           packed[i] = *reinterpret_cast<uint32_t*>(&pair);
         }
-        *reinterpret_cast<uint4*>(p_row + (c / 8) * (FA_P_BYTES / 2) + (((c % 8) ^ (r & 7)) << 4)) =
-            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        fa_st32(my_p + half * 32, packed);
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads P through the async proxy
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      fa_fence_before();
       __syncwarp();
       if (lane == 0) fa_mbar_arrive(fa_smem(&p_full[b]));
       l_run += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
