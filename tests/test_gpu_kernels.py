@@ -486,7 +486,7 @@ def test_gemm_decode_tcgen05_swiglu(m, inner, k):
     assert rel(out, want) < 5e-3
 
 
-@pytest.mark.parametrize("nh,nkv", [(8, 2), (5, 1), (4, 4)])
+@pytest.mark.parametrize("nh,nkv", [(8, 2), (5, 1), (4, 4), (6, 3)])
 def test_attention_prefill_tcgen05_kernel(nh, nkv):
     """The tcgen05 attention (head size 128) on the case of the mma.sync kernel's test: a whole prompt of 150 tokens,
     one of a single token, one that continues at position 100 with 70 more (across a block edge), a skipped one;

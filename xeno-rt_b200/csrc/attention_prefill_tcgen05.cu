@@ -317,14 +317,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       if (!ok) break;
       fa_fence_after();
       float s[FA_KEYS];
-#pragma unroll
-      for (int c = 0; c < FA_KEYS; c += 64) {
-        uint32_t v0[32], v1[32];  // two loads on their way before the wait
-        fa_ld32(v0, my_s + b * FA_KEYS + c);
-        fa_ld32(v1, my_s + b * FA_KEYS + c + 32);
+      {
+        uint32_t v0[32], v1[32], v2[32], v3[32];  // the whole row on its way before the one wait
+        fa_ld32(v0, my_s + b * FA_KEYS);
+        fa_ld32(v1, my_s + b * FA_KEYS + 32);
+        fa_ld32(v2, my_s + b * FA_KEYS + 64);
+        fa_ld32(v3, my_s + b * FA_KEYS + 96);
         fa_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { s[c + i] = __uint_as_float(v0[i]); s[c + 32 + i] = __uint_as_float(v1[i]); }
+        for (int i = 0; i < 32; ++i) {
+          s[i] = __uint_as_float(v0[i]); s[32 + i] = __uint_as_float(v1[i]);
+          s[64 + i] = __uint_as_float(v2[i]); s[96 + i] = __uint_as_float(v3[i]);
+        }
       }
       fa_fence_before();
       __syncwarp();
