@@ -16,6 +16,12 @@
 // Epilogues: store (32-bit or bfloat16), add into the 32-bit residual stream, SwiGLU (an item then
 // streams 128 gate rows and the 128 matching up rows into two accumulators).
 //
+// Where all items of a launch run at once (tiles x splits is no more than the multiprocessors), the
+// splits of a tile are the blocks of one thread-block cluster instead: each leaves its partial sums in
+// its own shared memory, the cluster meets, and every block adds and finishes its share of the tile's
+// rows from all blocks' shared memory (distributed shared memory), again in split order: no scratch
+// in global memory, no fence, no counter.
+//
 // Six warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues the MMAs, warps 2-5 read the
 // accumulators (tcgen05.ld, one TMEM lane quarter each) while the MMA warp fills the other
 // accumulator.  Every mbarrier wait is bounded; a wait that runs out raises the error flag and an
@@ -82,6 +88,16 @@ __device__ __forceinline__ void dg_ld16(uint32_t (&r)[16], uint32_t addr) {
                : "r"(addr));
 }
 __device__ __forceinline__ void dg_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float dg_ld_cluster(uint32_t local_smem, int rank) {  // the same place in another block of the cluster
+  uint32_t remote;
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem), "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+__device__ __forceinline__ void dg_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 struct DecodeGemmShape {
   int M, N, K, ldo;
@@ -92,6 +108,7 @@ struct DecodeGemmShape {
   int up_rows;       // SwiGLU: the up rows start this many rows after the gate rows
   int stages;        // ring depth
   int tmem_cols;     // power of two >= 2 accumulators
+  int clustered;     // the splits of a tile are one cluster; one item a block
 };
 
 // MODE 0: store, 1: add into float out, 2: SwiGLU.
@@ -253,6 +270,16 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             }
           }
         }
+      } else if (shape.clustered) {
+        // this split's sums into this block's shared memory, [accumulator column][weight row]: the ring is
+        // idle (a block has one item, and its products have completed)
+        float* xch = reinterpret_cast<float*>(smem);
+        for (int c = 0; c < acc_cols; c += 16) {
+          uint32_t v[16];
+          if (has_k) { dg_ld16(v, tmem_row + c); dg_wait_ld(); }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) xch[(size_t)(c + j) * DG_ROWS + r] = has_k ? __uint_as_float(v[j]) : 0.f;
+        }
       } else {
         // partial[(tile * splits + split)][group][weight row][NB]: a thread owns its row's NB floats
         float* mine = partial + ((size_t)item * GROUPS) * DG_ROWS * shape.nb;
@@ -272,7 +299,7 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         dg_fence_before();
         dg_mbar_arrive(dg_smem(&acc_empty[a]));
       }
-      if (shape.splits > 1) {
+      if (shape.splits > 1 && !shape.clustered) {
         // the block that brings a tile's last split adds the partials in split order
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
@@ -336,6 +363,56 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     if (!ok && lane == 0) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 4); }
   }
 
+  if (shape.clustered) {
+    // Every thread of every block of the cluster comes here, also after a wait that ran out (all waits
+    // are bounded).  Block `rank` finishes rows rank * per .. of the tile: consecutive threads take
+    // consecutive weight rows (consecutive output addresses) of one batch row.
+    dg_cluster_sync();
+    if (warp >= 2 && !*abort_flag) {
+      uint32_t rank;
+      asm("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+      const int tile = blockIdx.x / shape.splits;
+      const int per = (DG_ROWS + shape.splits - 1) / shape.splits;
+      const int row_lo = (int)rank * per;
+      const int rows_here = max(0, min(per, DG_ROWS - row_lo));
+      const int total = rows_here * shape.M;
+      const uint32_t xch_local = dg_smem(smem);
+      constexpr int UNROLL = 4;
+      for (int base = threadIdx.x - 64; base < total; base += 128 * UNROLL) {
+        float old[UNROLL], sums[UNROLL][GROUPS];
+        size_t at[UNROLL];
+        bool live[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int idx = base + u * 128;
+          const int m = idx / rows_here, row = row_lo + idx - m * rows_here;
+          const int n = tile * DG_ROWS + row;
+          live[u] = idx < total && n < shape.N;
+          at[u] = (size_t)m * shape.ldo + n;
+          old[u] = (MODE == 1 && live[u]) ? __ldcg(reinterpret_cast<const float*>(out) + at[u]) : 0.f;
+#pragma unroll
+          for (int gr = 0; gr < GROUPS; ++gr) {
+            float t = 0.f;
+            if (live[u]) {
+              const uint32_t where = xch_local + (uint32_t)(((gr * shape.nb + m) * DG_ROWS + row) * 4);
+              for (int sp = 0; sp < shape.splits; ++sp) t += dg_ld_cluster(where, sp);
+            }
+            sums[u][gr] = t;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          if (live[u]) {
+            float val = sums[u][0];
+            if (MODE == 2) val = (val / (1.0f + expf(-val))) * sums[u][GROUPS - 1];
+            if (MODE == 1) out[at[u]] = from_float<TO>(old[u] + val);
+            else out[at[u]] = from_float<TO>(val);
+          }
+        }
+      }
+    }
+    dg_cluster_sync();  // nobody leaves while another block may still read its shared memory
+  }
   dg_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -397,9 +474,19 @@ static int choose_splits(int tiles, int k_iters, int sms, int groups, int nb) {
   return best;
 }
 
+// XRT_DECODE_GEMM_CLUSTER=0 keeps the scratch-and-counter reduction everywhere, for comparison.
+inline bool decode_gemm_clusters_wanted() {
+  static int wanted = -1;
+  if (wanted < 0) {
+    const char* env = getenv("XRT_DECODE_GEMM_CLUSTER");
+    wanted = (env != nullptr && env[0] == '0') ? 0 : 1;
+  }
+  return wanted == 1;
+}
+
 template <int MODE, typename TO>
 int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorMap& map_w, const CUtensorMap& map_x,
-                       const DecodeGemmShape& shape, int smem, int blocks, int* error_flag, cudaStream_t stream) {
+                       DecodeGemmShape shape, int smem, int blocks, int sm_count, int* error_flag, cudaStream_t stream) {
   auto kernel = gemm_decode_tcgen05_kernel<MODE, TO>;
   static int allowed = 0;
   if (smem > allowed) {
@@ -407,8 +494,53 @@ int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorM
     if (err != cudaSuccess) return (int)err;
     allowed = smem;
   }
-  launch_kernel(kernel, dim3(blocks), dim3(DG_THREADS), (size_t)smem, stream, map_w, map_x, (TO*)out, partial, counters,
-                shape, error_flag);
+  // The splits of a tile as one cluster, if all clusters of the launch find room at the same time
+  // (asked once for each cluster size and shared-memory size)
+  const int items = shape.tiles * shape.splits;
+  shape.clustered = 0;
+  if (shape.splits > 1 && shape.splits <= 8 && items <= sm_count && decode_gemm_clusters_wanted()) {
+    static int held[9] = {}, held_smem[9] = {};  // clusters at once by cluster size: 0 unknown, -1 none
+    if (held[shape.splits] == 0 || held_smem[shape.splits] != smem) {
+      cudaLaunchConfig_t probe = {};
+      probe.gridDim = dim3(shape.splits, 1, 1);
+      probe.blockDim = dim3(DG_THREADS);
+      probe.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = shape.splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      probe.attrs = attr;
+      probe.numAttrs = 1;
+      int clusters = 0;
+      const bool asked = cudaOccupancyMaxActiveClusters(&clusters, kernel, &probe) == cudaSuccess;
+      cudaGetLastError();  // a refusal here is an answer, not an error of the stream
+      held[shape.splits] = (asked && clusters >= 1) ? clusters : -1;
+      held_smem[shape.splits] = smem;
+    }
+    if (held[shape.splits] >= shape.tiles) shape.clustered = 1;
+  }
+  if (!shape.clustered) {
+    launch_kernel(kernel, dim3(blocks), dim3(DG_THREADS), (size_t)smem, stream, map_w, map_x, (TO*)out, partial, counters,
+                  shape, error_flag);
+    return launch_status();
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(items);
+  config.blockDim = dim3(DG_THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int n_attrs = 0;
+  if (pdl_enabled()) {
+    attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attrs;
+  }
+  attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+  attrs[n_attrs].val.clusterDim.x = shape.splits; attrs[n_attrs].val.clusterDim.y = 1; attrs[n_attrs].val.clusterDim.z = 1;
+  ++n_attrs;
+  config.attrs = attrs;
+  config.numAttrs = n_attrs;
+  cudaLaunchKernelEx(&config, kernel, map_w, map_x, (TO*)out, partial, counters, shape, error_flag);
   return launch_status();
 }
 
@@ -458,6 +590,7 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05(void* out, const void* x, const void* w, 
   while (cols < 2 * groups * shape.nb) cols *= 2;
   if (cols > 512) return XRT_ERR_UNSUPPORTED;
   shape.tmem_cols = cols;
+  shape.clustered = 0;
   if (shape.splits > 1 && (partial == nullptr || counters == nullptr)) return XRT_ERR_ARGUMENT;
   const int smem = shape.stages * stage_bytes + 512 + 1024;
   const int items = shape.tiles * shape.splits;
@@ -466,13 +599,13 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05(void* out, const void* x, const void* w, 
   if (!xrt::dg_make_map(&map_w, w, w_rows, K, K, xrt::DG_ROWS) || !xrt::dg_make_map(&map_x, x, M, K, ldx, shape.nb))
     return XRT_ERR_UNSUPPORTED;
   if (mode == 1)
-    return xrt::launch_decode_gemm<1, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, error_flag, stream);
+    return xrt::launch_decode_gemm<1, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, stream);
   if (mode == 2) {
     if (out_dtype == XRT_BF16)
-      return xrt::launch_decode_gemm<2, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, error_flag, stream);
-    return xrt::launch_decode_gemm<2, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, error_flag, stream);
+      return xrt::launch_decode_gemm<2, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, stream);
+    return xrt::launch_decode_gemm<2, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, stream);
   }
   if (out_dtype == XRT_BF16)
-    return xrt::launch_decode_gemm<0, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, error_flag, stream);
-  return xrt::launch_decode_gemm<0, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, error_flag, stream);
+    return xrt::launch_decode_gemm<0, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, stream);
+  return xrt::launch_decode_gemm<0, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, stream);
 }
