@@ -1,11 +1,14 @@
 """Choice among the bfloat16 matrix-product kernels.  ``run`` returns False when none of the
 tensor-core kernels takes the shape, and the caller uses the CUDA-core kernel that takes any.
 
-Up to 16 rows: the cp.async weight-streaming kernel (its fixed cost is the lowest, which is what
-counts when a product reads 30 to 100 MB).  17 to 128 rows: the weight-streaming tcgen05 kernel with
-swapped operands and split K (the batch is the MMA's N, so its time stays the time to read the
-weight).  More rows (prompts): the tiled tcgen05 kernel.  ``XRT_DECODE_GEMM=stream`` or ``tcgen05``
-forces one of the two decode kernels wherever it applies, for comparison."""
+Up to 128 rows (decode steps): the weight-streaming tcgen05 kernel with swapped operands and split
+K (the batch is the MMA's N, so its time stays the time to read the weight); its splits of a tile
+meet through a thread-block cluster's shared memory.  The products that add into the residual
+stream are the exception up to 16 rows: there the cp.async weight-streaming kernel is faster
+(measured over whole steps of 1 to 16 sequences at the 8B shape: the others gain 1 to 11 % on the
+tcgen05 kernel, these lose 2 to 5 %).  More rows (prompts): the tiled tcgen05 kernel.
+``XRT_DECODE_GEMM=stream`` or ``tcgen05`` forces one of the two decode kernels wherever it applies,
+for comparison."""
 from __future__ import annotations
 
 import os
@@ -13,7 +16,7 @@ import os
 from ..csrc import ops
 
 FORCE = os.environ.get("XRT_DECODE_GEMM", "")
-STREAM_ROWS = 16
+STREAM_ROWS = 16  # products that add into the residual stream stay on the cp.async kernel up to here
 
 
 def aligned(x, weight) -> bool:
@@ -24,7 +27,12 @@ def aligned(x, weight) -> bool:
 
 def _product(out, x, weight, mode: str, up_rows: int = 0) -> None:
     rows = x.shape[0]
-    stream_rows = ops.STREAM_MAX_ROWS if FORCE == "stream" else (0 if FORCE == "tcgen05" else STREAM_ROWS)
+    if FORCE == "stream":
+        stream_rows = ops.STREAM_MAX_ROWS
+    elif FORCE == "tcgen05":
+        stream_rows = 0
+    else:
+        stream_rows = STREAM_ROWS if mode == "accumulate" else 0
     if rows <= stream_rows:
         ops.gemm_stream(out, x, weight, mode, up_rows)
     elif rows <= ops.DECODE_TCGEN05_MAX_ROWS:
