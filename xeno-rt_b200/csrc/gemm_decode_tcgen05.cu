@@ -557,6 +557,17 @@ XRT_EXPORT long long xrt_gemm_decode_tcgen05_scratch(int M, int N, int K, int mo
   return (long long)tiles * splits * (mode == 2 ? 2 : 1) * nb * xrt::DG_ROWS;
 }
 
+// What the launcher would do with this product: tiles[0] = tiles of 128 weight rows, tiles[1] = splits of K.
+// The caller that has another kernel for few rows uses it to see how evenly the items fill the device.
+XRT_EXPORT int xrt_gemm_decode_tcgen05_plan(int M, int N, int K, int mode, int sm_count, int* tiles_and_splits) {
+  if (M <= 0 || N <= 0 || K <= 0 || sm_count <= 0 || tiles_and_splits == nullptr) return XRT_ERR_ARGUMENT;
+  const int tiles = (N + xrt::DG_ROWS - 1) / xrt::DG_ROWS;
+  const int k_iters = (K + xrt::DG_BK - 1) / xrt::DG_BK;
+  tiles_and_splits[0] = tiles;
+  tiles_and_splits[1] = xrt::choose_splits(tiles, k_iters, sm_count, mode == 2 ? 2 : 1, (M + 15) / 16 * 16);
+  return XRT_OK;
+}
+
 // x: bfloat16 [M, K] with row stride ldx, M <= 128; w: bfloat16 [w_rows, K] contiguous; K and ldx
 // multiples of 8, bases 16-byte aligned.  out: [M, N] with row stride ldo.  Modes as for
 // xrt_gemm_stream.  partial: float32 scratch of xrt_gemm_decode_tcgen05_scratch floats (may be null

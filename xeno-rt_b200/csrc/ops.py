@@ -67,6 +67,8 @@ def library():
                 fn.restype = _I
             lib.xrt_gemm_decode_tcgen05_scratch.argtypes = [_I, _I, _I, _I, _I]
             lib.xrt_gemm_decode_tcgen05_scratch.restype = ctypes.c_longlong
+            lib.xrt_gemm_decode_tcgen05_plan.argtypes = [_I, _I, _I, _I, _I, ctypes.POINTER(ctypes.c_int)]
+            lib.xrt_gemm_decode_tcgen05_plan.restype = _I
             _lib = lib
     return _lib
 
@@ -390,6 +392,24 @@ def chain_end(discard: bool = False) -> None:
             chain_flush()
     finally:
         _chain = None
+
+
+_decode_plans: dict = {}
+
+
+def gemm_decode_tcgen05_fill(device, m: int, n: int, k: int, mode: str):
+    """(rounds, share of the multiprocessor-rounds that do work) of ``gemm_decode_tcgen05`` on this
+    product: its items (tiles of 128 weight rows x splits of K) run in rounds of one a multiprocessor."""
+    _, _, sms = device_state(device)
+    key = (sms, (m + 15) // 16, n, k, mode)
+    if key not in _decode_plans:
+        plan = (ctypes.c_int * 2)()
+        _check(library().xrt_gemm_decode_tcgen05_plan(m, n, k, {"store": 0, "accumulate": 1, "swiglu": 2}[mode], sms, plan),
+               "gemm_decode_tcgen05_plan")
+        items = plan[0] * plan[1]
+        rounds = -(-items // sms)
+        _decode_plans[key] = (rounds, items / (rounds * sms))
+    return _decode_plans[key]
 
 
 def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0) -> None:

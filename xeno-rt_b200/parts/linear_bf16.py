@@ -1,14 +1,12 @@
 """Choice among the bfloat16 matrix-product kernels.  ``run`` returns False when none of the
 tensor-core kernels takes the shape, and the caller uses the CUDA-core kernel that takes any.
 
-Up to 128 rows (decode steps): the weight-streaming tcgen05 kernel with swapped operands and split
-K (the batch is the MMA's N, so its time stays the time to read the weight); its splits of a tile
-meet through a thread-block cluster's shared memory.  The products that add into the residual
-stream are the exception up to 16 rows: there the cp.async weight-streaming kernel is faster
-(measured over whole steps of 1 to 16 sequences at the 8B shape: the others gain 1 to 11 % on the
-tcgen05 kernel, these lose 2 to 5 %).  More rows (prompts): the tiled tcgen05 kernel.
-``XRT_DECODE_GEMM=stream`` or ``tcgen05`` forces one of the two decode kernels wherever it applies,
-for comparison."""
+17 to 128 rows (decode steps of many sequences): the weight-streaming tcgen05 kernel with swapped
+operands and split K (the batch is the MMA's N, so its time stays the time to read the weight); its
+splits of a tile meet through a thread-block cluster's shared memory.  Up to 16 rows that kernel or
+the cp.async weight-streaming kernel, whichever suits the product (``_tcgen05_for_few_rows``).  More
+than 128 rows (prompts): the tiled tcgen05 kernel.  ``XRT_DECODE_GEMM=stream`` or ``tcgen05`` forces one
+of the two decode kernels wherever it applies, for comparison."""
 from __future__ import annotations
 
 import os
@@ -16,7 +14,7 @@ import os
 from ..csrc import ops
 
 FORCE = os.environ.get("XRT_DECODE_GEMM", "")
-STREAM_ROWS = 16  # products that add into the residual stream stay on the cp.async kernel up to here
+STREAM_ROWS = 16  # up to here the cp.async kernel is a candidate
 
 
 def aligned(x, weight) -> bool:
@@ -25,14 +23,32 @@ def aligned(x, weight) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and weight.is_contiguous())
 
 
+ACCUMULATE_MIN_K = 8192
+
+
+def _tcgen05_for_few_rows(x, weight, out, mode: str) -> bool:
+    """Up to 16 rows both decode kernels take the product.  The tcgen05 kernel runs its items one a
+    multiprocessor in rounds: it wins where they fill the rounds (one round at least 0.6 full, or
+    several at least 0.85 full).  Products that add into the residual stream stay on the cp.async
+    kernel unless K is long (it slows down with K: 2.6 TB/s at K = 25,600, where the tcgen05 kernel
+    reaches 4 TB/s; whole steps of 8 sequences at a width of 5,120 and an inner size of 25,600 went from
+    18.0 to 15.6 ms with this rule, and at 4,096 / 14,336 from 4.62 to 4.40 ms)."""
+    if mode == "accumulate" and x.shape[1] < ACCUMULATE_MIN_K:
+        return False
+    rounds, fill = ops.gemm_decode_tcgen05_fill(x.device, x.shape[0], out.shape[1], x.shape[1], mode)
+    return fill >= 0.6 and (rounds == 1 or fill >= 0.85)
+
+
 def _product(out, x, weight, mode: str, up_rows: int = 0) -> None:
     rows = x.shape[0]
     if FORCE == "stream":
         stream_rows = ops.STREAM_MAX_ROWS
     elif FORCE == "tcgen05":
         stream_rows = 0
+    elif rows > STREAM_ROWS:
+        stream_rows = 0
     else:
-        stream_rows = STREAM_ROWS if mode == "accumulate" else 0
+        stream_rows = 0 if _tcgen05_for_few_rows(x, weight, out, mode) else STREAM_ROWS
     if rows <= stream_rows:
         ops.gemm_stream(out, x, weight, mode, up_rows)
     elif rows <= ops.DECODE_TCGEN05_MAX_ROWS:
