@@ -23,7 +23,7 @@ def aligned(x, weight) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and weight.is_contiguous())
 
 
-ACCUMULATE_MIN_K = 8192
+ACCUMULATE_MIN_K = 16384
 
 
 def _tcgen05_for_few_rows(x, weight, out, mode: str) -> bool:
@@ -31,8 +31,9 @@ def _tcgen05_for_few_rows(x, weight, out, mode: str) -> bool:
     multiprocessor in rounds: it wins where they fill the rounds (one round at least 0.6 full, or
     several at least 0.85 full).  Products that add into the residual stream stay on the cp.async
     kernel unless K is long (it slows down with K: 2.6 TB/s at K = 25,600, where the tcgen05 kernel
-    reaches 4 TB/s; whole steps of 8 sequences at a width of 5,120 and an inner size of 25,600 went from
-    18.0 to 15.6 ms with this rule, and at 4,096 / 14,336 from 4.62 to 4.40 ms)."""
+    reaches 4 TB/s).  Whole steps of 8 sequences at a width of 5,120 and an inner size of 25,600 went
+    from 18.0 to 15.8 ms with this rule, and at 4,096 / 14,336 from 4.62 to 4.40 ms; with the limit at
+    8,192 instead the first gains another 1.5 % and single sequences at the second lose 4.5 %."""
     if mode == "accumulate" and x.shape[1] < ACCUMULATE_MIN_K:
         return False
     rounds, fill = ops.gemm_decode_tcgen05_fill(x.device, x.shape[0], out.shape[1], x.shape[1], mode)
