@@ -88,3 +88,30 @@ def test_spec_names_every_size_from_the_config():
     assert names["model.layers.2.self_attn.q_norm.weight"].shape == (32,)
     assert names["model.layers.0.mlp.down_proj.weight"].shape == (96, 160)
     assert "lm_head.weight" not in names
+
+
+def test_which_kernel_takes_a_decode_product_of_few_rows():
+    """The choice between the two weight-streaming kernels is host arithmetic over the product's sizes
+    (here for a device of 148 multiprocessors): the tcgen05 kernel where its tiles of 128 weight rows,
+    times its splits of K, fill the multiprocessors; the cp.async kernel else, and for products that add
+    into the residual stream unless K is long."""
+    from xeno_rt_b200.core import KernelError
+    from xeno_rt_b200.csrc import ops
+    from xeno_rt_b200.parts.linear_bf16 import tcgen05_for_few_rows as choice
+    try:
+        ops.library()  # the arithmetic lives beside the kernel it describes; building needs nvcc, not a GPU
+    except KernelError as exc:
+        pytest.skip(f"the kernel library cannot be built here: {exc}")
+    sms = 148
+    for rows in (1, 8, 16):
+        # width 4,096, inner 14,336, vocabulary 128,256, 32 + 2 x 8 heads of 128
+        assert choice(sms, rows, 6144, 4096, "store")          # 48 tiles x 3 splits = 144 items
+        assert choice(sms, rows, 14336, 4096, "swiglu")        # 112 items
+        assert choice(sms, rows, 128256, 4096, "store")        # 1,002 tiles: seven rounds, 0.97 full
+        assert not choice(sms, rows, 4096, 4096, "accumulate")
+        assert not choice(sms, rows, 4096, 14336, "accumulate")
+        # width 5,120, inner 25,600, 64 + 2 x 8 heads of 128
+        assert not choice(sms, rows, 10240, 5120, "store")     # 80 items: 0.54 full
+        assert not choice(sms, rows, 25600, 5120, "swiglu")    # 200 tiles: two rounds, 0.68 full
+        assert choice(sms, rows, 5120, 25600, "accumulate")    # long K
+        assert not choice(sms, rows, 5120, 8192, "accumulate")

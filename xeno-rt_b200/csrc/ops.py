@@ -397,10 +397,10 @@ def chain_end(discard: bool = False) -> None:
 _decode_plans: dict = {}
 
 
-def gemm_decode_tcgen05_fill(device, m: int, n: int, k: int, mode: str):
+def gemm_decode_tcgen05_fill(sms: int, m: int, n: int, k: int, mode: str):
     """(rounds, share of the multiprocessor-rounds that do work) of ``gemm_decode_tcgen05`` on this
-    product: its items (tiles of 128 weight rows x splits of K) run in rounds of one a multiprocessor."""
-    _, _, sms = device_state(device)
+    product on a device of ``sms`` multiprocessors: its items (tiles of 128 weight rows x splits of
+    K) run in rounds of one a multiprocessor.  Host arithmetic only: no device is needed."""
     key = (sms, (m + 15) // 16, n, k, mode)
     if key not in _decode_plans:
         plan = (ctypes.c_int * 2)()

@@ -4,7 +4,7 @@ tensor-core kernels takes the shape, and the caller uses the CUDA-core kernel th
 17 to 128 rows (decode steps of many sequences): the weight-streaming tcgen05 kernel with swapped
 operands and split K (the batch is the MMA's N, so its time stays the time to read the weight); its
 splits of a tile meet through a thread-block cluster's shared memory.  Up to 16 rows that kernel or
-the cp.async weight-streaming kernel, whichever suits the product (``_tcgen05_for_few_rows``).  More
+the cp.async weight-streaming kernel, whichever suits the product (``tcgen05_for_few_rows``).  More
 than 128 rows (prompts): the tiled tcgen05 kernel.  ``XRT_DECODE_GEMM=stream`` or ``tcgen05`` forces one
 of the two decode kernels wherever it applies, for comparison."""
 from __future__ import annotations
@@ -26,7 +26,7 @@ def aligned(x, weight) -> bool:
 ACCUMULATE_MIN_K = 16384
 
 
-def _tcgen05_for_few_rows(x, weight, out, mode: str) -> bool:
+def tcgen05_for_few_rows(sms: int, rows: int, n: int, k: int, mode: str) -> bool:
     """Up to 16 rows both decode kernels take the product.  The tcgen05 kernel runs its items one a
     multiprocessor in rounds: it wins where they fill the rounds (one round at least 0.6 full, or
     several at least 0.85 full).  Products that add into the residual stream stay on the cp.async
@@ -34,9 +34,9 @@ def _tcgen05_for_few_rows(x, weight, out, mode: str) -> bool:
     reaches 4 TB/s).  Whole steps of 8 sequences at a width of 5,120 and an inner size of 25,600 went
     from 18.0 to 15.8 ms with this rule, and at 4,096 / 14,336 from 4.62 to 4.40 ms; with the limit at
     8,192 instead the first gains another 1.5 % and single sequences at the second lose 4.5 %."""
-    if mode == "accumulate" and x.shape[1] < ACCUMULATE_MIN_K:
+    if mode == "accumulate" and k < ACCUMULATE_MIN_K:
         return False
-    rounds, fill = ops.gemm_decode_tcgen05_fill(x.device, x.shape[0], out.shape[1], x.shape[1], mode)
+    rounds, fill = ops.gemm_decode_tcgen05_fill(sms, rows, n, k, mode)
     return fill >= 0.6 and (rounds == 1 or fill >= 0.85)
 
 
@@ -49,7 +49,8 @@ def _product(out, x, weight, mode: str, up_rows: int = 0) -> None:
     elif rows > STREAM_ROWS:
         stream_rows = 0
     else:
-        stream_rows = 0 if _tcgen05_for_few_rows(x, weight, out, mode) else STREAM_ROWS
+        sms = ops.device_state(x.device)[2]
+        stream_rows = 0 if tcgen05_for_few_rows(sms, rows, out.shape[1], x.shape[1], mode) else STREAM_ROWS
     if rows <= stream_rows:
         ops.gemm_stream(out, x, weight, mode, up_rows)
     elif rows <= ops.DECODE_TCGEN05_MAX_ROWS:
