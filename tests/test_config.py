@@ -115,3 +115,21 @@ def test_which_kernel_takes_a_decode_product_of_few_rows():
         assert not choice(sms, rows, 25600, 5120, "swiglu")    # 200 tiles: two rounds, 0.68 full
         assert choice(sms, rows, 5120, 25600, "accumulate")    # long K
         assert not choice(sms, rows, 5120, 8192, "accumulate")
+
+
+def test_decode_attention_splits_cover_the_context_and_fill_the_rounds():
+    """How decode attention cuts a context into splits is host arithmetic: every key belongs to one split,
+    splits are whole cache blocks, and the counts are the ones that were measured fastest at 4,096 keys
+    and 8 kv heads (few sequences: many splits that merge inside a cluster of at most 16 blocks; many
+    sequences: few splits that fill the last round of blocks)."""
+    from xeno_rt_b200.parts.attention_bf16 import CLUSTER_MAX_SPLITS, decode_split
+    for n_seqs in (1, 2, 3, 8, 17, 64, 300):
+        for kv_heads in (1, 2, 8):
+            for context in (1, 63, 64, 65, 200, 4096, 5000, 32768):
+                chunk, splits = decode_split(n_seqs, kv_heads, context)
+                blocks = (context + 63) // 64
+                assert chunk % 64 == 0 and splits >= 1
+                assert chunk * splits >= context                 # every key is in a split
+                assert chunk * (splits - 1) < blocks * 64        # and no split is empty
+    assert [decode_split(b, 8, 4096)[1] for b in (1, 2, 4, 8, 16, 32, 64)] == [16, 16, 8, 6, 3, 3, 4]
+    assert decode_split(1, 8, 32768)[1] <= CLUSTER_MAX_SPLITS
