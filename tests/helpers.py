@@ -30,8 +30,17 @@ TINY_ODD = {
     "num_key_value_heads": 1, "head_dim": 48, "rope_theta": 50000.0, "rms_norm_eps": 3e-6,
     "tie_word_embeddings": False,
 }
+# A fourth one with the head size of the large models, so that whole-model runs reach the kernels
+# that only take it: the tcgen05 prompt attention, the decode attention fed by TMA, and (with a
+# prompt of more than 128 tokens) the tiled tcgen05 product.
+TINY_WIDE = {
+    "architectures": ["LlamaForCausalLM"], "vocab_size": 520, "max_position_embeddings": 1024,
+    "hidden_size": 256, "intermediate_size": 384, "num_hidden_layers": 2, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 128, "rope_theta": 20000.0, "rms_norm_eps": 2e-5,
+    "tie_word_embeddings": False,
+}
 CONFIGS = {"tiny-llama": (TINY_LLAMA, 0, "float32"), "tiny-qwen3": (TINY_QWEN3, 1, "bfloat16"),
-           "tiny-odd": (TINY_ODD, 2, "bfloat16")}
+           "tiny-odd": (TINY_ODD, 2, "bfloat16"), "tiny-wide": (TINY_WIDE, 3, "bfloat16")}
 
 
 def make_folder(tmp_path, name: str, sharpen: float = 1.0) -> str:
@@ -67,3 +76,33 @@ def scaled_error(got: np.ndarray, want: np.ndarray) -> float:
 # float64 oracle.  bfloat16: activations are rounded to 8 bits of mantissa at the inputs of every
 # matrix product and in the cache.
 TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+
+def check_greedy_tokens(plain_config, plain_weights, prompt, tokens, tolerance: float):
+    """Greedy tokens of the engine against the plain model along the engine's own path: the plain
+    logits of prompt + tokens (teacher-forced) say, at every generated place, which token is best
+    and by how much.  Where the two best logits lie further apart than twice the tolerance (of the
+    logit scale), the engine's token must be the best one; at a nearer tie either may win, and from
+    there on the engine's continuation is judged along its own path, not dropped.  Returns the plain
+    logits [len(prompt) + len(tokens), vocab]."""
+    from plain.model import forward_logits
+
+    want = forward_logits(plain_config, plain_weights, list(prompt) + list(tokens))
+    scale = np.abs(want).max()
+    for i, token in enumerate(tokens):
+        row = want[len(prompt) + i - 1]
+        top = np.sort(row)[-2:]
+        if top[1] - top[0] > 2 * tolerance * scale:
+            assert int(token) == int(np.argmax(row)), (list(prompt), i, int(token), int(np.argmax(row)))
+    return want
+
+
+def replay_logits(engine, prompt, tokens):
+    """Logits of every place of prompt + tokens through ``engine.step``: the prompt in one step, then
+    one token a step."""
+    from xeno_rt_b200.engine import StepEntry
+    slot = engine.open_slot()
+    rows = [engine.step([StepEntry(slot, list(prompt), list(range(len(prompt))))]).cpu().numpy()]
+    rows += [engine.step([StepEntry(slot, [int(t)], [0])]).cpu().numpy() for t in tokens]
+    engine.close_slot(slot)
+    return np.concatenate(rows)

@@ -73,7 +73,7 @@ def rope_frequencies(rope_dim: int, base: float) -> np.ndarray:
 
 
 def rope(x: np.ndarray, positions, n_heads: int, head_dim: int, rope_dim: int, base: float,
-         scale: float) -> np.ndarray:
+         scale: float, pairing: str = "split_half") -> np.ndarray:
     """Split-half rotation of every head at the token's absolute position.
 
     angle = pos * scale / f_i in float32 (as the reference computes it), then
@@ -81,6 +81,8 @@ def rope(x: np.ndarray, positions, n_heads: int, head_dim: int, rope_dim: int, b
     h[i+half] = x0 * sin + x1 * cos      with x0 = h[i], x1 = h[i + half].
     Elements at or beyond rope_dim stay as they are.
     crates/xrt-kernels/src/cpu/rope.rs:19-35 (apply), 59-68 (angles).
+    ``pairing`` = "interleaved" is not the reference's: x0 = h[2i], x1 = h[2i + 1] with the same
+    angles, for the library's position encodings that pair neighbouring dims.
     """
     t = x.shape[0]
     half = min(rope_dim, head_dim) // 2
@@ -89,10 +91,12 @@ def rope(x: np.ndarray, positions, n_heads: int, head_dim: int, rope_dim: int, b
     angle = (pos * np.float32(scale) / freqs.reshape(1, half)).astype(np.float32).astype(F64)
     sin, cos = np.sin(angle), np.cos(angle)
     heads = x.astype(F64).reshape(t, n_heads, head_dim).copy()
-    x0 = heads[:, :, :half].copy()
-    x1 = heads[:, :, half:2 * half].copy()
-    heads[:, :, :half] = x0 * cos[:, None, :] - x1 * sin[:, None, :]
-    heads[:, :, half:2 * half] = x0 * sin[:, None, :] + x1 * cos[:, None, :]
+    first = slice(0, 2 * half, 2) if pairing == "interleaved" else slice(0, half)
+    second = slice(1, 2 * half, 2) if pairing == "interleaved" else slice(half, 2 * half)
+    x0 = heads[:, :, first].copy()
+    x1 = heads[:, :, second].copy()
+    heads[:, :, first] = x0 * cos[:, None, :] - x1 * sin[:, None, :]
+    heads[:, :, second] = x0 * sin[:, None, :] + x1 * cos[:, None, :]
     return heads.reshape(t, n_heads * head_dim)
 
 

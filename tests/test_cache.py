@@ -183,3 +183,53 @@ def test_random_traffic_never_loses_or_doubles_a_block(window):
     for s in list(live):
         c.close_slot(s)
     assert all(g.allocator.free == 20 for g in c.kv_groups) and c.slots.free == 6
+
+
+def test_a_place_may_ask_for_several_storages_by_list_and_by_part_name():
+    """A mixer that wants keys AND a fixed-size state asks with a list; a layer with two parts that
+    keep something asks with a dict by part name; ``store`` answers in the same shape, and equal
+    needs still share one group of storage."""
+    from xeno_rt_b200.cache import KVStore, StateStore
+    needs = [[KVNeed(2, 16), StateNeed((4,))],
+             {"mixer": KVNeed(2, 16), "memory": [StateNeed((4,)), StateNeed((2, 2), "int32")]},
+             None, {}]
+    c = _cache(needs=needs)
+    assert len(c.kv_groups) == 1 and c.kv_groups[0].k.shape[0] == 2
+    assert len(c.state_groups) == 2
+    first = c.store(0)
+    assert isinstance(first, list) and isinstance(first[0], KVStore) and isinstance(first[1], StateStore)
+    second = c.store(1)
+    assert set(second) == {"mixer", "memory"} and isinstance(second["mixer"], KVStore)
+    assert [tuple(s.state.shape[1:]) for s in second["memory"]] == [(4,), (2, 2)]
+    assert second["mixer"].k.data_ptr() != first[0].k.data_ptr()
+    assert second["memory"][0].state.data_ptr() != first[1].state.data_ptr()
+    assert c.store(2) is None and c.store(3) == {}
+    with pytest.raises(CacheError, match="unknown cache need"):
+        _cache(needs=[{"mixer": 3}])
+
+
+def test_a_step_that_cannot_be_served_takes_nothing():
+    """reserve_all serves every sequence of a step or none: when a later sequence finds the pool
+    empty, the earlier ones give back what they just took."""
+    c = _cache(max_tokens=64 * 4, needs=[KVNeed(2, 16), KVNeed(2, 16, window=70)])
+    a, b, d = c.open_slot(), c.open_slot(), c.open_slot()
+    assert c.reserve_all([a], [70]) == [0]
+    c.advance(a, 70)                       # a holds 2 of 4 blocks
+    free = c.blocks_free()
+    with pytest.raises(CacheError, match="full"):
+        c.reserve_all([b, a, d], [64, 1, 130])  # b takes one, a none, d needs three: one is left
+    assert c.blocks_free() == free
+    c.check()
+    assert c.length(b) == 0 and c.length(a) == 70
+    assert c.reserve_all([b, a], [64, 1]) == [0, 70]
+    c.advance(b, 64)
+    c.advance(a, 1)
+    c.check()
+    with pytest.raises(CacheError):       # a limit of the model's positions, after an entry that was served
+        c.reserve_all([d, a], [10, 10_000])
+    assert c.blocks_free() == 1
+    c.check()
+    for s in (a, b, d):
+        c.close_slot(s)
+    c.check()
+    assert c.blocks_free() == 4

@@ -76,11 +76,44 @@ def test_unsupported_options_and_architectures():
         load_config("/nonexistent/folder")
 
 
+def test_options_that_would_be_ignored_are_refused():
+    with pytest.raises(Unsupported, match="hidden_act"):
+        config_from_dict(dict(TINY_LLAMA, hidden_act="gelu"))
+    with pytest.raises(Unsupported, match="partial_rotary_factor"):
+        config_from_dict(dict(TINY_QWEN3, partial_rotary_factor=0.5))
+    with pytest.raises(Unsupported, match="mlp_bias"):
+        config_from_dict(dict(TINY_LLAMA, mlp_bias=True))
+    with pytest.raises(Unsupported, match="use_sliding_window"):
+        config_from_dict(dict(TINY_QWEN3, use_sliding_window=True))
+    config_from_dict(dict(TINY_LLAMA, hidden_act="silu", partial_rotary_factor=1.0, mlp_bias=False))
+
+
+def test_stop_ids_of_generation_config_join_those_of_config(tmp_path):
+    """Folders of chat models list the ids that end a turn in generation_config.json."""
+    (tmp_path / "config.json").write_text(json.dumps(TINY_LLAMA))          # eos_token_id 7
+    assert load_config(str(tmp_path))[1].eos_token_ids == (7,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [9, 7, 12], "temperature": 0.6}))
+    arch, cfg = load_config(str(tmp_path))
+    assert cfg.eos_token_ids == (7, 9, 12)
+    assert arch.build_spec(cfg).stop_ids == (7, 9, 12)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 5}))
+    assert load_config(str(tmp_path))[1].eos_token_ids == (7, 5)
+    raw = {k: v for k, v in TINY_LLAMA.items() if k != "eos_token_id"}
+    (tmp_path / "config.json").write_text(json.dumps(raw))
+    assert load_config(str(tmp_path))[1].eos_token_ids == (5,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": "end"}))
+    with pytest.raises(ConfigError, match="generation_config.json.*eos_token_id"):
+        load_config(str(tmp_path))
+    (tmp_path / "generation_config.json").write_text("{")
+    with pytest.raises(ConfigError, match="not valid JSON"):
+        load_config(str(tmp_path))
+
+
 def test_spec_names_every_size_from_the_config():
     arch, cfg = config_from_dict(TINY_QWEN3)
     spec = arch.build_spec(cfg)
     assert len(spec.layers) == 3 and [p.layer for p in spec.schedule] == [0, 1, 2]
-    mixer = spec.layers[1].mixer
+    mixer = spec.layers[1].parts["mixer"][1]
     assert mixer.kind == "attention" and mixer.params["n_heads"] == 6 and mixer.params["head_dim"] == 32
     assert mixer.params["position"]["params"] == {"rope_dim": 32, "base": 1000000.0, "scale": 1.0}
     assert spec.lm_head.weights["weight"] == "model.embed_tokens.weight"  # tied
@@ -126,10 +159,29 @@ def test_decode_attention_splits_cover_the_context_and_fill_the_rounds():
     for n_seqs in (1, 2, 3, 8, 17, 64, 300):
         for kv_heads in (1, 2, 8):
             for context in (1, 63, 64, 65, 200, 4096, 5000, 32768):
-                chunk, splits = decode_split(n_seqs, kv_heads, context)
+                chunk, splits = decode_split(n_seqs, kv_heads, context, 148)
                 blocks = (context + 63) // 64
                 assert chunk % 64 == 0 and splits >= 1
                 assert chunk * splits >= context                 # every key is in a split
                 assert chunk * (splits - 1) < blocks * 64        # and no split is empty
-    assert [decode_split(b, 8, 4096)[1] for b in (1, 2, 4, 8, 16, 32, 64)] == [16, 16, 8, 6, 3, 3, 4]
-    assert decode_split(1, 8, 32768)[1] <= CLUSTER_MAX_SPLITS
+    assert [decode_split(b, 8, 4096, 148)[1] for b in (1, 2, 4, 8, 16, 32, 64)] == [16, 16, 8, 6, 3, 3, 4]
+    assert decode_split(1, 8, 32768, 148)[1] <= CLUSTER_MAX_SPLITS
+
+
+def test_the_merging_block_of_decode_attention_is_never_given_more_splits_than_its_shared_memory_holds():
+    """The block that merges a (token, kv head)'s splits inside the attention kernel keeps
+    group * (2 * splits + 1) floats in its dynamic shared memory.  For every head-size class and group
+    the launcher's limit fits the smallest launch (12 KB at head size 16), and the engine's own split
+    counts (at most 64) stay under it wherever the merge is fused."""
+    from xeno_rt_b200.csrc import ops
+    for head_dim in range(16, 257, 16):
+        cp = max(4 * 64 * (head_dim * 2 + 16), 8 * 16 * (2 + head_dim + 8) * 4)
+        for group in (1, 2, 4, 5, 8, 16):
+            limit = ops.attention_decode_fused_max_splits(head_dim, group)
+            smallest = min(cp, 4 * (head_dim // 64) * 8192) if head_dim % 64 == 0 else cp  # the TMA tiles
+            assert limit >= 1 and group * (2 * limit + 1) * 4 <= smallest
+    assert ops.attention_decode_fused_max_splits(16, 16) < 96      # the advised overflow case is now refused
+    assert ops.attention_decode_fused_max_splits(64, 16) < 288
+    assert ops.attention_decode_fused_max_splits(128, 4) >= 64     # the engine's cases are all fused
+    with pytest.raises(Exception):
+        ops.attention_decode_fused_max_splits(20, 4)

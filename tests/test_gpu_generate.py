@@ -8,7 +8,8 @@ import sys
 import numpy as np
 import pytest
 
-from helpers import CONFIGS, TOL, make_folder, random_prompts, scaled_error
+from helpers import (CONFIGS, TOL, check_greedy_tokens, make_folder, random_prompts, replay_logits,
+                     scaled_error)
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -36,13 +37,16 @@ def test_greedy_generation_matches_the_plain_implementation(folders, dtype):
     session = Runtime.load(folder, dtype=dtype).new_session()
     requests = [GenerateRequest(p, max_tokens=8, temperature=0.0, repetition_penalty=1.0, stop_ids=()) for p in prompts]
     results, stats = session.generate_batch(requests)
+    from plain.files import read_model_folder
+    cfg, weights = read_model_folder(folder)
     for p, r in zip(prompts, results):
-        want = _plain_greedy(folder, p, 8)
         if dtype == "float32":
-            assert r.tokens == want
-        else:  # bfloat16 may part ways at a near tie; up to there it must agree
-            agree = next((i for i, (a, b) in enumerate(zip(r.tokens, want)) if a != b), 8)
-            assert agree >= 4, (r.tokens, want)
+            assert r.tokens == _plain_greedy(folder, p, 8)
+        # every token is the plain model's best at its place unless the plain model's two best logits
+        # lie within the precision's tolerance there; and the logits along the way are the plain ones
+        want = check_greedy_tokens(cfg, weights, p, r.tokens, TOL[dtype])
+        got = replay_logits(session.backend.engine, p, r.tokens[:-1])
+        assert scaled_error(got, want[:len(got)]) < TOL[dtype]
         assert r.finish_reason == "length" and r.prompt_tokens == len(p)
     assert stats.tokens == 24 and stats.decode_steps == 7
     # one request through the single-request calls gives the same tokens as inside the batch
@@ -105,6 +109,43 @@ def test_command_line(folders):
     assert [list(map(int, l.split(","))) for l in lines] == [_plain_greedy(folder, p, 6) for p in prompts]
     assert "tokens in" in proc.stderr and "tok/s" in proc.stderr
     bad = subprocess.run(cmd[:4] + ["/nonexistent", "--prompt-ids", "1"], capture_output=True, text=True, timeout=600)
+    assert bad.returncode == 1 and "no such file" in bad.stderr
+
+
+def test_command_line_with_a_configuration_and_a_seed_as_the_model(tmp_path):
+    """``--random-config cfg.json --seed-weights N`` draws on the device the weights that
+    ``write_random_model`` writes for that seed: the command gives the tokens of ``--model`` on the
+    written folder (stored as shards here, with stop ids in generation_config.json)."""
+    from helpers import TINY_QWEN3
+    from xeno_rt_b200.weights import write_random_model
+    raw = dict(TINY_QWEN3, tie_word_embeddings=False)
+    del raw["eos_token_id"]
+    folder = write_random_model(str(tmp_path / "m"), raw, seed=21, dtype="bfloat16", shards=3)
+    config_file = str(tmp_path / "cfg.json")
+    json.dump(raw, open(config_file, "w"))
+    prompts = random_prompts(320, [6, 11], seed=4)
+    common = ["--dtype", "float32", "--max-tokens", "7", "--temperature", "0", "--repetition-penalty", "1.0",
+              "--prompt-ids", ",".join(map(str, prompts[0])), "--prompt-ids", ",".join(map(str, prompts[1]))]
+    xrt = [sys.executable, os.path.join(ROOT, "bin", "xrt"), "generate"]
+    a = subprocess.run(xrt + ["--model", folder] + common, capture_output=True, text=True, timeout=600)
+    b = subprocess.run(xrt + ["--random-config", config_file, "--seed-weights", "21"] + common,
+                       capture_output=True, text=True, timeout=600)
+    assert a.returncode == 0 and b.returncode == 0, a.stderr + b.stderr
+    tokens = [list(map(int, l.split(","))) for l in a.stdout.strip().splitlines() if l]
+    assert len(tokens) == 2 and all(len(t) == 7 for t in tokens) and a.stdout == b.stdout
+    other = subprocess.run(xrt + ["--random-config", config_file, "--seed-weights", "22"] + common,
+                           capture_output=True, text=True, timeout=600)
+    assert other.returncode == 0 and other.stdout != a.stdout
+    # the stop id of generation_config.json ends the first sequence where it would emit that id
+    stop = tokens[0][3]
+    json.dump({"eos_token_id": [stop]}, open(os.path.join(folder, "generation_config.json"), "w"))
+    c = subprocess.run(xrt + ["--model", folder] + common, capture_output=True, text=True, timeout=600)
+    assert c.returncode == 0 and c.stdout.splitlines()[0] == ",".join(map(str, tokens[0][:tokens[0].index(stop)]))
+    # the two sources exclude each other, and one of them is needed
+    both = subprocess.run(xrt + ["--model", folder, "--random-config", config_file] + common, capture_output=True, text=True)
+    none = subprocess.run(xrt + common, capture_output=True, text=True)
+    assert both.returncode == 2 and none.returncode == 2
+    bad = subprocess.run(xrt + ["--random-config", str(tmp_path / "nope.json")] + common, capture_output=True, text=True)
     assert bad.returncode == 1 and "no such file" in bad.stderr
 
 

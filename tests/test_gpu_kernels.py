@@ -97,7 +97,10 @@ def _cache_for(seq_lens, n_kv, hd, dtype, shuffle_seed=0):
                                                         (3, 3, 256, 64, True), (8, 2, 80, 80, False),
                                                         (12, 4, 128, 128, True), (7, 1, 128, 128, False),
                                                         (4, 2, 128, 64, False)])
-def test_qk_rope_kv_write(dtype, nh, nkv, hd, rope_dim, qk_norm):
+@pytest.mark.parametrize("pairing", ["split_half", "interleaved"])
+def test_qk_rope_kv_write(dtype, nh, nkv, hd, rope_dim, qk_norm, pairing):
+    """Head norms, rotation of the first ``rope_dim`` dims (pairs (i, i + rope_dim / 2) or (2i, 2i + 1);
+    the rest of the head untouched, crates/xrt-kernels/src/cpu/rope.rs:19-35), q output and cache write."""
     seq_lens = [70, 3]
     starts = [60, 0]  # the first sequence continues at position 60 and crosses a block edge
     new = [10, 3]
@@ -114,16 +117,20 @@ def test_qk_rope_kv_write(dtype, nh, nkv, hd, rope_dim, qk_norm):
     ops().rope_table(cs, tok_pos, freq, 1.0)
     q_out = torch.empty(T, qw, device=DEV, dtype=DT[dtype])
     ops().qk_rope_kv_write(q_out, k_pool, v_pool, qkv, qw, qw + kw, qn, kn, 1e-6, cs, tok_slot, tok_pos, table,
-                           nh, nkv, hd)
+                           nh, nkv, hd, pairing=pairing)
     q, k, v = f64(qkv[:, :qw]), f64(qkv[:, qw:qw + kw]), f64(qkv[:, qw + kw:])
     if qk_norm:
         q = pm.head_rmsnorm(q, f64(qn), nh, hd, 1e-6)
         k = pm.head_rmsnorm(k, f64(kn), nkv, hd, 1e-6)
     pos = tok_pos.cpu().numpy()
-    q = pm.rope(q, pos, nh, hd, rope_dim, 10000.0, 1.0)
-    k = pm.rope(k, pos, nkv, hd, rope_dim, 10000.0, 1.0)
+    if rope_dim < hd:  # the dims beyond rope_dim are what the norm left
+        untouched = q.reshape(T, nh, hd)[:, :, rope_dim:].copy()
+    q = pm.rope(q, pos, nh, hd, rope_dim, 10000.0, 1.0, pairing)
+    k = pm.rope(k, pos, nkv, hd, rope_dim, 10000.0, 1.0, pairing)
     tol = 2e-6 if dtype == "float32" else 5e-3
     assert rel(q_out, q) < tol
+    if rope_dim < hd:
+        assert rel(q_out.reshape(T, nh, hd)[:, :, rope_dim:], untouched) < tol
     tab = table.cpu().numpy()
     for t in range(T):
         slot, p = int(tok_slot[t]), int(pos[t])
@@ -523,63 +530,6 @@ def test_attention_prefill_tcgen05_kernel(nh, nkv):
         else:
             assert bool((out[at:at + new[s]] == 5.0).all())  # the skipped sequence's rows are untouched
         at += new[s]
-
-
-@pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
-@pytest.mark.parametrize("width,inner,vocab", [(1032, 2760, 1003), (4096, 9000, 520), (264, 40, 77)])
-def test_decode_chain(m, width, inner, vocab):
-    """Norm, gate/up with SwiGLU, down into the residual, norm of gathered rows and an output product
-    as ONE launch of the persistent kernel, against the same phases as kernels of their own (the
-    same bits for the norms; products differ in the order of the sums only) and against float64.
-    The sizes cut K into chunks (9,000 at 8 and at 16 rows) and leave ragged last units."""
-    from xeno_rt_b200.csrc import ops as o
-    torch.manual_seed(m + width)
-    resid = torch.randn(m, width, device=DEV)
-    norm_w = (1 + 0.1 * torch.randn(width, device=DEV)).to(torch.bfloat16)
-    final_w = 1 + 0.1 * torch.randn(width, device=DEV)  # a norm weight kept in 32-bit
-    w_gu = (torch.randn(2 * inner, width, device=DEV) * 0.05).to(torch.bfloat16)
-    w_down = (torch.randn(width, inner, device=DEV) * 0.05).to(torch.bfloat16)
-    w_out = (torch.randn(vocab, width, device=DEV) * 0.05).to(torch.bfloat16)
-    rows = torch.arange(m - 1, -1, -2, dtype=torch.int32, device=DEV)  # every second row, backwards
-
-    def run(chained):
-        x = resid.clone()
-        if chained:
-            o.chain_begin(DEV)
-        h = torch.empty(m, width, device=DEV, dtype=torch.bfloat16)
-        o.rmsnorm(h, x, norm_w, 1e-5)
-        act = torch.empty(m, inner, device=DEV, dtype=torch.bfloat16)
-        o.gemm_stream(act, h, w_gu, "swiglu", up_rows=inner)
-        o.gemm_stream(x, act, w_down, "accumulate")
-        hn = torch.empty(rows.numel(), width, device=DEV, dtype=torch.bfloat16)
-        o.rmsnorm(hn, x, final_w, 1e-6, rows)
-        logits = torch.empty(rows.numel(), vocab, device=DEV)
-        o.gemm_stream(logits, hn, w_out)
-        if chained:
-            before = o.launch_count()
-            o.chain_end()
-            assert o.launch_count() == before + 1
-        return h, act, x, hn, logits
-
-    one = run(True)
-    o.check_error_flag(DEV)
-    assert int(o.device_state(DEV)[1].abs().sum()) == 0  # the chunk counters are zero again
-    two = run(False)
-    assert torch.equal(one[0], two[0])
-    # later phases start from intermediates that differ in the last bit of bfloat16 here and there
-    for a, b, tol in zip(one[1:], two[1:], (1e-2, 1e-3, 1e-2, 2e-2)):
-        assert rel(a, f64(b)) < tol
-    # the strict check: every phase against float64 from the chain's own intermediates
-    h64 = pm.rmsnorm(f64(resid), f64(norm_w), 1e-5)
-    assert rel(one[0], h64) < 5e-3
-    gate_up = f64(one[0]) @ f64(w_gu).T
-    assert rel(one[1], pm.swiglu(gate_up[:, :inner], gate_up[:, inner:])) < 5e-3
-    assert rel(one[2], f64(resid) + f64(one[1]) @ f64(w_down).T) < 1e-5
-    assert rel(one[4], f64(one[3]) @ f64(w_out).T) < 1e-5
-    # a second launch right after the first gives the same bits (the barrier and the counters reset themselves)
-    again = run(True)
-    for a, b in zip(one, again):
-        assert torch.equal(a, b)
 
 
 def test_attention_prefill_tcgen05_scores_that_jump():

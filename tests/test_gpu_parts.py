@@ -167,7 +167,7 @@ class RunningMeanMixer:
 
 
 def _toy_spec(schedule=None, share=False):
-    from xeno_rt_b200.parts import LayerSpec, ModelSpec, PartSpec, SchedulePlace
+    from xeno_rt_b200.parts import ModelSpec, PartSpec, SchedulePlace, prenorm_layer
     d, vocab = 40, 50
     norm = lambda name: PartSpec("rmsnorm", {"width": d, "eps": 1e-5}, {"weight": name})
     attn = PartSpec("attention", {"width": d, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16, "qk_norm": False,
@@ -175,8 +175,8 @@ def _toy_spec(schedule=None, share=False):
                                   "position": {"kind": "rotary", "params": {"rope_dim": 16, "base": 100.0, "scale": 1.0}}},
                     {"q": "l0.q", "k": "l0.k", "v": "l0.v", "o": "l0.o"})
     ffn = lambda i: PartSpec("swiglu", {"width": d, "inner": 24}, {"gate": f"l{i}.g", "up": f"l{i}.u", "down": f"l{i}.d"})
-    layers = [LayerSpec(norm("l0.n1"), attn, norm("l0.n2"), ffn(0)),
-              LayerSpec(norm("l1.n1"), PartSpec("test_running_mean", {"width": d}, {"w": "l1.w"}), norm("l1.n2"), ffn(1))]
+    layers = [prenorm_layer(norm("l0.n1"), attn, norm("l0.n2"), ffn(0)),
+              prenorm_layer(norm("l1.n1"), PartSpec("test_running_mean", {"width": d}, {"w": "l1.w"}), norm("l1.n2"), ffn(1))]
     schedule = schedule or [SchedulePlace(0), SchedulePlace(1)]
     return ModelSpec(vocab_size=vocab, hidden_size=d, max_positions=256,
                      embedding=PartSpec("token", {"vocab_size": vocab, "width": d}, {"weight": "emb"}),
@@ -265,7 +265,7 @@ def test_a_layer_named_twice_and_a_layer_reading_anothers_cache():
 def _windowed_spec():
     """Three attention layers of one shape: keys of the last 70 positions, every key, and the last 150
     positions read from the first layer's storage (which must then keep 150)."""
-    from xeno_rt_b200.parts import LayerSpec, ModelSpec, PartSpec, SchedulePlace
+    from xeno_rt_b200.parts import ModelSpec, PartSpec, SchedulePlace, prenorm_layer
     d, vocab = 40, 50
     norm = lambda name: PartSpec("rmsnorm", {"width": d, "eps": 1e-5}, {"weight": name})
     attn = lambda i, window: PartSpec(
@@ -274,7 +274,7 @@ def _windowed_spec():
                       "position": {"kind": "rotary", "params": {"rope_dim": 16, "base": 100.0, "scale": 1.0}}},
         {"q": f"l{i}.q", "k": f"l{i}.k", "v": f"l{i}.v", "o": f"l{i}.o"})
     ffn = lambda i: PartSpec("swiglu", {"width": d, "inner": 24}, {"gate": f"l{i}.g", "up": f"l{i}.u", "down": f"l{i}.d"})
-    layer = lambda i, window: LayerSpec(norm(f"l{i}.n1"), attn(i, window), norm(f"l{i}.n2"), ffn(i))
+    layer = lambda i, window: prenorm_layer(norm(f"l{i}.n1"), attn(i, window), norm(f"l{i}.n2"), ffn(i))
     return ModelSpec(vocab_size=vocab, hidden_size=d, max_positions=512,
                      embedding=PartSpec("token", {"vocab_size": vocab, "width": d}, {"weight": "emb"}),
                      layers=[layer(0, 70), layer(1, None), layer(2, 150)],
@@ -407,7 +407,7 @@ def test_toy_feed_forward_with_routing_and_another_position_encoding():
     """Both toy parts are registered from here, chosen by the spec for one layer of two, built and
     stepped (whole, cut into steps, and in a batch of two) without a change to the framework."""
     from xeno_rt_b200.engine import Engine, StepEntry
-    from xeno_rt_b200.parts import LayerSpec, ModelSpec, PartSpec, SchedulePlace, register_part
+    from xeno_rt_b200.parts import ModelSpec, PartSpec, SchedulePlace, prenorm_layer, register_part
     register_part("feed_forward", "test_routed", RoutedFeedForward, replace=True)
     register_part("position", "test_linear_angles", LinearAngles, replace=True)
     d, vocab, hd, nh, nkv, experts, inner = 40, 50, 16, 3, 1, 3, 24
@@ -418,10 +418,10 @@ def test_toy_feed_forward_with_routing_and_another_position_encoding():
                                       "eps": 1e-5, "window": None, "position": position},
                         {"q": f"l{i}.q", "k": f"l{i}.k", "v": f"l{i}.v", "o": f"l{i}.o"})
     layers = [
-        LayerSpec(norm("l0.n1"), attn(0, {"kind": "test_linear_angles", "params": {"rope_dim": 12, "step": 0.05}}),
+        prenorm_layer(norm("l0.n1"), attn(0, {"kind": "test_linear_angles", "params": {"rope_dim": 12, "step": 0.05}}),
                   norm("l0.n2"), PartSpec("test_routed", {"width": d, "inner": inner, "experts": experts},
                                           {"router": "l0.r", "w1": "l0.w1", "w2": "l0.w2"})),
-        LayerSpec(norm("l1.n1"), attn(1, {"kind": "rotary", "params": {"rope_dim": 16, "base": 100.0, "scale": 1.0}}),
+        prenorm_layer(norm("l1.n1"), attn(1, {"kind": "rotary", "params": {"rope_dim": 16, "base": 100.0, "scale": 1.0}}),
                   norm("l1.n2"), PartSpec("swiglu", {"width": d, "inner": inner}, {"gate": "l1.g", "up": "l1.u", "down": "l1.d"})),
     ]
     spec = ModelSpec(vocab_size=vocab, hidden_size=d, max_positions=256,
@@ -493,6 +493,147 @@ def test_toy_feed_forward_with_routing_and_another_position_encoding():
             engine.close_slot(sb)
     engine.close_slot(sa)
     assert close(np.concatenate(got_a), want_a) and close(np.concatenate(got_b), want_b)
+
+
+class InterleavedAngles:
+    """A toy position encoding that turns NEIGHBOURING dims (2i, 2i + 1) of a head by pos * (i + 1) *
+    step radians: it says so with ``pairing`` and hands the attention mixer its table."""
+    pairing = "interleaved"
+
+    @classmethod
+    def weight_shapes(cls, params):
+        return {}
+
+    def __init__(self, params, weights, dtype, device):
+        self.rope_dim = params["rope_dim"]
+        self.half = self.rope_dim // 2
+        self.step = float(params["step"])
+
+    def tables(self, ctx):
+        key = ("test_interleaved_angles", self.half, self.step)
+        if key not in ctx.shared:
+            i = torch.arange(1, self.half + 1, device=ctx.tok_pos.device, dtype=torch.float32)
+            angle = ctx.tok_pos.float()[:, None] * (i * self.step)[None]
+            ctx.shared[key] = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1).contiguous()
+        return ctx.shared[key]
+
+
+def sandwich_residual(parts, x, ctx, stores, owns_cache):
+    """A toy arrangement with a norm before AND after each of mixer and feed-forward:
+    x += post(mixer(pre(x))); x += post(ffn(pre(x))).  It uses six named parts of the layer."""
+    branch = torch.zeros_like(x)
+    parts.mixer.forward(parts.pre_mixer.forward(x), branch, ctx, stores.get("mixer"), owns_cache)
+    x += parts.post_mixer.forward(branch).float()
+    branch = torch.zeros_like(x)
+    parts.ffn.forward(parts.pre_ffn.forward(x), branch, ctx)
+    x += parts.post_ffn.forward(branch).float()
+
+
+def _keys_and_memory_mixer():
+    from xeno_rt_b200.cache import StateNeed
+    from xeno_rt_b200.parts.attention import GroupedQueryAttention
+
+    class KeysAndMemoryMixer(GroupedQueryAttention):
+        """A toy mixer that keeps keys AND a fixed-size state: attention plus 0.5 * the running mean
+        of its inputs.  It asks the cache for both with a list and is handed a list of storages."""
+
+        def cache_need(self):
+            return [super().cache_need(), StateNeed((self.width,), "float32")]
+
+        def forward(self, h, residual, ctx, store, owns_cache=True):
+            keys, memory = store
+            super().forward(h, residual, ctx, keys, owns_cache)
+            cu = ctx.cu_seqlens.tolist()
+            for i, slot in enumerate(ctx.seq_slot.tolist()):
+                seg = h[cu[i]:cu[i + 1]].float()
+                sums = memory.state[slot] + torch.cumsum(seg, dim=0)
+                counts = torch.arange(1, seg.shape[0] + 1, device=h.device).float() + ctx.starts[i]
+                residual[cu[i]:cu[i + 1]] += 0.5 * sums / counts[:, None]
+                if owns_cache:
+                    memory.state[slot] = sums[-1]
+
+    KeysAndMemoryMixer.graph_safe = False
+    return KeysAndMemoryMixer
+
+
+def test_a_layer_of_six_parts_an_interleaved_encoding_and_a_mixer_with_keys_and_state():
+    """Defined here alone and run through the unmodified engine: an arrangement over six named parts
+    (norms before and after mixer and feed-forward), a position encoding that pairs neighbouring
+    dims over part of the head, and a mixer whose ``cache_need`` is a list (keys and a state)."""
+    from xeno_rt_b200.engine import Engine, Model, StepEntry
+    from xeno_rt_b200.parts import LayerSpec, ModelSpec, PartSpec, SchedulePlace, prenorm_layer, register_part
+    register_part("position", "test_interleaved_angles", InterleavedAngles, replace=True)
+    register_part("arrangement", "test_sandwich", sandwich_residual, replace=True)
+    register_part("mixer", "test_keys_and_memory", _keys_and_memory_mixer(), replace=True)
+    d, vocab, hd, nh, nkv, inner, rd, step = 40, 50, 16, 3, 1, 24, 10, 0.07
+    norm = lambda name: PartSpec("rmsnorm", {"width": d, "eps": 1e-5}, {"weight": name})
+    attn = lambda i, kind: PartSpec(kind, {"width": d, "n_heads": nh, "n_kv_heads": nkv, "head_dim": hd, "qk_norm": False,
+                                           "eps": 1e-5, "window": None,
+                                           "position": {"kind": "test_interleaved_angles",
+                                                        "params": {"rope_dim": rd, "step": step}}},
+                                    {"q": f"l{i}.q", "k": f"l{i}.k", "v": f"l{i}.v", "o": f"l{i}.o"})
+    ffn = lambda i: PartSpec("swiglu", {"width": d, "inner": inner}, {"gate": f"l{i}.g", "up": f"l{i}.u", "down": f"l{i}.d"})
+    sandwich = LayerSpec({"pre_mixer": ("norm", norm("l0.n1")), "mixer": ("mixer", attn(0, "attention")),
+                          "post_mixer": ("norm", norm("l0.n2")), "pre_ffn": ("norm", norm("l0.n3")),
+                          "ffn": ("feed_forward", ffn(0)), "post_ffn": ("norm", norm("l0.n4"))}, "test_sandwich")
+    layers = [sandwich, prenorm_layer(norm("l1.n1"), attn(1, "test_keys_and_memory"), norm("l1.n2"), ffn(1))]
+    spec = ModelSpec(vocab_size=vocab, hidden_size=d, max_positions=256,
+                     embedding=PartSpec("token", {"vocab_size": vocab, "width": d}, {"weight": "emb"}),
+                     layers=layers, schedule=[SchedulePlace(0), SchedulePlace(1)], final_norm=norm("fn"),
+                     lm_head=PartSpec("linear", {"vocab_size": vocab, "width": d}, {"weight": "emb"}))
+    model, tensors = _toy_model(spec)
+    assert {e.name for e in spec.expected_tensors()} >= {"l0.n3", "l0.n4"}
+    needs = model.cache_needs()
+    assert set(needs[0]) == {"mixer"} and isinstance(needs[1]["mixer"], list) and len(needs[1]["mixer"]) == 2
+    engine = Engine(model, 64 * 4)
+    assert len(engine.cache.kv_groups) == 1 and len(engine.cache.state_groups) == 1
+
+    def turn(t, heads, n):
+        t = t.reshape(n, heads, hd).copy()
+        angle = np.arange(n)[:, None] * (np.arange(1, rd // 2 + 1) * step)[None]
+        c, s_ = np.cos(angle)[:, None, :], np.sin(angle)[:, None, :]
+        a, b = t[..., 0:rd:2].copy(), t[..., 1:rd:2].copy()  # pairs (2j, 2j + 1) of the first rd dims
+        t[..., 0:rd:2], t[..., 1:rd:2] = a * c - b * s_, a * s_ + b * c
+        return t.reshape(n, heads * hd)
+
+    def plain(tokens):
+        w = {k: f64(v) for k, v in tensors.items()}
+        n = len(tokens)
+        x = pm.embedding(w["emb"], tokens)
+
+        def attention(i, h):
+            q, k, v = pm.linear(h, w[f"l{i}.q"]), pm.linear(h, w[f"l{i}.k"]), pm.linear(h, w[f"l{i}.v"])
+            return pm.linear(pm.causal_gqa_attention(turn(q, nh, n), turn(k, nkv, n), v, nh, nkv, hd), w[f"l{i}.o"])
+
+        def mlp(i, h):
+            return pm.linear(pm.swiglu(pm.linear(h, w[f"l{i}.g"]), pm.linear(h, w[f"l{i}.u"])), w[f"l{i}.d"])
+        x = x + pm.rmsnorm(attention(0, pm.rmsnorm(x, w["l0.n1"], 1e-5)), w["l0.n2"], 1e-5)
+        x = x + pm.rmsnorm(mlp(0, pm.rmsnorm(x, w["l0.n3"], 1e-5)), w["l0.n4"], 1e-5)
+        h = pm.rmsnorm(x, w["l1.n1"], 1e-5)
+        x = x + attention(1, h) + 0.5 * np.cumsum(h, axis=0) / np.arange(1, n + 1)[:, None]
+        x = x + mlp(1, pm.rmsnorm(x, w["l1.n2"], 1e-5))
+        return pm.linear(pm.rmsnorm(x, w["fn"], 1e-5), w["emb"])
+
+    rng = np.random.default_rng(5)
+    a, b = rng.integers(0, vocab, size=75).tolist(), rng.integers(0, vocab, size=20).tolist()
+    want_a, want_b = plain(a), plain(b)
+    close = lambda got, want: np.abs(got - want).max() / np.abs(want).max() < 2e-5
+    assert close(_run_cut(engine, a, [75]), want_a)
+    assert close(_run_cut(engine, a, [40] + [1] * 35), want_a)   # the slot is used again: the state starts at zero
+    sa, sb = engine.open_slot(), engine.open_slot()
+    first = engine.step([StepEntry(sb, b[:18], list(range(18))), StepEntry(sa, a[:70], list(range(70)))]).cpu().numpy()
+    got_b, got_a = [first[:18]], [first[18:]]
+    for t in range(5):
+        entries = ([StepEntry(sb, [b[18 + t]], [0])] if t < 2 else []) + [StepEntry(sa, [a[70 + t]], [0])]
+        out = engine.step(entries).cpu().numpy()
+        if t < 2:
+            got_b.append(out[:1])
+        got_a.append(out[-1:])
+        if t == 1:
+            engine.close_slot(sb)
+    engine.close_slot(sa)
+    assert close(np.concatenate(got_a), want_a) and close(np.concatenate(got_b), want_b)
+    engine.cache.check()
 
 
 def test_spec_errors():

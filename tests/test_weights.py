@@ -116,3 +116,86 @@ def test_check_tensors_passes_when_all_fits():
     exp = _expected(TINY_LLAMA)
     header = {e.name: {"dtype": "F32", "shape": list(e.shape)} for e in exp}
     check_tensors(exp, header)
+
+
+def _load(folder, raw, dtype=DType.F32, **kw):
+    arch, cfg = config_from_dict(raw)
+    spec = arch.build_spec(cfg)
+    return load_weights(folder, spec.expected_tensors(), dtype, "cpu", spec.ignorable_tensors, **kw), spec
+
+
+def test_a_sharded_folder_loads_to_the_same_tensors_as_the_single_file(tmp_path):
+    """Three shards and their index against the one-file folder of the same seed: every tensor
+    bit for bit, also the tensors that land side by side in one shared buffer."""
+    one = write_random_model(str(tmp_path / "one"), TINY_QWEN3, seed=1, dtype="bfloat16")
+    three = write_random_model(str(tmp_path / "three"), TINY_QWEN3, seed=1, dtype="bfloat16", shards=3)
+    files = sorted(f for f in os.listdir(three) if f.endswith(".safetensors"))
+    assert files == [f"model-0000{i}-of-00003.safetensors" for i in (1, 2, 3)]
+    assert not os.path.exists(os.path.join(three, "model.safetensors"))
+    index = json.load(open(os.path.join(three, "model.safetensors.index.json")))
+    assert set(index["weight_map"].values()) == set(files)
+    stats = {}
+    a, spec = _load(one, TINY_QWEN3, DType.BF16)
+    b, _ = _load(three, TINY_QWEN3, DType.BF16, fused_groups=spec.fused_groups(), stats=stats)
+    assert set(a) == set(b) and stats["files"] == 3
+    for name in a:
+        assert a[name].dtype == b[name].dtype and torch.equal(a[name], b[name]), name
+    group = ("model.layers.1.self_attn.q_proj.weight", "model.layers.1.self_attn.k_proj.weight",
+             "model.layers.1.self_attn.v_proj.weight")
+    assert group in spec.fused_groups()
+    fused = b.fused[group]
+    assert torch.equal(fused, torch.cat([a[n] for n in group]))
+    assert b[group[1]].data_ptr() == fused[192:].data_ptr()  # a view of the shared buffer: no second copy
+
+
+def test_loading_holds_no_more_of_the_file_than_a_staging_piece(tmp_path, monkeypatch):
+    """Tensors go to the device in pieces through a staging buffer of fixed size: with the piece set
+    to 1 KiB a folder of 300 KB loads with 1 KiB in flight at any time, bit for bit."""
+    from xeno_rt_b200.weights import loader
+    folder = write_random_model(str(tmp_path / "m"), TINY_QWEN3, seed=4, dtype="float32", shards=2)
+    whole, _ = _load(folder, TINY_QWEN3)
+    monkeypatch.setattr(loader, "STAGING_BYTES", 1024)
+    stats = {}
+    pieces, _ = _load(folder, TINY_QWEN3, stats=stats)
+    assert 0 < stats["peak_staging_bytes"] <= 1024
+    largest = max(t.numel() * t.element_size() for t in whole.values())
+    assert largest > 50 * 1024
+    for name in whole:
+        assert torch.equal(whole[name], pieces[name])
+
+
+def test_one_error_for_a_broken_sharded_folder(tmp_path):
+    """A shard that is gone, a tensor that the index sends to the wrong shard, a tensor held by two
+    shards, a tensor no shard holds and a wrong shape: all in ONE error."""
+    from xeno_rt_b200.weights import locate_tensors
+    folder = write_random_model(str(tmp_path / "m"), TINY_LLAMA, seed=0, dtype="float32", shards=3)
+    index_path = os.path.join(folder, "model.safetensors.index.json")
+    index = json.load(open(index_path))
+    files = sorted(set(index["weight_map"].values()))
+    first = read_safetensors(os.path.join(folder, files[0]))
+    second = read_safetensors(os.path.join(folder, files[1]))
+    moved = sorted(second)[0]
+    dup = sorted(first)[0]
+    second[dup] = first[dup].clone()                       # held by two shards
+    wrong = sorted(second)[-1]
+    second[wrong] = torch.zeros(3, 3)                       # wrong shape
+    write_safetensors(os.path.join(folder, files[1]), second)
+    index["weight_map"][moved] = files[0]                  # the index points at a shard that does not hold it
+    index["weight_map"]["model.phantom.weight"] = files[2]  # shard 3 is deleted below
+    json.dump(index, open(index_path, "w"))
+    os.remove(os.path.join(folder, files[2]))
+    with pytest.raises(WeightError) as err:
+        _load(folder, TINY_LLAMA)
+    text = str(err.value)
+    assert text.count("does not fit the model") == 1
+    assert f"missing shard file: {files[2]}" in text
+    assert "listed in the index but absent from their shard" in text and moved in text
+    assert "held by two shards (1)" in text and dup in text
+    assert "missing tensors" in text  # those of the deleted shard
+    assert "wrong shape or dtype" in text and f"{wrong}: shape [3, 3]" in text
+    header, where, problems, source = locate_tensors(folder)
+    assert source.endswith("index.json") and len(problems) >= 3
+    # an index that is not an index
+    open(index_path, "w").write("{\"weight_map\": 3}")
+    with pytest.raises(WeightError, match="weight_map"):
+        _load(folder, TINY_LLAMA)

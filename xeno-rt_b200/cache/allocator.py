@@ -1,4 +1,4 @@
-"""Host-side allocators of the cache: blocks of 64 token positions, and slots (one a sequence).
+"""Host-side allocators of the cache: blocks of token positions, and slots (one a sequence).
 
 Both are plain free lists with the bookkeeping that makes misuse an error instead of a silent
 fault: nothing is handed out twice, nothing is taken back twice, and what is free plus what is
@@ -32,8 +32,7 @@ class BlockAllocator:
         if n < 0:
             raise CacheError(f"cannot take {n} blocks")
         if n > len(self._free):
-            raise CacheError(f"the cache is full: {n} blocks of {64} tokens are needed, {len(self._free)} of "
-                             f"{self.count} are free")
+            raise CacheError(f"the cache is full: {n} blocks are needed, {len(self._free)} of {self.count} are free")
         out = [self._free.pop() for _ in range(n)]
         for b in out:
             self._held[b] = True

@@ -26,9 +26,8 @@ import torch
 
 from ..core import CacheError, DType, torch_dtype
 from .allocator import BlockAllocator, SlotAllocator
-from .spec import KVNeed, StateNeed
+from .spec import BLOCK_TOKENS, KVNeed, StateNeed
 
-BLOCK_TOKENS = 64
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32,
                  "int64": torch.int64}
 
@@ -76,10 +75,38 @@ class _KVGroup:
         return 2 * self.k.numel() * self.k.element_size()
 
 
+def _flatten(need, path=()):
+    """(path, need) for every single need inside what a place asks for: a need, None, a list of
+    those, or a dict from part names to those."""
+    if need is None:
+        return
+    if isinstance(need, dict):
+        for key, inner in need.items():
+            yield from _flatten(inner, path + (key,))
+    elif isinstance(need, (list, tuple)):
+        for i, inner in enumerate(need):
+            yield from _flatten(inner, path + (i,))
+    else:
+        yield path, need
+
+
+def _rebuild(need, stores: dict, path=()):
+    """The stores in the shape in which the needs were given."""
+    if need is None:
+        return None
+    if isinstance(need, dict):
+        return {key: _rebuild(inner, stores, path + (key,)) for key, inner in need.items()}
+    if isinstance(need, (list, tuple)):
+        return [_rebuild(inner, stores, path + (i,)) for i, inner in enumerate(need)]
+    return stores[path]
+
+
 class Cache:
-    """See the module text.  ``needs`` has one entry for each place of the model's schedule:
-    a ``KVNeed``, a ``StateNeed`` or None (a place that owns no cache, e.g. because it reads
-    another place's)."""
+    """See the module text.  ``needs`` has one entry for each place of the model's schedule: what
+    the place's parts ask for.  An entry is a ``KVNeed``, a ``StateNeed``, None (a place that owns
+    no cache, e.g. because it reads another place's), a list of those (a part that wants several
+    storages, say keys and a fixed-size state), or a dict from part names to those (a layer with
+    several parts that keep something); ``store(place)`` answers in the same shape."""
 
     def __init__(self, needs: list, max_tokens: int, max_positions: int, dtype: DType, device,
                  max_slots: int | None = None):
@@ -97,17 +124,17 @@ class Cache:
         self.lengths = [0] * self.max_slots
         self._n_seq_blocks = [0] * self.max_slots
 
-        kv_needs: dict[KVNeed, list[int]] = {}
-        state_needs: dict[StateNeed, list[int]] = {}
-        for entry, need in enumerate(needs):
-            if need is None:
-                continue
-            if isinstance(need, KVNeed):
-                kv_needs.setdefault(need, []).append(entry)
-            elif isinstance(need, StateNeed):
-                state_needs.setdefault(need, []).append(entry)
-            else:
-                raise CacheError(f"schedule place {entry}: unknown cache need {need!r}")
+        kv_needs: dict[KVNeed, list] = {}
+        state_needs: dict[StateNeed, list] = {}
+        self._needs = list(needs)
+        for place, asked in enumerate(needs):
+            for path, need in _flatten(asked):
+                if isinstance(need, KVNeed):
+                    kv_needs.setdefault(need, []).append((place, path))
+                elif isinstance(need, StateNeed):
+                    state_needs.setdefault(need, []).append((place, path))
+                else:
+                    raise CacheError(f"schedule place {place}: unknown cache need {need!r}")
         tdtype = torch_dtype(dtype)
         self.kv_groups = [_KVGroup(need, entries, self.n_blocks, self.max_slots, self.blocks_per_seq, tdtype,
                                    self.device) for need, entries in kv_needs.items()]
@@ -118,18 +145,20 @@ class Cache:
             tensor = torch.zeros((len(entries), self.max_slots) + tuple(need.shape),
                                  dtype=_STATE_DTYPES[need.dtype], device=self.device)
             self.state_groups.append((need, entries, tensor))
-        self._stores: dict[int, object] = {}
+        flat: dict[int, dict] = {}
         for group in self.kv_groups:
-            for i, entry in enumerate(group.entries):
-                self._stores[entry] = KVStore(group.k[i], group.v[i], group.table, group.need)
+            for i, (place, path) in enumerate(group.entries):
+                flat.setdefault(place, {})[path] = KVStore(group.k[i], group.v[i], group.table, group.need)
         for need, entries, tensor in self.state_groups:
-            for i, entry in enumerate(entries):
-                self._stores[entry] = StateStore(tensor[i], need)
+            for i, (place, path) in enumerate(entries):
+                flat.setdefault(place, {})[path] = StateStore(tensor[i], need)
+        self._stores = {place: _rebuild(asked, flat.get(place, {})) for place, asked in enumerate(needs)}
         self.sequence_state: dict[str, torch.Tensor] = {}
 
     # ------------------------------------------------------------------ storage
     def store(self, entry: int):
-        """The storage of schedule place ``entry`` (KVStore, StateStore or None)."""
+        """The storage of schedule place ``entry``, in the shape in which the place asked for it
+        (a KVStore or StateStore, None, a list, or a dict by part name)."""
         return self._stores.get(entry)
 
     def register_sequence_state(self, name: str, shape: tuple, dtype) -> torch.Tensor:
@@ -142,6 +171,11 @@ class Cache:
         tensor = torch.zeros((self.max_slots,) + tuple(shape), dtype=dtype, device=self.device)
         self.sequence_state[name] = tensor
         return tensor
+
+    @property
+    def capacity_tokens(self) -> int:
+        """Token positions the block pools hold."""
+        return self.n_blocks * BLOCK_TOKENS
 
     def nbytes(self) -> int:
         total = sum(g.nbytes() for g in self.kv_groups)
@@ -202,6 +236,33 @@ class Cache:
                 group.dirty.add(slot)
             self._n_seq_blocks[slot] = need_blocks
         return start
+
+    def unreserve(self, slot: int) -> None:
+        """Gives back the blocks that ``reserve`` took for tokens that never came (what the slot
+        holds beyond its length)."""
+        keep = max((self.length(slot) + BLOCK_TOKENS - 1) // BLOCK_TOKENS, 0)
+        have = self._n_seq_blocks[slot]
+        if have <= keep:
+            return
+        for group in self.kv_groups:
+            first = max(keep, group.first_block[slot])
+            group.allocator.give_back(int(b) for b in group.table_host[slot, first:have])
+            group.table_host[slot, keep:have] = -1
+            group.dirty.add(slot)
+        self._n_seq_blocks[slot] = keep
+
+    def reserve_all(self, slots, counts) -> list:
+        """``reserve`` for every sequence of a step, or for none: if one of them cannot be served,
+        what the earlier ones just took goes back before the error is raised."""
+        starts = []
+        try:
+            for slot, n_new in zip(slots, counts):
+                starts.append(self.reserve(slot, n_new))
+        except CacheError:
+            for slot in list(slots)[:len(starts)]:
+                self.unreserve(slot)
+            raise
+        return starts
 
     def advance(self, slot: int, n_new: int) -> None:
         if self.length(slot) + n_new > self._n_seq_blocks[slot] * BLOCK_TOKENS:

@@ -9,6 +9,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+BLOCK_TOKENS = 64  # token positions of one cache block; the attention kernels' key tile (csrc/common.cuh)
+
 
 @dataclass(frozen=True)
 class KVNeed:

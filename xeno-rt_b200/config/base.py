@@ -28,6 +28,11 @@ class ModelConfig:
     def to_dict(self) -> dict:  # pragma: no cover - interface
         raise NotImplementedError
 
+    def with_stop_ids(self, ids: tuple) -> "ModelConfig":
+        """The same configuration with ``ids`` as its stop ids (``eos_token_ids``)."""
+        import dataclasses
+        return dataclasses.replace(self, eos_token_ids=tuple(ids))
+
 
 class KeyReader:
     """Reads keys of a config.json dict with type checks and collects what was wrong, so that one
@@ -105,3 +110,22 @@ def read_config_json(folder: str) -> dict:
     if not isinstance(raw, dict):
         raise ConfigError(f"{path}: the top level must be an object")
     return raw
+
+
+def read_generation_stop_ids(folder: str) -> tuple:
+    """``eos_token_id`` (an integer or a list) of the folder's generation_config.json; () if the
+    file or the key is absent.  Folders of chat models keep the ids that end a turn there."""
+    path = os.path.join(folder, "generation_config.json")
+    if not os.path.exists(path):
+        return ()
+    try:
+        with open(path) as fh:
+            raw = json.load(fh)
+    except json.JSONDecodeError as exc:
+        raise ConfigError(f"{path}: not valid JSON ({exc})") from None
+    if not isinstance(raw, dict):
+        raise ConfigError(f"{path}: the top level must be an object")
+    reader = KeyReader(raw, where=path)
+    ids = reader.int_tuple("eos_token_id")
+    reader.finish()
+    return ids

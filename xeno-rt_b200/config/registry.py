@@ -10,7 +10,7 @@ from dataclasses import dataclass
 from typing import Callable
 
 from ..core import ConfigError, Unsupported
-from .base import ModelConfig, read_config_json
+from .base import ModelConfig, read_config_json, read_generation_stop_ids
 
 
 @dataclass(frozen=True)
@@ -54,4 +54,12 @@ def config_from_dict(raw: dict) -> tuple[Architecture, ModelConfig]:
 
 
 def load_config(folder: str) -> tuple[Architecture, ModelConfig]:
-    return config_from_dict(read_config_json(folder))
+    """The folder's config.json as a typed configuration.  Its stop ids are config.json's
+    ``eos_token_id`` followed by those of generation_config.json that it does not name already
+    (the reference takes its one id from the model file, crates/xrt-runtime/src/session.rs:110)."""
+    arch, config = config_from_dict(read_config_json(folder))
+    extra = read_generation_stop_ids(folder)
+    if extra:
+        own = tuple(getattr(config, "eos_token_ids", ()))
+        config = config.with_stop_ids(own + tuple(i for i in extra if i not in own))
+    return arch, config

@@ -566,18 +566,14 @@ inline int decode_tma_smem(int head_dim) {
   return 1024 + max(4 * (head_dim / 64) * DEC_BOX_BYTES, merge_bytes);
 }
 
-// XRT_DECODE_ATTN=nocluster keeps the merge by a second kernel or by the last block, for comparison.
+// Tuning::decode_attention = 3 keeps the merge by a second kernel or by the last block, for comparison.
 // Only for few (token, kv head) pairs: measured at the 8B shape, clusters win at 1 to 4 sequences (3.77
 // against 3.87 ms and 4.12 against 4.25 ms a step) and lose at 8 (4.90 against 4.68 ms: clusters of 6
 // blocks of 66 KB each are harder to place than single blocks).
 constexpr int DEC_CLUSTER_MAX_PAIRS = 32;
 
 inline bool decode_cluster_wanted(int n_splits, int pairs) {
-  static int off = -1;
-  if (off < 0) {
-    const char* env = getenv("XRT_DECODE_ATTN");
-    off = (env != nullptr && env[0] == 'n') ? 1 : 0;
-  }
+  const bool off = tuning().decode_attention == 3;
   return !off && n_splits >= 2 && n_splits <= DEC_MAX_CLUSTER && pairs <= DEC_CLUSTER_MAX_PAIRS;
 }
 
@@ -672,8 +668,8 @@ int launch_decode_as(__nv_bfloat16* out, float* part_o, float* part_ml, const __
 
 // Groups of at most 8 query heads take the form with the heads as the MMA's columns, fed by TMA when
 // the head size is a multiple of 64 and the caller says how many blocks the pools hold.
-// XRT_DECODE_ATTN in the environment, for comparison: "rows" keeps the heads-as-rows form everywhere,
-// "cp" keeps the 16-byte asynchronous copies.
+// Tuning::decode_attention, for comparison: 1 keeps the heads-as-rows form everywhere, 2 keeps the
+// 16-byte asynchronous copies, 3 keeps clusters off.
 template <int HD_MAX>
 int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_bfloat16* q,
                   const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, long long pool_rows, const int* tok_slot,
@@ -681,12 +677,7 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_
                   int head_dim, float scale, int window, int chunk, int n_splits, int* counters, int* error_flag,
                   cudaStream_t stream, bool* merged) {
   *merged = false;
-  static int rows_only = -1, copies_only = 0;
-  if (rows_only < 0) {
-    const char* env = getenv("XRT_DECODE_ATTN");
-    rows_only = (env != nullptr && env[0] == 'r') ? 1 : 0;
-    copies_only = (env != nullptr && env[0] == 'c') ? 1 : 0;
-  }
+  const bool rows_only = tuning().decode_attention == 1, copies_only = tuning().decode_attention == 2;
   if (n_heads / n_kv_heads <= 8 && !rows_only && !copies_only && pool_rows > 0 && head_dim % 64 == 0 &&
       (((uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0)
     return launch_decode_tma<HD_MAX>(out, part_o, part_ml, q, k_pool, v_pool, pool_rows, tok_slot, tok_pos, block_table,
@@ -701,7 +692,23 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_
                                          n_splits, counters, stream);
 }
 
+// The merge by a (token, kv head)'s last block keeps group * (2 * n_splits + 1) floats in the block's
+// dynamic shared memory.  The most splits for which that fits the smallest launch of any variant
+// (the cp.async tiles, the TMA tiles after their alignment slack); beyond it the second kernel merges.
+inline int decode_fused_max_splits(int head_dim, int group) {
+  const int tile_bytes = XRT_BLOCK_TOKENS * (head_dim * 2 + 16);
+  const int merge_bytes = DEC_WARPS * 16 * (2 + head_dim + 8) * (int)sizeof(float);
+  int smallest = max(4 * tile_bytes, merge_bytes);
+  if (head_dim % 64 == 0) smallest = min(smallest, decode_tma_smem(head_dim) - 1024);
+  return (smallest / (int)sizeof(float) / group - 1) / 2;
+}
+
 }  // namespace xrt
+
+XRT_EXPORT int xrt_attention_decode_fused_max_splits(int head_dim, int group) {
+  if (head_dim < 16 || head_dim > 256 || head_dim % 16 != 0 || group < 1 || group > 16) return XRT_ERR_UNSUPPORTED;
+  return xrt::decode_fused_max_splits(head_dim, group);
+}
 
 namespace xrt {
 
@@ -720,6 +727,8 @@ static int attention_decode_impl(void* out, float* part_o, float* part_ml, const
     return XRT_ERR_UNSUPPORTED;
   if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return XRT_ERR_ARGUMENT;
   if (n_tokens == 0) return XRT_OK;
+  // more splits than the merging block's shared memory holds: the second kernel merges them
+  if (counters != nullptr && n_splits > decode_fused_max_splits(head_dim, n_heads / n_kv_heads)) counters = nullptr;
   auto* o = (__nv_bfloat16*)out;
   auto* qp = (const __nv_bfloat16*)q;
   auto* kp = (const __nv_bfloat16*)k_pool;

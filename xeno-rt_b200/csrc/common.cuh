@@ -23,6 +23,15 @@
 
 namespace xrt {
 
+// Kernel variants a caller may force (tuning.cu holds the one instance; xrt_set_tuning sets it).
+struct Tuning {
+  bool pdl = true;                  // launch with programmatic dependent launch
+  int decode_attention = 0;         // 0 auto, 1 heads as rows, 2 cp.async copies, 3 no clusters
+  int gemm_tile_rows = 0;           // 0 auto, 128 or 256: the prefill product's tile
+  bool decode_gemm_clusters = true; // the decode product's splits meet through a cluster's shared memory
+};
+const Tuning& tuning();
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 
@@ -67,19 +76,12 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // overlaps the predecessor's tail and hides its own launch latency; pdl_wait() returns once the
 // predecessor has completed and its writes are visible.  Every kernel of the decode step calls
 // pdl_trigger() first (its successor may be launched) and pdl_wait() before it touches anything a
-// predecessor wrote or reads anything it will overwrite.  XRT_PDL=0 in the environment turns the
-// launch attribute off (the instructions are then no-ops).
+// predecessor wrote or reads anything it will overwrite.  Tuning::pdl = false turns the launch
+// attribute off (the instructions are then no-ops).
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-inline bool pdl_enabled() {
-  static int enabled = -1;
-  if (enabled < 0) {
-    const char* env = getenv("XRT_PDL");
-    enabled = (env != nullptr && env[0] == '0') ? 0 : 1;
-  }
-  return enabled == 1;
-}
+inline bool pdl_enabled() { return tuning().pdl; }
 
 template <typename... KArgs, typename... Args>
 inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

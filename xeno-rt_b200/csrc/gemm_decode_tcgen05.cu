@@ -474,15 +474,8 @@ static int choose_splits(int tiles, int k_iters, int sms, int groups, int nb) {
   return best;
 }
 
-// XRT_DECODE_GEMM_CLUSTER=0 keeps the scratch-and-counter reduction everywhere, for comparison.
-inline bool decode_gemm_clusters_wanted() {
-  static int wanted = -1;
-  if (wanted < 0) {
-    const char* env = getenv("XRT_DECODE_GEMM_CLUSTER");
-    wanted = (env != nullptr && env[0] == '0') ? 0 : 1;
-  }
-  return wanted == 1;
-}
+// Tuning::decode_gemm_clusters = false keeps the scratch-and-counter reduction everywhere, for comparison.
+inline bool decode_gemm_clusters_wanted() { return tuning().decode_gemm_clusters; }
 
 template <int MODE, typename TO>
 int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorMap& map_w, const CUtensorMap& map_x,

@@ -370,7 +370,7 @@ int launch_tcgen05_tiled(void* out, const CUtensorMap& map_x, const CUtensorMap&
 // Tiles of 256 rows for products of few tiles, when they keep the multiprocessors about as busy as
 // tiles of 128 rows would (the larger tile moves a third fewer operand bytes per flop and drains its
 // accumulator with twice the warps; with many tiles the overlap of the small tile's two accumulators wins).
-// XRT_GEMM_TILE_ROWS=128 or 256 forces one, for comparison.
+// Tuning::gemm_tile_rows = 128 or 256 forces one, for comparison.
 template <int MODE, typename TO>
 int launch_tcgen05(void* out, const CUtensorMap& map_x, const CUtensorMap& map_w, int M, int N, int K, int ldo,
                    int up_rows, int* error_flag, int sm_count, cudaStream_t stream) {
@@ -379,8 +379,7 @@ int launch_tcgen05(void* out, const CUtensorMap& map_x, const CUtensorMap& map_w
   auto busy = [&](long long tiles) { return (double)tiles / (double)(((tiles + sm_count - 1) / sm_count) * sm_count); };
   const long long small_tiles = ((M + 127) / 128) * tiles_n;
   const double small = busy(small_tiles), large = 1.25 * busy(((M + 255) / 256) * tiles_n);
-  static int forced = -1;
-  if (forced < 0) { const char* e = getenv("XRT_GEMM_TILE_ROWS"); forced = e ? atoi(e) : 0; }
+  const int forced = tuning().gemm_tile_rows;
   // measured at 2,048 and 8,192 rows: the large tile wins where the small one leaves under two rounds of work
   const bool use_large = forced == 256 || (forced != 128 && M > 128 && small_tiles <= 2 * sm_count && large > small);
   if (use_large)

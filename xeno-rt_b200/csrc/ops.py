@@ -7,7 +7,9 @@ no fallback: without a CUDA device or without the built library every function r
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import dataclasses
 import threading
 
 import torch
@@ -29,7 +31,7 @@ _SIGNATURES = {
     "xrt_swiglu": [_P, _P, _I, _I, _I, _I, _P],
     "xrt_rope_table": [_P, _P, _P, _F, _I, _I, _P],
     "xrt_qk_rope_kv_write": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I,
-                             _I, _I, _I, _I, _P],
+                             _I, _I, _I, _I, _I, _P],
     "xrt_attention_reference": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
     "xrt_gemm_reference": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -42,7 +44,6 @@ _SIGNATURES = {
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
     "xrt_sample": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P],
     "xrt_mark_seen": [_P, _I, _P, _P, _I, _I, _P],
-    "xrt_decode_chain": [_P, _I, _P, _I, _P, _P],
 }
 
 
@@ -65,6 +66,10 @@ def library():
                     raise KernelError(f"{path} does not export {name}") from None
                 fn.argtypes = argtypes
                 fn.restype = _I
+            lib.xrt_attention_decode_fused_max_splits.argtypes = [_I, _I]
+            lib.xrt_attention_decode_fused_max_splits.restype = _I
+            lib.xrt_set_tuning.argtypes = [_I, _I]
+            lib.xrt_set_tuning.restype = _I
             lib.xrt_gemm_decode_tcgen05_scratch.argtypes = [_I, _I, _I, _I, _I]
             lib.xrt_gemm_decode_tcgen05_scratch.restype = ctypes.c_longlong
             lib.xrt_gemm_decode_tcgen05_plan.argtypes = [_I, _I, _I, _I, _I, ctypes.POINTER(ctypes.c_int)]
@@ -74,11 +79,66 @@ def library():
 
 
 def _kernels():
-    """The library, for a launch that is issued now: phases waiting in a chain are launched first,
-    so that device work keeps the order in which the parts asked for it."""
-    if _chain is not None and _chain.entries:
-        chain_flush()
     return library()
+
+
+@dataclasses.dataclass(frozen=True)
+class Tuning:
+    """Which kernel variant runs where the library has several; the defaults are the measured
+    choices.  Set with ``set_tuning`` (process-wide, since the parts call the kernels directly) or
+    for a stretch of code with ``tuned(...)``; ``Engine(tuning=...)`` sets it when the engine is made.
+
+    ``graphs``           decode steps are replayed from CUDA graphs
+    ``pdl``              kernels of a step are launched with programmatic dependent launch
+    ``decode_gemm``      "auto", or "stream" / "tcgen05" to force one of the few-row products
+    ``decode_gemm_clusters``  splits of K of the tcgen05 few-row product meet through a cluster
+    ``decode_attention`` "auto", "rows" (query heads as MMA rows), "cp" (cp.async tiles), "nocluster"
+    ``prefill_attention`` "auto" or "mma" (the mma.sync kernel also where the tcgen05 one applies)
+    ``gemm_tile_rows``   0 (auto), 128 or 256: the tile of the prompt product
+    """
+    graphs: bool = True
+    pdl: bool = True
+    decode_gemm: str = "auto"
+    decode_gemm_clusters: bool = True
+    decode_attention: str = "auto"
+    prefill_attention: str = "auto"
+    gemm_tile_rows: int = 0
+
+
+_DECODE_ATTENTION = {"auto": 0, "rows": 1, "cp": 2, "nocluster": 3}
+_tuning = Tuning()
+
+
+def tuning() -> Tuning:
+    return _tuning
+
+
+def set_tuning(new: Tuning) -> None:
+    """Makes ``new`` the tuning of every later launch of this process."""
+    global _tuning
+    if new.decode_gemm not in ("auto", "stream", "tcgen05"):
+        raise KernelError(f"tuning: decode_gemm {new.decode_gemm!r} is not auto, stream or tcgen05")
+    if new.decode_attention not in _DECODE_ATTENTION:
+        raise KernelError(f"tuning: decode_attention {new.decode_attention!r} is not one of {sorted(_DECODE_ATTENTION)}")
+    if new.prefill_attention not in ("auto", "mma"):
+        raise KernelError(f"tuning: prefill_attention {new.prefill_attention!r} is not auto or mma")
+    lib = library()
+    for key, value in ((0, int(new.pdl)), (1, _DECODE_ATTENTION[new.decode_attention]),
+                       (2, int(new.gemm_tile_rows)), (3, int(new.decode_gemm_clusters))):
+        if lib.xrt_set_tuning(key, value) != 0:
+            raise KernelError(f"tuning: value {value} of setting {key} was refused")
+    _tuning = new
+
+
+@contextlib.contextmanager
+def tuned(**changes):
+    """``with tuned(prefill_attention="mma"): ...`` runs the body with these settings changed."""
+    before = _tuning
+    set_tuning(dataclasses.replace(before, **changes))
+    try:
+        yield
+    finally:
+        set_tuning(before)
 
 
 def require_device() -> None:
@@ -153,9 +213,6 @@ def rmsnorm(out, x, weight, eps: float, rows=None) -> None:
         raise KernelError("rmsnorm: shapes do not fit")
     if rows is not None and rows.numel() != n_rows:
         raise KernelError("rmsnorm: one row index per output row is needed")
-    if _chain is not None and _chain.takes_norm(out, x, weight, rows):
-        _chain.add_norm(out, x, weight, eps, rows)
-        return
     _check(_kernels().xrt_rmsnorm(_ptr(out, "out"), _ptr(x, "x", torch.float32), _ptr(weight, "weight"),
                                  _ptr(rows, "rows", torch.int32), n_rows, width, float(eps),
                                  _code(weight.dtype), _code(out.dtype), _stream()), "rmsnorm")
@@ -182,8 +239,12 @@ def rope_table(cos_sin, positions, freq, scale: float) -> None:
 
 def qk_rope_kv_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, q_norm_w, k_norm_w, eps: float,
                      cos_sin, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int, head_dim: int,
-                     write_kv: bool = True) -> None:
-    """Head norms, rotation, q output and cache write in one kernel; see rotary_kv.cu."""
+                     write_kv: bool = True, pairing: str = "split_half") -> None:
+    """Head norms, rotation, q output and cache write in one kernel; see rotary_kv.cu.  ``cos_sin``
+    [T, rope_dim / 2, 2] rotates the first rope_dim dims of every head: pairs (i, i + rope_dim / 2)
+    with ``pairing`` "split_half", pairs (2i, 2i + 1) with "interleaved"; the rest stays as it is."""
+    if pairing not in ("split_half", "interleaved"):
+        raise KernelError(f"qk_rope_kv_write: pairing {pairing!r} is not split_half or interleaved")
     n = qkv.shape[0]
     rope_half = 0 if cos_sin is None else cos_sin.shape[1]
     if q_out.shape != (n, n_heads * head_dim) or tok_slot.numel() != n or tok_pos.numel() != n:
@@ -202,7 +263,8 @@ def qk_rope_kv_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, q
         v_offset, _ptr(q_norm_w, "q_norm_w"), _ptr(k_norm_w, "k_norm_w"), float(eps),
         _ptr(cos_sin, "cos_sin", torch.float32), rope_half, _ptr(tok_slot, "tok_slot", torch.int32),
         _ptr(tok_pos, "tok_pos", torch.int32), _ptr(block_table, "block_table", torch.int32),
-        block_table.shape[1], n, n_heads, n_kv_heads, head_dim, 1 if write_kv else 0, _code(norm_dtype),
+        block_table.shape[1], n, n_heads, n_kv_heads, head_dim, 1 if write_kv else 0,
+        1 if pairing == "interleaved" else 0, _code(norm_dtype),
         _code(q_out.dtype), _code(cache_dtype), _stream()), "qk_rope_kv_write")
 
 
@@ -257,8 +319,9 @@ def check_error_flag(device) -> None:
     value = int(flag.item())
     if value != 0:
         flag.zero_()
-        for state in _chain_state.values():  # a chain that gave up leaves its barrier half counted
-            state.zero_()
+        key = flag.device.index if flag.device.index is not None else torch.cuda.current_device()
+        if key in _counters:  # a block that gave up never brought its tile's counter back to zero
+            _counters[key].zero_()
         raise KernelError(f"a kernel reported error {value}: a bounded wait on a copy or a tensor-core operation ran "
                           f"out; results of the last steps are not valid")
 
@@ -278,120 +341,7 @@ def device_state(device):
     if key not in _counters:
         _counters[key] = torch.zeros(_COUNTER_SLOTS, dtype=torch.int32, device=device)
         _sm_counts[key] = torch.cuda.get_device_properties(device).multi_processor_count
-        _chain_state[key] = torch.zeros(2, dtype=torch.int32, device=device)  # the chain kernel's barrier
     return error_flag(device), _counters[key], _sm_counts[key]
-
-
-# ---------------------------------------------------------------------------------------------------
-# The decode chain: norms and few-row products that parts ask for are queued and run by one launch of
-# the persistent kernel of decode_chain.cu instead of one kernel each.
-
-CHAIN_MAX_ROWS = 16
-CHAIN_MAX_PHASES = 12
-_chain_state: dict = {}
-_chain = None
-
-
-class _ChainPhase(ctypes.Structure):
-    _fields_ = [("x", _P), ("w", _P), ("out", _P), ("rows", _P), ("up_offset", ctypes.c_longlong),
-                ("kind", _I), ("mode", _I), ("m", _I), ("n", _I), ("k", _I), ("ldx", _I), ("ldo", _I),
-                ("out_dtype", _I), ("w_dtype", _I), ("unit_rows", _I), ("first_unit", _I), ("splits", _I),
-                ("chunk", _I), ("eps", _F), ("reserved", _I)]
-
-
-def chain_enabled() -> bool:
-    """XRT_DECODE_CHAIN=1 turns the chain on for model steps.  It is off by default: measured on a
-    B200 at the 8B shape a decode step of 8 sequences takes 5.69 ms with it and 5.28 ms with one
-    kernel per phase (1 sequence: 4.74 against 3.92 ms): a meeting of all blocks between two phases costs
-    about what a kernel boundary costs, and the ring of 135 KB a block holds only 3 microseconds of
-    the weight stream."""
-    import os
-    return os.environ.get("XRT_DECODE_CHAIN", "0") == "1"
-
-
-class _Chain:
-    """Phases waiting for one launch.  ``entries`` holds (phase, tensors kept alive, the call that
-    runs the phase as a kernel of its own)."""
-
-    def __init__(self, device):
-        self.device = torch.device(device)
-        self.entries = []
-
-    @staticmethod
-    def _aligned(*tensors) -> bool:
-        return all(t is None or (t.is_cuda and t.data_ptr() % 16 == 0) for t in tensors)
-
-    def takes_norm(self, out, x, weight, rows) -> bool:
-        width = out.shape[1]
-        return (0 < out.shape[0] <= CHAIN_MAX_ROWS and width % 4 == 0 and x.dtype == torch.float32
-                and out.is_contiguous() and x.is_contiguous() and weight.is_contiguous()
-                and self._aligned(out, x, weight) and (rows is None or rows.dtype == torch.int32))
-
-    def takes_product(self, out, x, w) -> bool:
-        return (0 < x.shape[0] <= CHAIN_MAX_ROWS and w.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
-                and w.is_contiguous() and self._aligned(x, w))
-
-    def _add(self, phase, keep, alone) -> None:
-        self.entries.append((phase, keep, alone))
-        if len(self.entries) == CHAIN_MAX_PHASES:
-            chain_flush()
-
-    def add_norm(self, out, x, weight, eps, rows) -> None:
-        ph = _ChainPhase(x=x.data_ptr(), w=weight.data_ptr(), out=out.data_ptr(),
-                         rows=0 if rows is None else rows.data_ptr(), up_offset=0, kind=0, mode=0, m=out.shape[0],
-                         n=0, k=out.shape[1], ldx=x.stride(0), ldo=out.stride(0), out_dtype=_code(out.dtype),
-                         w_dtype=_code(weight.dtype), eps=float(eps))
-        self._add(ph, (out, x, weight, rows), lambda: rmsnorm(out, x, weight, eps, rows))
-
-    def add_product(self, out, x, w, code: int, up_rows: int) -> None:
-        ph = _ChainPhase(x=x.data_ptr(), w=w.data_ptr(), out=out.data_ptr(), rows=0, up_offset=up_rows * w.shape[1],
-                         kind=1, mode=code, m=x.shape[0], n=out.shape[1], k=x.shape[1], ldx=x.stride(0),
-                         ldo=out.stride(0), out_dtype=_code(out.dtype), w_dtype=_code(w.dtype), eps=0.0)
-        mode = ("store", "accumulate", "swiglu")[code]
-        self._add(ph, (out, x, w), lambda: gemm_stream(out, x, w, mode, up_rows))
-
-
-def chain_begin(device) -> None:
-    """From here to ``chain_end`` norms and products of at most CHAIN_MAX_ROWS rows are queued; any
-    other kernel of this library launches what is queued first.  Only for code all of whose device
-    work goes through this module (a part says so with ``chain_safe = True``)."""
-    global _chain
-    if _chain is not None:
-        raise KernelError("a decode chain is open already")
-    device_state(device)
-    _chain = _Chain(device)
-
-
-def chain_flush() -> None:
-    global _chain
-    chain = _chain
-    if chain is None or not chain.entries:
-        return
-    entries, chain.entries = chain.entries, []
-    key = chain.device.index if chain.device.index is not None else torch.cuda.current_device()
-    flag, _, sms = device_state(chain.device)
-    sync = _chain_state[key]
-    phases = (_ChainPhase * len(entries))(*[e[0] for e in entries])
-    status = library().xrt_decode_chain(ctypes.addressof(phases), len(entries), sync.data_ptr(), sms, flag.data_ptr(),
-                                        _stream())
-    if status == -2:  # sizes the persistent kernel does not take: each phase as a kernel of its own
-        _chain = None
-        try:
-            for _, _, alone in entries:
-                alone()
-        finally:
-            _chain = chain
-        return
-    _check(status, "decode_chain")
-
-
-def chain_end(discard: bool = False) -> None:
-    global _chain
-    try:
-        if not discard:
-            chain_flush()
-    finally:
-        _chain = None
 
 
 _decode_plans: dict = {}
@@ -469,9 +419,6 @@ def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
     if x.stride(1) != 1 or out.stride(1) != 1 or not x.is_cuda or not out.is_cuda:
         raise KernelError("gemm_stream: rows must be contiguous and on a CUDA device")
     code = {"store": 0, "accumulate": 1, "swiglu": 2}[mode]
-    if _chain is not None and _chain.takes_product(out, x, w):
-        _chain.add_product(out, x, w, code, up_rows)
-        return
     _check(_kernels().xrt_gemm_stream(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
                                      _code(out.dtype), code, up_rows, _stream()), "gemm_stream")
 
@@ -501,6 +448,8 @@ def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_h
             _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
             float(scale), int(window), int(chunk), int(n_splits), flag.data_ptr(), _stream(), ctypes.byref(merged)),
             "attention_decode")
+        if n_splits > 1 and not merged.value and n_splits > attention_decode_fused_max_splits(head_dim, n_heads // n_kv_heads):
+            add_launches(1)  # too many splits for the merging block: the combine kernel ran
         return
     _check(_kernels().xrt_attention_decode(
         _ptr(out, "out", torch.bfloat16), _ptr(part_o, "part_o"), _ptr(part_ml, "part_ml"),
@@ -511,6 +460,15 @@ def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_h
         "attention_decode")
     if n_splits > 1 and not merged.value:
         add_launches(1)  # the combine kernel
+
+
+def attention_decode_fused_max_splits(head_dim: int, group: int) -> int:
+    """The most splits that the last block of a (token, kv head) can merge inside the attention
+    kernel (its shared memory holds the splits' maxima and sums); host arithmetic only."""
+    n = library().xrt_attention_decode_fused_max_splits(int(head_dim), int(group))
+    if n < 0:
+        raise KernelError("attention_decode_fused_max_splits: head size or group outside what the kernels take")
+    return n
 
 
 def attention_prefill(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, block_table, max_new: int,

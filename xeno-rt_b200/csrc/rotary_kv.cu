@@ -6,6 +6,8 @@
 //   angle = pos * scale / base^(2i/rope_dim), in 32-bit   crates/xrt-kernels/src/cpu/rope.rs:59-68
 //   h[i]      = x0 * cos - x1 * sin                        crates/xrt-kernels/src/cpu/rope.rs:19-35
 //   h[i+half] = x0 * sin + x1 * cos      (x0 = h[i], x1 = h[i + half]; split-half pairing)
+// The reference pairs (i, i + half) only.  `interleaved` pairs (2i, 2i + 1) instead, for position
+// encodings that rotate neighbours; dims from 2 * rope_half on are left as they are either way.
 //   head norm = RMSNorm over each head slice, one weight   crates/xrt-models/src/llama.rs:1025-1040
 //   order     = projection, head norm, rotation, cache     crates/xrt-models/src/llama.rs:488-503
 #include "common.cuh"
@@ -35,7 +37,7 @@ __global__ void qk_rope_kv_write_kernel(
     const float2* __restrict__ cos_sin, int rope_half,
     const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
     const int* __restrict__ block_table, int max_blocks,
-    int n_heads, int n_kv_heads, int head_dim, int write_kv) {
+    int n_heads, int n_kv_heads, int head_dim, int write_kv, int interleaved) {
   extern __shared__ float staged[];  // [warps][head_dim]
   pdl_trigger();
   pdl_wait();
@@ -92,7 +94,12 @@ __global__ void qk_rope_kv_write_kernel(
 #pragma unroll
     for (int j = 0; j < MAX_PER_LANE; ++j) {
       const int d = lane + 32 * j;
-      if (d < rope_half) {
+      if (interleaved) {
+        if (d < 2 * rope_half) {
+          const float2 a = cs[d >> 1];
+          v[j] = (d & 1) ? mine[d - 1] * a.y + mine[d] * a.x : mine[d] * a.x - mine[d + 1] * a.y;
+        }
+      } else if (d < rope_half) {
         const float2 a = cs[d];
         v[j] = mine[d] * a.x - mine[d + rope_half] * a.y;
       } else if (d < 2 * rope_half) {
@@ -226,13 +233,13 @@ XRT_EXPORT int xrt_qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, con
                                     int k_offset, int v_offset, const void* q_norm_w, const void* k_norm_w,
                                     float eps, const float* cos_sin, int rope_half, const int* tok_slot,
                                     const int* tok_pos, const int* block_table, int max_blocks, int n_tokens,
-                                    int n_heads, int n_kv_heads, int head_dim, int write_kv, int norm_dtype,
-                                    int q_dtype, int cache_dtype, cudaStream_t stream) {
+                                    int n_heads, int n_kv_heads, int head_dim, int write_kv, int interleaved,
+                                    int norm_dtype, int q_dtype, int cache_dtype, cudaStream_t stream) {
   if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0) return XRT_ERR_ARGUMENT;
   if (head_dim > 256 || 2 * rope_half > head_dim) return XRT_ERR_UNSUPPORTED;
   if ((q_norm_w == nullptr) != (k_norm_w == nullptr)) return XRT_ERR_ARGUMENT;
   if (n_tokens == 0) return XRT_OK;
-  const bool fast = head_dim == 128 && (rope_half == 0 || rope_half == 64) && row_stride % 4 == 0 && k_offset % 4 == 0 &&
+  const bool fast = head_dim == 128 && (rope_half == 0 || (rope_half == 64 && !interleaved)) && row_stride % 4 == 0 && k_offset % 4 == 0 &&
                     v_offset % 4 == 0 &&
                     (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)cos_sin) & 15) == 0;
   if (fast) {
@@ -258,7 +265,7 @@ XRT_EXPORT int xrt_qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, con
         xrt::launch_kernel(xrt::qk_rope_kv_write_kernel<TN, TQ, TC, 8>, grid, dim3(warps * 32), smem, stream,
             (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, qkv, row_stride, k_offset, v_offset, (const TN*)q_norm_w,
             (const TN*)k_norm_w, eps, (const float2*)cos_sin, rope_half, tok_slot, tok_pos, block_table,
-            max_blocks, n_heads, n_kv_heads, head_dim, write_kv);
+            max_blocks, n_heads, n_kv_heads, head_dim, write_kv, interleaved);
       });
     });
   });

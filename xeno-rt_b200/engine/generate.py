@@ -17,6 +17,7 @@ from __future__ import annotations
 import time
 from dataclasses import dataclass, field
 
+from ..cache.spec import BLOCK_TOKENS
 from ..core import RuntimeFault
 from ..sampling import SamplerConfig
 
@@ -121,13 +122,13 @@ def validate_request(request: GenerateRequest, vocab_size: int, context_length: 
     request.sampler_config().validate()
 
 
-def tokens_held(request: GenerateRequest, context_length: int, unit: int = 64) -> int:
+def tokens_held(request: GenerateRequest, context_length: int, unit: int = BLOCK_TOKENS) -> int:
     """Cache tokens a request may come to hold, rounded up to the cache's unit."""
     most = min(len(request.prompt_ids) + max(request.max_tokens, 0), context_length)
     return (most + unit - 1) // unit * unit
 
 
-def plan_batches(requests, context_length: int, capacity_tokens: int, max_batch: int, unit: int = 64):
+def plan_batches(requests, context_length: int, capacity_tokens: int, max_batch: int, unit: int = BLOCK_TOKENS):
     """Cuts the requests, in order, into batches that fit the cache: at most ``max_batch``
     sequences and at most ``capacity_tokens`` held tokens a batch.  Returns lists of indices."""
     batches, current, used = [], [], 0

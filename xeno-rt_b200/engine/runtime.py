@@ -123,7 +123,7 @@ class Session:
         self.last_stats = None
 
     def _backend_for(self, capacity: int) -> DeviceBackend:
-        if self.backend is None or self.backend.engine.cache.n_blocks * 64 < capacity:
+        if self.backend is None or self.backend.engine.cache.capacity_tokens < capacity:
             self.backend = None  # let the old cache go before the new one is made
             self.backend = DeviceBackend(Engine(self.runtime.model, capacity, max_slots=self.runtime.max_batch))
         return self.backend
@@ -140,7 +140,7 @@ class Session:
             capacity = min(capacity, max(self.runtime.cache_tokens, held[0]))
         backend = self._backend_for(capacity)
         results, stats = generate(backend, requests, model.vocab_size, context, model.spec.stop_ids,
-                                  capacity_tokens=backend.engine.cache.n_blocks * 64,
+                                  capacity_tokens=backend.engine.cache.capacity_tokens,
                                   max_batch=self.runtime.max_batch, on_token=on_token)
         self.last_stats = stats
         return results, stats

@@ -13,7 +13,7 @@ power of two) and one graph launch runs what would otherwise be hundreds of kern
 """
 from __future__ import annotations
 
-import os
+import collections
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -26,6 +26,7 @@ from ..parts import StepContext
 from ..parts.context import context_bucket
 
 GRAPH_MAX_BATCH = 256
+GRAPH_KEEP = 16  # captured decode steps kept at a time; the one used longest ago goes first
 
 
 @dataclass
@@ -138,8 +139,8 @@ def build_context(entries, cache: Cache, vocab_size: int, dtype, device, pad_to:
     Returns (context, wanted rows as a device tensor or None).  ``pad_to`` appends padding rows
     (slot -1) up to that many tokens; padding changes no result."""
     _check_entries(entries, vocab_size)
-    starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
     new_lens = [len(e.tokens) for e in entries]
+    starts = cache.reserve_all([e.slot for e in entries], new_lens)
     padded = max(sum(new_lens), pad_to or 0)
     n = len(entries)
     size = layout(padded, n)["size"]
@@ -176,7 +177,9 @@ class _DecodeGraph:
         torch.cuda.synchronize()
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
-        with torch.cuda.graph(self.graph):
+        # all graphs of an engine capture into one memory pool: they never run at the same time, so
+        # the room of one step's intermediates serves every graph
+        with torch.cuda.graph(self.graph, pool=engine.graph_pool):
             ctx = make()
             ctx.captured = True
             self.logits = model.forward(ctx, cache, self.rows)
@@ -187,15 +190,22 @@ class Engine:
     """A model with its cache.  ``step`` is the one way tokens go through the model; generation
     and trace replay both call it."""
 
-    def __init__(self, model, max_tokens: int, max_slots: int | None = None, use_graphs: bool | None = None):
+    def __init__(self, model, max_tokens: int, max_slots: int | None = None, use_graphs: bool | None = None,
+                 tuning: "ops.Tuning | None" = None):
+        """``tuning`` (an ``ops.Tuning``) becomes the process's kernel tuning; ``use_graphs`` None
+        follows its ``graphs``."""
         self.model = model
         self.cache = model.new_cache(max_tokens, max_slots)
         self.last_context = None
         self.staging = _Staging(model.device)
+        if tuning is not None:
+            ops.set_tuning(tuning)
         if use_graphs is None:
-            use_graphs = os.environ.get("XRT_NO_GRAPHS", "0") in ("", "0")
+            use_graphs = ops.tuning().graphs
         self.use_graphs = use_graphs and model.device.type == "cuda" and model.graph_safe
-        self._graphs: dict[tuple, _DecodeGraph] = {}  # (batch bucket, context bucket) -> graph
+        self._graphs: "collections.OrderedDict[tuple, _DecodeGraph]" = collections.OrderedDict()
+        #             (batch bucket, context bucket) -> graph, least recently used first
+        self.graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
 
     def open_slot(self) -> int:
         return self.cache.open_slot()
@@ -243,12 +253,15 @@ class Engine:
         _check_entries(entries, model.vocab_size)
         n = len(entries)
         bucket = batch_bucket(n)
-        starts = [self.cache.reserve(e.slot, 1) for e in entries]
+        starts = self.cache.reserve_all([e.slot for e in entries], [1] * n)
         key = (bucket, context_bucket(max(starts) + 1))
         g = self._graphs.get(key)
         if g is None:
+            while len(self._graphs) >= GRAPH_KEEP:  # a batch that shrinks while its contexts grow meets many keys
+                self._graphs.popitem(last=False)
             self.cache.flush_tables()
             g = self._graphs[key] = _DecodeGraph(self, *key)
+        self._graphs.move_to_end(key)
         turn, host = self.staging.take(g.size)
         wanted = fill_arrays(host.numpy(), entries, starts, bucket, bucket)
         g.static.copy_(host, non_blocking=True)

@@ -13,7 +13,7 @@ from dataclasses import dataclass
 from ..config import ModelConfig, register_architecture
 from ..config.base import KeyReader
 from ..core import Unsupported
-from ..parts import LayerSpec, ModelSpec, PartSpec, SchedulePlace
+from ..parts import ModelSpec, PartSpec, SchedulePlace, prenorm_layer
 
 
 @dataclass(frozen=True)
@@ -68,6 +68,12 @@ class LlamaConfig(ModelConfig):
         for key in ("attention_bias", "mlp_bias"):
             if raw.get(key):
                 raise Unsupported(f"config.json: {key} = true is not supported; the architecture has no biases")
+        if raw.get("hidden_act", "silu") != "silu":
+            raise Unsupported(f"config.json: hidden_act {raw['hidden_act']!r} is not supported; the feed-forward of "
+                              f"this architecture is SiLU-gated (crates/xrt-kernels/src/cpu/silu.rs:1-3)")
+        if raw.get("partial_rotary_factor") not in (None, 1, 1.0):
+            raise Unsupported(f"config.json: partial_rotary_factor {raw['partial_rotary_factor']!r} is not supported; "
+                              f"this architecture rotates all of a head")
         if raw.get("use_sliding_window"):
             raise Unsupported("config.json: use_sliding_window = true is not supported by this architecture")
         return cls(architecture=arch, vocab_size=vocab, max_position_embeddings=max_pos, hidden_size=hidden,
@@ -118,7 +124,7 @@ def build_spec(cfg: LlamaConfig) -> ModelSpec:
         if cfg.qk_norm:
             attn_weights["q_norm"] = p + "self_attn.q_norm.weight"
             attn_weights["k_norm"] = p + "self_attn.k_norm.weight"
-        layers.append(LayerSpec(
+        layers.append(prenorm_layer(
             mixer_norm=PartSpec("rmsnorm", {"width": d, "eps": eps}, {"weight": p + "input_layernorm.weight"}),
             mixer=PartSpec("attention", {"width": d, "n_heads": cfg.num_attention_heads,
                                          "n_kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
@@ -128,8 +134,7 @@ def build_spec(cfg: LlamaConfig) -> ModelSpec:
                               {"weight": p + "post_attention_layernorm.weight"}),
             ffn=PartSpec("swiglu", {"width": d, "inner": cfg.intermediate_size},
                          {"gate": p + "mlp.gate_proj.weight", "up": p + "mlp.up_proj.weight",
-                          "down": p + "mlp.down_proj.weight"}),
-            arrangement="prenorm_residual"))
+                          "down": p + "mlp.down_proj.weight"})))
     head_name = "model.embed_tokens.weight" if cfg.tie_word_embeddings else "lm_head.weight"
     return ModelSpec(
         vocab_size=cfg.vocab_size, hidden_size=d, max_positions=cfg.max_position_embeddings,

@@ -26,7 +26,11 @@ class GroupedQueryAttention:
     ``o`` [width, n_heads*head_dim], and with qk_norm ``q_norm``, ``k_norm`` [head_dim]."""
 
     graph_safe = True
-    chain_safe = True
+
+    @classmethod
+    def fused_weights(cls, params):
+        """q, k and v are one matrix [q rows, k rows, v rows] for one product."""
+        return {"qkv": ("q", "k", "v")}
 
     @classmethod
     def weight_shapes(cls, params):
@@ -52,13 +56,18 @@ class GroupedQueryAttention:
         self.q_width = self.n_heads * self.head_dim
         self.kv_width = self.n_kv_heads * self.head_dim
         # one fused weight for the three products; the reference fuses only their dispatch (447-486)
-        self.w_qkv = torch.cat([weights["q"], weights["k"], weights["v"]], dim=0).contiguous()
+        self.w_qkv = weights.get("qkv")
+        if self.w_qkv is None:  # tensors that came one by one
+            self.w_qkv = torch.cat([weights["q"], weights["k"], weights["v"]], dim=0).contiguous()
         self.w_q = self.w_qkv[: self.q_width]
         self.w_o = weights["o"]
         self.q_norm = weights.get("q_norm") if params.get("qk_norm") else None
         self.k_norm = weights.get("k_norm") if params.get("qk_norm") else None
         position = params.get("position") or {"kind": "none", "params": {}}
         self.position = part_class("position", position["kind"])(position.get("params", {}), {}, dtype, device)
+        rope_dim = getattr(self.position, "rope_dim", 0)
+        if rope_dim > self.head_dim:
+            raise ConfigError(f"rope_dim {rope_dim} exceeds the head size {self.head_dim}")
         self.scale = 1.0 / math.sqrt(self.head_dim)
         self.dtype = dtype
         self.act_dtype = torch_dtype(dtype)
@@ -72,7 +81,8 @@ class GroupedQueryAttention:
         q = torch.empty((n, self.q_width), dtype=self.act_dtype, device=h.device)
         ops.qk_rope_kv_write(q, store.k, store.v, qkv, self.q_width, self.q_width + self.kv_width, self.q_norm,
                              self.k_norm, self.eps, self.position.tables(ctx), ctx.tok_slot, ctx.tok_pos,
-                             store.block_table, self.n_heads, self.n_kv_heads, self.head_dim, write_kv=owns_cache)
+                             store.block_table, self.n_heads, self.n_kv_heads, self.head_dim, write_kv=owns_cache,
+                             pairing=getattr(self.position, "pairing", "split_half"))
         # padding rows belong to no sequence: kernels that walk sequences leave them unwritten
         attended = torch.zeros_like(q) if sum(ctx.new_lens) < ctx.n_tokens else torch.empty_like(q)
         self.attend(attended, q, ctx, store)

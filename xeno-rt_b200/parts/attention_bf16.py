@@ -2,15 +2,12 @@
 and the caller uses the kernel that takes any."""
 from __future__ import annotations
 
-import os
-
+from ..cache.spec import BLOCK_TOKENS
 from ..csrc import ops
 from .context import context_bucket
 
-SM_COUNT = 148
 DECODE_BLOCKS_PER_SM = 3   # 70 KB of shared memory a block at head size 128
 TCGEN05_MIN_NEW = 32       # prompts at least this long use the tcgen05 attention (tiles of 128 query rows)
-PREFILL_KERNEL = os.environ.get("XRT_PREFILL_ATTN", "")  # "mma" forces the mma.sync kernel, for comparison
 FUSED_COMBINE_MAX = 32     # (tokens x kv heads) up to which the splits are merged inside the attention kernel (measured again with 6 splits at 8 sequences: the second kernel is still faster there)
 SPLIT_OVERHEAD_TILES = 2   # what a block costs beside its tiles (query load, merge, partials), in tiles of 64 keys
 CLUSTER_MAX_PAIRS, CLUSTER_MAX_SPLITS = 32, 16  # up to so many (token, kv head) pairs the kernel runs a pair's splits
@@ -21,15 +18,16 @@ SPLIT_MERGE_TILES = 0.6    # what every further split costs the merge of a (toke
 #                            at 1, 2 and 4 sequences: 16, 8..16 and 8 splits are the fastest there, not 32, 22 and 13)
 
 
-def decode_split(n_seqs: int, n_kv_heads: int, max_context: int):
+def decode_split(n_seqs: int, n_kv_heads: int, max_context: int, sms: int):
     """(keys a split, number of splits) for decode attention.  Blocks run in rounds of what the GPU
     holds at once; the time is about rounds x (tiles a split + a fixed cost) + a cost of merging that
     grows with the splits, so the split count is chosen to fill the last round (512 pairs of sequence
     and kv head in 2 splits are 2.3 rounds and run like 3; in 4 splits they are 4.6 rounds of half the
-    length).  At least two tiles a split where the context allows."""
-    blocks = max(1, (max_context + 63) // 64)
+    length).  At least two tiles a split where the context allows.  ``sms``: the device's
+    multiprocessors."""
+    blocks = max(1, (max_context + BLOCK_TOKENS - 1) // BLOCK_TOKENS)
     pairs = max(1, n_seqs * n_kv_heads)
-    slots = SM_COUNT * DECODE_BLOCKS_PER_SM
+    slots = sms * DECODE_BLOCKS_PER_SM
     costs = {}
     for splits in range(1, max(1, min((blocks + 1) // 2, 64)) + 1):
         tiles = -(-blocks // splits)
@@ -37,22 +35,23 @@ def decode_split(n_seqs: int, n_kv_heads: int, max_context: int):
         clustered = pairs <= CLUSTER_MAX_PAIRS and real <= CLUSTER_MAX_SPLITS
         # whole clusters have to find room: about two blocks a multiprocessor instead of three (measured at 4
         # sequences: 8 splits, 256 blocks, beat 13 and 16)
-        rounds = -(-pairs * real // (SM_COUNT * 2 if clustered else slots))
+        rounds = -(-pairs * real // (sms * 2 if clustered else slots))
         merge = CLUSTER_MERGE_TILES if clustered else SPLIT_MERGE_TILES
         costs.setdefault(real, rounds * (tiles + SPLIT_OVERHEAD_TILES) + merge * real)
     least = min(costs.values())
     # among the counts within 4 % of the least cost: one that divides the blocks evenly if there is one, then the smallest
     close = [n for n, c in costs.items() if c <= 1.04 * least]
     best = min(close, key=lambda n: (blocks % n != 0, n))
-    chunk = 64 * (-(-blocks // best))
-    return chunk, -(-blocks * 64 // chunk)
+    chunk = BLOCK_TOKENS * (-(-blocks // best))
+    return chunk, -(-blocks * BLOCK_TOKENS // chunk)
 
 
 def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window) -> bool:
     if n_heads // n_kv_heads > 16:
         return False
     if ctx.all_single and ctx.n_tokens <= 65535:
-        chunk, n_splits = decode_split(ctx.n_tokens, n_kv_heads, context_bucket(ctx.max_context))
+        sms = ops.device_state(q.device)[2]
+        chunk, n_splits = decode_split(ctx.n_tokens, n_kv_heads, context_bucket(ctx.max_context), sms)
         # few sequences: the last block of a (token, kv head) merges its splits (one launch less);
         # many: a second kernel merges them with more threads (measured faster from 8 sequences on)
         fused = ctx.n_tokens * n_kv_heads <= FUSED_COMBINE_MAX
@@ -60,7 +59,8 @@ def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window) -> boo
                              n_kv_heads, head_dim, scale, window, chunk, n_splits, fused=fused)
         return True
     if ctx.n_seqs <= 65535 and n_heads <= 65535:
-        if head_dim == 128 and window == 0 and ctx.max_new >= TCGEN05_MIN_NEW and PREFILL_KERNEL != "mma":
+        if (head_dim == 128 and window == 0 and ctx.max_new >= TCGEN05_MIN_NEW
+                and ops.tuning().prefill_attention != "mma"):
             ops.attention_prefill_tcgen05(out, q, store.k, store.v, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
                                           store.block_table, ctx.max_new, n_heads, n_kv_heads, head_dim, scale)
             return True

@@ -13,7 +13,6 @@ class TokenEmbedding:
     params: ``vocab_size``, ``width``.  weights: ``weight`` [vocab, width]."""
 
     graph_safe = True
-    chain_safe = True
 
     @classmethod
     def weight_shapes(cls, params):
@@ -36,7 +35,6 @@ class OutputHead:
     parts the same tensor name.  params: ``vocab_size``, ``width``.  weights: ``weight``."""
 
     graph_safe = True
-    chain_safe = True
 
     @classmethod
     def weight_shapes(cls, params):

@@ -15,7 +15,11 @@ class SwiGLUFeedForward:
     weights: ``gate``, ``up`` [inner, width], ``down`` [width, inner]."""
 
     graph_safe = True
-    chain_safe = True
+
+    @classmethod
+    def fused_weights(cls, params):
+        """gate and up are one matrix [gate rows, up rows] for one product."""
+        return {"gate_up": ("gate", "up")}
 
     @classmethod
     def weight_shapes(cls, params):
@@ -26,7 +30,9 @@ class SwiGLUFeedForward:
         self.width = int(params["width"])
         self.inner = int(params["inner"])
         # one fused weight [2 * inner, width]: gate rows, then up rows
-        self.w_gate_up = torch.cat([weights["gate"], weights["up"]], dim=0).contiguous()
+        self.w_gate_up = weights.get("gate_up")
+        if self.w_gate_up is None:  # tensors that came one by one
+            self.w_gate_up = torch.cat([weights["gate"], weights["up"]], dim=0).contiguous()
         self.w_down = weights["down"]
         self.act_dtype = torch_dtype(dtype)
 

@@ -5,15 +5,12 @@ tensor-core kernels takes the shape, and the caller uses the CUDA-core kernel th
 operands and split K (the batch is the MMA's N, so its time stays the time to read the weight); its
 splits of a tile meet through a thread-block cluster's shared memory.  Up to 16 rows that kernel or
 the cp.async weight-streaming kernel, whichever suits the product (``tcgen05_for_few_rows``).  More
-than 128 rows (prompts): the tiled tcgen05 kernel.  ``XRT_DECODE_GEMM=stream`` or ``tcgen05`` forces one
-of the two decode kernels wherever it applies, for comparison."""
+than 128 rows (prompts): the tiled tcgen05 kernel.  ``ops.Tuning.decode_gemm`` = "stream" or "tcgen05"
+forces one of the two decode kernels wherever it applies, for comparison."""
 from __future__ import annotations
-
-import os
 
 from ..csrc import ops
 
-FORCE = os.environ.get("XRT_DECODE_GEMM", "")
 STREAM_ROWS = 16  # up to here the cp.async kernel is a candidate
 
 
@@ -42,9 +39,10 @@ def tcgen05_for_few_rows(sms: int, rows: int, n: int, k: int, mode: str) -> bool
 
 def _product(out, x, weight, mode: str, up_rows: int = 0) -> None:
     rows = x.shape[0]
-    if FORCE == "stream":
+    force = ops.tuning().decode_gemm
+    if force == "stream":
         stream_rows = ops.STREAM_MAX_ROWS
-    elif FORCE == "tcgen05":
+    elif force == "tcgen05":
         stream_rows = 0
     elif rows > STREAM_ROWS:
         stream_rows = 0

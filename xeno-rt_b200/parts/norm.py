@@ -13,7 +13,6 @@ class RMSNorm:
     """params: ``width``, ``eps``.  weights: ``weight`` [width]."""
 
     graph_safe = True
-    chain_safe = True
 
     @classmethod
     def weight_shapes(cls, params):

@@ -8,9 +8,10 @@ Roles and the interface each class must have (all take ``(params, weights, dtype
 
 norm            ``forward(x, rows=None) -> normed``: x is the float32 residual stream [T, D];
                 the result has the compute dtype; ``rows`` (int32 device tensor) gathers rows.
-mixer           ``cache_need() -> KVNeed | StateNeed | None`` and
+mixer           ``cache_need() -> KVNeed | StateNeed | list of them | None`` and
                 ``forward(h, residual, ctx, store, owns_cache) -> None``: adds its result into the
-                float32 ``residual`` [T, D] in place; ``store`` is the cache storage of its place.
+                float32 ``residual`` [T, D] in place; ``store`` is the cache storage it asked for
+                (a list of storages if it asked with a list).
 feed_forward    ``forward(h, residual, ctx) -> None``: adds its result into ``residual``.
 position        ``tables(ctx) -> tensor | None``: per-step rotation table [T, half, 2] of
                 (cos, sin), cached in ``ctx.shared``; None means no rotation.
@@ -20,11 +21,12 @@ A part class may set ``graph_safe = True`` to say that its ``forward`` only laun
 in stream order whose shapes depend on nothing but the number of tokens and the context bucket (no
 reads back to the host, no data-dependent Python branches); decode steps of a model whose parts
 all say so are captured in CUDA graphs, any other model runs every step kernel by kernel.
-``chain_safe = True`` says that all device work of ``forward`` goes through the kernel functions of
-``csrc.ops`` (torch is used to allocate only): steps of few tokens of a model whose parts all say so
-queue their norms and products and run them in one persistent kernel between two attention calls.
 
-arrangement     a function ``(layer_parts, x, ctx, store, owns_cache) -> None`` that runs one layer.
+arrangement     a function ``(layer_parts, x, ctx, stores, owns_cache) -> None`` that runs one layer:
+                ``layer_parts`` holds every part of the layer by the name its LayerSpec gave it,
+                ``stores`` maps a part's name to the cache storage that part asked for.
+A part class may have ``fused_weights(params) -> {role: (roles, ...)}``: tensors that it wants one after
+another (along rows) in one buffer; when the loader could arrange that, ``weights[role]`` is that buffer.
 """
 from __future__ import annotations
 

@@ -1,23 +1,27 @@
-"""Rotary position encoding with split-half pairing.
+"""Rotary position encoding.
 
 The divisor table f_i = base^(2i / rope_dim) is computed once in float32 as the reference does
 (crates/xrt-kernels/src/cpu/rope.rs:10-16); each step computes (cos, sin) of
 pos * scale / f_i in 32-bit for the step's tokens (rope.rs:59-68).  The rotation itself is applied
-by the attention mixer's fused kernel from this table, so any encoding that is a rotation of
-(i, i + half) pairs by position-dependent angles fits this interface by returning another table.
+by the attention mixer's fused kernel from this table, so any encoding that is a rotation of pairs
+of a head's dims by position-dependent angles fits this interface by returning another table.  A
+position part says which dims pair up with ``pairing``: "split_half" (i with i + rope_dim / 2, the
+reference's and the default, rope.rs:19-35) or "interleaved" (2i with 2i + 1); dims from rope_dim on
+stay as they are (rope.rs:19-35 rotates ``rope_dim`` dims of each head only).
 """
 from __future__ import annotations
 
 import numpy as np
 import torch
 
+from ..core import ConfigError
 from ..csrc import ops
 from .registry import register_part
 
 
 class RotaryEncoding:
     """params: ``rope_dim`` (even, at most the head size), ``base``, ``scale`` (multiplies the
-    position).  No weights."""
+    position), ``pairing`` ("split_half" or "interleaved").  No weights."""
 
     @classmethod
     def weight_shapes(cls, params):
@@ -27,6 +31,11 @@ class RotaryEncoding:
         self.rope_dim = int(params["rope_dim"])
         self.base = float(params["base"])
         self.scale = float(params.get("scale", 1.0))
+        self.pairing = str(params.get("pairing", "split_half"))
+        if self.rope_dim <= 0 or self.rope_dim % 2:
+            raise ConfigError(f"rope_dim {self.rope_dim} must be a positive even number")
+        if self.pairing not in ("split_half", "interleaved"):
+            raise ConfigError(f"pairing {self.pairing!r} is not split_half or interleaved")
         self.half = self.rope_dim // 2
         i = np.arange(self.half, dtype=np.float32)
         freq = np.power(np.float32(self.base), (np.float32(2.0) * i) / np.float32(self.rope_dim)).astype(np.float32)
@@ -45,6 +54,8 @@ class RotaryEncoding:
 
 class NoPositionEncoding:
     """Leaves q and k as they are."""
+
+    pairing = "split_half"
 
     @classmethod
     def weight_shapes(cls, params):

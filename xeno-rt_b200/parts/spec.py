@@ -27,12 +27,19 @@ class PartSpec:
 
 @dataclass
 class LayerSpec:
-    """One layer: a mixer and a feed-forward, each behind a norm, put together by ``arrangement``."""
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    ffn_norm: PartSpec
-    ffn: PartSpec
+    """One layer: its parts by name, ``{name: (role, PartSpec)}`` in the order they are built, and
+    the ``arrangement`` that runs them around the residual stream.  The arrangement receives all of
+    the layer's parts, so a layer with more norms, two mixers side by side or no feed-forward is
+    another arrangement over another dict and nothing else."""
+    parts: dict
     arrangement: str = "prenorm_residual"
+
+
+def prenorm_layer(mixer_norm: PartSpec, mixer: PartSpec, ffn_norm: PartSpec, ffn: PartSpec) -> LayerSpec:
+    """The layer of crates/xrt-models/src/llama.rs:433-602: a mixer and a feed-forward, each behind
+    a norm, each added to the residual stream."""
+    return LayerSpec({"mixer_norm": ("norm", mixer_norm), "mixer": ("mixer", mixer),
+                      "ffn_norm": ("norm", ffn_norm), "ffn": ("feed_forward", ffn)}, "prenorm_residual")
 
 
 @dataclass
@@ -61,10 +68,8 @@ class ModelSpec:
         """Every (role, spec) of the model, each weight-bearing part once."""
         yield "embedding", self.embedding
         for layer in self.layers:
-            yield "norm", layer.mixer_norm
-            yield "mixer", layer.mixer
-            yield "norm", layer.ffn_norm
-            yield "feed_forward", layer.ffn
+            for role, part in layer.parts.values():
+                yield role, part
         yield "norm", self.final_norm
         yield "lm_head", self.lm_head
 
@@ -86,6 +91,20 @@ class ModelSpec:
                     raise ConfigError(f"tensor {name} is used with two shapes: {seen[name].shape} and {e.shape}")
                 seen[name] = e
         return list(seen.values())
+
+    def fused_groups(self) -> list[tuple]:
+        """Tuples of tensor names that a part wants one after another in one buffer (its class says
+        so with ``fused_weights``); the loader then reads them straight into that buffer."""
+        from .registry import part_class
+
+        groups = []
+        for role, spec in self.part_specs():
+            fused = getattr(part_class(role, spec.kind), "fused_weights", None)
+            for roles in (fused(spec.params).values() if fused else ()):
+                names = tuple(spec.weights[r] for r in roles)
+                if names not in groups:
+                    groups.append(names)
+        return groups
 
     def validate(self) -> None:
         from ..core import ConfigError

@@ -81,12 +81,13 @@ def random_tensors(expected, seed: int, dtype: DType) -> dict[str, torch.Tensor]
     return out
 
 
-def write_random_model(folder: str, config, seed: int, dtype=DType.F32) -> str:
+def write_random_model(folder: str, config, seed: int, dtype=DType.F32, shards: int = 1) -> str:
     """Writes ``config.json`` and ``model.safetensors`` for ``config`` (a typed configuration or
-    a config.json dict) with weights drawn from ``seed``; returns the folder."""
+    a config.json dict) with weights drawn from ``seed``; returns the folder.  With ``shards`` > 1
+    the tensors go into that many shard files beside an index, as large checkpoints are stored."""
     from ..config import config_from_dict
     from ..core import parse_dtype, safetensors_code
-    from .safetensors_io import write_safetensors
+    from .safetensors_io import write_safetensors, write_sharded_safetensors
 
     dtype = parse_dtype(dtype)
     raw = config if isinstance(config, dict) else config.to_dict()
@@ -98,6 +99,9 @@ def write_random_model(folder: str, config, seed: int, dtype=DType.F32) -> str:
     with open(os.path.join(folder, "config.json"), "w") as fh:
         json.dump(out_config, fh, indent=2)
     tensors = random_tensors(spec.expected_tensors(), seed, dtype)
-    write_safetensors(os.path.join(folder, "model.safetensors"), tensors,
-                      metadata={"format": "pt", "seed": seed, "dtype": safetensors_code(dtype)})
+    metadata = {"format": "pt", "seed": seed, "dtype": safetensors_code(dtype)}
+    if shards > 1:
+        write_sharded_safetensors(folder, tensors, shards, metadata)
+    else:
+        write_safetensors(os.path.join(folder, "model.safetensors"), tensors, metadata)
     return folder

@@ -53,6 +53,49 @@ def read_safetensors_header(path: str) -> tuple[dict, int]:
     return header, data_start
 
 
+class TensorFile:
+    """One safetensors file kept open as a read-only memory map, so that a tensor's bytes are
+    paged in only when they are asked for and no more of the file is ever held than the caller
+    copies out."""
+
+    def __init__(self, path: str):
+        self.path = path
+        self.header, self.data_start = read_safetensors_header(path)
+        self._fh = open(path, "rb")
+        self._map = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_READ)
+
+    def nbytes(self, name: str) -> int:
+        lo, hi = self.header[name]["data_offsets"]
+        return hi - lo
+
+    def bytes_of(self, name: str, begin: int = 0, count: int | None = None) -> np.ndarray:
+        """A uint8 view (no copy) of ``count`` bytes of tensor ``name`` from byte ``begin`` on."""
+        lo, hi = self.header[name]["data_offsets"]
+        count = hi - lo - begin if count is None else count
+        if begin < 0 or count < 0 or begin + count > hi - lo:
+            raise WeightError(f"{self.path}: bytes {begin}..{begin + count} are outside tensor {name}")
+        return np.frombuffer(self._map, dtype=np.uint8, count=count, offset=self.data_start + lo + begin)
+
+    def close(self) -> None:
+        if self._map is not None:
+            try:
+                self._map.close()
+            except BufferError:  # a view handed out is still alive; the map goes with it
+                pass
+            self._map = None
+            self._fh.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
+def stored_dtype(code: str) -> torch.dtype:
+    return _TORCH[code]
+
+
 def read_safetensors(path: str, names=None) -> dict[str, torch.Tensor]:
     """Reads tensors (all, or those in ``names``) as CPU torch tensors of their stored dtype."""
     header, data_start = read_safetensors_header(path)
@@ -94,3 +137,30 @@ def write_safetensors(path: str, tensors: dict[str, torch.Tensor], metadata: dic
         for name in order:
             t = tensors[name].detach().cpu().contiguous()
             fh.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+
+
+def write_sharded_safetensors(folder: str, tensors: dict[str, torch.Tensor], n_shards: int,
+                              metadata: dict | None = None) -> list[str]:
+    """Writes ``tensors`` as ``model-0000i-of-0000n.safetensors`` files with about equal bytes each
+    (in name order) and the index ``model.safetensors.index.json`` whose ``weight_map`` sends each
+    name to its file.  Returns the shard file names."""
+    import json as _json
+    names = sorted(tensors)
+    n_shards = max(1, min(int(n_shards), len(names)))
+    total = sum(tensors[n].numel() * tensors[n].element_size() for n in names)
+    shards: list[dict] = [{} for _ in range(n_shards)]
+    used, k = 0, 0
+    for i, name in enumerate(names):
+        left_names, left_shards = len(names) - i, n_shards - k
+        if shards[k] and k + 1 < n_shards and (used >= total * (k + 1) / n_shards or left_names < left_shards):
+            k += 1
+        shards[k][name] = tensors[name]
+        used += tensors[name].numel() * tensors[name].element_size()
+    files = [f"model-{i + 1:05d}-of-{n_shards:05d}.safetensors" for i in range(n_shards)]
+    weight_map = {}
+    for file, part in zip(files, shards):
+        write_safetensors(os.path.join(folder, file), part, metadata)
+        weight_map.update({name: file for name in part})
+    with open(os.path.join(folder, "model.safetensors.index.json"), "w") as fh:
+        _json.dump({"metadata": {"total_size": total}, "weight_map": weight_map}, fh, indent=1, sort_keys=True)
+    return files
