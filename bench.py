@@ -241,6 +241,20 @@ def run_ours(args) -> int:
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device: bench.py needs a B200"}))
         return 1
+    if args.tuning:
+        import dataclasses
+        from xeno_rt_b200.csrc import ops
+        fields = {f.name: f.type for f in dataclasses.fields(ops.Tuning)}
+        changes = {}
+        for item in args.tuning.split(","):
+            key, _, value = item.partition("=")
+            if key not in fields:
+                print(f"bench.py: --tuning {key!r} is not one of {sorted(fields)}")
+                return 2
+            current = getattr(ops.Tuning(), key)
+            changes[key] = (value.lower() in ("1", "true", "on")) if isinstance(current, bool) else type(current)(
+                int(value, 0) if isinstance(current, int) else value)
+        ops.set_tuning(dataclasses.replace(ops.tuning(), **changes))
     shape_name, shape_cfg = SHAPES[args.shape]
     cfg = dict(shape_cfg)
     full_layers = cfg["num_hidden_layers"]
@@ -314,6 +328,8 @@ def main() -> int:
                         help="the model shape to time (the default is the headline configuration)")
     parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                         help="prompt length of --only prefill (the full line always uses 2,048)")
+    parser.add_argument("--tuning", default="", metavar="KEY=VALUE[,KEY=VALUE...]",
+                        help="kernel variants to force, as fields of xeno_rt_b200.csrc.ops.Tuning (for comparisons)")
     parser.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                         help="a short run of one part, for profiling; prints its own small JSON line")
     args = parser.parse_args()

@@ -271,7 +271,9 @@ __global__ void attention_combine_kernel(__nv_bfloat16* __restrict__ out, const 
                                          const int* __restrict__ tok_pos, int n_tokens, int n_heads, int head_dim,
                                          int window, int chunk, int n_splits) {
   pdl_trigger();
+  if (threadIdx.x == 0) XRT_TL(60);
   pdl_wait();
+  if (threadIdx.x == 0) XRT_TL(61);
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp_global >= n_tokens * n_heads) return;
   const int tok = warp_global / n_heads;
@@ -354,12 +356,16 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const __nv_bfloat16* __restrict__ q, const int* __restrict__ tok_slot,
                             const int* __restrict__ tok_pos, const int* __restrict__ block_table, int max_blocks,
                             int n_heads, int n_kv_heads, int head_dim, float scale_log2, int window, int chunk,
-                            int n_splits, int* __restrict__ counters, int* __restrict__ error_flag, int clustered) {
+                            int n_splits, int* __restrict__ counters, int* __restrict__ error_flag, int clustered,
+                            Prefetch pf) {
   constexpr int D_TILES = HD_MAX / 8;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full[2];
   pdl_trigger();
+  if (threadIdx.x == 0) XRT_TL(50);
+  if (threadIdx.x == DEC_WARPS * 32 - 1)
+    prefetch_l2_part(pf, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z);
   // The step's arrays (slots, positions, block table) were written before the step began: they may be
   // read, and tiles of old keys fetched, while the kernel before this one (which writes q and the
   // newest key and value) is still running.
@@ -417,6 +423,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const bool early = has_keys && begin + XRT_BLOCK_TOKENS <= len - 1;
   if (threadIdx.x == 0 && early) issue_tile(0, 0);
   pdl_wait();
+  if (threadIdx.x == 0) XRT_TL(51);
   const __nv_bfloat16* qt = q + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
   uint32_t qb[D_TILES / 2][2];
 #pragma unroll
@@ -453,6 +460,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     if (!clustered) return;  // in a cluster the block still meets the others (its state below is meaningless)
   }
 
+  if (threadIdx.x == 0) XRT_TL(52);
   // this warp's state into the merge area: row = head; the sums are spread over the lanes of a t
   float* merge_m = reinterpret_cast<float*>(smem);
   float* merge_l = merge_m + DEC_WARPS * 16;
@@ -476,6 +484,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   if (!clustered) {
     decode_finish(smem, out, part_o, part_ml, counters, tok, kv_head, split, n_splits, chunk, first_key, len, group, n_heads,
                   n_kv_heads, head_dim);
+    if (threadIdx.x == 0) XRT_TL(53);
     return;
   }
 
@@ -574,7 +583,7 @@ constexpr int DEC_CLUSTER_MAX_PAIRS = 32;
 
 inline bool decode_cluster_wanted(int n_splits, int pairs) {
   const bool off = tuning().decode_attention == 3;
-  return !off && n_splits >= 2 && n_splits <= DEC_MAX_CLUSTER && pairs <= DEC_CLUSTER_MAX_PAIRS;
+  return !off && n_splits >= 2 && n_splits <= DEC_MAX_CLUSTER && pairs <= tuning().decode_cluster_pairs;
 }
 
 template <int HD_MAX>
@@ -640,7 +649,7 @@ int launch_decode_tma(__nv_bfloat16* out, float* part_o, float* part_ml, const _
   config.numAttrs = n_attrs;
   cudaLaunchKernelEx(&config, kernel, map_k, map_v, out, part_o, part_ml, q, tok_slot, tok_pos, block_table, max_blocks,
                      n_heads, n_kv_heads, head_dim, scale * 1.4426950408889634f, window, chunk, n_splits, counters, error_flag,
-                     clustered ? 1 : 0);
+                     clustered ? 1 : 0, take_prefetch());
   return launch_status();
 }
 
@@ -704,6 +713,8 @@ inline int decode_fused_max_splits(int head_dim, int group) {
 }
 
 }  // namespace xrt
+
+XRT_TL_EXPORT(attention_decode)
 
 XRT_EXPORT int xrt_attention_decode_fused_max_splits(int head_dim, int group) {
   if (head_dim < 16 || head_dim > 256 || head_dim % 16 != 0 || group < 1 || group > 16) return XRT_ERR_UNSUPPORTED;

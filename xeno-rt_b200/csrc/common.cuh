@@ -29,8 +29,33 @@ struct Tuning {
   int decode_attention = 0;         // 0 auto, 1 heads as rows, 2 cp.async copies, 3 no clusters
   int gemm_tile_rows = 0;           // 0 auto, 128 or 256: the prefill product's tile
   bool decode_gemm_clusters = true; // the decode product's splits meet through a cluster's shared memory
+  int decode_gemm_ring_kb = 200;    // shared memory of the decode product's ring of weight slabs
+  int decode_cluster_pairs = 128;    // decode attention merges its splits as clusters up to so many (token, kv head) pairs
 };
 const Tuning& tuning();
+
+// A stretch of memory (weights that a later kernel of the step will stream) that a kernel asks the
+// L2 to fetch while it runs.  The products of a decode step that read 30 to 50 MB are bound by the
+// latency of their first loads from HBM, not by bandwidth, and HBM idles across every boundary between
+// two kernels: a kernel that leaves bandwidth unused (a norm, the rotation, attention over a few
+// sequences, a small product) starts the next product's weights on their way, and that product then
+// streams from the L2.  Nothing waits for a prefetch and nothing depends on it having happened.
+struct Prefetch {
+  const char* ptr = nullptr;
+  unsigned long long bytes = 0;  // a multiple of 16; ptr is 16-byte aligned
+};
+// The hint left by xrt_hint_prefetch for the next launch that can carry one; taking it clears it.
+Prefetch take_prefetch();
+constexpr int PREFETCH_EXTRA_BLOCKS = 64;  // blocks that a kernel of a handful of blocks adds to carry a prefetch
+
+// Part `part` of `parts` of a prefetch, issued by ONE thread: pieces of 16 KB, dealt out in turn.
+__device__ __forceinline__ void prefetch_l2_part(Prefetch pf, unsigned part, unsigned parts) {
+  constexpr unsigned long long PIECE = 16384;
+  for (unsigned long long at = (unsigned long long)part * PIECE; at < pf.bytes; at += (unsigned long long)parts * PIECE) {
+    const unsigned size = (unsigned)(pf.bytes - at < PIECE ? pf.bytes - at : PIECE);
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf.ptr + at), "r"(size) : "memory");
+  }
+}
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -106,6 +131,34 @@ inline int launch_status() {
 }
 
 }  // namespace xrt
+
+#ifdef XRT_TIMELINE
+namespace xrt {
+static __device__ unsigned long long tl_buf[1 << 16][2];
+static __device__ unsigned int tl_n;
+__device__ __forceinline__ void tl_stamp(int id) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  unsigned smid;
+  asm("mov.u32 %0, %%smid;" : "=r"(smid));
+  const unsigned i = atomicAdd(&tl_n, 1u);
+  const unsigned lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  if (i < (1u << 16)) { tl_buf[i][0] = t; tl_buf[i][1] = ((unsigned long long)id << 32) | ((unsigned long long)smid << 20) | (lin & 0xfffff); }
+}
+}  // namespace xrt
+#define XRT_TL(id) xrt::tl_stamp(id)
+#define XRT_TL_EXPORT(name)                                                                          \
+  extern "C" __attribute__((visibility("default"))) int xrt_timeline_##name(void* host, int reset) { \
+    unsigned n = 0;                                                                                  \
+    cudaMemcpyFromSymbol(&n, xrt::tl_n, 4);                                                          \
+    if (host) cudaMemcpyFromSymbol(host, xrt::tl_buf, sizeof(xrt::tl_buf));                          \
+    if (reset) { unsigned z = 0; cudaMemcpyToSymbol(xrt::tl_n, &z, 4); }                             \
+    return (int)n;                                                                                   \
+  }
+#else
+#define XRT_TL(id) do {} while (0)
+#define XRT_TL_EXPORT(name)
+#endif
 
 // Dispatch on a dtype code: runs BODY with `T` bound to float or __nv_bfloat16.
 #define XRT_DISPATCH_DTYPE(code, T, ...)            \

@@ -88,13 +88,11 @@ __device__ __forceinline__ void dg_ld16(uint32_t (&r)[16], uint32_t addr) {
                : "r"(addr));
 }
 __device__ __forceinline__ void dg_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ float dg_ld_cluster(uint32_t local_smem, int rank) {  // the same place in another block of the cluster
-  uint32_t remote;
-  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem), "r"(rank));
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-  return v;
-}
+// The two halves of a cluster meeting, thread by thread: a block may store into another block's shared
+// memory only once that block runs, which the first meeting (arrive at the start, wait before the first
+// store) makes sure of without holding anybody up.
+__device__ __forceinline__ void dg_cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void dg_cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 __device__ __forceinline__ void dg_cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -116,7 +114,7 @@ template <int MODE, typename TO>
 __global__ void __launch_bounds__(DG_THREADS, 1)
 gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                            TO* __restrict__ out, float* __restrict__ partial, int* __restrict__ counters,
-                           const DecodeGemmShape shape, int* __restrict__ error_flag) {
+                           const DecodeGemmShape shape, int* __restrict__ error_flag, Prefetch pf) {
   constexpr int GROUPS = MODE == 2 ? 2 : 1;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -131,15 +129,17 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
+  float* recv = reinterpret_cast<float*>(smem + (size_t)stages * stage_bytes + 512);  // the cluster's sums for this block's rows
 
   pdl_trigger();
+  if (shape.clustered) dg_cluster_arrive();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_items = shape.tiles * shape.splits;
   const int k_iters_total = (shape.K + DG_BK - 1) / DG_BK;
   const int acc_cols = GROUPS * shape.nb;  // TMEM columns of one accumulator set
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) { dg_mbar_init(dg_smem(&full[s]), 1); dg_mbar_init(dg_smem(&empty[s]), 1); }
+    for (int s = 0; s < stages; ++s) { dg_mbar_init(dg_smem(&full[s]), 2); dg_mbar_init(dg_smem(&empty[s]), 1); }
     for (int a = 0; a < 2; ++a) { dg_mbar_init(dg_smem(&acc_full[a]), 1); dg_mbar_init(dg_smem(&acc_empty[a]), 128); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -159,34 +159,80 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-      int it = 0;
-      bool ok = true, waited = false;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const int tile = item / shape.splits, split = item % shape.splits;
-        const int kb0 = split * shape.k_per_split;
-        const int kb1 = min(k_iters_total, kb0 + shape.k_per_split);
-        // Blocks that work at the same time start their walk over K at different slabs (a rotation
-        // that depends on the tile only, so the order of the sum is fixed per output element):
-        // otherwise every block asks the L2 for the same few lines of X at the same moment.
-        const int span = kb1 - kb0, rotate = span > 0 ? (tile * 5) % span : 0;
-        for (int i = 0; i < span; ++i, ++it) {
-          const int kb = kb0 + (i + rotate) % span;
-          const int s = it % stages;
-          ok = dg_mbar_wait(dg_smem(&empty[s]), ((it / stages) & 1) ^ 1, abort_flag);
-          if (!ok) break;
-          const uint32_t bar = dg_smem(&full[s]);
-          unsigned char* stage = smem + (size_t)s * stage_bytes;
-          dg_mbar_expect_tx(bar, GROUPS * DG_W_BYTES + x_bytes);
-          // the weights do not depend on the step: they may be on their way while the kernel before
-          // this one finishes; X does, so the first X load waits for it
-          dg_tma_load_2d(dg_smem(stage), &map_w, kb * DG_BK, tile * DG_ROWS, bar);
-          if (MODE == 2) dg_tma_load_2d(dg_smem(stage + DG_W_BYTES), &map_w, kb * DG_BK, shape.up_rows + tile * DG_ROWS, bar);
-          if (!waited) { pdl_wait(); waited = true; }
-          dg_tma_load_2d(dg_smem(stage + GROUPS * DG_W_BYTES), &map_x, kb * DG_BK, 0, bar);
+      XRT_TL(20);
+      // The walk over this block's slabs: items in turn, and inside an item the slabs of its split of K.
+      // Blocks that work at the same time start their walk over K at different slabs (a rotation that
+      // depends on the tile only, so the order of the sum is fixed per output element): otherwise every
+      // block asks the L2 for the same few lines of X at the same moment.
+      struct Walk {
+        int item, i, span, kb0, rotate, tile;
+        __device__ void enter(const DecodeGemmShape& sh, int k_total) {
+          tile = item / sh.splits;
+          kb0 = (item % sh.splits) * sh.k_per_split;
+          span = max(0, min(k_total, kb0 + sh.k_per_split) - kb0);
+          rotate = span > 0 ? (tile * 5) % span : 0;
+          i = 0;
         }
+        __device__ bool settle(const DecodeGemmShape& sh, int k_total, int n_items, int stride) {
+          while (item < n_items) {  // skips items without slabs (a split beyond K)
+            if (i < span) return true;
+            item += stride;
+            if (item < n_items) enter(sh, k_total);
+          }
+          return false;
+        }
+        __device__ int kb() const { return kb0 + (i + rotate) % span; }
+      };
+      Walk walk;
+      walk.item = blockIdx.x;
+      if (walk.item < n_items) walk.enter(shape, k_iters_total);
+      const uint32_t w_bytes = GROUPS * DG_W_BYTES;
+      auto load_w = [&](const Walk& at, int s) {
+        const uint32_t bar = dg_smem(&full[s]);
+        unsigned char* stage = smem + (size_t)s * stage_bytes;
+        dg_mbar_expect_tx(bar, w_bytes);
+        dg_tma_load_2d(dg_smem(stage), &map_w, at.kb() * DG_BK, at.tile * DG_ROWS, bar);
+        if (MODE == 2) dg_tma_load_2d(dg_smem(stage + DG_W_BYTES), &map_w, at.kb() * DG_BK, shape.up_rows + at.tile * DG_ROWS, bar);
+      };
+      auto load_x = [&](const Walk& at, int s) {
+        const uint32_t bar = dg_smem(&full[s]);
+        dg_mbar_expect_tx(bar, x_bytes);
+        dg_tma_load_2d(dg_smem(smem + (size_t)s * stage_bytes + GROUPS * DG_W_BYTES), &map_x, at.kb() * DG_BK, 0, bar);
+      };
+      // The weights do not depend on the step: the whole ring is filled with them while the kernel
+      // before this one finishes.  X does: its loads follow once that kernel has completed.  A stage's
+      // barrier takes two arrivals (weights asked for, X asked for) and the bytes of both.
+      Walk ahead = walk;
+      int filled = 0;
+      while (filled < stages && ahead.settle(shape, k_iters_total, n_items, gridDim.x)) {
+        load_w(ahead, filled);
+        ++ahead.i;
+        ++filled;
       }
+      pdl_wait();
+      XRT_TL(21);
+      int it = 0;
+      bool ok = true;
+      while (it < filled && walk.settle(shape, k_iters_total, n_items, gridDim.x)) {
+        load_x(walk, it);
+        ++walk.i;
+        ++it;
+      }
+      while (ok && walk.settle(shape, k_iters_total, n_items, gridDim.x)) {
+        const int s = it % stages;
+        ok = dg_mbar_wait(dg_smem(&empty[s]), ((it / stages) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        load_w(walk, s);
+        load_x(walk, s);
+        ++walk.i;
+        ++it;
+      }
+      XRT_TL(22);
       if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 4); }
+    } else if (lane == 1) {
+      prefetch_l2_part(pf, blockIdx.x, gridDim.x);  // weights of a later product, while this one streams its own
     }
+    if (shape.clustered) dg_cluster_wait();
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
@@ -222,8 +268,10 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       }
       if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 4); }
     }
+    if (shape.clustered) dg_cluster_wait();
   } else {
     // ---------------------------------------------------------------- epilogue
+    if (shape.clustered) dg_cluster_wait();  // every block of the cluster runs: its shared memory may be written
     pdl_wait();  // the output (and the residual it adds into) belongs to the step
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;  // weight row inside the tile = TMEM lane
@@ -271,14 +319,21 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
           }
         }
       } else if (shape.clustered) {
-        // this split's sums into this block's shared memory, [accumulator column][weight row]: the ring is
-        // idle (a block has one item, and its products have completed)
-        float* xch = reinterpret_cast<float*>(smem);
+        // This split's sums go to the blocks of the cluster that finish them: block d of the cluster owns
+        // rows d * per .. of the tile, and keeps one slot a split, [slot][accumulator column][row], in a
+        // part of its shared memory that its own ring never uses.  Remote stores, no reply awaited.
+        const int per = (DG_ROWS + shape.splits - 1) / shape.splits;
+        const int owner = r / per, local = r - owner * per;
+        uint32_t remote;
+        asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(dg_smem(recv)), "r"(owner));
+        remote += (uint32_t)((split * acc_cols * per + local) * 4);
         for (int c = 0; c < acc_cols; c += 16) {
           uint32_t v[16];
           if (has_k) { dg_ld16(v, tmem_row + c); dg_wait_ld(); }
 #pragma unroll
-          for (int j = 0; j < 16; ++j) xch[(size_t)(c + j) * DG_ROWS + r] = has_k ? __uint_as_float(v[j]) : 0.f;
+          for (int j = 0; j < 16; ++j)
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)((c + j) * per * 4)),
+                         "f"(has_k ? __uint_as_float(v[j]) : 0.f) : "memory");
         }
       } else {
         // partial[(tile * splits + split)][group][weight row][NB]: a thread owns its row's NB floats
@@ -365,8 +420,10 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 
   if (shape.clustered) {
     // Every thread of every block of the cluster comes here, also after a wait that ran out (all waits
-    // are bounded).  Block `rank` finishes rows rank * per .. of the tile: consecutive threads take
-    // consecutive weight rows (consecutive output addresses) of one batch row.
+    // are bounded).  After the meeting every split's sums for this block's rows lie in its own shared
+    // memory; it adds them in split order and finishes its rows: consecutive threads take consecutive
+    // weight rows (consecutive output addresses) of one batch row.  Nothing touches another block's
+    // memory after the meeting, so a block may leave when it is done.
     dg_cluster_sync();
     if (warp >= 2 && !*abort_flag) {
       uint32_t rank;
@@ -376,7 +433,7 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       const int row_lo = (int)rank * per;
       const int rows_here = max(0, min(per, DG_ROWS - row_lo));
       const int total = rows_here * shape.M;
-      const uint32_t xch_local = dg_smem(smem);
+      const int slot_floats = acc_cols * per;
       constexpr int UNROLL = 4;
       for (int base = threadIdx.x - 64; base < total; base += 128 * UNROLL) {
         float old[UNROLL], sums[UNROLL][GROUPS];
@@ -385,8 +442,8 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           const int idx = base + u * 128;
-          const int m = idx / rows_here, row = row_lo + idx - m * rows_here;
-          const int n = tile * DG_ROWS + row;
+          const int m = idx / rows_here, local = idx - m * rows_here;
+          const int n = tile * DG_ROWS + row_lo + local;
           live[u] = idx < total && n < shape.N;
           at[u] = (size_t)m * shape.ldo + n;
           old[u] = (MODE == 1 && live[u]) ? __ldcg(reinterpret_cast<const float*>(out) + at[u]) : 0.f;
@@ -394,8 +451,8 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
           for (int gr = 0; gr < GROUPS; ++gr) {
             float t = 0.f;
             if (live[u]) {
-              const uint32_t where = xch_local + (uint32_t)(((gr * shape.nb + m) * DG_ROWS + row) * 4);
-              for (int sp = 0; sp < shape.splits; ++sp) t += dg_ld_cluster(where, sp);
+              const float* mine = recv + (size_t)(gr * shape.nb + m) * per + local;
+              for (int sp = 0; sp < shape.splits; ++sp) t += mine[(size_t)sp * slot_floats];
             }
             sums[u][gr] = t;
           }
@@ -411,15 +468,19 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         }
       }
     }
-    dg_cluster_sync();  // nobody leaves while another block may still read its shared memory
   }
   dg_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) XRT_TL(23);
   if (warp == 1) {
     dg_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(shape.tmem_cols));
   }
 }
+
+}  // namespace xrt
+XRT_TL_EXPORT(gemm_decode)
+namespace xrt {
 
 typedef CUresult (*DgEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -511,9 +572,10 @@ int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorM
     }
     if (held[shape.splits] >= shape.tiles) shape.clustered = 1;
   }
+  const Prefetch pf = take_prefetch();
   if (!shape.clustered) {
     launch_kernel(kernel, dim3(blocks), dim3(DG_THREADS), (size_t)smem, stream, map_w, map_x, (TO*)out, partial, counters,
-                  shape, error_flag);
+                  shape, error_flag, pf);
     return launch_status();
   }
   cudaLaunchConfig_t config = {};
@@ -533,7 +595,7 @@ int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorM
   ++n_attrs;
   config.attrs = attrs;
   config.numAttrs = n_attrs;
-  cudaLaunchKernelEx(&config, kernel, map_w, map_x, (TO*)out, partial, counters, shape, error_flag);
+  cudaLaunchKernelEx(&config, kernel, map_w, map_x, (TO*)out, partial, counters, shape, error_flag, pf);
   return launch_status();
 }
 
@@ -586,7 +648,11 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05(void* out, const void* x, const void* w, 
   const int groups = mode == 2 ? 2 : 1;
   const int x_bytes = shape.nb * xrt::DG_BK * 2;
   const int stage_bytes = groups * xrt::DG_W_BYTES + ((x_bytes + 1023) & ~1023);
-  const int budget = 200 * 1024;
+  // where K is split, a block also keeps the cluster's sums for its share of a tile's rows:
+  // splits x accumulator columns x ceil(128 / splits) floats
+  const int per = shape.splits > 1 ? (xrt::DG_ROWS + shape.splits - 1) / shape.splits : 0;
+  const int recv_bytes = shape.splits * groups * shape.nb * per * 4;
+  const int budget = xrt::tuning().decode_gemm_ring_kb * 1024 - recv_bytes;
   shape.stages = budget / stage_bytes;
   if (shape.stages > 12) shape.stages = 12;
   if (shape.stages < 2) return XRT_ERR_UNSUPPORTED;
@@ -596,7 +662,7 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05(void* out, const void* x, const void* w, 
   shape.tmem_cols = cols;
   shape.clustered = 0;
   if (shape.splits > 1 && (partial == nullptr || counters == nullptr)) return XRT_ERR_ARGUMENT;
-  const int smem = shape.stages * stage_bytes + 512 + 1024;
+  const int smem = shape.stages * stage_bytes + 512 + recv_bytes + 1024;
   const int items = shape.tiles * shape.splits;
   const int blocks = items < sm_count ? items : sm_count;
   CUtensorMap map_w, map_x;

@@ -42,7 +42,7 @@ __device__ __forceinline__ void gs_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
 template <int M_TILES, int MODE, int GS_STAGES, int ROW_GROUPS, typename TO>
 __global__ void __launch_bounds__(GS_THREADS, (M_TILES >= 4 ? 2 : 1))
 gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                   int M, int N, int K, int ldx, int ldo, long long up_offset) {
+                   int M, int N, int K, int ldx, int ldo, long long up_offset, Prefetch pf) {
   // ROW_GROUPS groups of 8 weight rows a block (SwiGLU: as many gate groups and as many up groups);
   // every X fragment a warp loads is used for all of them, which is what keeps the L1 traffic of
   // many batch rows below the shared-memory traffic of the weights
@@ -55,6 +55,8 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
   extern __shared__ __align__(128) unsigned char smem[];
 
   pdl_trigger();
+  if (threadIdx.x == 0) XRT_TL(30);
+  if (threadIdx.x == GS_THREADS - 1) prefetch_l2_part(pf, blockIdx.x, gridDim.x);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * BLOCK_ROWS;
   const int n_slabs = (K + GS_SLAB - 1) / GS_SLAB;
@@ -87,6 +89,7 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
   // The weights do not depend on the step: the first slabs are on their way while the kernel before
   // this one finishes.  X and the output do: wait for it here.
   pdl_wait();
+  if (threadIdx.x == 0) XRT_TL(31);
   const __nv_bfloat16* xlo[M_TILES];
   const __nv_bfloat16* xhi[M_TILES];
 #pragma unroll
@@ -153,6 +156,7 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
       p[(g + 8) * P_ROW + 2 * t] = acc[gr][mt][2];
       p[(g + 8) * P_ROW + 2 * t + 1] = acc[gr][mt][3];
     }
+  if (threadIdx.x == 0) XRT_TL(32);
   __syncthreads();
   for (int e = threadIdx.x; e < M_TILES * 16 * BLOCK_ROWS; e += blockDim.x) {
     const int nb = e % BLOCK_ROWS, m = e / BLOCK_ROWS;
@@ -173,6 +177,7 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
     else if (MODE == 1) *dst = from_float<TO>(to_float(*dst) + first);
     else *dst = from_float<TO>(first);
   }
+  if (threadIdx.x == 0) XRT_TL(33);
 }
 
 template <int M_TILES, int MODE, int GS_STAGES, int ROW_GROUPS, typename TO>
@@ -191,7 +196,7 @@ int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, 
   }
   const int blocks = (N + ROW_GROUPS * GS_ROWS - 1) / (ROW_GROUPS * GS_ROWS);
   launch_kernel(kernel, dim3(blocks), dim3(GS_THREADS), SMEM, stream, (TO*)out, (const __nv_bfloat16*)x,
-                (const __nv_bfloat16*)w, M, N, K, ldx, ldo, up_offset);
+                (const __nv_bfloat16*)w, M, N, K, ldx, ldo, up_offset, take_prefetch());
   return launch_status();
 }
 
@@ -220,6 +225,8 @@ int dispatch_stream(void* out, const void* x, const void* w, int M, int N, int K
 }
 
 }  // namespace xrt
+
+XRT_TL_EXPORT(gemm_stream)
 
 // x: bfloat16 [M, K] with row stride ldx (a multiple of 8); w: bfloat16 [N, K] contiguous, K a
 // multiple of 8; out: [M, N] with row stride ldo.  mode 0 stores, 1 adds into a float32 out, 2 computes

@@ -68,6 +68,8 @@ def library():
                 fn.restype = _I
             lib.xrt_attention_decode_fused_max_splits.argtypes = [_I, _I]
             lib.xrt_attention_decode_fused_max_splits.restype = _I
+            lib.xrt_hint_prefetch.argtypes = [_P, ctypes.c_ulonglong]
+            lib.xrt_hint_prefetch.restype = _I
             lib.xrt_set_tuning.argtypes = [_I, _I]
             lib.xrt_set_tuning.restype = _I
             lib.xrt_gemm_decode_tcgen05_scratch.argtypes = [_I, _I, _I, _I, _I]
@@ -103,6 +105,9 @@ class Tuning:
     decode_attention: str = "auto"
     prefill_attention: str = "auto"
     gemm_tile_rows: int = 0
+    prefetch: int = 0
+    decode_gemm_ring_kb: int = 200
+    decode_cluster_pairs: int = 128
 
 
 _DECODE_ATTENTION = {"auto": 0, "rows": 1, "cp": 2, "nocluster": 3}
@@ -124,7 +129,8 @@ def set_tuning(new: Tuning) -> None:
         raise KernelError(f"tuning: prefill_attention {new.prefill_attention!r} is not auto or mma")
     lib = library()
     for key, value in ((0, int(new.pdl)), (1, _DECODE_ATTENTION[new.decode_attention]),
-                       (2, int(new.gemm_tile_rows)), (3, int(new.decode_gemm_clusters))):
+                       (2, int(new.gemm_tile_rows)), (3, int(new.decode_gemm_clusters)),
+                       (4, int(new.decode_gemm_ring_kb)), (5, int(new.decode_cluster_pairs))):
         if lib.xrt_set_tuning(key, value) != 0:
             raise KernelError(f"tuning: value {value} of setting {key} was refused")
     _tuning = new
@@ -193,6 +199,27 @@ def _check(status: int, what: str) -> None:
     if status == -2:
         raise KernelError(f"{what}: sizes or dtypes outside what the kernel handles")
     raise KernelError(f"{what}: CUDA launch error {status}")
+
+
+def hint_prefetch(tensor, begin_bytes: int = 0, max_bytes: int | None = None) -> int:
+    """Asks the next kernel of this library that can carry one (the norm, the rotation, decode
+    attention, the few-row products) to start ``tensor``'s bytes from ``begin_bytes`` on, at most
+    ``max_bytes`` of them, on their way into the L2 while it runs.  Returns how many bytes were
+    asked for.  The products of a decode step are bound by the latency of HBM at their start and at
+    every boundary between kernels; weights that wait in the L2 take that away.  A hint that no
+    kernel picks up is dropped by the next hint; nothing depends on a prefetch having happened."""
+    if tensor is None or not tensor.is_cuda or not tensor.is_contiguous():
+        return 0
+    total = tensor.numel() * tensor.element_size()
+    begin = min(total, (begin_bytes + 15) // 16 * 16)
+    size = total - begin if max_bytes is None else min(total - begin, max_bytes)
+    size -= size % 16
+    address = tensor.data_ptr() + begin
+    if size <= 0 or address % 16:
+        return 0
+    if library().xrt_hint_prefetch(address, size) != 0:
+        raise KernelError("hint_prefetch: the address is not 16-byte aligned")
+    return size
 
 
 def embedding(out, table, ids, error_flag) -> None:

@@ -153,15 +153,30 @@ qk_rope_kv_write_128_kernel(
     const float2* __restrict__ cos_sin, int rope_half,
     const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
     const int* __restrict__ block_table, int max_blocks,
-    int n_heads, int n_kv_heads, int write_kv) {
+    int n_tokens, int n_heads, int n_kv_heads, int write_kv, Prefetch pf) {
   constexpr int HD = 128;
   pdl_trigger();
-  pdl_wait();
+  if ((int)blockIdx.x >= n_tokens) {  // a block that only carries the prefetch
+    if (threadIdx.x == 0) prefetch_l2_part(pf, blockIdx.x - n_tokens, gridDim.x - n_tokens);
+    return;
+  }
+  // The step's arrays (slots, positions, block table) were written before the step began, and the norm
+  // weights never change: they are read while the kernel before this one finishes.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int n_slots = n_heads + (write_kv ? 2 * n_kv_heads : 0);
   const int slot = tok_slot[t];
   const int pos = tok_pos[t];
+  int block = -1;
+  if (slot >= 0 && write_kv) block = block_table[(size_t)slot * max_blocks + pos / XRT_BLOCK_TOKENS];
+  float qn[4] = {1.f, 1.f, 1.f, 1.f}, kn[4] = {1.f, 1.f, 1.f, 1.f};
+  if (q_norm_w != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { qn[j] = to_float(q_norm_w[4 * lane + j]); kn[j] = to_float(k_norm_w[4 * lane + j]); }
+  }
+  if (threadIdx.x == 0) XRT_TL(40);
+  pdl_wait();
+  if (threadIdx.x == 0) XRT_TL(41);
   // (cos, sin) of this lane's four pairs: dims 4 * (lane % 16) .. of the first half
   float c[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
   if (rope_half > 0 && slot >= 0) {
@@ -169,8 +184,6 @@ qk_rope_kv_write_128_kernel(
     const float4 a = cs[0], b = cs[1];
     c[0] = a.x; sn[0] = a.y; c[1] = a.z; sn[1] = a.w; c[2] = b.x; sn[2] = b.y; c[3] = b.z; sn[3] = b.w;
   }
-  int block = -1;
-  if (slot >= 0 && write_kv) block = block_table[(size_t)slot * max_blocks + pos / XRT_BLOCK_TOKENS];
   for (int head_slot = warp; head_slot < n_slots; head_slot += 8) {
     int kind, head;
     if (head_slot < n_heads) { kind = 0; head = head_slot; }
@@ -194,7 +207,7 @@ qk_rope_kv_write_128_kernel(
       for (int j = 0; j < 4; ++j) sq = fmaf(v[j], v[j], sq);
       const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)HD + eps);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) v[j] = (v[j] * inv) * to_float(norm_w[4 * lane + j]);
+      for (int j = 0; j < 4; ++j) v[j] = (v[j] * inv) * (kind == 0 ? qn[j] : kn[j]);
     }
     if (kind != 2 && rope_half > 0) {
 #pragma unroll
@@ -211,9 +224,12 @@ qk_rope_kv_write_128_kernel(
       store4_as(pool + (((size_t)block * n_kv_heads + head) * XRT_BLOCK_TOKENS + pos % XRT_BLOCK_TOKENS) * HD + 4 * lane, v);
     }
   }
+  if (threadIdx.x == 0) XRT_TL(43);
 }
 
 }  // namespace xrt
+
+XRT_TL_EXPORT(rope)
 
 XRT_EXPORT int xrt_rope_table(float* cos_sin, const int* pos, const float* freq, float scale, int n_tokens,
                               int half, cudaStream_t stream) {
@@ -243,13 +259,15 @@ XRT_EXPORT int xrt_qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, con
                     v_offset % 4 == 0 &&
                     (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)cos_sin) & 15) == 0;
   if (fast) {
+    const xrt::Prefetch pf = xrt::take_prefetch();
+    const int grid = n_tokens + (pf.bytes ? xrt::PREFETCH_EXTRA_BLOCKS : 0);
     XRT_DISPATCH_DTYPE(norm_dtype, TN, {
       XRT_DISPATCH_DTYPE(q_dtype, TQ, {
         XRT_DISPATCH_DTYPE(cache_dtype, TC, {
-          xrt::launch_kernel(xrt::qk_rope_kv_write_128_kernel<TN, TQ, TC>, dim3(n_tokens), dim3(256), 0, stream,
+          xrt::launch_kernel(xrt::qk_rope_kv_write_128_kernel<TN, TQ, TC>, dim3(grid), dim3(256), 0, stream,
               (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, qkv, row_stride, k_offset, v_offset, (const TN*)q_norm_w,
               (const TN*)k_norm_w, eps, (const float2*)cos_sin, rope_half, tok_slot, tok_pos, block_table,
-              max_blocks, n_heads, n_kv_heads, write_kv);
+              max_blocks, n_tokens, n_heads, n_kv_heads, write_kv, pf);
         });
       });
     });

@@ -10,7 +10,7 @@ DECODE_BLOCKS_PER_SM = 3   # 70 KB of shared memory a block at head size 128
 TCGEN05_MIN_NEW = 32       # prompts at least this long use the tcgen05 attention (tiles of 128 query rows)
 FUSED_COMBINE_MAX = 32     # (tokens x kv heads) up to which the splits are merged inside the attention kernel (measured again with 6 splits at 8 sequences: the second kernel is still faster there)
 SPLIT_OVERHEAD_TILES = 2   # what a block costs beside its tiles (query load, merge, partials), in tiles of 64 keys
-CLUSTER_MAX_PAIRS, CLUSTER_MAX_SPLITS = 32, 16  # up to so many (token, kv head) pairs the kernel runs a pair's splits
+CLUSTER_MAX_PAIRS, CLUSTER_MAX_SPLITS = 128, 16  # up to so many (token, kv head) pairs the kernel runs a pair's splits
 #                            as one thread-block cluster that merges itself through distributed shared memory (csrc/
 #                            attention_decode.cu has the same two numbers); a split then costs the merge far less
 CLUSTER_MERGE_TILES = 0.2
