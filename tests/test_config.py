@@ -164,7 +164,7 @@ def test_decode_attention_splits_cover_the_context_and_fill_the_rounds():
                 assert chunk % 64 == 0 and splits >= 1
                 assert chunk * splits >= context                 # every key is in a split
                 assert chunk * (splits - 1) < blocks * 64        # and no split is empty
-    assert [decode_split(b, 8, 4096, 148)[1] for b in (1, 2, 4, 8, 16, 32, 64)] == [16, 16, 8, 6, 3, 3, 4]
+    assert [decode_split(b, 8, 4096, 148)[1] for b in (1, 2, 4, 8, 16, 32, 64)] == [16, 16, 8, 4, 2, 3, 4]
     assert decode_split(1, 8, 32768, 148)[1] <= CLUSTER_MAX_SPLITS
 
 

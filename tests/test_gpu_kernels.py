@@ -323,6 +323,80 @@ def test_attention_decode_kernel(nh, nkv, hd, chunk, n_splits, fused):
         assert rel(out[row], want) < 1.5e-2, (row, s)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,qk_norm,rotate", [(8, 2, 128, True, True), (4, 4, 64, False, True), (6, 1, 128, False, False),
+                                                      (2, 1, 256, True, True), (32, 8, 128, False, True)])
+@pytest.mark.parametrize("chunk,n_splits,fused", [(704, 1, True), (128, 6, True), (128, 6, False), (64, 11, True)])
+def test_attention_decode_from_the_product_of_q_k_v(nh, nkv, hd, qk_norm, rotate, chunk, n_splits, fused):
+    """The decode attention that does the step before it itself: from the 32-bit q/k/v rows it norms
+    and rotates q and k, writes the newest key and value into the cache (nothing else in the pools
+    changes) and attends over the old keys and the newest one.  Sequences whose newest position is the
+    first of a block, the last of a block, the very first, and a padding row; against the plain
+    functions, and against the two kernels it replaces."""
+    torch.manual_seed(nh + hd + chunk + n_splits)
+    lens = [1, 64, 65, 300, 700]  # lengths AFTER the step: the newest position is len - 1
+    k_pool, v_pool, table = _cache_for(lens, nkv, hd, torch.bfloat16, shuffle_seed=hd + 1)
+    ks = [torch.randn(n, nkv, hd, device=DEV) for n in lens]
+    vs = [torch.randn(n, nkv, hd, device=DEV) for n in lens]
+    for s in range(len(lens)):  # the cache holds all positions but the newest
+        _fill_cache(k_pool, v_pool, table, s + 1, ks[s][:-1], vs[s][:-1])
+    order = [3, 0, -1, 4, 1, 2]
+    T, qw, kw = len(order), nh * hd, nkv * hd
+    qkv = torch.randn(T, qw + 2 * kw + 8, device=DEV)  # a row longer than q, k, v
+    tok_slot = torch.tensor([s + 1 if s >= 0 else -1 for s in order], dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([lens[s] - 1 if s >= 0 else 0 for s in order], dtype=torch.int32, device=DEV)
+    qn = (1 + 0.1 * torch.randn(hd, device=DEV)) if qk_norm else None
+    kn = (1 + 0.1 * torch.randn(hd, device=DEV)) if qk_norm else None
+    cs = None
+    if rotate:
+        freq = torch.from_numpy(pm.rope_frequencies(hd, 10000.0)).to(DEV)
+        cs = torch.empty(T, hd // 2, 2, device=DEV)
+        ops().rope_table(cs, tok_pos, freq, 1.0)
+    from xeno_rt_b200.csrc import ops as o
+    assert o.attention_decode_takes_qkv(nh, nkv, hd, hd // 2 if rotate else 0, "split_half")
+    # the two kernels it replaces, on copies of the pools
+    k2, v2 = k_pool.clone(), v_pool.clone()
+    q2 = torch.empty(T, qw, device=DEV, dtype=torch.bfloat16)
+    ops().qk_rope_kv_write(q2, k2, v2, qkv, qw, qw + kw, qn, kn, 1e-6, cs, tok_slot, tok_pos, table, nh, nkv, hd)
+    two = torch.full((T, qw), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops().attention_decode(two, q2, k2, v2, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd), 0, chunk, n_splits,
+                           fused=fused)
+    out = torch.full((T, qw), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops().attention_decode_qkv(out, qkv, qw, qw + kw, qn, kn, 1e-6, cs, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd,
+                               1 / math.sqrt(hd), 0, chunk, n_splits, fused=fused)
+    o.check_error_flag(DEV)
+    assert int(o.device_state(DEV)[1].abs().sum()) == 0
+    # the cache: the same rows were written as by the kernel it replaces (norm sums differ in their order)
+    assert int((k_pool != 0).any(dim=-1).sum()) == int((k2 != 0).any(dim=-1).sum())
+    assert rel(k_pool, f64(k2)) < 1e-2 and torch.equal(v_pool, v2)
+    live = [r for r, s in enumerate(order) if s >= 0]
+    assert rel(out[live], f64(two[live])) < 2e-2
+    pos = tok_pos.cpu().numpy()
+    q, k = f64(qkv[:, :qw]), f64(qkv[:, qw:qw + kw])
+    if qk_norm:
+        q, k = pm.head_rmsnorm(q, f64(qn), nh, hd, 1e-6), pm.head_rmsnorm(k, f64(kn), nkv, hd, 1e-6)
+    if rotate:
+        q, k = pm.rope(q, pos, nh, hd, hd, 10000.0, 1.0), pm.rope(k, pos, nkv, hd, hd, 10000.0, 1.0)
+    bf = lambda x, width: f64(torch.as_tensor(x).to(torch.bfloat16)).reshape(len(x), width)
+    for row, s in enumerate(order):
+        if s < 0:
+            assert float(out[row].float().abs().sum()) == 0.0
+            continue
+        n = lens[s]
+        keys = np.concatenate([bf(ks[s][:-1], kw), bf(k[row:row + 1], kw)])
+        values = np.concatenate([bf(vs[s][:-1], kw), bf(f64(qkv[row:row + 1, qw + kw:qw + 2 * kw]), kw)])
+        q_full = np.zeros((n, qw))
+        q_full[n - 1] = bf(q[row:row + 1], qw)[0]
+        want = pm.causal_gqa_attention(q_full, keys, values, nh, nkv, hd)[n - 1]
+        assert rel(out[row], want) < 1.5e-2, (row, s)
+    # a layer that reads another layer's cache: nothing is written, the newest key is there already
+    before_k, before_v = k_pool.clone(), v_pool.clone()
+    again = torch.full((T, qw), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops().attention_decode_qkv(again, qkv[:, :qw].contiguous(), qw, qw + kw, qn, kn, 1e-6, cs, k_pool, v_pool, tok_slot,
+                               tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd), 0, chunk, n_splits, write_kv=False, fused=fused)
+    assert torch.equal(k_pool, before_k) and torch.equal(v_pool, before_v)
+    assert rel(again[live], f64(out[live])) < 1e-2
+
+
 def test_attention_decode_finds_a_far_key_and_respects_the_window():
     nh, nkv, hd, S = 8, 2, 128, 1500
     k_pool, v_pool, table = _cache_for([S], nkv, hd, torch.bfloat16, shuffle_seed=2)

@@ -349,6 +349,26 @@ __device__ __forceinline__ bool dec_mbar_wait(uint32_t bar, uint32_t parity) {
   return false;
 }
 
+// What the kernel needs to do the step between the q/k/v product and attention itself (head norms,
+// rotation, the newest key and value into the cache: crates/xrt-models/src/llama.rs:488-503) instead of
+// a kernel of its own before it.  qkv == nullptr: q comes rotated in bfloat16 as before.
+struct DecodeFusedInput {
+  const float* qkv = nullptr;        // [tokens, row_stride] 32-bit: q at 0, k at k_offset, v at v_offset
+  int row_stride = 0, k_offset = 0, v_offset = 0;
+  const void* q_norm_w = nullptr;    // [head_dim] or null (no head norm); both or neither
+  const void* k_norm_w = nullptr;
+  int norm_dtype = XRT_F32;
+  float eps = 0.f;
+  const float2* cos_sin = nullptr;   // [tokens, head_dim / 2] (cos, sin), or null: no rotation
+  __nv_bfloat16* k_pool = nullptr;   // null: the newest key and value are in the cache already (a layer that reads another's)
+  __nv_bfloat16* v_pool = nullptr;
+};
+
+__device__ __forceinline__ float dec_norm_weight(const void* w, int dtype, int d) {
+  return dtype == XRT_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[d])
+                           : reinterpret_cast<const float*>(w)[d];
+}
+
 template <int HD_MAX>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -357,15 +377,14 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ tok_pos, const int* __restrict__ block_table, int max_blocks,
                             int n_heads, int n_kv_heads, int head_dim, float scale_log2, int window, int chunk,
                             int n_splits, int* __restrict__ counters, int* __restrict__ error_flag, int clustered,
-                            Prefetch pf) {
+                            const DecodeFusedInput fused) {
   constexpr int D_TILES = HD_MAX / 8;
+  __shared__ __align__(16) __nv_bfloat16 newest[2][HD_MAX];  // the step's own key and value of this kv head
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full[2];
   pdl_trigger();
   if (threadIdx.x == 0) XRT_TL(50);
-  if (threadIdx.x == DEC_WARPS * 32 - 1)
-    prefetch_l2_part(pf, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z);
   // The step's arrays (slots, positions, block table) were written before the step began: they may be
   // read, and tiles of old keys fetched, while the kernel before this one (which writes q and the
   // newest key and value) is still running.
@@ -419,20 +438,116 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   };
 
   // query operand: column g = head g of the group (zero at or beyond the group)
-  // the first tile before the wait, unless it holds the newest key (position len - 1)
-  const bool early = has_keys && begin + XRT_BLOCK_TOKENS <= len - 1;
+  // The first tile before the wait, unless it holds the newest key (position len - 1) and the kernel
+  // before this one writes that key; when this kernel writes it itself, the tile's row is patched below.
+  const bool holds_newest = has_keys && len - 1 >= begin && len - 1 < end;
+  const bool writes_newest = fused.qkv != nullptr && fused.k_pool != nullptr && holds_newest;
+  const bool early = has_keys && (fused.qkv != nullptr || begin + XRT_BLOCK_TOKENS <= len - 1);
   if (threadIdx.x == 0 && early) issue_tile(0, 0);
   pdl_wait();
   if (threadIdx.x == 0) XRT_TL(51);
-  const __nv_bfloat16* qt = q + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
   uint32_t qb[D_TILES / 2][2];
+  if (fused.qkv == nullptr) {
+    const __nv_bfloat16* qt = q + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
 #pragma unroll
-  for (int ks = 0; ks < D_TILES / 2; ++ks)
+    for (int ks = 0; ks < D_TILES / 2; ++ks)
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int dim = ks * 16 + e * 8 + 2 * t;
-      qb[ks][e] = (g < group && dim < head_dim) ? *reinterpret_cast<const uint32_t*>(qt + (size_t)g * head_dim + dim) : 0u;
+      for (int e = 0; e < 2; ++e) {
+        const int dim = ks * 16 + e * 8 + 2 * t;
+        qb[ks][e] = (g < group && dim < head_dim) ? *reinterpret_cast<const uint32_t*>(qt + (size_t)g * head_dim + dim) : 0u;
+      }
+  } else {
+    // head_dim == HD_MAX here.  This lane holds dims ks * 16 + e * 8 + 2t, +1 of head g: the partner of a
+    // dim in the rotation, head_dim / 2 further on, is in the same lane (ks + D_TILES / 4).
+    constexpr int HALF_KS = D_TILES / 4;
+    const float* qrow = fused.qkv + (size_t)tok * fused.row_stride + ((size_t)kv_head * group + g) * HD_MAX;
+    float x[D_TILES / 2][2][2];
+    float sq = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D_TILES / 2; ++ks)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float2 two = g < group ? *reinterpret_cast<const float2*>(qrow + ks * 16 + e * 8 + 2 * t) : make_float2(0.f, 0.f);
+        x[ks][e][0] = two.x;
+        x[ks][e][1] = two.y;
+        sq = fmaf(two.x, two.x, sq);
+        sq = fmaf(two.y, two.y, sq);
+      }
+    if (fused.q_norm_w != nullptr) {
+      sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+      const float inv = 1.0f / sqrtf(sq / (float)HD_MAX + fused.eps);
+#pragma unroll
+      for (int ks = 0; ks < D_TILES / 2; ++ks)
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            x[ks][e][j] = (x[ks][e][j] * inv) * dec_norm_weight(fused.q_norm_w, fused.norm_dtype, ks * 16 + e * 8 + 2 * t + j);
     }
+    if (fused.cos_sin != nullptr) {
+      const float2* cs = fused.cos_sin + (size_t)tok * (HD_MAX / 2);
+#pragma unroll
+      for (int ks = 0; ks < HALF_KS; ++ks)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float4 a = *reinterpret_cast<const float4*>(cs + ks * 16 + e * 8 + 2 * t);  // (cos, sin) of two dims
+          const float c2[2] = {a.x, a.z}, s2[2] = {a.y, a.w};
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const float x0 = x[ks][e][j], x1 = x[ks + HALF_KS][e][j];
+            x[ks][e][j] = x0 * c2[j] - x1 * s2[j];
+            x[ks + HALF_KS][e][j] = x0 * s2[j] + x1 * c2[j];
+          }
+        }
+    }
+#pragma unroll
+    for (int ks = 0; ks < D_TILES / 2; ++ks)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) qb[ks][e] = g < group ? pack_bf16(x[ks][e][0], x[ks][e][1]) : 0u;
+    if (writes_newest) {
+      // Warp 0: the newest key (head norm, rotation); warp 1: the newest value.  A lane holds dims
+      // lane + 32 j; the rotation's partner of a dim is in the same lane.  Both go to the cache for the
+      // steps to come and to shared memory for this step (the tile's row is patched when it has landed).
+      if (warp < 2) {
+        constexpr int PER_LANE = HD_MAX / 32;
+        const float* row = fused.qkv + (size_t)tok * fused.row_stride + (warp == 0 ? fused.k_offset : fused.v_offset) +
+                           (size_t)kv_head * HD_MAX;
+        float y[PER_LANE];
+        float ssq = 0.f;
+#pragma unroll
+        for (int j = 0; j < PER_LANE; ++j) {
+          y[j] = row[lane + 32 * j];
+          ssq = fmaf(y[j], y[j], ssq);
+        }
+        if (warp == 0 && fused.k_norm_w != nullptr) {
+          const float inv = 1.0f / sqrtf(warp_sum(ssq) / (float)HD_MAX + fused.eps);
+#pragma unroll
+          for (int j = 0; j < PER_LANE; ++j) y[j] = (y[j] * inv) * dec_norm_weight(fused.k_norm_w, fused.norm_dtype, lane + 32 * j);
+        }
+        if (warp == 0 && fused.cos_sin != nullptr) {
+          const float2* cs = fused.cos_sin + (size_t)tok * (HD_MAX / 2);
+#pragma unroll
+          for (int j = 0; j < PER_LANE / 2; ++j) {
+            const float2 a = cs[lane + 32 * j];
+            const float x0 = y[j], x1 = y[j + PER_LANE / 2];
+            y[j] = x0 * a.x - x1 * a.y;
+            y[j + PER_LANE / 2] = x0 * a.y + x1 * a.x;
+          }
+        }
+        const int block = blocks[(len - 1) / XRT_BLOCK_TOKENS];
+        __nv_bfloat16* pool = warp == 0 ? fused.k_pool : fused.v_pool;
+        __nv_bfloat16* dst = pool + (((size_t)block * n_kv_heads + kv_head) * XRT_BLOCK_TOKENS + (len - 1) % XRT_BLOCK_TOKENS) * HD_MAX;
+#pragma unroll
+        for (int j = 0; j < PER_LANE; ++j) {
+          const __nv_bfloat16 b = __float2bfloat16_rn(y[j]);
+          newest[warp][lane + 32 * j] = b;
+          if (block >= 0) dst[lane + 32 * j] = b;
+        }
+      }
+      __syncthreads();
+    }
+  }
   HeadColumnState<D_TILES> st;
   st.init();
   const int n_tiles = has_keys ? (end - begin + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS : 0;  // begin is a multiple of 64
@@ -442,6 +557,18 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     // the buffer of tile i + 1 held tile i - 1, which every warp left before the barrier that ended the last round
     if (threadIdx.x == 0 && i + 1 < n_tiles) issue_tile(i + 1, (i + 1) & 1);
     if (!dec_mbar_wait(full_addr[i & 1], (uint32_t)(i >> 1) & 1u)) failed = 1;
+    if (writes_newest && i == n_tiles - 1) {
+      // the newest key and value into their row of the tile that has just landed (whatever the copy
+      // read there): piece c of row r lies at piece c ^ (r % 8) of its box of 64 dims
+      const int r = (len - 1) % XRT_BLOCK_TOKENS;
+      if (threadIdx.x < 2 * (HD_MAX / 8)) {
+        const int which = threadIdx.x / (HD_MAX / 8), piece = threadIdx.x % (HD_MAX / 8);
+        unsigned char* tile = (which == 0 ? k_tiles : v_tiles) + (i & 1) * tile_bytes;
+        *reinterpret_cast<uint4*>(tile + (piece >> 3) * DEC_BOX_BYTES + r * 128 + (((piece & 7) ^ (r & 7)) << 4)) =
+            *reinterpret_cast<const uint4*>(&newest[which][piece * 8]);
+      }
+      __syncthreads();
+    }
     const int key_abs = begin + i * XRT_BLOCK_TOKENS + warp * 16;
     if (!failed && key_abs < end)  // only the first and the last 16 keys a warp sees can hold a hidden key
       attend_16_keys_heads<D_TILES, true>(st, qb, k_tiles + (i & 1) * tile_bytes, v_tiles + (i & 1) * tile_bytes,
@@ -591,7 +718,7 @@ int launch_decode_tma(__nv_bfloat16* out, float* part_o, float* part_ml, const _
                       const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, long long pool_rows, const int* tok_slot,
                       const int* tok_pos, const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
                       int head_dim, float scale, int window, int chunk, int n_splits, int* counters, int* error_flag,
-                      cudaStream_t stream, bool* merged) {
+                      cudaStream_t stream, bool* merged, const DecodeFusedInput& fused) {
   CUtensorMap map_k, map_v;
   if (!dec_make_map(&map_k, k_pool, pool_rows, head_dim) || !dec_make_map(&map_v, v_pool, pool_rows, head_dim))
     return XRT_ERR_UNSUPPORTED;
@@ -649,7 +776,7 @@ int launch_decode_tma(__nv_bfloat16* out, float* part_o, float* part_ml, const _
   config.numAttrs = n_attrs;
   cudaLaunchKernelEx(&config, kernel, map_k, map_v, out, part_o, part_ml, q, tok_slot, tok_pos, block_table, max_blocks,
                      n_heads, n_kv_heads, head_dim, scale * 1.4426950408889634f, window, chunk, n_splits, counters, error_flag,
-                     clustered ? 1 : 0, take_prefetch());
+                     clustered ? 1 : 0, fused);
   return launch_status();
 }
 
@@ -684,14 +811,20 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_
                   const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, long long pool_rows, const int* tok_slot,
                   const int* tok_pos, const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
                   int head_dim, float scale, int window, int chunk, int n_splits, int* counters, int* error_flag,
-                  cudaStream_t stream, bool* merged) {
+                  cudaStream_t stream, bool* merged, const DecodeFusedInput& fused) {
   *merged = false;
   const bool rows_only = tuning().decode_attention == 1, copies_only = tuning().decode_attention == 2;
   if (n_heads / n_kv_heads <= 8 && !rows_only && !copies_only && pool_rows > 0 && head_dim % 64 == 0 &&
-      (((uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0)
+      (((uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0) {
+    // the kernel's own rotation walks a head of exactly the class's size in 32-bit pairs and quads
+    if (fused.qkv != nullptr && (head_dim != HD_MAX || fused.row_stride % 4 != 0 || fused.k_offset % 4 != 0 ||
+                                 fused.v_offset % 4 != 0 || (((uintptr_t)fused.qkv | (uintptr_t)fused.cos_sin) & 15) != 0))
+      return XRT_ERR_UNSUPPORTED;
     return launch_decode_tma<HD_MAX>(out, part_o, part_ml, q, k_pool, v_pool, pool_rows, tok_slot, tok_pos, block_table,
                                      max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
-                                     counters, error_flag, stream, merged);
+                                     counters, error_flag, stream, merged, fused);
+  }
+  if (fused.qkv != nullptr) return XRT_ERR_UNSUPPORTED;  // only the kernel above rotates and writes the cache itself
   if (n_heads / n_kv_heads <= 8 && !rows_only)
     return launch_decode_as<HD_MAX, true>(out, part_o, part_ml, q, k_pool, v_pool, tok_slot, tok_pos, block_table,
                                           max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk,
@@ -730,7 +863,8 @@ static int attention_decode_impl(void* out, float* part_o, float* part_ml, const
                                  const void* v_pool, int n_blocks, const int* tok_slot, const int* tok_pos,
                                  const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
                                  int head_dim, float scale, int window, int chunk, int n_splits, int* counters,
-                                 int* error_flag, cudaStream_t stream, int* merged_out = nullptr) {
+                                 int* error_flag, cudaStream_t stream, int* merged_out = nullptr,
+                                 const DecodeFusedInput& fused = DecodeFusedInput()) {
   if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || chunk <= 0 || n_splits <= 0)
     return XRT_ERR_ARGUMENT;
   if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256 || n_heads / n_kv_heads > 16 ||
@@ -749,7 +883,7 @@ static int attention_decode_impl(void* out, float* part_o, float* part_ml, const
   const long long pool_rows = (long long)n_blocks * n_kv_heads * XRT_BLOCK_TOKENS;  // 0: the pools' size is not known
 #define XRT_DECODE(HD) status = launch_decode<HD>(o, part_o, part_ml, qp, kp, vp, pool_rows, tok_slot, tok_pos, block_table, \
                                                   max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window,      \
-                                                  chunk, n_splits, counters, error_flag, stream, &merged)
+                                                  chunk, n_splits, counters, error_flag, stream, &merged, fused)
   if (head_dim <= 32) XRT_DECODE(32);
   else if (head_dim <= 64) XRT_DECODE(64);
   else if (head_dim <= 128) XRT_DECODE(128);
@@ -801,6 +935,34 @@ XRT_EXPORT int xrt_attention_decode_fused(void* out, float* part_o, float* part_
   return xrt::attention_decode_impl(out, part_o, part_ml, q, k_pool, v_pool, n_blocks, tok_slot, tok_pos, block_table,
                                     max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
                                     counters, error_flag, stream, merged);
+}
+
+// The same, fed with the 32-bit output of the q/k/v product instead of a rotated q: the kernel applies
+// the head norms (q_norm_w, k_norm_w: [head_dim] in norm_dtype, or both null) and the split-half rotation
+// over the whole head (cos_sin: float32 [n_tokens, head_dim / 2, 2], or null), and the block that holds a
+// sequence's newest position writes its key and value into the cache (write_kv = 0: they are there
+// already).  Only where the kernel fed by TMA runs: head_dim 64, 128 or 256, at most 8 query heads a kv
+// head, n_blocks known; anything else is refused (-2) and the caller runs the rotation as a kernel of
+// its own.  counters may be null (then a second kernel merges splits that did not merge as clusters).
+XRT_EXPORT int xrt_attention_decode_qkv(void* out, float* part_o, float* part_ml, int* counters, const float* qkv,
+                                        int row_stride, int k_offset, int v_offset, const void* q_norm_w,
+                                        const void* k_norm_w, int norm_dtype, float eps, const float* cos_sin,
+                                        int write_kv, void* k_pool, void* v_pool, int n_blocks, const int* tok_slot,
+                                        const int* tok_pos, const int* block_table, int max_blocks, int n_tokens,
+                                        int n_heads, int n_kv_heads, int head_dim, float scale, int window, int chunk,
+                                        int n_splits, int* error_flag, cudaStream_t stream, int* merged) {
+  if (qkv == nullptr || (q_norm_w == nullptr) != (k_norm_w == nullptr) || n_blocks <= 0) return XRT_ERR_ARGUMENT;
+  if (norm_dtype != XRT_F32 && norm_dtype != XRT_BF16) return XRT_ERR_UNSUPPORTED;
+  xrt::DecodeFusedInput fused;
+  fused.qkv = qkv;
+  fused.row_stride = row_stride; fused.k_offset = k_offset; fused.v_offset = v_offset;
+  fused.q_norm_w = q_norm_w; fused.k_norm_w = k_norm_w; fused.norm_dtype = norm_dtype; fused.eps = eps;
+  fused.cos_sin = (const float2*)cos_sin;
+  fused.k_pool = write_kv ? (__nv_bfloat16*)k_pool : nullptr;
+  fused.v_pool = write_kv ? (__nv_bfloat16*)v_pool : nullptr;
+  return xrt::attention_decode_impl(out, part_o, part_ml, nullptr, k_pool, v_pool, n_blocks, tok_slot, tok_pos, block_table,
+                                    max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
+                                    counters, error_flag, stream, merged, fused);
 }
 
 // ---------------------------------------------------------------------------------------------

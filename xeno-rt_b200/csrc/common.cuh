@@ -29,33 +29,9 @@ struct Tuning {
   int decode_attention = 0;         // 0 auto, 1 heads as rows, 2 cp.async copies, 3 no clusters
   int gemm_tile_rows = 0;           // 0 auto, 128 or 256: the prefill product's tile
   bool decode_gemm_clusters = true; // the decode product's splits meet through a cluster's shared memory
-  int decode_gemm_ring_kb = 200;    // shared memory of the decode product's ring of weight slabs
   int decode_cluster_pairs = 128;    // decode attention merges its splits as clusters up to so many (token, kv head) pairs
 };
 const Tuning& tuning();
-
-// A stretch of memory (weights that a later kernel of the step will stream) that a kernel asks the
-// L2 to fetch while it runs.  The products of a decode step that read 30 to 50 MB are bound by the
-// latency of their first loads from HBM, not by bandwidth, and HBM idles across every boundary between
-// two kernels: a kernel that leaves bandwidth unused (a norm, the rotation, attention over a few
-// sequences, a small product) starts the next product's weights on their way, and that product then
-// streams from the L2.  Nothing waits for a prefetch and nothing depends on it having happened.
-struct Prefetch {
-  const char* ptr = nullptr;
-  unsigned long long bytes = 0;  // a multiple of 16; ptr is 16-byte aligned
-};
-// The hint left by xrt_hint_prefetch for the next launch that can carry one; taking it clears it.
-Prefetch take_prefetch();
-constexpr int PREFETCH_EXTRA_BLOCKS = 64;  // blocks that a kernel of a handful of blocks adds to carry a prefetch
-
-// Part `part` of `parts` of a prefetch, issued by ONE thread: pieces of 16 KB, dealt out in turn.
-__device__ __forceinline__ void prefetch_l2_part(Prefetch pf, unsigned part, unsigned parts) {
-  constexpr unsigned long long PIECE = 16384;
-  for (unsigned long long at = (unsigned long long)part * PIECE; at < pf.bytes; at += (unsigned long long)parts * PIECE) {
-    const unsigned size = (unsigned)(pf.bytes - at < PIECE ? pf.bytes - at : PIECE);
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf.ptr + at), "r"(size) : "memory");
-  }
-}
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -114,7 +114,7 @@ template <int MODE, typename TO>
 __global__ void __launch_bounds__(DG_THREADS, 1)
 gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                            TO* __restrict__ out, float* __restrict__ partial, int* __restrict__ counters,
-                           const DecodeGemmShape shape, int* __restrict__ error_flag, Prefetch pf) {
+                           const DecodeGemmShape shape, int* __restrict__ error_flag) {
   constexpr int GROUPS = MODE == 2 ? 2 : 1;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -229,8 +229,6 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       }
       XRT_TL(22);
       if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 4); }
-    } else if (lane == 1) {
-      prefetch_l2_part(pf, blockIdx.x, gridDim.x);  // weights of a later product, while this one streams its own
     }
     if (shape.clustered) dg_cluster_wait();
   } else if (warp == 1) {
@@ -572,10 +570,9 @@ int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorM
     }
     if (held[shape.splits] >= shape.tiles) shape.clustered = 1;
   }
-  const Prefetch pf = take_prefetch();
   if (!shape.clustered) {
     launch_kernel(kernel, dim3(blocks), dim3(DG_THREADS), (size_t)smem, stream, map_w, map_x, (TO*)out, partial, counters,
-                  shape, error_flag, pf);
+                  shape, error_flag);
     return launch_status();
   }
   cudaLaunchConfig_t config = {};
@@ -595,7 +592,7 @@ int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorM
   ++n_attrs;
   config.attrs = attrs;
   config.numAttrs = n_attrs;
-  cudaLaunchKernelEx(&config, kernel, map_w, map_x, (TO*)out, partial, counters, shape, error_flag, pf);
+  cudaLaunchKernelEx(&config, kernel, map_w, map_x, (TO*)out, partial, counters, shape, error_flag);
   return launch_status();
 }
 
@@ -652,7 +649,7 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05(void* out, const void* x, const void* w, 
   // splits x accumulator columns x ceil(128 / splits) floats
   const int per = shape.splits > 1 ? (xrt::DG_ROWS + shape.splits - 1) / shape.splits : 0;
   const int recv_bytes = shape.splits * groups * shape.nb * per * 4;
-  const int budget = xrt::tuning().decode_gemm_ring_kb * 1024 - recv_bytes;
+  const int budget = 200 * 1024 - recv_bytes;
   shape.stages = budget / stage_bytes;
   if (shape.stages > 12) shape.stages = 12;
   if (shape.stages < 2) return XRT_ERR_UNSUPPORTED;

@@ -42,7 +42,7 @@ __device__ __forceinline__ void gs_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
 template <int M_TILES, int MODE, int GS_STAGES, int ROW_GROUPS, typename TO>
 __global__ void __launch_bounds__(GS_THREADS, (M_TILES >= 4 ? 2 : 1))
 gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                   int M, int N, int K, int ldx, int ldo, long long up_offset, Prefetch pf) {
+                   int M, int N, int K, int ldx, int ldo, long long up_offset) {
   // ROW_GROUPS groups of 8 weight rows a block (SwiGLU: as many gate groups and as many up groups);
   // every X fragment a warp loads is used for all of them, which is what keeps the L1 traffic of
   // many batch rows below the shared-memory traffic of the weights
@@ -56,7 +56,6 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
 
   pdl_trigger();
   if (threadIdx.x == 0) XRT_TL(30);
-  if (threadIdx.x == GS_THREADS - 1) prefetch_l2_part(pf, blockIdx.x, gridDim.x);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * BLOCK_ROWS;
   const int n_slabs = (K + GS_SLAB - 1) / GS_SLAB;
@@ -196,7 +195,7 @@ int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, 
   }
   const int blocks = (N + ROW_GROUPS * GS_ROWS - 1) / (ROW_GROUPS * GS_ROWS);
   launch_kernel(kernel, dim3(blocks), dim3(GS_THREADS), SMEM, stream, (TO*)out, (const __nv_bfloat16*)x,
-                (const __nv_bfloat16*)w, M, N, K, ldx, ldo, up_offset, take_prefetch());
+                (const __nv_bfloat16*)w, M, N, K, ldx, ldo, up_offset);
   return launch_status();
 }
 

@@ -43,13 +43,9 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
 template <typename TW, typename TO, int CHUNKS>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_vec_kernel(TO* __restrict__ out, const float* __restrict__ x, const TW* __restrict__ w,
-                   const int* __restrict__ rows, int n_rows, int width, float eps, Prefetch pf) {
+                   const int* __restrict__ rows, int width, float eps) {
   __shared__ float scratch[33];
   pdl_trigger();
-  if ((int)blockIdx.x >= n_rows) {  // a block that only carries the prefetch
-    if (threadIdx.x == 0) prefetch_l2_part(pf, blockIdx.x - n_rows, gridDim.x - n_rows);
-    return;
-  }
   // the weight does not depend on the step: it is on its way while the kernel before this one finishes
   float wv[CHUNKS][4];
 #pragma unroll
@@ -121,21 +117,19 @@ XRT_EXPORT int xrt_rmsnorm(void* out, const float* x, const void* weight, const 
                            int width, float eps, int weight_dtype, int out_dtype, cudaStream_t stream) {
   if (n_rows < 0 || width <= 0) return XRT_ERR_ARGUMENT;
   if (n_rows == 0) return XRT_OK;
-  const xrt::Prefetch pf = xrt::take_prefetch();
-  const int grid = n_rows + (pf.bytes ? xrt::PREFETCH_EXTRA_BLOCKS : 0);
   const bool vec = width % 4 == 0 && width <= 8 * xrt::NORM_THREADS * 4 && (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
   const int chunks = (width / 4 + xrt::NORM_THREADS - 1) / xrt::NORM_THREADS;
   const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
   XRT_DISPATCH_DTYPE(weight_dtype, TW, {
     XRT_DISPATCH_DTYPE(out_dtype, TO, {
       if (vec && chunks <= 1)
-        xrt::launch_kernel(xrt::rmsnorm_vec_kernel<TW, TO, 1>, dim3(grid), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, n_rows, width, eps, pf);
+        xrt::launch_kernel(xrt::rmsnorm_vec_kernel<TW, TO, 1>, dim3(n_rows), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
       else if (vec && chunks <= 2)
-        xrt::launch_kernel(xrt::rmsnorm_vec_kernel<TW, TO, 2>, dim3(grid), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, n_rows, width, eps, pf);
+        xrt::launch_kernel(xrt::rmsnorm_vec_kernel<TW, TO, 2>, dim3(n_rows), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
       else if (vec && chunks <= 4)
-        xrt::launch_kernel(xrt::rmsnorm_vec_kernel<TW, TO, 4>, dim3(grid), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, n_rows, width, eps, pf);
+        xrt::launch_kernel(xrt::rmsnorm_vec_kernel<TW, TO, 4>, dim3(n_rows), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
       else if (vec)
-        xrt::launch_kernel(xrt::rmsnorm_vec_kernel<TW, TO, 8>, dim3(grid), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, n_rows, width, eps, pf);
+        xrt::launch_kernel(xrt::rmsnorm_vec_kernel<TW, TO, 8>, dim3(n_rows), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
       else
         xrt::launch_kernel(xrt::rmsnorm_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
     });

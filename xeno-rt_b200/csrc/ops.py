@@ -39,6 +39,8 @@ _SIGNATURES = {
     "xrt_gemm_decode_tcgen05": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_attention_decode_fused": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P],
     "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P],
+    "xrt_attention_decode_qkv": [_P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I,
+                                 _I, _I, _F, _I, _I, _I, _P, _P, _P],
     "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "xrt_attention_prefill_tcgen05": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
@@ -68,8 +70,6 @@ def library():
                 fn.restype = _I
             lib.xrt_attention_decode_fused_max_splits.argtypes = [_I, _I]
             lib.xrt_attention_decode_fused_max_splits.restype = _I
-            lib.xrt_hint_prefetch.argtypes = [_P, ctypes.c_ulonglong]
-            lib.xrt_hint_prefetch.restype = _I
             lib.xrt_set_tuning.argtypes = [_I, _I]
             lib.xrt_set_tuning.restype = _I
             lib.xrt_gemm_decode_tcgen05_scratch.argtypes = [_I, _I, _I, _I, _I]
@@ -97,6 +97,8 @@ class Tuning:
     ``decode_attention`` "auto", "rows" (query heads as MMA rows), "cp" (cp.async tiles), "nocluster"
     ``prefill_attention`` "auto" or "mma" (the mma.sync kernel also where the tcgen05 one applies)
     ``gemm_tile_rows``   0 (auto), 128 or 256: the tile of the prompt product
+    ``decode_cluster_pairs``  decode attention merges a (token, kv head)'s splits as one thread-block
+                         cluster up to so many pairs a step; beyond, partials and a second kernel
     """
     graphs: bool = True
     pdl: bool = True
@@ -105,8 +107,6 @@ class Tuning:
     decode_attention: str = "auto"
     prefill_attention: str = "auto"
     gemm_tile_rows: int = 0
-    prefetch: int = 0
-    decode_gemm_ring_kb: int = 200
     decode_cluster_pairs: int = 128
 
 
@@ -130,7 +130,7 @@ def set_tuning(new: Tuning) -> None:
     lib = library()
     for key, value in ((0, int(new.pdl)), (1, _DECODE_ATTENTION[new.decode_attention]),
                        (2, int(new.gemm_tile_rows)), (3, int(new.decode_gemm_clusters)),
-                       (4, int(new.decode_gemm_ring_kb)), (5, int(new.decode_cluster_pairs))):
+                       (4, int(new.decode_cluster_pairs))):
         if lib.xrt_set_tuning(key, value) != 0:
             raise KernelError(f"tuning: value {value} of setting {key} was refused")
     _tuning = new
@@ -199,27 +199,6 @@ def _check(status: int, what: str) -> None:
     if status == -2:
         raise KernelError(f"{what}: sizes or dtypes outside what the kernel handles")
     raise KernelError(f"{what}: CUDA launch error {status}")
-
-
-def hint_prefetch(tensor, begin_bytes: int = 0, max_bytes: int | None = None) -> int:
-    """Asks the next kernel of this library that can carry one (the norm, the rotation, decode
-    attention, the few-row products) to start ``tensor``'s bytes from ``begin_bytes`` on, at most
-    ``max_bytes`` of them, on their way into the L2 while it runs.  Returns how many bytes were
-    asked for.  The products of a decode step are bound by the latency of HBM at their start and at
-    every boundary between kernels; weights that wait in the L2 take that away.  A hint that no
-    kernel picks up is dropped by the next hint; nothing depends on a prefetch having happened."""
-    if tensor is None or not tensor.is_cuda or not tensor.is_contiguous():
-        return 0
-    total = tensor.numel() * tensor.element_size()
-    begin = min(total, (begin_bytes + 15) // 16 * 16)
-    size = total - begin if max_bytes is None else min(total - begin, max_bytes)
-    size -= size % 16
-    address = tensor.data_ptr() + begin
-    if size <= 0 or address % 16:
-        return 0
-    if library().xrt_hint_prefetch(address, size) != 0:
-        raise KernelError("hint_prefetch: the address is not 16-byte aligned")
-    return size
 
 
 def embedding(out, table, ids, error_flag) -> None:
@@ -486,6 +465,51 @@ def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_h
         float(scale), int(window), int(chunk), int(n_splits), flag.data_ptr(), _stream(), ctypes.byref(merged)),
         "attention_decode")
     if n_splits > 1 and not merged.value:
+        add_launches(1)  # the combine kernel
+
+
+def attention_decode_takes_qkv(n_heads: int, n_kv_heads: int, head_dim: int, rope_half: int, pairing: str) -> bool:
+    """Whether ``attention_decode_qkv`` takes these sizes (the kernel fed by TMA does the step between
+    the q/k/v product and attention itself): head size 64, 128 or 256, at most 8 query heads a kv head,
+    a split-half rotation over the whole head or none, and no other decode attention kernel forced."""
+    return (head_dim in (64, 128, 256) and n_heads // n_kv_heads <= 8 and rope_half in (0, head_dim // 2)
+            and (pairing == "split_half" or rope_half == 0) and tuning().decode_attention in ("auto", "nocluster"))
+
+
+def attention_decode_qkv(out, qkv, k_offset: int, v_offset: int, q_norm_w, k_norm_w, eps: float, cos_sin, k_pool, v_pool,
+                         tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                         window: int, chunk: int, n_splits: int, write_kv: bool = True, fused: bool = True) -> None:
+    """Decode attention straight from the 32-bit output of the q/k/v product: per-head norms, rotation,
+    the newest key and value into the cache (unless ``write_kv`` is False) and attention over the cache
+    in ONE kernel (csrc/attention_decode.cu).  ``qkv``: float32 [n, row] with q at 0, k at ``k_offset``,
+    v at ``v_offset``.  Check ``attention_decode_takes_qkv`` first; other sizes raise."""
+    n = qkv.shape[0]
+    if out.shape != (n, n_heads * head_dim) or tok_slot.numel() != n or tok_pos.numel() != n:
+        raise KernelError("attention_decode_qkv: shapes do not fit")
+    if k_pool.shape != v_pool.shape or k_pool.shape[1:] != (n_kv_heads, 64, head_dim):
+        raise KernelError("attention_decode_qkv: the cache pool must be [blocks, kv heads, 64, head_dim]")
+    if ((write_kv and qkv.shape[1] < v_offset + n_kv_heads * head_dim) or qkv.shape[1] < n_heads * head_dim
+            or (cos_sin is not None and cos_sin.shape[1] != head_dim // 2)):
+        raise KernelError("attention_decode_qkv: the q/k/v row or the rotation table does not fit the heads")
+    part_o = part_ml = None
+    merged = ctypes.c_int(0)
+    flag, counters, _ = device_state(qkv.device)
+    if n_splits > 1:
+        part_o = torch.empty(n * n_heads * n_splits * head_dim, dtype=torch.float32, device=qkv.device)
+        part_ml = torch.empty(n * n_heads * n_splits * 2, dtype=torch.float32, device=qkv.device)
+    use_counters = fused and n_splits > 1 and n * n_kv_heads <= _COUNTER_SLOTS
+    norm_dtype = q_norm_w.dtype if q_norm_w is not None else torch.float32
+    _check(_kernels().xrt_attention_decode_qkv(
+        _ptr(out, "out", torch.bfloat16), _ptr(part_o, "part_o"), _ptr(part_ml, "part_ml"),
+        counters.data_ptr() if use_counters else 0, _ptr(qkv, "qkv", torch.float32), qkv.shape[1], int(k_offset),
+        int(v_offset), _ptr(q_norm_w, "q_norm_w"), _ptr(k_norm_w, "k_norm_w", norm_dtype), _code(norm_dtype), float(eps),
+        _ptr(cos_sin, "cos_sin", torch.float32), 1 if write_kv else 0, _ptr(k_pool, "k_pool", torch.bfloat16),
+        _ptr(v_pool, "v_pool", torch.bfloat16), k_pool.shape[0], _ptr(tok_slot, "tok_slot", torch.int32),
+        _ptr(tok_pos, "tok_pos", torch.int32), _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n,
+        n_heads, n_kv_heads, head_dim, float(scale), int(window), int(chunk), int(n_splits), flag.data_ptr(), _stream(),
+        ctypes.byref(merged)), "attention_decode_qkv")
+    if n_splits > 1 and not merged.value and (
+            not use_counters or n_splits > attention_decode_fused_max_splits(head_dim, n_heads // n_kv_heads)):
         add_launches(1)  # the combine kernel
 
 

@@ -153,13 +153,9 @@ qk_rope_kv_write_128_kernel(
     const float2* __restrict__ cos_sin, int rope_half,
     const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
     const int* __restrict__ block_table, int max_blocks,
-    int n_tokens, int n_heads, int n_kv_heads, int write_kv, Prefetch pf) {
+    int n_heads, int n_kv_heads, int write_kv) {
   constexpr int HD = 128;
   pdl_trigger();
-  if ((int)blockIdx.x >= n_tokens) {  // a block that only carries the prefetch
-    if (threadIdx.x == 0) prefetch_l2_part(pf, blockIdx.x - n_tokens, gridDim.x - n_tokens);
-    return;
-  }
   // The step's arrays (slots, positions, block table) were written before the step began, and the norm
   // weights never change: they are read while the kernel before this one finishes.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -259,15 +255,13 @@ XRT_EXPORT int xrt_qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, con
                     v_offset % 4 == 0 &&
                     (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)cos_sin) & 15) == 0;
   if (fast) {
-    const xrt::Prefetch pf = xrt::take_prefetch();
-    const int grid = n_tokens + (pf.bytes ? xrt::PREFETCH_EXTRA_BLOCKS : 0);
     XRT_DISPATCH_DTYPE(norm_dtype, TN, {
       XRT_DISPATCH_DTYPE(q_dtype, TQ, {
         XRT_DISPATCH_DTYPE(cache_dtype, TC, {
-          xrt::launch_kernel(xrt::qk_rope_kv_write_128_kernel<TN, TQ, TC>, dim3(grid), dim3(256), 0, stream,
+          xrt::launch_kernel(xrt::qk_rope_kv_write_128_kernel<TN, TQ, TC>, dim3(n_tokens), dim3(256), 0, stream,
               (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, qkv, row_stride, k_offset, v_offset, (const TN*)q_norm_w,
               (const TN*)k_norm_w, eps, (const float2*)cos_sin, rope_half, tok_slot, tok_pos, block_table,
-              max_blocks, n_tokens, n_heads, n_kv_heads, write_kv, pf);
+              max_blocks, n_heads, n_kv_heads, write_kv);
         });
       });
     });

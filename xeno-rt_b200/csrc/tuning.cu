@@ -9,18 +9,11 @@ static Tuning g_tuning;
 
 const Tuning& tuning() { return g_tuning; }
 
-static Prefetch g_prefetch;
-
-Prefetch take_prefetch() {
-  Prefetch pf = g_prefetch;
-  g_prefetch = Prefetch();
-  return pf;
-}
-
 }  // namespace xrt
 
 // key: 0 pdl (1 on, 0 off); 1 decode_attention (0 auto, 1 heads as rows, 2 cp.async copies, 3 no
-// clusters); 2 gemm_tile_rows (0 auto, 128, 256); 3 decode_gemm_clusters (1 on, 0 off).
+// clusters); 2 gemm_tile_rows (0 auto, 128, 256); 3 decode_gemm_clusters (1 on, 0 off); 4 decode_cluster_pairs
+// (decode attention merges its splits as clusters up to so many (token, kv head) pairs).
 XRT_EXPORT int xrt_set_tuning(int key, int value) {
   using xrt::g_tuning;
   switch (key) {
@@ -28,19 +21,7 @@ XRT_EXPORT int xrt_set_tuning(int key, int value) {
     case 1: if (value < 0 || value > 3) return XRT_ERR_ARGUMENT; g_tuning.decode_attention = value; return XRT_OK;
     case 2: if (value != 0 && value != 128 && value != 256) return XRT_ERR_ARGUMENT; g_tuning.gemm_tile_rows = value; return XRT_OK;
     case 3: g_tuning.decode_gemm_clusters = value != 0; return XRT_OK;
-    case 4: if (value < 32 || value > 200) return XRT_ERR_ARGUMENT; g_tuning.decode_gemm_ring_kb = value; return XRT_OK;
-    case 5: if (value < 0) return XRT_ERR_ARGUMENT; g_tuning.decode_cluster_pairs = value; return XRT_OK;
+    case 4: if (value < 0) return XRT_ERR_ARGUMENT; g_tuning.decode_cluster_pairs = value; return XRT_OK;
     default: return XRT_ERR_ARGUMENT;
   }
-}
-
-// Asks the next launch of this library that can carry a prefetch (the norm, the rotation, the decode
-// attention and the few-row products) to start `bytes` bytes at `ptr` on their way into the L2.  ptr
-// must be 16-byte aligned; bytes is rounded down to a multiple of 16.  A null ptr or 0 bytes clears
-// the hint.  The hint belongs to the calling thread's next launch: callers launch from one thread.
-XRT_EXPORT int xrt_hint_prefetch(const void* ptr, unsigned long long bytes) {
-  if (((uintptr_t)ptr & 15) != 0) return XRT_ERR_ARGUMENT;
-  xrt::g_prefetch.ptr = (const char*)ptr;
-  xrt::g_prefetch.bytes = ptr == nullptr ? 0 : (bytes & ~15ull);
-  return XRT_OK;
 }

@@ -54,12 +54,6 @@ class Model:
         for layer in self.layers:
             parts += list(layer.values())
         self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
-        # the weight that each place of the schedule is followed by: what the next layer (or the output
-        # matrix) reads first, for parts that start it on its way into the L2 while they finish
-        firsts = [next((w for w in (getattr(p, "first_weight", None) for p in layer.values()) if w is not None), None)
-                  for layer in self.layers]
-        order = [firsts[place.layer] for place in spec.schedule]
-        self._next_weight = order[1:] + [getattr(self.lm_head, "first_weight", None)]
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -150,7 +144,6 @@ class Model:
         for i, place in enumerate(self.spec.schedule):
             owns = place.cache_from is None
             stores = cache.store(i if owns else place.cache_from) or {}
-            ctx.shared["next_weight"] = self._next_weight[i]
             self.arrangements[place.layer](self.layers[place.layer], x, ctx, stores, owns)
         if want_rows is None or want_rows.numel() == 0:
             return None

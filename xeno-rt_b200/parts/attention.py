@@ -60,7 +60,6 @@ class GroupedQueryAttention:
         if self.w_qkv is None:  # tensors that came one by one
             self.w_qkv = torch.cat([weights["q"], weights["k"], weights["v"]], dim=0).contiguous()
         self.w_q = self.w_qkv[: self.q_width]
-        self.first_weight = self.w_qkv
         self.w_o = weights["o"]
         self.q_norm = weights.get("q_norm") if params.get("qk_norm") else None
         self.k_norm = weights.get("k_norm") if params.get("qk_norm") else None
@@ -78,24 +77,25 @@ class GroupedQueryAttention:
 
     def forward(self, h, residual, ctx, store, owns_cache=True):
         n = h.shape[0]
-        mask = ops.tuning().prefetch if n <= 64 else 0
-        if mask & 4:
-            ops.hint_prefetch(self.w_o)
         qkv = linear(h, self.w_qkv if owns_cache else self.w_q, out_dtype=torch.float32)
-        if mask & 8:
-            ops.hint_prefetch(self.w_o)
-        q = torch.empty((n, self.q_width), dtype=self.act_dtype, device=h.device)
-        ops.qk_rope_kv_write(q, store.k, store.v, qkv, self.q_width, self.q_width + self.kv_width, self.q_norm,
-                             self.k_norm, self.eps, self.position.tables(ctx), ctx.tok_slot, ctx.tok_pos,
-                             store.block_table, self.n_heads, self.n_kv_heads, self.head_dim, write_kv=owns_cache,
-                             pairing=getattr(self.position, "pairing", "split_half"))
+        window = int(self.window) if self.window else 0
+        pairing = getattr(self.position, "pairing", "split_half")
+        cos_sin = self.position.tables(ctx)
         # padding rows belong to no sequence: kernels that walk sequences leave them unwritten
-        attended = torch.zeros_like(q) if sum(ctx.new_lens) < ctx.n_tokens else torch.empty_like(q)
-        if mask & 16:
-            ops.hint_prefetch(self.w_o)
-        self.attend(attended, q, ctx, store)
-        if mask & 32:
-            ops.hint_prefetch(ctx.shared.get("next_weight"), 0, 48 << 20)
+        padded = sum(ctx.new_lens) < ctx.n_tokens
+        attended = (torch.zeros if padded else torch.empty)((n, self.q_width), dtype=self.act_dtype, device=h.device)
+        if self.dtype is DType.BF16:
+            from . import attention_bf16
+            if attention_bf16.decode_from_qkv(attended, qkv, self.q_width, self.q_width + self.kv_width, self.q_norm,
+                                              self.k_norm, self.eps, cos_sin, pairing, ctx, store, self.n_heads,
+                                              self.n_kv_heads, self.head_dim, self.scale, window, owns_cache):
+                qkv = None
+        if qkv is not None:
+            q = torch.empty((n, self.q_width), dtype=self.act_dtype, device=h.device)
+            ops.qk_rope_kv_write(q, store.k, store.v, qkv, self.q_width, self.q_width + self.kv_width, self.q_norm,
+                                 self.k_norm, self.eps, cos_sin, ctx.tok_slot, ctx.tok_pos, store.block_table,
+                                 self.n_heads, self.n_kv_heads, self.head_dim, write_kv=owns_cache, pairing=pairing)
+            self.attend(attended, q, ctx, store)
         linear(attended, self.w_o, accumulate_into=residual)
 
     def attend(self, out, q, ctx, store):

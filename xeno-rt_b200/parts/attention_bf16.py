@@ -10,7 +10,7 @@ DECODE_BLOCKS_PER_SM = 3   # 70 KB of shared memory a block at head size 128
 TCGEN05_MIN_NEW = 32       # prompts at least this long use the tcgen05 attention (tiles of 128 query rows)
 FUSED_COMBINE_MAX = 32     # (tokens x kv heads) up to which the splits are merged inside the attention kernel (measured again with 6 splits at 8 sequences: the second kernel is still faster there)
 SPLIT_OVERHEAD_TILES = 2   # what a block costs beside its tiles (query load, merge, partials), in tiles of 64 keys
-CLUSTER_MAX_PAIRS, CLUSTER_MAX_SPLITS = 128, 16  # up to so many (token, kv head) pairs the kernel runs a pair's splits
+CLUSTER_MAX_SPLITS = 16   # up to ops.Tuning.decode_cluster_pairs (token, kv head) pairs the kernel runs a pair's splits
 #                            as one thread-block cluster that merges itself through distributed shared memory (csrc/
 #                            attention_decode.cu has the same two numbers); a split then costs the merge far less
 CLUSTER_MERGE_TILES = 0.2
@@ -32,7 +32,7 @@ def decode_split(n_seqs: int, n_kv_heads: int, max_context: int, sms: int):
     for splits in range(1, max(1, min((blocks + 1) // 2, 64)) + 1):
         tiles = -(-blocks // splits)
         real = -(-blocks // tiles)  # splits that hold keys
-        clustered = pairs <= CLUSTER_MAX_PAIRS and real <= CLUSTER_MAX_SPLITS
+        clustered = pairs <= ops.tuning().decode_cluster_pairs and real <= CLUSTER_MAX_SPLITS
         # whole clusters have to find room: about two blocks a multiprocessor instead of three (measured at 4
         # sequences: 8 splits, 256 blocks, beat 13 and 16)
         rounds = -(-pairs * real // (sms * 2 if clustered else slots))
@@ -44,6 +44,24 @@ def decode_split(n_seqs: int, n_kv_heads: int, max_context: int, sms: int):
     best = min(close, key=lambda n: (blocks % n != 0, n))
     chunk = BLOCK_TOKENS * (-(-blocks // best))
     return chunk, -(-blocks * BLOCK_TOKENS // chunk)
+
+
+def decode_from_qkv(out, qkv, k_offset, v_offset, q_norm, k_norm, eps, cos_sin, pairing, ctx, store, n_heads, n_kv_heads,
+                    head_dim, scale, window, write_kv) -> bool:
+    """A decode step's attention straight from the q/k/v product's output: the kernel does the head norms,
+    the rotation and the cache write itself (one kernel and one boundary less a layer).  False where that
+    kernel does not take the case; the caller then runs the rotation kernel and ``run``."""
+    rope_half = 0 if cos_sin is None else cos_sin.shape[1]
+    if not (ctx.all_single and ctx.n_tokens <= 65535
+            and ops.attention_decode_takes_qkv(n_heads, n_kv_heads, head_dim, rope_half, pairing)):
+        return False
+    sms = ops.device_state(qkv.device)[2]
+    chunk, n_splits = decode_split(ctx.n_tokens, n_kv_heads, context_bucket(ctx.max_context), sms)
+    fused = ctx.n_tokens * n_kv_heads <= FUSED_COMBINE_MAX
+    ops.attention_decode_qkv(out, qkv, k_offset, v_offset, q_norm, k_norm, eps, cos_sin, store.k, store.v, ctx.tok_slot,
+                             ctx.tok_pos, store.block_table, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
+                             write_kv=write_kv, fused=fused)
+    return True
 
 
 def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window) -> bool:

@@ -1,7 +1,6 @@
 """Arrangements: how the parts of one layer are put together around the residual stream."""
 from __future__ import annotations
 
-from ..csrc import ops
 from .registry import register_part
 
 
@@ -39,15 +38,8 @@ def prenorm_residual(parts: LayerParts, x, ctx, stores, owns_cache: bool) -> Non
     """x += mixer(norm(x)); x += feed_forward(norm(x))   (crates/xrt-models/src/llama.rs:433-602).
     ``x`` is the float32 residual stream and is updated in place; the sums are 32-bit.  ``stores``
     maps a part's name to the cache storage it asked for."""
-    mask = ops.tuning().prefetch if ctx.n_tokens <= 64 else 0
-    if mask & 1:
-        ops.hint_prefetch(getattr(parts.mixer, "first_weight", None), 0, 48 << 20)
-    h = parts.mixer_norm.forward(x)
-    parts.mixer.forward(h, x, ctx, stores.get("mixer"), owns_cache)
-    if mask & 2:
-        ops.hint_prefetch(getattr(parts.ffn, "first_weight", None), 0, 32 << 20)
-    h = parts.ffn_norm.forward(x)
-    parts.ffn.forward(h, x, ctx)
+    parts.mixer.forward(parts.mixer_norm.forward(x), x, ctx, stores.get("mixer"), owns_cache)
+    parts.ffn.forward(parts.ffn_norm.forward(x), x, ctx)
 
 
 register_part("arrangement", "prenorm_residual", prenorm_residual)

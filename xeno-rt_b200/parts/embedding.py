@@ -42,7 +42,6 @@ class OutputHead:
 
     def __init__(self, params, weights, dtype, device):
         self.weight = weights["weight"]
-        self.first_weight = self.weight
 
     def forward(self, normed):
         return linear(normed, self.weight, out_dtype=torch.float32)

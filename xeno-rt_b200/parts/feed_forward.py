@@ -34,23 +34,17 @@ class SwiGLUFeedForward:
         if self.w_gate_up is None:  # tensors that came one by one
             self.w_gate_up = torch.cat([weights["gate"], weights["up"]], dim=0).contiguous()
         self.w_down = weights["down"]
-        self.first_weight = self.w_gate_up
         self.act_dtype = torch_dtype(dtype)
 
     def forward(self, h, residual, ctx):
         act = torch.empty((h.shape[0], self.inner), dtype=self.act_dtype, device=h.device)
         fused = False
-        mask = ops.tuning().prefetch if h.shape[0] <= 64 else 0
-        if mask & 64:
-            ops.hint_prefetch(self.w_down, 0, 32 << 20)
         if self.act_dtype == torch.bfloat16 and h.dtype == torch.bfloat16:
             from . import linear_bf16
             fused = linear_bf16.run_swiglu(act, h, self.w_gate_up, self.inner)
         if not fused:
             gate_up = linear(h, self.w_gate_up, out_dtype=torch.float32)
             ops.swiglu(act, gate_up)
-        if mask & 128:
-            ops.hint_prefetch(ctx.shared.get("next_weight"), 0, 48 << 20)
         linear(act, self.w_down, accumulate_into=residual)
 
 
