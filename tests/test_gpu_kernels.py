@@ -606,6 +606,46 @@ def test_attention_prefill_tcgen05_kernel(nh, nkv):
         at += new[s]
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 16])
+@pytest.mark.parametrize("width,inner,out_rows,norm_dtype", [(1032, 2760, 1536, torch.float32), (256, 520, 392, torch.bfloat16),
+                                                            (4096, 1024, 4096, torch.bfloat16)])
+def test_a_product_prepares_the_norm_that_follows_and_the_next_product_finishes_it(m, width, inner, out_rows, norm_dtype):
+    """residual += act . down^T by the cp.async kernel, which also leaves residual * norm weight in
+    bfloat16 and every row's partial sums of squares; then the tcgen05 few-row product of that with
+    another matrix, which multiplies row m by 1 / sqrt(mean square + eps).  Against the plain
+    functions (norm, then product), store and SwiGLU, and the residual against the plain sum."""
+    from xeno_rt_b200.csrc import ops as o
+    torch.manual_seed(m + width + inner)
+    eps = 1e-5
+    resid = torch.randn(m, width, device=DEV) * 2
+    act = (torch.randn(m, inner, device=DEV)).to(torch.bfloat16)
+    w_down = (torch.randn(width, inner, device=DEV) * 0.05).to(torch.bfloat16)
+    w_norm = (1 + 0.1 * torch.randn(width, device=DEV)).to(norm_dtype)
+    w_next = (torch.randn(2 * out_rows, width, device=DEV) * 0.05).to(torch.bfloat16)
+    want_resid = f64(resid) + f64(act) @ f64(w_down).T
+    x = resid.clone()
+    scaled = torch.full((m, width), 9.0, device=DEV, dtype=torch.bfloat16)
+    squares = torch.full((o.gemm_stream_norm_parts(m, width), m), 9.0, device=DEV)
+    o.gemm_stream(x, act, w_down, "accumulate", norm=(scaled, w_norm, squares))
+    assert rel(x, want_resid) < 1e-5
+    plain = resid.clone()
+    o.gemm_stream(plain, act, w_down, "accumulate")
+    assert torch.equal(x, plain)  # the residual itself is what the product without the norm writes
+    assert rel(scaled, f64(x) * f64(w_norm)) < 5e-3
+    assert rel(squares.sum(0), (f64(x) ** 2).sum(1)) < 1e-5
+    normed = pm.rmsnorm(f64(x), f64(w_norm), eps)
+    out = torch.empty(m, 2 * out_rows, device=DEV)
+    o.gemm_decode_tcgen05(out, scaled, w_next, "store", squares=squares, eps=eps)
+    assert rel(out, normed @ f64(w_next).T) < 6e-3
+    act2 = torch.empty(m, out_rows, device=DEV, dtype=torch.bfloat16)
+    o.gemm_decode_tcgen05(act2, scaled, w_next, "swiglu", up_rows=out_rows, squares=squares, eps=eps)
+    gate_up = normed @ f64(w_next).T
+    assert rel(act2, pm.swiglu(gate_up[:, :out_rows], gate_up[:, out_rows:])) < 1.2e-2
+    o.check_error_flag(DEV)
+    with pytest.raises(Exception):
+        o.gemm_stream(x, act, w_down, "store", norm=(scaled, w_norm, squares))
+
+
 def test_attention_prefill_tcgen05_scores_that_jump():
     """The kernel takes its exponents against a reference value that moves only when a row's maximum
     has outgrown it by more than 8 (in base 2), and then rescales what it has accumulated.  Here the

@@ -234,7 +234,8 @@ def test_a_step_fed_with_ids_on_the_device_gives_the_logits_of_the_same_ids_from
 
 VARIANTS = [{"decode_gemm": "stream"}, {"decode_gemm": "tcgen05"}, {"decode_gemm": "tcgen05", "decode_gemm_clusters": False},
             {"decode_attention": "nocluster"}, {"decode_attention": "cp"}, {"decode_attention": "rows"},
-            {"prefill_attention": "mma"}, {"gemm_tile_rows": 128}, {"gemm_tile_rows": 256}, {"pdl": False}]
+            {"prefill_attention": "mma"}, {"gemm_tile_rows": 128}, {"gemm_tile_rows": 256}, {"pdl": False},
+            {"pending_norm": "force"}, {"pending_norm": "off"}, {"decode_cluster_pairs": 0}]
 
 
 @pytest.mark.parametrize("variant", VARIANTS, ids=lambda v: ",".join(f"{k}={x}" for k, x in v.items()))

@@ -109,12 +109,24 @@ struct DecodeGemmShape {
   int clustered;     // the splits of a tile are one cluster; one item a block
 };
 
+// The RMSNorm of this product's input, when the product before it prepared it (gemm_stream.cu's head has
+// the arithmetic): X is then residual * norm weight, `squares` holds `parts` partial sums of squares for
+// every batch row ([parts, M]), and the epilogue multiplies batch row m's results by
+// 1 / sqrt(sum of its parts / width + eps).  The parts are added in a fixed order, in 32-bit, by the
+// epilogue warps while the weights stream.
+struct RowScale {
+  const float* squares = nullptr;
+  int parts = 0;
+  int width = 1;
+  float eps = 0.f;
+};
+
 // MODE 0: store, 1: add into float out, 2: SwiGLU.
 template <int MODE, typename TO>
 __global__ void __launch_bounds__(DG_THREADS, 1)
 gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                            TO* __restrict__ out, float* __restrict__ partial, int* __restrict__ counters,
-                           const DecodeGemmShape shape, int* __restrict__ error_flag) {
+                           const DecodeGemmShape shape, int* __restrict__ error_flag, const RowScale scale) {
   constexpr int GROUPS = MODE == 2 ? 2 : 1;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -129,7 +141,8 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
-  float* recv = reinterpret_cast<float*>(smem + (size_t)stages * stage_bytes + 512);  // the cluster's sums for this block's rows
+  float* row_inv = reinterpret_cast<float*>(smem + (size_t)stages * stage_bytes + 512);  // [nb] when the input's norm is pending
+  float* recv = reinterpret_cast<float*>(smem + (size_t)stages * stage_bytes + 1024);    // the cluster's sums for this block's rows
 
   pdl_trigger();
   if (shape.clustered) dg_cluster_arrive();
@@ -271,6 +284,21 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     // ---------------------------------------------------------------- epilogue
     if (shape.clustered) dg_cluster_wait();  // every block of the cluster runs: its shared memory may be written
     pdl_wait();  // the output (and the residual it adds into) belongs to the step
+    if (scale.squares != nullptr) {
+      // 1 / rms of every batch row from the parts the product before this one left: sixteen lanes a row
+      // take every sixteenth part each and meet in a fixed order
+      const int tid = threadIdx.x - 64, sub = tid & 15;
+      for (int m = tid >> 4; m < shape.nb; m += 8) {
+        float sum = 0.f;
+        if (m < shape.M)
+          for (int p = sub; p < scale.parts; p += 16) sum += __ldcg(scale.squares + (size_t)p * shape.M + m);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (sub == 0) row_inv[m] = m < shape.M ? 1.0f / sqrtf(sum / (float)scale.width + scale.eps) : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+    const bool scaled = scale.squares != nullptr;
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;  // weight row inside the tile = TMEM lane
     int item_i = 0;
@@ -307,8 +335,9 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             for (int j = 0; j < 16; ++j) {
               const int m = c + j;
               if (m < shape.M) {
-                float val = __uint_as_float(v[j]);
-                if (MODE == 2) val = (val / (1.0f + expf(-val))) * __uint_as_float(u[j]);
+                const float inv = scaled ? row_inv[m] : 1.f;
+                float val = __uint_as_float(v[j]) * inv;
+                if (MODE == 2) val = (val / (1.0f + expf(-val))) * (__uint_as_float(u[j]) * inv);
                 TO* dst = out + (size_t)m * shape.ldo + n;
                 if (MODE == 1) *dst = from_float<TO>(old[j] + val);
                 else *dst = from_float<TO>(val);
@@ -400,8 +429,9 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 if (m0 + j < shape.M) {
-                  float val = sums[0][j];
-                  if (MODE == 2) val = (val / (1.0f + expf(-val))) * sums[GROUPS - 1][j];
+                  const float inv = scaled ? row_inv[m0 + j] : 1.f;
+                  float val = sums[0][j] * inv;
+                  if (MODE == 2) val = (val / (1.0f + expf(-val))) * (sums[GROUPS - 1][j] * inv);
                   TO* dst = out + (size_t)(m0 + j) * shape.ldo + n;
                   if (MODE == 1) *dst = from_float<TO>(old[j] + val);
                   else *dst = from_float<TO>(val);
@@ -434,13 +464,14 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       const int slot_floats = acc_cols * per;
       constexpr int UNROLL = 4;
       for (int base = threadIdx.x - 64; base < total; base += 128 * UNROLL) {
-        float old[UNROLL], sums[UNROLL][GROUPS];
+        float old[UNROLL], sums[UNROLL][GROUPS], inv[UNROLL];
         size_t at[UNROLL];
         bool live[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           const int idx = base + u * 128;
           const int m = idx / rows_here, local = idx - m * rows_here;
+          inv[u] = (scale.squares != nullptr && idx < total) ? row_inv[m] : 1.f;
           const int n = tile * DG_ROWS + row_lo + local;
           live[u] = idx < total && n < shape.N;
           at[u] = (size_t)m * shape.ldo + n;
@@ -458,8 +489,8 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           if (live[u]) {
-            float val = sums[u][0];
-            if (MODE == 2) val = (val / (1.0f + expf(-val))) * sums[u][GROUPS - 1];
+            float val = sums[u][0] * inv[u];
+            if (MODE == 2) val = (val / (1.0f + expf(-val))) * (sums[u][GROUPS - 1] * inv[u]);
             if (MODE == 1) out[at[u]] = from_float<TO>(old[u] + val);
             else out[at[u]] = from_float<TO>(val);
           }
@@ -477,6 +508,10 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 }
 
 }  // namespace xrt
+XRT_EXPORT int xrt_gemm_decode_tcgen05_normed(void* out, const void* x, const void* w, float* partial, int* counters,
+                                              int M, int N, int K, int ldx, int ldo, int w_rows, int out_dtype, int mode,
+                                              int up_rows, int sm_count, int* error_flag, const float* squares,
+                                              int square_parts, float eps, cudaStream_t stream);
 XRT_TL_EXPORT(gemm_decode)
 namespace xrt {
 
@@ -538,7 +573,8 @@ inline bool decode_gemm_clusters_wanted() { return tuning().decode_gemm_clusters
 
 template <int MODE, typename TO>
 int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorMap& map_w, const CUtensorMap& map_x,
-                       DecodeGemmShape shape, int smem, int blocks, int sm_count, int* error_flag, cudaStream_t stream) {
+                       DecodeGemmShape shape, int smem, int blocks, int sm_count, int* error_flag, const RowScale& scale,
+                       cudaStream_t stream) {
   auto kernel = gemm_decode_tcgen05_kernel<MODE, TO>;
   static int allowed = 0;
   if (smem > allowed) {
@@ -572,7 +608,7 @@ int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorM
   }
   if (!shape.clustered) {
     launch_kernel(kernel, dim3(blocks), dim3(DG_THREADS), (size_t)smem, stream, map_w, map_x, (TO*)out, partial, counters,
-                  shape, error_flag);
+                  shape, error_flag, scale);
     return launch_status();
   }
   cudaLaunchConfig_t config = {};
@@ -592,7 +628,7 @@ int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorM
   ++n_attrs;
   config.attrs = attrs;
   config.numAttrs = n_attrs;
-  cudaLaunchKernelEx(&config, kernel, map_w, map_x, (TO*)out, partial, counters, shape, error_flag);
+  cudaLaunchKernelEx(&config, kernel, map_w, map_x, (TO*)out, partial, counters, shape, error_flag, scale);
   return launch_status();
 }
 
@@ -628,6 +664,20 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05_plan(int M, int N, int K, int mode, int s
 XRT_EXPORT int xrt_gemm_decode_tcgen05(void* out, const void* x, const void* w, float* partial, int* counters, int M,
                                        int N, int K, int ldx, int ldo, int w_rows, int out_dtype, int mode,
                                        int up_rows, int sm_count, int* error_flag, cudaStream_t stream) {
+  return xrt_gemm_decode_tcgen05_normed(out, x, w, partial, counters, M, N, K, ldx, ldo, w_rows, out_dtype, mode, up_rows,
+                                        sm_count, error_flag, nullptr, 0, 0.f, stream);
+}
+
+// The same for an input whose RMSNorm the product before it prepared (xrt_gemm_stream_norm): x is the
+// residual times the norm weight, squares = float32 [square_parts, M] its partial sums of squares;
+// every batch row's result is multiplied by 1 / sqrt(sum of its parts / K + eps).  squares null: as above.
+XRT_EXPORT int xrt_gemm_decode_tcgen05_normed(void* out, const void* x, const void* w, float* partial, int* counters,
+                                              int M, int N, int K, int ldx, int ldo, int w_rows, int out_dtype, int mode,
+                                              int up_rows, int sm_count, int* error_flag, const float* squares,
+                                              int square_parts, float eps, cudaStream_t stream) {
+  if (squares != nullptr && (square_parts <= 0 || mode == 1)) return XRT_ERR_ARGUMENT;
+  xrt::RowScale scale;
+  scale.squares = squares; scale.parts = square_parts; scale.width = K; scale.eps = eps;
   if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldo < N || mode < 0 || mode > 2 || sm_count <= 0) return XRT_ERR_ARGUMENT;
   if (mode == 1 && out_dtype != XRT_F32) return XRT_ERR_ARGUMENT;
   if (mode == 2 ? w_rows < up_rows + N : w_rows < N) return XRT_ERR_ARGUMENT;
@@ -649,7 +699,7 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05(void* out, const void* x, const void* w, 
   // splits x accumulator columns x ceil(128 / splits) floats
   const int per = shape.splits > 1 ? (xrt::DG_ROWS + shape.splits - 1) / shape.splits : 0;
   const int recv_bytes = shape.splits * groups * shape.nb * per * 4;
-  const int budget = 200 * 1024 - recv_bytes;
+  const int budget = 200 * 1024 - 512 - recv_bytes;
   shape.stages = budget / stage_bytes;
   if (shape.stages > 12) shape.stages = 12;
   if (shape.stages < 2) return XRT_ERR_UNSUPPORTED;
@@ -659,20 +709,20 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05(void* out, const void* x, const void* w, 
   shape.tmem_cols = cols;
   shape.clustered = 0;
   if (shape.splits > 1 && (partial == nullptr || counters == nullptr)) return XRT_ERR_ARGUMENT;
-  const int smem = shape.stages * stage_bytes + 512 + recv_bytes + 1024;
+  const int smem = shape.stages * stage_bytes + 1024 + recv_bytes + 1024;
   const int items = shape.tiles * shape.splits;
   const int blocks = items < sm_count ? items : sm_count;
   CUtensorMap map_w, map_x;
   if (!xrt::dg_make_map(&map_w, w, w_rows, K, K, xrt::DG_ROWS) || !xrt::dg_make_map(&map_x, x, M, K, ldx, shape.nb))
     return XRT_ERR_UNSUPPORTED;
   if (mode == 1)
-    return xrt::launch_decode_gemm<1, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, stream);
+    return xrt::launch_decode_gemm<1, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, stream);
   if (mode == 2) {
     if (out_dtype == XRT_BF16)
-      return xrt::launch_decode_gemm<2, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, stream);
-    return xrt::launch_decode_gemm<2, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, stream);
+      return xrt::launch_decode_gemm<2, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, stream);
+    return xrt::launch_decode_gemm<2, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, stream);
   }
   if (out_dtype == XRT_BF16)
-    return xrt::launch_decode_gemm<0, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, stream);
-  return xrt::launch_decode_gemm<0, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, stream);
+    return xrt::launch_decode_gemm<0, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, stream);
+  return xrt::launch_decode_gemm<0, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, stream);
 }

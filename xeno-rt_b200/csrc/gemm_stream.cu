@@ -17,6 +17,14 @@
 // MMA's M (16 a tile), the weight rows its N.  The warps' partial sums meet in shared memory and
 // are added in warp order: a row's result does not depend on the number of rows M.
 // Measured on a B200 with M = 8: 5.97 TB/s on the output matrix (1.05 GB), 5.2 TB/s on gate/up.
+//
+// A product that adds into the residual stream can also prepare the RMSNorm that follows it
+// (crates/xrt-kernels/src/cpu/rmsnorm.rs:26-43), so that no norm kernel has to run between two
+// products of a decode step: beside the new residual it writes residual * norm weight in bfloat16
+// (the next product's operand) and, for every batch row, the sum of squares of the new residual over
+// this block's weight rows (one float a block and batch row, summed by the next product in block
+// order).  That product multiplies its result by 1 / sqrt(mean square + eps): W . ((x * inv) * w) =
+// inv * (W . (x * w)), with the statistics in 32-bit from the 32-bit residual.
 #include "common.cuh"
 
 namespace xrt {
@@ -38,11 +46,20 @@ __device__ __forceinline__ void gs_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// What a residual-adding product writes for the norm that follows: see the file's head.
+struct NormEmit {
+  __nv_bfloat16* scaled = nullptr;  // [M, ld] bfloat16: new residual * weight
+  const void* weight = nullptr;     // [N] norm weight, 32-bit or bfloat16
+  float* squares = nullptr;         // [blocks, M]: this block's sum of squares of each batch row
+  int ld = 0;
+  int weight_dtype = XRT_F32;
+};
+
 // MODE 0: store, 1: add into float out, 2: SwiGLU (two groups of rows: gate and up)
 template <int M_TILES, int MODE, int GS_STAGES, int ROW_GROUPS, typename TO>
 __global__ void __launch_bounds__(GS_THREADS, (M_TILES >= 4 ? 2 : 1))
 gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                   int M, int N, int K, int ldx, int ldo, long long up_offset) {
+                   int M, int N, int K, int ldx, int ldo, long long up_offset, const NormEmit emit) {
   // ROW_GROUPS groups of 8 weight rows a block (SwiGLU: as many gate groups and as many up groups);
   // every X fragment a warp loads is used for all of them, which is what keeps the L1 traffic of
   // many batch rows below the shared-memory traffic of the weights
@@ -56,6 +73,13 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
 
   pdl_trigger();
   if (threadIdx.x == 0) XRT_TL(30);
+  // the weight of the norm that follows never changes: this thread's element of it is on its way now
+  float emit_w = 0.f;
+  if (MODE == 1 && emit.scaled != nullptr) {
+    const int wrow = min(blockIdx.x * (ROW_GROUPS * GS_ROWS) + (int)(threadIdx.x % (ROW_GROUPS * GS_ROWS)), N - 1);
+    emit_w = emit.weight_dtype == XRT_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(emit.weight)[wrow])
+                                           : reinterpret_cast<const float*>(emit.weight)[wrow];
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * BLOCK_ROWS;
   const int n_slabs = (K + GS_SLAB - 1) / GS_SLAB;
@@ -157,12 +181,12 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
     }
   if (threadIdx.x == 0) XRT_TL(32);
   __syncthreads();
-  for (int e = threadIdx.x; e < M_TILES * 16 * BLOCK_ROWS; e += blockDim.x) {
+  for (int e = threadIdx.x; e < M_TILES * 16 * BLOCK_ROWS; e += blockDim.x) {  // the same trips for a whole warp
     const int nb = e % BLOCK_ROWS, m = e / BLOCK_ROWS;
     const int rg = nb / GS_ROWS, n = nb % GS_ROWS;
     const int mt = m / 16, mr = m % 16;
     const int row = row0 + nb;
-    if (m >= M || row >= N) continue;
+    const bool live = m < M && row < N;
     auto total = [&](int gr) {
       float sum = 0.f;
 #pragma unroll
@@ -170,18 +194,33 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
         sum += partial[((((size_t)ww * GROUPS + gr) * M_TILES + mt) * 16 + mr) * P_ROW + n];
       return sum;
     };
-    const float first = total(rg);
-    TO* dst = out + (size_t)m * ldo + row;
-    if (MODE == 2) *dst = from_float<TO>((first / (1.0f + expf(-first))) * total(ROW_GROUPS + rg));
-    else if (MODE == 1) *dst = from_float<TO>(to_float(*dst) + first);
-    else *dst = from_float<TO>(first);
+    float square = 0.f;
+    if (live) {
+      const float first = total(rg);
+      TO* dst = out + (size_t)m * ldo + row;
+      if (MODE == 2) *dst = from_float<TO>((first / (1.0f + expf(-first))) * total(ROW_GROUPS + rg));
+      else if (MODE == 1) {
+        const float updated = to_float(*dst) + first;
+        *dst = from_float<TO>(updated);
+        if (emit.scaled != nullptr) {
+          emit.scaled[(size_t)m * emit.ld + row] = __float2bfloat16_rn(updated * emit_w);  // e % BLOCK_ROWS == threadIdx.x % BLOCK_ROWS
+          square = updated * updated;
+        }
+      } else *dst = from_float<TO>(first);
+    }
+    if (MODE == 1 && emit.squares != nullptr) {
+      // the block's rows of one batch row sit in BLOCK_ROWS neighbouring lanes: summed in a fixed order
+#pragma unroll
+      for (int o = 1; o < BLOCK_ROWS; o <<= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
+      if (nb == 0 && m < M) emit.squares[(size_t)blockIdx.x * M + m] = square;
+    }
   }
   if (threadIdx.x == 0) XRT_TL(33);
 }
 
 template <int M_TILES, int MODE, int GS_STAGES, int ROW_GROUPS, typename TO>
 int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
-                         long long up_offset, cudaStream_t stream) {
+                         long long up_offset, const NormEmit& emit, cudaStream_t stream) {
   constexpr int GROUPS = ROW_GROUPS * (MODE == 2 ? 2 : 1);
   constexpr int RING_BYTES = GS_STAGES * GROUPS * GS_ROWS * GS_ROW_BYTES;
   constexpr int PARTIAL_BYTES = GS_WARPS * GROUPS * M_TILES * 16 * (GS_ROWS + 1) * (int)sizeof(float);
@@ -195,7 +234,7 @@ int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, 
   }
   const int blocks = (N + ROW_GROUPS * GS_ROWS - 1) / (ROW_GROUPS * GS_ROWS);
   launch_kernel(kernel, dim3(blocks), dim3(GS_THREADS), SMEM, stream, (TO*)out, (const __nv_bfloat16*)x,
-                (const __nv_bfloat16*)w, M, N, K, ldx, ldo, up_offset);
+                (const __nv_bfloat16*)w, M, N, K, ldx, ldo, up_offset, emit);
   return launch_status();
 }
 
@@ -204,42 +243,70 @@ int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, 
 // 5) and lose on others; over a whole decode step of 8 sequences 3 stages is the fastest.
 template <int M_TILES, int MODE, typename TO>
 int launch_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, long long up_offset,
-                  cudaStream_t stream) {
+                  const NormEmit& emit, cudaStream_t stream) {
   // more than 32 batch rows: two row groups a block halve the X traffic per weight byte
   constexpr int RG = M_TILES >= 4 ? 2 : 1;
-  return launch_stream_staged<M_TILES, MODE, 3, RG, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, stream);
+  return launch_stream_staged<M_TILES, MODE, 3, RG, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, stream);
 }
 
 template <int M_TILES>
 int dispatch_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, int out_dtype,
-                    int mode, long long up_offset, cudaStream_t stream) {
-  if (mode == 1) return launch_stream<M_TILES, 1, float>(out, x, w, M, N, K, ldx, ldo, 0, stream);
+                    int mode, long long up_offset, const NormEmit& emit, cudaStream_t stream) {
+  if (mode == 1) return launch_stream<M_TILES, 1, float>(out, x, w, M, N, K, ldx, ldo, 0, emit, stream);
   if (mode == 2) {
     if (out_dtype == XRT_BF16)
-      return launch_stream<M_TILES, 2, __nv_bfloat16>(out, x, w, M, N, K, ldx, ldo, up_offset, stream);
-    return launch_stream<M_TILES, 2, float>(out, x, w, M, N, K, ldx, ldo, up_offset, stream);
+      return launch_stream<M_TILES, 2, __nv_bfloat16>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, stream);
+    return launch_stream<M_TILES, 2, float>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, stream);
   }
-  if (out_dtype == XRT_BF16) return launch_stream<M_TILES, 0, __nv_bfloat16>(out, x, w, M, N, K, ldx, ldo, 0, stream);
-  return launch_stream<M_TILES, 0, float>(out, x, w, M, N, K, ldx, ldo, 0, stream);
+  if (out_dtype == XRT_BF16) return launch_stream<M_TILES, 0, __nv_bfloat16>(out, x, w, M, N, K, ldx, ldo, 0, emit, stream);
+  return launch_stream<M_TILES, 0, float>(out, x, w, M, N, K, ldx, ldo, 0, emit, stream);
 }
 
 }  // namespace xrt
 
 XRT_TL_EXPORT(gemm_stream)
 
+XRT_EXPORT int xrt_gemm_stream_norm(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
+                                    int out_dtype, int mode, int up_rows, void* scaled, int ld_scaled,
+                                    const void* norm_weight, int norm_dtype, float* squares, cudaStream_t stream);
+
 // x: bfloat16 [M, K] with row stride ldx (a multiple of 8); w: bfloat16 [N, K] contiguous, K a
 // multiple of 8; out: [M, N] with row stride ldo.  mode 0 stores, 1 adds into a float32 out, 2 computes
 // silu(x . W[n]) * (x . W[n + up_rows]) for n < N.  M is at most 64.
 XRT_EXPORT int xrt_gemm_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
                                int out_dtype, int mode, int up_rows, cudaStream_t stream) {
+  return xrt_gemm_stream_norm(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_rows, nullptr, 0, nullptr, XRT_F32, nullptr,
+                              stream);
+}
+
+// How many floats a batch row `squares` holds one of: the blocks of the launch (M at most 16).
+XRT_EXPORT int xrt_gemm_stream_norm_blocks(int M, int N) {
+  if (M <= 0 || N <= 0 || M > 16) return XRT_ERR_UNSUPPORTED;
+  return (N + xrt::GS_ROWS - 1) / xrt::GS_ROWS;
+}
+
+// The same; with mode 1 and `scaled` not null the product also prepares the norm that follows it (see
+// the file's head): scaled = bfloat16 [M, ld_scaled] receives (new residual) * norm_weight ([N], in
+// norm_dtype), squares = float32 [xrt_gemm_stream_norm_blocks(M, N), M] the blocks' sums of squares.
+// Only for M <= 16 (one group of weight rows a block).
+XRT_EXPORT int xrt_gemm_stream_norm(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
+                                    int out_dtype, int mode, int up_rows, void* scaled, int ld_scaled,
+                                    const void* norm_weight, int norm_dtype, float* squares, cudaStream_t stream) {
   if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldo < N || mode < 0 || mode > 2) return XRT_ERR_ARGUMENT;
   if (mode == 1 && out_dtype != XRT_F32) return XRT_ERR_ARGUMENT;
   if (out_dtype != XRT_F32 && out_dtype != XRT_BF16) return XRT_ERR_UNSUPPORTED;
   if (K % 8 != 0 || ldx % 8 != 0 || M > 64) return XRT_ERR_UNSUPPORTED;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return XRT_ERR_UNSUPPORTED;
+  xrt::NormEmit emit;
+  if (scaled != nullptr) {
+    if (mode != 1 || norm_weight == nullptr || squares == nullptr || ld_scaled < N) return XRT_ERR_ARGUMENT;
+    if (M > 16 || (norm_dtype != XRT_F32 && norm_dtype != XRT_BF16)) return XRT_ERR_UNSUPPORTED;
+    emit.scaled = (__nv_bfloat16*)scaled; emit.weight = norm_weight; emit.squares = squares;
+    emit.ld = ld_scaled; emit.weight_dtype = norm_dtype;
+  }
   if (M == 0) return XRT_OK;
   const long long up_offset = (long long)up_rows * K;
-  if (M <= 16) return xrt::dispatch_stream<1>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, stream);
-  if (M <= 32) return xrt::dispatch_stream<2>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, stream);
-  return xrt::dispatch_stream<4>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, stream);
+  if (M <= 16) return xrt::dispatch_stream<1>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, emit, stream);
+  if (M <= 32) return xrt::dispatch_stream<2>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, emit, stream);
+  return xrt::dispatch_stream<4>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, emit, stream);
 }

@@ -35,6 +35,8 @@ _SIGNATURES = {
     "xrt_attention_reference": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
     "xrt_gemm_reference": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "xrt_gemm_stream_norm": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P, _P],
+    "xrt_gemm_decode_tcgen05_normed": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P],
     "xrt_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_gemm_decode_tcgen05": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_attention_decode_fused": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P],
@@ -70,6 +72,8 @@ def library():
                 fn.restype = _I
             lib.xrt_attention_decode_fused_max_splits.argtypes = [_I, _I]
             lib.xrt_attention_decode_fused_max_splits.restype = _I
+            lib.xrt_gemm_stream_norm_blocks.argtypes = [_I, _I]
+            lib.xrt_gemm_stream_norm_blocks.restype = _I
             lib.xrt_set_tuning.argtypes = [_I, _I]
             lib.xrt_set_tuning.restype = _I
             lib.xrt_gemm_decode_tcgen05_scratch.argtypes = [_I, _I, _I, _I, _I]
@@ -97,6 +101,9 @@ class Tuning:
     ``decode_attention`` "auto", "rows" (query heads as MMA rows), "cp" (cp.async tiles), "nocluster"
     ``prefill_attention`` "auto" or "mma" (the mma.sync kernel also where the tcgen05 one applies)
     ``gemm_tile_rows``   0 (auto), 128 or 256: the tile of the prompt product
+    ``pending_norm``     "auto": a few-row product that adds into the residual prepares the norm that follows
+                         it where the next product runs on the kernel that can finish it; "off": never
+                         (a norm kernel runs); "force": wherever the kernels allow, whatever the sizes
     ``decode_cluster_pairs``  decode attention merges a (token, kv head)'s splits as one thread-block
                          cluster up to so many pairs a step; beyond, partials and a second kernel
     """
@@ -108,6 +115,7 @@ class Tuning:
     prefill_attention: str = "auto"
     gemm_tile_rows: int = 0
     decode_cluster_pairs: int = 128
+    pending_norm: str = "auto"
 
 
 _DECODE_ATTENTION = {"auto": 0, "rows": 1, "cp": 2, "nocluster": 3}
@@ -125,6 +133,8 @@ def set_tuning(new: Tuning) -> None:
         raise KernelError(f"tuning: decode_gemm {new.decode_gemm!r} is not auto, stream or tcgen05")
     if new.decode_attention not in _DECODE_ATTENTION:
         raise KernelError(f"tuning: decode_attention {new.decode_attention!r} is not one of {sorted(_DECODE_ATTENTION)}")
+    if new.pending_norm not in ("auto", "off", "force"):
+        raise KernelError(f"tuning: pending_norm {new.pending_norm!r} is not auto, off or force")
     if new.prefill_attention not in ("auto", "mma"):
         raise KernelError(f"tuning: prefill_attention {new.prefill_attention!r} is not auto or mma")
     lib = library()
@@ -368,9 +378,11 @@ def gemm_decode_tcgen05_fill(sms: int, m: int, n: int, k: int, mode: str):
     return _decode_plans[key]
 
 
-def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
+def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, squares=None, eps: float = 0.0) -> None:
     """bfloat16 product for at most 128 rows on the tcgen05 tensor cores with swapped operands:
-    the weight is streamed once by TMA, K is split across blocks and summed in split order."""
+    the weight is streamed once by TMA, K is split across blocks and summed in split order.
+    ``squares`` (float32 [parts, rows], from ``gemm_stream(..., norm=...)``): ``x`` is a residual times
+    its norm weight, and every row's result is multiplied by 1 / sqrt(sum of its parts / K + eps)."""
     m, k = x.shape
     n = out.shape[1]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -387,10 +399,13 @@ def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0) -> Non
     lib = library()
     floats = lib.xrt_gemm_decode_tcgen05_scratch(m, n, k, code, sms)
     partial = torch.empty(floats, dtype=torch.float32, device=x.device) if floats else None
-    _check(lib.xrt_gemm_decode_tcgen05(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), _ptr(partial, "partial"),
-                                       counters.data_ptr(), m, n, k, x.stride(0), out.stride(0), w.shape[0],
-                                       _code(out.dtype), code, up_rows, sms, flag.data_ptr(), _stream()),
-           "gemm_decode_tcgen05")
+    if squares is not None and (mode == "accumulate" or squares.dim() != 2 or squares.shape[1] != m):
+        raise KernelError("gemm_decode_tcgen05: squares must be [parts, rows], and not with accumulate")
+    _check(lib.xrt_gemm_decode_tcgen05_normed(
+        out.data_ptr(), x.data_ptr(), _ptr(w, "w"), _ptr(partial, "partial"), counters.data_ptr(), m, n, k, x.stride(0),
+        out.stride(0), w.shape[0], _code(out.dtype), code, up_rows, sms, flag.data_ptr(),
+        _ptr(squares, "squares", torch.float32), 0 if squares is None else squares.shape[0], float(eps), _stream()),
+        "gemm_decode_tcgen05")
 
 
 def gemm_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
@@ -412,9 +427,23 @@ def gemm_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
            "gemm_tcgen05")
 
 
-def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
+STREAM_NORM_MAX_ROWS = 16
+
+
+def gemm_stream_norm_parts(m: int, n: int) -> int:
+    """How many partial sums of squares a row ``gemm_stream(..., norm=...)`` leaves (host arithmetic)."""
+    parts = library().xrt_gemm_stream_norm_blocks(int(m), int(n))
+    if parts <= 0:
+        raise KernelError("gemm_stream: a following norm can be prepared for at most 16 rows")
+    return parts
+
+
+def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0, norm=None) -> None:
     """bfloat16 product for at most 64 rows that streams the weight once; ``mode`` is "store",
-    "accumulate" (into a float32 out) or "swiglu" (out[m, n] = silu(x . w[n]) * (x . w[n + up_rows]))."""
+    "accumulate" (into a float32 out) or "swiglu" (out[m, n] = silu(x . w[n]) * (x . w[n + up_rows])).
+    ``norm`` = (scaled, weight, squares) with "accumulate" and at most 16 rows: the product also
+    prepares the RMSNorm that follows it: ``scaled`` (bfloat16 [m, n]) receives the new residual times
+    ``weight`` ([n]), ``squares`` (float32 [gemm_stream_norm_parts(m, n), m]) its sums of squares."""
     m, k = x.shape
     n = out.shape[1]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -425,8 +454,18 @@ def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
     if x.stride(1) != 1 or out.stride(1) != 1 or not x.is_cuda or not out.is_cuda:
         raise KernelError("gemm_stream: rows must be contiguous and on a CUDA device")
     code = {"store": 0, "accumulate": 1, "swiglu": 2}[mode]
-    _check(_kernels().xrt_gemm_stream(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
-                                     _code(out.dtype), code, up_rows, _stream()), "gemm_stream")
+    if norm is None:
+        _check(_kernels().xrt_gemm_stream(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
+                                         _code(out.dtype), code, up_rows, _stream()), "gemm_stream")
+        return
+    scaled, weight, squares = norm
+    if (mode != "accumulate" or scaled.shape != (m, n) or scaled.stride(1) != 1 or weight.numel() != n
+            or tuple(squares.shape) != (gemm_stream_norm_parts(m, n), m)):
+        raise KernelError("gemm_stream: the buffers of the following norm do not fit the product")
+    _check(_kernels().xrt_gemm_stream_norm(
+        out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0), _code(out.dtype), code, up_rows,
+        _ptr(scaled, "scaled", torch.bfloat16), scaled.stride(0), _ptr(weight, "weight"), _code(weight.dtype),
+        _ptr(squares, "squares", torch.float32), _stream()), "gemm_stream")
 
 
 def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int,

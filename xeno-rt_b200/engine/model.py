@@ -54,6 +54,12 @@ class Model:
         for layer in self.layers:
             parts += list(layer.values())
         self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
+        # what each place of the schedule is followed by: the first norm of the layer that runs next and
+        # the part that takes its result, for arrangements that say so (see parts/block.py)
+        firsts = [getattr(fn, "first_norm", None) for fn in self.arrangements]
+        order = [firsts[place.layer](self.layers[place.layer]) if firsts[place.layer] else None
+                 for place in spec.schedule]
+        self._next_layer = order[1:] + [None]
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -144,7 +150,9 @@ class Model:
         for i, place in enumerate(self.spec.schedule):
             owns = place.cache_from is None
             stores = cache.store(i if owns else place.cache_from) or {}
+            ctx.shared["next_layer"] = self._next_layer[i]
             self.arrangements[place.layer](self.layers[place.layer], x, ctx, stores, owns)
+        ctx.pending = ctx.then_norm = None
         if want_rows is None or want_rows.numel() == 0:
             return None
         return self.lm_head.forward(self.final_norm.forward(x, want_rows))

@@ -75,8 +75,18 @@ class GroupedQueryAttention:
     def cache_need(self):
         return KVNeed(self.n_kv_heads, self.head_dim, self.window)
 
+    def takes_pending_norm(self, rows: int, device) -> bool:
+        """Whether the first product of ``forward`` can finish a norm that the part before prepared."""
+        if self.dtype is not DType.BF16:
+            return False
+        from . import linear_bf16
+        return linear_bf16.takes_pending(rows, self.w_qkv.shape[0], self.width, "store", device)
+
     def forward(self, h, residual, ctx, store, owns_cache=True):
         n = h.shape[0]
+        then_norm = getattr(ctx, "then_norm", None)  # for this part's last product only
+        if then_norm is not None:
+            ctx.then_norm = None
         qkv = linear(h, self.w_qkv if owns_cache else self.w_q, out_dtype=torch.float32)
         window = int(self.window) if self.window else 0
         pairing = getattr(self.position, "pairing", "split_half")
@@ -96,7 +106,10 @@ class GroupedQueryAttention:
                                  self.k_norm, self.eps, cos_sin, ctx.tok_slot, ctx.tok_pos, store.block_table,
                                  self.n_heads, self.n_kv_heads, self.head_dim, write_kv=owns_cache, pairing=pairing)
             self.attend(attended, q, ctx, store)
-        linear(attended, self.w_o, accumulate_into=residual)
+        if then_norm is not None:
+            _, ctx.pending = linear(attended, self.w_o, accumulate_into=residual, then_norm=then_norm)
+        else:
+            linear(attended, self.w_o, accumulate_into=residual)
 
     def attend(self, out, q, ctx, store):
         window = int(self.window) if self.window else 0

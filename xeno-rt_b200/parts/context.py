@@ -38,6 +38,16 @@ class StepContext:
     captured: bool = False  # the step is being captured into (or replayed from) a CUDA graph:
     #                         launch shapes must not depend on the sequences' lengths
     shared: dict = field(default_factory=dict)
+    # A part that adds into the residual stream may prepare the norm that follows it: the arrangement
+    # names that norm in ``then_norm`` before it calls the part, and a part that did so leaves the
+    # result (a parts.norm.PendingNorm) in ``pending``.  Parts that know nothing of this leave both alone.
+    then_norm: object = None
+    pending: object = None
+
+    def take_pending(self, norm):
+        """The prepared result of ``norm`` if the part that ran last left one, else None."""
+        pending, self.pending, self.then_norm = self.pending, None, None
+        return pending if pending is not None and pending.norm is norm else None
 
 
 def context_bucket(max_context: int) -> int:

@@ -36,6 +36,13 @@ class SwiGLUFeedForward:
         self.w_down = weights["down"]
         self.act_dtype = torch_dtype(dtype)
 
+    def takes_pending_norm(self, rows: int, device) -> bool:
+        """Whether the first product of ``forward`` can finish a norm that the part before prepared."""
+        if self.act_dtype != torch.bfloat16:
+            return False
+        from . import linear_bf16
+        return linear_bf16.takes_pending(rows, self.inner, self.width, "swiglu", device)
+
     def forward(self, h, residual, ctx):
         act = torch.empty((h.shape[0], self.inner), dtype=self.act_dtype, device=h.device)
         fused = False
@@ -45,7 +52,11 @@ class SwiGLUFeedForward:
         if not fused:
             gate_up = linear(h, self.w_gate_up, out_dtype=torch.float32)
             ops.swiglu(act, gate_up)
-        linear(act, self.w_down, accumulate_into=residual)
+        # the last product may prepare the norm that follows this part (ctx.then_norm, see parts/context.py)
+        if getattr(ctx, "then_norm", None) is not None:
+            _, ctx.pending = linear(act, self.w_down, accumulate_into=residual, then_norm=ctx.then_norm)
+        else:
+            linear(act, self.w_down, accumulate_into=residual)
 
 
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)

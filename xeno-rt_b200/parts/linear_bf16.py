@@ -9,6 +9,8 @@ than 128 rows (prompts): the tiled tcgen05 kernel.  ``ops.Tuning.decode_gemm`` =
 forces one of the two decode kernels wherever it applies, for comparison."""
 from __future__ import annotations
 
+import torch
+
 from ..csrc import ops
 
 STREAM_ROWS = 16  # up to here the cp.async kernel is a candidate
@@ -57,6 +59,41 @@ def _product(out, x, weight, mode: str, up_rows: int = 0) -> None:
         ops.gemm_tcgen05(out, x, weight, mode, up_rows)
 
 
+def takes_pending(rows: int, n: int, k: int, mode: str, device) -> bool:
+    """Whether a product of these sizes would run on the kernel that can finish a pending norm (the
+    tcgen05 few-row product), so that the product before it may prepare the norm instead of a kernel."""
+    wish = ops.tuning().pending_norm
+    if rows > ops.DECODE_TCGEN05_MAX_ROWS or k % 8 or wish == "off" or (ops.tuning().decode_gemm == "stream" and wish != "force"):
+        return False
+    if rows > STREAM_ROWS or ops.tuning().decode_gemm == "tcgen05" or wish == "force":
+        return True
+    return tcgen05_for_few_rows(ops.device_state(device)[2], rows, n, k, mode)
+
+
+def run_pending(out, pending, weight, up_rows: int = 0) -> None:
+    """out = the product of a pending norm's result with weight^T (SwiGLU with ``up_rows``)."""
+    ops.gemm_decode_tcgen05(out, pending.scaled, weight, "swiglu" if up_rows else "store", up_rows,
+                            squares=pending.squares, eps=pending.eps)
+
+
+def run_with_norm(out, x, weight, norm):
+    """out += x . weight^T, and the RMSNorm ``norm`` of the new out prepared on the way: a PendingNorm,
+    or None when the kernel that takes this product cannot do that (the caller then runs it plainly)."""
+    from .norm import PendingNorm, RMSNorm
+    rows, n = x.shape[0], out.shape[1]
+    if (not isinstance(norm, RMSNorm) or norm.width != n or not aligned(x, weight) or rows > ops.STREAM_NORM_MAX_ROWS
+            or (ops.tuning().decode_gemm == "tcgen05" and ops.tuning().pending_norm != "force") or not out.is_contiguous()
+            or ops.tuning().pending_norm == "off"):
+        return None
+    if (ops.tuning().decode_gemm != "stream" and ops.tuning().pending_norm != "force"
+            and tcgen05_for_few_rows(ops.device_state(x.device)[2], rows, n, x.shape[1], "accumulate")):
+        return None
+    scaled = torch.empty((rows, n), dtype=torch.bfloat16, device=x.device)
+    squares = torch.empty((ops.gemm_stream_norm_parts(rows, n), rows), dtype=torch.float32, device=x.device)
+    ops.gemm_stream(out, x, weight, "accumulate", norm=(scaled, norm.weight, squares))
+    return PendingNorm(scaled, squares, norm.eps, norm)
+
+
 def run(out, x, weight, accumulate: bool) -> bool:
     if not aligned(x, weight):
         return False
@@ -67,6 +104,10 @@ def run(out, x, weight, accumulate: bool) -> bool:
 def run_swiglu(out, x, weight_gate_up, inner: int) -> bool:
     """out = silu(x . gate^T) * (x . up^T) for the fused weight [2 * inner, width]; False if no
     fused kernel takes the shape."""
+    from .norm import PendingNorm
+    if isinstance(x, PendingNorm):
+        run_pending(out, x, weight_gate_up, inner)
+        return True
     if not aligned(x, weight_gate_up):
         return False
     _product(out, x, weight_gate_up, "swiglu", inner)
