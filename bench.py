@@ -233,6 +233,70 @@ def time_e2e(model, batch: int, context: int, steps: int):
     return out
 
 
+WORKLOADS = {
+    # name: (shape, prompts, shortest, longest prompt, decode steps)
+    "config3": ("qwen3-8b", 16, 64, 2048, 256),
+    "config4": ("qwen3-32b", 8, 2048, 2048, 512),
+}
+
+
+def run_workload(args) -> int:
+    """The two stated workloads beside the headline: 16 prompts of seeded uniform lengths in [64, 2048] in
+    one step of unequal lengths, then 256 decode steps (Qwen3-8B shape); 8 prompts of 2,048 tokens, then 512
+    decode steps (Qwen3-32B shape).  Both through ``Session.generate_batch`` (host token ids in and out,
+    host clock), run twice: the first run captures the decode graphs.  Prints one JSON line with the prompts'
+    tokens a second against the FLOP of the drawn lengths and the decoded tokens a second against the
+    bytes a step has to read (every weight once, the cache of the live sequences at their mean length)."""
+    import torch
+    import xeno_rt_b200  # noqa: F401
+    from xeno_rt_b200 import GenerateRequest, Runtime
+    from xeno_rt_b200.engine import Model
+
+    shape, n_prompts, shortest, longest, steps = WORKLOADS[args.workload]
+    if args.steps != 64:  # the default of --steps belongs to the headline run
+        steps = args.steps
+    shape_name, shape_cfg = SHAPES[shape]
+    cfg = dict(shape_cfg)
+    full_layers = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = n_layers = args.layers or full_layers
+    pk = peaks()
+    model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    gen = torch.Generator().manual_seed(2024)
+    lengths = torch.randint(shortest, longest + 1, (n_prompts,), generator=gen).tolist()
+    prompts = [torch.randint(0, model.vocab_size, (n,), generator=gen).tolist() for n in lengths]
+    session = Runtime(model, max_batch=n_prompts).new_session()
+    make = lambda: [GenerateRequest(p, max_tokens=steps + 1, temperature=0.0, repetition_penalty=1.0, stop_ids=())
+                    for p in prompts]
+    session.generate_batch(make())
+    torch.cuda.synchronize()
+    clocks = ClockSampler()
+    clocks.start()
+    results, stats = session.generate_batch(make())
+    clock_record = clocks.stop()
+    assert all(len(r.tokens) == steps + 1 for r in results)
+    d, f, hd = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    qw, kw = cfg["num_attention_heads"] * hd, cfg["num_key_value_heads"] * hd
+    per_token = 2 * n_layers * ((qw + 2 * kw) * d + d * qw + 3 * f * d)
+    flops = (sum(lengths) * per_token + sum(n_layers * 2 * qw * n * n for n in lengths)
+             + n_prompts * 2 * cfg["vocab_size"] * d)
+    decode_s = stats.seconds - stats.prefill_seconds
+    mean_tokens = sum(n + 1 + steps / 2 for n in lengths)
+    bytes_step = weight_bytes_per_step(cfg, n_layers) + mean_tokens * kv_bytes_per_token(cfg, n_layers)
+    achieved = bytes_step * stats.decode_steps / decode_s / 1e9
+    print(json.dumps({
+        "workload": args.workload, "impl": "ours", "model": shape_name, "layers": n_layers, "layers_of_model": full_layers,
+        "prompts": n_prompts, "prompt_tokens": sum(lengths), "shortest": min(lengths), "longest": max(lengths),
+        "decode_steps": stats.decode_steps, "through": "Session.generate_batch, host clock", "peaks": pk["source"],
+        "prefill": {"value": round(sum(lengths) / stats.prefill_seconds, 1), "unit": "tokens/s",
+                    "ms": round(stats.prefill_seconds * 1e3, 2), "tflops": round(flops / stats.prefill_seconds / 1e12, 1),
+                    "frac": round(flops / stats.prefill_seconds / (pk["bf16_tflops"] * 1e12), 4)},
+        "decode": {"value": round(stats.decode_tokens_per_second, 1), "unit": "tokens/s",
+                   "ms_per_step": round(decode_s / stats.decode_steps * 1e3, 4), "achieved_gbs": round(achieved, 1),
+                   "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "clocks": clock_record}))
+    return 0
+
+
 def run_ours(args) -> int:
     import torch
     import xeno_rt_b200  # noqa: F401
@@ -241,8 +305,26 @@ def run_ours(args) -> int:
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device: bench.py needs a B200"}))
         return 1
+    if apply_tuning(args):
+        return 2
+    shape_name, shape_cfg = SHAPES[args.shape]
+    cfg = dict(shape_cfg)
+    full_layers = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = args.layers or full_layers
+    n_layers = cfg["num_hidden_layers"]
+    pk = peaks()
+    t0 = time.time()
+    model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    torch.cuda.synchronize()
+    setup_s = time.time() - t0
+    return run_timed(args, model, cfg, shape_name, full_layers, n_layers, pk, setup_s)
+
+
+def apply_tuning(args) -> int:
+    """--tuning KEY=VALUE,... onto the kernels' tuning; returns 2 after a message if a key is unknown."""
     if args.tuning:
         import dataclasses
+        import xeno_rt_b200  # noqa: F401
         from xeno_rt_b200.csrc import ops
         fields = {f.name: f.type for f in dataclasses.fields(ops.Tuning)}
         changes = {}
@@ -255,16 +337,11 @@ def run_ours(args) -> int:
             changes[key] = (value.lower() in ("1", "true", "on")) if isinstance(current, bool) else type(current)(
                 int(value, 0) if isinstance(current, int) else value)
         ops.set_tuning(dataclasses.replace(ops.tuning(), **changes))
-    shape_name, shape_cfg = SHAPES[args.shape]
-    cfg = dict(shape_cfg)
-    full_layers = cfg["num_hidden_layers"]
-    cfg["num_hidden_layers"] = args.layers or full_layers
-    n_layers = cfg["num_hidden_layers"]
-    pk = peaks()
-    t0 = time.time()
-    model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
-    torch.cuda.synchronize()
-    setup_s = time.time() - t0
+    return 0
+
+
+def run_timed(args, model, cfg, shape_name, full_layers, n_layers, pk, setup_s) -> int:
+    import torch
 
     if args.only == "prefill":  # a short run for profiling: one prompt (of 2,048 tokens unless --prefill-tokens says otherwise)
         prefill_ms = time_prefill(model, args.prefill_tokens, iters=max(1, args.steps), warmup=args.warmup)
@@ -328,6 +405,9 @@ def main() -> int:
                         help="the model shape to time (the default is the headline configuration)")
     parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                         help="prompt length of --only prefill (the full line always uses 2,048)")
+    parser.add_argument("--workload", default="", choices=["", *sorted(WORKLOADS)],
+                        help="one of the two further workloads instead of the headline line (16 unequal prompts then "
+                             "256 decode steps at the Qwen3-8B shape; 8 x 2,048 then 512 steps at the Qwen3-32B shape)")
     parser.add_argument("--tuning", default="", metavar="KEY=VALUE[,KEY=VALUE...]",
                         help="kernel variants to force, as fields of xeno_rt_b200.csrc.ops.Tuning (for comparisons)")
     parser.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
@@ -343,6 +423,9 @@ def main() -> int:
         return 2
     if args.warmup < 3 and args.only == "all":
         args.warmup = 3
+    if args.workload:
+        apply_tuning(args)
+        return run_workload(args)
     return run_ours(args)
 
 

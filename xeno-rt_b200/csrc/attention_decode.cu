@@ -12,7 +12,7 @@
 // (m, l, o) partials that the combine kernel merges in split order.  Nothing depends on how many
 // other tokens the launch carries, and launch shapes depend on `chunk` and the grid only, so the
 // launch can be captured in a CUDA graph and replayed for other lengths.
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 #include "attention_mma.cuh"
 
@@ -271,9 +271,7 @@ __global__ void attention_combine_kernel(__nv_bfloat16* __restrict__ out, const 
                                          const int* __restrict__ tok_pos, int n_tokens, int n_heads, int head_dim,
                                          int window, int chunk, int n_splits) {
   pdl_trigger();
-  if (threadIdx.x == 0) XRT_TL(60);
   pdl_wait();
-  if (threadIdx.x == 0) XRT_TL(61);
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp_global >= n_tokens * n_heads) return;
   const int tok = warp_global / n_heads;
@@ -384,7 +382,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full[2];
   pdl_trigger();
-  if (threadIdx.x == 0) XRT_TL(50);
   // The step's arrays (slots, positions, block table) were written before the step began: they may be
   // read, and tiles of old keys fetched, while the kernel before this one (which writes q and the
   // newest key and value) is still running.
@@ -445,7 +442,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const bool early = has_keys && (fused.qkv != nullptr || begin + XRT_BLOCK_TOKENS <= len - 1);
   if (threadIdx.x == 0 && early) issue_tile(0, 0);
   pdl_wait();
-  if (threadIdx.x == 0) XRT_TL(51);
   uint32_t qb[D_TILES / 2][2];
   if (fused.qkv == nullptr) {
     const __nv_bfloat16* qt = q + ((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim;
@@ -587,7 +583,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     if (!clustered) return;  // in a cluster the block still meets the others (its state below is meaningless)
   }
 
-  if (threadIdx.x == 0) XRT_TL(52);
   // this warp's state into the merge area: row = head; the sums are spread over the lanes of a t
   float* merge_m = reinterpret_cast<float*>(smem);
   float* merge_l = merge_m + DEC_WARPS * 16;
@@ -611,7 +606,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   if (!clustered) {
     decode_finish(smem, out, part_o, part_ml, counters, tok, kv_head, split, n_splits, chunk, first_key, len, group, n_heads,
                   n_kv_heads, head_dim);
-    if (threadIdx.x == 0) XRT_TL(53);
     return;
   }
 
@@ -662,27 +656,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-typedef CUresult (*DecEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static DecEncodeFn dec_encode() {
-  static DecEncodeFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<DecEncodeFn>(ptr);
-  }
-  return fn;
-}
-
 // A map over a cache pool, a row-major bfloat16 matrix [blocks * kv heads * 64, head_dim], seen as
 // [head_dim / 64 pieces][rows][64 dims]: a box is 64 dims x 64 rows x all pieces, 128-byte swizzle, so one copy
 // brings a whole tile of 64 keys as head_dim / 64 boxes of 64 rows x 128 bytes, one behind the other.
 static bool dec_make_map(CUtensorMap* map, const void* base, long long rows, int head_dim) {
-  DecEncodeFn encode = dec_encode();
+  sm100::TensorMapEncodeFn encode = sm100::tensor_map_encoder();
   if (encode == nullptr) return false;
   const cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(head_dim / 64)};
   const cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2, 128u};
@@ -847,7 +825,6 @@ inline int decode_fused_max_splits(int head_dim, int group) {
 
 }  // namespace xrt
 
-XRT_TL_EXPORT(attention_decode)
 
 XRT_EXPORT int xrt_attention_decode_fused_max_splits(int head_dim, int group) {
   if (head_dim < 16 || head_dim > 256 || head_dim % 16 != 0 || group < 1 || group > 16) return XRT_ERR_UNSUPPORTED;
@@ -970,6 +947,8 @@ XRT_EXPORT int xrt_attention_decode_qkv(void* out, float* part_o, float* part_ml
 // image.  See attention_decode_static.h for who needs this and what the limits are.
 #include <stdio.h>
 
+#include <mutex>
+
 #include "attention_decode_static.h"
 
 namespace xrt {
@@ -980,6 +959,7 @@ constexpr int STATIC_MAX_DEVICES = 64;
 // In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
 static __device__ __align__(256) float decode_static_scratch[STATIC_SCRATCH_FLOATS];
 static float* decode_static_scratch_address[STATIC_MAX_DEVICES] = {};
+static std::mutex decode_static_setup;
 
 static void refuse(char* message, int message_len, const char* text) {
   if (message != nullptr && message_len > 0) snprintf(message, (size_t)message_len, "%s", text);
@@ -1018,7 +998,9 @@ int xrt_attention_decode_static(void* out, const void* q, const void* k_pool, co
     xrt::refuse(message, message_len, "xrt_attention_decode_static: device ordinal out of range");
     return XRT_ERR_UNSUPPORTED;
   }
-  // Set-up, once a device, with that device current: the device address of the scratch array.
+  // Set-up, once a device, with that device current: the device address of the scratch array.  Two host
+  // threads that make a device's first call at the same moment are serialised here.
+  std::lock_guard<std::mutex> guard(xrt::decode_static_setup);
   if (xrt::decode_static_scratch_address[device] == nullptr) {
     float* address = nullptr;
     err = cudaGetSymbolAddress((void**)&address, xrt::decode_static_scratch);

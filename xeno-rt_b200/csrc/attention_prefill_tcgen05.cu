@@ -25,11 +25,11 @@
 //             completed) only on those rare moves instead of once a step.
 // Every mbarrier wait is bounded; a wait that runs out raises the error flag and an abort flag, all
 // roles leave their loops, TMEM is freed and the block returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace xrt {
+
+using namespace sm100;
 
 constexpr int FA_ROWS = 128, FA_KEYS = 128, FA_HD = 128, FA_STAGES = 3;
 constexpr int FA_Q_BYTES = FA_ROWS * FA_HD * 2;        // 32 KB (two halves of 16 KB)
@@ -39,86 +39,7 @@ constexpr int FA_STAGE_BYTES = 4 * FA_KV_HALF;         // K halves, then V halve
 constexpr int FA_P_COLS = FA_KEYS / 2;                 // P in TMEM: bfloat16 pairs, 64 columns of 32 bits a step
 constexpr int FA_P_BUFFERS = 2;                        // P of a step is written while the product before it still reads its own
 constexpr int fa_smem_bytes(int nh) { return nh * FA_Q_BYTES + FA_STAGES * FA_STAGE_BYTES + 512 + 1024; }
-constexpr long long FA_SPIN_LIMIT = 1ll << 24;
 
-__device__ __forceinline__ uint32_t fa_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void fa_mbar_init(uint32_t bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void fa_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void fa_mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool fa_mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (long long spin = 0; spin < FA_SPIN_LIMIT; ++spin) {
-    uint32_t done;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    if (done) return true;
-    if ((spin & 1023) == 1023 && *abort_flag) return false;
-  }
-  return false;
-}
-__device__ __forceinline__ void fa_tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-// K-major operand: rows of 128 bytes (64 bfloat16 of the contraction), 128-byte swizzle, groups of
-// eight rows 1024 bytes apart.
-__device__ __forceinline__ uint64_t fa_desc_k_major(uint32_t addr) {
-  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
-         ((uint64_t)2 << 61);
-}
-// MN-major operand (V as stored, [key][dim]): 128-byte rows hold 64 consecutive dims of one key
-// (the contraction index advances from row to row); groups of eight keys are 1024 bytes apart
-// (stride byte offset), the next 64 dims are `chunk_bytes` further (leading byte offset).
-__device__ __forceinline__ uint64_t fa_desc_mn_major(uint32_t addr, uint32_t chunk_bytes) {
-  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(chunk_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
-         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// kind::f16, bfloat16 A and B, float32 D; A K-major; B K-major or MN-major (bit 16).
-__device__ __forceinline__ constexpr uint32_t fa_instr_desc(int m, int n, bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void fa_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-               " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-               ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-// The same with A read from tensor memory: row r of A in lane r, two bfloat16 of the contraction a
-// 32-bit column (the lower index in the lower half), 8 columns an instruction.
-__device__ __forceinline__ void fa_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
-                                              uint32_t accumulate) {
-  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-               " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
-               ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void fa_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void fa_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fa_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fa_st32(uint32_t addr, const uint32_t (&r)[32]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-               "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-               ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-                 "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-                 "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-                 "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-               : "memory");
-}
-__device__ __forceinline__ void fa_ld32(uint32_t (&r)[32], uint32_t addr) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-               : "r"(addr));
-}
 // 2^x by the special-function unit; exp2(-inf) = 0.  Inputs are differences to a running maximum
 // (at most 0) and the result feeds a bfloat16 product or a 32-bit sum: the unit's 2 ulp are far
 // inside bfloat16's 8 bits.
@@ -127,7 +48,6 @@ __device__ __forceinline__ float fa_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ void fa_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // NH = query heads of one kv head that a block serves; its K and V tiles are fetched once for all of
 // them.  With steps of 128 keys (two cache blocks: a tcgen05.mma costs about a hundred cycles
@@ -174,32 +94,32 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   constexpr int TMEM_COLS = 512;  // S: NH x 2 buffers x 128 columns; O: NH x 128; P: NH x 2 buffers x 64
 
   if (threadIdx.x == 0) {
-    fa_mbar_init(fa_smem(q_full), 1);
+    mbar_init(smem_u32(q_full), 1);
     for (int s = 0; s < FA_STAGES; ++s) {
-      fa_mbar_init(fa_smem(&k_full[s]), 1); fa_mbar_init(fa_smem(&k_empty[s]), 1);
-      fa_mbar_init(fa_smem(&v_full[s]), 1); fa_mbar_init(fa_smem(&v_empty[s]), 1);
+      mbar_init(smem_u32(&k_full[s]), 1); mbar_init(smem_u32(&k_empty[s]), 1);
+      mbar_init(smem_u32(&v_full[s]), 1); mbar_init(smem_u32(&v_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
       // the softmax warps arrive once each (lane 0, after the warp has synchronised): hundreds of
       // arrivals on one shared-memory word would serialise
-      fa_mbar_init(fa_smem(&s_full[b]), 1);
-      fa_mbar_init(fa_smem(&s_empty[b]), 4 * NH);
+      mbar_init(smem_u32(&s_full[b]), 1);
+      mbar_init(smem_u32(&s_empty[b]), 4 * NH);
     }
     for (int b = 0; b < FA_P_BUFFERS; ++b) {
-      fa_mbar_init(fa_smem(&p_full[b]), 4 * NH);
-      fa_mbar_init(fa_smem(&p_empty[b]), 1);
+      mbar_init(smem_u32(&p_full[b]), 4 * NH);
+      mbar_init(smem_u32(&p_empty[b]), 1);
     }
-    fa_mbar_init(fa_smem(pv_done), 1);
+    mbar_init(smem_u32(pv_done), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(fa_smem(tmem_slot)), "n"(TMEM_COLS));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
-  fa_fence_before();
+  fence_before();
   __syncthreads();
-  fa_fence_after();
+  fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s = tmem_base;                        // [head][buffer] x 64 columns
   const uint32_t tmem_o = tmem_base + NH * 2 * FA_KEYS;     // [head] x 128 columns
@@ -211,12 +131,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
-      fa_mbar_expect_tx(fa_smem(q_full), NH * FA_Q_BYTES);
+      mbar_arrive_expect_tx(smem_u32(q_full), NH * FA_Q_BYTES);
 #pragma unroll
       for (int h = 0; h < NH; ++h) {
-        fa_tma_load_2d(fa_smem(q_tiles + h * FA_Q_BYTES), &map_q, (head0 + h) * FA_HD, tok0 + row0, fa_smem(q_full));
-        fa_tma_load_2d(fa_smem(q_tiles + h * FA_Q_BYTES + FA_Q_BYTES / 2), &map_q, (head0 + h) * FA_HD + 64, tok0 + row0,
-                       fa_smem(q_full));
+        tma_load_2d(smem_u32(q_tiles + h * FA_Q_BYTES), &map_q, (head0 + h) * FA_HD, tok0 + row0, smem_u32(q_full));
+        tma_load_2d(smem_u32(q_tiles + h * FA_Q_BYTES + FA_Q_BYTES / 2), &map_q, (head0 + h) * FA_HD + 64, tok0 + row0,
+                       smem_u32(q_full));
       }
       const int* blocks = block_table + (size_t)slot * max_blocks;
       const int n_blocks = (start + last_row + 1 + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS;  // cache blocks the rows see
@@ -228,21 +148,21 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
         for (int part = 0; part < 2; ++part)
           pool_row[part] = (blocks[min(2 * j + part, n_blocks - 1)] * n_kv_heads + kv_head) * XRT_BLOCK_TOKENS;
-        ok = fa_mbar_wait(fa_smem(&k_empty[s]), ((j / FA_STAGES) & 1) ^ 1, abort_flag);
+        ok = mbar_wait(smem_u32(&k_empty[s]), ((j / FA_STAGES) & 1) ^ 1, abort_flag);
         if (!ok) break;
-        fa_mbar_expect_tx(fa_smem(&k_full[s]), 2 * FA_KV_HALF);
+        mbar_arrive_expect_tx(smem_u32(&k_full[s]), 2 * FA_KV_HALF);
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
-          fa_tma_load_2d(fa_smem(stage + part * FA_BOX), &map_k, 0, pool_row[part], fa_smem(&k_full[s]));
-          fa_tma_load_2d(fa_smem(stage + FA_KV_HALF + part * FA_BOX), &map_k, 64, pool_row[part], fa_smem(&k_full[s]));
+          tma_load_2d(smem_u32(stage + part * FA_BOX), &map_k, 0, pool_row[part], smem_u32(&k_full[s]));
+          tma_load_2d(smem_u32(stage + FA_KV_HALF + part * FA_BOX), &map_k, 64, pool_row[part], smem_u32(&k_full[s]));
         }
-        ok = fa_mbar_wait(fa_smem(&v_empty[s]), ((j / FA_STAGES) & 1) ^ 1, abort_flag);
+        ok = mbar_wait(smem_u32(&v_empty[s]), ((j / FA_STAGES) & 1) ^ 1, abort_flag);
         if (!ok) break;
-        fa_mbar_expect_tx(fa_smem(&v_full[s]), 2 * FA_KV_HALF);
+        mbar_arrive_expect_tx(smem_u32(&v_full[s]), 2 * FA_KV_HALF);
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
-          fa_tma_load_2d(fa_smem(stage + 2 * FA_KV_HALF + part * FA_BOX), &map_v, 0, pool_row[part], fa_smem(&v_full[s]));
-          fa_tma_load_2d(fa_smem(stage + 3 * FA_KV_HALF + part * FA_BOX), &map_v, 64, pool_row[part], fa_smem(&v_full[s]));
+          tma_load_2d(smem_u32(stage + 2 * FA_KV_HALF + part * FA_BOX), &map_v, 0, pool_row[part], smem_u32(&v_full[s]));
+          tma_load_2d(smem_u32(stage + 3 * FA_KV_HALF + part * FA_BOX), &map_v, 64, pool_row[part], smem_u32(&v_full[s]));
         }
       }
       if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 5); }
@@ -250,26 +170,26 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
-      constexpr uint32_t idesc_qk = fa_instr_desc(FA_ROWS, FA_KEYS, false);
-      constexpr uint32_t idesc_pv = fa_instr_desc(FA_ROWS, FA_HD, true);
-      bool ok = fa_mbar_wait(fa_smem(q_full), 0, abort_flag);
+      constexpr uint32_t idesc_qk = instr_desc(FA_ROWS, FA_KEYS, false);
+      constexpr uint32_t idesc_pv = instr_desc(FA_ROWS, FA_HD, true);
+      bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag);
       auto issue_qk = [&](int j) {
         const int s = j % FA_STAGES, b = j & 1;
-        if (!fa_mbar_wait(fa_smem(&k_full[s]), (j / FA_STAGES) & 1, abort_flag)) return false;
-        if (!fa_mbar_wait(fa_smem(&s_empty[b]), ((j >> 1) & 1) ^ 1, abort_flag)) return false;
-        fa_fence_after();
+        if (!mbar_wait(smem_u32(&k_full[s]), (j / FA_STAGES) & 1, abort_flag)) return false;
+        if (!mbar_wait(smem_u32(&s_empty[b]), ((j >> 1) & 1) ^ 1, abort_flag)) return false;
+        fence_after();
         unsigned char* stage = kv_ring + s * FA_STAGE_BYTES;
 #pragma unroll
         for (int h = 0; h < NH; ++h) {
 #pragma unroll
           for (int ks = 0; ks < FA_HD / 16; ++ks) {  // 16 dims a step; 4 steps a 64-dim half
-            const uint64_t a = fa_desc_k_major(fa_smem(q_tiles + h * FA_Q_BYTES + (ks / 4) * (FA_Q_BYTES / 2))) + 2 * (ks % 4);
-            const uint64_t bd = fa_desc_k_major(fa_smem(stage + (ks / 4) * FA_KV_HALF)) + 2 * (ks % 4);
-            fa_mma(tmem_s + (h * 2 + b) * FA_KEYS, a, bd, idesc_qk, ks > 0);
+            const uint64_t a = desc_k_major(smem_u32(q_tiles + h * FA_Q_BYTES + (ks / 4) * (FA_Q_BYTES / 2))) + 2 * (ks % 4);
+            const uint64_t bd = desc_k_major(smem_u32(stage + (ks / 4) * FA_KV_HALF)) + 2 * (ks % 4);
+            mma_f16(tmem_s + (h * 2 + b) * FA_KEYS, a, bd, idesc_qk, ks > 0);
           }
         }
-        fa_commit(fa_smem(&s_full[b]));
-        fa_commit(fa_smem(&k_empty[s]));
+        commit(smem_u32(&s_full[b]));
+        commit(smem_u32(&k_empty[s]));
         return true;
       };
       if (ok) ok = issue_qk(0);
@@ -278,22 +198,22 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (!ok) break;
         const int s = j % FA_STAGES;
         const int pb = j & 1;
-        ok = fa_mbar_wait(fa_smem(&p_full[pb]), (uint32_t)(j >> 1) & 1u, abort_flag) &&  // P is written, and O rescaled if it had to be
-             fa_mbar_wait(fa_smem(&v_full[s]), (j / FA_STAGES) & 1, abort_flag);
+        ok = mbar_wait(smem_u32(&p_full[pb]), (uint32_t)(j >> 1) & 1u, abort_flag) &&  // P is written, and O rescaled if it had to be
+             mbar_wait(smem_u32(&v_full[s]), (j / FA_STAGES) & 1, abort_flag);
         if (!ok) break;
-        fa_fence_after();
+        fence_after();
         unsigned char* stage = kv_ring + s * FA_STAGE_BYTES;
 #pragma unroll
         for (int h = 0; h < NH; ++h) {
 #pragma unroll
           for (int ks = 0; ks < FA_KEYS / 16; ++ks) {  // 16 keys a step
-            const uint64_t bd = fa_desc_mn_major(fa_smem(stage + 2 * FA_KV_HALF + ks * 2048), FA_KV_HALF);
-            fa_mma_a_tmem(tmem_o + h * FA_HD, tmem_p + (h * FA_P_BUFFERS + pb) * FA_P_COLS + ks * 8, bd, idesc_pv, j > 0 || ks > 0);
+            const uint64_t bd = desc_mn_major(smem_u32(stage + 2 * FA_KV_HALF + ks * 2048), FA_KV_HALF);
+            mma_f16_a_tmem(tmem_o + h * FA_HD, tmem_p + (h * FA_P_BUFFERS + pb) * FA_P_COLS + ks * 8, bd, idesc_pv, j > 0 || ks > 0);
           }
         }
-        fa_commit(fa_smem(pv_done));
-        fa_commit(fa_smem(&v_empty[s]));
-        fa_commit(fa_smem(&p_empty[pb]));
+        commit(smem_u32(pv_done));
+        commit(smem_u32(&v_empty[s]));
+        commit(smem_u32(&p_empty[pb]));
       }
       if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 5); }
     }
@@ -313,26 +233,26 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int b = j & 1;
-      ok = fa_mbar_wait(fa_smem(&s_full[b]), (j >> 1) & 1, abort_flag);
+      ok = mbar_wait(smem_u32(&s_full[b]), (j >> 1) & 1, abort_flag);
       if (!ok) break;
-      fa_fence_after();
+      fence_after();
       float s[FA_KEYS];
       {
         uint32_t v0[32], v1[32], v2[32], v3[32];  // the whole row on its way before the one wait
-        fa_ld32(v0, my_s + b * FA_KEYS);
-        fa_ld32(v1, my_s + b * FA_KEYS + 32);
-        fa_ld32(v2, my_s + b * FA_KEYS + 64);
-        fa_ld32(v3, my_s + b * FA_KEYS + 96);
-        fa_wait_ld();
+        tmem_ld32(v0, my_s + b * FA_KEYS);
+        tmem_ld32(v1, my_s + b * FA_KEYS + 32);
+        tmem_ld32(v2, my_s + b * FA_KEYS + 64);
+        tmem_ld32(v3, my_s + b * FA_KEYS + 96);
+        tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           s[i] = __uint_as_float(v0[i]); s[32 + i] = __uint_as_float(v1[i]);
           s[64 + i] = __uint_as_float(v2[i]); s[96 + i] = __uint_as_float(v3[i]);
         }
       }
-      fa_fence_before();
+      fence_before();
       __syncwarp();
-      if (lane == 0) fa_mbar_arrive(fa_smem(&s_empty[b]));  // the tensor core may write the block after next into this buffer
+      if (lane == 0) mbar_arrive(smem_u32(&s_empty[b]));  // the tensor core may write the block after next into this buffer
       const int key0 = j * FA_KEYS;
       // Only blocks that reach past the first row's last visible key can hide a key from a row
       // (uniform over the thread block); every other block skips the comparisons.
@@ -353,21 +273,21 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       if (__any_sync(0xffffffffu, moves)) {
         const float factor = (moves && m_ref != -INFINITY) ? fa_exp2(m_ref - m_tile) : 1.0f;
         if (j > 0) {  // O holds the products of the blocks so far: they must have completed before it is rewritten
-          ok = fa_mbar_wait(fa_smem(pv_done), (uint32_t)(j - 1) & 1u, abort_flag);
+          ok = mbar_wait(smem_u32(pv_done), (uint32_t)(j - 1) & 1u, abort_flag);
           if (!ok) break;
-          fa_fence_after();
+          fence_after();
           if (__any_sync(0xffffffffu, factor != 1.0f)) {
 #pragma unroll
             for (int c = 0; c < FA_HD; c += 32) {
               uint32_t v[32];
-              fa_ld32(v, my_o + c);
-              fa_wait_ld();
+              tmem_ld32(v, my_o + c);
+              tmem_wait_ld();
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
-              fa_st32(my_o + c, v);
+              tmem_st32(my_o + c, v);
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            fa_fence_before();
+            fence_before();
           }
         }
         l_run *= factor;
@@ -379,9 +299,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       // consecutive keys a column.  Two P buffers a head: with one, the exponents of a step could
       // only be stored when the product of the step before had completed, and that product only
       // when they all were: the tensor core and the softmax threads took turns.
-      ok = fa_mbar_wait(fa_smem(&p_empty[b]), ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_flag);
+      ok = mbar_wait(smem_u32(&p_empty[b]), ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_flag);
       if (!ok) break;
-      fa_fence_after();
+      fence_after();
       const uint32_t my_p = tmem_p + lane_base + (h * FA_P_BUFFERS + b) * FA_P_COLS;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -394,24 +314,24 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
           packed[i] = *reinterpret_cast<uint32_t*>(&pair);
         }
-        fa_st32(my_p + half * 32, packed);
+        tmem_st32(my_p + half * 32, packed);
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      fa_fence_before();
+      fence_before();
       __syncwarp();
-      if (lane == 0) fa_mbar_arrive(fa_smem(&p_full[b]));
+      if (lane == 0) mbar_arrive(smem_u32(&p_full[b]));
       l_run += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
     }
-    if (ok && n_tiles > 0) ok = fa_mbar_wait(fa_smem(pv_done), (uint32_t)(n_tiles - 1) & 1u, abort_flag);
+    if (ok && n_tiles > 0) ok = mbar_wait(smem_u32(pv_done), (uint32_t)(n_tiles - 1) & 1u, abort_flag);
     if (ok && n_tiles > 0) {
-      fa_fence_after();
+      fence_after();
       const float inv = row_live ? 1.0f / l_run : 0.f;
       __nv_bfloat16* dst = out + ((size_t)(tok0 + row) * n_heads + head) * FA_HD;
 #pragma unroll
       for (int c = 0; c < FA_HD; c += 32) {
         uint32_t v[32];
-        fa_ld32(v, my_o + c);  // all lanes take part; rows beyond the sequence store nothing
-        fa_wait_ld();
+        tmem_ld32(v, my_o + c);  // all lanes take part; rows beyond the sequence store nothing
+        tmem_wait_ld();
         if (row_live) {
 #pragma unroll
           for (int d = 0; d < 32; d += 8) {
@@ -426,46 +346,22 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           }
         }
       }
-      fa_fence_before();
+      fence_before();
     }
     if (!ok && lane == 0) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 5); }
   }
 
-  fa_fence_before();
+  fence_before();
   __syncthreads();
   if (warp == 1) {
-    fa_fence_after();
+    fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TMEM_COLS));
   }
 }
 
-typedef CUresult (*FaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static FaEncodeFn fa_encode() {
-  static FaEncodeFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<FaEncodeFn>(ptr);
-  }
-  return fn;
-}
-
 // A map over a row-major bfloat16 matrix [rows, cols], boxes of box_rows x 64 columns, 128-byte swizzle.
 static bool fa_make_map(CUtensorMap* map, const void* base, long long rows, int cols, int box_rows) {
-  FaEncodeFn encode = fa_encode();
-  if (encode == nullptr) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-  const cuuint32_t elem[2] = {1u, 1u};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return sm100::make_map_bf16_2d(map, base, rows, cols, cols, box_rows);
 }
 
 }  // namespace xrt

@@ -108,34 +108,6 @@ inline int launch_status() {
 
 }  // namespace xrt
 
-#ifdef XRT_TIMELINE
-namespace xrt {
-static __device__ unsigned long long tl_buf[1 << 16][2];
-static __device__ unsigned int tl_n;
-__device__ __forceinline__ void tl_stamp(int id) {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  unsigned smid;
-  asm("mov.u32 %0, %%smid;" : "=r"(smid));
-  const unsigned i = atomicAdd(&tl_n, 1u);
-  const unsigned lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-  if (i < (1u << 16)) { tl_buf[i][0] = t; tl_buf[i][1] = ((unsigned long long)id << 32) | ((unsigned long long)smid << 20) | (lin & 0xfffff); }
-}
-}  // namespace xrt
-#define XRT_TL(id) xrt::tl_stamp(id)
-#define XRT_TL_EXPORT(name)                                                                          \
-  extern "C" __attribute__((visibility("default"))) int xrt_timeline_##name(void* host, int reset) { \
-    unsigned n = 0;                                                                                  \
-    cudaMemcpyFromSymbol(&n, xrt::tl_n, 4);                                                          \
-    if (host) cudaMemcpyFromSymbol(host, xrt::tl_buf, sizeof(xrt::tl_buf));                          \
-    if (reset) { unsigned z = 0; cudaMemcpyToSymbol(xrt::tl_n, &z, 4); }                             \
-    return (int)n;                                                                                   \
-  }
-#else
-#define XRT_TL(id) do {} while (0)
-#define XRT_TL_EXPORT(name)
-#endif
-
 // Dispatch on a dtype code: runs BODY with `T` bound to float or __nv_bfloat16.
 #define XRT_DISPATCH_DTYPE(code, T, ...)            \
   do {                                              \

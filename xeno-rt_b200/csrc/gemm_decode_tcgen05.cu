@@ -26,68 +26,17 @@
 // accumulators (tcgen05.ld, one TMEM lane quarter each) while the MMA warp fills the other
 // accumulator.  Every mbarrier wait is bounded; a wait that runs out raises the error flag and an
 // abort flag, all roles leave their loops, TMEM is freed and the block returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace xrt {
+
+using namespace sm100;
 
 constexpr int DG_ROWS = 128, DG_BK = 64, DG_UMMA_K = 16;
 constexpr int DG_W_BYTES = DG_ROWS * DG_BK * 2;  // 16 KB: one slab of one group of weight rows
 constexpr int DG_THREADS = 192;
-constexpr long long DG_SPIN_LIMIT = 1ll << 24;
 constexpr int DG_MAX_SPLITS = 8;
 
-__device__ __forceinline__ uint32_t dg_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void dg_mbar_init(uint32_t bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void dg_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void dg_mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool dg_mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (long long spin = 0; spin < DG_SPIN_LIMIT; ++spin) {
-    uint32_t done;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    if (done) return true;
-    if ((spin & 1023) == 1023 && *abort_flag) return false;
-  }
-  return false;
-}
-__device__ __forceinline__ void dg_tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-// K-major operand in 128-byte-swizzled rows of 128 bytes, groups of eight rows 1024 bytes apart.
-__device__ __forceinline__ uint64_t dg_smem_desc(uint32_t addr) {
-  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
-         ((uint64_t)2 << 61);
-}
-// kind::f16, bfloat16 A and B, float32 D, both K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t dg_instr_desc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(DG_ROWS >> 4) << 24);
-}
-__device__ __forceinline__ void dg_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-               " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-               ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void dg_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void dg_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void dg_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void dg_ld16(uint32_t (&r)[16], uint32_t addr) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-               : "r"(addr));
-}
-__device__ __forceinline__ void dg_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // The two halves of a cluster meeting, thread by thread: a block may store into another block's shared
 // memory only once that block runs, which the first meeting (arrive at the start, wait before the first
 // store) makes sure of without holding anybody up.
@@ -152,18 +101,18 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
   const int acc_cols = GROUPS * shape.nb;  // TMEM columns of one accumulator set
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) { dg_mbar_init(dg_smem(&full[s]), 2); dg_mbar_init(dg_smem(&empty[s]), 1); }
-    for (int a = 0; a < 2; ++a) { dg_mbar_init(dg_smem(&acc_full[a]), 1); dg_mbar_init(dg_smem(&acc_empty[a]), 128); }
+    for (int s = 0; s < stages; ++s) { mbar_init(smem_u32(&full[s]), 2); mbar_init(smem_u32(&empty[s]), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&acc_full[a]), 1); mbar_init(smem_u32(&acc_empty[a]), 128); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dg_smem(tmem_slot)), "r"(shape.tmem_cols));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(shape.tmem_cols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
-  dg_fence_before();
+  fence_before();
   __syncthreads();
-  dg_fence_after();
+  fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   // item -> (tile, split); consecutive items are the splits of one tile
@@ -172,7 +121,6 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-      XRT_TL(20);
       // The walk over this block's slabs: items in turn, and inside an item the slabs of its split of K.
       // Blocks that work at the same time start their walk over K at different slabs (a rotation that
       // depends on the tile only, so the order of the sum is fixed per output element): otherwise every
@@ -201,16 +149,16 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       if (walk.item < n_items) walk.enter(shape, k_iters_total);
       const uint32_t w_bytes = GROUPS * DG_W_BYTES;
       auto load_w = [&](const Walk& at, int s) {
-        const uint32_t bar = dg_smem(&full[s]);
+        const uint32_t bar = smem_u32(&full[s]);
         unsigned char* stage = smem + (size_t)s * stage_bytes;
-        dg_mbar_expect_tx(bar, w_bytes);
-        dg_tma_load_2d(dg_smem(stage), &map_w, at.kb() * DG_BK, at.tile * DG_ROWS, bar);
-        if (MODE == 2) dg_tma_load_2d(dg_smem(stage + DG_W_BYTES), &map_w, at.kb() * DG_BK, shape.up_rows + at.tile * DG_ROWS, bar);
+        mbar_arrive_expect_tx(bar, w_bytes);
+        tma_load_2d(smem_u32(stage), &map_w, at.kb() * DG_BK, at.tile * DG_ROWS, bar);
+        if (MODE == 2) tma_load_2d(smem_u32(stage + DG_W_BYTES), &map_w, at.kb() * DG_BK, shape.up_rows + at.tile * DG_ROWS, bar);
       };
       auto load_x = [&](const Walk& at, int s) {
-        const uint32_t bar = dg_smem(&full[s]);
-        dg_mbar_expect_tx(bar, x_bytes);
-        dg_tma_load_2d(dg_smem(smem + (size_t)s * stage_bytes + GROUPS * DG_W_BYTES), &map_x, at.kb() * DG_BK, 0, bar);
+        const uint32_t bar = smem_u32(&full[s]);
+        mbar_arrive_expect_tx(bar, x_bytes);
+        tma_load_2d(smem_u32(smem + (size_t)s * stage_bytes + GROUPS * DG_W_BYTES), &map_x, at.kb() * DG_BK, 0, bar);
       };
       // The weights do not depend on the step: the whole ring is filled with them while the kernel
       // before this one finishes.  X does: its loads follow once that kernel has completed.  A stage's
@@ -223,7 +171,6 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         ++filled;
       }
       pdl_wait();
-      XRT_TL(21);
       int it = 0;
       bool ok = true;
       while (it < filled && walk.settle(shape, k_iters_total, n_items, gridDim.x)) {
@@ -233,21 +180,20 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       }
       while (ok && walk.settle(shape, k_iters_total, n_items, gridDim.x)) {
         const int s = it % stages;
-        ok = dg_mbar_wait(dg_smem(&empty[s]), ((it / stages) & 1) ^ 1, abort_flag);
+        ok = mbar_wait(smem_u32(&empty[s]), ((it / stages) & 1) ^ 1, abort_flag);
         if (!ok) break;
         load_w(walk, s);
         load_x(walk, s);
         ++walk.i;
         ++it;
       }
-      XRT_TL(22);
       if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 4); }
     }
     if (shape.clustered) dg_cluster_wait();
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
-      const uint32_t idesc = dg_instr_desc(shape.nb);
+      const uint32_t idesc = instr_desc(DG_ROWS, shape.nb);
       int it = 0, item_i = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++item_i) {
@@ -255,27 +201,27 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         const int kb0 = split * shape.k_per_split;
         const int kb1 = min(k_iters_total, kb0 + shape.k_per_split);
         const int a = item_i & 1;
-        ok = dg_mbar_wait(dg_smem(&acc_empty[a]), ((item_i >> 1) & 1) ^ 1, abort_flag);
+        ok = mbar_wait(smem_u32(&acc_empty[a]), ((item_i >> 1) & 1) ^ 1, abort_flag);
         if (!ok) break;
-        dg_fence_after();
+        fence_after();
         const uint32_t tmem_d = tmem_base + a * acc_cols;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {  // the slabs arrive in the producer's rotated order
           const int s = it % stages;
-          ok = dg_mbar_wait(dg_smem(&full[s]), (it / stages) & 1, abort_flag);
+          ok = mbar_wait(smem_u32(&full[s]), (it / stages) & 1, abort_flag);
           if (!ok) break;
-          dg_fence_after();
+          fence_after();
           unsigned char* stage = smem + (size_t)s * stage_bytes;
-          const uint64_t desc_x = dg_smem_desc(dg_smem(stage + GROUPS * DG_W_BYTES));
+          const uint64_t desc_x = desc_k_major(smem_u32(stage + GROUPS * DG_W_BYTES));
 #pragma unroll
           for (int gr = 0; gr < GROUPS; ++gr) {
-            const uint64_t desc_w = dg_smem_desc(dg_smem(stage + gr * DG_W_BYTES));
+            const uint64_t desc_w = desc_k_major(smem_u32(stage + gr * DG_W_BYTES));
 #pragma unroll
             for (int k = 0; k < DG_BK / DG_UMMA_K; ++k)
-              dg_mma(tmem_d + gr * shape.nb, desc_w + 2 * k, desc_x + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+              mma_f16(tmem_d + gr * shape.nb, desc_w + 2 * k, desc_x + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          dg_commit(dg_smem(&empty[s]));
+          commit(smem_u32(&empty[s]));
         }
-        if (ok) dg_commit(dg_smem(&acc_full[a]));
+        if (ok) commit(smem_u32(&acc_full[a]));
       }
       if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 4); }
     }
@@ -311,17 +257,17 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       const int n = tile * DG_ROWS + r;  // output column = weight row
       const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * acc_cols;
       if (has_k) {
-        ok = dg_mbar_wait(dg_smem(&acc_full[a]), (item_i >> 1) & 1, abort_flag);
+        ok = mbar_wait(smem_u32(&acc_full[a]), (item_i >> 1) & 1, abort_flag);
         if (!ok) break;
-        dg_fence_after();
+        fence_after();
       }
       if (shape.splits == 1) {
         // one split: straight to the output
         for (int c = 0; c < shape.nb; c += 16) {
           uint32_t v[16], u[16];
-          dg_ld16(v, tmem_row + c);
-          if (MODE == 2) dg_ld16(u, tmem_row + shape.nb + c);
-          dg_wait_ld();
+          tmem_ld16(v, tmem_row + c);
+          if (MODE == 2) tmem_ld16(u, tmem_row + shape.nb + c);
+          tmem_wait_ld();
           if (n < shape.N) {
             // the residual values first, all sixteen loads in flight (a load may not pass a store that
             // could alias it: read-modify-write one value at a time would wait for each in turn)
@@ -352,11 +298,11 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         const int per = (DG_ROWS + shape.splits - 1) / shape.splits;
         const int owner = r / per, local = r - owner * per;
         uint32_t remote;
-        asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(dg_smem(recv)), "r"(owner));
+        asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(recv)), "r"(owner));
         remote += (uint32_t)((split * acc_cols * per + local) * 4);
         for (int c = 0; c < acc_cols; c += 16) {
           uint32_t v[16];
-          if (has_k) { dg_ld16(v, tmem_row + c); dg_wait_ld(); }
+          if (has_k) { tmem_ld16(v, tmem_row + c); tmem_wait_ld(); }
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)((c + j) * per * 4)),
@@ -367,7 +313,7 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         float* mine = partial + ((size_t)item * GROUPS) * DG_ROWS * shape.nb;
         for (int c = 0; c < acc_cols; c += 16) {
           uint32_t v[16];
-          if (has_k) { dg_ld16(v, tmem_row + c); dg_wait_ld(); }
+          if (has_k) { tmem_ld16(v, tmem_row + c); tmem_wait_ld(); }
           const int gr = c / shape.nb, col = c - gr * shape.nb;
           float4* dst4 = reinterpret_cast<float4*>(mine + ((size_t)gr * DG_ROWS + r) * shape.nb + col);
 #pragma unroll
@@ -378,8 +324,8 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         }
       }
       if (has_k) {
-        dg_fence_before();
-        dg_mbar_arrive(dg_smem(&acc_empty[a]));
+        fence_before();
+        mbar_arrive(smem_u32(&acc_empty[a]));
       }
       if (shape.splits > 1 && !shape.clustered) {
         // the block that brings a tile's last split adds the partials in split order
@@ -498,49 +444,16 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       }
     }
   }
-  dg_fence_before();
+  fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) XRT_TL(23);
   if (warp == 1) {
-    dg_fence_after();
+    fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(shape.tmem_cols));
   }
 }
 
-}  // namespace xrt
-XRT_EXPORT int xrt_gemm_decode_tcgen05_normed(void* out, const void* x, const void* w, float* partial, int* counters,
-                                              int M, int N, int K, int ldx, int ldo, int w_rows, int out_dtype, int mode,
-                                              int up_rows, int sm_count, int* error_flag, const float* squares,
-                                              int square_parts, float eps, cudaStream_t stream);
-XRT_TL_EXPORT(gemm_decode)
-namespace xrt {
-
-typedef CUresult (*DgEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static DgEncodeFn dg_encode() {
-  static DgEncodeFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<DgEncodeFn>(ptr);
-  }
-  return fn;
-}
-
 static bool dg_make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
-  DgEncodeFn encode = dg_encode();
-  if (encode == nullptr) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)DG_BK, (cuuint32_t)box_rows};
-  const cuuint32_t elem[2] = {1u, 1u};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return sm100::make_map_bf16_2d(map, base, rows, cols, ld, box_rows);
 }
 
 // Splits of K: more splits fill the multiprocessors more evenly when the tiles are few, but every
@@ -661,16 +574,9 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05_plan(int M, int N, int K, int mode, int s
 // xrt_gemm_stream.  partial: float32 scratch of xrt_gemm_decode_tcgen05_scratch floats (may be null
 // when that is 0); counters: int32 [at least ceil(N / 128)], zero before the first call (the
 // kernel leaves them zero).  error_flag (may be null) is set to 4 if a bounded wait ran out.
-XRT_EXPORT int xrt_gemm_decode_tcgen05(void* out, const void* x, const void* w, float* partial, int* counters, int M,
-                                       int N, int K, int ldx, int ldo, int w_rows, int out_dtype, int mode,
-                                       int up_rows, int sm_count, int* error_flag, cudaStream_t stream) {
-  return xrt_gemm_decode_tcgen05_normed(out, x, w, partial, counters, M, N, K, ldx, ldo, w_rows, out_dtype, mode, up_rows,
-                                        sm_count, error_flag, nullptr, 0, 0.f, stream);
-}
-
-// The same for an input whose RMSNorm the product before it prepared (xrt_gemm_stream_norm): x is the
-// residual times the norm weight, squares = float32 [square_parts, M] its partial sums of squares;
-// every batch row's result is multiplied by 1 / sqrt(sum of its parts / K + eps).  squares null: as above.
+// squares not null: the input's RMSNorm was prepared by the product before it (xrt_gemm_stream_norm):
+// x is the residual times the norm weight, squares = float32 [square_parts, M] its partial sums of
+// squares, and every batch row's result is multiplied by 1 / sqrt(sum of its parts / K + eps).
 XRT_EXPORT int xrt_gemm_decode_tcgen05_normed(void* out, const void* x, const void* w, float* partial, int* counters,
                                               int M, int N, int K, int ldx, int ldo, int w_rows, int out_dtype, int mode,
                                               int up_rows, int sm_count, int* error_flag, const float* squares,
@@ -725,4 +631,12 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05_normed(void* out, const void* x, const vo
   if (out_dtype == XRT_BF16)
     return xrt::launch_decode_gemm<0, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, stream);
   return xrt::launch_decode_gemm<0, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, stream);
+}
+
+// The same without a pending norm.
+XRT_EXPORT int xrt_gemm_decode_tcgen05(void* out, const void* x, const void* w, float* partial, int* counters, int M,
+                                       int N, int K, int ldx, int ldo, int w_rows, int out_dtype, int mode,
+                                       int up_rows, int sm_count, int* error_flag, cudaStream_t stream) {
+  return xrt_gemm_decode_tcgen05_normed(out, x, w, partial, counters, M, N, K, ldx, ldo, w_rows, out_dtype, mode, up_rows,
+                                        sm_count, error_flag, nullptr, 0, 0.f, stream);
 }

@@ -72,7 +72,6 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
   extern __shared__ __align__(128) unsigned char smem[];
 
   pdl_trigger();
-  if (threadIdx.x == 0) XRT_TL(30);
   // the weight of the norm that follows never changes: this thread's element of it is on its way now
   float emit_w = 0.f;
   if (MODE == 1 && emit.scaled != nullptr) {
@@ -112,7 +111,6 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
   // The weights do not depend on the step: the first slabs are on their way while the kernel before
   // this one finishes.  X and the output do: wait for it here.
   pdl_wait();
-  if (threadIdx.x == 0) XRT_TL(31);
   const __nv_bfloat16* xlo[M_TILES];
   const __nv_bfloat16* xhi[M_TILES];
 #pragma unroll
@@ -179,7 +177,6 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
       p[(g + 8) * P_ROW + 2 * t] = acc[gr][mt][2];
       p[(g + 8) * P_ROW + 2 * t + 1] = acc[gr][mt][3];
     }
-  if (threadIdx.x == 0) XRT_TL(32);
   __syncthreads();
   for (int e = threadIdx.x; e < M_TILES * 16 * BLOCK_ROWS; e += blockDim.x) {  // the same trips for a whole warp
     const int nb = e % BLOCK_ROWS, m = e / BLOCK_ROWS;
@@ -215,7 +212,6 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
       if (nb == 0 && m < M) emit.squares[(size_t)blockIdx.x * M + m] = square;
     }
   }
-  if (threadIdx.x == 0) XRT_TL(33);
 }
 
 template <int M_TILES, int MODE, int GS_STAGES, int ROW_GROUPS, typename TO>
@@ -264,28 +260,16 @@ int dispatch_stream(void* out, const void* x, const void* w, int M, int N, int K
 
 }  // namespace xrt
 
-XRT_TL_EXPORT(gemm_stream)
-
-XRT_EXPORT int xrt_gemm_stream_norm(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
-                                    int out_dtype, int mode, int up_rows, void* scaled, int ld_scaled,
-                                    const void* norm_weight, int norm_dtype, float* squares, cudaStream_t stream);
-
-// x: bfloat16 [M, K] with row stride ldx (a multiple of 8); w: bfloat16 [N, K] contiguous, K a
-// multiple of 8; out: [M, N] with row stride ldo.  mode 0 stores, 1 adds into a float32 out, 2 computes
-// silu(x . W[n]) * (x . W[n + up_rows]) for n < N.  M is at most 64.
-XRT_EXPORT int xrt_gemm_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
-                               int out_dtype, int mode, int up_rows, cudaStream_t stream) {
-  return xrt_gemm_stream_norm(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_rows, nullptr, 0, nullptr, XRT_F32, nullptr,
-                              stream);
-}
-
 // How many floats a batch row `squares` holds one of: the blocks of the launch (M at most 16).
 XRT_EXPORT int xrt_gemm_stream_norm_blocks(int M, int N) {
   if (M <= 0 || N <= 0 || M > 16) return XRT_ERR_UNSUPPORTED;
   return (N + xrt::GS_ROWS - 1) / xrt::GS_ROWS;
 }
 
-// The same; with mode 1 and `scaled` not null the product also prepares the norm that follows it (see
+// x: bfloat16 [M, K] with row stride ldx (a multiple of 8); w: bfloat16 [N, K] contiguous, K a
+// multiple of 8; out: [M, N] with row stride ldo.  mode 0 stores, 1 adds into a float32 out, 2 computes
+// silu(x . W[n]) * (x . W[n + up_rows]) for n < N.  M is at most 64.
+// With mode 1 and `scaled` not null the product also prepares the norm that follows it (see
 // the file's head): scaled = bfloat16 [M, ld_scaled] receives (new residual) * norm_weight ([N], in
 // norm_dtype), squares = float32 [xrt_gemm_stream_norm_blocks(M, N), M] the blocks' sums of squares.
 // Only for M <= 16 (one group of weight rows a block).
@@ -309,4 +293,11 @@ XRT_EXPORT int xrt_gemm_stream_norm(void* out, const void* x, const void* w, int
   if (M <= 16) return xrt::dispatch_stream<1>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, emit, stream);
   if (M <= 32) return xrt::dispatch_stream<2>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, emit, stream);
   return xrt::dispatch_stream<4>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, emit, stream);
+}
+
+// The same without a norm to prepare.
+XRT_EXPORT int xrt_gemm_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
+                               int out_dtype, int mode, int up_rows, cudaStream_t stream) {
+  return xrt_gemm_stream_norm(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_rows, nullptr, 0, nullptr, XRT_F32, nullptr,
+                              stream);
 }

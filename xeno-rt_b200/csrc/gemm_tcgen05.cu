@@ -22,11 +22,11 @@
 // Every output element is the sum over K in one fixed order, whatever M is.
 // Every wait on an mbarrier is bounded.  A wait that runs out raises the error flag and an abort
 // flag in shared memory; all roles leave their loops, the block frees its TMEM and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace xrt {
+
+using namespace sm100;
 
 constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_UMMA_K = 16;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;        // 16 KB: 128 rows of X, one slab of K
@@ -45,69 +45,6 @@ template <int MT> struct TcShape {
   static constexpr int SMEM = STAGES * STAGE_BYTES + STAGING_BYTES + 256 + 1024;  // + barriers + alignment slack
 };
 constexpr int TC_TMEM_COLS = 512;
-constexpr long long TC_SPIN_LIMIT = 1ll << 24;
-
-__device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void tc_mbar_init(uint32_t bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void tc_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void tc_mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// Bounded wait for the phase of the given parity.  False if it ran out or another role aborted.
-__device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (long long spin = 0; spin < TC_SPIN_LIMIT; ++spin) {
-    uint32_t done;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    if (done) return true;
-    if ((spin & 1023) == 1023 && *abort_flag) return false;
-  }
-  return false;
-}
-__device__ __forceinline__ void tc_tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-// Shared-memory matrix descriptor: K-major, 128-byte swizzle, rows 128 bytes apart, groups of
-// eight rows 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell).
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr) {
-  uint64_t desc = 0;
-  desc |= (uint64_t)((addr & 0x3FFFF) >> 4);          // start address, bits [0, 14)
-  desc |= (uint64_t)1 << 16;                          // leading byte offset (unused with swizzle), bits [16, 30)
-  desc |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset, bits [32, 46)
-  desc |= (uint64_t)1 << 46;                          // version, bits [46, 48)
-  desc |= (uint64_t)2 << 61;                          // layout type SWIZZLE_128B, bits [61, 64)
-  return desc;
-}
-// Instruction descriptor of kind::f16: bfloat16 A and B, float32 D, both K-major, M x N.
-__host__ __device__ constexpr uint32_t tc_instr_desc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-               " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-               ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_ld32(uint32_t (&r)[32], uint32_t addr) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-               : "r"(addr));
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Four consecutive outputs of one row: 16 bytes of float32 (stored, or added into the residual
 // stream) or 8 bytes of bfloat16.
@@ -159,18 +96,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   const int k_iters = (K + TC_BK - 1) / TC_BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < TC_STAGES; ++s) { tc_mbar_init(tc_smem(&full[s]), 1); tc_mbar_init(tc_smem(&empty[s]), 1); }
-    for (int a = 0; a < 2; ++a) { tc_mbar_init(tc_smem(&acc_full[a]), 1); tc_mbar_init(tc_smem(&acc_empty[a]), 32 * TcShape<MT>::EPI_WARPS); }
+    for (int s = 0; s < TC_STAGES; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&acc_full[a]), 1); mbar_init(smem_u32(&acc_empty[a]), 32 * TcShape<MT>::EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // the MMA warp owns the TMEM allocation
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(tmem_slot)), "r"(TC_TMEM_COLS));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TC_TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
-  tc_fence_before();
+  fence_before();
   __syncthreads();
-  tc_fence_after();
+  fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
@@ -184,18 +121,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         const int m_blk = tile % tiles_m, n_blk = tile / tiles_m;
         for (int kb = 0; kb < k_iters; ++kb, ++it) {
           const int s = it % TC_STAGES;
-          ok = tc_mbar_wait(tc_smem(&empty[s]), ((it / TC_STAGES) & 1) ^ 1, abort_flag);
+          ok = mbar_wait(smem_u32(&empty[s]), ((it / TC_STAGES) & 1) ^ 1, abort_flag);
           if (!ok) break;
-          const uint32_t bar = tc_smem(&full[s]);
-          tc_mbar_expect_tx(bar, STAGE_A + TC_B_BYTES);
+          const uint32_t bar = smem_u32(&full[s]);
+          mbar_arrive_expect_tx(bar, STAGE_A + TC_B_BYTES);
 #pragma unroll
           for (int h = 0; h < MT; ++h)
-            tc_tma_load_2d(tc_smem(a_stages + s * STAGE_A + h * TC_A_BYTES), &map_x, kb * TC_BK,
+            tma_load_2d(smem_u32(a_stages + s * STAGE_A + h * TC_A_BYTES), &map_x, kb * TC_BK,
                            (m_blk * MT + h) * TC_BM, bar);
           const int w_row0 = n_blk * N_PER_TILE;
           const int w_row1 = MODE == 2 ? up_rows + w_row0 : w_row0 + 128;
-          tc_tma_load_2d(tc_smem(b_stages + s * TC_B_BYTES), &map_w, kb * TC_BK, w_row0, bar);
-          tc_tma_load_2d(tc_smem(b_stages + s * TC_B_BYTES + TC_B_BYTES / 2), &map_w, kb * TC_BK, w_row1, bar);
+          tma_load_2d(smem_u32(b_stages + s * TC_B_BYTES), &map_w, kb * TC_BK, w_row0, bar);
+          tma_load_2d(smem_u32(b_stages + s * TC_B_BYTES + TC_B_BYTES / 2), &map_w, kb * TC_BK, w_row1, bar);
         }
       }
       if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 3); }
@@ -203,31 +140,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
-      constexpr uint32_t idesc = tc_instr_desc(TC_BM, TC_BN);
+      constexpr uint32_t idesc = instr_desc(TC_BM, TC_BN);
       int it = 0, tile_i = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tile_i) {
         const int a = tile_i % ACC_SETS;
-        ok = tc_mbar_wait(tc_smem(&acc_empty[a]), ((tile_i / ACC_SETS) & 1) ^ 1, abort_flag);
+        ok = mbar_wait(smem_u32(&acc_empty[a]), ((tile_i / ACC_SETS) & 1) ^ 1, abort_flag);
         if (!ok) break;
-        tc_fence_after();
+        fence_after();
         const uint32_t tmem_d = tmem_base + a * MT * TC_BN;
         for (int kb = 0; kb < k_iters; ++kb, ++it) {
           const int s = it % TC_STAGES;
-          ok = tc_mbar_wait(tc_smem(&full[s]), (it / TC_STAGES) & 1, abort_flag);
+          ok = mbar_wait(smem_u32(&full[s]), (it / TC_STAGES) & 1, abort_flag);
           if (!ok) break;
-          tc_fence_after();
-          const uint64_t desc_b = tc_smem_desc(tc_smem(b_stages + s * TC_B_BYTES));
+          fence_after();
+          const uint64_t desc_b = desc_k_major(smem_u32(b_stages + s * TC_B_BYTES));
 #pragma unroll
           for (int h = 0; h < MT; ++h) {
-            const uint64_t desc_a = tc_smem_desc(tc_smem(a_stages + s * STAGE_A + h * TC_A_BYTES));
+            const uint64_t desc_a = desc_k_major(smem_u32(a_stages + s * STAGE_A + h * TC_A_BYTES));
 #pragma unroll
             for (int k = 0; k < TC_BK / TC_UMMA_K; ++k)  // 32 bytes further along K inside the swizzle atom
-              tc_mma(tmem_d + h * TC_BN, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0);
+              mma_f16(tmem_d + h * TC_BN, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0);
           }
-          tc_commit(tc_smem(&empty[s]));
+          commit(smem_u32(&empty[s]));
         }
-        if (ok) tc_commit(tc_smem(&acc_full[a]));
+        if (ok) commit(smem_u32(&acc_full[a]));
       }
       if (!ok) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 3); }
     }
@@ -240,9 +177,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tile_i) {
       const int m_blk = tile % tiles_m, n_blk = tile / tiles_m;
       const int a = tile_i % ACC_SETS;
-      ok = tc_mbar_wait(tc_smem(&acc_full[a]), (tile_i / ACC_SETS) & 1, abort_flag);
+      ok = mbar_wait(smem_u32(&acc_full[a]), (tile_i / ACC_SETS) & 1, abort_flag);
       if (!ok) break;
-      tc_fence_after();
+      fence_after();
       const int row0 = (m_blk * MT + half) * TC_BM + quarter * 32;  // the warp's first row
       const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (a * MT + half) * TC_BN;
       const int col0 = n_blk * N_PER_TILE;
@@ -254,18 +191,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll 1
       for (int c = 0; c < N_PER_TILE; c += 32) {
         uint32_t v[32];
-        tc_ld32(v, tmem_row + c);
+        tmem_ld32(v, tmem_row + c);
         if (MODE == 2) {
           uint32_t u[32];
-          tc_ld32(u, tmem_row + TC_BN / 2 + c);
-          tc_wait_ld();
+          tmem_ld32(u, tmem_row + TC_BN / 2 + c);
+          tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float g = __uint_as_float(v[j]);
             v[j] = __float_as_uint((g / (1.0f + expf(-g))) * __uint_as_float(u[j]));
           }
         } else {
-          tc_wait_ld();
+          tmem_wait_ld();
         }
 #pragma unroll
         for (int j = 0; j < 32; ++j) patch[lane * 33 + j] = __uint_as_float(v[j]);
@@ -306,47 +243,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         }
         __syncwarp();
       }
-      tc_fence_before();
-      tc_mbar_arrive(tc_smem(&acc_empty[a]));
+      fence_before();
+      mbar_arrive(smem_u32(&acc_empty[a]));
     }
     if (!ok && lane == 0) { *abort_flag = 1; if (error_flag != nullptr) atomicExch(error_flag, 3); }
   }
 
-  tc_fence_before();
+  fence_before();
   __syncthreads();
   if (warp == 1) {
-    tc_fence_after();
+    fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_TMEM_COLS));
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
 // A map over a row-major bfloat16 matrix [rows, cols] with row stride ld, boxes of 128 rows x 64 columns.
 static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld) {
-  EncodeTiledFn encode = encode_tiled();
-  if (encode == nullptr) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, 128u};
-  const cuuint32_t elem[2] = {1u, 1u};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return sm100::make_map_bf16_2d(map, base, rows, cols, ld, 128);
 }
 
 template <int MODE, int MT, typename TO>

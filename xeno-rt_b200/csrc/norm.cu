@@ -53,9 +53,7 @@ rmsnorm_vec_kernel(TO* __restrict__ out, const float* __restrict__ x, const TW* 
     const int c = (threadIdx.x + i * NORM_THREADS) * 4;
     if (c < width) Vec4Of<TW>::load(w + c, wv[i]);
   }
-  if (threadIdx.x == 0) XRT_TL(10);
   pdl_wait();
-  if (threadIdx.x == 0) XRT_TL(11);
   const int r = blockIdx.x;
   const int src = rows != nullptr ? rows[r] : r;
   const float* xr = x + (size_t)src * width;
@@ -84,7 +82,6 @@ rmsnorm_vec_kernel(TO* __restrict__ out, const float* __restrict__ x, const TW* 
       store4(dst + c, y);
     }
   }
-  if (threadIdx.x == 0) XRT_TL(13);
 }
 
 // any width
@@ -111,7 +108,6 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
 
 }  // namespace xrt
 
-XRT_TL_EXPORT(norm)
 
 XRT_EXPORT int xrt_rmsnorm(void* out, const float* x, const void* weight, const int* rows, int n_rows,
                            int width, float eps, int weight_dtype, int out_dtype, cudaStream_t stream) {

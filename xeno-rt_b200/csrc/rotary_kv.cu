@@ -170,9 +170,7 @@ qk_rope_kv_write_128_kernel(
 #pragma unroll
     for (int j = 0; j < 4; ++j) { qn[j] = to_float(q_norm_w[4 * lane + j]); kn[j] = to_float(k_norm_w[4 * lane + j]); }
   }
-  if (threadIdx.x == 0) XRT_TL(40);
   pdl_wait();
-  if (threadIdx.x == 0) XRT_TL(41);
   // (cos, sin) of this lane's four pairs: dims 4 * (lane % 16) .. of the first half
   float c[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
   if (rope_half > 0 && slot >= 0) {
@@ -220,12 +218,10 @@ qk_rope_kv_write_128_kernel(
       store4_as(pool + (((size_t)block * n_kv_heads + head) * XRT_BLOCK_TOKENS + pos % XRT_BLOCK_TOKENS) * HD + 4 * lane, v);
     }
   }
-  if (threadIdx.x == 0) XRT_TL(43);
 }
 
 }  // namespace xrt
 
-XRT_TL_EXPORT(rope)
 
 XRT_EXPORT int xrt_rope_table(float* cos_sin, const int* pos, const float* freq, float scale, int n_tokens,
                               int half, cudaStream_t stream) {
