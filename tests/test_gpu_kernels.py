@@ -646,6 +646,40 @@ def test_a_product_prepares_the_norm_that_follows_and_the_next_product_finishes_
         o.gemm_stream(x, act, w_down, "store", norm=(scaled, w_norm, squares))
 
 
+@pytest.mark.parametrize("m", [129, 300, 1000])
+@pytest.mark.parametrize("width,inner,out_rows,norm_dtype", [(1032, 520, 392, torch.float32), (256, 2760, 1536, torch.bfloat16),
+                                                            (4096, 1024, 2048, torch.bfloat16)])
+def test_a_prompt_product_prepares_the_norm_that_follows_and_the_next_finishes_it(m, width, inner, out_rows, norm_dtype):
+    """The same for prompts: the tiled tcgen05 product adds into the residual and leaves residual * norm
+    weight and one partial sum of squares a tile of 256 columns; the next tiled product scales its rows."""
+    from xeno_rt_b200.csrc import ops as o
+    torch.manual_seed(m + width + inner)
+    eps = 1e-6
+    resid = torch.randn(m, width, device=DEV) * 2
+    act = (torch.randn(m, inner, device=DEV)).to(torch.bfloat16)
+    w_down = (torch.randn(width, inner, device=DEV) * 0.05).to(torch.bfloat16)
+    w_norm = (1 + 0.1 * torch.randn(width, device=DEV)).to(norm_dtype)
+    w_next = (torch.randn(2 * out_rows, width, device=DEV) * 0.05).to(torch.bfloat16)
+    x = resid.clone()
+    scaled = torch.full((m, width), 9.0, device=DEV, dtype=torch.bfloat16)
+    squares = torch.full((o.gemm_tcgen05_norm_parts(width), m), 9.0, device=DEV)
+    o.gemm_tcgen05(x, act, w_down, "accumulate", norm=(scaled, w_norm, squares))
+    plain = resid.clone()
+    o.gemm_tcgen05(plain, act, w_down, "accumulate")
+    assert torch.equal(x, plain) and rel(x, f64(resid) + f64(act) @ f64(w_down).T) < 1e-5
+    assert rel(scaled, f64(x) * f64(w_norm)) < 5e-3
+    assert rel(squares.sum(0), (f64(x) ** 2).sum(1)) < 1e-5
+    normed = pm.rmsnorm(f64(x), f64(w_norm), eps)
+    out = torch.empty(m, 2 * out_rows, device=DEV)
+    o.gemm_tcgen05(out, scaled, w_next, "store", squares=squares, eps=eps)
+    assert rel(out, normed @ f64(w_next).T) < 6e-3
+    act2 = torch.empty(m, out_rows, device=DEV, dtype=torch.bfloat16)
+    o.gemm_tcgen05(act2, scaled, w_next, "swiglu", up_rows=out_rows, squares=squares, eps=eps)
+    gate_up = normed @ f64(w_next).T
+    assert rel(act2, pm.swiglu(gate_up[:, :out_rows], gate_up[:, out_rows:])) < 1.2e-2
+    o.check_error_flag(DEV)
+
+
 def test_attention_prefill_tcgen05_scores_that_jump():
     """The kernel takes its exponents against a reference value that moves only when a row's maximum
     has outgrown it by more than 8 (in base 2), and then rescales what it has accumulated.  Here the

@@ -33,6 +33,28 @@ struct Tuning {
 };
 const Tuning& tuning();
 
+// A norm that is finished by the product after it.  A product that adds into the residual stream can
+// prepare the RMSNorm that follows (crates/xrt-kernels/src/cpu/rmsnorm.rs:26-43), so that no norm kernel
+// has to run between two products: beside the new residual it writes residual * norm weight in bfloat16
+// (the next product's operand) and, for every row, partial sums of squares of the new residual (NormEmit:
+// `squares` is [parts, rows]; what a part covers is the emitting kernel's business).  The next product
+// multiplies row m of its result by 1 / sqrt(sum of the row's parts / width + eps) (RowScale), since
+// W . ((x * inv) * w) = inv * (W . (x * w)).  The statistics are 32-bit sums over the 32-bit residual,
+// added in a fixed order.
+struct NormEmit {
+  __nv_bfloat16* scaled = nullptr;  // [M, ld] bfloat16: new residual * weight
+  const void* weight = nullptr;     // [N] norm weight, 32-bit or bfloat16
+  float* squares = nullptr;         // [parts, M]
+  int ld = 0;
+  int weight_dtype = XRT_F32;
+};
+struct RowScale {
+  const float* squares = nullptr;   // [parts, M], or null: the input is what it is
+  int parts = 0;
+  int width = 1;
+  float eps = 0.f;
+};
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -58,18 +58,6 @@ struct DecodeGemmShape {
   int clustered;     // the splits of a tile are one cluster; one item a block
 };
 
-// The RMSNorm of this product's input, when the product before it prepared it (gemm_stream.cu's head has
-// the arithmetic): X is then residual * norm weight, `squares` holds `parts` partial sums of squares for
-// every batch row ([parts, M]), and the epilogue multiplies batch row m's results by
-// 1 / sqrt(sum of its parts / width + eps).  The parts are added in a fixed order, in 32-bit, by the
-// epilogue warps while the weights stream.
-struct RowScale {
-  const float* squares = nullptr;
-  int parts = 0;
-  int width = 1;
-  float eps = 0.f;
-};
-
 // MODE 0: store, 1: add into float out, 2: SwiGLU.
 template <int MODE, typename TO>
 __global__ void __launch_bounds__(DG_THREADS, 1)

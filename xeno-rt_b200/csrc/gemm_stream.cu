@@ -18,13 +18,8 @@
 // are added in warp order: a row's result does not depend on the number of rows M.
 // Measured on a B200 with M = 8: 5.97 TB/s on the output matrix (1.05 GB), 5.2 TB/s on gate/up.
 //
-// A product that adds into the residual stream can also prepare the RMSNorm that follows it
-// (crates/xrt-kernels/src/cpu/rmsnorm.rs:26-43), so that no norm kernel has to run between two
-// products of a decode step: beside the new residual it writes residual * norm weight in bfloat16
-// (the next product's operand) and, for every batch row, the sum of squares of the new residual over
-// this block's weight rows (one float a block and batch row, summed by the next product in block
-// order).  That product multiplies its result by 1 / sqrt(mean square + eps): W . ((x * inv) * w) =
-// inv * (W . (x * w)), with the statistics in 32-bit from the 32-bit residual.
+// A product that adds into the residual stream can also prepare the RMSNorm that follows it (NormEmit,
+// common.cuh): here the parts of a row's sum of squares are one a block (its 8 or 16 weight rows).
 #include "common.cuh"
 
 namespace xrt {
@@ -45,15 +40,6 @@ __device__ __forceinline__ void gs_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-
-// What a residual-adding product writes for the norm that follows: see the file's head.
-struct NormEmit {
-  __nv_bfloat16* scaled = nullptr;  // [M, ld] bfloat16: new residual * weight
-  const void* weight = nullptr;     // [N] norm weight, 32-bit or bfloat16
-  float* squares = nullptr;         // [blocks, M]: this block's sum of squares of each batch row
-  int ld = 0;
-  int weight_dtype = XRT_F32;
-};
 
 // MODE 0: store, 1: add into float out, 2: SwiGLU (two groups of rows: gate and up)
 template <int M_TILES, int MODE, int GS_STAGES, int ROW_GROUPS, typename TO>

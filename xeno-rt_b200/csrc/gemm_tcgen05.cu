@@ -72,7 +72,8 @@ __device__ __forceinline__ void store_quad(__nv_bfloat16* dst, float a, float b,
 template <int MODE, int MT, typename TO>
 __global__ void __launch_bounds__(TcShape<MT>::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                    TO* __restrict__ out, int M, int N, int K, int ldo, int up_rows, int* __restrict__ error_flag) {
+                    TO* __restrict__ out, int M, int N, int K, int ldo, int up_rows, int* __restrict__ error_flag,
+                    const NormEmit emit, const RowScale scale) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int TC_STAGES = TcShape<MT>::STAGES, ACC_SETS = TcShape<MT>::ACC_SETS;
@@ -177,10 +178,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tile_i) {
       const int m_blk = tile % tiles_m, n_blk = tile / tiles_m;
       const int a = tile_i % ACC_SETS;
+      const int row0 = (m_blk * MT + half) * TC_BM + quarter * 32;  // the warp's first row
+      // a pending norm of the input (RowScale): this lane's row's 1 / rms, from the parts the product before
+      // this one left, added in part order while the tile's products still run
+      float row_inv = 1.f;
+      if (MODE != 1 && scale.squares != nullptr) {
+        float sum = 0.f;
+        if (row0 + lane < M)
+          for (int p = 0; p < scale.parts; ++p) sum += __ldcg(scale.squares + (size_t)p * M + row0 + lane);
+        row_inv = 1.0f / sqrtf(sum / (float)scale.width + scale.eps);
+      }
       ok = mbar_wait(smem_u32(&acc_full[a]), (tile_i / ACC_SETS) & 1, abort_flag);
       if (!ok) break;
       fence_after();
-      const int row0 = (m_blk * MT + half) * TC_BM + quarter * 32;  // the warp's first row
       const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (a * MT + half) * TC_BN;
       const int col0 = n_blk * N_PER_TILE;
       // A thread holds one ROW of the accumulator; written as it is, every store instruction of the
@@ -188,6 +198,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       // writes it with 16 bytes a lane, four whole 128-byte row pieces an instruction.
       float* patch = staging + (warp - 2) * 32 * 33;
       const int sub_row = lane >> 3, sub_col = (lane & 7) * 4;
+      float squares[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // of rows it * 4 + sub_row, this lane's columns
 #pragma unroll 1
       for (int c = 0; c < N_PER_TILE; c += 32) {
         uint32_t v[32];
@@ -198,11 +209,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const float g = __uint_as_float(v[j]);
-            v[j] = __float_as_uint((g / (1.0f + expf(-g))) * __uint_as_float(u[j]));
+            const float g = __uint_as_float(v[j]) * row_inv;
+            v[j] = __float_as_uint((g / (1.0f + expf(-g))) * (__uint_as_float(u[j]) * row_inv));
           }
         } else {
           tmem_wait_ld();
+          if (MODE == 0 && scale.squares != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * row_inv);
+          }
         }
 #pragma unroll
         for (int j = 0; j < 32; ++j) patch[lane * 33 + j] = __uint_as_float(v[j]);
@@ -227,9 +242,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           if (row < M) {
             TO* dst = out + (size_t)row * ldo + col;
             if (col + 3 < N && (((uintptr_t)dst) & (4 * sizeof(TO) - 1)) == 0) {
-              if (MODE == 1)
-                store_quad<0>(dst, old[it].x + src[0], old[it].y + src[1], old[it].z + src[2], old[it].w + src[3]);
-              else
+              if (MODE == 1) {
+                const float4 sum = make_float4(old[it].x + src[0], old[it].y + src[1], old[it].z + src[2], old[it].w + src[3]);
+                store_quad<0>(dst, sum.x, sum.y, sum.z, sum.w);
+                if (emit.scaled != nullptr) {  // the launcher made sure that N is a multiple of 4 and the buffers aligned
+                  float w4[4];
+                  if (emit.weight_dtype == XRT_BF16) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(emit.weight) + col);
+                    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+                    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+                    w4[0] = __low2float(lo); w4[1] = __high2float(lo); w4[2] = __low2float(hi); w4[3] = __high2float(hi);
+                  } else {
+                    const float4 raw = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(emit.weight) + col);
+                    w4[0] = raw.x; w4[1] = raw.y; w4[2] = raw.z; w4[3] = raw.w;
+                  }
+                  store_quad<0>(emit.scaled + (size_t)row * emit.ld + col, sum.x * w4[0], sum.y * w4[1], sum.z * w4[2], sum.w * w4[3]);
+                  squares[it] = fmaf(sum.x, sum.x, squares[it]);
+                  squares[it] = fmaf(sum.y, sum.y, squares[it]);
+                  squares[it] = fmaf(sum.z, sum.z, squares[it]);
+                  squares[it] = fmaf(sum.w, sum.w, squares[it]);
+                }
+              } else
                 store_quad<0>(dst, src[0], src[1], src[2], src[3]);
             } else {
 #pragma unroll
@@ -242,6 +275,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           }
         }
         __syncwarp();
+      }
+      if (MODE == 1 && emit.squares != nullptr) {
+        // a row's columns of this tile sit in eight neighbouring lanes: summed in a fixed order, one part a tile of columns
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          float sum = squares[it];
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+          const int row = row0 + it * 4 + sub_row;
+          if ((lane & 7) == 0 && row < M) emit.squares[(size_t)n_blk * M + row] = sum;
+        }
       }
       fence_before();
       mbar_arrive(smem_u32(&acc_empty[a]));
@@ -264,7 +309,8 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int
 
 template <int MODE, int MT, typename TO>
 int launch_tcgen05_tiled(void* out, const CUtensorMap& map_x, const CUtensorMap& map_w, int M, int N, int K, int ldo,
-                         int up_rows, int* error_flag, int sm_count, cudaStream_t stream) {
+                         int up_rows, int* error_flag, int sm_count, const NormEmit& emit, const RowScale& scale,
+                         cudaStream_t stream) {
   auto kernel = gemm_tcgen05_kernel<MODE, MT, TO>;
   static bool allowed = false;
   if (!allowed) {
@@ -275,8 +321,9 @@ int launch_tcgen05_tiled(void* out, const CUtensorMap& map_x, const CUtensorMap&
   constexpr int n_per_tile = MODE == 2 ? TC_BN / 2 : TC_BN;
   const int tiles = ((M + MT * TC_BM - 1) / (MT * TC_BM)) * ((N + n_per_tile - 1) / n_per_tile);
   const int blocks = tiles < sm_count ? tiles : sm_count;
+  // (no programmatic dependent launch: see attention_prefill_tcgen05.cu's launcher)
   kernel<<<blocks, TcShape<MT>::THREADS, TcShape<MT>::SMEM, stream>>>(map_x, map_w, (TO*)out, M, N, K, ldo, up_rows,
-                                                                      error_flag);
+                                                                      error_flag, emit, scale);
   return launch_status();
 }
 
@@ -286,7 +333,8 @@ int launch_tcgen05_tiled(void* out, const CUtensorMap& map_x, const CUtensorMap&
 // Tuning::gemm_tile_rows = 128 or 256 forces one, for comparison.
 template <int MODE, typename TO>
 int launch_tcgen05(void* out, const CUtensorMap& map_x, const CUtensorMap& map_w, int M, int N, int K, int ldo,
-                   int up_rows, int* error_flag, int sm_count, cudaStream_t stream) {
+                   int up_rows, int* error_flag, int sm_count, const NormEmit& emit, const RowScale& scale,
+                   cudaStream_t stream) {
   constexpr int n_per_tile = MODE == 2 ? TC_BN / 2 : TC_BN;
   const long long tiles_n = (N + n_per_tile - 1) / n_per_tile;
   auto busy = [&](long long tiles) { return (double)tiles / (double)(((tiles + sm_count - 1) / sm_count) * sm_count); };
@@ -296,24 +344,49 @@ int launch_tcgen05(void* out, const CUtensorMap& map_x, const CUtensorMap& map_w
   // measured at 2,048 and 8,192 rows: the large tile wins where the small one leaves under two rounds of work
   const bool use_large = forced == 256 || (forced != 128 && M > 128 && small_tiles <= 2 * sm_count && large > small);
   if (use_large)
-    return launch_tcgen05_tiled<MODE, 2, TO>(out, map_x, map_w, M, N, K, ldo, up_rows, error_flag, sm_count, stream);
-  return launch_tcgen05_tiled<MODE, 1, TO>(out, map_x, map_w, M, N, K, ldo, up_rows, error_flag, sm_count, stream);
+    return launch_tcgen05_tiled<MODE, 2, TO>(out, map_x, map_w, M, N, K, ldo, up_rows, error_flag, sm_count, emit, scale, stream);
+  return launch_tcgen05_tiled<MODE, 1, TO>(out, map_x, map_w, M, N, K, ldo, up_rows, error_flag, sm_count, emit, scale, stream);
 }
 
 }  // namespace xrt
+
+// How many parts of a row's sum of squares a product that prepares the following norm leaves: one a tile
+// of 256 output columns.
+XRT_EXPORT int xrt_gemm_tcgen05_norm_parts(int N) { return N <= 0 ? XRT_ERR_ARGUMENT : (N + xrt::TC_BN - 1) / xrt::TC_BN; }
 
 // x: bfloat16 [M, K] with row stride ldx; w: bfloat16 [rows, K] contiguous; K and ldx multiples of 8,
 // both bases 16-byte aligned.  out: [M, N] with row stride ldo.  mode 0 stores, 1 adds into a float32
 // out, 2 computes silu(x . W[n]) * (x . W[n + up_rows]) for n < N (W then has up_rows + N rows).
 // error_flag (may be null) is set to 3 if a bounded wait inside the kernel ran out.
-XRT_EXPORT int xrt_gemm_tcgen05(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
-                                int w_rows, int out_dtype, int mode, int up_rows, int* error_flag,
-                                cudaStream_t stream) {
+// A norm that the next product finishes (common.cuh, NormEmit and RowScale).  With mode 1 and `scaled`
+// not null (bfloat16 [M, ld_scaled], N a multiple of 4, 16-byte aligned like norm_weight [N] in norm_dtype and
+// out) the product also writes (new out) * norm_weight there and the rows' sums of squares, one part a
+// tile of 256 columns, into squares = float32 [xrt_gemm_tcgen05_norm_parts(N), M].  With mode 0 or 2 and
+// in_squares not null (float32 [in_parts, M]) x is such a prepared input: row m of the result is
+// multiplied by 1 / sqrt(sum of the row's parts / K + eps).
+XRT_EXPORT int xrt_gemm_tcgen05_normed(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
+                                       int w_rows, int out_dtype, int mode, int up_rows, int* error_flag, void* scaled,
+                                       int ld_scaled, const void* norm_weight, int norm_dtype, float* squares,
+                                       const float* in_squares, int in_parts, float eps, cudaStream_t stream) {
   if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldo < N || mode < 0 || mode > 2) return XRT_ERR_ARGUMENT;
   if (mode == 1 && out_dtype != XRT_F32) return XRT_ERR_ARGUMENT;
   if (mode == 2 ? w_rows < up_rows + N : w_rows < N) return XRT_ERR_ARGUMENT;
   if (out_dtype != XRT_F32 && out_dtype != XRT_BF16) return XRT_ERR_UNSUPPORTED;
   if (K % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return XRT_ERR_UNSUPPORTED;
+  xrt::NormEmit emit;
+  xrt::RowScale scale;
+  if (scaled != nullptr) {
+    if (mode != 1 || norm_weight == nullptr || squares == nullptr || ld_scaled < N) return XRT_ERR_ARGUMENT;
+    if (N % 4 != 0 || ldo % 4 != 0 || ld_scaled % 4 != 0 || (norm_dtype != XRT_F32 && norm_dtype != XRT_BF16) ||
+        (((uintptr_t)scaled | (uintptr_t)norm_weight | (uintptr_t)out) & 15) != 0)
+      return XRT_ERR_UNSUPPORTED;
+    emit.scaled = (__nv_bfloat16*)scaled; emit.weight = norm_weight; emit.squares = squares;
+    emit.ld = ld_scaled; emit.weight_dtype = norm_dtype;
+  }
+  if (in_squares != nullptr) {
+    if (mode == 1 || in_parts <= 0) return XRT_ERR_ARGUMENT;
+    scale.squares = in_squares; scale.parts = in_parts; scale.width = K; scale.eps = eps;
+  }
   if (M == 0) return XRT_OK;
   static int sm_count = 0;
   if (sm_count == 0) {
@@ -324,13 +397,22 @@ XRT_EXPORT int xrt_gemm_tcgen05(void* out, const void* x, const void* w, int M, 
   }
   CUtensorMap map_x, map_w;
   if (!xrt::make_map(&map_x, x, M, K, ldx) || !xrt::make_map(&map_w, w, w_rows, K, K)) return XRT_ERR_UNSUPPORTED;
-  if (mode == 1) return xrt::launch_tcgen05<1, float>(out, map_x, map_w, M, N, K, ldo, 0, error_flag, sm_count, stream);
+  if (mode == 1)
+    return xrt::launch_tcgen05<1, float>(out, map_x, map_w, M, N, K, ldo, 0, error_flag, sm_count, emit, scale, stream);
   if (mode == 2) {
     if (out_dtype == XRT_BF16)
-      return xrt::launch_tcgen05<2, __nv_bfloat16>(out, map_x, map_w, M, N, K, ldo, up_rows, error_flag, sm_count, stream);
-    return xrt::launch_tcgen05<2, float>(out, map_x, map_w, M, N, K, ldo, up_rows, error_flag, sm_count, stream);
+      return xrt::launch_tcgen05<2, __nv_bfloat16>(out, map_x, map_w, M, N, K, ldo, up_rows, error_flag, sm_count, emit, scale, stream);
+    return xrt::launch_tcgen05<2, float>(out, map_x, map_w, M, N, K, ldo, up_rows, error_flag, sm_count, emit, scale, stream);
   }
   if (out_dtype == XRT_BF16)
-    return xrt::launch_tcgen05<0, __nv_bfloat16>(out, map_x, map_w, M, N, K, ldo, 0, error_flag, sm_count, stream);
-  return xrt::launch_tcgen05<0, float>(out, map_x, map_w, M, N, K, ldo, 0, error_flag, sm_count, stream);
+    return xrt::launch_tcgen05<0, __nv_bfloat16>(out, map_x, map_w, M, N, K, ldo, 0, error_flag, sm_count, emit, scale, stream);
+  return xrt::launch_tcgen05<0, float>(out, map_x, map_w, M, N, K, ldo, 0, error_flag, sm_count, emit, scale, stream);
+}
+
+// The same without a norm on either side.
+XRT_EXPORT int xrt_gemm_tcgen05(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
+                                int w_rows, int out_dtype, int mode, int up_rows, int* error_flag,
+                                cudaStream_t stream) {
+  return xrt_gemm_tcgen05_normed(out, x, w, M, N, K, ldx, ldo, w_rows, out_dtype, mode, up_rows, error_flag, nullptr, 0,
+                                 nullptr, XRT_F32, nullptr, nullptr, 0, 0.f, stream);
 }

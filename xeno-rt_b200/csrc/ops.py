@@ -36,6 +36,7 @@ _SIGNATURES = {
     "xrt_gemm_reference": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_stream_norm": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P, _P],
+    "xrt_gemm_tcgen05_normed": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _I, _P, _P, _I, _F, _P],
     "xrt_gemm_decode_tcgen05_normed": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P],
     "xrt_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_gemm_decode_tcgen05": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -72,6 +73,8 @@ def library():
                 fn.restype = _I
             lib.xrt_attention_decode_fused_max_splits.argtypes = [_I, _I]
             lib.xrt_attention_decode_fused_max_splits.restype = _I
+            lib.xrt_gemm_tcgen05_norm_parts.argtypes = [_I]
+            lib.xrt_gemm_tcgen05_norm_parts.restype = _I
             lib.xrt_gemm_stream_norm_blocks.argtypes = [_I, _I]
             lib.xrt_gemm_stream_norm_blocks.restype = _I
             lib.xrt_set_tuning.argtypes = [_I, _I]
@@ -408,9 +411,16 @@ def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, square
         "gemm_decode_tcgen05")
 
 
-def gemm_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
+def gemm_tcgen05_norm_parts(n: int) -> int:
+    """How many partial sums of squares a row ``gemm_tcgen05(..., norm=...)`` leaves (host arithmetic)."""
+    return library().xrt_gemm_tcgen05_norm_parts(int(n))
+
+
+def gemm_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, norm=None, squares=None, eps: float = 0.0) -> None:
     """bfloat16 product for many rows on the tcgen05 tensor cores with TMA-fed operands; modes as
-    for ``gemm_stream``."""
+    for ``gemm_stream``.  ``norm`` = (scaled, weight, squares) with "accumulate": the product prepares the
+    RMSNorm that follows it (as ``gemm_stream`` does; ``squares`` is float32 [gemm_tcgen05_norm_parts(n), m]).
+    ``squares`` (with "store" or "swiglu"): ``x`` is such a prepared input (as for ``gemm_decode_tcgen05``)."""
     m, k = x.shape
     n = out.shape[1]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -422,9 +432,20 @@ def gemm_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0) -> None:
         raise KernelError("gemm_tcgen05: rows must be contiguous and on a CUDA device")
     code = {"store": 0, "accumulate": 1, "swiglu": 2}[mode]
     flag = error_flag(x.device)
-    _check(_kernels().xrt_gemm_tcgen05(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
-                                      w.shape[0], _code(out.dtype), code, up_rows, flag.data_ptr(), _stream()),
-           "gemm_tcgen05")
+    scaled = weight = emitted = None
+    if norm is not None:
+        scaled, weight, emitted = norm
+        if (mode != "accumulate" or scaled.shape != (m, n) or scaled.stride(1) != 1 or weight.numel() != n
+                or tuple(emitted.shape) != (gemm_tcgen05_norm_parts(n), m)):
+            raise KernelError("gemm_tcgen05: the buffers of the following norm do not fit the product")
+    if squares is not None and (mode == "accumulate" or squares.dim() != 2 or squares.shape[1] != m):
+        raise KernelError("gemm_tcgen05: squares must be [parts, rows], and not with accumulate")
+    _check(_kernels().xrt_gemm_tcgen05_normed(
+        out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0), w.shape[0], _code(out.dtype), code,
+        up_rows, flag.data_ptr(), _ptr(scaled, "scaled", torch.bfloat16), 0 if scaled is None else scaled.stride(0),
+        _ptr(weight, "weight"), _code(weight.dtype) if weight is not None else 0, _ptr(emitted, "squares", torch.float32),
+        _ptr(squares, "squares", torch.float32), 0 if squares is None else squares.shape[0], float(eps), _stream()),
+        "gemm_tcgen05")
 
 
 STREAM_NORM_MAX_ROWS = 16

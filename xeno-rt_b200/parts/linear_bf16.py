@@ -63,7 +63,11 @@ def takes_pending(rows: int, n: int, k: int, mode: str, device) -> bool:
     """Whether a product of these sizes would run on the kernel that can finish a pending norm (the
     tcgen05 few-row product), so that the product before it may prepare the norm instead of a kernel."""
     wish = ops.tuning().pending_norm
-    if rows > ops.DECODE_TCGEN05_MAX_ROWS or k % 8 or wish == "off" or (ops.tuning().decode_gemm == "stream" and wish != "force"):
+    if k % 8 or wish == "off":
+        return False
+    if rows > ops.DECODE_TCGEN05_MAX_ROWS:
+        return True  # the tiled tcgen05 product of prompts
+    if ops.tuning().decode_gemm == "stream" and wish != "force":
         return False
     if rows > STREAM_ROWS or ops.tuning().decode_gemm == "tcgen05" or wish == "force":
         return True
@@ -72,8 +76,8 @@ def takes_pending(rows: int, n: int, k: int, mode: str, device) -> bool:
 
 def run_pending(out, pending, weight, up_rows: int = 0) -> None:
     """out = the product of a pending norm's result with weight^T (SwiGLU with ``up_rows``)."""
-    ops.gemm_decode_tcgen05(out, pending.scaled, weight, "swiglu" if up_rows else "store", up_rows,
-                            squares=pending.squares, eps=pending.eps)
+    kernel = ops.gemm_decode_tcgen05 if pending.shape[0] <= ops.DECODE_TCGEN05_MAX_ROWS else ops.gemm_tcgen05
+    kernel(out, pending.scaled, weight, "swiglu" if up_rows else "store", up_rows, squares=pending.squares, eps=pending.eps)
 
 
 def run_with_norm(out, x, weight, norm):
@@ -81,6 +85,13 @@ def run_with_norm(out, x, weight, norm):
     or None when the kernel that takes this product cannot do that (the caller then runs it plainly)."""
     from .norm import PendingNorm, RMSNorm
     rows, n = x.shape[0], out.shape[1]
+    if (isinstance(norm, RMSNorm) and norm.width == n and aligned(x, weight) and rows > ops.DECODE_TCGEN05_MAX_ROWS
+            and n % 4 == 0 and out.is_contiguous() and ops.tuning().pending_norm != "off"
+            and norm.weight.data_ptr() % 16 == 0):  # a prompt: the tiled tcgen05 product
+        scaled = torch.empty((rows, n), dtype=torch.bfloat16, device=x.device)
+        squares = torch.empty((ops.gemm_tcgen05_norm_parts(n), rows), dtype=torch.float32, device=x.device)
+        ops.gemm_tcgen05(out, x, weight, "accumulate", norm=(scaled, norm.weight, squares))
+        return PendingNorm(scaled, squares, norm.eps, norm)
     if (not isinstance(norm, RMSNorm) or norm.width != n or not aligned(x, weight) or rows > ops.STREAM_NORM_MAX_ROWS
             or (ops.tuning().decode_gemm == "tcgen05" and ops.tuning().pending_norm != "force") or not out.is_contiguous()
             or ops.tuning().pending_norm == "off"):
