@@ -311,6 +311,8 @@ def run_ours(args) -> int:
     cfg = dict(shape_cfg)
     full_layers = cfg["num_hidden_layers"]
     cfg["num_hidden_layers"] = args.layers or full_layers
+    # the positions the run needs (rotary tables are computed, not stored: only the cache's limit moves)
+    cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], args.context, args.prefill_tokens)
     n_layers = cfg["num_hidden_layers"]
     pk = peaks()
     t0 = time.time()
