@@ -395,6 +395,15 @@ def test_attention_decode_from_the_product_of_q_k_v(nh, nkv, hd, qk_norm, rotate
                                tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd), 0, chunk, n_splits, write_kv=False, fused=fused)
     assert torch.equal(k_pool, before_k) and torch.equal(v_pool, before_v)
     assert rel(again[live], f64(out[live])) < 1e-2
+    # a window of 100 keys (the newest key is its last): against the two kernels on the same cache
+    ops().attention_decode(two, q2, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd), 100, chunk,
+                           n_splits, fused=fused)
+    ops().attention_decode_qkv(again, qkv, qw, qw + kw, qn, kn, 1e-6, cs, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd,
+                               1 / math.sqrt(hd), 100, chunk, n_splits, write_kv=False, fused=fused)
+    assert rel(again[live], f64(two[live])) < 2e-2
+    ref = torch.empty_like(two)
+    ops().attention_reference(ref, q2, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd), window=100)
+    assert rel(again[live], f64(ref[live])) < 2e-2
 
 
 def test_attention_decode_finds_a_far_key_and_respects_the_window():
