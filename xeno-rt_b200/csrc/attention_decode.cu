@@ -418,6 +418,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __syncthreads();
 
   const int* blocks = block_table + (size_t)slot * max_blocks;
+  // keys and values are read once a step: their lines are the first to leave the L2
+  const uint64_t once = sm100::policy_evict_first();
   auto issue_tile = [&](int tile_index, int buffer) {  // one thread
     const int key0 = begin + tile_index * XRT_BLOCK_TOKENS;
     const int row0 = (blocks[key0 / XRT_BLOCK_TOKENS] * n_kv_heads + kv_head) * XRT_BLOCK_TOKENS;
@@ -426,11 +428,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     // one copy a tile: the map's third dimension walks the row's pieces of 64 dims, so that the boxes of 64 rows x
     // 128 bytes land one behind the other (a copy instruction costs the thread that issues it about 200 cycles,
     // and this thread's warp has its 16 keys to work on like the others)
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                 ::"r"(smem_addr(k_tiles + buffer * tile_bytes)), "l"(&map_k), "r"(0), "r"(row0), "r"(0), "r"(full_addr[buffer])
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+                 ::"r"(smem_addr(k_tiles + buffer * tile_bytes)), "l"(&map_k), "r"(0), "r"(row0), "r"(0), "r"(full_addr[buffer]), "l"(once)
                  : "memory");
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                 ::"r"(smem_addr(v_tiles + buffer * tile_bytes)), "l"(&map_v), "r"(0), "r"(row0), "r"(0), "r"(full_addr[buffer])
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+                 ::"r"(smem_addr(v_tiles + buffer * tile_bytes)), "l"(&map_v), "r"(0), "r"(row0), "r"(0), "r"(full_addr[buffer]), "l"(once)
                  : "memory");
   };
 

@@ -46,6 +46,21 @@ __device__ __forceinline__ void dg_cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// Weight rows of a tile that one block of a cluster finishes: ceil(128 / splits), rounded up to a
+// multiple of 4 so that a thread can take four rows at once; the last block has the remainder.
+__host__ __device__ inline int dg_rows_per_block(int splits) { return ((DG_ROWS + splits - 1) / splits + 3) & ~3; }
+
+__device__ __forceinline__ void store_four(float* dst, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store_four(__nv_bfloat16* dst, const float (&v)[4]) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 packed;
+  packed.x = *reinterpret_cast<uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
 struct DecodeGemmShape {
   int M, N, K, ldo;
   int nb;            // batch rows padded to a multiple of 16: the MMA's N
@@ -136,12 +151,16 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       walk.item = blockIdx.x;
       if (walk.item < n_items) walk.enter(shape, k_iters_total);
       const uint32_t w_bytes = GROUPS * DG_W_BYTES;
+      // a weight is read once a step: its lines leave the L2 first, and what the step reads again
+      // (activations, the residual, the partial sums, the kernels' code) stays (measured at the
+      // 8B shape, context 4096: 4 to 7 percent of a step of 17 to 64 sequences)
+      const uint64_t once = policy_evict_first();
       auto load_w = [&](const Walk& at, int s) {
         const uint32_t bar = smem_u32(&full[s]);
         unsigned char* stage = smem + (size_t)s * stage_bytes;
         mbar_arrive_expect_tx(bar, w_bytes);
-        tma_load_2d(smem_u32(stage), &map_w, at.kb() * DG_BK, at.tile * DG_ROWS, bar);
-        if (MODE == 2) tma_load_2d(smem_u32(stage + DG_W_BYTES), &map_w, at.kb() * DG_BK, shape.up_rows + at.tile * DG_ROWS, bar);
+        tma_load_2d(smem_u32(stage), &map_w, at.kb() * DG_BK, at.tile * DG_ROWS, bar, once);
+        if (MODE == 2) tma_load_2d(smem_u32(stage + DG_W_BYTES), &map_w, at.kb() * DG_BK, shape.up_rows + at.tile * DG_ROWS, bar, once);
       };
       auto load_x = [&](const Walk& at, int s) {
         const uint32_t bar = smem_u32(&full[s]);
@@ -283,7 +302,7 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         // This split's sums go to the blocks of the cluster that finish them: block d of the cluster owns
         // rows d * per .. of the tile, and keeps one slot a split, [slot][accumulator column][row], in a
         // part of its shared memory that its own ring never uses.  Remote stores, no reply awaited.
-        const int per = (DG_ROWS + shape.splits - 1) / shape.splits;
+        const int per = dg_rows_per_block(shape.splits);
         const int owner = r / per, local = r - owner * per;
         uint32_t remote;
         asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(recv)), "r"(owner));
@@ -391,43 +410,81 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       uint32_t rank;
       asm("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
       const int tile = blockIdx.x / shape.splits;
-      const int per = (DG_ROWS + shape.splits - 1) / shape.splits;
+      const int per = dg_rows_per_block(shape.splits);
       const int row_lo = (int)rank * per;
       const int rows_here = max(0, min(per, DG_ROWS - row_lo));
-      const int total = rows_here * shape.M;
       const int slot_floats = acc_cols * per;
-      constexpr int UNROLL = 4;
-      for (int base = threadIdx.x - 64; base < total; base += 128 * UNROLL) {
-        float old[UNROLL], sums[UNROLL][GROUPS], inv[UNROLL];
-        size_t at[UNROLL];
-        bool live[UNROLL];
+      const int n_lo = tile * DG_ROWS + row_lo;
+      // Four weight rows a thread where the output allows it (16 bytes of shared memory a split, one
+      // load and one store of four outputs): the four warps have little else to hide latency behind,
+      // so the loop's cost is its instruction count.  per, row_lo and rows_here are multiples of 4.
+      const bool by_four = shape.N % 4 == 0 && shape.ldo % 4 == 0 && ((uintptr_t)out & (sizeof(TO) * 4 - 1)) == 0;
+      if (by_four) {
+        const int quads = rows_here / 4;
+        const int total = quads * shape.M;
+        constexpr int UNROLL = 4;
+        for (int base = threadIdx.x - 64; base < total; base += 128 * UNROLL) {
+          float4 old[UNROLL], sums[UNROLL][GROUPS];
+          int m_of[UNROLL], n_of[UNROLL];
+          bool live[UNROLL];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-          const int idx = base + u * 128;
-          const int m = idx / rows_here, local = idx - m * rows_here;
-          inv[u] = (scale.squares != nullptr && idx < total) ? row_inv[m] : 1.f;
-          const int n = tile * DG_ROWS + row_lo + local;
-          live[u] = idx < total && n < shape.N;
-          at[u] = (size_t)m * shape.ldo + n;
-          old[u] = (MODE == 1 && live[u]) ? __ldcg(reinterpret_cast<const float*>(out) + at[u]) : 0.f;
+          for (int u = 0; u < UNROLL; ++u) {
+            const int idx = base + u * 128;
+            const int m = idx / quads, local = (idx - m * quads) * 4;
+            m_of[u] = m;
+            n_of[u] = n_lo + local;
+            live[u] = idx < total && n_of[u] < shape.N;
+            old[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (MODE == 1 && live[u])
+              old[u] = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(out) + (size_t)m * shape.ldo + n_of[u]));
 #pragma unroll
-          for (int gr = 0; gr < GROUPS; ++gr) {
-            float t = 0.f;
-            if (live[u]) {
-              const float* mine = recv + (size_t)(gr * shape.nb + m) * per + local;
-              for (int sp = 0; sp < shape.splits; ++sp) t += mine[(size_t)sp * slot_floats];
+            for (int gr = 0; gr < GROUPS; ++gr) {
+              float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (live[u]) {
+                const float* mine = recv + (size_t)(gr * shape.nb + m) * per + local;
+                for (int sp = 0; sp < shape.splits; ++sp) {
+                  const float4 part = *reinterpret_cast<const float4*>(mine + (size_t)sp * slot_floats);
+                  t.x += part.x; t.y += part.y; t.z += part.z; t.w += part.w;
+                }
+              }
+              sums[u][gr] = t;
             }
-            sums[u][gr] = t;
+          }
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            if (!live[u]) continue;
+            const float inv = scale.squares != nullptr ? row_inv[m_of[u]] : 1.f;
+            float val[4] = {sums[u][0].x * inv, sums[u][0].y * inv, sums[u][0].z * inv, sums[u][0].w * inv};
+            if (MODE == 2) {
+              const float4 up = sums[u][GROUPS - 1];
+              const float ups[4] = {up.x * inv, up.y * inv, up.z * inv, up.w * inv};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) val[j] = (val[j] / (1.0f + expf(-val[j]))) * ups[j];
+            }
+            if (MODE == 1) { val[0] += old[u].x; val[1] += old[u].y; val[2] += old[u].z; val[3] += old[u].w; }
+            store_four(out + (size_t)m_of[u] * shape.ldo + n_of[u], val);
           }
         }
+      } else {
+        const int total = rows_here * shape.M;
+        for (int idx = threadIdx.x - 64; idx < total; idx += 128) {
+          const int m = idx / rows_here, local = idx - m * rows_here;
+          const int n = n_lo + local;
+          if (n >= shape.N) continue;
+          const float inv = scale.squares != nullptr ? row_inv[m] : 1.f;
+          float sums[GROUPS];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-          if (live[u]) {
-            float val = sums[u][0] * inv[u];
-            if (MODE == 2) val = (val / (1.0f + expf(-val))) * (sums[u][GROUPS - 1] * inv[u]);
-            if (MODE == 1) out[at[u]] = from_float<TO>(old[u] + val);
-            else out[at[u]] = from_float<TO>(val);
+          for (int gr = 0; gr < GROUPS; ++gr) {
+            const float* mine = recv + (size_t)(gr * shape.nb + m) * per + local;
+            float t = 0.f;
+            for (int sp = 0; sp < shape.splits; ++sp) t += mine[(size_t)sp * slot_floats];
+            sums[gr] = t;
           }
+          float val = sums[0] * inv;
+          if (MODE == 2) val = (val / (1.0f + expf(-val))) * (sums[GROUPS - 1] * inv);
+          TO* dst = out + (size_t)m * shape.ldo + n;
+          if (MODE == 1) *dst = from_float<TO>(*reinterpret_cast<const float*>(dst) + val);
+          else *dst = from_float<TO>(val);
         }
       }
     }
@@ -591,7 +648,7 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05_normed(void* out, const void* x, const vo
   const int stage_bytes = groups * xrt::DG_W_BYTES + ((x_bytes + 1023) & ~1023);
   // where K is split, a block also keeps the cluster's sums for its share of a tile's rows:
   // splits x accumulator columns x ceil(128 / splits) floats
-  const int per = shape.splits > 1 ? (xrt::DG_ROWS + shape.splits - 1) / shape.splits : 0;
+  const int per = shape.splits > 1 ? xrt::dg_rows_per_block(shape.splits) : 0;
   const int recv_bytes = shape.splits * groups * shape.nb * per * 4;
   const int budget = 200 * 1024 - 512 - recv_bytes;
   shape.stages = budget / stage_bytes;

@@ -47,6 +47,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
 
+// A cache policy for data that is read once (a weight, a cache of keys): its lines are the first
+// to leave the L2, so that what is read again (code, activations, the residual) stays there.
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar), "l"(policy) : "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major operand: rows of 128 bytes (64 bfloat16 of the
 // contraction), 128-byte swizzle, groups of eight rows 1024 bytes apart (stride byte offset, bits
 // [32, 46)), start address in bits [0, 14), descriptor version 1 in bits [46, 48), layout type
