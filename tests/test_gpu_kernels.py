@@ -655,6 +655,50 @@ def test_a_product_prepares_the_norm_that_follows_and_the_next_product_finishes_
         o.gemm_stream(x, act, w_down, "store", norm=(scaled, w_norm, squares))
 
 
+@pytest.mark.parametrize("m", [5, 17, 40, 64, 128])
+@pytest.mark.parametrize("width,inner,out_rows,norm_dtype", [(1032, 2760, 392, torch.float32), (256, 4096, 1536, torch.bfloat16),
+                                                            (4096, 4096, 1024, torch.bfloat16), (5120, 4096, 256, torch.float32),
+                                                            (3072, 2760, 256, torch.bfloat16)])
+def test_a_clustered_few_row_product_prepares_the_norm_that_follows(m, width, inner, out_rows, norm_dtype):
+    """The same by the tcgen05 few-row product where its splits of K run as clusters: the blocks that finish
+    a tile's rows leave residual * norm weight and one partial sum of squares a block.  Widths that end
+    inside a tile (1032 = 8 tiles of 128 and 8 rows) and splits whose rows do not divide evenly (three
+    splits: 44, 44 and 40 rows; six: five of 24 and one of 8) are among the cases, if the device holds
+    their clusters."""
+    from xeno_rt_b200.csrc import ops as o
+    torch.manual_seed(m + width + inner)
+    eps = 1e-5
+    parts = o.gemm_decode_tcgen05_norm_parts(m, width, inner, DEV)
+    if parts == 0:
+        assert width not in (1032, 256, 4096), "these sizes split K into clusters of 4 and 8 on a B200"
+        pytest.skip("the device does not hold this product's clusters all at once")
+    resid = torch.randn(m, width, device=DEV) * 2
+    act = (torch.randn(m, inner, device=DEV)).to(torch.bfloat16)
+    w_down = (torch.randn(width, inner, device=DEV) * 0.05).to(torch.bfloat16)
+    w_norm = (1 + 0.1 * torch.randn(width, device=DEV)).to(norm_dtype)
+    w_next = (torch.randn(2 * out_rows, width, device=DEV) * 0.05).to(torch.bfloat16)
+    x = resid.clone()
+    scaled = torch.full((m, width), 9.0, device=DEV, dtype=torch.bfloat16)
+    squares = torch.full((parts, m), 9.0, device=DEV)
+    o.gemm_decode_tcgen05(x, act, w_down, "accumulate", norm=(scaled, w_norm, squares))
+    plain = resid.clone()
+    o.gemm_decode_tcgen05(plain, act, w_down, "accumulate")
+    assert torch.equal(x, plain) and rel(x, f64(resid) + f64(act) @ f64(w_down).T) < 1e-5
+    assert rel(scaled, f64(x) * f64(w_norm)) < 5e-3
+    assert rel(squares.sum(0), (f64(x) ** 2).sum(1)) < 1e-5
+    again = torch.full_like(squares, 7.0)
+    y = resid.clone()
+    o.gemm_decode_tcgen05(y, act, w_down, "accumulate", norm=(torch.empty_like(scaled), w_norm, again))
+    assert torch.equal(again, squares)  # a fixed order of addition
+    normed = pm.rmsnorm(f64(x), f64(w_norm), eps)
+    out = torch.empty(m, 2 * out_rows, device=DEV)
+    o.gemm_decode_tcgen05(out, scaled, w_next, "store", squares=squares, eps=eps)
+    assert rel(out, normed @ f64(w_next).T) < 6e-3
+    o.check_error_flag(DEV)
+    with pytest.raises(Exception):
+        o.gemm_decode_tcgen05(x, act, w_down, "store", norm=(scaled, w_norm, squares))
+
+
 @pytest.mark.parametrize("m", [129, 300, 1000])
 @pytest.mark.parametrize("width,inner,out_rows,norm_dtype", [(1032, 520, 392, torch.float32), (256, 2760, 1536, torch.bfloat16),
                                                             (4096, 1024, 2048, torch.bfloat16)])

@@ -78,7 +78,8 @@ template <int MODE, typename TO>
 __global__ void __launch_bounds__(DG_THREADS, 1)
 gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                            TO* __restrict__ out, float* __restrict__ partial, int* __restrict__ counters,
-                           const DecodeGemmShape shape, int* __restrict__ error_flag, const RowScale scale) {
+                           const DecodeGemmShape shape, int* __restrict__ error_flag, const RowScale scale,
+                           const NormEmit emit) {
   constexpr int GROUPS = MODE == 2 ? 2 : 1;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -420,6 +421,9 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       // so the loop's cost is its instruction count.  per, row_lo and rows_here are multiples of 4.
       const bool by_four = shape.N % 4 == 0 && shape.ldo % 4 == 0 && ((uintptr_t)out & (sizeof(TO) * 4 - 1)) == 0;
       if (by_four) {
+        // after the meeting nothing is left in flight into this block's ring: room for the shares of
+        // the sums of squares, [batch row][four weight rows]
+        float* square_parts = reinterpret_cast<float*>(smem);
         const int quads = rows_here / 4;
         const int total = quads * shape.M;
         constexpr int UNROLL = 4;
@@ -463,6 +467,37 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             }
             if (MODE == 1) { val[0] += old[u].x; val[1] += old[u].y; val[2] += old[u].z; val[3] += old[u].w; }
             store_four(out + (size_t)m_of[u] * shape.ldo + n_of[u], val);
+            if (MODE == 1 && emit.scaled != nullptr) {
+              // the norm that follows: new residual * its weight for the next product, and this thread's
+              // share of the row's sum of squares, to be added in a fixed order below
+              float w4[4];
+              if (emit.weight_dtype == XRT_BF16) {
+                const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(emit.weight) + n_of[u]);
+                const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                w4[0] = lo.x; w4[1] = lo.y; w4[2] = hi.x; w4[3] = hi.y;
+              } else {
+                const float4 raw = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(emit.weight) + n_of[u]);
+                w4[0] = raw.x; w4[1] = raw.y; w4[2] = raw.z; w4[3] = raw.w;
+              }
+              const float scaled4[4] = {val[0] * w4[0], val[1] * w4[1], val[2] * w4[2], val[3] * w4[3]};
+              store_four(emit.scaled + (size_t)m_of[u] * emit.ld + n_of[u], scaled4);
+              square_parts[base + u * 128] = (val[0] * val[0] + val[1] * val[1]) + (val[2] * val[2] + val[3] * val[3]);
+            }
+          }
+          if (MODE == 1 && emit.scaled != nullptr) {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u)
+              if (!live[u] && base + u * 128 < total) square_parts[base + u * 128] = 0.f;  // rows beyond N
+          }
+        }
+        if (MODE == 1 && emit.squares != nullptr) {
+          // part (this block) of every batch row's sum of squares: its threads' shares in row order
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          for (int m = threadIdx.x - 64; m < shape.M; m += 128) {
+            float sum = 0.f;
+            for (int q = 0; q < quads; ++q) sum += square_parts[m * quads + q];
+            emit.squares[(size_t)blockIdx.x * shape.M + m] = sum;
           }
         }
       } else {
@@ -529,44 +564,61 @@ static int choose_splits(int tiles, int k_iters, int sms, int groups, int nb) {
 // Tuning::decode_gemm_clusters = false keeps the scratch-and-counter reduction everywhere, for comparison.
 inline bool decode_gemm_clusters_wanted() { return tuning().decode_gemm_clusters; }
 
+// The kernel's limit of dynamic shared memory only ever grows (setting it anew would lower it): one
+// record for each instance of the kernel.
+template <int MODE, typename TO>
+cudaError_t allow_shared_memory(int smem) {
+  static int allowed = 0;
+  if (smem <= allowed) return cudaSuccess;
+  const cudaError_t err = cudaFuncSetAttribute(gemm_decode_tcgen05_kernel<MODE, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (err == cudaSuccess) allowed = smem;
+  return err;
+}
+
+// Whether the splits of a tile run as one cluster: all clusters of the launch must find room at the
+// same time (asked once for each cluster size and shared-memory size).
+template <int MODE, typename TO>
+bool decode_gemm_as_clusters(const DecodeGemmShape& shape, int smem, int sm_count) {
+  auto kernel = gemm_decode_tcgen05_kernel<MODE, TO>;
+  const int items = shape.tiles * shape.splits;
+  if (!(shape.splits > 1 && shape.splits <= 8 && items <= sm_count && decode_gemm_clusters_wanted())) return false;
+  if (allow_shared_memory<MODE, TO>(smem) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  static int held[9] = {}, held_smem[9] = {};  // clusters at once by cluster size: 0 unknown, -1 none
+  if (held[shape.splits] == 0 || held_smem[shape.splits] != smem) {
+    cudaLaunchConfig_t probe = {};
+    probe.gridDim = dim3(shape.splits, 1, 1);
+    probe.blockDim = dim3(DG_THREADS);
+    probe.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = shape.splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    probe.attrs = attr;
+    probe.numAttrs = 1;
+    int clusters = 0;
+    const bool asked = cudaOccupancyMaxActiveClusters(&clusters, kernel, &probe) == cudaSuccess;
+    cudaGetLastError();  // a refusal here is an answer, not an error of the stream
+    held[shape.splits] = (asked && clusters >= 1) ? clusters : -1;
+    held_smem[shape.splits] = smem;
+  }
+  return held[shape.splits] >= shape.tiles;
+}
+
 template <int MODE, typename TO>
 int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorMap& map_w, const CUtensorMap& map_x,
                        DecodeGemmShape shape, int smem, int blocks, int sm_count, int* error_flag, const RowScale& scale,
-                       cudaStream_t stream) {
+                       const NormEmit& emit, cudaStream_t stream) {
   auto kernel = gemm_decode_tcgen05_kernel<MODE, TO>;
-  static int allowed = 0;
-  if (smem > allowed) {
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (err != cudaSuccess) return (int)err;
-    allowed = smem;
-  }
-  // The splits of a tile as one cluster, if all clusters of the launch find room at the same time
-  // (asked once for each cluster size and shared-memory size)
+  const cudaError_t err = allow_shared_memory<MODE, TO>(smem);
+  if (err != cudaSuccess) return (int)err;
   const int items = shape.tiles * shape.splits;
-  shape.clustered = 0;
-  if (shape.splits > 1 && shape.splits <= 8 && items <= sm_count && decode_gemm_clusters_wanted()) {
-    static int held[9] = {}, held_smem[9] = {};  // clusters at once by cluster size: 0 unknown, -1 none
-    if (held[shape.splits] == 0 || held_smem[shape.splits] != smem) {
-      cudaLaunchConfig_t probe = {};
-      probe.gridDim = dim3(shape.splits, 1, 1);
-      probe.blockDim = dim3(DG_THREADS);
-      probe.dynamicSmemBytes = smem;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = shape.splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-      probe.attrs = attr;
-      probe.numAttrs = 1;
-      int clusters = 0;
-      const bool asked = cudaOccupancyMaxActiveClusters(&clusters, kernel, &probe) == cudaSuccess;
-      cudaGetLastError();  // a refusal here is an answer, not an error of the stream
-      held[shape.splits] = (asked && clusters >= 1) ? clusters : -1;
-      held_smem[shape.splits] = smem;
-    }
-    if (held[shape.splits] >= shape.tiles) shape.clustered = 1;
-  }
+  shape.clustered = decode_gemm_as_clusters<MODE, TO>(shape, smem, sm_count) ? 1 : 0;
+  if (emit.scaled != nullptr && !shape.clustered) return XRT_ERR_UNSUPPORTED;  // only the clusters' finish prepares a norm
   if (!shape.clustered) {
     launch_kernel(kernel, dim3(blocks), dim3(DG_THREADS), (size_t)smem, stream, map_w, map_x, (TO*)out, partial, counters,
-                  shape, error_flag, scale);
+                  shape, error_flag, scale, emit);
     return launch_status();
   }
   cudaLaunchConfig_t config = {};
@@ -586,7 +638,7 @@ int launch_decode_gemm(void* out, float* partial, int* counters, const CUtensorM
   ++n_attrs;
   config.attrs = attrs;
   config.numAttrs = n_attrs;
-  cudaLaunchKernelEx(&config, kernel, map_w, map_x, (TO*)out, partial, counters, shape, error_flag, scale);
+  cudaLaunchKernelEx(&config, kernel, map_w, map_x, (TO*)out, partial, counters, shape, error_flag, scale, emit);
   return launch_status();
 }
 
@@ -614,6 +666,74 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05_plan(int M, int N, int K, int mode, int s
   return XRT_OK;
 }
 
+namespace xrt {
+
+// Sizes of a launch from the sizes of the product (host arithmetic): the shape the kernel gets, its
+// dynamic shared memory and its blocks when the splits are not clusters.
+static int plan_decode_gemm(int M, int N, int K, int ldo, int mode, int up_rows, int sm_count, DecodeGemmShape* shape_out,
+                            int* smem_out, int* blocks_out) {
+  DecodeGemmShape shape;
+  shape.M = M; shape.N = N; shape.K = K; shape.ldo = ldo;
+  shape.nb = (M + 15) / 16 * 16;
+  shape.tiles = (N + DG_ROWS - 1) / DG_ROWS;
+  const int k_iters = (K + DG_BK - 1) / DG_BK;
+  shape.splits = choose_splits(shape.tiles, k_iters, sm_count, mode == 2 ? 2 : 1, shape.nb);
+  shape.k_per_split = (k_iters + shape.splits - 1) / shape.splits;
+  shape.up_rows = up_rows;
+  const int groups = mode == 2 ? 2 : 1;
+  const int x_bytes = shape.nb * DG_BK * 2;
+  const int stage_bytes = groups * DG_W_BYTES + ((x_bytes + 1023) & ~1023);
+  // where K is split, a block also keeps the cluster's sums for its share of a tile's rows:
+  // splits x accumulator columns x rows a block finishes, floats
+  const int per = shape.splits > 1 ? dg_rows_per_block(shape.splits) : 0;
+  const int recv_bytes = shape.splits * groups * shape.nb * per * 4;
+  const int budget = 200 * 1024 - 512 - recv_bytes;
+  shape.stages = budget / stage_bytes;
+  if (shape.stages > 12) shape.stages = 12;
+  if (shape.stages < 2) return XRT_ERR_UNSUPPORTED;
+  int cols = 32;
+  while (cols < 2 * groups * shape.nb) cols *= 2;
+  if (cols > 512) return XRT_ERR_UNSUPPORTED;
+  shape.tmem_cols = cols;
+  shape.clustered = 0;
+  *smem_out = shape.stages * stage_bytes + 1024 + recv_bytes + 1024;
+  const int items = shape.tiles * shape.splits;
+  *blocks_out = items < sm_count ? items : sm_count;
+  *shape_out = shape;
+  return XRT_OK;
+}
+
+static int decode_gemm(void* out, const void* x, const void* w, float* partial, int* counters, int M, int N, int K, int ldx,
+                       int ldo, int w_rows, int out_dtype, int mode, int up_rows, int sm_count, int* error_flag,
+                       const RowScale& scale, const NormEmit& emit, cudaStream_t stream) {
+  if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldo < N || mode < 0 || mode > 2 || sm_count <= 0) return XRT_ERR_ARGUMENT;
+  if (mode == 1 && out_dtype != XRT_F32) return XRT_ERR_ARGUMENT;
+  if (mode == 2 ? w_rows < up_rows + N : w_rows < N) return XRT_ERR_ARGUMENT;
+  if (out_dtype != XRT_F32 && out_dtype != XRT_BF16) return XRT_ERR_UNSUPPORTED;
+  if (K % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || M > 128) return XRT_ERR_UNSUPPORTED;
+  if (M == 0) return XRT_OK;
+  DecodeGemmShape shape;
+  int smem = 0, blocks = 0;
+  const int planned = plan_decode_gemm(M, N, K, ldo, mode, up_rows, sm_count, &shape, &smem, &blocks);
+  if (planned != XRT_OK) return planned;
+  if (shape.splits > 1 && (partial == nullptr || counters == nullptr)) return XRT_ERR_ARGUMENT;
+  CUtensorMap map_w, map_x;
+  if (!dg_make_map(&map_w, w, w_rows, K, K, DG_ROWS) || !dg_make_map(&map_x, x, M, K, ldx, shape.nb))
+    return XRT_ERR_UNSUPPORTED;
+  if (mode == 1)
+    return launch_decode_gemm<1, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, emit, stream);
+  if (mode == 2) {
+    if (out_dtype == XRT_BF16)
+      return launch_decode_gemm<2, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, emit, stream);
+    return launch_decode_gemm<2, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, emit, stream);
+  }
+  if (out_dtype == XRT_BF16)
+    return launch_decode_gemm<0, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, emit, stream);
+  return launch_decode_gemm<0, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, emit, stream);
+}
+
+}  // namespace xrt
+
 // x: bfloat16 [M, K] with row stride ldx, M <= 128; w: bfloat16 [w_rows, K] contiguous; K and ldx
 // multiples of 8, bases 16-byte aligned.  out: [M, N] with row stride ldo.  Modes as for
 // xrt_gemm_stream.  partial: float32 scratch of xrt_gemm_decode_tcgen05_scratch floats (may be null
@@ -629,53 +749,40 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05_normed(void* out, const void* x, const vo
   if (squares != nullptr && (square_parts <= 0 || mode == 1)) return XRT_ERR_ARGUMENT;
   xrt::RowScale scale;
   scale.squares = squares; scale.parts = square_parts; scale.width = K; scale.eps = eps;
-  if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldo < N || mode < 0 || mode > 2 || sm_count <= 0) return XRT_ERR_ARGUMENT;
-  if (mode == 1 && out_dtype != XRT_F32) return XRT_ERR_ARGUMENT;
-  if (mode == 2 ? w_rows < up_rows + N : w_rows < N) return XRT_ERR_ARGUMENT;
-  if (out_dtype != XRT_F32 && out_dtype != XRT_BF16) return XRT_ERR_UNSUPPORTED;
-  if (K % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || M > 128) return XRT_ERR_UNSUPPORTED;
-  if (M == 0) return XRT_OK;
+  return xrt::decode_gemm(out, x, w, partial, counters, M, N, K, ldx, ldo, w_rows, out_dtype, mode, up_rows, sm_count,
+                          error_flag, scale, xrt::NormEmit(), stream);
+}
+
+// How many partial sums of squares a row xrt_gemm_decode_tcgen05_norm leaves (one a block: tiles x
+// splits), or 0 when this product cannot prepare a norm on the current device: only the finish of
+// splits that run as clusters does.
+XRT_EXPORT int xrt_gemm_decode_tcgen05_norm_parts(int M, int N, int K, int sm_count) {
+  if (M <= 0 || M > 128 || N <= 0 || K <= 0 || sm_count <= 0 || N % 4 != 0) return 0;
   xrt::DecodeGemmShape shape;
-  shape.M = M; shape.N = N; shape.K = K; shape.ldo = ldo;
-  shape.nb = (M + 15) / 16 * 16;
-  shape.tiles = (N + xrt::DG_ROWS - 1) / xrt::DG_ROWS;
-  const int k_iters = (K + xrt::DG_BK - 1) / xrt::DG_BK;
-  shape.splits = xrt::choose_splits(shape.tiles, k_iters, sm_count, mode == 2 ? 2 : 1, shape.nb);
-  shape.k_per_split = (k_iters + shape.splits - 1) / shape.splits;
-  shape.up_rows = up_rows;
-  const int groups = mode == 2 ? 2 : 1;
-  const int x_bytes = shape.nb * xrt::DG_BK * 2;
-  const int stage_bytes = groups * xrt::DG_W_BYTES + ((x_bytes + 1023) & ~1023);
-  // where K is split, a block also keeps the cluster's sums for its share of a tile's rows:
-  // splits x accumulator columns x ceil(128 / splits) floats
-  const int per = shape.splits > 1 ? xrt::dg_rows_per_block(shape.splits) : 0;
-  const int recv_bytes = shape.splits * groups * shape.nb * per * 4;
-  const int budget = 200 * 1024 - 512 - recv_bytes;
-  shape.stages = budget / stage_bytes;
-  if (shape.stages > 12) shape.stages = 12;
-  if (shape.stages < 2) return XRT_ERR_UNSUPPORTED;
-  int cols = 32;
-  while (cols < 2 * groups * shape.nb) cols *= 2;
-  if (cols > 512) return XRT_ERR_UNSUPPORTED;
-  shape.tmem_cols = cols;
-  shape.clustered = 0;
-  if (shape.splits > 1 && (partial == nullptr || counters == nullptr)) return XRT_ERR_ARGUMENT;
-  const int smem = shape.stages * stage_bytes + 1024 + recv_bytes + 1024;
-  const int items = shape.tiles * shape.splits;
-  const int blocks = items < sm_count ? items : sm_count;
-  CUtensorMap map_w, map_x;
-  if (!xrt::dg_make_map(&map_w, w, w_rows, K, K, xrt::DG_ROWS) || !xrt::dg_make_map(&map_x, x, M, K, ldx, shape.nb))
+  int smem = 0, blocks = 0;
+  if (xrt::plan_decode_gemm(M, N, K, N, 1, 0, sm_count, &shape, &smem, &blocks) != XRT_OK) return 0;
+  return xrt::decode_gemm_as_clusters<1, float>(shape, smem, sm_count) ? shape.tiles * shape.splits : 0;
+}
+
+// out (float32 [M, N]) += x . w^T, and the RMSNorm that follows prepared on the way, as
+// xrt_gemm_stream_norm does: scaled (bfloat16 [M, ld_scaled]) = new out * norm_weight ([N], float32 or
+// bfloat16 by norm_dtype), squares (float32 [xrt_gemm_decode_tcgen05_norm_parts, M]) = the rows' partial
+// sums of squares.  N, ldo and ld_scaled multiples of 4; out and norm_weight 16-byte aligned, scaled 8.
+// XRT_ERR_UNSUPPORTED where xrt_gemm_decode_tcgen05_norm_parts is 0.
+XRT_EXPORT int xrt_gemm_decode_tcgen05_norm(void* out, const void* x, const void* w, float* partial, int* counters, int M,
+                                            int N, int K, int ldx, int ldo, int w_rows, int sm_count, int* error_flag,
+                                            void* scaled, int ld_scaled, const void* norm_weight, int norm_dtype,
+                                            float* squares, cudaStream_t stream) {
+  if (scaled == nullptr || norm_weight == nullptr || squares == nullptr || ld_scaled < N) return XRT_ERR_ARGUMENT;
+  if (norm_dtype != XRT_F32 && norm_dtype != XRT_BF16) return XRT_ERR_UNSUPPORTED;
+  if (N % 4 != 0 || ldo % 4 != 0 || ld_scaled % 4 != 0 || ((uintptr_t)out & 15) || ((uintptr_t)norm_weight & 15) ||
+      ((uintptr_t)scaled & 7))
     return XRT_ERR_UNSUPPORTED;
-  if (mode == 1)
-    return xrt::launch_decode_gemm<1, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, stream);
-  if (mode == 2) {
-    if (out_dtype == XRT_BF16)
-      return xrt::launch_decode_gemm<2, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, stream);
-    return xrt::launch_decode_gemm<2, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, stream);
-  }
-  if (out_dtype == XRT_BF16)
-    return xrt::launch_decode_gemm<0, __nv_bfloat16>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, stream);
-  return xrt::launch_decode_gemm<0, float>(out, partial, counters, map_w, map_x, shape, smem, blocks, sm_count, error_flag, scale, stream);
+  xrt::NormEmit emit;
+  emit.scaled = (__nv_bfloat16*)scaled; emit.weight = norm_weight; emit.squares = squares;
+  emit.ld = ld_scaled; emit.weight_dtype = norm_dtype;
+  return xrt::decode_gemm(out, x, w, partial, counters, M, N, K, ldx, ldo, w_rows, XRT_F32, 1, 0, sm_count, error_flag,
+                          xrt::RowScale(), emit, stream);
 }
 
 // The same without a pending norm.

@@ -40,6 +40,8 @@ _SIGNATURES = {
     "xrt_gemm_decode_tcgen05_normed": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P],
     "xrt_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_gemm_decode_tcgen05": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "xrt_gemm_decode_tcgen05_norm": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _I, _P, _P],
+    "xrt_gemm_decode_tcgen05_norm_parts": [_I, _I, _I, _I],
     "xrt_attention_decode_fused": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P],
     "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P],
     "xrt_attention_decode_qkv": [_P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I,
@@ -381,11 +383,28 @@ def gemm_decode_tcgen05_fill(sms: int, m: int, n: int, k: int, mode: str):
     return _decode_plans[key]
 
 
-def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, squares=None, eps: float = 0.0) -> None:
+_decode_norm_parts: dict = {}
+
+
+def gemm_decode_tcgen05_norm_parts(m: int, n: int, k: int, device) -> int:
+    """How many partial sums of squares a row ``gemm_decode_tcgen05(..., norm=...)`` leaves, or 0 when
+    that product cannot prepare a norm on this device (only splits of K that run as clusters do).
+    Asks the device once for each class of sizes."""
+    sms = device_state(device)[2]
+    key = (sms, (m + 15) // 16, n, k, tuning().decode_gemm_clusters)
+    if key not in _decode_norm_parts:
+        with torch.cuda.device(device):
+            _decode_norm_parts[key] = library().xrt_gemm_decode_tcgen05_norm_parts(int(m), int(n), int(k), sms)
+    return _decode_norm_parts[key]
+
+
+def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, squares=None, eps: float = 0.0, norm=None) -> None:
     """bfloat16 product for at most 128 rows on the tcgen05 tensor cores with swapped operands:
     the weight is streamed once by TMA, K is split across blocks and summed in split order.
-    ``squares`` (float32 [parts, rows], from ``gemm_stream(..., norm=...)``): ``x`` is a residual times
-    its norm weight, and every row's result is multiplied by 1 / sqrt(sum of its parts / K + eps)."""
+    ``squares`` (float32 [parts, rows], from a product with ``norm=...``): ``x`` is a residual times
+    its norm weight, and every row's result is multiplied by 1 / sqrt(sum of its parts / K + eps).
+    ``norm`` = (scaled, weight, squares) with "accumulate", where ``gemm_decode_tcgen05_norm_parts`` is
+    not 0: the product prepares the RMSNorm that follows it, as ``gemm_stream`` does."""
     m, k = x.shape
     n = out.shape[1]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -404,6 +423,18 @@ def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, square
     partial = torch.empty(floats, dtype=torch.float32, device=x.device) if floats else None
     if squares is not None and (mode == "accumulate" or squares.dim() != 2 or squares.shape[1] != m):
         raise KernelError("gemm_decode_tcgen05: squares must be [parts, rows], and not with accumulate")
+    if norm is not None:
+        scaled, weight, emitted = norm
+        parts = gemm_decode_tcgen05_norm_parts(m, n, k, x.device)
+        if (mode != "accumulate" or out.dtype != torch.float32 or parts == 0 or scaled.shape != (m, n) or scaled.stride(1) != 1
+                or weight.numel() != n or tuple(emitted.shape) != (parts, m) or not emitted.is_contiguous()):
+            raise KernelError("gemm_decode_tcgen05: the buffers of the following norm do not fit the product")
+        _check(lib.xrt_gemm_decode_tcgen05_norm(
+            out.data_ptr(), x.data_ptr(), _ptr(w, "w"), _ptr(partial, "partial"), counters.data_ptr(), m, n, k, x.stride(0),
+            out.stride(0), w.shape[0], sms, flag.data_ptr(), _ptr(scaled, "scaled", torch.bfloat16), scaled.stride(0),
+            _ptr(weight, "weight"), _code(weight.dtype), _ptr(emitted, "squares", torch.float32), _stream()),
+            "gemm_decode_tcgen05")
+        return
     _check(lib.xrt_gemm_decode_tcgen05_normed(
         out.data_ptr(), x.data_ptr(), _ptr(w, "w"), _ptr(partial, "partial"), counters.data_ptr(), m, n, k, x.stride(0),
         out.stride(0), w.shape[0], _code(out.dtype), code, up_rows, sms, flag.data_ptr(),

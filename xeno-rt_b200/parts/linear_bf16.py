@@ -39,24 +39,25 @@ def tcgen05_for_few_rows(sms: int, rows: int, n: int, k: int, mode: str) -> bool
     return fill >= 0.6 and (rounds == 1 or fill >= 0.85)
 
 
-def _product(out, x, weight, mode: str, up_rows: int = 0) -> None:
-    rows = x.shape[0]
+def _decode_kernel(rows: int, n: int, k: int, mode: str, device) -> str:
+    """Which of the two decode kernels takes a product of at most 128 rows: "stream" or "tcgen05"."""
     force = ops.tuning().decode_gemm
     if force == "stream":
-        stream_rows = ops.STREAM_MAX_ROWS
-    elif force == "tcgen05":
-        stream_rows = 0
-    elif rows > STREAM_ROWS:
-        stream_rows = 0
-    else:
-        sms = ops.device_state(x.device)[2]
-        stream_rows = 0 if tcgen05_for_few_rows(sms, rows, out.shape[1], x.shape[1], mode) else STREAM_ROWS
-    if rows <= stream_rows:
-        ops.gemm_stream(out, x, weight, mode, up_rows)
-    elif rows <= ops.DECODE_TCGEN05_MAX_ROWS:
-        ops.gemm_decode_tcgen05(out, x, weight, mode, up_rows)
-    else:
+        return "stream" if rows <= ops.STREAM_MAX_ROWS else "tcgen05"
+    if force == "tcgen05" or rows > STREAM_ROWS:
+        return "tcgen05"
+    sms = ops.device_state(device)[2]
+    return "tcgen05" if tcgen05_for_few_rows(sms, rows, n, k, mode) else "stream"
+
+
+def _product(out, x, weight, mode: str, up_rows: int = 0) -> None:
+    rows = x.shape[0]
+    if rows > ops.DECODE_TCGEN05_MAX_ROWS:
         ops.gemm_tcgen05(out, x, weight, mode, up_rows)
+    elif _decode_kernel(rows, out.shape[1], x.shape[1], mode, x.device) == "stream":
+        ops.gemm_stream(out, x, weight, mode, up_rows)
+    else:
+        ops.gemm_decode_tcgen05(out, x, weight, mode, up_rows)
 
 
 def takes_pending(rows: int, n: int, k: int, mode: str, device) -> bool:
@@ -84,24 +85,31 @@ def run_with_norm(out, x, weight, norm):
     """out += x . weight^T, and the RMSNorm ``norm`` of the new out prepared on the way: a PendingNorm,
     or None when the kernel that takes this product cannot do that (the caller then runs it plainly)."""
     from .norm import PendingNorm, RMSNorm
-    rows, n = x.shape[0], out.shape[1]
-    if (isinstance(norm, RMSNorm) and norm.width == n and aligned(x, weight) and rows > ops.DECODE_TCGEN05_MAX_ROWS
-            and n % 4 == 0 and out.is_contiguous() and ops.tuning().pending_norm != "off"
-            and norm.weight.data_ptr() % 16 == 0):  # a prompt: the tiled tcgen05 product
-        scaled = torch.empty((rows, n), dtype=torch.bfloat16, device=x.device)
-        squares = torch.empty((ops.gemm_tcgen05_norm_parts(n), rows), dtype=torch.float32, device=x.device)
-        ops.gemm_tcgen05(out, x, weight, "accumulate", norm=(scaled, norm.weight, squares))
-        return PendingNorm(scaled, squares, norm.eps, norm)
-    if (not isinstance(norm, RMSNorm) or norm.width != n or not aligned(x, weight) or rows > ops.STREAM_NORM_MAX_ROWS
-            or (ops.tuning().decode_gemm == "tcgen05" and ops.tuning().pending_norm != "force") or not out.is_contiguous()
-            or ops.tuning().pending_norm == "off"):
+    rows, n, k = x.shape[0], out.shape[1], x.shape[1]
+    wish = ops.tuning().pending_norm
+    if (not isinstance(norm, RMSNorm) or norm.width != n or not aligned(x, weight) or not out.is_contiguous()
+            or wish == "off"):
         return None
-    if (ops.tuning().decode_gemm != "stream" and ops.tuning().pending_norm != "force"
-            and tcgen05_for_few_rows(ops.device_state(x.device)[2], rows, n, x.shape[1], "accumulate")):
-        return None
+    by_four = n % 4 == 0 and norm.weight.data_ptr() % 16 == 0  # what the tcgen05 kernels' vector stores need
+    if rows > ops.DECODE_TCGEN05_MAX_ROWS:  # a prompt: the tiled tcgen05 product
+        if not by_four:
+            return None
+        kernel, parts = ops.gemm_tcgen05, ops.gemm_tcgen05_norm_parts(n)
+    else:
+        choice = _decode_kernel(rows, n, k, "accumulate", x.device)
+        if wish == "force" and rows <= ops.STREAM_NORM_MAX_ROWS:
+            choice = "stream"
+        if choice == "stream":
+            if rows > ops.STREAM_NORM_MAX_ROWS:
+                return None
+            kernel, parts = ops.gemm_stream, ops.gemm_stream_norm_parts(rows, n)
+        else:  # the few-row tcgen05 product prepares a norm where its splits of K run as clusters
+            kernel, parts = ops.gemm_decode_tcgen05, ops.gemm_decode_tcgen05_norm_parts(rows, n, k, x.device)
+            if parts == 0 or not by_four:
+                return None
     scaled = torch.empty((rows, n), dtype=torch.bfloat16, device=x.device)
-    squares = torch.empty((ops.gemm_stream_norm_parts(rows, n), rows), dtype=torch.float32, device=x.device)
-    ops.gemm_stream(out, x, weight, "accumulate", norm=(scaled, norm.weight, squares))
+    squares = torch.empty((parts, rows), dtype=torch.float32, device=x.device)
+    kernel(out, x, weight, "accumulate", norm=(scaled, norm.weight, squares))
     return PendingNorm(scaled, squares, norm.eps, norm)
 
 
