@@ -426,7 +426,8 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         float* square_parts = reinterpret_cast<float*>(smem);
         const int quads = rows_here / 4;
         const int total = quads * shape.M;
-        constexpr int UNROLL = 4;
+        constexpr int UNROLL = 1;
+#pragma unroll 1
         for (int base = threadIdx.x - 64; base < total; base += 128 * UNROLL) {
           float4 old[UNROLL], sums[UNROLL][GROUPS];
           int m_of[UNROLL], n_of[UNROLL];
@@ -536,15 +537,66 @@ static bool dg_make_map(CUtensorMap* map, const void* base, int rows, int cols, 
   return sm100::make_map_bf16_2d(map, base, rows, cols, ld, box_rows);
 }
 
+// How many clusters of 2 .. 8 blocks of this kernel (one block a multiprocessor) the device runs at
+// the same time: asked of the current device once; where there is none (host arithmetic only), or
+// it has another number of multiprocessors than asked about, nine tenths of them, which is what a
+// B200 answers within one cluster (148: 45 clusters of 3, 33 of 4, 26 of 5, 22 of 6).
+struct ClusterLimits { int held[9]; };
+static const ClusterLimits& cluster_limits(int sms) {
+  static ClusterLimits estimate, asked;
+  static int estimate_sms = 0, asked_sms = -1;
+  if (asked_sms == -1) {
+    asked_sms = 0;
+    int device = 0, count = 0;
+    if (cudaGetDevice(&device) == cudaSuccess &&
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess) {
+      auto kernel = gemm_decode_tcgen05_kernel<0, __nv_bfloat16>;
+      const int smem = 200 * 1024;
+      bool ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess;
+      for (int size = 2; ok && size <= 8; ++size) {
+        cudaLaunchConfig_t probe = {};
+        probe.gridDim = dim3(size, 1, 1);
+        probe.blockDim = dim3(DG_THREADS);
+        probe.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = size; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        probe.attrs = attr;
+        probe.numAttrs = 1;
+        int clusters = 0;
+        ok = cudaOccupancyMaxActiveClusters(&clusters, kernel, &probe) == cudaSuccess;
+        asked.held[size] = clusters;
+      }
+      if (ok) asked_sms = count;
+    }
+    cudaGetLastError();  // no device, or a refusal: an answer, not an error of a stream
+  }
+  if (sms == asked_sms) return asked;
+  if (sms != estimate_sms) {
+    for (int size = 2; size <= 8; ++size) estimate.held[size] = sms * 9 / 10 / size;
+    estimate_sms = sms;
+  }
+  return estimate;
+}
+
+// Tuning::decode_gemm_clusters = false keeps the scratch-and-counter reduction everywhere, for comparison.
+inline bool decode_gemm_clusters_wanted() { return tuning().decode_gemm_clusters; }
+
 // Splits of K: more splits fill the multiprocessors more evenly when the tiles are few, but every
-// split writes and the last reads a 128 x NB partial tile.  The choice minimises
-// (weight bytes + partial traffic) / (share of the block rounds that do work).  It depends on N, K
-// and the padded batch NB (16, 32, ... 128), so a row's sum has the same order for every batch of
-// the same NB; between NB classes it may differ by rounding.  At least 4 slabs a split.
+// split has its price.  Where all items run at once and the device holds a tile's splits as one
+// cluster, they meet through shared memory: a ramp, a meeting and a short finish, measured about
+// the time of 350 KB of weights an item.  Else every split writes and the last reads a 128 x NB
+// partial tile, with a fence, a counter, and one block that finishes all of a tile's rows: the time of
+// 450 KB an item at NB = 16, growing with NB (12 microseconds at 64 rows).  The choice minimises
+// (weight bytes + that) / (share of the block rounds that do work).  It depends on N, K and the
+// padded batch NB (16, 32, ... 128), so a row's sum has the same order for every batch of the same
+// NB; between NB classes it may differ by rounding.  At least 4 slabs a split.
 static int choose_splits(int tiles, int k_iters, int sms, int groups, int nb) {
   int best = 1;
   double best_cost = 0.0;
   const double weight_bytes = (double)groups * DG_ROWS * k_iters * DG_BK * 2;
+  const ClusterLimits& limits = cluster_limits(sms);
+  const bool clusters = decode_gemm_clusters_wanted();
   for (int s = 1; s <= DG_MAX_SPLITS; ++s) {
     const int per = (k_iters + s - 1) / s;
     if (s > 1 && per < 4) break;
@@ -552,17 +604,17 @@ static int choose_splits(int tiles, int k_iters, int sms, int groups, int nb) {
     const long long items = (long long)tiles * s;
     const long long rounds = (items + sms - 1) / sms;
     const double busy = (double)items / (double)(rounds * sms);
-    // a split item also pays for its fence, counter and barriers, and its epilogue cannot hide behind
-    // the next item's few slabs: measured about 10 microseconds an item, the time of 450 KB of weights
-    const double partial_bytes = s > 1 ? 2.0 * s * groups * nb * DG_ROWS * 4 + s * 450.0 * 1024 : 0.0;
-    const double cost = (weight_bytes + partial_bytes) / busy;
+    double split_bytes = 0.0;
+    if (s > 1 && s <= 8 && clusters && items <= sms && tiles <= limits.held[s])
+      split_bytes = s * 350.0 * 1024;
+    else if (s > 1)
+      split_bytes = 2.0 * s * groups * nb * DG_ROWS * 4 + s * 450.0 * 1024 * (0.75 + nb / 64.0);
+    const double cost = (weight_bytes + split_bytes) / busy;
     if (s == 1 || cost < best_cost * 0.98) { best_cost = cost; best = s; }
   }
   return best;
 }
 
-// Tuning::decode_gemm_clusters = false keeps the scratch-and-counter reduction everywhere, for comparison.
-inline bool decode_gemm_clusters_wanted() { return tuning().decode_gemm_clusters; }
 
 // The kernel's limit of dynamic shared memory only ever grows (setting it anew would lower it): one
 // record for each instance of the kernel.
