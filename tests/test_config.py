@@ -166,6 +166,14 @@ def test_decode_attention_splits_cover_the_context_and_fill_the_rounds():
                 assert chunk * (splits - 1) < blocks * 64        # and no split is empty
     assert [decode_split(b, 8, 4096, 148)[1] for b in (1, 2, 4, 8, 16, 32, 64)] == [16, 16, 8, 4, 2, 3, 4]
     assert decode_split(1, 8, 32768, 148)[1] <= CLUSTER_MAX_SPLITS
+    # unequal lengths: what a sequence holds on average decides how many blocks have work, so the keys are cut
+    # finer when most sequences are far shorter than the longest; a mean as long as the longest changes nothing
+    for n_seqs in (8, 16, 64):
+        assert decode_split(n_seqs, 8, 4096, 148, 4096) == decode_split(n_seqs, 8, 4096, 148)
+        assert decode_split(n_seqs, 8, 4096, 148, 1024)[1] > decode_split(n_seqs, 8, 4096, 148)[1]
+        for mean in (1, 300, 1024, 5000):
+            chunk, splits = decode_split(n_seqs, 8, 4096, 148, mean)
+            assert chunk % 64 == 0 and chunk * splits >= 4096 and chunk * (splits - 1) < 4096
 
 
 def test_the_merging_block_of_decode_attention_is_never_given_more_splits_than_its_shared_memory_holds():

@@ -173,6 +173,27 @@ def test_long_decoding(setups, engines, tmp_path, name, dtype):
     assert scaled_error(got[worst:worst + 1], ref[worst:worst + 1]) < TOL[dtype], worst
 
 
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("name", ["tiny-odd", "tiny-wide"])
+def test_decode_steps_of_very_unequal_lengths(setups, tmp_path, name, graphs):
+    """Sequences of 3, 70, 300 and 900 tokens decode together: attention cuts its keys by the longest and
+    by the mean length (finer than for four sequences of 900), so most splits of the short sequences hold
+    no key at all, and the batch crosses a power of two of the mean on the way.  Every row against the
+    plain implementation."""
+    from plain.files import read_model_folder
+    from plain.model import forward_logits
+    from xeno_rt_b200.engine import Engine, Model
+    folder = make_folder(tmp_path, name, sharpen=3.0)
+    cfg, weights = read_model_folder(folder)
+    prompts = random_prompts(cfg["vocab_size"], [3 + 12, 70 + 12, 300 + 12, 900 + 12], seed=21)
+    engine = Engine(Model.load(folder, dtype="bfloat16"), max_tokens=64 * 24, use_graphs=graphs)
+    got = _batch(engine, prompts, decode=12)
+    for p, g in zip(prompts, got):
+        assert scaled_error(g, forward_logits(cfg, weights, p)) < TOL["bfloat16"], len(p)
+    if graphs:
+        assert len({key[2] for key in engine._graphs}) >= 1 and all(key[2] <= key[1] for key in engine._graphs)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_steps_of_several_tokens_continue_a_sequence(setups, engines, dtype):
     """Chunks of unequal size (not only prompts and single tokens) continue where the slot stands."""

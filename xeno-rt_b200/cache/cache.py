@@ -25,6 +25,7 @@ import numpy as np
 import torch
 
 from ..core import CacheError, DType, torch_dtype
+from ..core.staging import PinnedRing
 from .allocator import BlockAllocator, SlotAllocator
 from .spec import BLOCK_TOKENS, KVNeed, StateNeed
 
@@ -121,6 +122,7 @@ class Cache:
         if self.max_slots <= 0:
             raise CacheError(f"max_slots {self.max_slots} must be positive")
         self.slots = SlotAllocator(self.max_slots)
+        self._table_ring = PinnedRing(self.device)
         self.lengths = [0] * self.max_slots
         self._n_seq_blocks = [0] * self.max_slots
 
@@ -286,9 +288,15 @@ class Cache:
                 continue
             rows = sorted(group.dirty)
             if self.device.type == "cuda":
-                idx = torch.tensor(rows, dtype=torch.int64, device=self.device)
-                host_rows = torch.from_numpy(np.ascontiguousarray(group.table_host[rows]))
-                group.table.index_copy_(0, idx, host_rows.to(self.device))
+                # the changed rows and their numbers through one pinned buffer and one copy that the host
+                # does not wait for: with sequences of unequal lengths some row changes at nearly every step
+                width = group.table_host.shape[1]
+                turn, host = self._table_ring.take(len(rows) * (width + 1))
+                host[:len(rows)] = torch.tensor(rows, dtype=torch.int32)
+                host[len(rows):].view(len(rows), width).copy_(torch.from_numpy(group.table_host[rows]))
+                dev = host.to(self.device, non_blocking=True)
+                self._table_ring.copied(turn)
+                group.table.index_copy_(0, dev[:len(rows)].to(torch.int64), dev[len(rows):].view(len(rows), width))
             else:
                 group.table[rows] = torch.from_numpy(group.table_host[rows])
             group.dirty.clear()

@@ -698,7 +698,7 @@ int launch_decode_tma(__nv_bfloat16* out, float* part_o, float* part_ml, const _
                       const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, long long pool_rows, const int* tok_slot,
                       const int* tok_pos, const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
                       int head_dim, float scale, int window, int chunk, int n_splits, int* counters, int* error_flag,
-                      cudaStream_t stream, bool* merged, const DecodeFusedInput& fused) {
+                      cudaStream_t stream, bool* merged, const DecodeFusedInput& fused, bool clusters) {
   CUtensorMap map_k, map_v;
   if (!dec_make_map(&map_k, k_pool, pool_rows, head_dim) || !dec_make_map(&map_v, v_pool, pool_rows, head_dim))
     return XRT_ERR_UNSUPPORTED;
@@ -713,7 +713,7 @@ int launch_decode_tma(__nv_bfloat16* out, float* part_o, float* part_ml, const _
   // 2 to 16 splits: the splits of a (token, kv head) as one thread-block cluster that merges itself
   // through distributed shared memory, if the device can hold such a cluster (asked once a size)
   static int cluster_ok[DEC_MAX_CLUSTER + 1][5] = {};  // by splits and head-size class: 0 unknown, 1 yes, 2 no
-  const bool clustered = decode_cluster_wanted(n_splits, n_tokens * n_kv_heads) && [&]() {
+  const bool clustered = clusters && decode_cluster_wanted(n_splits, n_tokens * n_kv_heads) && [&]() {
     int& known = cluster_ok[n_splits][HD_MAX / 64];
     if (known == 0) {
       known = 2;
@@ -791,7 +791,7 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_
                   const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, long long pool_rows, const int* tok_slot,
                   const int* tok_pos, const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
                   int head_dim, float scale, int window, int chunk, int n_splits, int* counters, int* error_flag,
-                  cudaStream_t stream, bool* merged, const DecodeFusedInput& fused) {
+                  cudaStream_t stream, bool* merged, const DecodeFusedInput& fused, bool clusters) {
   *merged = false;
   const bool rows_only = tuning().decode_attention == 1, copies_only = tuning().decode_attention == 2;
   if (n_heads / n_kv_heads <= 8 && !rows_only && !copies_only && pool_rows > 0 && head_dim % 64 == 0 &&
@@ -802,7 +802,7 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_
       return XRT_ERR_UNSUPPORTED;
     return launch_decode_tma<HD_MAX>(out, part_o, part_ml, q, k_pool, v_pool, pool_rows, tok_slot, tok_pos, block_table,
                                      max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
-                                     counters, error_flag, stream, merged, fused);
+                                     counters, error_flag, stream, merged, fused, clusters);
   }
   if (fused.qkv != nullptr) return XRT_ERR_UNSUPPORTED;  // only the kernel above rotates and writes the cache itself
   if (n_heads / n_kv_heads <= 8 && !rows_only)
@@ -843,7 +843,7 @@ static int attention_decode_impl(void* out, float* part_o, float* part_ml, const
                                  const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
                                  int head_dim, float scale, int window, int chunk, int n_splits, int* counters,
                                  int* error_flag, cudaStream_t stream, int* merged_out = nullptr,
-                                 const DecodeFusedInput& fused = DecodeFusedInput()) {
+                                 const DecodeFusedInput& fused = DecodeFusedInput(), bool clusters = true) {
   if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || chunk <= 0 || n_splits <= 0)
     return XRT_ERR_ARGUMENT;
   if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256 || n_heads / n_kv_heads > 16 ||
@@ -862,7 +862,7 @@ static int attention_decode_impl(void* out, float* part_o, float* part_ml, const
   const long long pool_rows = (long long)n_blocks * n_kv_heads * XRT_BLOCK_TOKENS;  // 0: the pools' size is not known
 #define XRT_DECODE(HD) status = launch_decode<HD>(o, part_o, part_ml, qp, kp, vp, pool_rows, tok_slot, tok_pos, block_table, \
                                                   max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window,      \
-                                                  chunk, n_splits, counters, error_flag, stream, &merged, fused)
+                                                  chunk, n_splits, counters, error_flag, stream, &merged, fused, clusters)
   if (head_dim <= 32) XRT_DECODE(32);
   else if (head_dim <= 64) XRT_DECODE(64);
   else if (head_dim <= 128) XRT_DECODE(128);
@@ -890,16 +890,18 @@ static int attention_decode_impl(void* out, float* part_o, float* part_ml, const
 // n_blocks: blocks in each pool (0 if unknown: the kernels fed by TMA are then not used); error_flag
 // (may be null): raised if a bounded wait on a copy ran out; *merged (may be null) is set to 1 when
 // the attention kernel merged its splits itself, as thread-block clusters (then the partials are not
-// touched and no second kernel runs), else 0.
+// touched and no second kernel runs), else 0.  clusters = 0 keeps the splits from merging as clusters:
+// a cluster lives until its longest block is done, so where the sequences' lengths are far apart the
+// blocks of a short sequence's splits would hold their places for nothing.
 // This entry point merges the splits with a second kernel.
 XRT_EXPORT int xrt_attention_decode(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
                                     const void* v_pool, int n_blocks, const int* tok_slot, const int* tok_pos,
                                     const int* block_table, int max_blocks, int n_tokens, int n_heads, int n_kv_heads,
                                     int head_dim, float scale, int window, int chunk, int n_splits, int* error_flag,
-                                    cudaStream_t stream, int* merged) {
+                                    cudaStream_t stream, int* merged, int clusters) {
   return xrt::attention_decode_impl(out, part_o, part_ml, q, k_pool, v_pool, n_blocks, tok_slot, tok_pos, block_table,
                                     max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
-                                    nullptr, error_flag, stream, merged);
+                                    nullptr, error_flag, stream, merged, xrt::DecodeFusedInput(), clusters != 0);
 }
 
 // The same, with the merge done by the block that brings a (token, kv head)'s last split: one
@@ -909,11 +911,11 @@ XRT_EXPORT int xrt_attention_decode_fused(void* out, float* part_o, float* part_
                                           const void* k_pool, const void* v_pool, int n_blocks, const int* tok_slot,
                                           const int* tok_pos, const int* block_table, int max_blocks, int n_tokens,
                                           int n_heads, int n_kv_heads, int head_dim, float scale, int window, int chunk,
-                                          int n_splits, int* error_flag, cudaStream_t stream, int* merged) {
+                                          int n_splits, int* error_flag, cudaStream_t stream, int* merged, int clusters) {
   if (counters == nullptr) return XRT_ERR_ARGUMENT;
   return xrt::attention_decode_impl(out, part_o, part_ml, q, k_pool, v_pool, n_blocks, tok_slot, tok_pos, block_table,
                                     max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
-                                    counters, error_flag, stream, merged);
+                                    counters, error_flag, stream, merged, xrt::DecodeFusedInput(), clusters != 0);
 }
 
 // The same, fed with the 32-bit output of the q/k/v product instead of a rotated q: the kernel applies
@@ -929,7 +931,7 @@ XRT_EXPORT int xrt_attention_decode_qkv(void* out, float* part_o, float* part_ml
                                         int write_kv, void* k_pool, void* v_pool, int n_blocks, const int* tok_slot,
                                         const int* tok_pos, const int* block_table, int max_blocks, int n_tokens,
                                         int n_heads, int n_kv_heads, int head_dim, float scale, int window, int chunk,
-                                        int n_splits, int* error_flag, cudaStream_t stream, int* merged) {
+                                        int n_splits, int* error_flag, cudaStream_t stream, int* merged, int clusters) {
   if (qkv == nullptr || (q_norm_w == nullptr) != (k_norm_w == nullptr) || n_blocks <= 0) return XRT_ERR_ARGUMENT;
   if (norm_dtype != XRT_F32 && norm_dtype != XRT_BF16) return XRT_ERR_UNSUPPORTED;
   xrt::DecodeFusedInput fused;
@@ -941,7 +943,7 @@ XRT_EXPORT int xrt_attention_decode_qkv(void* out, float* part_o, float* part_ml
   fused.v_pool = write_kv ? (__nv_bfloat16*)v_pool : nullptr;
   return xrt::attention_decode_impl(out, part_o, part_ml, nullptr, k_pool, v_pool, n_blocks, tok_slot, tok_pos, block_table,
                                     max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
-                                    counters, error_flag, stream, merged, fused);
+                                    counters, error_flag, stream, merged, fused, clusters != 0);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1018,7 +1020,7 @@ int xrt_attention_decode_static(void* out, const void* q, const void* k_pool, co
   // the pools' size is not among this entry's arguments: 0 keeps it on the kernels that need no tensor map
   const int status = xrt_attention_decode(out, scratch + ml_floats, scratch, q, k_pool, v_pool, 0, tok_slot, tok_pos,
                                           block_table, max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, scale,
-                                          window, chunk, n_splits, nullptr, stream, nullptr);
+                                          window, chunk, n_splits, nullptr, stream, nullptr, 1);
   if (status == XRT_ERR_ARGUMENT) xrt::refuse(message, message_len, "xrt_attention_decode_static: the kernel refused its arguments");
   if (status == XRT_ERR_UNSUPPORTED)
     xrt::refuse(message, message_len, "xrt_attention_decode_static: head_dim must be a multiple of 16 up to 256, at most "

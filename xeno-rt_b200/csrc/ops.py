@@ -42,10 +42,10 @@ _SIGNATURES = {
     "xrt_gemm_decode_tcgen05": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_gemm_decode_tcgen05_norm": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _I, _P, _P],
     "xrt_gemm_decode_tcgen05_norm_parts": [_I, _I, _I, _I],
-    "xrt_attention_decode_fused": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P],
-    "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P],
+    "xrt_attention_decode_fused": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P, _I],
+    "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P, _I],
     "xrt_attention_decode_qkv": [_P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I,
-                                 _I, _I, _F, _I, _I, _I, _P, _P, _P],
+                                 _I, _I, _F, _I, _I, _I, _P, _P, _P, _I],
     "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "xrt_attention_prefill_tcgen05": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
@@ -521,10 +521,13 @@ def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0, norm=None) -> 
 
 
 def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int,
-                     head_dim: int, scale: float, window: int, chunk: int, n_splits: int, fused: bool = True) -> None:
+                     head_dim: int, scale: float, window: int, chunk: int, n_splits: int, fused: bool = True,
+                     clusters: bool = True) -> None:
     """bfloat16 attention of one token a sequence over its cache blocks, split along the keys.
     ``fused``: the splits are merged by the last block of each (token, kv head) instead of by a
-    second kernel (needs the device's tile counters; falls back when there are too many)."""
+    second kernel (needs the device's tile counters; falls back when there are too many).
+    ``clusters`` False: the splits never merge as thread-block clusters (for sequences of very unequal
+    lengths: a cluster holds its places until its longest block is done)."""
     n = q.shape[0]
     if q.shape != (n, n_heads * head_dim) or out.shape != q.shape or tok_slot.numel() != n or tok_pos.numel() != n:
         raise KernelError("attention_decode: shapes do not fit")
@@ -543,8 +546,8 @@ def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_h
             _ptr(q, "q", torch.bfloat16), _ptr(k_pool, "k_pool", torch.bfloat16), _ptr(v_pool, "v_pool", torch.bfloat16),
             k_pool.shape[0], _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
             _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
-            float(scale), int(window), int(chunk), int(n_splits), flag.data_ptr(), _stream(), ctypes.byref(merged)),
-            "attention_decode")
+            float(scale), int(window), int(chunk), int(n_splits), flag.data_ptr(), _stream(), ctypes.byref(merged),
+            1 if clusters else 0), "attention_decode")
         if n_splits > 1 and not merged.value and n_splits > attention_decode_fused_max_splits(head_dim, n_heads // n_kv_heads):
             add_launches(1)  # too many splits for the merging block: the combine kernel ran
         return
@@ -553,8 +556,8 @@ def attention_decode(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_h
         _ptr(q, "q", torch.bfloat16), _ptr(k_pool, "k_pool", torch.bfloat16), _ptr(v_pool, "v_pool", torch.bfloat16),
         k_pool.shape[0], _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
         _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
-        float(scale), int(window), int(chunk), int(n_splits), flag.data_ptr(), _stream(), ctypes.byref(merged)),
-        "attention_decode")
+        float(scale), int(window), int(chunk), int(n_splits), flag.data_ptr(), _stream(), ctypes.byref(merged),
+        1 if clusters else 0), "attention_decode")
     if n_splits > 1 and not merged.value:
         add_launches(1)  # the combine kernel
 
@@ -569,7 +572,8 @@ def attention_decode_takes_qkv(n_heads: int, n_kv_heads: int, head_dim: int, rop
 
 def attention_decode_qkv(out, qkv, k_offset: int, v_offset: int, q_norm_w, k_norm_w, eps: float, cos_sin, k_pool, v_pool,
                          tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                         window: int, chunk: int, n_splits: int, write_kv: bool = True, fused: bool = True) -> None:
+                         window: int, chunk: int, n_splits: int, write_kv: bool = True, fused: bool = True,
+                         clusters: bool = True) -> None:
     """Decode attention straight from the 32-bit output of the q/k/v product: per-head norms, rotation,
     the newest key and value into the cache (unless ``write_kv`` is False) and attention over the cache
     in ONE kernel (csrc/attention_decode.cu).  ``qkv``: float32 [n, row] with q at 0, k at ``k_offset``,
@@ -598,7 +602,7 @@ def attention_decode_qkv(out, qkv, k_offset: int, v_offset: int, q_norm_w, k_nor
         _ptr(v_pool, "v_pool", torch.bfloat16), k_pool.shape[0], _ptr(tok_slot, "tok_slot", torch.int32),
         _ptr(tok_pos, "tok_pos", torch.int32), _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n,
         n_heads, n_kv_heads, head_dim, float(scale), int(window), int(chunk), int(n_splits), flag.data_ptr(), _stream(),
-        ctypes.byref(merged)), "attention_decode_qkv")
+        ctypes.byref(merged), 1 if clusters else 0), "attention_decode_qkv")
     if n_splits > 1 and not merged.value and (
             not use_counters or n_splits > attention_decode_fused_max_splits(head_dim, n_heads // n_kv_heads)):
         add_launches(1)  # the combine kernel

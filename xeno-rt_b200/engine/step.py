@@ -21,6 +21,7 @@ import torch
 
 from ..cache import Cache
 from ..core import RuntimeFault
+from ..core.staging import PinnedRing
 from ..csrc import ops
 from ..parts import StepContext
 from ..parts.context import context_bucket
@@ -36,36 +37,6 @@ class StepEntry:
     slot: int
     tokens: list
     want: list = field(default_factory=list)
-
-
-class _Staging:
-    """Pinned host buffers for the step's arrays, used in turn; a buffer is reused only after the
-    copy that read it has completed."""
-
-    def __init__(self, device, count: int = 4):
-        self.device = torch.device(device)
-        self.pinned = self.device.type == "cuda"
-        self.buffers = [None] * count
-        self.events = [None] * count
-        self.turn = 0
-
-    def take(self, n_ints: int):
-        i = self.turn
-        self.turn = (self.turn + 1) % len(self.buffers)
-        if self.events[i] is not None:
-            self.events[i].synchronize()
-        buf = self.buffers[i]
-        if buf is None or buf.numel() < n_ints:
-            size = max(1024, 1 << (n_ints - 1).bit_length())
-            buf = torch.empty(size, dtype=torch.int32, pin_memory=self.pinned)
-            self.buffers[i] = buf
-        return i, buf[:n_ints]
-
-    def copied(self, i: int) -> None:
-        if self.pinned:
-            event = torch.cuda.Event()
-            event.record()
-            self.events[i] = event
 
 
 def batch_bucket(n: int) -> int:
@@ -123,7 +94,12 @@ def fill_arrays(buf: np.ndarray, entries, starts, padded: int, n_rows: int):
     return wanted
 
 
-def context_from(dev: torch.Tensor, padded: int, n_rows: int, new_lens, starts, dtype, max_context=None):
+def mean_context_of(starts, new_lens, rows: int) -> int:
+    """The sequences' lengths after the step, summed and divided by the step's rows (padding rows hold nothing)."""
+    return -(-sum(s + k for s, k in zip(starts, new_lens)) // max(1, rows))
+
+
+def context_from(dev: torch.Tensor, padded: int, n_rows: int, new_lens, starts, dtype, max_context=None, mean_context=None):
     lay = layout(padded, n_rows)
     view = lambda k: dev[lay[k][0]:lay[k][1]]
     return StepContext(
@@ -131,6 +107,7 @@ def context_from(dev: torch.Tensor, padded: int, n_rows: int, new_lens, starts, 
         cu_seqlens=view("cu"), seq_slot=view("seq_slot"), seq_start=view("seq_start"), new_lens=list(new_lens),
         starts=list(starts), all_single=all(k == 1 for k in new_lens), max_new=max(new_lens),
         max_context=max_context if max_context is not None else max(s + k for s, k in zip(starts, new_lens)),
+        mean_context=mean_context if mean_context is not None else mean_context_of(starts, new_lens, n_rows),
         dtype=dtype)
 
 
@@ -144,7 +121,7 @@ def build_context(entries, cache: Cache, vocab_size: int, dtype, device, pad_to:
     padded = max(sum(new_lens), pad_to or 0)
     n = len(entries)
     size = layout(padded, n)["size"]
-    staging = staging or _Staging(device, count=1)
+    staging = staging or PinnedRing(device, count=1)
     turn, host = staging.take(size)
     wanted = fill_arrays(host.numpy(), entries, starts, padded, n)
     dev = host.to(device, non_blocking=True)
@@ -156,7 +133,7 @@ def build_context(entries, cache: Cache, vocab_size: int, dtype, device, pad_to:
 class _DecodeGraph:
     """One captured decode step for up to ``bucket`` sequences."""
 
-    def __init__(self, engine: "Engine", bucket: int, context: int):
+    def __init__(self, engine: "Engine", bucket: int, context: int, mean_context: int):
         model, cache = engine.model, engine.cache
         self.bucket = bucket
         self.size = layout(bucket, bucket)["size"]
@@ -166,7 +143,7 @@ class _DecodeGraph:
         self.static[lay["seq_slot"][0]:lay["seq_slot"][1]] = -1
         self.rows = torch.arange(bucket, dtype=torch.int32, device=model.device)
         make = lambda: context_from(self.static, bucket, bucket, [1] * bucket, [0] * bucket, model.dtype,
-                                    max_context=context)
+                                    max_context=context, mean_context=mean_context)
         side = torch.cuda.Stream(device=model.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -197,14 +174,14 @@ class Engine:
         self.model = model
         self.cache = model.new_cache(max_tokens, max_slots)
         self.last_context = None
-        self.staging = _Staging(model.device)
+        self.staging = PinnedRing(model.device)
         if tuning is not None:
             ops.set_tuning(tuning)
         if use_graphs is None:
             use_graphs = ops.tuning().graphs
         self.use_graphs = use_graphs and model.device.type == "cuda" and model.graph_safe
         self._graphs: "collections.OrderedDict[tuple, _DecodeGraph]" = collections.OrderedDict()
-        #             (batch bucket, context bucket) -> graph, least recently used first
+        #             (batch bucket, context bucket, mean context bucket) -> graph, least recently used first
         self.graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
 
     def open_slot(self) -> int:
@@ -254,7 +231,9 @@ class Engine:
         n = len(entries)
         bucket = batch_bucket(n)
         starts = self.cache.reserve_all([e.slot for e in entries], [1] * n)
-        key = (bucket, context_bucket(max(starts) + 1))
+        # launch shapes follow the longest context and, where lengths are unequal, the mean one (both by
+        # powers of two): attention cuts its keys finer when most sequences are far shorter than the longest
+        key = (bucket, context_bucket(max(starts) + 1), context_bucket(mean_context_of(starts, [1] * n, bucket)))
         g = self._graphs.get(key)
         if g is None:
             while len(self._graphs) >= GRAPH_KEEP:  # a batch that shrinks while its contexts grow meets many keys

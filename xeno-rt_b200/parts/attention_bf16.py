@@ -18,24 +18,32 @@ SPLIT_MERGE_TILES = 0.6    # what every further split costs the merge of a (toke
 #                            at 1, 2 and 4 sequences: 16, 8..16 and 8 splits are the fastest there, not 32, 22 and 13)
 
 
-def decode_split(n_seqs: int, n_kv_heads: int, max_context: int, sms: int):
+def decode_split(n_seqs: int, n_kv_heads: int, max_context: int, sms: int, mean_context: int = 0):
     """(keys a split, number of splits) for decode attention.  Blocks run in rounds of what the GPU
     holds at once; the time is about rounds x (tiles a split + a fixed cost) + a cost of merging that
     grows with the splits, so the split count is chosen to fill the last round (512 pairs of sequence
     and kv head in 2 splits are 2.3 rounds and run like 3; in 4 splits they are 4.6 rounds of half the
     length).  At least two tiles a split where the context allows.  ``sms``: the device's
-    multiprocessors."""
+    multiprocessors.  ``mean_context`` (0: all as long as the longest): what a sequence holds on
+    average; a split beyond a sequence's end has no keys and ends at once, so with unequal lengths
+    only mean / keys-a-split of a sequence's blocks fill the rounds, and finer splits keep the one
+    long sequence from being the whole step's time."""
     blocks = max(1, (max_context + BLOCK_TOKENS - 1) // BLOCK_TOKENS)
+    mean_blocks = blocks if mean_context <= 0 else min(blocks, max(1, -(-mean_context // BLOCK_TOKENS)))
     pairs = max(1, n_seqs * n_kv_heads)
     slots = sms * DECODE_BLOCKS_PER_SM
     costs = {}
     for splits in range(1, max(1, min((blocks + 1) // 2, 64)) + 1):
         tiles = -(-blocks // splits)
-        real = -(-blocks // tiles)  # splits that hold keys
-        clustered = pairs <= ops.tuning().decode_cluster_pairs and real <= CLUSTER_MAX_SPLITS
+        real = -(-blocks // tiles)  # splits that hold keys of the longest sequence
+        working = min(real, -(-mean_blocks // tiles))  # and of a sequence of mean length
+        # clusters only where the lengths are about equal: a cluster holds its places until its longest
+        # block is done (measured with 16 lengths between 249 and 1,997: 166 against 141 microseconds a layer)
+        clustered = (pairs <= ops.tuning().decode_cluster_pairs and real <= CLUSTER_MAX_SPLITS
+                     and mean_blocks == blocks)
         # whole clusters have to find room: about two blocks a multiprocessor instead of three (measured at 4
         # sequences: 8 splits, 256 blocks, beat 13 and 16)
-        rounds = -(-pairs * real // (sms * 2 if clustered else slots))
+        rounds = -(-pairs * working // (sms * 2 if clustered else slots))
         merge = CLUSTER_MERGE_TILES if clustered else SPLIT_MERGE_TILES
         costs.setdefault(real, rounds * (tiles + SPLIT_OVERHEAD_TILES) + merge * real)
     least = min(costs.values())
@@ -44,6 +52,14 @@ def decode_split(n_seqs: int, n_kv_heads: int, max_context: int, sms: int):
     best = min(close, key=lambda n: (blocks % n != 0, n))
     chunk = BLOCK_TOKENS * (-(-blocks // best))
     return chunk, -(-blocks * BLOCK_TOKENS // chunk)
+
+
+def _decode_split_of(ctx, n_kv_heads: int, device):
+    """(keys a split, splits, whether splits may merge as clusters) for the step's lengths, by their powers of two."""
+    sms = ops.device_state(device)[2]
+    longest = context_bucket(ctx.max_context)
+    mean = min(longest, context_bucket(ctx.mean_context)) if ctx.mean_context > 0 else 0
+    return decode_split(ctx.n_tokens, n_kv_heads, longest, sms, mean) + (mean == 0 or mean == longest,)
 
 
 def decode_from_qkv(out, qkv, k_offset, v_offset, q_norm, k_norm, eps, cos_sin, pairing, ctx, store, n_heads, n_kv_heads,
@@ -55,12 +71,11 @@ def decode_from_qkv(out, qkv, k_offset, v_offset, q_norm, k_norm, eps, cos_sin, 
     if not (ctx.all_single and ctx.n_tokens <= 65535
             and ops.attention_decode_takes_qkv(n_heads, n_kv_heads, head_dim, rope_half, pairing)):
         return False
-    sms = ops.device_state(qkv.device)[2]
-    chunk, n_splits = decode_split(ctx.n_tokens, n_kv_heads, context_bucket(ctx.max_context), sms)
+    chunk, n_splits, clusters = _decode_split_of(ctx, n_kv_heads, qkv.device)
     fused = ctx.n_tokens * n_kv_heads <= FUSED_COMBINE_MAX
     ops.attention_decode_qkv(out, qkv, k_offset, v_offset, q_norm, k_norm, eps, cos_sin, store.k, store.v, ctx.tok_slot,
                              ctx.tok_pos, store.block_table, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
-                             write_kv=write_kv, fused=fused)
+                             write_kv=write_kv, fused=fused, clusters=clusters)
     return True
 
 
@@ -68,13 +83,12 @@ def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window) -> boo
     if n_heads // n_kv_heads > 16:
         return False
     if ctx.all_single and ctx.n_tokens <= 65535:
-        sms = ops.device_state(q.device)[2]
-        chunk, n_splits = decode_split(ctx.n_tokens, n_kv_heads, context_bucket(ctx.max_context), sms)
+        chunk, n_splits, clusters = _decode_split_of(ctx, n_kv_heads, q.device)
         # few sequences: the last block of a (token, kv head) merges its splits (one launch less);
         # many: a second kernel merges them with more threads (measured faster from 8 sequences on)
         fused = ctx.n_tokens * n_kv_heads <= FUSED_COMBINE_MAX
         ops.attention_decode(out, q, store.k, store.v, ctx.tok_slot, ctx.tok_pos, store.block_table, n_heads,
-                             n_kv_heads, head_dim, scale, window, chunk, n_splits, fused=fused)
+                             n_kv_heads, head_dim, scale, window, chunk, n_splits, fused=fused, clusters=clusters)
         return True
     if ctx.n_seqs <= 65535 and n_heads <= 65535:
         if (head_dim == 128 and window == 0 and ctx.max_new >= TCGEN05_MIN_NEW

@@ -18,7 +18,8 @@ class StepContext:
     ``seq_start`` [n] length of each sequence before this step.
     Host values: ``new_lens`` tokens each sequence brings; ``starts``; ``all_single`` every
     sequence brings exactly one token (a decode step); ``max_new`` and ``max_context`` the
-    largest new-token count and the largest length after the step.
+    largest new-token count and the largest length after the step; ``mean_context`` the lengths
+    after the step summed over the sequences and divided by the rows of the step (0: not known).
     ``shared`` holds what parts compute once per step and share across layers (rotation tables).
     """
     n_tokens: int
@@ -35,6 +36,7 @@ class StepContext:
     max_new: int
     max_context: int
     dtype: DType
+    mean_context: int = 0
     captured: bool = False  # the step is being captured into (or replayed from) a CUDA graph:
     #                         launch shapes must not depend on the sequences' lengths
     shared: dict = field(default_factory=dict)
