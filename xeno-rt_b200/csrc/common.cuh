@@ -123,6 +123,48 @@ inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
   cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
 }
 
+// The same launch with a range of global memory that the kernel reads once (a weight): its lines
+// are marked as streaming in the L2 (an access-policy window of the launch), so they are the first to
+// leave and what the step reads again stays.  For kernels whose copies cannot carry a cache hint
+// themselves.  The window is cut to what the device allows.
+template <typename... KArgs, typename... Args>
+inline void launch_kernel_streaming(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    const void* read_once, size_t read_once_bytes, Args... args) {
+  static int max_window = -1;
+  if (max_window < 0) {
+    int device = 0, value = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&value, cudaDevAttrMaxAccessPolicyWindowSize, device) != cudaSuccess)
+      value = 0;
+    cudaGetLastError();
+    max_window = value;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  int n = 0;
+  if (pdl_enabled()) {
+    attribute[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (max_window > 0 && read_once != nullptr && read_once_bytes > 0) {
+    attribute[n].id = cudaLaunchAttributeAccessPolicyWindow;
+    attribute[n].val.accessPolicyWindow.base_ptr = const_cast<void*>(read_once);
+    attribute[n].val.accessPolicyWindow.num_bytes = read_once_bytes < (size_t)max_window ? read_once_bytes : (size_t)max_window;
+    attribute[n].val.accessPolicyWindow.hitRatio = 1.0f;
+    attribute[n].val.accessPolicyWindow.hitProp = cudaAccessPropertyStreaming;
+    attribute[n].val.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+    ++n;
+  }
+  config.attrs = n ? attribute : nullptr;
+  config.numAttrs = n;
+  cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+
 inline int launch_status() {
   cudaError_t err = cudaPeekAtLastError();
   return err == cudaSuccess ? XRT_OK : (int)err;

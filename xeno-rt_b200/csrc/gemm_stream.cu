@@ -215,8 +215,10 @@ int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, 
     allowed = true;
   }
   const int blocks = (N + ROW_GROUPS * GS_ROWS - 1) / (ROW_GROUPS * GS_ROWS);
-  launch_kernel(kernel, dim3(blocks), dim3(GS_THREADS), SMEM, stream, (TO*)out, (const __nv_bfloat16*)x,
-                (const __nv_bfloat16*)w, M, N, K, ldx, ldo, up_offset, emit);
+  // the weight is read once a step (cp.async carries no cache hint here): marked as streaming in the L2
+  const size_t weight_bytes = ((size_t)(MODE == 2 ? up_offset / K : 0) + (size_t)N) * (size_t)K * sizeof(__nv_bfloat16);
+  launch_kernel_streaming(kernel, dim3(blocks), dim3(GS_THREADS), SMEM, stream, w, weight_bytes, (TO*)out,
+                          (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, M, N, K, ldx, ldo, up_offset, emit);
   return launch_status();
 }
 

@@ -22,7 +22,8 @@ def aligned(x, weight) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and weight.is_contiguous())
 
 
-ACCUMULATE_MIN_K = 16384
+ACCUMULATE_MIN_K = 16384       # from here on a product that adds into the residual stream may take the tcgen05 kernel
+ACCUMULATE_MIN_K_9_ROWS = 8192  # and from here on with 9 to 16 rows
 
 
 def tcgen05_for_few_rows(sms: int, rows: int, n: int, k: int, mode: str) -> bool:
@@ -30,10 +31,13 @@ def tcgen05_for_few_rows(sms: int, rows: int, n: int, k: int, mode: str) -> bool
     multiprocessor in rounds: it wins where they fill the rounds (one round at least 0.6 full, or
     several at least 0.85 full).  Products that add into the residual stream stay on the cp.async
     kernel unless K is long (it slows down with K: 2.6 TB/s at K = 25,600, where the tcgen05 kernel
-    reaches 4 TB/s).  Whole steps of 8 sequences at a width of 5,120 and an inner size of 25,600 went
-    from 18.0 to 15.8 ms with this rule, and at 4,096 / 14,336 from 4.62 to 4.40 ms; with the limit at
-    8,192 instead the first gains another 1.5 % and single sequences at the second lose 4.5 %."""
-    if mode == "accumulate" and k < ACCUMULATE_MIN_K:
+    reaches 4 TB/s) and, below K = 16,384, the rows are more than 8 (its time grows with the rows, the
+    tcgen05 kernel's does not).  Measured, whole steps at a width of 4,096 and an inner size of 14,336,
+    the down product on the tcgen05 kernel against the cp.async kernel: 1 sequence 3.50 against 3.39 ms,
+    8 sequences 4.04 against 4.04, 16 sequences 4.80 against 4.94; and the output product too (K = 4,096):
+    3.68, 4.17 and 4.86 ms.  At a width of 5,120 and an inner size of 25,600, 8 sequences: 15.8 against
+    18.0 ms with the long-K rule."""
+    if mode == "accumulate" and k < (ACCUMULATE_MIN_K if rows <= 8 else ACCUMULATE_MIN_K_9_ROWS):
         return False
     rounds, fill = ops.gemm_decode_tcgen05_fill(sms, rows, n, k, mode)
     return fill >= 0.6 and (rounds == 1 or fill >= 0.85)
