@@ -147,7 +147,7 @@ def test_which_kernel_takes_a_decode_product_of_few_rows():
         assert not choice(sms, rows, 10240, 5120, "store")     # 80 items: 0.54 full
         assert not choice(sms, rows, 25600, 5120, "swiglu")    # 200 tiles: two rounds, 0.68 full
         assert choice(sms, rows, 5120, 25600, "accumulate")    # long K
-        assert choice(sms, rows, 5120, 8192, "accumulate") == (rows > 8)
+        assert choice(sms, rows, 5120, 8192, "accumulate")     # 640 blocks of the cp.async kernel: two rounds, 0.54 full
 
 
 def test_decode_attention_splits_cover_the_context_and_fill_the_rounds():

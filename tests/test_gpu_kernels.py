@@ -650,9 +650,18 @@ def test_a_product_prepares_the_norm_that_follows_and_the_next_product_finishes_
     o.gemm_decode_tcgen05(act2, scaled, w_next, "swiglu", up_rows=out_rows, squares=squares, eps=eps)
     gate_up = normed @ f64(w_next).T
     assert rel(act2, pm.swiglu(gate_up[:, :out_rows], gate_up[:, out_rows:])) < 1.2e-2
+    # the cp.async kernel finishes a pending norm too
+    out.fill_(7.0)
+    o.gemm_stream(out, scaled, w_next, "store", squares=squares, eps=eps)
+    assert rel(out, normed @ f64(w_next).T) < 6e-3
+    act2.fill_(7.0)
+    o.gemm_stream(act2, scaled, w_next, "swiglu", up_rows=out_rows, squares=squares, eps=eps)
+    assert rel(act2, pm.swiglu(gate_up[:, :out_rows], gate_up[:, out_rows:])) < 1.2e-2
     o.check_error_flag(DEV)
     with pytest.raises(Exception):
         o.gemm_stream(x, act, w_down, "store", norm=(scaled, w_norm, squares))
+    with pytest.raises(Exception):
+        o.gemm_stream(x, act, w_down, "accumulate", squares=squares, eps=eps)
 
 
 @pytest.mark.parametrize("m", [5, 17, 40, 64, 128])

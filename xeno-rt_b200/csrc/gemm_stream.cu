@@ -45,7 +45,7 @@ __device__ __forceinline__ void gs_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
 template <int M_TILES, int MODE, int GS_STAGES, int ROW_GROUPS, typename TO>
 __global__ void __launch_bounds__(GS_THREADS, (M_TILES >= 4 ? 2 : 1))
 gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                   int M, int N, int K, int ldx, int ldo, long long up_offset, const NormEmit emit) {
+                   int M, int N, int K, int ldx, int ldo, long long up_offset, const NormEmit emit, const RowScale scale) {
   // ROW_GROUPS groups of 8 weight rows a block (SwiGLU: as many gate groups and as many up groups);
   // every X fragment a warp loads is used for all of them, which is what keeps the L1 traffic of
   // many batch rows below the shared-memory traffic of the weights
@@ -97,6 +97,18 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
   // The weights do not depend on the step: the first slabs are on their way while the kernel before
   // this one finishes.  X and the output do: wait for it here.
   pdl_wait();
+  // x with a pending norm (the product before this one left residual * norm weight and the parts of every
+  // row's sum of squares): warp w adds the parts of rows w, w + 8, ... in a fixed order; the factors
+  // 1 / sqrt(mean square + eps) multiply the finished sums below
+  __shared__ float row_inv[M_TILES * 16];
+  if (MODE != 1 && scale.squares != nullptr) {
+    for (int m = warp; m < M; m += GS_WARPS) {
+      float sum = 0.f;
+      for (int p = lane; p < scale.parts; p += 32) sum += __ldcg(scale.squares + (size_t)p * M + m);
+      sum = warp_sum(sum);
+      if (lane == 0) row_inv[m] = rsqrtf(sum / (float)scale.width + scale.eps);
+    }
+  }
   const __nv_bfloat16* xlo[M_TILES];
   const __nv_bfloat16* xhi[M_TILES];
 #pragma unroll
@@ -179,9 +191,10 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
     };
     float square = 0.f;
     if (live) {
-      const float first = total(rg);
+      const float inv = (MODE != 1 && scale.squares != nullptr) ? row_inv[m] : 1.f;
+      const float first = total(rg) * inv;
       TO* dst = out + (size_t)m * ldo + row;
-      if (MODE == 2) *dst = from_float<TO>((first / (1.0f + expf(-first))) * total(ROW_GROUPS + rg));
+      if (MODE == 2) *dst = from_float<TO>((first / (1.0f + expf(-first))) * (total(ROW_GROUPS + rg) * inv));
       else if (MODE == 1) {
         const float updated = to_float(*dst) + first;
         *dst = from_float<TO>(updated);
@@ -202,7 +215,7 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
 
 template <int M_TILES, int MODE, int GS_STAGES, int ROW_GROUPS, typename TO>
 int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
-                         long long up_offset, const NormEmit& emit, cudaStream_t stream) {
+                         long long up_offset, const NormEmit& emit, const RowScale& scale, cudaStream_t stream) {
   constexpr int GROUPS = ROW_GROUPS * (MODE == 2 ? 2 : 1);
   constexpr int RING_BYTES = GS_STAGES * GROUPS * GS_ROWS * GS_ROW_BYTES;
   constexpr int PARTIAL_BYTES = GS_WARPS * GROUPS * M_TILES * 16 * (GS_ROWS + 1) * (int)sizeof(float);
@@ -218,7 +231,7 @@ int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, 
   // the weight is read once a step (cp.async carries no cache hint here): marked as streaming in the L2
   const size_t weight_bytes = ((size_t)(MODE == 2 ? up_offset / K : 0) + (size_t)N) * (size_t)K * sizeof(__nv_bfloat16);
   launch_kernel_streaming(kernel, dim3(blocks), dim3(GS_THREADS), SMEM, stream, w, weight_bytes, (TO*)out,
-                          (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, M, N, K, ldx, ldo, up_offset, emit);
+                          (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, M, N, K, ldx, ldo, up_offset, emit, scale);
   return launch_status();
 }
 
@@ -227,23 +240,24 @@ int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, 
 // 5) and lose on others; over a whole decode step of 8 sequences 3 stages is the fastest.
 template <int M_TILES, int MODE, typename TO>
 int launch_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, long long up_offset,
-                  const NormEmit& emit, cudaStream_t stream) {
+                  const NormEmit& emit, const RowScale& scale, cudaStream_t stream) {
   // more than 32 batch rows: two row groups a block halve the X traffic per weight byte
   constexpr int RG = M_TILES >= 4 ? 2 : 1;
-  return launch_stream_staged<M_TILES, MODE, 3, RG, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, stream);
+  return launch_stream_staged<M_TILES, MODE, 3, RG, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, scale, stream);
 }
 
 template <int M_TILES>
 int dispatch_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, int out_dtype,
-                    int mode, long long up_offset, const NormEmit& emit, cudaStream_t stream) {
-  if (mode == 1) return launch_stream<M_TILES, 1, float>(out, x, w, M, N, K, ldx, ldo, 0, emit, stream);
+                    int mode, long long up_offset, const NormEmit& emit, const RowScale& scale, cudaStream_t stream) {
+  if (mode == 1) return launch_stream<M_TILES, 1, float>(out, x, w, M, N, K, ldx, ldo, 0, emit, scale, stream);
   if (mode == 2) {
     if (out_dtype == XRT_BF16)
-      return launch_stream<M_TILES, 2, __nv_bfloat16>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, stream);
-    return launch_stream<M_TILES, 2, float>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, stream);
+      return launch_stream<M_TILES, 2, __nv_bfloat16>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, scale, stream);
+    return launch_stream<M_TILES, 2, float>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, scale, stream);
   }
-  if (out_dtype == XRT_BF16) return launch_stream<M_TILES, 0, __nv_bfloat16>(out, x, w, M, N, K, ldx, ldo, 0, emit, stream);
-  return launch_stream<M_TILES, 0, float>(out, x, w, M, N, K, ldx, ldo, 0, emit, stream);
+  if (out_dtype == XRT_BF16)
+    return launch_stream<M_TILES, 0, __nv_bfloat16>(out, x, w, M, N, K, ldx, ldo, 0, emit, scale, stream);
+  return launch_stream<M_TILES, 0, float>(out, x, w, M, N, K, ldx, ldo, 0, emit, scale, stream);
 }
 
 }  // namespace xrt
@@ -261,9 +275,16 @@ XRT_EXPORT int xrt_gemm_stream_norm_blocks(int M, int N) {
 // the file's head): scaled = bfloat16 [M, ld_scaled] receives (new residual) * norm_weight ([N], in
 // norm_dtype), squares = float32 [xrt_gemm_stream_norm_blocks(M, N), M] the blocks' sums of squares.
 // Only for M <= 16 (one group of weight rows a block).
-XRT_EXPORT int xrt_gemm_stream_norm(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
-                                    int out_dtype, int mode, int up_rows, void* scaled, int ld_scaled,
-                                    const void* norm_weight, int norm_dtype, float* squares, cudaStream_t stream) {
+// in_squares not null (modes 0 and 2): x is the result of such a product, residual * norm weight, and
+// in_squares = float32 [in_parts, M] the parts of its rows' sums of squares: every row of the result is
+// multiplied by 1 / sqrt(sum of the row's parts / K + eps).
+XRT_EXPORT int xrt_gemm_stream_normed(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
+                                      int out_dtype, int mode, int up_rows, void* scaled, int ld_scaled,
+                                      const void* norm_weight, int norm_dtype, float* squares, const float* in_squares,
+                                      int in_parts, float eps, cudaStream_t stream) {
+  if (in_squares != nullptr && (in_parts <= 0 || mode == 1)) return XRT_ERR_ARGUMENT;
+  xrt::RowScale scale;
+  scale.squares = in_squares; scale.parts = in_parts; scale.width = K; scale.eps = eps;
   if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldo < N || mode < 0 || mode > 2) return XRT_ERR_ARGUMENT;
   if (mode == 1 && out_dtype != XRT_F32) return XRT_ERR_ARGUMENT;
   if (out_dtype != XRT_F32 && out_dtype != XRT_BF16) return XRT_ERR_UNSUPPORTED;
@@ -278,9 +299,17 @@ XRT_EXPORT int xrt_gemm_stream_norm(void* out, const void* x, const void* w, int
   }
   if (M == 0) return XRT_OK;
   const long long up_offset = (long long)up_rows * K;
-  if (M <= 16) return xrt::dispatch_stream<1>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, emit, stream);
-  if (M <= 32) return xrt::dispatch_stream<2>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, emit, stream);
-  return xrt::dispatch_stream<4>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, emit, stream);
+  if (M <= 16) return xrt::dispatch_stream<1>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, emit, scale, stream);
+  if (M <= 32) return xrt::dispatch_stream<2>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, emit, scale, stream);
+  return xrt::dispatch_stream<4>(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_offset, emit, scale, stream);
+}
+
+// The same with an x that is what it is.
+XRT_EXPORT int xrt_gemm_stream_norm(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
+                                    int out_dtype, int mode, int up_rows, void* scaled, int ld_scaled,
+                                    const void* norm_weight, int norm_dtype, float* squares, cudaStream_t stream) {
+  return xrt_gemm_stream_normed(out, x, w, M, N, K, ldx, ldo, out_dtype, mode, up_rows, scaled, ld_scaled, norm_weight,
+                                norm_dtype, squares, nullptr, 0, 0.f, stream);
 }
 
 // The same without a norm to prepare.

@@ -36,6 +36,7 @@ _SIGNATURES = {
     "xrt_gemm_reference": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_stream_norm": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P, _P],
+    "xrt_gemm_stream_normed": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P, _P, _I, _F, _P],
     "xrt_gemm_tcgen05_normed": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _I, _P, _P, _I, _F, _P],
     "xrt_gemm_decode_tcgen05_normed": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P],
     "xrt_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -490,12 +491,14 @@ def gemm_stream_norm_parts(m: int, n: int) -> int:
     return parts
 
 
-def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0, norm=None) -> None:
+def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0, norm=None, squares=None, eps: float = 0.0) -> None:
     """bfloat16 product for at most 64 rows that streams the weight once; ``mode`` is "store",
     "accumulate" (into a float32 out) or "swiglu" (out[m, n] = silu(x . w[n]) * (x . w[n + up_rows])).
     ``norm`` = (scaled, weight, squares) with "accumulate" and at most 16 rows: the product also
     prepares the RMSNorm that follows it: ``scaled`` (bfloat16 [m, n]) receives the new residual times
-    ``weight`` ([n]), ``squares`` (float32 [gemm_stream_norm_parts(m, n), m]) its sums of squares."""
+    ``weight`` ([n]), ``squares`` (float32 [gemm_stream_norm_parts(m, n), m]) its sums of squares.
+    ``squares`` (float32 [parts, m], with "store" or "swiglu"): ``x`` is such a prepared input, and every
+    row's result is multiplied by 1 / sqrt(sum of its parts / k + eps) (as for ``gemm_decode_tcgen05``)."""
     m, k = x.shape
     n = out.shape[1]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -506,6 +509,13 @@ def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0, norm=None) -> 
     if x.stride(1) != 1 or out.stride(1) != 1 or not x.is_cuda or not out.is_cuda:
         raise KernelError("gemm_stream: rows must be contiguous and on a CUDA device")
     code = {"store": 0, "accumulate": 1, "swiglu": 2}[mode]
+    if squares is not None:
+        if norm is not None or mode == "accumulate" or squares.dim() != 2 or squares.shape[1] != m or not squares.is_contiguous():
+            raise KernelError("gemm_stream: squares must be [parts, rows], and not with accumulate or a following norm")
+        _check(_kernels().xrt_gemm_stream_normed(
+            out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0), _code(out.dtype), code, up_rows,
+            0, 0, 0, 0, 0, _ptr(squares, "squares", torch.float32), squares.shape[0], float(eps), _stream()), "gemm_stream")
+        return
     if norm is None:
         _check(_kernels().xrt_gemm_stream(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
                                          _code(out.dtype), code, up_rows, _stream()), "gemm_stream")

@@ -24,6 +24,15 @@ def aligned(x, weight) -> bool:
 
 ACCUMULATE_MIN_K = 16384       # from here on a product that adds into the residual stream may take the tcgen05 kernel
 ACCUMULATE_MIN_K_9_ROWS = 8192  # and from here on with 9 to 16 rows
+STREAM_BLOCKS_PER_SM = 4        # blocks of the cp.async kernel that a multiprocessor holds at once (registers)
+
+
+def stream_kernel_waves(sms: int, n: int) -> float:
+    """How full the cp.async kernel's rounds of blocks are for ``n`` weight rows (8 rows a block): 1 when all
+    blocks run at once, else rounds / whole rounds.  640 blocks on 592 places are two rounds, the second
+    nearly empty: such a product runs at half its rate (measured: 84 MB in 33 microseconds)."""
+    waves = -(-n // 8) / (sms * STREAM_BLOCKS_PER_SM)
+    return 1.0 if waves <= 1.0 else waves / -(-waves // 1)
 
 
 def tcgen05_for_few_rows(sms: int, rows: int, n: int, k: int, mode: str) -> bool:
@@ -32,15 +41,17 @@ def tcgen05_for_few_rows(sms: int, rows: int, n: int, k: int, mode: str) -> bool
     several at least 0.85 full).  Products that add into the residual stream stay on the cp.async
     kernel unless K is long (it slows down with K: 2.6 TB/s at K = 25,600, where the tcgen05 kernel
     reaches 4 TB/s) and, below K = 16,384, the rows are more than 8 (its time grows with the rows, the
-    tcgen05 kernel's does not).  Measured, whole steps at a width of 4,096 and an inner size of 14,336,
-    the down product on the tcgen05 kernel against the cp.async kernel: 1 sequence 3.50 against 3.39 ms,
-    8 sequences 4.04 against 4.04, 16 sequences 4.80 against 4.94; and the output product too (K = 4,096):
-    3.68, 4.17 and 4.86 ms.  At a width of 5,120 and an inner size of 25,600, 8 sequences: 15.8 against
-    18.0 ms with the long-K rule."""
-    if mode == "accumulate" and k < (ACCUMULATE_MIN_K if rows <= 8 else ACCUMULATE_MIN_K_9_ROWS):
-        return False
+    tcgen05 kernel's does not), or unless the cp.async kernel's own rounds of blocks are badly filled.
+    Measured, whole steps at a width of 4,096 and an inner size of 14,336, the down product on the
+    tcgen05 kernel against the cp.async kernel: 1 sequence 3.50 against 3.39 ms, 8 sequences 4.04
+    against 4.04, 16 sequences 4.80 against 4.94; and the output product too (K = 4,096): 3.68, 4.17
+    and 4.86 ms.  At a width of 5,120 and an inner size of 25,600, 8 sequences: 15.8 against 18.0 ms
+    with the long-K rule."""
     rounds, fill = ops.gemm_decode_tcgen05_fill(sms, rows, n, k, mode)
-    return fill >= 0.6 and (rounds == 1 or fill >= 0.85)
+    fills = fill >= 0.6 and (rounds == 1 or fill >= 0.85)
+    if mode == "accumulate" and k < (ACCUMULATE_MIN_K if rows <= 8 else ACCUMULATE_MIN_K_9_ROWS):
+        return fills and fill > stream_kernel_waves(sms, n) + 0.2
+    return fills
 
 
 def _decode_kernel(rows: int, n: int, k: int, mode: str, device) -> str:
@@ -65,24 +76,31 @@ def _product(out, x, weight, mode: str, up_rows: int = 0) -> None:
 
 
 def takes_pending(rows: int, n: int, k: int, mode: str, device) -> bool:
-    """Whether a product of these sizes would run on the kernel that can finish a pending norm (the
-    tcgen05 few-row product), so that the product before it may prepare the norm instead of a kernel."""
+    """Whether the product before one of these sizes should prepare its input's norm instead of a norm
+    kernel: where the tcgen05 kernels take the product.  The cp.async kernel can finish a pending norm
+    too, but every one of its many short-lived blocks then adds up the parts of the rows' sums of
+    squares before its first product: at a width of 5,120 and an inner size of 25,600 a step of 8
+    sequences took 14.93 ms that way against 14.68 ms with the two norm kernels a layer
+    (``ops.Tuning.pending_norm`` = "force" chooses it all the same)."""
     wish = ops.tuning().pending_norm
     if k % 8 or wish == "off":
         return False
-    if rows > ops.DECODE_TCGEN05_MAX_ROWS:
-        return True  # the tiled tcgen05 product of prompts
-    if ops.tuning().decode_gemm == "stream" and wish != "force":
-        return False
-    if rows > STREAM_ROWS or ops.tuning().decode_gemm == "tcgen05" or wish == "force":
+    if rows > ops.DECODE_TCGEN05_MAX_ROWS or wish == "force":
         return True
-    return tcgen05_for_few_rows(ops.device_state(device)[2], rows, n, k, mode)
+    return _decode_kernel(rows, n, k, mode, device) == "tcgen05"
 
 
 def run_pending(out, pending, weight, up_rows: int = 0) -> None:
     """out = the product of a pending norm's result with weight^T (SwiGLU with ``up_rows``)."""
-    kernel = ops.gemm_decode_tcgen05 if pending.shape[0] <= ops.DECODE_TCGEN05_MAX_ROWS else ops.gemm_tcgen05
-    kernel(out, pending.scaled, weight, "swiglu" if up_rows else "store", up_rows, squares=pending.squares, eps=pending.eps)
+    rows = pending.shape[0]
+    mode = "swiglu" if up_rows else "store"
+    if rows > ops.DECODE_TCGEN05_MAX_ROWS:
+        kernel = ops.gemm_tcgen05
+    elif _decode_kernel(rows, out.shape[1], pending.scaled.shape[1], mode, out.device) == "stream":
+        kernel = ops.gemm_stream
+    else:
+        kernel = ops.gemm_decode_tcgen05
+    kernel(out, pending.scaled, weight, mode, up_rows, squares=pending.squares, eps=pending.eps)
 
 
 def run_with_norm(out, x, weight, norm):
