@@ -324,6 +324,10 @@ __global__ void attention_combine_kernel(__nv_bfloat16* __restrict__ out, const 
 // the wait for tile i.  The wait is bounded: if it runs out the block raises the error flag, waits
 // (bounded) for its copies in flight and leaves without writing.
 constexpr int DEC_BOX_BYTES = 64 * 128;
+// Tiles of 64 keys and values in shared memory: one being worked on, the others on their way.  Three were
+// measured against two at the 8B shape, context 4,096: the same time at 1 to 16 sequences, 9.48 against
+// 9.15 ms at 64 (a block of 97 KB leaves room for two a multiprocessor instead of three).
+constexpr int DEC_STAGES = 2;
 constexpr unsigned DEC_SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t dec_map_rank(uint32_t local_smem, int rank) {  // the same place in another block of the cluster
@@ -380,7 +384,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __shared__ __align__(16) __nv_bfloat16 newest[2][HD_MAX];  // the step's own key and value of this kv head
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) uint64_t full[2];
+  __shared__ __align__(8) uint64_t full[DEC_STAGES];
   pdl_trigger();
   // The step's arrays (slots, positions, block table) were written before the step began: they may be
   // read, and tiles of old keys fetched, while the kernel before this one (which writes q and the
@@ -407,12 +411,13 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int boxes = head_dim / 64;
   const int tile_bytes = boxes * DEC_BOX_BYTES;
-  unsigned char* k_tiles = smem;                   // [2][boxes][64 rows x 128 bytes]
-  unsigned char* v_tiles = smem + 2 * tile_bytes;
-  const uint32_t full_addr[2] = {smem_addr(&full[0]), smem_addr(&full[1])};
+  unsigned char* k_tiles = smem;                   // [stages][boxes][64 rows x 128 bytes]
+  unsigned char* v_tiles = smem + DEC_STAGES * tile_bytes;
+  const uint32_t full_base = smem_addr(&full[0]);
+  auto full_addr = [full_base](int stage) { return full_base + 8u * (uint32_t)stage; };
   if (threadIdx.x == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full_addr[0]));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full_addr[1]));
+#pragma unroll
+    for (int j = 0; j < DEC_STAGES; ++j) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full_addr(j)));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -423,16 +428,16 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   auto issue_tile = [&](int tile_index, int buffer) {  // one thread
     const int key0 = begin + tile_index * XRT_BLOCK_TOKENS;
     const int row0 = (blocks[key0 / XRT_BLOCK_TOKENS] * n_kv_heads + kv_head) * XRT_BLOCK_TOKENS;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_addr[buffer]), "r"(2 * tile_bytes)
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_addr(buffer)), "r"(2 * tile_bytes)
                  : "memory");
     // one copy a tile: the map's third dimension walks the row's pieces of 64 dims, so that the boxes of 64 rows x
     // 128 bytes land one behind the other (a copy instruction costs the thread that issues it about 200 cycles,
     // and this thread's warp has its 16 keys to work on like the others)
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
-                 ::"r"(smem_addr(k_tiles + buffer * tile_bytes)), "l"(&map_k), "r"(0), "r"(row0), "r"(0), "r"(full_addr[buffer]), "l"(once)
+                 ::"r"(smem_addr(k_tiles + buffer * tile_bytes)), "l"(&map_k), "r"(0), "r"(row0), "r"(0), "r"(full_addr(buffer)), "l"(once)
                  : "memory");
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
-                 ::"r"(smem_addr(v_tiles + buffer * tile_bytes)), "l"(&map_v), "r"(0), "r"(row0), "r"(0), "r"(full_addr[buffer]), "l"(once)
+                 ::"r"(smem_addr(v_tiles + buffer * tile_bytes)), "l"(&map_v), "r"(0), "r"(row0), "r"(0), "r"(full_addr(buffer)), "l"(once)
                  : "memory");
   };
 
@@ -549,19 +554,23 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   HeadColumnState<D_TILES> st;
   st.init();
   const int n_tiles = has_keys ? (end - begin + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS : 0;  // begin is a multiple of 64
-  if (threadIdx.x == 0 && n_tiles > 0 && !early) issue_tile(0, 0);
+  if (threadIdx.x == 0) {
+    if (n_tiles > 0 && !early) issue_tile(0, 0);
+    for (int j = 1; j < DEC_STAGES - 1 && j < n_tiles; ++j) issue_tile(j, j);
+  }
   int failed = 0, i = 0;
   for (; i < n_tiles; ++i) {
-    // the buffer of tile i + 1 held tile i - 1, which every warp left before the barrier that ended the last round
-    if (threadIdx.x == 0 && i + 1 < n_tiles) issue_tile(i + 1, (i + 1) & 1);
-    if (!dec_mbar_wait(full_addr[i & 1], (uint32_t)(i >> 1) & 1u)) failed = 1;
+    // the buffer of tile i + stages - 1 held tile i - 1, which every warp left before the barrier that ended the last round
+    const int ahead = i + DEC_STAGES - 1, stage = i % DEC_STAGES;
+    if (threadIdx.x == 0 && ahead < n_tiles) issue_tile(ahead, ahead % DEC_STAGES);
+    if (!dec_mbar_wait(full_addr(stage), (uint32_t)(i / DEC_STAGES) & 1u)) failed = 1;
     if (writes_newest && i == n_tiles - 1) {
       // the newest key and value into their row of the tile that has just landed (whatever the copy
       // read there): piece c of row r lies at piece c ^ (r % 8) of its box of 64 dims
       const int r = (len - 1) % XRT_BLOCK_TOKENS;
       if (threadIdx.x < 2 * (HD_MAX / 8)) {
         const int which = threadIdx.x / (HD_MAX / 8), piece = threadIdx.x % (HD_MAX / 8);
-        unsigned char* tile = (which == 0 ? k_tiles : v_tiles) + (i & 1) * tile_bytes;
+        unsigned char* tile = (which == 0 ? k_tiles : v_tiles) + stage * tile_bytes;
         *reinterpret_cast<uint4*>(tile + (piece >> 3) * DEC_BOX_BYTES + r * 128 + (((piece & 7) ^ (r & 7)) << 4)) =
             *reinterpret_cast<const uint4*>(&newest[which][piece * 8]);
       }
@@ -569,7 +578,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
     const int key_abs = begin + i * XRT_BLOCK_TOKENS + warp * 16;
     if (!failed && key_abs < end)  // only the first and the last 16 keys a warp sees can hold a hidden key
-      attend_16_keys_heads<D_TILES, true>(st, qb, k_tiles + (i & 1) * tile_bytes, v_tiles + (i & 1) * tile_bytes,
+      attend_16_keys_heads<D_TILES, true>(st, qb, k_tiles + stage * tile_bytes, v_tiles + stage * tile_bytes,
                                           warp * 16, key_abs, first_key, len,
                                           key_abs < first_key || key_abs + 16 > len, head_dim, scale_log2);
     if (__syncthreads_or(failed)) { failed = 1; break; }
@@ -578,8 +587,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     if (threadIdx.x == 0) {
       if (error_flag != nullptr) atomicCAS(error_flag, 0, 6);
       // copies in flight write this block's shared memory: they must have landed before it is given back
-      dec_mbar_wait(full_addr[i & 1], (uint32_t)(i >> 1) & 1u);
-      if (i + 1 < n_tiles) dec_mbar_wait(full_addr[(i + 1) & 1], (uint32_t)((i + 1) >> 1) & 1u);
+      for (int j = i; j < i + DEC_STAGES && j < n_tiles; ++j)
+        dec_mbar_wait(full_addr(j % DEC_STAGES), (uint32_t)(j / DEC_STAGES) & 1u);
     }
     __syncthreads();
     if (!clustered) return;  // in a cluster the block still meets the others (its state below is meaningless)
@@ -679,7 +688,7 @@ constexpr int DEC_MAX_CLUSTER = 16;
 // block's merged state for the cluster merge
 inline int decode_tma_smem(int head_dim) {
   const int merge_bytes = DEC_WARPS * 16 * (2 + head_dim + 8) * (int)sizeof(float) + (2 * 16 + 8 * head_dim) * (int)sizeof(float);
-  return 1024 + max(4 * (head_dim / 64) * DEC_BOX_BYTES, merge_bytes);
+  return 1024 + max(2 * DEC_STAGES * (head_dim / 64) * DEC_BOX_BYTES, merge_bytes);
 }
 
 // Tuning::decode_attention = 3 keeps the merge by a second kernel or by the last block, for comparison.
