@@ -244,7 +244,9 @@ def run_workload(args) -> int:
     """The two stated workloads beside the headline: 16 prompts of seeded uniform lengths in [64, 2048] in
     one step of unequal lengths, then 256 decode steps (Qwen3-8B shape); 8 prompts of 2,048 tokens, then 512
     decode steps (Qwen3-32B shape).  Both through ``Session.generate_batch`` (host token ids in and out,
-    host clock), run twice: the first run captures the decode graphs.  Prints one JSON line with the prompts'
+    host clock), run three times: the first run captures the decode graphs, the second settles the
+    allocator's blocks (a prompt step that has to ask the driver for memory takes up to twice as long),
+    the third is timed.  Prints one JSON line with the prompts'
     tokens a second against the FLOP of the drawn lengths and the decoded tokens a second against the
     bytes a step has to read (every weight once, the cache of the live sequences at their mean length)."""
     import torch
@@ -267,7 +269,8 @@ def run_workload(args) -> int:
     session = Runtime(model, max_batch=n_prompts).new_session()
     make = lambda: [GenerateRequest(p, max_tokens=steps + 1, temperature=0.0, repetition_penalty=1.0, stop_ids=())
                     for p in prompts]
-    session.generate_batch(make())
+    for _ in range(2):  # the first run captures the decode graphs, the second settles the allocator's blocks
+        session.generate_batch(make())
     torch.cuda.synchronize()
     clocks = ClockSampler()
     clocks.start()
