@@ -50,6 +50,12 @@ __device__ __forceinline__ void dg_cluster_sync() {
 // multiple of 4 so that a thread can take four rows at once; the last block has the remainder.
 __host__ __device__ inline int dg_rows_per_block(int splits) { return ((DG_ROWS + splits - 1) / splits + 3) & ~3; }
 
+// x * sigmoid(x) for a result of type TO.  A bfloat16 result keeps 8 bits: the fast exponential and
+// division (2 ulp of 32-bit each) change none of them, and are a tenth of the instructions, which is
+// what an epilogue that runs once a block pays for (its code comes cold from the L2).
+template <typename TO> __device__ __forceinline__ float silu_for(float x) { return x / (1.0f + expf(-x)); }
+template <> __device__ __forceinline__ float silu_for<__nv_bfloat16>(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
 __device__ __forceinline__ void store_four(float* dst, const float (&v)[4]) {
   *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
 }
@@ -285,18 +291,19 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
               for (int j = 0; j < 16; ++j)
                 old[j] = c + j < shape.M ? __ldcg(reinterpret_cast<const float*>(out) + (size_t)(c + j) * shape.ldo + n) : 0.f;
             }
+            // sixteen values worked out side by side (rows beyond M too: their stores are left out), so
+            // that one element's exponential and division do not wait for the one before it
+            float val[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const int m = c + j;
-              if (m < shape.M) {
-                const float inv = scaled ? row_inv[m] : 1.f;
-                float val = __uint_as_float(v[j]) * inv;
-                if (MODE == 2) val = (val / (1.0f + expf(-val))) * (__uint_as_float(u[j]) * inv);
-                TO* dst = out + (size_t)m * shape.ldo + n;
-                if (MODE == 1) *dst = from_float<TO>(old[j] + val);
-                else *dst = from_float<TO>(val);
-              }
+              const float inv = scaled ? row_inv[c + j] : 1.f;
+              val[j] = __uint_as_float(v[j]) * inv;
+              if (MODE == 2) val[j] = silu_for<TO>(val[j]) * (__uint_as_float(u[j]) * inv);
+              if (MODE == 1) val[j] += old[j];
             }
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c + j < shape.M) out[(size_t)(c + j) * shape.ldo + n] = from_float<TO>(val[j]);
           }
         }
       } else if (shape.clustered) {
@@ -380,17 +387,17 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 for (int j = 0; j < 16; ++j)
                   old[j] = m0 + j < shape.M ? __ldcg(reinterpret_cast<const float*>(out) + (size_t)(m0 + j) * shape.ldo + n) : 0.f;
               }
+              float val[16];
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                if (m0 + j < shape.M) {
-                  const float inv = scaled ? row_inv[m0 + j] : 1.f;
-                  float val = sums[0][j] * inv;
-                  if (MODE == 2) val = (val / (1.0f + expf(-val))) * (sums[GROUPS - 1][j] * inv);
-                  TO* dst = out + (size_t)(m0 + j) * shape.ldo + n;
-                  if (MODE == 1) *dst = from_float<TO>(old[j] + val);
-                  else *dst = from_float<TO>(val);
-                }
+                const float inv = scaled ? row_inv[m0 + j] : 1.f;
+                val[j] = sums[0][j] * inv;
+                if (MODE == 2) val[j] = silu_for<TO>(val[j]) * (sums[GROUPS - 1][j] * inv);
+                if (MODE == 1) val[j] += old[j];
               }
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (m0 + j < shape.M) out[(size_t)(m0 + j) * shape.ldo + n] = from_float<TO>(val[j]);
             }
           }
         }
@@ -464,7 +471,7 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
               const float4 up = sums[u][GROUPS - 1];
               const float ups[4] = {up.x * inv, up.y * inv, up.z * inv, up.w * inv};
 #pragma unroll
-              for (int j = 0; j < 4; ++j) val[j] = (val[j] / (1.0f + expf(-val[j]))) * ups[j];
+              for (int j = 0; j < 4; ++j) val[j] = silu_for<TO>(val[j]) * ups[j];
             }
             if (MODE == 1) { val[0] += old[u].x; val[1] += old[u].y; val[2] += old[u].z; val[3] += old[u].w; }
             store_four(out + (size_t)m_of[u] * shape.ldo + n_of[u], val);
