@@ -68,6 +68,13 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * BLOCK_ROWS;
   const int n_slabs = (K + GS_SLAB - 1) / GS_SLAB;
+  // Every block starts its walk over K at another slab and wraps around: blocks that all run at once
+  // would else ask for the same columns of every weight row at the same time, addresses a whole row
+  // apart, which a few memory channels serve (measured alone, 8 rows: N 5,120 / K 8,192 29.8 -> 23.8 us,
+  // K 25,600 85.0 -> 71.8 us; N 4,096 / K 14,336 the same).  The start follows the weight row (by
+  // 64 rows, which every block size divides), so a row's sum has the same order whatever the batch.
+  const int first_slab = (int)(((unsigned)(row0 / 64) * 5u) % (unsigned)n_slabs);
+  auto slab_of = [&](int turn) { const int at = turn + first_slab; return at >= n_slabs ? at - n_slabs : at; };
 
   // where this thread's copies come from and go to (the same for every slab, shifted by the slab)
   const __nv_bfloat16* copy_src[COPIES];
@@ -82,7 +89,7 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
     copy_k[i] = j * 8;
   }
   auto issue = [&](int s) {
-    const int k0 = s * GS_SLAB;
+    const int k0 = slab_of(s) * GS_SLAB;
     const uint32_t stage = (uint32_t)((s % GS_STAGES) * STAGE_BYTES);
 #pragma unroll
     for (int i = 0; i < COPIES; ++i)  // K is a multiple of 8: a piece is wholly inside (16) or outside (zeros)
@@ -130,7 +137,7 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
   for (int s = 0; s < n_slabs; ++s) {
     uint4 xa[2][M_TILES], xb[2][M_TILES];
     auto load_x = [&](int h) {
-      const int k = s * GS_SLAB + warp * 64 + h * 32 + t * 8;
+      const int k = slab_of(s) * GS_SLAB + warp * 64 + h * 32 + t * 8;
       const bool inside = k < K;  // differs between lanes; only loads are conditional, every lane runs the MMAs
 #pragma unroll
       for (int mt = 0; mt < M_TILES; ++mt) {
@@ -237,12 +244,17 @@ int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, 
 
 // Three stages: 26 KB a block; registers allow four blocks a multiprocessor.  Rings of 4, 5 and 6
 // stages were measured: they help single shapes (the output matrix at one row reaches 6.7 TB/s with
-// 5) and lose on others; over a whole decode step of 8 sequences 3 stages is the fastest.
+// 5) and lose on others; over a whole decode step of 8 sequences 3 stages is the fastest, except for the
+// products that add into the residual stream, where 4 stages with the rotated walk are (alone, 8 rows:
+// K 4,096 9.2 -> 8.6 us, K 14,336 26.6 -> 26.1, N 5,120 / K 25,600 85.0 -> 68.4; whole steps 1 % faster).
 template <int M_TILES, int MODE, typename TO>
 int launch_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, long long up_offset,
                   const NormEmit& emit, const RowScale& scale, cudaStream_t stream) {
   // more than 32 batch rows: two row groups a block halve the X traffic per weight byte
   constexpr int RG = M_TILES >= 4 ? 2 : 1;
+  // products that add into the residual stream (long K, few blocks a multiprocessor): four stages
+  if (MODE == 1 && M_TILES == 1)
+    return launch_stream_staged<M_TILES, MODE, 4, RG, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, scale, stream);
   return launch_stream_staged<M_TILES, MODE, 3, RG, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, scale, stream);
 }
 
