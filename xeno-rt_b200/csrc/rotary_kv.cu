@@ -178,44 +178,61 @@ qk_rope_kv_write_128_kernel(
     const float4 a = cs[0], b = cs[1];
     c[0] = a.x; sn[0] = a.y; c[1] = a.z; sn[1] = a.w; c[2] = b.x; sn[2] = b.y; c[3] = b.z; sn[3] = b.w;
   }
-  for (int head_slot = warp; head_slot < n_slots; head_slot += 8) {
-    int kind, head;
-    if (head_slot < n_heads) { kind = 0; head = head_slot; }
-    else if (head_slot < n_heads + n_kv_heads) { kind = 1; head = head_slot - n_heads; }
-    else { kind = 2; head = head_slot - n_heads - n_kv_heads; }
-    float v[4];
-    if (slot < 0) {  // a padding row: q is zeroed, the cache is not touched
+  // A warp takes head slots warp, warp + 8, ...; it asks for the rows of up to four of them before it
+  // works on the first (the rows come from the L2, and one load in flight a warp left the kernel waiting).
+  constexpr int AHEAD = 4;
+  for (int first = warp; first < n_slots; first += 8 * AHEAD) {
+    float4 raw[AHEAD];
+    if (slot >= 0) {
+#pragma unroll
+      for (int a = 0; a < AHEAD; ++a) {
+        const int head_slot = first + 8 * a;
+        if (head_slot < n_slots) {
+          const int kind = head_slot < n_heads ? 0 : (head_slot < n_heads + n_kv_heads ? 1 : 2);
+          const int head = head_slot - (kind == 0 ? 0 : (kind == 1 ? n_heads : n_heads + n_kv_heads));
+          const float* src = qkv + (size_t)t * row_stride + (kind == 0 ? 0 : (kind == 1 ? k_offset : v_offset)) + head * HD;
+          raw[a] = *reinterpret_cast<const float4*>(src + 4 * lane);
+        }
+      }
+    }
+#pragma unroll
+    for (int a = 0; a < AHEAD; ++a) {
+      const int head_slot = first + 8 * a;
+      if (head_slot >= n_slots) break;
+      const int kind = head_slot < n_heads ? 0 : (head_slot < n_heads + n_kv_heads ? 1 : 2);
+      const int head = head_slot - (kind == 0 ? 0 : (kind == 1 ? n_heads : n_heads + n_kv_heads));
+      float v[4];
+      if (slot < 0) {  // a padding row: q is zeroed, the cache is not touched
+        if (kind == 0) {
+          v[0] = v[1] = v[2] = v[3] = 0.f;
+          store4_as(q_out + (size_t)t * n_heads * HD + head * HD + 4 * lane, v);
+        }
+        continue;
+      }
+      v[0] = raw[a].x; v[1] = raw[a].y; v[2] = raw[a].z; v[3] = raw[a].w;
+      const TN* norm_w = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+      if (norm_w != nullptr) {
+        float sq = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sq = fmaf(v[j], v[j], sq);
+        const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)HD + eps);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = (v[j] * inv) * (kind == 0 ? qn[j] : kn[j]);
+      }
+      if (kind != 2 && rope_half > 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+          // first half: x0 cos - x1 sin; second half: x0 sin + x1 cos, with x0 the first-half element
+          v[j] = lane < 16 ? v[j] * c[j] - other * sn[j] : other * sn[j] + v[j] * c[j];
+        }
+      }
       if (kind == 0) {
-        v[0] = v[1] = v[2] = v[3] = 0.f;
         store4_as(q_out + (size_t)t * n_heads * HD + head * HD + 4 * lane, v);
+      } else if (block >= 0) {  // the host reserves blocks before the step; otherwise nothing to write into
+        TC* pool = kind == 1 ? k_pool : v_pool;
+        store4_as(pool + (((size_t)block * n_kv_heads + head) * XRT_BLOCK_TOKENS + pos % XRT_BLOCK_TOKENS) * HD + 4 * lane, v);
       }
-      continue;
-    }
-    const float* src = qkv + (size_t)t * row_stride + (kind == 0 ? 0 : (kind == 1 ? k_offset : v_offset)) + head * HD;
-    const float4 raw = *reinterpret_cast<const float4*>(src + 4 * lane);
-    v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
-    const TN* norm_w = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
-    if (norm_w != nullptr) {
-      float sq = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) sq = fmaf(v[j], v[j], sq);
-      const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)HD + eps);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) v[j] = (v[j] * inv) * (kind == 0 ? qn[j] : kn[j]);
-    }
-    if (kind != 2 && rope_half > 0) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
-        // first half: x0 cos - x1 sin; second half: x0 sin + x1 cos, with x0 the first-half element
-        v[j] = lane < 16 ? v[j] * c[j] - other * sn[j] : other * sn[j] + v[j] * c[j];
-      }
-    }
-    if (kind == 0) {
-      store4_as(q_out + (size_t)t * n_heads * HD + head * HD + 4 * lane, v);
-    } else if (block >= 0) {  // the host reserves blocks before the step; otherwise nothing to write into
-      TC* pool = kind == 1 ? k_pool : v_pool;
-      store4_as(pool + (((size_t)block * n_kv_heads + head) * XRT_BLOCK_TOKENS + pos % XRT_BLOCK_TOKENS) * HD + 4 * lane, v);
     }
   }
 }
