@@ -544,45 +544,55 @@ static bool dg_make_map(CUtensorMap* map, const void* base, int rows, int cols, 
   return sm100::make_map_bf16_2d(map, base, rows, cols, ld, box_rows);
 }
 
+// The kernel's limit of dynamic shared memory only ever grows (setting it anew would lower it): one
+// record for each instance of the kernel.
+template <int MODE, typename TO>
+cudaError_t allow_shared_memory(int smem) {
+  static int allowed = 0;
+  if (smem <= allowed) return cudaSuccess;
+  const cudaError_t err = cudaFuncSetAttribute(gemm_decode_tcgen05_kernel<MODE, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (err == cudaSuccess) allowed = smem;
+  return err;
+}
+
 // How many clusters of 2 .. 8 blocks of this kernel (one block a multiprocessor) the device runs at
 // the same time: asked of the current device once; where there is none (host arithmetic only), or
 // it has another number of multiprocessors than asked about, nine tenths of them, which is what a
 // B200 answers within one cluster (148: 45 clusters of 3, 33 of 4, 26 of 5, 22 of 6).
-struct ClusterLimits { int held[9]; };
-static const ClusterLimits& cluster_limits(int sms) {
-  static ClusterLimits estimate, asked;
-  static int estimate_sms = 0, asked_sms = -1;
-  if (asked_sms == -1) {
-    asked_sms = 0;
-    int device = 0, count = 0;
-    if (cudaGetDevice(&device) == cudaSuccess &&
-        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess) {
-      auto kernel = gemm_decode_tcgen05_kernel<0, __nv_bfloat16>;
-      const int smem = 200 * 1024;
-      bool ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess;
-      for (int size = 2; ok && size <= 8; ++size) {
-        cudaLaunchConfig_t probe = {};
-        probe.gridDim = dim3(size, 1, 1);
-        probe.blockDim = dim3(DG_THREADS);
-        probe.dynamicSmemBytes = smem;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = size; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-        probe.attrs = attr;
-        probe.numAttrs = 1;
-        int clusters = 0;
-        ok = cudaOccupancyMaxActiveClusters(&clusters, kernel, &probe) == cudaSuccess;
-        asked.held[size] = clusters;
-      }
-      if (ok) asked_sms = count;
+struct ClusterLimits { int sms; int held[9]; };
+static ClusterLimits ask_cluster_limits() {
+  ClusterLimits asked = {};
+  int device = 0, count = 0;
+  if (cudaGetDevice(&device) == cudaSuccess &&
+      cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess) {
+    auto kernel = gemm_decode_tcgen05_kernel<0, __nv_bfloat16>;
+    const int smem = 200 * 1024;
+    bool ok = allow_shared_memory<0, __nv_bfloat16>(smem) == cudaSuccess;
+    for (int size = 2; ok && size <= 8; ++size) {
+      cudaLaunchConfig_t probe = {};
+      probe.gridDim = dim3(size, 1, 1);
+      probe.blockDim = dim3(DG_THREADS);
+      probe.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = size; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      probe.attrs = attr;
+      probe.numAttrs = 1;
+      int clusters = 0;
+      ok = cudaOccupancyMaxActiveClusters(&clusters, kernel, &probe) == cudaSuccess;
+      asked.held[size] = clusters;
     }
-    cudaGetLastError();  // no device, or a refusal: an answer, not an error of a stream
+    if (ok) asked.sms = count;
   }
-  if (sms == asked_sms) return asked;
-  if (sms != estimate_sms) {
-    for (int size = 2; size <= 8; ++size) estimate.held[size] = sms * 9 / 10 / size;
-    estimate_sms = sms;
-  }
+  cudaGetLastError();  // no device, or a refusal: an answer, not an error of a stream
+  return asked;
+}
+static ClusterLimits cluster_limits(int sms) {
+  static const ClusterLimits asked = ask_cluster_limits();  // once, whichever thread comes first
+  if (sms == asked.sms) return asked;
+  ClusterLimits estimate = {};
+  estimate.sms = sms;
+  for (int size = 2; size <= 8; ++size) estimate.held[size] = sms * 9 / 10 / size;
   return estimate;
 }
 
@@ -602,7 +612,7 @@ static int choose_splits(int tiles, int k_iters, int sms, int groups, int nb) {
   int best = 1;
   double best_cost = 0.0;
   const double weight_bytes = (double)groups * DG_ROWS * k_iters * DG_BK * 2;
-  const ClusterLimits& limits = cluster_limits(sms);
+  const ClusterLimits limits = cluster_limits(sms);
   const bool clusters = decode_gemm_clusters_wanted();
   for (int s = 1; s <= DG_MAX_SPLITS; ++s) {
     const int per = (k_iters + s - 1) / s;
@@ -622,17 +632,6 @@ static int choose_splits(int tiles, int k_iters, int sms, int groups, int nb) {
   return best;
 }
 
-
-// The kernel's limit of dynamic shared memory only ever grows (setting it anew would lower it): one
-// record for each instance of the kernel.
-template <int MODE, typename TO>
-cudaError_t allow_shared_memory(int smem) {
-  static int allowed = 0;
-  if (smem <= allowed) return cudaSuccess;
-  const cudaError_t err = cudaFuncSetAttribute(gemm_decode_tcgen05_kernel<MODE, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (err == cudaSuccess) allowed = smem;
-  return err;
-}
 
 // Whether the splits of a tile run as one cluster: all clusters of the launch must find room at the
 // same time (asked once for each cluster size and shared-memory size).
