@@ -17,10 +17,17 @@
 // streams 128 gate rows and the 128 matching up rows into two accumulators).
 //
 // Where all items of a launch run at once (tiles x splits is no more than the multiprocessors), the
-// splits of a tile are the blocks of one thread-block cluster instead: each leaves its partial sums in
-// its own shared memory, the cluster meets, and every block adds and finishes its share of the tile's
-// rows from all blocks' shared memory (distributed shared memory), again in split order: no scratch
-// in global memory, no fence, no counter.
+// splits of a tile are the blocks of one thread-block cluster instead, if the device holds so many
+// clusters of that size at once: each block sends its partial sums for a share of the tile's rows to the
+// block that finishes them (remote stores into shared memory that the ring never uses), the cluster
+// meets once, and every block adds and finishes its rows locally, again in split order: no scratch in
+// global memory, no fence, no counter.  Such a finish can also prepare the RMSNorm that follows a
+// product that adds into the residual stream (NormEmit), and every epilogue can finish a norm that the
+// product before prepared (RowScale).
+//
+// The weight is read once a step: its TMA loads carry an evict-first policy for the L2, so that what the
+// step reads again (activations, the residual, partial sums, code) stays there.  How many splits a product
+// gets, and whether they meet as a cluster, is decided from measured costs (choose_splits).
 //
 // Six warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues the MMAs, warps 2-5 read the
 // accumulators (tcgen05.ld, one TMEM lane quarter each) while the MMA warp fills the other
