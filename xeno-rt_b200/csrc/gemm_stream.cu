@@ -19,7 +19,10 @@
 // Measured on a B200 with M = 8: 5.97 TB/s on the output matrix (1.05 GB), 5.2 TB/s on gate/up.
 //
 // A product that adds into the residual stream can also prepare the RMSNorm that follows it (NormEmit,
-// common.cuh): here the parts of a row's sum of squares are one a block (its 8 or 16 weight rows).
+// common.cuh): here the parts of a row's sum of squares are one a block (its 8 or 16 weight rows); and
+// the kernel can finish a norm that the product before prepared (RowScale).  Those products keep four
+// stages.  Every 64 weight rows start their walk over K at another slab, and the weight is marked as
+// streaming in the L2 by the launch's access-policy window (it is read once a step).
 #include "common.cuh"
 
 namespace xrt {
