@@ -335,6 +335,7 @@ __device__ __forceinline__ uint32_t dec_map_rank(uint32_t local_smem, int rank) 
   asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem), "r"(rank));
   return remote;
 }
+constexpr int DEC_MAX_CLUSTER = 16;  // the most splits that merge as one cluster
 __device__ __forceinline__ float dec_ld_cluster(uint32_t addr) {
   float v;
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
@@ -651,14 +652,27 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const uint32_t ml_local = smem_addr(cta_ml), o_local = smem_addr(cta_o);
     for (int idx = split * per + threadIdx.x; idx < min(total, (split + 1) * per); idx += blockDim.x) {
       const int row = idx / head_dim;
+      // every block's (m, l, o) of this output asked for before the first is used: the remote loads are in
+      // flight together (one after the other they were most of a step's attention at one sequence)
+      float ms[DEC_MAX_CLUSTER], ls[DEC_MAX_CLUSTER], os[DEC_MAX_CLUSTER];
+#pragma unroll
+      for (int s2 = 0; s2 < DEC_MAX_CLUSTER; ++s2) {
+        ms[s2] = -INFINITY; ls[s2] = 0.f; os[s2] = 0.f;
+        if (s2 < n_splits) {
+          ms[s2] = dec_ld_cluster(dec_map_rank(ml_local + row * 8, s2));
+          ls[s2] = dec_ld_cluster(dec_map_rank(ml_local + row * 8 + 4, s2));
+          os[s2] = dec_ld_cluster(dec_map_rank(o_local + idx * 4, s2));
+        }
+      }
       float m = -INFINITY;
-      for (int s2 = 0; s2 < n_splits; ++s2) m = fmaxf(m, dec_ld_cluster(dec_map_rank(ml_local + row * 8, s2)));
+#pragma unroll
+      for (int s2 = 0; s2 < DEC_MAX_CLUSTER; ++s2) m = fmaxf(m, ms[s2]);
       float l = 0.f, o = 0.f;
-      for (int s2 = 0; s2 < n_splits; ++s2) {
-        const float ms = dec_ld_cluster(dec_map_rank(ml_local + row * 8, s2));
-        const float f = ms == -INFINITY ? 0.f : exp2f(ms - m);
-        l += f * dec_ld_cluster(dec_map_rank(ml_local + row * 8 + 4, s2));
-        o += f * dec_ld_cluster(dec_map_rank(o_local + idx * 4, s2));
+#pragma unroll
+      for (int s2 = 0; s2 < DEC_MAX_CLUSTER; ++s2) {  // in split order
+        const float f = ms[s2] == -INFINITY ? 0.f : exp2f(ms[s2] - m);
+        l += f * ls[s2];
+        o += f * os[s2];
       }
       out[((size_t)tok * n_heads + (size_t)kv_head * group) * head_dim + idx] = __float2bfloat16_rn(o / l);
     }
@@ -682,7 +696,6 @@ static bool dec_make_map(CUtensorMap* map, const void* base, long long rows, int
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-constexpr int DEC_MAX_CLUSTER = 16;
 
 // shared memory of the TMA kernel: the tiles (or the warps' states that reuse their room), then a
 // block's merged state for the cluster merge
