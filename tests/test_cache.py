@@ -2,6 +2,7 @@
 import random
 
 import pytest
+import torch
 
 import xeno_rt_b200  # noqa: F401
 from xeno_rt_b200.cache import BlockAllocator, Cache, KVNeed, SlotAllocator, StateNeed
@@ -233,3 +234,37 @@ def test_a_step_that_cannot_be_served_takes_nothing():
         c.close_slot(s)
     c.check()
     assert c.blocks_free() == 4
+
+
+def test_block_tables_reach_the_device_tensor_row_by_row():
+    """flush_tables brings the changed rows of the host's block tables into the device tensor (here a
+    CPU tensor) and nothing else; sequences of unequal lengths change some row at nearly every step."""
+    c = _cache(max_tokens=64 * 8, needs=[KVNeed(2, 16)])
+    a, b = c.open_slot(), c.open_slot()
+    c.reserve_all([a, b], [70, 5])
+    c.flush_tables()
+    table = c.store(0).block_table
+    assert (table[a, :2] >= 0).all() and table[a, 2] == -1 and table[b, 0] >= 0 and table[b, 1] == -1
+    c.advance(a, 70)
+    c.advance(b, 5)
+    before = table.clone()
+    c.reserve_all([a, b], [1, 60])   # b crosses into its second block, a stays in its second
+    c.flush_tables()
+    assert (table[a] == before[a]).all() and table[b, 1] >= 0 and (table[b, 0] == before[b, 0])
+    c.check()
+
+
+def test_pinned_buffers_are_used_in_turn_and_grow():
+    """The ring of host buffers behind every small copy to the device: a buffer comes back only after
+    the others, and a larger request gets a larger buffer (on the CPU nothing is pinned or waited for)."""
+    from xeno_rt_b200.core.staging import PinnedRing
+    ring = PinnedRing("cpu", count=3)
+    turns = []
+    for n in (10, 20, 5000, 7):
+        turn, buf = ring.take(n)
+        assert buf.numel() == n and buf.dtype == torch.int32
+        buf.fill_(n)
+        ring.copied(turn)
+        turns.append(turn)
+    assert turns == [0, 1, 2, 0]
+    assert ring.buffers[2].numel() >= 5000 and ring.buffers[0].numel() >= 1024
