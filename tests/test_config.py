@@ -127,7 +127,7 @@ def test_which_kernel_takes_a_decode_product_of_few_rows():
     """The choice between the two weight-streaming kernels is host arithmetic over the product's sizes
     (here for a device of 148 multiprocessors): the tcgen05 kernel where its tiles of 128 weight rows,
     times its splits of K, fill the multiprocessors; the cp.async kernel else, and for products that add
-    into the residual stream unless K is long (16,384; 8,192 with more than 8 rows)."""
+    into the residual stream up to 8 rows, and beyond below K = 8,192, unless its own rounds of blocks fill badly."""
     from xeno_rt_b200.core import KernelError
     from xeno_rt_b200.csrc import ops
     from xeno_rt_b200.parts.linear_bf16 import tcgen05_for_few_rows as choice
@@ -146,8 +146,8 @@ def test_which_kernel_takes_a_decode_product_of_few_rows():
         # width 5,120, inner 25,600, 64 + 2 x 8 heads of 128
         assert not choice(sms, rows, 10240, 5120, "store")     # 80 items: 0.54 full
         assert not choice(sms, rows, 25600, 5120, "swiglu")    # 200 tiles: two rounds, 0.68 full
-        assert choice(sms, rows, 5120, 25600, "accumulate")    # long K
-        assert choice(sms, rows, 5120, 8192, "accumulate")     # 640 blocks of the cp.async kernel: two rounds, 0.54 full
+        assert choice(sms, rows, 5120, 25600, "accumulate") == (rows > 8)
+        assert choice(sms, rows, 5120, 8192, "accumulate") == (rows > 8)  # 320 blocks of 16 rows: one round
 
 
 def test_decode_attention_splits_cover_the_context_and_fill_the_rounds():

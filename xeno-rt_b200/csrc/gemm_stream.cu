@@ -250,14 +250,41 @@ int launch_stream_staged(void* out, const void* x, const void* w, int M, int N, 
 // 5) and lose on others; over a whole decode step of 8 sequences 3 stages is the fastest, except for the
 // products that add into the residual stream, where 4 stages with the rotated walk are (alone, 8 rows:
 // K 4,096 9.2 -> 8.6 us, K 14,336 26.6 -> 26.1, N 5,120 / K 25,600 85.0 -> 68.4; whole steps 1 % faster).
+// Multiprocessors of the current device (148 where there is none to ask: host arithmetic only).
+inline int stream_sm_count() {
+  static const int count = [] {
+    int device = 0, value = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || value <= 0)
+      value = 148;
+    cudaGetLastError();
+    return value;
+  }();
+  return count;
+}
+
+// Groups of 8 weight rows a block for a product of up to 16 rows that adds into the residual stream: one,
+// unless its blocks would then not all run at once (four a multiprocessor) and blocks of two groups would
+// (three a multiprocessor with their four stages).  640 blocks on 592 places are two rounds, the second
+// nearly empty; measured alone at 8 rows, N 5,120: K 8,192 23.4 -> 16.6 us, K 25,600 68.9 -> 48.4 us
+// (N 4,096, whose 512 blocks fit, loses with two groups: 26.2 -> 27.1 us at K 14,336).
+inline int stream_row_groups_accumulate(int N) {
+  const int sms = stream_sm_count();
+  if ((N + GS_ROWS - 1) / GS_ROWS <= sms * 4) return 1;
+  return (N + 2 * GS_ROWS - 1) / (2 * GS_ROWS) <= sms * 3 ? 2 : 1;
+}
+
 template <int M_TILES, int MODE, typename TO>
 int launch_stream(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, long long up_offset,
                   const NormEmit& emit, const RowScale& scale, cudaStream_t stream) {
   // more than 32 batch rows: two row groups a block halve the X traffic per weight byte
   constexpr int RG = M_TILES >= 4 ? 2 : 1;
   // products that add into the residual stream (long K, few blocks a multiprocessor): four stages
-  if (MODE == 1 && M_TILES == 1)
+  if (MODE == 1 && M_TILES == 1) {
+    if (stream_row_groups_accumulate(N) == 2)
+      return launch_stream_staged<M_TILES, MODE, 4, 2, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, scale, stream);
     return launch_stream_staged<M_TILES, MODE, 4, RG, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, scale, stream);
+  }
   return launch_stream_staged<M_TILES, MODE, 3, RG, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, scale, stream);
 }
 
@@ -280,7 +307,8 @@ int dispatch_stream(void* out, const void* x, const void* w, int M, int N, int K
 // How many floats a batch row `squares` holds one of: the blocks of the launch (M at most 16).
 XRT_EXPORT int xrt_gemm_stream_norm_blocks(int M, int N) {
   if (M <= 0 || N <= 0 || M > 16) return XRT_ERR_UNSUPPORTED;
-  return (N + xrt::GS_ROWS - 1) / xrt::GS_ROWS;
+  const int rows = xrt::GS_ROWS * xrt::stream_row_groups_accumulate(N);
+  return (N + rows - 1) / rows;
 }
 
 // x: bfloat16 [M, K] with row stride ldx (a multiple of 8); w: bfloat16 [N, K] contiguous, K a

@@ -22,16 +22,20 @@ def aligned(x, weight) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and weight.is_contiguous())
 
 
-ACCUMULATE_MIN_K = 16384       # from here on a product that adds into the residual stream may take the tcgen05 kernel
-ACCUMULATE_MIN_K_9_ROWS = 8192  # and from here on with 9 to 16 rows
+ACCUMULATE_MIN_K_9_ROWS = 8192  # a product of 9 to 16 rows that adds into the residual stream takes the tcgen05 kernel from here on
 STREAM_BLOCKS_PER_SM = 4        # blocks of the cp.async kernel that a multiprocessor holds at once (registers)
 
 
-def stream_kernel_waves(sms: int, n: int) -> float:
+def stream_kernel_waves(sms: int, n: int, accumulate: bool = False) -> float:
     """How full the cp.async kernel's rounds of blocks are for ``n`` weight rows (8 rows a block): 1 when all
     blocks run at once, else rounds / whole rounds.  640 blocks on 592 places are two rounds, the second
-    nearly empty: such a product runs at half its rate (measured: 84 MB in 33 microseconds)."""
-    waves = -(-n // 8) / (sms * STREAM_BLOCKS_PER_SM)
+    nearly empty: such a product runs at half its rate (measured: 84 MB in 33 microseconds).  A product
+    that adds into the residual stream takes 16 rows a block where that makes one round of it (three
+    such blocks a multiprocessor), as ``csrc/gemm_stream.cu:stream_row_groups_accumulate`` decides."""
+    blocks = -(-n // 8)
+    if accumulate and blocks > sms * STREAM_BLOCKS_PER_SM and -(-n // 16) <= sms * 3:
+        return 1.0
+    waves = blocks / (sms * STREAM_BLOCKS_PER_SM)
     return 1.0 if waves <= 1.0 else waves / -(-waves // 1)
 
 
@@ -39,18 +43,15 @@ def tcgen05_for_few_rows(sms: int, rows: int, n: int, k: int, mode: str) -> bool
     """Up to 16 rows both decode kernels take the product.  The tcgen05 kernel runs its items one a
     multiprocessor in rounds: it wins where they fill the rounds (one round at least 0.6 full, or
     several at least 0.85 full).  Products that add into the residual stream stay on the cp.async
-    kernel unless K is long (it slows down with K: 2.6 TB/s at K = 25,600, where the tcgen05 kernel
-    reaches 4 TB/s) and, below K = 16,384, the rows are more than 8 (its time grows with the rows, the
-    tcgen05 kernel's does not), or unless the cp.async kernel's own rounds of blocks are badly filled.
-    Measured, whole steps at a width of 4,096 and an inner size of 14,336, the down product on the
-    tcgen05 kernel against the cp.async kernel: 1 sequence 3.50 against 3.39 ms, 8 sequences 4.04
-    against 4.04, 16 sequences 4.80 against 4.94; and the output product too (K = 4,096): 3.68, 4.17
-    and 4.86 ms.  At a width of 5,120 and an inner size of 25,600, 8 sequences: 15.8 against 18.0 ms
-    with the long-K rule."""
+    kernel up to 8 rows, and from 9 rows on below K = 8,192 (its time grows with the rows, the tcgen05
+    kernel's does not), unless its own rounds of blocks are badly filled.  Measured alone and back to
+    back, cp.async against tcgen05 in microseconds at 1 / 8 / 16 rows: N 4,096, K 4,096: 7.6 / 8.6 / 10.3
+    against 11.5; K 14,336: 22.7 / 26.1 / 29.2 against 26.4; N 5,120, K 8,192: 15.0 / 16.6 / 21.4 against
+    21.2; K 25,600: 44.7 / 48.4 / 66.7 against 55.0."""
     rounds, fill = ops.gemm_decode_tcgen05_fill(sms, rows, n, k, mode)
     fills = fill >= 0.6 and (rounds == 1 or fill >= 0.85)
-    if mode == "accumulate" and k < (ACCUMULATE_MIN_K if rows <= 8 else ACCUMULATE_MIN_K_9_ROWS):
-        return fills and fill > stream_kernel_waves(sms, n) + 0.2
+    if mode == "accumulate" and (rows <= 8 or k < ACCUMULATE_MIN_K_9_ROWS):
+        return fills and fill > stream_kernel_waves(sms, n, accumulate=True) + 0.2
     return fills
 
 
