@@ -720,14 +720,20 @@ XRT_EXPORT long long xrt_gemm_decode_tcgen05_scratch(int M, int N, int K, int mo
   return (long long)tiles * splits * (mode == 2 ? 2 : 1) * nb * xrt::DG_ROWS;
 }
 
-// What the launcher would do with this product: tiles[0] = tiles of 128 weight rows, tiles[1] = splits of K.
-// The caller that has another kernel for few rows uses it to see how evenly the items fill the device.
-XRT_EXPORT int xrt_gemm_decode_tcgen05_plan(int M, int N, int K, int mode, int sm_count, int* tiles_and_splits) {
-  if (M <= 0 || N <= 0 || K <= 0 || sm_count <= 0 || tiles_and_splits == nullptr) return XRT_ERR_ARGUMENT;
+// What the launcher would do with this product: plan[0] = tiles of 128 weight rows, plan[1] = splits of K,
+// plan[2] = 1 if the splits of a tile would meet as a cluster (by the device's limits where there is a
+// device, by their estimate else), 0 if through scratch and the merging block or if K is not split.
+// The caller that has another kernel for few rows uses it to decide between the two.
+XRT_EXPORT int xrt_gemm_decode_tcgen05_plan(int M, int N, int K, int mode, int sm_count, int* plan) {
+  if (M <= 0 || N <= 0 || K <= 0 || sm_count <= 0 || plan == nullptr) return XRT_ERR_ARGUMENT;
   const int tiles = (N + xrt::DG_ROWS - 1) / xrt::DG_ROWS;
   const int k_iters = (K + xrt::DG_BK - 1) / xrt::DG_BK;
-  tiles_and_splits[0] = tiles;
-  tiles_and_splits[1] = xrt::choose_splits(tiles, k_iters, sm_count, mode == 2 ? 2 : 1, (M + 15) / 16 * 16);
+  const int splits = xrt::choose_splits(tiles, k_iters, sm_count, mode == 2 ? 2 : 1, (M + 15) / 16 * 16);
+  plan[0] = tiles;
+  plan[1] = splits;
+  plan[2] = splits > 1 && splits <= 8 && xrt::decode_gemm_clusters_wanted() && (long long)tiles * splits <= sm_count &&
+                    tiles <= xrt::cluster_limits(sm_count).held[splits]
+                ? 1 : 0;
   return XRT_OK;
 }
 

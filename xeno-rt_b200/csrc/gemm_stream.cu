@@ -111,12 +111,32 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
   // row's sum of squares): warp w adds the parts of rows w, w + 8, ... in a fixed order; the factors
   // 1 / sqrt(mean square + eps) multiply the finished sums below
   __shared__ float row_inv[M_TILES * 16];
+  __shared__ float inv_shares[GS_THREADS];
   if (MODE != 1 && scale.squares != nullptr) {
-    for (int m = warp; m < M; m += GS_WARPS) {
+    if (GS_THREADS % M == 0) {
+      // the parts lie [part][row]: thread t adds elements t, t + 256, ... (whole 128-byte lines a warp), all of
+      // one row since 256 is a multiple of M; then the row's 256 / M shares are added in thread order
+      const int total = scale.parts * M;
       float sum = 0.f;
-      for (int p = lane; p < scale.parts; p += 32) sum += __ldcg(scale.squares + (size_t)p * M + m);
-      sum = warp_sum(sum);
-      if (lane == 0) row_inv[m] = rsqrtf(sum / (float)scale.width + scale.eps);
+#pragma unroll 4
+      for (int e = threadIdx.x; e < total; e += GS_THREADS) sum += __ldcg(scale.squares + e);
+      // lanes of a warp that meet the same row (every M-th) add up by a fixed tree, then the warps in order
+      for (int o = 16; o >= M; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      inv_shares[threadIdx.x] = sum;
+      __syncthreads();
+      if (threadIdx.x < M) {
+        const int step = M > 32 ? M : 32;
+        float row = 0.f;
+        for (int j = threadIdx.x; j < GS_THREADS; j += step) row += inv_shares[j];
+        row_inv[threadIdx.x] = rsqrtf(row / (float)scale.width + scale.eps);
+      }
+    } else {
+      for (int m = warp; m < M; m += GS_WARPS) {
+        float sum = 0.f;
+        for (int p = lane; p < scale.parts; p += 32) sum += __ldcg(scale.squares + (size_t)p * M + m);
+        sum = warp_sum(sum);
+        if (lane == 0) row_inv[m] = rsqrtf(sum / (float)scale.width + scale.eps);
+      }
     }
   }
   const __nv_bfloat16* xlo[M_TILES];
@@ -285,6 +305,11 @@ int launch_stream(void* out, const void* x, const void* w, int M, int N, int K, 
       return launch_stream_staged<M_TILES, MODE, 4, 2, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, scale, stream);
     return launch_stream_staged<M_TILES, MODE, 4, RG, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, scale, stream);
   }
+  // a product of up to 16 rows whose blocks of 8 weight rows would not all run at once: 16 rows a block
+  // (alone at 8 rows, N 6,144 / K 4,096: 12.9 -> 8.9 us; N 10,240 / K 5,120: 23.0 -> 20.9; N 8,192 / K 8,192:
+  // 31.2 -> 28.1; three groups the same, four groups with two stages slower but for the last)
+  if (MODE == 0 && M_TILES == 1 && (N + GS_ROWS - 1) / GS_ROWS > stream_sm_count() * 4)
+    return launch_stream_staged<M_TILES, MODE, 3, 2, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, scale, stream);
   return launch_stream_staged<M_TILES, MODE, 3, RG, TO>(out, x, w, M, N, K, ldx, ldo, up_offset, emit, scale, stream);
 }
 

@@ -373,14 +373,22 @@ def gemm_decode_tcgen05_fill(sms: int, m: int, n: int, k: int, mode: str):
     """(rounds, share of the multiprocessor-rounds that do work) of ``gemm_decode_tcgen05`` on this
     product on a device of ``sms`` multiprocessors: its items (tiles of 128 weight rows x splits of
     K) run in rounds of one a multiprocessor.  Host arithmetic only: no device is needed."""
-    key = (sms, (m + 15) // 16, n, k, mode)
+    return gemm_decode_tcgen05_plan(sms, m, n, k, mode)[:2]
+
+
+def gemm_decode_tcgen05_plan(sms: int, m: int, n: int, k: int, mode: str):
+    """(rounds, fill, kind of reduction) of ``gemm_decode_tcgen05`` on this product: the kind is "none" (K is not
+    split), "cluster" (the splits of a tile meet as a thread-block cluster) or "scratch" (partial sums in
+    global memory, merged by the block that brings a tile's last split)."""
+    key = (sms, (m + 15) // 16, n, k, mode, tuning().decode_gemm_clusters)
     if key not in _decode_plans:
-        plan = (ctypes.c_int * 2)()
+        plan = (ctypes.c_int * 3)()
         _check(library().xrt_gemm_decode_tcgen05_plan(m, n, k, {"store": 0, "accumulate": 1, "swiglu": 2}[mode], sms, plan),
                "gemm_decode_tcgen05_plan")
         items = plan[0] * plan[1]
         rounds = -(-items // sms)
-        _decode_plans[key] = (rounds, items / (rounds * sms))
+        kind = "none" if plan[1] == 1 else ("cluster" if plan[2] else "scratch")
+        _decode_plans[key] = (rounds, items / (rounds * sms), kind)
     return _decode_plans[key]
 
 

@@ -48,10 +48,16 @@ def tcgen05_for_few_rows(sms: int, rows: int, n: int, k: int, mode: str) -> bool
     back, cp.async against tcgen05 in microseconds at 1 / 8 / 16 rows: N 4,096, K 4,096: 7.6 / 8.6 / 10.3
     against 11.5; K 14,336: 22.7 / 26.1 / 29.2 against 26.4; N 5,120, K 8,192: 15.0 / 16.6 / 21.4 against
     21.2; K 25,600: 44.7 / 48.4 / 66.7 against 55.0."""
-    rounds, fill = ops.gemm_decode_tcgen05_fill(sms, rows, n, k, mode)
+    rounds, fill, reduction = ops.gemm_decode_tcgen05_plan(sms, rows, n, k, mode)
     fills = fill >= 0.6 and (rounds == 1 or fill >= 0.85)
     if mode == "accumulate" and (rows <= 8 or k < ACCUMULATE_MIN_K_9_ROWS):
         return fills and fill > stream_kernel_waves(sms, n, accumulate=True) + 0.2
+    if mode == "store" and reduction == "scratch":
+        # splits that the device does not hold as clusters end in one block that merges a tile: the cp.async
+        # kernel with 16 weight rows a block is faster then (N 6,144, K 4,096, alone at 1 / 8 / 16 rows: 8.4 /
+        # 8.9 / 9.7 against 14.4 us; whole steps of 1 / 8 / 16 sequences 3.27 -> 3.12, 3.90 -> 3.78, 4.77 -> 4.69
+        # ms, with the norm before it run by the norm kernel again)
+        return False
     return fills
 
 
@@ -78,17 +84,17 @@ def _product(out, x, weight, mode: str, up_rows: int = 0) -> None:
 
 def takes_pending(rows: int, n: int, k: int, mode: str, device) -> bool:
     """Whether the product before one of these sizes should prepare its input's norm instead of a norm
-    kernel: where the tcgen05 kernels take the product.  The cp.async kernel can finish a pending norm
-    too, but every one of its many short-lived blocks then adds up the parts of the rows' sums of
-    squares before its first product: at a width of 5,120 and an inner size of 25,600 a step of 8
-    sequences took 14.93 ms that way against 14.68 ms with the two norm kernels a layer
-    (``ops.Tuning.pending_norm`` = "force" chooses it all the same)."""
+    kernel: where the tcgen05 kernels take the product, and where the cp.async kernel takes a plain
+    ("store") product (whole steps at a width of 4,096 with q/k/v on it: 1 / 2 / 4 / 8 sequences 3.11 -> 3.09,
+    3.20 -> 3.17, 3.43 -> 3.40, 3.79 -> 3.77 ms).  Its SwiGLU product has thousands of short-lived blocks that
+    would each add up the parts of the rows' sums of squares before their first product: there the norm
+    kernel stays (``ops.Tuning.pending_norm`` = "force" chooses the product all the same)."""
     wish = ops.tuning().pending_norm
     if k % 8 or wish == "off":
         return False
     if rows > ops.DECODE_TCGEN05_MAX_ROWS or wish == "force":
         return True
-    return _decode_kernel(rows, n, k, mode, device) == "tcgen05"
+    return _decode_kernel(rows, n, k, mode, device) == "tcgen05" or mode == "store"
 
 
 def run_pending(out, pending, weight, up_rows: int = 0) -> None:
