@@ -367,7 +367,7 @@ def run_timed(args, model, cfg, shape_name, full_layers, n_layers, pk, setup_s) 
     for b in (1, 64):
         r = time_decode(model, b, args.context, max(8, args.steps // 2), args.warmup)
         points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
-    prefill_ms = time_prefill(model, PREFILL_TOKENS, iters=5, warmup=max(3, args.warmup // 2))
+    prefill_ms = time_prefill(model, PREFILL_TOKENS, iters=9, warmup=max(3, args.warmup // 2))
     flops = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
     e2e = time_e2e(model, args.batch, args.context, args.steps)
 
