@@ -246,7 +246,7 @@ def test_fill_normal_matches_the_host_generator(dtype):
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 16, 17, 40, 64])
-@pytest.mark.parametrize("n,k", [(203, 104), (64, 4096), (136, 96), (8, 40), (24, 1544)])
+@pytest.mark.parametrize("n,k", [(203, 104), (64, 4096), (136, 96), (8, 40), (24, 1544), (5000, 264), (4744, 1032)])
 def test_gemm_stream(m, n, k):
     x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
@@ -617,9 +617,10 @@ def test_attention_prefill_tcgen05_kernel(nh, nkv):
 
 @pytest.mark.parametrize("m", [1, 3, 8, 16])
 @pytest.mark.parametrize("width,inner,out_rows,norm_dtype", [(1032, 2760, 1536, torch.float32), (256, 520, 392, torch.bfloat16),
-                                                            (4096, 1024, 4096, torch.bfloat16)])
+                                                            (4096, 1024, 4096, torch.bfloat16), (5120, 264, 5000, torch.float32)])
 def test_a_product_prepares_the_norm_that_follows_and_the_next_product_finishes_it(m, width, inner, out_rows, norm_dtype):
-    """residual += act . down^T by the cp.async kernel, which also leaves residual * norm weight in
+    """(The widest case has more weight rows than the kernel's blocks of 8 rows can all run at once: blocks of 16.)
+    residual += act . down^T by the cp.async kernel, which also leaves residual * norm weight in
     bfloat16 and every row's partial sums of squares; then the tcgen05 few-row product of that with
     another matrix, which multiplies row m by 1 / sqrt(mean square + eps).  Against the plain
     functions (norm, then product), store and SwiGLU, and the residual against the plain sum."""
