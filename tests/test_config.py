@@ -175,6 +175,17 @@ def test_decode_attention_splits_cover_the_context_and_fill_the_rounds():
         for mean in (1, 300, 1024, 5000):
             chunk, splits = decode_split(n_seqs, 8, 4096, 148, mean)
             assert chunk % 64 == 0 and chunk * splits >= 4096 and chunk * (splits - 1) < 4096
+    # a windowed layer: the kernels count its splits from the cache block of the first visible key, so the keys to
+    # cut are the window and what is left of that block, however long the sequence is
+    from xeno_rt_b200.parts.attention_bf16 import visible_span
+    assert visible_span(4096, 0) == 4096 and visible_span(40, 100) == 40
+    for window in (1, 2, 63, 64, 65, 100, 128, 1000):
+        span = visible_span(1 << 20, window)
+        assert span % 64 == 0
+        for length in range(1, 400):  # the newest key is length - 1; the first visible one max(0, length - window)
+            first_block_key = max(0, length - window) // 64 * 64
+            assert length - first_block_key <= span
+        assert span - 64 < window + 63  # and not a block more than the worst case needs
 
 
 def test_the_merging_block_of_decode_attention_is_never_given_more_splits_than_its_shared_memory_holds():

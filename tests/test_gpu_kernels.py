@@ -436,6 +436,40 @@ def test_attention_decode_finds_a_far_key_and_respects_the_window():
         assert torch.allclose(out.float(), ref.float(), atol=3e-2)
 
 
+@pytest.mark.parametrize("hd", [128, 80])
+def test_attention_decode_window_splits_start_at_the_window(hd):
+    """A windowed layer's splits are counted from the cache block of its first visible key, so three splits
+    of 64 keys cover a window of 150 keys at the end of 1,500 (keys 1,350 .. 1,499, from block key 1,344).
+    The window's first key is made to stand out; one key less in the window and it is gone."""
+    nh, nkv, S, window = 8, 2, 1500, 150
+    torch.manual_seed(hd)
+    k_pool, v_pool, table = _cache_for([S, 40], nkv, hd, torch.bfloat16, shuffle_seed=3)
+    k = torch.randn(S, nkv, hd, device=DEV) * 0.1
+    v = torch.randn(S, nkv, hd, device=DEV)
+    q = torch.randn(2, nh, hd, device=DEV) * 0.1
+    first = S - window
+    k[first, 1] = q[0, 6] * 400  # head 6 reads kv head 1
+    _fill_cache(k_pool, v_pool, table, 1, k, v)
+    _fill_cache(k_pool, v_pool, table, 2, k[:40].contiguous(), v[:40].contiguous())  # shorter than the window
+    qf = q.reshape(2, nh * hd).to(torch.bfloat16)
+    tok_pos = torch.tensor([S - 1, 39], dtype=torch.int32, device=DEV)
+    tok_slot = torch.tensor([1, 2], dtype=torch.int32, device=DEV)
+    target = v[first, 1].to(torch.bfloat16).float()
+    ref = torch.empty_like(qf)
+    ops().attention_reference(ref, qf, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd), window=window)
+    assert torch.allclose(ref.float().reshape(2, nh, hd)[0, 6], target, atol=3e-2)
+    for chunk, n_splits in ((64, 3), (128, 2), (256, 1)):
+        for fused in (False, True):
+            for clusters in (False, True):
+                out = torch.full_like(qf, 7.0)
+                ops().attention_decode(out, qf, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd),
+                                       window, chunk, n_splits, fused=fused, clusters=clusters)
+                assert torch.allclose(out.float(), ref.float(), atol=3e-2), (chunk, fused, clusters)
+                ops().attention_decode(out, qf, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd),
+                                       window - 1, chunk, n_splits, fused=fused, clusters=clusters)
+                assert not torch.allclose(out.float().reshape(2, nh, hd)[0, 6], target, atol=0.2)
+
+
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (5, 1, 48), (8, 2, 128), (6, 3, 80), (2, 1, 256)])
 def test_attention_prefill_kernel(nh, nkv, hd):
     """Four sequences end to end: a whole prompt of 150 tokens, one of a single token, one that

@@ -4,7 +4,8 @@
 // softmax over the cached positions, parallel over kv heads with the group's query heads inside.)
 //
 // Grid (splits, kv heads, tokens).  A block of four warps serves one kv head of one token for the
-// keys [split * chunk, (split + 1) * chunk): the group's query heads (up to 16) are the rows of the
+// keys [split * chunk, (split + 1) * chunk), counted from the cache block of the token's first visible key
+// (position 0 without a window): the group's query heads (up to 16) are the rows of the
 // MMA, so the group shares every key and value that is read.  Tiles of 64 keys (one cache block,
 // contiguous in memory) are copied to shared memory with cp.async, double-buffered; warp w takes
 // keys 16w .. 16w+16 of each tile with its own online-softmax state; the four states are merged
@@ -19,6 +20,19 @@
 namespace xrt {
 
 constexpr int DEC_WARPS = 4;
+
+// Keys of split s of a token that sees the keys [first_key, len): splits are counted from the cache block
+// that holds the first visible key (position 0 without a window), `chunk` keys each, so that a windowed
+// layer's splits all hold keys however long the sequence is.  The kernels and both combine steps share this.
+__device__ __forceinline__ int split_begin(int split, int chunk, int first_key) {
+  return (first_key / XRT_BLOCK_TOKENS) * XRT_BLOCK_TOKENS + split * chunk;
+}
+__device__ __forceinline__ int split_end(int split, int chunk, int first_key, int len) {
+  return min(split_begin(split, chunk, first_key) + chunk, len);
+}
+__device__ __forceinline__ bool split_live(int split, int chunk, int first_key, int len) {
+  return split_begin(split, chunk, first_key) < len;
+}
 
 // What every form of the kernel does once its four warps have left their running state in the merge
 // area [warps][16 rows] of shared memory: merge them in warp order, write the output (one split) or
@@ -62,10 +76,9 @@ __device__ __forceinline__ void decode_finish(unsigned char* smem, __nv_bfloat16
   __shared__ int is_last;
   __threadfence();
   __syncthreads();
-  const int first_block_key = (first_key / XRT_BLOCK_TOKENS) * XRT_BLOCK_TOKENS;
   if (threadIdx.x == 0) {
     int n_live = 0;
-    for (int s = 0; s < n_splits; ++s) n_live += max(s * chunk, first_block_key) < min((s + 1) * chunk, len);
+    for (int s = 0; s < n_splits; ++s) n_live += split_live(s, chunk, first_key, len);
     int* counter = counters + tok * n_kv_heads + kv_head;
     const int before = atomicAdd(counter, 1);
     is_last = before == n_live - 1;
@@ -79,7 +92,7 @@ __device__ __forceinline__ void decode_finish(unsigned char* smem, __nv_bfloat16
   float* row_l = all_l + group * n_splits;            // [group]
   for (int i = threadIdx.x; i < group * n_splits; i += blockDim.x) {
     const int row = i / n_splits, s = i - row * n_splits;
-    const bool live = max(s * chunk, first_block_key) < min((s + 1) * chunk, len);
+    const bool live = split_live(s, chunk, first_key, len);
     const size_t p = ((size_t)tok * n_heads + kv_head * group + row) * n_splits + s;
     all_m[i] = live ? __ldcg(part_ml + p * 2) : -INFINITY;
     all_l[i] = live ? __ldcg(part_ml + p * 2 + 1) : 0.f;
@@ -142,8 +155,8 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   const int pos = tok_pos[tok];
   const int len = pos + 1;
   const int first_key = window > 0 ? max(0, len - window) : 0;
-  const int begin = max(split * chunk, (first_key / XRT_BLOCK_TOKENS) * XRT_BLOCK_TOKENS);
-  const int end = min((split + 1) * chunk, len);
+  const int begin = split_begin(split, chunk, first_key);
+  const int end = split_end(split, chunk, first_key, len);
   if (begin >= end) return;  // this split holds no visible key: the combine step skips it too
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -282,11 +295,10 @@ __global__ void attention_combine_kernel(__nv_bfloat16* __restrict__ out, const 
   }
   const int len = tok_pos[tok] + 1;
   const int first_key = window > 0 ? max(0, len - window) : 0;
-  const int first_block_key = (first_key / XRT_BLOCK_TOKENS) * XRT_BLOCK_TOKENS;
   const size_t base = (size_t)warp_global * n_splits;
   float m = -INFINITY;
   for (int s = 0; s < n_splits; ++s) {
-    const bool live = max(s * chunk, first_block_key) < min((s + 1) * chunk, len);
+    const bool live = split_live(s, chunk, first_key, len);
     if (live) m = fmaxf(m, part_ml[(base + s) * 2]);
   }
   float l = 0.f;
@@ -297,7 +309,7 @@ __global__ void attention_combine_kernel(__nv_bfloat16* __restrict__ out, const 
   // in flight at once (a dead split's partials are never read: they may hold anything)
 #pragma unroll 4
   for (int s = 0; s < n_splits; ++s) {
-    const bool live = max(s * chunk, first_block_key) < min((s + 1) * chunk, len);
+    const bool live = split_live(s, chunk, first_key, len);
     const float ms = live ? part_ml[(base + s) * 2] : -INFINITY;
     const float ls = live ? part_ml[(base + s) * 2 + 1] : 0.f;
     const float f = ms == -INFINITY ? 0.f : exp2f(ms - m);
@@ -404,8 +416,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   }
   const int len = tok_pos[tok] + 1;
   const int first_key = window > 0 ? max(0, len - window) : 0;
-  const int begin = max(split * chunk, (first_key / XRT_BLOCK_TOKENS) * XRT_BLOCK_TOKENS);
-  const int end = min((split + 1) * chunk, len);
+  const int begin = split_begin(split, chunk, first_key);
+  const int end = split_end(split, chunk, first_key, len);
   const bool has_keys = begin < end;
   if (!has_keys && !clustered) { pdl_wait(); return; }  // this split holds no visible key: the combine step skips it too
 
@@ -906,7 +918,8 @@ static int attention_decode_impl(void* out, float* part_o, float* part_ml, const
 
 // q, out: bfloat16 [n_tokens, n_heads * head_dim], one token a sequence; pools bfloat16
 // [blocks, kv heads, 64, head_dim].  `chunk` (a multiple of 64) keys a split, `n_splits` splits
-// cover the longest sequence the launch may meet.  part_o: float32 [n_tokens * n_heads * n_splits *
+// cover the longest sequence the launch may meet (with a window: the window and what is left of the cache
+// block that holds its first key, window + 63 keys at most; splits are counted from that block).  part_o: float32 [n_tokens * n_heads * n_splits *
 // head_dim] and part_ml: float32 [n_tokens * n_heads * n_splits * 2] are scratch, needed when
 // n_splits > 1.  The group n_heads / n_kv_heads is at most 16; n_tokens at most 65535.
 // n_blocks: blocks in each pool (0 if unknown: the kernels fed by TMA are then not used); error_flag

@@ -54,11 +54,21 @@ def decode_split(n_seqs: int, n_kv_heads: int, max_context: int, sms: int, mean_
     return chunk, -(-blocks * BLOCK_TOKENS // chunk)
 
 
-def _decode_split_of(ctx, n_kv_heads: int, device):
-    """(keys a split, splits, whether splits may merge as clusters) for the step's lengths, by their powers of two."""
+def visible_span(context: int, window: int) -> int:
+    """Keys between the cache block that holds a token's first visible key and the token itself, at most: the
+    whole context without a window (0), else the window and what is left of its first block."""
+    if window <= 0:
+        return context
+    return min(context, -(-(window + BLOCK_TOKENS - 1) // BLOCK_TOKENS) * BLOCK_TOKENS)
+
+
+def _decode_split_of(ctx, n_kv_heads: int, device, window: int = 0):
+    """(keys a split, splits, whether splits may merge as clusters) for the step's lengths, by their powers of
+    two.  The kernels count a windowed layer's splits from the block of the first visible key, so its splits
+    are cut from the window's span however long the sequences are."""
     sms = ops.device_state(device)[2]
-    longest = context_bucket(ctx.max_context)
-    mean = min(longest, context_bucket(ctx.mean_context)) if ctx.mean_context > 0 else 0
+    longest = visible_span(context_bucket(ctx.max_context), window)
+    mean = min(longest, visible_span(context_bucket(ctx.mean_context), window)) if ctx.mean_context > 0 else 0
     return decode_split(ctx.n_tokens, n_kv_heads, longest, sms, mean) + (mean == 0 or mean == longest,)
 
 
@@ -71,7 +81,7 @@ def decode_from_qkv(out, qkv, k_offset, v_offset, q_norm, k_norm, eps, cos_sin, 
     if not (ctx.all_single and ctx.n_tokens <= 65535
             and ops.attention_decode_takes_qkv(n_heads, n_kv_heads, head_dim, rope_half, pairing)):
         return False
-    chunk, n_splits, clusters = _decode_split_of(ctx, n_kv_heads, qkv.device)
+    chunk, n_splits, clusters = _decode_split_of(ctx, n_kv_heads, qkv.device, window)
     fused = ctx.n_tokens * n_kv_heads <= FUSED_COMBINE_MAX
     ops.attention_decode_qkv(out, qkv, k_offset, v_offset, q_norm, k_norm, eps, cos_sin, store.k, store.v, ctx.tok_slot,
                              ctx.tok_pos, store.block_table, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits,
@@ -83,7 +93,7 @@ def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window) -> boo
     if n_heads // n_kv_heads > 16:
         return False
     if ctx.all_single and ctx.n_tokens <= 65535:
-        chunk, n_splits, clusters = _decode_split_of(ctx, n_kv_heads, q.device)
+        chunk, n_splits, clusters = _decode_split_of(ctx, n_kv_heads, q.device, window)
         # few sequences: the last block of a (token, kv head) merges its splits (one launch less);
         # many: a second kernel merges them with more threads (measured faster from 8 sequences on)
         fused = ctx.n_tokens * n_kv_heads <= FUSED_COMBINE_MAX
