@@ -325,6 +325,68 @@ def run_ours(args) -> int:
     return run_timed(args, model, cfg, shape_name, full_layers, n_layers, pk, setup_s)
 
 
+def run_attention_only(args) -> int:
+    """--only attention: the decode attention kernel alone for --batch sequences of --context keys with the shape's
+    heads, --window keys visible (0: all), 20 launches back to back in a CUDA graph; one small JSON line.
+    --splits-from context cuts a windowed layer's splits as a layer without a window would have them."""
+    import math
+    import torch
+    import xeno_rt_b200  # noqa: F401
+    from xeno_rt_b200.cache import BLOCK_TOKENS
+    from xeno_rt_b200.csrc import ops
+    from xeno_rt_b200.parts.attention_bf16 import FUSED_COMBINE_MAX, decode_split, visible_span
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: bench.py needs a B200"}))
+        return 1
+    if apply_tuning(args):
+        return 2
+    cfg = SHAPES[args.shape][1]
+    heads, kv_heads = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    head_dim = cfg.get("head_dim", cfg["hidden_size"] // heads)
+    dev = torch.device("cuda:0")
+    batch, context, window = args.batch, args.context, args.window
+    blocks_each = -(-context // BLOCK_TOKENS)
+    k = torch.randn(batch * blocks_each + 1, kv_heads, BLOCK_TOKENS, head_dim, device=dev, dtype=torch.bfloat16)
+    v = torch.randn_like(k)
+    table = torch.arange(1, 1 + batch * blocks_each, dtype=torch.int32, device=dev).reshape(batch, blocks_each)
+    table = torch.cat([torch.full((1, blocks_each), -1, dtype=torch.int32, device=dev), table])  # slot 0 stays empty
+    q = torch.randn(batch, heads * head_dim, device=dev, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    pos = torch.full((batch,), context - 1, dtype=torch.int32, device=dev)
+    slot = torch.arange(1, batch + 1, dtype=torch.int32, device=dev)
+    span = visible_span(context, window) if args.splits_from == "window" else context
+    chunk, n_splits = decode_split(batch, kv_heads, span, ops.device_state(dev)[2])
+    fused = batch * kv_heads <= FUSED_COMBINE_MAX
+
+    def launch():
+        ops.attention_decode(out, q, k, v, slot, pos, table, heads, kv_heads, head_dim, 1 / math.sqrt(head_dim), window,
+                             chunk, n_splits, fused=fused)
+
+    for _ in range(max(3, args.warmup)):
+        launch()
+    graph, repeats = torch.cuda.CUDAGraph(), 20
+    with torch.cuda.graph(graph):
+        for _ in range(repeats):
+            launch()
+    graph.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    ops.check_error_flag(dev)
+    us = start.elapsed_time(stop) / repeats * 1000
+    keys = min(context, window + BLOCK_TOKENS - 1) if window > 0 else context
+    read = batch * keys * kv_heads * head_dim * 2 * 2
+    print(json.dumps({"only": "attention", "us": round(us, 2), "batch": batch, "context": context, "window": window,
+                      "keys_a_split": chunk, "splits": n_splits, "heads": heads, "kv_heads": kv_heads,
+                      "head_dim": head_dim, "gbs_upper": round(read / us / 1000, 1),
+                      "flush": "none: launches back to back; cache of %d MB" % (2 * k.numel() * 2 // 2**20)}))
+    return 0
+
+
 def apply_tuning(args) -> int:
     """--tuning KEY=VALUE,... onto the kernels' tuning; returns 2 after a message if a key is unknown."""
     if args.tuning:
@@ -415,8 +477,13 @@ def main() -> int:
                              "256 decode steps at the Qwen3-8B shape; 8 x 2,048 then 512 steps at the Qwen3-32B shape)")
     parser.add_argument("--tuning", default="", metavar="KEY=VALUE[,KEY=VALUE...]",
                         help="kernel variants to force, as fields of xeno_rt_b200.csrc.ops.Tuning (for comparisons)")
-    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
-                        help="a short run of one part, for profiling; prints its own small JSON line")
+    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention"],
+                        help="a short run of one part, for profiling; prints its own small JSON line "
+                             "(attention: the decode attention kernel alone)")
+    parser.add_argument("--window", type=int, default=0, help="--only attention: keys a token sees (0 = all)")
+    parser.add_argument("--splits-from", default="window", choices=["window", "context"],
+                        help="--only attention with a window: cut the splits from the window's span (what the engine "
+                             "does) or from the whole context (what a layer without a window gets)")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -428,6 +495,8 @@ def main() -> int:
         return 2
     if args.warmup < 3 and args.only == "all":
         args.warmup = 3
+    if args.only == "attention":
+        return run_attention_only(args)
     if args.workload:
         apply_tuning(args)
         return run_workload(args)
