@@ -436,6 +436,37 @@ def test_attention_decode_finds_a_far_key_and_respects_the_window():
         assert torch.allclose(out.float(), ref.float(), atol=3e-2)
 
 
+@pytest.mark.parametrize("hd,rise", [(128, 0.07), (80, 0.07), (128, 0.2), (64, -0.05)])
+def test_attention_decode_scores_that_rise_slowly(hd, rise):
+    """The decode kernels move the reference value of a head's exponents only when a score has outgrown it by more
+    than 8 in base 2.  Scores that rise (or fall) by ``rise`` a key make the reference lag behind the maximum for
+    tiles on end (0.07 a key: 6.5 in base 2 between the 16 keys a warp sees in one tile and in the next), or jump at
+    every tile (0.2): the result must be the plain one either way, for one split and for several."""
+    nh, nkv, S = 8, 2, 900
+    torch.manual_seed(7)
+    k_pool, v_pool, table = _cache_for([S], nkv, hd, torch.bfloat16, shuffle_seed=4)
+    u = torch.randn(nkv, hd, device=DEV)
+    u = u / u.norm(dim=-1, keepdim=True)
+    ramp = torch.arange(S, device=DEV, dtype=torch.float32)[:, None, None] * rise * math.sqrt(hd)
+    k = (u[None] * ramp / 4 + torch.randn(S, nkv, hd, device=DEV) * 0.05)
+    v = torch.randn(S, nkv, hd, device=DEV)
+    q = (u.repeat_interleave(nh // nkv, dim=0) * 4)[None]  # head h reads kv head h // 4: score = rise * position + noise
+    _fill_cache(k_pool, v_pool, table, 1, k, v)
+    qf = q.reshape(1, nh * hd).to(torch.bfloat16)
+    tok_pos = torch.tensor([S - 1], dtype=torch.int32, device=DEV)
+    tok_slot = torch.tensor([1], dtype=torch.int32, device=DEV)
+    bf = lambda x: f64(x.to(torch.bfloat16))
+    q_full = np.zeros((S, nh * hd))
+    q_full[S - 1] = bf(qf)[0]
+    want = pm.causal_gqa_attention(q_full, bf(k).reshape(S, nkv * hd), bf(v).reshape(S, nkv * hd), nh, nkv, hd)[S - 1]
+    for chunk, n_splits in ((960, 1), (256, 4), (64, 15)):
+        for fused in (False, True):
+            out = torch.full_like(qf, 7.0)
+            ops().attention_decode(out, qf, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd), 0,
+                                   chunk, n_splits, fused=fused)
+            assert rel(out[0], want) < 1.5e-2, (chunk, n_splits, fused)
+
+
 @pytest.mark.parametrize("hd", [128, 80])
 def test_attention_decode_window_splits_start_at_the_window(hd):
     """A windowed layer's splits are counted from the cache block of its first visible key, so three splits

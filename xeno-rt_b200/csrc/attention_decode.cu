@@ -336,10 +336,12 @@ __global__ void attention_combine_kernel(__nv_bfloat16* __restrict__ out, const 
 // the wait for tile i.  The wait is bounded: if it runs out the block raises the error flag, waits
 // (bounded) for its copies in flight and leaves without writing.
 constexpr int DEC_BOX_BYTES = 64 * 128;
-// Tiles of 64 keys and values in shared memory: one being worked on, the others on their way.  Three were
-// measured against two at the 8B shape, context 4,096: the same time at 1 to 16 sequences, 9.48 against
-// 9.15 ms at 64 (a block of 97 KB leaves room for two a multiprocessor instead of three).
-constexpr int DEC_STAGES = 2;
+// Tiles of 64 keys and values in shared memory: one being worked on, the others on their way.  A tile's copy takes
+// about 1.1 microseconds to land and a block's four warps about 0.8 to work one off, so with two buffers (one copy in
+// flight) a tile costs (1.1 + 0.8) / 2 = 1 microsecond, with three what the warps need.  Three where two blocks a
+// multiprocessor hold the whole launch (97 KB a block at head size 128); two where more blocks have to be
+// resident to fill the device (measured at 64 sequences, three against two everywhere: 9.48 against 9.15 ms a step).
+constexpr int DEC_MAX_STAGES = 3;
 constexpr unsigned DEC_SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t dec_map_rank(uint32_t local_smem, int rank) {  // the same place in another block of the cluster
@@ -392,12 +394,12 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ tok_pos, const int* __restrict__ block_table, int max_blocks,
                             int n_heads, int n_kv_heads, int head_dim, float scale_log2, int window, int chunk,
                             int n_splits, int* __restrict__ counters, int* __restrict__ error_flag, int clustered,
-                            const DecodeFusedInput fused) {
+                            int stages, const DecodeFusedInput fused) {
   constexpr int D_TILES = HD_MAX / 8;
   __shared__ __align__(16) __nv_bfloat16 newest[2][HD_MAX];  // the step's own key and value of this kv head
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) uint64_t full[DEC_STAGES];
+  __shared__ __align__(8) uint64_t full[DEC_MAX_STAGES];
   pdl_trigger();
   // The step's arrays (slots, positions, block table) were written before the step began: they may be
   // read, and tiles of old keys fetched, while the kernel before this one (which writes q and the
@@ -425,33 +427,42 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int boxes = head_dim / 64;
   const int tile_bytes = boxes * DEC_BOX_BYTES;
   unsigned char* k_tiles = smem;                   // [stages][boxes][64 rows x 128 bytes]
-  unsigned char* v_tiles = smem + DEC_STAGES * tile_bytes;
+  unsigned char* v_tiles = smem + stages * tile_bytes;
   const uint32_t full_base = smem_addr(&full[0]);
   auto full_addr = [full_base](int stage) { return full_base + 8u * (uint32_t)stage; };
   if (threadIdx.x == 0) {
 #pragma unroll
-    for (int j = 0; j < DEC_STAGES; ++j) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full_addr(j)));
+    for (int j = 0; j < DEC_MAX_STAGES; ++j) asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(full_addr(j)));  // two asking threads
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
 
   const int* blocks = block_table + (size_t)slot * max_blocks;
+  const int n_tiles = has_keys ? (end - begin + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS : 0;  // begin is a multiple of 64
   // keys and values are read once a step: their lines are the first to leave the L2
   const uint64_t once = sm100::policy_evict_first();
-  auto issue_tile = [&](int tile_index, int buffer) {  // one thread
-    const int key0 = begin + tile_index * XRT_BLOCK_TOKENS;
-    const int row0 = (blocks[key0 / XRT_BLOCK_TOKENS] * n_kv_heads + kv_head) * XRT_BLOCK_TOKENS;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_addr(buffer)), "r"(2 * tile_bytes)
+  // Lane 0 of warp 0 asks for a tile's keys, lane 0 of warp 1 for its values (a copy instruction costs the thread
+  // that issues it about 200 cycles, and its warp has its 16 keys to work on like the others).  Each has the cache
+  // block's number of the tile it asks for next in a register, read from the block table a tile earlier: that
+  // read's latency is not in the way of the copy.
+  const bool asks = lane == 0 && warp < 2;
+  auto block_of = [&](int tile_index) { return __ldg(blocks + begin / XRT_BLOCK_TOKENS + tile_index); };
+  int next_block = 0;
+  auto issue_tile = [&](int tile_index, int buffer, int block) {  // the two asking threads
+    const int row0 = (block * n_kv_heads + kv_head) * XRT_BLOCK_TOKENS;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_addr(buffer)), "r"(tile_bytes)
                  : "memory");
     // one copy a tile: the map's third dimension walks the row's pieces of 64 dims, so that the boxes of 64 rows x
-    // 128 bytes land one behind the other (a copy instruction costs the thread that issues it about 200 cycles,
-    // and this thread's warp has its 16 keys to work on like the others)
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
-                 ::"r"(smem_addr(k_tiles + buffer * tile_bytes)), "l"(&map_k), "r"(0), "r"(row0), "r"(0), "r"(full_addr(buffer)), "l"(once)
-                 : "memory");
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
-                 ::"r"(smem_addr(v_tiles + buffer * tile_bytes)), "l"(&map_v), "r"(0), "r"(row0), "r"(0), "r"(full_addr(buffer)), "l"(once)
-                 : "memory");
+    // 128 bytes land one behind the other
+    if (warp == 0)
+      asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+                   ::"r"(smem_addr(k_tiles + buffer * tile_bytes)), "l"(&map_k), "r"(0), "r"(row0), "r"(0), "r"(full_addr(buffer)), "l"(once)
+                   : "memory");
+    else
+      asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+                   ::"r"(smem_addr(v_tiles + buffer * tile_bytes)), "l"(&map_v), "r"(0), "r"(row0), "r"(0), "r"(full_addr(buffer)), "l"(once)
+                   : "memory");
+    if (tile_index + 1 < n_tiles) next_block = block_of(tile_index + 1);
   };
 
   // query operand: column g = head g of the group (zero at or beyond the group)
@@ -460,7 +471,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const bool holds_newest = has_keys && len - 1 >= begin && len - 1 < end;
   const bool writes_newest = fused.qkv != nullptr && fused.k_pool != nullptr && holds_newest;
   const bool early = has_keys && (fused.qkv != nullptr || begin + XRT_BLOCK_TOKENS <= len - 1);
-  if (threadIdx.x == 0 && early) issue_tile(0, 0);
+  if (asks && early) issue_tile(0, 0, block_of(0));
   pdl_wait();
   uint32_t qb[D_TILES / 2][2];
   if (fused.qkv == nullptr) {
@@ -566,17 +577,18 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   }
   HeadColumnState<D_TILES> st;
   st.init();
-  const int n_tiles = has_keys ? (end - begin + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS : 0;  // begin is a multiple of 64
-  if (threadIdx.x == 0) {
-    if (n_tiles > 0 && !early) issue_tile(0, 0);
-    for (int j = 1; j < DEC_STAGES - 1 && j < n_tiles; ++j) issue_tile(j, j);
+  if (asks) {
+    if (n_tiles > 0 && !early) issue_tile(0, 0, block_of(0));
+    for (int j = 1; j < stages - 1 && j < n_tiles; ++j) issue_tile(j, j, next_block);
   }
   int failed = 0, i = 0;
+  int stage = 0, ahead_stage = stages - 1;  // i % stages and (i + stages - 1) % stages
+  uint32_t parity = 0;                      // (i / stages) % 2
   for (; i < n_tiles; ++i) {
     // the buffer of tile i + stages - 1 held tile i - 1, which every warp left before the barrier that ended the last round
-    const int ahead = i + DEC_STAGES - 1, stage = i % DEC_STAGES;
-    if (threadIdx.x == 0 && ahead < n_tiles) issue_tile(ahead, ahead % DEC_STAGES);
-    if (!dec_mbar_wait(full_addr(stage), (uint32_t)(i / DEC_STAGES) & 1u)) failed = 1;
+    const int ahead = i + stages - 1;
+    if (asks && ahead < n_tiles) issue_tile(ahead, ahead_stage, next_block);
+    if (!dec_mbar_wait(full_addr(stage), parity)) failed = 1;
     if (writes_newest && i == n_tiles - 1) {
       // the newest key and value into their row of the tile that has just landed (whatever the copy
       // read there): piece c of row r lies at piece c ^ (r % 8) of its box of 64 dims
@@ -595,13 +607,15 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                                           warp * 16, key_abs, first_key, len,
                                           key_abs < first_key || key_abs + 16 > len, head_dim, scale_log2);
     if (__syncthreads_or(failed)) { failed = 1; break; }
+    ahead_stage = stage;
+    if (++stage == stages) { stage = 0; parity ^= 1u; }
   }
   if (failed) {
     if (threadIdx.x == 0) {
       if (error_flag != nullptr) atomicCAS(error_flag, 0, 6);
       // copies in flight write this block's shared memory: they must have landed before it is given back
-      for (int j = i; j < i + DEC_STAGES && j < n_tiles; ++j)
-        dec_mbar_wait(full_addr(j % DEC_STAGES), (uint32_t)(j / DEC_STAGES) & 1u);
+      for (int j = i; j < i + stages && j < n_tiles; ++j)
+        dec_mbar_wait(full_addr(j % stages), (uint32_t)(j / stages) & 1u);
     }
     __syncthreads();
     if (!clustered) return;  // in a cluster the block still meets the others (its state below is meaningless)
@@ -711,9 +725,25 @@ static bool dec_make_map(CUtensorMap* map, const void* base, long long rows, int
 
 // shared memory of the TMA kernel: the tiles (or the warps' states that reuse their room), then a
 // block's merged state for the cluster merge
-inline int decode_tma_smem(int head_dim) {
+inline int decode_tma_smem(int head_dim, int stages = 2) {
   const int merge_bytes = DEC_WARPS * 16 * (2 + head_dim + 8) * (int)sizeof(float) + (2 * 16 + 8 * head_dim) * (int)sizeof(float);
-  return 1024 + max(2 * DEC_STAGES * (head_dim / 64) * DEC_BOX_BYTES, merge_bytes);
+  return 1024 + max(2 * stages * (head_dim / 64) * DEC_BOX_BYTES, merge_bytes);
+}
+
+// Three buffers where the blocks that fit a multiprocessor with three (at most three a multiprocessor, as with
+// two) hold the whole launch; else two.
+inline int decode_tma_stages(int head_dim, long long blocks) {
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0, count = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
+      return 2;
+    sms = count;
+  }
+  const int each = decode_tma_smem(head_dim, DEC_MAX_STAGES) + 2048;  // with the kernel's static arrays
+  const int resident = min(3, 226 * 1024 / each);
+  return blocks <= (long long)sms * resident ? DEC_MAX_STAGES : 2;
 }
 
 // Tuning::decode_attention = 3 keeps the merge by a second kernel or by the last block, for comparison.
@@ -736,38 +766,53 @@ int launch_decode_tma(__nv_bfloat16* out, float* part_o, float* part_ml, const _
   CUtensorMap map_k, map_v;
   if (!dec_make_map(&map_k, k_pool, pool_rows, head_dim) || !dec_make_map(&map_v, v_pool, pool_rows, head_dim))
     return XRT_ERR_UNSUPPORTED;
-  const int smem = decode_tma_smem(head_dim);
   auto kernel = attention_decode_tma_kernel<HD_MAX>;
   static int smem_allowed = 0;  // raised once a size class; not a stream operation
-  if (smem > 48 * 1024 && smem > smem_allowed) {
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (err != cudaSuccess) return (int)err;
-    smem_allowed = smem;
-  }
+  auto allow = [&](int bytes) {
+    if (bytes > 48 * 1024 && bytes > smem_allowed) {
+      cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      if (err != cudaSuccess) return (int)err;
+      smem_allowed = bytes;
+    }
+    return 0;
+  };
   // 2 to 16 splits: the splits of a (token, kv head) as one thread-block cluster that merges itself
   // through distributed shared memory, if the device can hold such a cluster (asked once a size)
-  static int cluster_ok[DEC_MAX_CLUSTER + 1][5] = {};  // by splits and head-size class: 0 unknown, 1 yes, 2 no
-  const bool clustered = clusters && decode_cluster_wanted(n_splits, n_tokens * n_kv_heads) && [&]() {
-    int& known = cluster_ok[n_splits][HD_MAX / 64];
+  // by splits, head-size class and buffers: 0 unknown, else 1 + the clusters that the device holds at once
+  static int cluster_room[DEC_MAX_CLUSTER + 1][5][DEC_MAX_STAGES + 1] = {};
+  auto clusters_held = [&](int buffers) {
+    int& known = cluster_room[n_splits][HD_MAX / 64][buffers];
     if (known == 0) {
-      known = 2;
-      if (n_splits <= 8 || cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+      known = 1;
+      const int bytes = decode_tma_smem(head_dim, buffers);
+      if (allow(bytes) == 0 &&
+          (n_splits <= 8 || cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess)) {
         cudaLaunchConfig_t probe = {};
         probe.gridDim = dim3(n_splits, 1, 1);
         probe.blockDim = dim3(DEC_WARPS * 32);
-        probe.dynamicSmemBytes = smem;
+        probe.dynamicSmemBytes = bytes;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = n_splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
         probe.attrs = attr;
         probe.numAttrs = 1;
         int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &probe) == cudaSuccess && clusters >= 1) known = 1;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &probe) == cudaSuccess && clusters >= 1) known = 1 + clusters;
         cudaGetLastError();  // a refusal here is an answer, not an error of the stream
       }
     }
-    return known == 1;
-  }();
+    return known - 1;
+  };
+  int stages = decode_tma_stages(head_dim, (long long)n_splits * n_kv_heads * n_tokens);
+  bool clustered = false;
+  if (clusters && decode_cluster_wanted(n_splits, n_tokens * n_kv_heads)) {
+    // clusters of larger blocks are harder to place: three buffers only where all of the launch's clusters still
+    // run at once (16 splits of 2 sequences with three: 3.44 against 3.38 ms a step)
+    if (stages > 2 && clusters_held(stages) < n_tokens * n_kv_heads) stages = 2;
+    clustered = clusters_held(stages) >= 1;
+  }
+  const int smem = decode_tma_smem(head_dim, stages);
+  if (int err = allow(smem)) return err;
   *merged = clustered;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(n_splits, n_kv_heads, n_tokens);
@@ -790,7 +835,7 @@ int launch_decode_tma(__nv_bfloat16* out, float* part_o, float* part_ml, const _
   config.numAttrs = n_attrs;
   cudaLaunchKernelEx(&config, kernel, map_k, map_v, out, part_o, part_ml, q, tok_slot, tok_pos, block_table, max_blocks,
                      n_heads, n_kv_heads, head_dim, scale * 1.4426950408889634f, window, chunk, n_splits, counters, error_flag,
-                     clustered ? 1 : 0, fused);
+                     clustered ? 1 : 0, stages, fused);
   return launch_status();
 }
 

@@ -283,7 +283,9 @@ __device__ __forceinline__ void attend_keys(SoftmaxState<D_TILES>& st, const uin
 // Lane (g, t) holds heads 2t and 2t + 1: their running maxima (equal in all lanes of a t), its share
 // of their sums, and for every 16 dims the outputs (dim g, dim g + 8) x (head 2t, head 2t + 1).
 
-__device__ __forceinline__ float fast_exp2(float x) {  // 2^x for x <= 0; -inf gives 0
+constexpr float DEC_REFERENCE_SLACK = 8.f;  // how far (base 2) a score may outgrow the reference of a head's exponents
+
+__device__ __forceinline__ float fast_exp2(float x) {  // 2^x; -inf gives 0
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
@@ -328,13 +330,24 @@ __device__ __forceinline__ void attend_16_keys_heads(HeadColumnState<D_TILES>& s
   const uint32_t k_base = SWIZZLED ? smem_addr(ks_tile + (key_row + (lane & 15)) * 128)
                                    : smem_addr(ks_tile + (key_row + (lane & 15)) * row_bytes + (lane >> 4) * 16);
   const uint32_t k_piece = (uint32_t)((lane >> 4) ^ (lane & 7));  // this lane's piece of a step, before the step's own bits
+  // The loads of LOADS_AHEAD steps are asked for before the first of their products: the instructions run in the
+  // order they are written, and a product straight after its own load waited out that load's latency every step.
+  constexpr int LOADS_AHEAD = D_TILES / 2 < 8 ? D_TILES / 2 : 8;
 #pragma unroll
-  for (int ks = 0; ks < D_TILES / 2; ++ks) {
-    if (ks * 16 < head_dim) {
-      uint32_t kf[4];
-      if (SWIZZLED) ldmatrix_x4(kf, k_base + (ks >> 2) * 8192 + ((k_piece ^ ((2 * ks) & 7)) << 4));
-      else ldmatrix_x4(kf, k_base + ks * 32);
-      mma_16816(s[ks & 1], kf, qb[ks][0], qb[ks][1]);
+  for (int ks0 = 0; ks0 < D_TILES / 2; ks0 += LOADS_AHEAD) {
+    uint32_t kf[LOADS_AHEAD][4];
+#pragma unroll
+    for (int j = 0; j < LOADS_AHEAD; ++j) {
+      const int ks = ks0 + j;
+      if (ks * 16 < head_dim) {
+        if (SWIZZLED) ldmatrix_x4(kf[j], k_base + (ks >> 2) * 8192 + ((k_piece ^ ((2 * ks) & 7)) << 4));
+        else ldmatrix_x4(kf[j], k_base + ks * 32);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < LOADS_AHEAD; ++j) {
+      const int ks = ks0 + j;
+      if (ks * 16 < head_dim) mma_16816(s[ks & 1], kf[j], qb[ks][0], qb[ks][1]);
     }
   }
   // c0, c1: key g x heads 2t, 2t+1; c2, c3: key g + 8
@@ -348,23 +361,34 @@ __device__ __forceinline__ void attend_16_keys_heads(HeadColumnState<D_TILES>& s
     }
     v[e] = live ? (s[0][e] + s[1][e]) * scale_log2 : -INFINITY;
   }
-  float corr[2];
+  // st.m is the reference value of a head's exponents, not its running maximum: it moves only when a score has
+  // outgrown it by more than 8 in base 2 (weights then reach 2^8 at most, far inside bfloat16 and the 32-bit
+  // sums), so most tiles need neither the maximum over the keys (three shuffles a head, one after the other)
+  // nor a rescaled output.  The vote is uniform over the warp.
+  float corr[2] = {1.f, 1.f};
+  const bool rescale = __any_sync(0xffffffffu, fmaxf(v[0], v[2]) - st.m[0] > DEC_REFERENCE_SLACK ||
+                                                   fmaxf(v[1], v[3]) - st.m[1] > DEC_REFERENCE_SLACK);
+  if (rescale) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float tile_max = fmaxf(v[h], v[h + 2]);
+      tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
+      tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
+      tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
+      const float m_new = fmaxf(st.m[h], tile_max);
+      // a head with no live key so far keeps m = -inf; 2^(-inf - -inf) must not be NaN
+      corr[h] = m_new == -INFINITY ? 1.f : fast_exp2(st.m[h] - m_new);
+      st.m[h] = m_new;
+      st.l[h] *= corr[h];
+    }
+  }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    float tile_max = fmaxf(v[h], v[h + 2]);
-    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
-    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
-    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
-    const float m_new = fmaxf(st.m[h], tile_max);
-    // a head with no live key so far keeps m = -inf; 2^(-inf - -inf) must not be NaN
-    corr[h] = m_new == -INFINITY ? 1.f : fast_exp2(st.m[h] - m_new);
-    st.m[h] = m_new;
-    const float base = m_new == -INFINITY ? 0.f : m_new;  // then every score is -inf and every weight 0
+    const float base = st.m[h] == -INFINITY ? 0.f : st.m[h];  // then every score is -inf and every weight 0
     v[h] = fast_exp2(v[h] - base);
     v[h + 2] = fast_exp2(v[h + 2] - base);
-    st.l[h] = st.l[h] * corr[h] + (v[h] + v[h + 2]);
+    st.l[h] += v[h] + v[h + 2];
   }
-  const bool rescale = __any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f);
   const uint32_t p_lo = transpose_8x8(pack_bf16(v[0], v[1]));  // keys 2t, 2t+1 of head g
   const uint32_t p_hi = transpose_8x8(pack_bf16(v[2], v[3]));  // keys 2t+8, 2t+9
   // V^T as the A operand (transposed load): matrix j = keys (j / 2) * 8 .., dims dt * 16 + (j % 2) * 8 ..
@@ -380,22 +404,29 @@ __device__ __forceinline__ void attend_16_keys_heads(HeadColumnState<D_TILES>& s
     keep_hi = (live(key_abs + 2 * t + 8) ? 0x0000ffffu : 0u) | (live(key_abs + 2 * t + 9) ? 0xffff0000u : 0u);
   }
 #pragma unroll
-  for (int dt = 0; dt < D_TILES / 2; ++dt) {
-    if (dt * 16 < head_dim) {
-      uint32_t vf[4];
-      if (SWIZZLED) {
-        ldmatrix_x4_trans(vf, v_base + (dt >> 2) * 8192 + ((v_piece ^ ((2 * dt) & 7)) << 4));
-        if (masked) { vf[0] &= keep_lo; vf[1] &= keep_lo; vf[2] &= keep_hi; vf[3] &= keep_hi; }
-      } else {
-        ldmatrix_x4_trans(vf, v_base + dt * 32);
+  for (int dt0 = 0; dt0 < D_TILES / 2; dt0 += LOADS_AHEAD) {
+    uint32_t vf[LOADS_AHEAD][4];
+#pragma unroll
+    for (int j = 0; j < LOADS_AHEAD; ++j) {
+      const int dt = dt0 + j;
+      if (dt * 16 < head_dim) {
+        if (SWIZZLED) ldmatrix_x4_trans(vf[j], v_base + (dt >> 2) * 8192 + ((v_piece ^ ((2 * dt) & 7)) << 4));
+        else ldmatrix_x4_trans(vf[j], v_base + dt * 32);
       }
-      if (rescale) {
-        st.o[dt][0] *= corr[0];
-        st.o[dt][1] *= corr[1];
-        st.o[dt][2] *= corr[0];
-        st.o[dt][3] *= corr[1];
+    }
+#pragma unroll
+    for (int j = 0; j < LOADS_AHEAD; ++j) {
+      const int dt = dt0 + j;
+      if (dt * 16 < head_dim) {
+        if (SWIZZLED && masked) { vf[j][0] &= keep_lo; vf[j][1] &= keep_lo; vf[j][2] &= keep_hi; vf[j][3] &= keep_hi; }
+        if (rescale) {
+          st.o[dt][0] *= corr[0];
+          st.o[dt][1] *= corr[1];
+          st.o[dt][2] *= corr[0];
+          st.o[dt][3] *= corr[1];
+        }
+        mma_16816(st.o[dt], vf[j], p_lo, p_hi);
       }
-      mma_16816(st.o[dt], vf, p_lo, p_hi);
     }
   }
 }
