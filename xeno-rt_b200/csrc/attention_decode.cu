@@ -806,9 +806,10 @@ int launch_decode_tma(__nv_bfloat16* out, float* part_o, float* part_ml, const _
   int stages = decode_tma_stages(head_dim, (long long)n_splits * n_kv_heads * n_tokens);
   bool clustered = false;
   if (clusters && decode_cluster_wanted(n_splits, n_tokens * n_kv_heads)) {
-    // clusters of larger blocks are harder to place: three buffers only where all of the launch's clusters still
-    // run at once (16 splits of 2 sequences with three: 3.44 against 3.38 ms a step)
-    if (stages > 2 && clusters_held(stages) < n_tokens * n_kv_heads) stages = 2;
+    // clusters of larger blocks are harder to place: three buffers only for clusters of up to four blocks (8 splits
+    // of 4 sequences with three: 3.49 against 3.35 ms a step; 16 splits of 2 sequences: 3.44 against 3.38) and
+    // where all of the launch's clusters still run at once
+    if (stages > 2 && (n_splits > 4 || clusters_held(stages) < n_tokens * n_kv_heads)) stages = 2;
     clustered = clusters_held(stages) >= 1;
   }
   const int smem = decode_tma_smem(head_dim, stages);
