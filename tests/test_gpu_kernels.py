@@ -436,6 +436,31 @@ def test_attention_decode_finds_a_far_key_and_respects_the_window():
         assert torch.allclose(out.float(), ref.float(), atol=3e-2)
 
 
+@pytest.mark.parametrize("hd", [128, 64])
+def test_attention_decode_launches_of_many_blocks(hd):
+    """The kernel fed by TMA keeps three tile buffers where two blocks a multiprocessor hold the launch and two
+    where more blocks have to be resident: 48 tokens x 2 kv heads x 4 splits are 384 blocks (two buffers), 6 tokens 48
+    (three).  The 48 slots read prefixes of different lengths of the same cache blocks; the reference kernel says what
+    must come out, with the splits merged as clusters, by the last block and by the second kernel."""
+    nh, nkv, S, T = 8, 2, 520, 48
+    torch.manual_seed(hd + 5)
+    k_pool, v_pool, table = _cache_for([S], nkv, hd, torch.bfloat16, shuffle_seed=5)
+    _fill_cache(k_pool, v_pool, table, 1, torch.randn(S, nkv, hd, device=DEV), torch.randn(S, nkv, hd, device=DEV))
+    table = torch.cat([table[:1], table[1:2].repeat(T, 1)])  # slots 1 .. T share the sequence's blocks
+    tok_slot = torch.arange(1, T + 1, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([60 + (457 * i) % 460 for i in range(T)], dtype=torch.int32, device=DEV)
+    q = (torch.randn(T, nh * hd, device=DEV) * 0.3).to(torch.bfloat16)
+    ref = torch.empty_like(q)
+    ops().attention_reference(ref, q, k_pool, v_pool, tok_slot, tok_pos, table, nh, nkv, hd, 1 / math.sqrt(hd))
+    for tokens in (T, 6):
+        for fused, clusters in ((True, True), (True, False), (False, False)):
+            out = torch.full_like(q, 7.0)
+            ops().attention_decode(out[:tokens], q[:tokens], k_pool, v_pool, tok_slot[:tokens], tok_pos[:tokens], table, nh, nkv,
+                                   hd, 1 / math.sqrt(hd), 0, 192, 3 if tokens == 6 else 4, fused=fused, clusters=clusters)
+            assert rel(out[:tokens], f64(ref[:tokens])) < 1.5e-2, (tokens, fused, clusters)
+            assert float((out[tokens:].float() - 7.0).abs().max()) == 0.0 if tokens < T else True
+
+
 @pytest.mark.parametrize("hd,rise", [(128, 0.07), (80, 0.07), (128, 0.2), (64, -0.05)])
 def test_attention_decode_scores_that_rise_slowly(hd, rise):
     """The decode kernels move the reference value of a head's exponents only when a score has outgrown it by more

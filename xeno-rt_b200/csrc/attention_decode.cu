@@ -336,12 +336,17 @@ __global__ void attention_combine_kernel(__nv_bfloat16* __restrict__ out, const 
 // the wait for tile i.  The wait is bounded: if it runs out the block raises the error flag, waits
 // (bounded) for its copies in flight and leaves without writing.
 constexpr int DEC_BOX_BYTES = 64 * 128;
-// Tiles of 64 keys and values in shared memory: one being worked on, the others on their way.  A tile's copy takes
-// about 1.1 microseconds to land and a block's four warps about 0.8 to work one off, so with two buffers (one copy in
-// flight) a tile costs (1.1 + 0.8) / 2 = 1 microsecond, with three what the warps need.  Three where two blocks a
-// multiprocessor hold the whole launch (97 KB a block at head size 128); two where more blocks have to be
-// resident to fill the device (measured at 64 sequences, three against two everywhere: 9.48 against 9.15 ms a step).
-constexpr int DEC_MAX_STAGES = 3;
+// Tiles of 64 keys and of 64 values in shared memory, each kind in a ring and on barriers of its own: one tile being
+// worked on, the others on their way.  A tile's copy takes about 1.1 microseconds to land and a block's four warps
+// about 0.8 to work a tile off, so with two buffers (one copy in flight) a tile costs (1.1 + 0.8) / 2 = 1
+// microsecond, with three what the warps need.  The values are read in the second half of a tile's work, so two
+// buffers are enough for them when the keys have three: 81 KB a block at head size 128 instead of 97.  The size
+// matters beyond this kernel: what a block leaves free of a multiprocessor's shared memory is where the blocks
+// of the next product wait with their first weights (the same kernel with 32 KB of unused shared memory: 3.59
+// against 3.35 ms a step at 4 sequences).  Three key buffers where two blocks a multiprocessor hold the whole launch;
+// two where more blocks have to be resident to fill the device (64 sequences with three: 9.17 against 8.80 ms).
+constexpr int DEC_MAX_STAGES = 3;   // buffers of keys at most
+constexpr int DEC_VALUE_STAGES = 2;  // buffers of values
 constexpr unsigned DEC_SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t dec_map_rank(uint32_t local_smem, int rank) {  // the same place in another block of the cluster
@@ -399,7 +404,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __shared__ __align__(16) __nv_bfloat16 newest[2][HD_MAX];  // the step's own key and value of this kv head
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) uint64_t full[DEC_MAX_STAGES];
+  __shared__ __align__(8) uint64_t full[DEC_MAX_STAGES + DEC_VALUE_STAGES];  // keys' buffers, then values'
   pdl_trigger();
   // The step's arrays (slots, positions, block table) were written before the step began: they may be
   // read, and tiles of old keys fetched, while the kernel before this one (which writes q and the
@@ -427,12 +432,14 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int boxes = head_dim / 64;
   const int tile_bytes = boxes * DEC_BOX_BYTES;
   unsigned char* k_tiles = smem;                   // [stages][boxes][64 rows x 128 bytes]
-  unsigned char* v_tiles = smem + stages * tile_bytes;
+  unsigned char* v_tiles = smem + stages * tile_bytes;  // [DEC_VALUE_STAGES][boxes][64 rows x 128 bytes]
   const uint32_t full_base = smem_addr(&full[0]);
-  auto full_addr = [full_base](int stage) { return full_base + 8u * (uint32_t)stage; };
+  auto k_full = [full_base](int stage) { return full_base + 8u * (uint32_t)stage; };
+  auto v_full = [full_base](int stage) { return full_base + 8u * (uint32_t)(DEC_MAX_STAGES + stage); };
   if (threadIdx.x == 0) {
 #pragma unroll
-    for (int j = 0; j < DEC_MAX_STAGES; ++j) asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(full_addr(j)));  // two asking threads
+    for (int j = 0; j < DEC_MAX_STAGES + DEC_VALUE_STAGES; ++j)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full_base + 8u * (uint32_t)j));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -441,26 +448,27 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int n_tiles = has_keys ? (end - begin + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS : 0;  // begin is a multiple of 64
   // keys and values are read once a step: their lines are the first to leave the L2
   const uint64_t once = sm100::policy_evict_first();
-  // Lane 0 of warp 0 asks for a tile's keys, lane 0 of warp 1 for its values (a copy instruction costs the thread
-  // that issues it about 200 cycles, and its warp has its 16 keys to work on like the others).  Each has the cache
-  // block's number of the tile it asks for next in a register, read from the block table a tile earlier: that
-  // read's latency is not in the way of the copy.
+  // Lane 0 of warp 0 asks for the tiles of keys, lane 0 of warp 1 for the tiles of values (a copy instruction costs
+  // the thread that issues it about 200 cycles, and its warp has its 16 keys to work on like the others).  Each has
+  // the cache block's number of the tile it asks for next in a register, read from the block table a tile earlier:
+  // that read's latency is not in the way of the copy.
   const bool asks = lane == 0 && warp < 2;
+  const int my_stages = warp == 0 ? stages : DEC_VALUE_STAGES;  // of the ring this thread asks for
   auto block_of = [&](int tile_index) { return __ldg(blocks + begin / XRT_BLOCK_TOKENS + tile_index); };
   int next_block = 0;
-  auto issue_tile = [&](int tile_index, int buffer, int block) {  // the two asking threads
+  auto issue_tile = [&](int tile_index, int buffer, int block) {  // the two asking threads, each into its own ring
     const int row0 = (block * n_kv_heads + kv_head) * XRT_BLOCK_TOKENS;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_addr(buffer)), "r"(tile_bytes)
-                 : "memory");
+    const uint32_t bar = warp == 0 ? k_full(buffer) : v_full(buffer);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tile_bytes) : "memory");
     // one copy a tile: the map's third dimension walks the row's pieces of 64 dims, so that the boxes of 64 rows x
     // 128 bytes land one behind the other
     if (warp == 0)
       asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
-                   ::"r"(smem_addr(k_tiles + buffer * tile_bytes)), "l"(&map_k), "r"(0), "r"(row0), "r"(0), "r"(full_addr(buffer)), "l"(once)
+                   ::"r"(smem_addr(k_tiles + buffer * tile_bytes)), "l"(&map_k), "r"(0), "r"(row0), "r"(0), "r"(bar), "l"(once)
                    : "memory");
     else
       asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
-                   ::"r"(smem_addr(v_tiles + buffer * tile_bytes)), "l"(&map_v), "r"(0), "r"(row0), "r"(0), "r"(full_addr(buffer)), "l"(once)
+                   ::"r"(smem_addr(v_tiles + buffer * tile_bytes)), "l"(&map_v), "r"(0), "r"(row0), "r"(0), "r"(bar), "l"(once)
                    : "memory");
     if (tile_index + 1 < n_tiles) next_block = block_of(tile_index + 1);
   };
@@ -579,43 +587,52 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   st.init();
   if (asks) {
     if (n_tiles > 0 && !early) issue_tile(0, 0, block_of(0));
-    for (int j = 1; j < stages - 1 && j < n_tiles; ++j) issue_tile(j, j, next_block);
+    for (int j = 1; j < my_stages - 1 && j < n_tiles; ++j) issue_tile(j, j, next_block);
   }
   int failed = 0, i = 0;
-  int stage = 0, ahead_stage = stages - 1;  // i % stages and (i + stages - 1) % stages
-  uint32_t parity = 0;                      // (i / stages) % 2
+  int k_stage = 0, v_stage = 0;             // i % stages, i % DEC_VALUE_STAGES
+  int ahead_stage = my_stages - 1;          // an asking thread: (i + its ring's buffers - 1) % its ring's buffers
+  uint32_t k_parity = 0, v_parity = 0;      // (i / buffers) % 2
   for (; i < n_tiles; ++i) {
-    // the buffer of tile i + stages - 1 held tile i - 1, which every warp left before the barrier that ended the last round
-    const int ahead = i + stages - 1;
+    // the buffer of tile i + buffers - 1 held tile i - 1, which every warp left before the barrier that ended the last round
+    const int ahead = i + my_stages - 1;
     if (asks && ahead < n_tiles) issue_tile(ahead, ahead_stage, next_block);
-    if (!dec_mbar_wait(full_addr(stage), parity)) failed = 1;
+    if (!dec_mbar_wait(k_full(k_stage), k_parity)) failed = 1;
     if (writes_newest && i == n_tiles - 1) {
+      if (!dec_mbar_wait(v_full(v_stage), v_parity)) failed = 1;
       // the newest key and value into their row of the tile that has just landed (whatever the copy
       // read there): piece c of row r lies at piece c ^ (r % 8) of its box of 64 dims
       const int r = (len - 1) % XRT_BLOCK_TOKENS;
       if (threadIdx.x < 2 * (HD_MAX / 8)) {
         const int which = threadIdx.x / (HD_MAX / 8), piece = threadIdx.x % (HD_MAX / 8);
-        unsigned char* tile = (which == 0 ? k_tiles : v_tiles) + stage * tile_bytes;
+        unsigned char* tile = which == 0 ? k_tiles + k_stage * tile_bytes : v_tiles + v_stage * tile_bytes;
         *reinterpret_cast<uint4*>(tile + (piece >> 3) * DEC_BOX_BYTES + r * 128 + (((piece & 7) ^ (r & 7)) << 4)) =
             *reinterpret_cast<const uint4*>(&newest[which][piece * 8]);
       }
       __syncthreads();
     }
     const int key_abs = begin + i * XRT_BLOCK_TOKENS + warp * 16;
-    if (!failed && key_abs < end)  // only the first and the last 16 keys a warp sees can hold a hidden key
-      attend_16_keys_heads<D_TILES, true>(st, qb, k_tiles + stage * tile_bytes, v_tiles + stage * tile_bytes,
-                                          warp * 16, key_abs, first_key, len,
-                                          key_abs < first_key || key_abs + 16 > len, head_dim, scale_log2);
+    if (!failed && key_abs < end) {  // only the first and the last 16 keys a warp sees can hold a hidden key
+      const uint32_t values_bar = v_full(v_stage);
+      if (!attend_16_keys_heads<D_TILES, true>(st, qb, k_tiles + k_stage * tile_bytes, v_tiles + v_stage * tile_bytes,
+                                               warp * 16, key_abs, first_key, len,
+                                               key_abs < first_key || key_abs + 16 > len, head_dim, scale_log2,
+                                               [&] { return dec_mbar_wait(values_bar, v_parity); }))
+        failed = 1;
+    }
     if (__syncthreads_or(failed)) { failed = 1; break; }
-    ahead_stage = stage;
-    if (++stage == stages) { stage = 0; parity ^= 1u; }
+    ahead_stage = warp == 0 ? k_stage : v_stage;
+    if (++k_stage == stages) { k_stage = 0; k_parity ^= 1u; }
+    if (++v_stage == DEC_VALUE_STAGES) { v_stage = 0; v_parity ^= 1u; }
   }
   if (failed) {
     if (threadIdx.x == 0) {
       if (error_flag != nullptr) atomicCAS(error_flag, 0, 6);
       // copies in flight write this block's shared memory: they must have landed before it is given back
       for (int j = i; j < i + stages && j < n_tiles; ++j)
-        dec_mbar_wait(full_addr(j % stages), (uint32_t)(j / stages) & 1u);
+        dec_mbar_wait(k_full(j % stages), (uint32_t)(j / stages) & 1u);
+      for (int j = i; j < i + DEC_VALUE_STAGES && j < n_tiles; ++j)
+        dec_mbar_wait(v_full(j % DEC_VALUE_STAGES), (uint32_t)(j / DEC_VALUE_STAGES) & 1u);
     }
     __syncthreads();
     if (!clustered) return;  // in a cluster the block still meets the others (its state below is meaningless)
@@ -727,7 +744,7 @@ static bool dec_make_map(CUtensorMap* map, const void* base, long long rows, int
 // block's merged state for the cluster merge
 inline int decode_tma_smem(int head_dim, int stages = 2) {
   const int merge_bytes = DEC_WARPS * 16 * (2 + head_dim + 8) * (int)sizeof(float) + (2 * 16 + 8 * head_dim) * (int)sizeof(float);
-  return 1024 + max(2 * stages * (head_dim / 64) * DEC_BOX_BYTES, merge_bytes);
+  return 1024 + max((stages + DEC_VALUE_STAGES) * (head_dim / 64) * DEC_BOX_BYTES, merge_bytes);
 }
 
 // Three buffers where the blocks that fit a multiprocessor with three (at most three a multiprocessor, as with
@@ -806,9 +823,9 @@ int launch_decode_tma(__nv_bfloat16* out, float* part_o, float* part_ml, const _
   int stages = decode_tma_stages(head_dim, (long long)n_splits * n_kv_heads * n_tokens);
   bool clustered = false;
   if (clusters && decode_cluster_wanted(n_splits, n_tokens * n_kv_heads)) {
-    // clusters of larger blocks are harder to place: three buffers only for clusters of up to four blocks (8 splits
-    // of 4 sequences with three: 3.49 against 3.35 ms a step; 16 splits of 2 sequences: 3.44 against 3.38) and
-    // where all of the launch's clusters still run at once
+    // clusters of larger blocks are harder to place: three buffers of keys only for clusters of up to four blocks (8
+    // splits of 4 sequences with three: 3.59 against 3.35 ms a step; 16 splits of 2 sequences: 3.44 against 3.38)
+    // and where all of the launch's clusters still run at once
     if (stages > 2 && (n_splits > 4 || clusters_held(stages) < n_tokens * n_kv_heads)) stages = 2;
     clustered = clusters_held(stages) >= 1;
   }

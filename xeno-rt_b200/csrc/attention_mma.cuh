@@ -318,11 +318,13 @@ struct HeadColumnState {
 // (8 KB each, the boxes of a tile one after another), the 16-byte piece c of row r stored at piece
 // c ^ (r % 8).  Such a tile holds the whole cache block, also rows beyond the sequence, which may be
 // anything: masked keys' values are cleared in the registers (0 x NaN would poison the sum).
-template <int D_TILES, bool SWIZZLED = false>
-__device__ __forceinline__ void attend_16_keys_heads(HeadColumnState<D_TILES>& st, const uint32_t (*qb)[2],
+// `values_ready` is called once the weights are known and before the values' tile is read: a kernel whose
+// values land on a barrier of their own waits there; false (a bounded wait ran out) leaves the output as it was.
+template <int D_TILES, bool SWIZZLED = false, class ValuesReady>
+__device__ __forceinline__ bool attend_16_keys_heads(HeadColumnState<D_TILES>& st, const uint32_t (*qb)[2],
                                                      const unsigned char* ks_tile, const unsigned char* vs_tile,
                                                      int key_row, int key_abs, int key_lo, int key_hi, bool masked,
-                                                     int head_dim, float scale_log2) {
+                                                     int head_dim, float scale_log2, ValuesReady&& values_ready) {
   const int lane = threadIdx.x & 31, g = lane >> 2;
   const int row_bytes = tile_row_bytes(head_dim);
   float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // two chains of dependent MMAs
@@ -391,6 +393,7 @@ __device__ __forceinline__ void attend_16_keys_heads(HeadColumnState<D_TILES>& s
   }
   const uint32_t p_lo = transpose_8x8(pack_bf16(v[0], v[1]));  // keys 2t, 2t+1 of head g
   const uint32_t p_hi = transpose_8x8(pack_bf16(v[2], v[3]));  // keys 2t+8, 2t+9
+  if (!values_ready()) return false;
   // V^T as the A operand (transposed load): matrix j = keys (j / 2) * 8 .., dims dt * 16 + (j % 2) * 8 ..
   const int j = lane >> 3, r = lane & 7;
   const uint32_t v_base = SWIZZLED ? smem_addr(vs_tile + (key_row + (j >> 1) * 8 + r) * 128)
@@ -429,6 +432,16 @@ __device__ __forceinline__ void attend_16_keys_heads(HeadColumnState<D_TILES>& s
       }
     }
   }
+  return true;
+}
+
+template <int D_TILES, bool SWIZZLED = false>
+__device__ __forceinline__ void attend_16_keys_heads(HeadColumnState<D_TILES>& st, const uint32_t (*qb)[2],
+                                                     const unsigned char* ks_tile, const unsigned char* vs_tile,
+                                                     int key_row, int key_abs, int key_lo, int key_hi, bool masked,
+                                                     int head_dim, float scale_log2) {
+  attend_16_keys_heads<D_TILES, SWIZZLED>(st, qb, ks_tile, vs_tile, key_row, key_abs, key_lo, key_hi, masked, head_dim,
+                                          scale_log2, [] { return true; });
 }
 
 }  // namespace xrt
