@@ -82,7 +82,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   // (the heads are the grid's fastest dimension).  With the query tiles fastest, the last heads' long tiles started
   // when most multiprocessors were already idle: a prompt of 2,048 tokens is 512 blocks of 1 to 16 steps on 148
   // multiprocessors, 42 steps on the busiest that way against 33 this way (71.5 -> 61.2 us a layer).
-  const int q_index = gridDim.y - 1 - blockIdx.y, head0 = blockIdx.x * NH, seq = blockIdx.z;
+  // Of several prompts, every prompt's tiles at a query index come before any tile at a lower one (a tile beyond a
+  // shorter prompt's end leaves at once): the prompts are the grid's second dimension, the query tiles its slowest.
+  const int q_index = gridDim.z - 1 - blockIdx.z, head0 = blockIdx.x * NH, seq = blockIdx.y;
   const int slot = seq_slot[seq];
   const int tok0 = cu_seqlens[seq];
   const int n_new = cu_seqlens[seq + 1] - tok0;
@@ -398,7 +400,7 @@ XRT_EXPORT int xrt_attention_prefill_tcgen05(void* out, const void* q, const voi
     if (err != cudaSuccess) return (int)err;
     allowed = true;
   }
-  dim3 grid(n_heads, (max_new + xrt::FA_ROWS - 1) / xrt::FA_ROWS, n_seqs);
+  dim3 grid(n_heads, n_seqs, (max_new + xrt::FA_ROWS - 1) / xrt::FA_ROWS);
   // launched without programmatic dependent launch: a block needs a multiprocessor to itself, so nothing of it can
   // run beside the kernel before it, and the early launch was measured slower (28.2 against 27.8 ms a prompt of 2,048)
   xrt::attention_prefill_tcgen05_kernel<1><<<grid, 64 + 128, xrt::fa_smem_bytes(1), stream>>>(
