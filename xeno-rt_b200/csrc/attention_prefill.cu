@@ -27,8 +27,9 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
                          int n_heads, int n_kv_heads, int head_dim, float scale_log2, int window) {
   constexpr int D_TILES = HD_MAX / 8;
   extern __shared__ __align__(16) unsigned char smem[];
-  // later query tiles walk more keys: they are scheduled first
-  const int q_tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
+  // later query tiles walk more keys: they are scheduled first, the longest tiles of all heads and of all the step's
+  // prompts before any shorter one (heads are the grid's fastest dimension, query tiles its slowest)
+  const int q_tile = gridDim.z - 1 - blockIdx.z, head = blockIdx.x, seq = blockIdx.y;
   const int slot = seq_slot[seq];
   if (slot < 0) return;
   const int tok0 = cu_seqlens[seq];
@@ -143,7 +144,7 @@ int launch_prefill(__nv_bfloat16* out, const __nv_bfloat16* q, const __nv_bfloat
     if (err != cudaSuccess) return (int)err;
     smem_allowed = smem;
   }
-  dim3 grid((max_new + PRE_ROWS - 1) / PRE_ROWS, n_heads, n_seqs);
+  dim3 grid(n_heads, n_seqs, (max_new + PRE_ROWS - 1) / PRE_ROWS);
   kernel<<<grid, PRE_WARPS * 32, smem, stream>>>(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, block_table,
                                                 max_blocks, n_heads, n_kv_heads, head_dim,
                                                 scale * 1.4426950408889634f, window);
@@ -161,7 +162,7 @@ XRT_EXPORT int xrt_attention_prefill(void* out, const void* q, const void* k_poo
                                      const int* block_table, int max_blocks, int n_seqs, int max_new, int n_heads,
                                      int n_kv_heads, int head_dim, float scale, int window, cudaStream_t stream) {
   if (n_seqs < 0 || max_new < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return XRT_ERR_ARGUMENT;
-  if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256 || n_seqs > 65535 || n_heads > 65535) return XRT_ERR_UNSUPPORTED;
+  if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256 || n_seqs > 65535 || (max_new + xrt::PRE_ROWS - 1) / xrt::PRE_ROWS > 65535) return XRT_ERR_UNSUPPORTED;
   if (n_seqs == 0 || max_new == 0) return XRT_OK;
   auto* o = (__nv_bfloat16*)out;
   auto* qp = (const __nv_bfloat16*)q;
